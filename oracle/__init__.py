@@ -1,0 +1,163 @@
+"""ctypes front-end of the CPU checkers.  TEST INFRASTRUCTURE ONLY.
+
+`port` wraps liboracle.so (the C restatement, pto_oracle.c) and is always available; `ref` wraps
+_ref/libpto_ref.so (tile programs compiled against the reference's own CPU-simulation headers) and
+is None where that library was never built.  Nothing in the product package imports this module:
+only the tests, the smoke check and the benchmark's CPU-baseline leg do.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_i64 = ctypes.c_int64
+
+
+def _p(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def build(force=False):
+    """Compile liboracle.so (and _ref/libpto_ref.so when the reference tree is present)."""
+    so = os.path.join(_HERE, "liboracle.so")
+    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(os.path.join(_HERE, "pto_oracle.c")):
+        subprocess.check_call(["make", "-C", _HERE, "liboracle.so"], stdout=subprocess.DEVNULL)
+    ref_so = os.path.join(_HERE, "_ref", "libpto_ref.so")
+    if os.path.isdir("/root/reference/include/pto") and (force or not os.path.exists(ref_so)):
+        subprocess.check_call(["make", "-C", _HERE, "ref"], stdout=subprocess.DEVNULL)
+
+
+class _Lib:
+    """Thin numpy wrapper; `prefix` is 'pto_oracle_' (restatement) or 'pto_ref_' (reference build)."""
+
+    def __init__(self, path, prefix):
+        self.lib = ctypes.CDLL(path)
+        self.prefix = prefix
+        self.path = path
+
+    def _f(self, name):
+        return getattr(self.lib, self.prefix + name)
+
+    def has(self, name):
+        return hasattr(self.lib, self.prefix + name)
+
+    # -- vector ops
+    def tcvt_f32_f16(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape, np.uint16)
+        self._f("tcvt_f32_f16")(_p(x), _p(out), _i64(x.size))
+        return out.view(np.float16)
+
+    def tcvt_f32_bf16(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape, np.uint16)
+        self._f("tcvt_f32_bf16")(_p(x), _p(out), _i64(x.size))
+        return out  # raw bf16 bits
+
+    def tcvt_f32_i32(self, x, mode=1):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape, np.int32)
+        self._f("tcvt_f32_i32")(_p(x), _p(out), _i64(x.size), int(mode))
+        return out
+
+    def texp_f32(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty_like(x)
+        self._f("texp_f32")(_p(x), _p(out), _i64(x.size))
+        return out
+
+    def tgather(self, src0, idx):
+        src0 = np.ascontiguousarray(src0)
+        idx = np.ascontiguousarray(idx, np.int32)
+        assert src0.ndim == 2 and src0.itemsize in (2, 4)
+        out = np.empty(idx.shape, src0.dtype)
+        name = "tgather_f32" if src0.itemsize == 4 else "tgather_b16"
+        rc = self._f(name)(_p(src0), src0.shape[0], src0.shape[1], _p(idx), _p(out), _i64(idx.size))
+        if rc != 0:
+            raise ValueError(f"{self.prefix}{name}: unsupported shape {src0.shape}")
+        return out
+
+    def tgather_mask(self, src, pattern):
+        src = np.ascontiguousarray(src)
+        div = {1: 2, 2: 2, 3: 4, 4: 4, 5: 4, 6: 4, 7: 1}[int(pattern)]
+        out = np.empty(src.shape[0] * (src.shape[1] // div), src.dtype)
+        name = "tgather_mask_f32" if src.itemsize == 4 else "tgather_mask_b16"
+        rc = self._f(name)(_p(src), _p(out), src.shape[0], src.shape[1], int(pattern))
+        if rc != 0:
+            raise ValueError(f"{self.prefix}{name}: unsupported shape {src.shape}")
+        return out
+
+    def trowmax_f32(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape[0], np.float32)
+        rc = self._f("trowmax_f32")(_p(x), _p(out), x.shape[0], x.shape[1])
+        assert rc == 0
+        return out
+
+    def trowsum_f32(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape[0], np.float32)
+        rc = self._f("trowsum_f32")(_p(x), _p(out), x.shape[0], x.shape[1])
+        assert rc == 0
+        return out
+
+    # -- GEMM
+    def gemm_f16f32(self, a, b, b_layout):
+        """a: (m,k) fp16; b: (k,n) fp16 when b_layout == 0, (n,k) when 1.  Returns (m,n) fp32."""
+        a = np.ascontiguousarray(a, np.float16)
+        b = np.ascontiguousarray(b, np.float16)
+        m, k = a.shape
+        n = b.shape[1] if b_layout == 0 else b.shape[0]
+        c = np.empty((m, n), np.float32)
+        rc = self._f("gemm_f16f32")(_p(a), _p(b), _p(c), m, n, k, int(b_layout))
+        if rc != 0:
+            raise ValueError("gemm: unsupported shape")
+        return c
+
+    def gemm_f16f32_window(self, a, b, b_layout, r0, r1, c0, c1):
+        """Restatement only: computes C[r0:r1, c0:c1] of the full product and returns that window."""
+        a = np.ascontiguousarray(a, np.float16)
+        b = np.ascontiguousarray(b, np.float16)
+        m, k = a.shape
+        n = b.shape[1] if b_layout == 0 else b.shape[0]
+        c = np.zeros((m, n), np.float32) if (m * n <= (1 << 26)) else None
+        if c is None:
+            raise ValueError("window helper is for matrices up to 64M outputs")
+        rc = self._f("gemm_f16f32_window")(_p(a), _p(b), _p(c), m, n, k, int(b_layout), r0, r1, c0, c1)
+        assert rc == 0
+        return c[r0:r1, c0:c1].copy()
+
+    # -- attention (one head)
+    def attn_head_f16(self, q, k, v, causal, scale):
+        q = np.ascontiguousarray(q, np.float16)
+        k = np.ascontiguousarray(k, np.float16)
+        v = np.ascontiguousarray(v, np.float16)
+        o = np.empty(q.shape, np.float32)
+        rc = self._f("attn_head_f16")(_p(q), _p(k), _p(v), _p(o), q.shape[0], k.shape[0], q.shape[1], int(causal),
+                                      ctypes.c_float(scale))
+        if rc != 0:
+            raise ValueError("attn_head: unsupported shape")
+        return o
+
+    def fa_tiled_f16(self, q, k, v, causal, scale, tile_s1=256):
+        q = np.ascontiguousarray(q, np.float16)
+        k = np.ascontiguousarray(k, np.float16)
+        v = np.ascontiguousarray(v, np.float16)
+        o = np.empty(q.shape, np.float32)
+        rc = self._f("fa_tiled_f16")(_p(q), _p(k), _p(v), _p(o), q.shape[0], k.shape[0], q.shape[1], int(causal),
+                                     ctypes.c_float(scale), int(tile_s1))
+        assert rc == 0
+        return o
+
+
+def _load():
+    build()
+    port = _Lib(os.path.join(_HERE, "liboracle.so"), "pto_oracle_")
+    ref_path = os.path.join(_HERE, "_ref", "libpto_ref.so")
+    ref = _Lib(ref_path, "pto_ref_") if os.path.exists(ref_path) else None
+    return port, ref
+
+
+port, ref = _load()

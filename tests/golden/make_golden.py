@@ -1,0 +1,219 @@
+#!/usr/bin/env python3
+"""Regenerate the golden fixtures in this directory from the reference's own generator scripts.
+
+Run where the reference tree is available:
+
+    python tests/golden/make_golden.py [--reference /path/to/pto-isa]
+
+Each reference `gen_data.py` is loaded as a module *from where it lies* (nothing is copied), its
+generator function is called with the case list its own `__main__` block uses (restated below with
+the file:line it comes from, because those lists live under `if __name__ == "__main__"` and two of
+the scripts would otherwise try to create directories inside the reference tree), in the same
+order and after the same `np.random.seed(...)`, so the bytes are the ones the reference's test
+drivers would feed to its kernels.  Inputs and goldens of the cases on the GEMM / attention /
+vector hot path are packed into compressed .npz files here.
+
+The fixtures travel with the repository; the reference tree does not have to exist where the
+tests run.
+"""
+import argparse
+import importlib.util
+import os
+import sys
+import tempfile
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def load(path, name):
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)  # runs the module-level np.random.seed(...)
+    return mod
+
+
+def read(path, dtype, shape=None):
+    a = np.fromfile(path, dtype=dtype)
+    return a.reshape(shape) if shape is not None else a
+
+
+def in_case_dir(tmp, name):
+    d = os.path.join(tmp, name)
+    os.makedirs(d, exist_ok=True)
+    os.chdir(d)
+    return d
+
+
+def gen_tcvt(ref, tmp, out):
+    # tests/cpu/st/testcase/tcvt/gen_data.py:62-72 (case list), :20-38 (generator)
+    mod = load(os.path.join(ref, "tests/cpu/st/testcase/tcvt/gen_data.py"), "ref_tcvt_gen")
+    P = mod.TCvtParams
+    rint = "RoundMode::CAST_RINT"
+    cases = [
+        P(np.float32, np.int32, 128, 128, rint), P(np.int32, np.float32, 256, 64, rint),
+        P(np.float32, np.int16, 16, 32, rint), P(np.float32, np.int32, 32, 512, rint),
+        P(np.int16, np.int32, 2, 512, rint), P(np.float32, np.int32, 4, 4096, rint),
+        P(np.int16, np.float32, 64, 64, rint), P(np.float32, np.float16, 64, 64, rint),
+        P(np.float16, np.uint8, 64, 64, rint),
+    ]
+    keep = {}
+    for i, p in enumerate(cases, start=1):
+        d = in_case_dir(tmp, f"tcvt_case{i}")
+        mod.gen_golden(p)
+        if i in (1, 4, 6, 8):  # f32->i32 (three shapes) and f32->f16
+            keep[f"case{i}_src"] = read(os.path.join(d, "x1_gm.bin"), p.srctype, (p.m, p.n))
+            keep[f"case{i}_golden"] = read(os.path.join(d, "golden.bin"), p.dsttype, (p.m, p.n))
+    np.savez_compressed(os.path.join(out, "tcvt.npz"), **keep)
+
+
+def gen_tgather(ref, tmp, out):
+    # tests/cpu/st/testcase/tgather/gen_data.py:132-173 (case list), :92-129 (generator)
+    mod = load(os.path.join(ref, "tests/cpu/st/testcase/tgather/gen_data.py"), "ref_tgather_gen")
+    M, D = mod.TGatherParamsMasked, mod.TGatherParams1D
+    f32, f16 = np.float32, np.half
+    cases = [
+        M("float_P0101", f32, f32, 4, 64, 1), M("float_P1010", f32, f32, 7, 1024, 2),
+        M("float_P0001", f32, f32, 3, 1056, 3), M("float_P0010", f32, f32, 4, 128, 4),
+        M("float_P0100", f32, f32, 5, 256, 5), M("float_P1000", f32, f32, 6, 288, 6),
+        M("float_P1111", f32, f32, 7, 320, 7),
+        M("half_P0101", f16, f16, 5, 128, 1), M("half_P1010", f16, f16, 7, 1024, 2),
+        M("half_P0001", f16, f16, 3, 1056, 3), M("half_P0100", f16, f16, 5, 256, 5),
+        M("half_P1000", f16, f16, 6, 288, 6),
+        M("U16_P0101", np.uint16, np.uint16, 5, 128, 1), M("U16_P1010", np.uint16, np.uint16, 7, 1024, 2),
+        M("I16_P0001", np.int16, np.int16, 3, 1056, 3), M("I16_P0010", np.int16, np.int16, 4, 128, 4),
+        M("U32_P0100", np.uint32, np.uint32, 5, 256, 5), M("I32_P1000", np.int32, np.int32, 6, 288, 6),
+        M("I32_P1111", np.int32, np.int32, 7, 320, 7),
+        D("1D_float_32x1024_16x64", f32, 32, 1024, 16, 64), D("1D_int32_32x512_16x256", np.int32, 32, 512, 16, 256),
+        D("1D_half_16x1024_16x128", np.float16, 16, 1024, 16, 128), D("1D_int16_32x256_32x64", np.int16, 32, 256, 32, 64),
+    ]
+    keep = {}
+    for p in cases:
+        d = in_case_dir(tmp, "tgather_" + p.testname)
+        mod.original_dir = tmp  # the generator chdir()s back to this global after a masked case
+        mod.gen_golden_data(p)
+        if isinstance(p, M):
+            keep[f"{p.testname}__src"] = read(os.path.join(d, "x1_gm.bin"), p.src_type, (p.row, p.col))
+            keep[f"{p.testname}__golden"] = read(os.path.join(d, "golden.bin"), p.dst_type)
+            keep[f"{p.testname}__pattern"] = np.array(p.pattern)
+        else:
+            keep[f"{p.testname}__src0"] = read(os.path.join(d, "src0.bin"), p.src_type, (p.src_row, p.src_col))
+            keep[f"{p.testname}__idx"] = read(os.path.join(d, "src1.bin"), np.int32, (p.dst_row, p.dst_col))
+            keep[f"{p.testname}__golden"] = read(os.path.join(d, "golden.bin"), p.src_type, (p.dst_row, p.dst_col))
+    np.savez_compressed(os.path.join(out, "tgather.npz"), **keep)
+
+
+def gen_tmatmul(ref, tmp, out):
+    # tests/cpu/st/testcase/tmatmul/gen_data.py:86-96 (case list), :34-59 (generator)
+    mod = load(os.path.join(ref, "tests/cpu/st/testcase/tmatmul/gen_data.py"), "ref_tmatmul_gen")
+    P = mod.tmatmulParams
+    cases = [
+        ("case1", P(np.float16, np.float16, np.float32, 40, 50, 60, False)),
+        ("case2", P(np.int8, np.int8, np.int32, 6, 7, 8, False)),
+        ("case3", P(np.float16, np.float16, np.float32, 128, 128, 64, False, repeats=5)),
+        ("case4", P(np.float32, np.float32, np.float32, 120, 110, 50, False)),
+    ]
+    keep = {}
+    for name, p in cases:
+        d = in_case_dir(tmp, "tmatmul_" + name)
+        mod.gen_golden_data(name, p)
+        if name == "case2":
+            continue
+        keep[f"{name}_a"] = read(os.path.join(d, "x1_gm.bin"), p.atype, (p.repeats, p.m, p.k))
+        keep[f"{name}_b"] = read(os.path.join(d, "x2_gm.bin"), p.btype, (p.repeats, p.k, p.n))
+        keep[f"{name}_golden"] = read(os.path.join(d, "golden.bin"), p.ctype, (p.m, p.n))
+    np.savez_compressed(os.path.join(out, "tmatmul.npz"), **keep)
+
+
+def gen_rowops(ref, tmp, out):
+    keep = {}
+    # tests/cpu/st/testcase/trowmax/gen_data.py:79-85 (case list), :17-35 (generator)
+    mod = load(os.path.join(ref, "tests/cpu/st/testcase/trowmax/gen_data.py"), "ref_trowmax_gen")
+    P = mod.TRowmaxParams
+    for i, p in enumerate([P(np.float32, 64, 64, 64, 64, 64, 64), P(np.float16, 64, 64, 64, 64, 64, 64),
+                           P(np.float16, 161, 161, 32, 32, 161, 161), P(np.float32, 77, 81, 32, 16, 77, 81),
+                           P(np.float32, 32, 32, 32, 16, 32, 32)]):
+        in_case_dir(tmp, f"trowmax_{i}")
+        src, golden = mod.gen_golden_data_trowmax("", p)
+        keep[f"trowmax{i}_src"] = src
+        keep[f"trowmax{i}_golden"] = golden
+        keep[f"trowmax{i}_valid"] = np.array([min(p.tile_row, p.valid_row), min(p.tile_col, p.valid_col)])
+    # tests/cpu/st/testcase/trowsum/gen_data.py:69-72 (case list), :17-43 (generator)
+    mod = load(os.path.join(ref, "tests/cpu/st/testcase/trowsum/gen_data.py"), "ref_trowsum_gen")
+    P = mod.trowsumParams
+    for i, p in enumerate([P(np.float32, 64, 64, 64, 64, 64, 64), P(np.float16, 16, 256, 16, 256, 16, 256)]):
+        in_case_dir(tmp, f"trowsum_{i}")
+        _, src, golden = mod.gen_golden_data_trowsum("", p)
+        keep[f"trowsum{i}_src"] = src
+        keep[f"trowsum{i}_golden"] = golden[:, 0].copy()
+    # tests/cpu/st/testcase/texp/gen_data.py:79-85 (case list), :17-41 (generator)
+    mod = load(os.path.join(ref, "tests/cpu/st/testcase/texp/gen_data.py"), "ref_texp_gen")
+    P = mod.TExpParams
+    for i, p in enumerate([P(np.float32, 64, 64, 64, 64, 64, 64), P(np.float16, 64, 64, 64, 64, 64, 64),
+                           P(np.float16, 32, 32, 32, 32, 32, 32), P(np.float32, 32, 32, 32, 32, 32, 32),
+                           P(np.float32, 32, 16, 32, 16, 32, 16)]):
+        in_case_dir(tmp, f"texp_{i}")
+        _, src, golden = mod.gen_golden_data_texp("", p)
+        keep[f"texp{i}_src"] = src
+        keep[f"texp{i}_golden"] = golden
+    np.savez_compressed(os.path.join(out, "rowops.npz"), **keep)
+
+
+def gen_attention(ref, tmp, out):
+    keep = {}
+    # tests/cpu/st/testcase/tflashattn/gen_data.py:62-73: 64 x 32 fp32 head, float64 golden
+    mod = load(os.path.join(ref, "tests/cpu/st/testcase/tflashattn/gen_data.py"), "ref_tflashattn_gen")
+    d = os.path.join(tmp, "tflashattn_case1")
+    mod.gen_case(d, seq_len=64, head_dim=32, seed=20251220, init_scale=0.02)
+    for key, f in (("q", "x1_gm.bin"), ("k", "x2_gm.bin"), ("v", "x3_gm.bin"), ("golden", "golden.bin")):
+        keep[f"tflashattn_{key}"] = read(os.path.join(d, f), np.float32, (64, 32))
+    # kernels/manual/common/flash_atten/scripts/gen_data.py:32-149: the streaming-softmax NumPy model of
+    # the flash-attention kernel (TILE_S1 = 256, fp16 P, fp32 O), seeded np.random.seed(7) at import.
+    # S1 = 512 gives two key tiles: with a single tile the generator never divides by the row sum (:141-147).
+    mod = load(os.path.join(ref, "kernels/manual/common/flash_atten/scripts/gen_data.py"), "ref_fa_gen")
+    for name, s0, s1, causal in (("fa_nc_128x512", 128, 512, False), ("fa_causal_128x512", 128, 512, True)):
+        d = os.path.join(tmp, name)
+        os.makedirs(d, exist_ok=True)
+        mod.gen_case(d, s0, s1, 128, 128, 256, causal)
+        keep[f"{name}_q"] = read(os.path.join(d, "q.bin"), np.float16, (s0, 128))
+        keep[f"{name}_k"] = read(os.path.join(d, "kt.bin"), np.float16, (s1, 128))  # K rows: s1 x head
+        keep[f"{name}_v"] = read(os.path.join(d, "v.bin"), np.float16, (s1, 128))
+        keep[f"{name}_o"] = read(os.path.join(d, "o.bin"), np.float32, (s0, 128))
+    np.savez_compressed(os.path.join(out, "attention.npz"), **keep)
+
+
+def gen_gemm(ref, tmp, out):
+    # kernels/manual/a2a3/gemm_performance/scripts/gen_data.py:18-45: A m x k and B k x n fp16 drawn
+    # uniform(-5, 5) after np.random.seed(19), golden = fp32 np.matmul, B written transposed (n x k, the
+    # Layout::DN operand).  The reference calls it for 6144^3 (:62-66); the same generator is called here for
+    # a 128 x 256 x 192 problem (m, n multiples of the 128 x 256 base tile, k of the 64 step).
+    mod = load(os.path.join(ref, "kernels/manual/a2a3/gemm_performance/scripts/gen_data.py"), "ref_gemm_gen")
+    m, k, n = 128, 192, 256
+    d = in_case_dir(tmp, "gemm_small")
+    mod.gen_golden_data(mod.GemmParams(np.float16, np.float16, np.float32, m, k, n, False, np.float32))
+    np.savez_compressed(os.path.join(out, "gemm.npz"),
+                        a=read(os.path.join(d, "input/x1_gm.bin"), np.float16, (m, k)),
+                        b_dn=read(os.path.join(d, "input/x2_gm.bin"), np.float16, (n, k)),
+                        golden=read(os.path.join(d, "output/golden.bin"), np.float32, (m, n)))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    cwd = os.getcwd()
+    with tempfile.TemporaryDirectory() as tmp:
+        try:
+            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm):
+                os.chdir(tmp)
+                fn(args.reference, tmp, HERE)
+        finally:
+            os.chdir(cwd)
+    for f in sorted(os.listdir(HERE)):
+        if f.endswith(".npz"):
+            print(f, os.path.getsize(os.path.join(HERE, f)))
+
+
+if __name__ == "__main__":
+    sys.exit(main())

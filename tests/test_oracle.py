@@ -1,0 +1,234 @@
+"""The CPU restatement (oracle/pto_oracle.c) against (1) the golden vectors produced by the reference's
+own generator scripts and (2) the reference's CPU-simulation headers compiled as oracle/_ref/libpto_ref.so.
+
+Comparison rule for the reference's goldens is its own `ResultCmp` (tests/common/test_common.h:211-300):
+an element is wrong when |diff| > eps and |diff / expected| > eps; a case passes while the number of
+wrong elements is <= size * eps.  eps values are the ones the reference's test mains use.
+"""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+
+port, ref = oracle.port, oracle.ref
+needs_ref = pytest.mark.skipif(ref is None, reason="reference CPU-simulation build (oracle/_ref) not present")
+
+
+def result_cmp(golden, actual, eps):
+    g = np.asarray(golden, np.float64).ravel()
+    a = np.asarray(actual, np.float64).ravel()
+    diff = np.abs(g - a)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        rel = np.where(g != 0, diff / np.abs(g), np.inf)
+    bad = (diff > eps) & (rel > eps)
+    return int(bad.sum()) <= g.size * eps
+
+
+def load(golden_dir, name):
+    return np.load(os.path.join(golden_dir, name))
+
+
+# ------------------------------------------------------------------ golden vectors (reference generators)
+
+def test_tcvt_golden(golden_dir):
+    z = load(golden_dir, "tcvt.npz")
+    # tcvt case8: fp32 -> fp16 64x64, exact (tests/cpu/st/testcase/tcvt/main.cpp:126-129)
+    assert np.array_equal(port.tcvt_f32_f16(z["case8_src"]).view(np.uint16), z["case8_golden"].view(np.uint16))
+    for c in ("case1", "case4", "case6"):  # fp32 -> int32, CAST_RINT
+        assert np.array_equal(port.tcvt_f32_i32(z[f"{c}_src"], 1), z[f"{c}_golden"])
+
+
+def test_tgather_golden(golden_dir):
+    z = load(golden_dir, "tgather.npz")
+    names = sorted({k.split("__")[0] for k in z.files})
+    assert len(names) == 23
+    for n in names:
+        if n.startswith("1D_"):
+            src0, idx, g = z[f"{n}__src0"], z[f"{n}__idx"], z[f"{n}__golden"]
+            bits = src0.view(np.uint32 if src0.itemsize == 4 else np.uint16)
+            out = port.tgather(bits.view(np.float32) if src0.itemsize == 4 else bits, idx)
+            assert np.array_equal(out.view(bits.dtype), g.view(bits.dtype)), n
+        else:
+            src, g, pat = z[f"{n}__src"], z[f"{n}__golden"], int(z[f"{n}__pattern"])
+            bits = src.view(np.uint32 if src.itemsize == 4 else np.uint16)
+            out = port.tgather_mask(bits.view(np.float32) if src.itemsize == 4 else bits, pat)
+            assert np.array_equal(out.view(bits.dtype), g.view(bits.dtype)), n
+
+
+def test_rowops_golden(golden_dir):
+    z = load(golden_dir, "rowops.npz")
+    for i in (0, 3, 4):  # fp32 TROWMAX cases
+        src, g, (vr, vc) = z[f"trowmax{i}_src"], z[f"trowmax{i}_golden"], z[f"trowmax{i}_valid"]
+        assert np.array_equal(port.trowmax_f32(src[:vr, :vc]), g)
+    src, g = z["trowsum0_src"], z["trowsum0_golden"]  # fp32 TROWSUM 64x64, eps 1e-3
+    assert result_cmp(g, port.trowsum_f32(src), 1e-3)
+    for i in (0, 3, 4):  # fp32 TEXP cases, eps 1e-3
+        assert result_cmp(z[f"texp{i}_golden"], port.texp_f32(z[f"texp{i}_src"]), 1e-3)
+
+
+def test_tmatmul_golden(golden_dir):
+    z = load(golden_dir, "tmatmul.npz")
+    import ctypes
+    P = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    # case1: 40x50x60 fp16 -> fp32
+    a, b, g = z["case1_a"][0], z["case1_b"][0], z["case1_golden"]
+    c = np.empty(g.shape, np.float32)
+    port.lib.pto_oracle_tmatmul_f16f32(P(np.ascontiguousarray(a)), P(np.ascontiguousarray(b)), P(c), 40, 50, 60)
+    assert result_cmp(g, c, 1e-3)
+    # case3: split-K, five 128x128x64 products accumulated == one GEMM with k = 5*128 in 64-wide steps
+    a = np.concatenate(list(z["case3_a"]), axis=1)  # (128, 640)
+    b = np.concatenate(list(z["case3_b"]), axis=0)  # (640, 64)
+    c = np.zeros((128, 64), np.float32)
+    assert port.lib.pto_oracle_gemm_f16f32_window(P(a), P(b), P(c), 128, 64, 640, 0, 0, 128, 0, 64) == 0
+    assert result_cmp(z["case3_golden"], c, 1e-3)
+    # case4: 120x110x50 fp32
+    a, b, g = z["case4_a"][0], z["case4_b"][0], z["case4_golden"]
+    c = np.empty(g.shape, np.float32)
+    port.lib.pto_oracle_tmatmul_f32(P(np.ascontiguousarray(a)), P(np.ascontiguousarray(b)), P(c), 120, 110, 50)
+    assert result_cmp(g, c, 1e-3)
+
+
+def test_gemm_golden(golden_dir):
+    # generator of kernels/manual/a2a3/gemm_performance (B handed over as n x k); kernel self-check eps 1e-3
+    z = load(golden_dir, "gemm.npz")
+    c = port.gemm_f16f32(z["a"], z["b_dn"], 1)
+    assert result_cmp(z["golden"], c, 1e-3)
+    # same product with B given k x n
+    c2 = port.gemm_f16f32(z["a"], np.ascontiguousarray(z["b_dn"].T), 0)
+    assert np.array_equal(c, c2)
+
+
+def test_attention_golden(golden_dir):
+    z = load(golden_dir, "attention.npz")
+    import ctypes
+    P = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    # reference unit test: 64x32 fp32 head against a float64 model, eps 2e-4 (tflashattn/main.cpp:42-44)
+    q, k, v, g = (np.ascontiguousarray(z[f"tflashattn_{n}"]) for n in ("q", "k", "v", "golden"))
+    o = np.empty_like(g)
+    port.lib.pto_oracle_attn_head_f32_plain(P(q), P(k), P(v), P(o), 64, 32)
+    assert result_cmp(g, o, 2e-4)
+    # streaming-softmax model of the flash-attention kernel (TILE_S1 = 256), kernel self-check eps 1e-3
+    scale = 1.0 / np.sqrt(128.0)
+    for name, causal in (("fa_nc_128x512", 0), ("fa_causal_128x512", 1)):
+        q, k, v, g = (z[f"{name}_{n}"] for n in ("q", "k", "v", "o"))
+        o = port.fa_tiled_f16(q, k, v, causal, scale, 256)
+        assert result_cmp(g, o, 1e-3), name
+        assert np.abs(o - g).max() < 2e-3 * max(1.0, np.abs(g).max()), name
+        o_plain = port.attn_head_f16(q, k, v, causal, scale)
+        assert result_cmp(g, o_plain, 1e-3), name
+
+
+# ------------------------------------------------------------------ bit-exact against the reference build
+
+def _rng(seed):
+    return np.random.default_rng(seed)
+
+
+@needs_ref
+def test_tcvt_matches_reference_bits():
+    r = _rng(1)
+    special = np.array([0, -0.0, np.inf, -np.inf, np.nan, 65504, 65520, 65519.99, 1e-8, 6e-8, 5.96e-8, 2.98e-8,
+                        2.9802322e-8, 3e-8, 6.1e-5, 6.1035156e-5, 1e5, -1e5, 1e-45], np.float32)
+    x = np.concatenate([r.standard_normal(1 << 18).astype(np.float32), special,
+                        r.integers(0, 2 ** 32, 1 << 18, dtype=np.uint32).view(np.float32)])
+    assert np.array_equal(port.tcvt_f32_f16(x).view(np.uint16), ref.tcvt_f32_f16(x).view(np.uint16))
+    assert np.array_equal(port.tcvt_f32_bf16(x), ref.tcvt_f32_bf16(x))
+    xi = (r.standard_normal(4096) * 1000).astype(np.float32)
+    xi[:8] = [0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 3.5, -3.5]
+    for mode in range(1, 7):
+        assert np.array_equal(port.tcvt_f32_i32(xi, mode), ref.tcvt_f32_i32(xi, mode)), mode
+
+
+@needs_ref
+def test_bf16_rne_bit_trick():
+    # the reference has no bf16 case; pin round-to-nearest-even on ties and near-ties with the integer identity
+    r = _rng(2)
+    u = r.integers(0, 2 ** 32, 1 << 16, dtype=np.uint32)
+    u[:4096] = (u[:4096] & 0xFFFF0000) | 0x8000  # exact ties
+    u[4096:8192] = (u[4096:8192] & 0xFFFF0000) | 0x7FFF
+    u[8192:12288] = (u[8192:12288] & 0xFFFF0000) | 0x8001
+    x = u.view(np.float32)
+    finite = np.isfinite(x)
+    want = ((u.astype(np.uint64) + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    got = ref.tcvt_f32_bf16(x)
+    assert np.array_equal(got[finite], want[finite])
+    assert np.array_equal(port.tcvt_f32_bf16(x), got)
+
+
+@needs_ref
+def test_vector_ops_match_reference_bits():
+    r = _rng(3)
+    x = (r.standard_normal(50000) * 4).astype(np.float32)
+    assert np.array_equal(port.texp_f32(x), ref.texp_f32(x))
+    m = r.standard_normal((37, 1000)).astype(np.float32)
+    assert np.array_equal(port.trowmax_f32(m), ref.trowmax_f32(m))
+    assert np.array_equal(port.trowsum_f32(m), ref.trowsum_f32(m))
+    src = r.standard_normal((32, 1024)).astype(np.float32)
+    idx = r.integers(-100, 32 * 1024 + 100, 5000).astype(np.int32)  # includes negative / too-large -> 0
+    assert np.array_equal(port.tgather(src, idx), ref.tgather(src, idx))
+    s16 = r.integers(0, 65536, (16, 1024)).astype(np.uint16)
+    idx = r.integers(-5, 16 * 1024 + 5, 3000).astype(np.int32)
+    assert np.array_equal(port.tgather(s16, idx), ref.tgather(s16, idx))
+    for pat in range(1, 8):
+        s = r.standard_normal((64, 256)).astype(np.float32)
+        assert np.array_equal(port.tgather_mask(s, pat), ref.tgather_mask(s, pat))
+        s = r.integers(0, 65536, (16, 64)).astype(np.uint16)
+        assert np.array_equal(port.tgather_mask(s, pat), ref.tgather_mask(s, pat))
+
+
+@needs_ref
+@pytest.mark.parametrize("b_layout", [0, 1])
+def test_gemm_matches_reference_bits(b_layout):
+    r = _rng(4 + b_layout)
+    m, n, k = 256, 512, 320
+    a = r.uniform(-1, 1, (m, k)).astype(np.float16)
+    b = r.uniform(-1, 1, (k, n) if b_layout == 0 else (n, k)).astype(np.float16)
+    assert np.array_equal(port.gemm_f16f32(a, b, b_layout), ref.gemm_f16f32(a, b, b_layout))
+
+
+@needs_ref
+def test_tmatmul_unit_cases_match_reference_bits(golden_dir):
+    import ctypes
+    P = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    z = load(golden_dir, "tmatmul.npz")
+    a, b = np.ascontiguousarray(z["case1_a"][0]), np.ascontiguousarray(z["case1_b"][0])
+    c1 = np.empty((40, 60), np.float32)
+    c2 = np.empty((40, 60), np.float32)
+    assert ref.lib.pto_ref_tmatmul_case(1, P(a), P(b), P(c1)) == 0
+    port.lib.pto_oracle_tmatmul_f16f32(P(a), P(b), P(c2), 40, 50, 60)
+    assert np.array_equal(c1, c2)
+    assert result_cmp(z["case1_golden"], c1, 1e-3)
+
+
+@needs_ref
+@pytest.mark.parametrize("shape", [(128, 128, 128), (128, 512, 128), (256, 256, 128), (128, 256, 64)])
+@pytest.mark.parametrize("causal", [0, 1])
+def test_attention_matches_reference_bits(shape, causal):
+    s0, s1, d = shape
+    r = _rng(10 + s1 + causal)
+    q = (r.standard_normal((s0, d)) / np.sqrt(np.sqrt(d))).astype(np.float16)
+    k = (r.standard_normal((s1, d)) / np.sqrt(np.sqrt(d))).astype(np.float16)
+    v = r.standard_normal((s1, d)).astype(np.float16)
+    scale = 1.0 / np.sqrt(d)
+    o_ref = ref.attn_head_f16(q, k, v, causal, scale)
+    assert np.array_equal(port.attn_head_f16(q, k, v, causal, scale), o_ref)
+    # the streaming recurrence agrees with the plain sequence to fp32 rounding
+    o_t = port.fa_tiled_f16(q, k, v, causal, scale, 128)
+    assert np.abs(o_t - o_ref).max() <= 2e-3 * max(np.abs(o_ref).max(), 1e-3)
+
+
+@needs_ref
+def test_reference_unit_test_kernel(golden_dir):
+    """The unmodified reference test kernel (64x32 fp32 head) against its golden and the restatement."""
+    import ctypes
+    P = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    z = load(golden_dir, "attention.npz")
+    q, k, v, g = (np.ascontiguousarray(z[f"tflashattn_{n}"]) for n in ("q", "k", "v", "golden"))
+    o1 = np.empty_like(g)
+    o2 = np.empty_like(g)
+    assert ref.lib.pto_ref_tflashattn_64x32(P(q), P(k), P(v), P(o1)) == 0
+    port.lib.pto_oracle_attn_head_f32_plain(P(q), P(k), P(v), P(o2), 64, 32)
+    assert result_cmp(g, o1, 2e-4)
+    assert np.array_equal(o1, o2)
