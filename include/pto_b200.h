@@ -1,0 +1,152 @@
+/*
+ * pto_b200.h - C ABI of libpto_b200.so, the B200 (sm_100a) backend for the PTO tile-ISA hot path:
+ * fp16 GEMM, flash-attention forward and the vector tile ops (TCVT, TGATHER, TROWMAX, TROWSUM, TEXP, ...).
+ *
+ * Conventions (the same as the reference's only FFI, `call_kernel`, demos/torch_jit/gemm/gemm_kernel.cpp:259-262
+ * and demos/torch_jit/flash_atten/fa_kernel.cpp:1017-1037; paths are relative to the reference root):
+ *   - plain pointers and sizes only; pointers are DEVICE pointers unless the function name ends in `_host`;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream); work is enqueued
+ *     asynchronously and the caller synchronises, exactly like the reference launchers
+ *     (kernels/manual/a2a3/gemm_performance/main.cpp:49-52);
+ *   - no allocation of caller-visible buffers: outputs and workspaces are caller-provided;
+ *   - every function returns an int status (0 = ok); `pto_b200_last_error()` gives the text of the
+ *     last failure on the calling thread.  The `call_kernel`-shaped shims return void like the
+ *     reference's and leave their status in `pto_b200_last_status()`.
+ * The library never falls back to a CPU path: without a usable sm_100 device every call fails.
+ */
+#ifndef PTO_B200_H
+#define PTO_B200_H
+
+#include <stdbool.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PTO_B200_OK 0
+#define PTO_B200_ERR_BAD_ARGUMENT 1
+#define PTO_B200_ERR_UNSUPPORTED_SHAPE 2
+#define PTO_B200_ERR_CUDA 3
+#define PTO_B200_ERR_DEVICE_WAIT_TIMEOUT 4
+#define PTO_B200_ERR_TOO_LARGE 5
+
+/* RoundMode values of the reference (include/pto/common/type.hpp:167-176). */
+#define PTO_B200_CAST_RINT 1
+#define PTO_B200_CAST_ROUND 2
+#define PTO_B200_CAST_FLOOR 3
+#define PTO_B200_CAST_CEIL 4
+#define PTO_B200_CAST_TRUNC 5
+#define PTO_B200_CAST_ODD 6
+
+/* MaskPattern values of the reference (include/pto/common/type.hpp:95-106). */
+#define PTO_B200_P0101 1
+#define PTO_B200_P1010 2
+#define PTO_B200_P0001 3
+#define PTO_B200_P0010 4
+#define PTO_B200_P0100 5
+#define PTO_B200_P1000 6
+#define PTO_B200_P1111 7
+
+/* Elementwise operators for pto_b200_tbinary_f32 / pto_b200_tscalar_f32 / pto_b200_trowexpand_f32. */
+#define PTO_B200_OP_ADD 0
+#define PTO_B200_OP_SUB 1
+#define PTO_B200_OP_MUL 2
+#define PTO_B200_OP_DIV 3
+#define PTO_B200_OP_MAX 4
+#define PTO_B200_OP_MIN 5
+
+/* ---- library state ------------------------------------------------------------------------------ */
+
+/* ABI version of this header. */
+int pto_b200_version(void);
+/* Text of the last error raised on the calling thread ("" if none). */
+const char *pto_b200_last_error(void);
+/* Status left by the last void-returning `call_kernel`-shaped shim on the calling thread. */
+int pto_b200_last_status(void);
+/* Reads (and clears) the device-side status record that kernels with bounded waits report into.
+ * Synchronises `stream`.  Returns 0, or PTO_B200_ERR_DEVICE_WAIT_TIMEOUT if a kernel gave up on a wait. */
+int pto_b200_device_status(void *stream);
+
+/* ---- vector tile ops ---------------------------------------------------------------------------- */
+
+/* TCVT fp32 -> fp16 / bf16 over n contiguous elements: IEEE round-to-nearest-even, overflow to infinity,
+ * NaN quieted.  Replaces TCVT(dst, src, RoundMode) of include/pto/common/pto_instr.hpp:864-879 for
+ * float->float pairs (CPU semantics: include/pto/cpu/TCvt.hpp:76-81, where the round mode is ignored). */
+int pto_b200_tcvt_f32_f16(const float *src, uint16_t *dst, int64_t n, void *stream);
+int pto_b200_tcvt_f32_bf16(const float *src, uint16_t *dst, int64_t n, void *stream);
+/* TCVT fp32 -> int32 with a round mode (include/pto/cpu/TCvt.hpp:28-63, :72-75). */
+int pto_b200_tcvt_f32_i32(const float *src, int32_t *dst, int64_t n, int round_mode, void *stream);
+
+/* TGATHER index form, dst[i] = src0_flat[idx[i]], an index < 0 or >= src_numel gives 0.
+ * Replaces TGATHER(dst, src0, idx) of include/pto/common/pto_instr.hpp:800-806
+ * (include/pto/cpu/TGather.hpp:68-100).  `elem_bytes` is 4 or 2 (bit copy). */
+int pto_b200_tgather(const void *src0, int64_t src_numel, const int32_t *idx, void *dst, int64_t n, int elem_bytes,
+                     void *stream);
+/* TGATHER mask form: keeps the columns selected by a MaskPattern, packed contiguously
+ * (include/pto/common/pto_instr.hpp:824-830, include/pto/cpu/TGather.hpp:102-129). */
+int pto_b200_tgather_mask(const void *src, void *dst, int rows, int cols, int pattern, int elem_bytes, void *stream);
+
+/* TROWMAX / TROWSUM: dst[r] = max / sum over the `cols` valid columns of row r; rows are `row_stride`
+ * elements apart (include/pto/common/pto_instr.hpp:990, :942; include/pto/cpu/TRowMax.hpp:20-59,
+ * TRowSum.hpp:17-63).  The sum is a tree reduction in fp32 (the reference sums sequentially). */
+int pto_b200_trowmax_f32(const float *src, float *dst, int rows, int cols, int64_t row_stride, void *stream);
+int pto_b200_trowsum_f32(const float *src, float *dst, int rows, int cols, int64_t row_stride, void *stream);
+/* TEXP (include/pto/common/pto_instr.hpp:1129, include/pto/cpu/TExp.hpp:22-60). */
+int pto_b200_texp_f32(const float *src, float *dst, int64_t n, void *stream);
+/* TADD / TSUB / TMUL / TDIV / TMAX / TMIN: dst = a op b (include/pto/common/pto_instr.hpp:56-120). */
+int pto_b200_tbinary_f32(const float *a, const float *b, float *dst, int64_t n, int op, void *stream);
+/* TADDS / TMULS / ...: dst = a op scalar (include/pto/common/pto_instr.hpp:1161, :1188). */
+int pto_b200_tscalar_f32(const float *a, float scalar, float *dst, int64_t n, int op, void *stream);
+/* TROWEXPANDSUB / MUL / DIV / ADD / MAX / MIN: dst[r, c] = a[r, c] op row_scalar[r]
+ * (include/pto/common/pto_instr.hpp:1057-1073, include/pto/cpu/TRowExpandOp.hpp:38-76). */
+int pto_b200_trowexpand_f32(const float *a, const float *row_scalar, float *dst, int rows, int cols, int op,
+                            void *stream);
+
+/* ---- GEMM --------------------------------------------------------------------------------------- */
+
+/* C[m x n] fp32 = A[m x k] fp16 * B, fp32 accumulation.  b_layout 0: B is k x n row-major (Layout::ND);
+ * 1: B is stored n x k row-major, the Layout::DN view the reference kernel uses for its second operand.
+ * Replaces LaunchGEMME2E<T>(out, src0, src1, stream) of
+ * kernels/manual/a2a3/gemm_performance/gemm_performance_kernel.cpp:243-264 for any m, n, k
+ * (k a multiple of 8; n a multiple of 8 when b_layout is 0). */
+int pto_b200_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
+                         void *stream);
+/* `batch` independent problems of the same shape, operands `*_stride` elements apart. */
+int pto_b200_gemm_f16f32_batched(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
+                                 int batch, int64_t a_stride, int64_t b_stride, int64_t c_stride, void *stream);
+/* Same product with HOST buffers: copies A and B in, runs the kernel, copies C out, synchronises. */
+int pto_b200_gemm_f16f32_host(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout);
+
+/* ---- flash attention forward -------------------------------------------------------------------- */
+
+/* O = softmax(scale * Q K^T [+ causal mask]) V for batch*heads independent heads.
+ * q: [batch*heads, sq, d], k, v: [batch*heads, sk, d] fp16 contiguous; o: same shape as q, fp32
+ * (out_f16 = 0, the reference's o_out type) or fp16 (out_f16 = 1).  Row max is taken on the raw logits,
+ * p = exp(scale * (x - max)) in fp32, p is rounded to fp16 for the second product, O is normalised by
+ * the fp32 row sum at the end; the causal mask hides keys beyond the query's own index.
+ * Replaces LaunchTFA<...>(...) of kernels/manual/common/flash_atten/fa_performance_kernel.cpp:970-1004,
+ * one launch per head there; d must be 128 (the reference's only head size), sq and sk multiples of 128. */
+int pto_b200_flash_attn_fwd_f16(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o, int batch_heads,
+                                int sq, int sk, int d, int causal, float scale, int out_f16, void *stream);
+/* HOST-buffer variant (copies in, runs, copies out, synchronises). */
+int pto_b200_flash_attn_fwd_f16_host(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o,
+                                     int batch_heads, int sq, int sk, int d, int causal, float scale, int out_f16);
+
+/* ---- drop-in shims with the reference's FFI signatures ------------------------------------------ */
+
+/* demos/torch_jit/gemm/gemm_kernel.cpp:259-262 `call_kernel(blockDim, stream, out, src0, src1)`: the 6144^3
+ * fp16 -> fp32 GEMM with src1 stored n x k.  blockDim is accepted and ignored (the grid is sized here). */
+void pto_b200_gemm_call_kernel(uint32_t blockDim, void *stream, uint8_t *out, uint8_t *src0, uint8_t *src1);
+/* demos/torch_jit/flash_atten/fa_kernel.cpp:1017-1037 `call_kernel(stream, headSize, s0, s1, is_causal, q, k, v,
+ * o_out, <seven workspace pointers>)`: one head, fp32 o_out.  The workspaces hold the reference's global-memory
+ * FIFOs between its cube and vector cores; here those hand-offs stay on chip, so they are accepted and unused. */
+void pto_b200_fa_call_kernel(void *stream, int headSize, int s0, int s1, bool is_causal, uint8_t *q, uint8_t *k,
+                             uint8_t *v, uint8_t *o_out, float *qk_ws, uint16_t *p_ws, float *pmax_ws, float *pv_ws,
+                             float *gsum, float *expmax, float *o_parts);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* PTO_B200_H */

@@ -81,8 +81,8 @@ class _Lib:
 
     def tgather_mask(self, src, pattern):
         src = np.ascontiguousarray(src)
-        div = {1: 2, 2: 2, 3: 4, 4: 4, 5: 4, 6: 4, 7: 1}[int(pattern)]
-        out = np.empty(src.shape[0] * (src.shape[1] // div), src.dtype)
+        div, off = {1: (2, 0), 2: (2, 1), 3: (4, 0), 4: (4, 1), 5: (4, 2), 6: (4, 3), 7: (1, 0)}[int(pattern)]
+        out = np.empty(src.shape[0] * ((src.shape[1] - off + div - 1) // div), src.dtype)
         name = "tgather_mask_f32" if src.itemsize == 4 else "tgather_mask_b16"
         rc = self._f(name)(_p(src), _p(out), src.shape[0], src.shape[1], int(pattern))
         if rc != 0:

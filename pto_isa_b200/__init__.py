@@ -1,0 +1,14 @@
+"""pto_isa_b200 - host side of the B200 (sm_100a) backend for the PTO tile-ISA hot path.
+
+The product is libpto_b200.so (hand-written CUDA behind the C ABI of include/pto_b200.h).  This package
+is the thin Python host layer over that ABI, in the role the reference's ctypes loaders play
+(demos/torch_jit/gemm/jit_util_gemm.py, demos/torch_jit/flash_atten/jit_util_flash.py): it passes
+torch CUDA tensors' device pointers and the current stream.  There is no CPU or PyTorch fallback:
+if the library is missing or a call fails, an exception is raised.
+"""
+from ._lib import PtoB200Error, lib, lib_path  # noqa: F401
+from . import ops  # noqa: F401
+from .ops import (  # noqa: F401
+    TCVT, TGATHER, TGATHER_MASK, TROWMAX, TROWSUM, TEXP, TROWEXPANDSUB, TROWEXPANDMUL, TROWEXPANDDIV,
+    TADD, TSUB, TMAX, TMULS, TADDS, gemm, gemm_host, flash_attn_fwd, flash_attn_fwd_host, device_status,
+)

@@ -1,0 +1,327 @@
+// The C ABI of libpto_b200.so (declared in include/pto_b200.h): argument checks, stream handling and the
+// host-buffer variants around the kernel launchers.  No torch types, no allocation of caller-visible
+// buffers, no CPU fallback: a call without a usable CUDA device fails with PTO_B200_ERR_CUDA.
+#include "../../include/pto_b200.h"
+#include "internal.h"
+#include "ptx.cuh"
+
+using namespace pto_b200;
+
+namespace {
+
+inline cudaStream_t as_stream(void *s)
+{
+    return static_cast<cudaStream_t>(s);
+}
+
+int bad(const char *what)
+{
+    set_error_text("%s", what);
+    return kErrBadArgument;
+}
+
+// Device scratch for the *_host entry points: grown on demand, kept for reuse, one set per process.
+struct HostArena {
+    void *ptr[4] = {nullptr, nullptr, nullptr, nullptr};
+    size_t cap[4] = {0, 0, 0, 0};
+    cudaStream_t stream = nullptr;
+};
+HostArena g_arena;
+
+int arena_get(int slot, size_t bytes, void **out)
+{
+    if (g_arena.cap[slot] < bytes) {
+        if (g_arena.ptr[slot] != nullptr) {
+            cudaFree(g_arena.ptr[slot]);
+            g_arena.ptr[slot] = nullptr;
+            g_arena.cap[slot] = 0;
+        }
+        int rc = check_cuda(cudaMalloc(&g_arena.ptr[slot], bytes), "cudaMalloc(host-variant staging)");
+        if (rc != kOk) {
+            return rc;
+        }
+        g_arena.cap[slot] = bytes;
+    }
+    *out = g_arena.ptr[slot];
+    return kOk;
+}
+
+int arena_stream(cudaStream_t *s)
+{
+    if (g_arena.stream == nullptr) {
+        int rc = check_cuda(cudaStreamCreateWithFlags(&g_arena.stream, cudaStreamNonBlocking), "cudaStreamCreate");
+        if (rc != kOk) {
+            return rc;
+        }
+    }
+    *s = g_arena.stream;
+    return kOk;
+}
+
+} // namespace
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+int pto_b200_version(void)
+{
+    return 1;
+}
+
+const char *pto_b200_last_error(void)
+{
+    return error_text();
+}
+
+int pto_b200_last_status(void)
+{
+    return last_status();
+}
+
+int pto_b200_device_status(void *stream)
+{
+    return fetch_device_status(as_stream(stream));
+}
+
+// ------------------------------------------------------------------ vector ops
+
+int pto_b200_tcvt_f32_f16(const float *src, uint16_t *dst, int64_t n, void *stream)
+{
+    if (n < 0 || (n > 0 && (src == nullptr || dst == nullptr))) {
+        return bad("tcvt_f32_f16: null pointer or negative length");
+    }
+    return launch_tcvt_f32_16(src, dst, n, false, as_stream(stream));
+}
+
+int pto_b200_tcvt_f32_bf16(const float *src, uint16_t *dst, int64_t n, void *stream)
+{
+    if (n < 0 || (n > 0 && (src == nullptr || dst == nullptr))) {
+        return bad("tcvt_f32_bf16: null pointer or negative length");
+    }
+    return launch_tcvt_f32_16(src, dst, n, true, as_stream(stream));
+}
+
+int pto_b200_tcvt_f32_i32(const float *src, int32_t *dst, int64_t n, int round_mode, void *stream)
+{
+    if (n < 0 || (n > 0 && (src == nullptr || dst == nullptr))) {
+        return bad("tcvt_f32_i32: null pointer or negative length");
+    }
+    if (round_mode < 0 || round_mode > 6) {
+        return bad("tcvt_f32_i32: unknown round mode");
+    }
+    return launch_tcvt_f32_i32(src, dst, n, round_mode, as_stream(stream));
+}
+
+int pto_b200_tgather(const void *src0, int64_t src_numel, const int32_t *idx, void *dst, int64_t n, int elem_bytes,
+                     void *stream)
+{
+    if (n < 0 || src_numel < 0 || (n > 0 && (idx == nullptr || dst == nullptr)) || (src_numel > 0 && src0 == nullptr)) {
+        return bad("tgather: null pointer or negative length");
+    }
+    if (elem_bytes != 2 && elem_bytes != 4) {
+        return bad("tgather: element size must be 2 or 4 bytes");
+    }
+    if (src_numel > 0x7fffffffLL) {
+        set_error_text("tgather: source larger than the 32-bit index range");
+        return kErrTooLarge;
+    }
+    return launch_tgather(src0, src_numel, idx, dst, n, elem_bytes, as_stream(stream));
+}
+
+int pto_b200_tgather_mask(const void *src, void *dst, int rows, int cols, int pattern, int elem_bytes, void *stream)
+{
+    if (rows < 0 || cols < 0 || (rows > 0 && cols > 0 && (src == nullptr || dst == nullptr))) {
+        return bad("tgather_mask: null pointer or negative shape");
+    }
+    if (elem_bytes != 2 && elem_bytes != 4) {
+        return bad("tgather_mask: element size must be 2 or 4 bytes");
+    }
+    if (pattern < 1 || pattern > 7) {
+        return bad("tgather_mask: unknown mask pattern");
+    }
+    return launch_tgather_mask(src, dst, rows, cols, pattern, elem_bytes, as_stream(stream));
+}
+
+int pto_b200_trowmax_f32(const float *src, float *dst, int rows, int cols, int64_t row_stride, void *stream)
+{
+    if (rows < 0 || cols <= 0 || row_stride < cols || (rows > 0 && (src == nullptr || dst == nullptr))) {
+        return bad("trowmax: bad shape or null pointer");
+    }
+    return launch_trow_reduce(src, dst, rows, cols, row_stride, true, as_stream(stream));
+}
+
+int pto_b200_trowsum_f32(const float *src, float *dst, int rows, int cols, int64_t row_stride, void *stream)
+{
+    if (rows < 0 || cols <= 0 || row_stride < cols || (rows > 0 && (src == nullptr || dst == nullptr))) {
+        return bad("trowsum: bad shape or null pointer");
+    }
+    return launch_trow_reduce(src, dst, rows, cols, row_stride, false, as_stream(stream));
+}
+
+int pto_b200_texp_f32(const float *src, float *dst, int64_t n, void *stream)
+{
+    if (n < 0 || (n > 0 && (src == nullptr || dst == nullptr))) {
+        return bad("texp: null pointer or negative length");
+    }
+    return launch_texp(src, dst, n, as_stream(stream));
+}
+
+int pto_b200_tbinary_f32(const float *a, const float *b, float *dst, int64_t n, int op, void *stream)
+{
+    if (n < 0 || (n > 0 && (a == nullptr || b == nullptr || dst == nullptr)) || op < 0 || op > 5) {
+        return bad("tbinary: bad argument");
+    }
+    return launch_tbinary(a, b, dst, n, op, as_stream(stream));
+}
+
+int pto_b200_tscalar_f32(const float *a, float scalar, float *dst, int64_t n, int op, void *stream)
+{
+    if (n < 0 || (n > 0 && (a == nullptr || dst == nullptr)) || op < 0 || op > 5) {
+        return bad("tscalar: bad argument");
+    }
+    return launch_tscalar(a, scalar, dst, n, op, as_stream(stream));
+}
+
+int pto_b200_trowexpand_f32(const float *a, const float *row_scalar, float *dst, int rows, int cols, int op,
+                            void *stream)
+{
+    if (rows < 0 || cols < 0 || op < 0 || op > 5 ||
+        (rows > 0 && cols > 0 && (a == nullptr || row_scalar == nullptr || dst == nullptr))) {
+        return bad("trowexpand: bad argument");
+    }
+    return launch_trowexpand(a, row_scalar, dst, rows, cols, op, as_stream(stream));
+}
+
+// ------------------------------------------------------------------ GEMM
+
+int pto_b200_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
+                         void *stream)
+{
+    return launch_gemm_f16f32(a, b, c, m, n, k, b_layout, as_stream(stream));
+}
+
+int pto_b200_gemm_f16f32_batched(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
+                                 int batch, int64_t a_stride, int64_t b_stride, int64_t c_stride, void *stream)
+{
+    if (batch < 0) {
+        return bad("gemm_batched: negative batch");
+    }
+    for (int i = 0; i < batch; ++i) {
+        const int rc = launch_gemm_f16f32(a + i * a_stride, b + i * b_stride, c + i * c_stride, m, n, k, b_layout,
+                                          as_stream(stream));
+        if (rc != kOk) {
+            return rc;
+        }
+    }
+    return kOk;
+}
+
+int pto_b200_gemm_f16f32_host(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout)
+{
+    if (a == nullptr || b == nullptr || c == nullptr || m <= 0 || n <= 0 || k <= 0) {
+        return bad("gemm_host: bad argument");
+    }
+    const size_t a_bytes = static_cast<size_t>(m) * k * 2, b_bytes = static_cast<size_t>(n) * k * 2,
+                 c_bytes = static_cast<size_t>(m) * n * 4;
+    void *da, *db, *dc;
+    cudaStream_t s;
+    int rc;
+    if ((rc = arena_stream(&s)) != kOk || (rc = arena_get(0, a_bytes, &da)) != kOk ||
+        (rc = arena_get(1, b_bytes, &db)) != kOk || (rc = arena_get(2, c_bytes, &dc)) != kOk) {
+        return rc;
+    }
+    if ((rc = check_cuda(cudaMemcpyAsync(da, a, a_bytes, cudaMemcpyHostToDevice, s), "H2D A")) != kOk ||
+        (rc = check_cuda(cudaMemcpyAsync(db, b, b_bytes, cudaMemcpyHostToDevice, s), "H2D B")) != kOk) {
+        return rc;
+    }
+    rc = launch_gemm_f16f32(static_cast<const uint16_t *>(da), static_cast<const uint16_t *>(db),
+                            static_cast<float *>(dc), m, n, k, b_layout, s);
+    if (rc != kOk) {
+        return rc;
+    }
+    if ((rc = check_cuda(cudaMemcpyAsync(c, dc, c_bytes, cudaMemcpyDeviceToHost, s), "D2H C")) != kOk) {
+        return rc;
+    }
+    return check_cuda(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+}
+
+// ------------------------------------------------------------------ flash attention
+
+int pto_b200_flash_attn_fwd_f16(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o, int batch_heads,
+                                int sq, int sk, int d, int causal, float scale, int out_f16, void *stream)
+{
+    if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || batch_heads <= 0 || sq <= 0 || sk <= 0) {
+        return bad("flash_attn_fwd: bad argument");
+    }
+    return launch_flash_attn_fwd(q, k, v, o, batch_heads, sq, sk, d, causal, scale, out_f16, as_stream(stream));
+}
+
+int pto_b200_flash_attn_fwd_f16_host(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o,
+                                     int batch_heads, int sq, int sk, int d, int causal, float scale, int out_f16)
+{
+    if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || batch_heads <= 0 || sq <= 0 || sk <= 0 ||
+        d <= 0) {
+        return bad("flash_attn_fwd_host: bad argument");
+    }
+    const size_t q_bytes = static_cast<size_t>(batch_heads) * sq * d * 2;
+    const size_t kv_bytes = static_cast<size_t>(batch_heads) * sk * d * 2;
+    const size_t o_bytes = static_cast<size_t>(batch_heads) * sq * d * (out_f16 ? 2 : 4);
+    void *dq, *dk, *dv, *dout;
+    cudaStream_t s;
+    int rc;
+    if ((rc = arena_stream(&s)) != kOk || (rc = arena_get(0, q_bytes, &dq)) != kOk ||
+        (rc = arena_get(1, kv_bytes, &dk)) != kOk || (rc = arena_get(2, kv_bytes, &dv)) != kOk ||
+        (rc = arena_get(3, o_bytes, &dout)) != kOk) {
+        return rc;
+    }
+    if ((rc = check_cuda(cudaMemcpyAsync(dq, q, q_bytes, cudaMemcpyHostToDevice, s), "H2D Q")) != kOk ||
+        (rc = check_cuda(cudaMemcpyAsync(dk, k, kv_bytes, cudaMemcpyHostToDevice, s), "H2D K")) != kOk ||
+        (rc = check_cuda(cudaMemcpyAsync(dv, v, kv_bytes, cudaMemcpyHostToDevice, s), "H2D V")) != kOk) {
+        return rc;
+    }
+    rc = launch_flash_attn_fwd(static_cast<const uint16_t *>(dq), static_cast<const uint16_t *>(dk),
+                               static_cast<const uint16_t *>(dv), dout, batch_heads, sq, sk, d, causal, scale,
+                               out_f16, s);
+    if (rc != kOk) {
+        return rc;
+    }
+    if ((rc = check_cuda(cudaMemcpyAsync(o, dout, o_bytes, cudaMemcpyDeviceToHost, s), "D2H O")) != kOk) {
+        return rc;
+    }
+    return check_cuda(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+}
+
+// ------------------------------------------------------------------ reference-shaped shims
+
+void pto_b200_gemm_call_kernel(uint32_t blockDim, void *stream, uint8_t *out, uint8_t *src0, uint8_t *src1)
+{
+    (void)blockDim;
+    set_last_status(launch_gemm_f16f32(reinterpret_cast<const uint16_t *>(src0),
+                                       reinterpret_cast<const uint16_t *>(src1), reinterpret_cast<float *>(out), 6144,
+                                       6144, 6144, 1, as_stream(stream)));
+}
+
+void pto_b200_fa_call_kernel(void *stream, int headSize, int s0, int s1, bool is_causal, uint8_t *q, uint8_t *k,
+                             uint8_t *v, uint8_t *o_out, float *qk_ws, uint16_t *p_ws, float *pmax_ws, float *pv_ws,
+                             float *gsum, float *expmax, float *o_parts)
+{
+    (void)qk_ws;
+    (void)p_ws;
+    (void)pmax_ws;
+    (void)pv_ws;
+    (void)gsum;
+    (void)expmax;
+    (void)o_parts;
+    if (headSize != 128 || (s0 % 128) != 0) {
+        // the reference returns silently for these (fa_kernel.cpp:1051-1059); the status says why
+        set_error_text("fa call_kernel: headSize must be 128 and s0 a multiple of 128");
+        set_last_status(kErrUnsupportedShape);
+        return;
+    }
+    set_last_status(launch_flash_attn_fwd(reinterpret_cast<const uint16_t *>(q), reinterpret_cast<const uint16_t *>(k),
+                                          reinterpret_cast<const uint16_t *>(v), o_out, 1, s0, s1, headSize,
+                                          is_causal ? 1 : 0, 0.08838834764831845f, 0, as_stream(stream)));
+}
+
+} // extern "C"
+#pragma GCC visibility pop

@@ -1,0 +1,63 @@
+// Declarations shared by the translation units of libpto_b200.so (not part of the public ABI).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pto_b200 {
+
+struct DeviceStatus;
+
+// number of SMs of the current device (cached per device)
+int sm_count();
+// cudaGetLastError() mapped to a status code; records the CUDA error text for pto_b200_last_error()
+int check_launch();
+int check_cuda(cudaError_t e, const char *what);
+void set_error_text(const char *fmt, ...);
+const char *error_text();
+void set_last_status(int code);
+int last_status();
+// per-device status record in global memory that kernels with bounded waits report into;
+// allocated on first use for the current device
+DeviceStatus *device_status_ptr();
+// reads the status record back (synchronises `stream`) and clears it; returns its code
+int fetch_device_status(cudaStream_t stream);
+
+// cuTensorMapEncodeTiled resolved through the runtime (no link-time dependency on libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn();
+
+// Encodes a tiled tensor map over a row-major 2-D (rows x cols) or 3-D (outer x rows x cols) array of
+// 16-bit (or 32-bit) elements with a (box_rows x box_cols) box and 128-byte swizzle.  Returns a status code.
+int make_tmap_2d(CUtensorMap *map, const void *base, int elem_bytes, uint64_t rows, uint64_t cols,
+                 uint64_t row_stride_elems, uint32_t box_rows, uint32_t box_cols, bool swizzle128);
+int make_tmap_3d(CUtensorMap *map, const void *base, int elem_bytes, uint64_t outer, uint64_t rows, uint64_t cols,
+                 uint64_t row_stride_elems, uint64_t outer_stride_elems, uint32_t box_rows, uint32_t box_cols,
+                 bool swizzle128);
+
+// vector ops
+int launch_tcvt_f32_16(const float *src, uint16_t *dst, int64_t n, bool bf16, cudaStream_t stream);
+int launch_tcvt_f32_i32(const float *src, int32_t *dst, int64_t n, int mode, cudaStream_t stream);
+int launch_tgather(const void *src0, int64_t numel, const int32_t *idx, void *dst, int64_t n, int elem_bytes,
+                   cudaStream_t stream);
+int launch_tgather_mask(const void *src, void *dst, int rows, int cols, int pattern, int elem_bytes,
+                        cudaStream_t stream);
+int launch_trow_reduce(const float *src, float *dst, int rows, int cols, int64_t row_stride, bool is_max,
+                       cudaStream_t stream);
+int launch_texp(const float *src, float *dst, int64_t n, cudaStream_t stream);
+int launch_tbinary(const float *a, const float *b, float *dst, int64_t n, int op, cudaStream_t stream);
+int launch_tscalar(const float *a, float s, float *dst, int64_t n, int op, cudaStream_t stream);
+int launch_trowexpand(const float *a, const float *row_scalar, float *dst, int rows, int cols, int op,
+                      cudaStream_t stream);
+
+// GEMM: C[m x n] fp32 = A[m x k] fp16 * B, B given k x n row-major (b_layout 0) or n x k row-major (1)
+int launch_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
+                       cudaStream_t stream);
+
+// flash attention forward; q/k/v/o are [batch*heads, seq, d] contiguous; out_f16 selects the output type
+int launch_flash_attn_fwd(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o, int bh, int sq, int sk,
+                          int d, int causal, float scale, int out_f16, cudaStream_t stream);
+
+} // namespace pto_b200

@@ -1,0 +1,469 @@
+// Vector tile ops of the PTO surface as HBM-streaming kernels for sm_100a:
+// TCVT (fp32 -> fp16 / bf16 / int32), TGATHER (index and mask forms), TROWMAX, TROWSUM, TEXP,
+// TROWEXPAND{SUB,MUL,DIV}, and the elementwise binary / scalar ops of the attention softmax.
+//
+// All of them are memory-bound: 128-bit streaming loads that bypass L1, 128-bit streaming stores,
+// one warp per row with shuffle reductions for the row ops, grids sized from the element count.
+// Semantics follow the reference's CPU simulation (paths relative to the reference root):
+//   TCVT     include/pto/cpu/TCvt.hpp:65-92   float->float is an IEEE round-to-nearest-even cast (round
+//            mode ignored, overflow to infinity, NaN quieted keeping sign and top payload bits);
+//            float->int applies the round mode in double and casts (:28-63)
+//   TGATHER  include/pto/cpu/TGather.hpp:68-129  out-of-range (incl. negative) index -> 0; mask form packs
+//   TROWMAX / TROWSUM / TEXP  include/pto/cpu/TRowMax.hpp:20-59, TRowSum.hpp:17-63, TExp.hpp:22-60
+//   TROWEXPAND*  include/pto/cpu/TRowExpandOp.hpp:38-76
+#include "ptx.cuh"
+#include "internal.h"
+
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+
+namespace pto_b200 {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+// ---------------------------------------------------------------- TCVT
+
+__device__ __forceinline__ uint32_t cvt2_f16(float lo, float hi)
+{
+    // cvt.rn.f16x2.f32 d, a, b : a -> upper half, b -> lower half
+    uint32_t d;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    // NaN: the hardware returns the canonical 0x7fff; the reference keeps sign and payload.
+    const uint32_t ulo = __float_as_uint(lo), uhi = __float_as_uint(hi);
+    if ((ulo & 0x7fffffffu) > 0x7f800000u) {
+        d = (d & 0xffff0000u) | ((ulo >> 16) & 0x8000u) | 0x7e00u | ((ulo >> 13) & 0x3ffu);
+    }
+    if ((uhi & 0x7fffffffu) > 0x7f800000u) {
+        d = (d & 0x0000ffffu) | ((((uhi >> 16) & 0x8000u) | 0x7e00u | ((uhi >> 13) & 0x3ffu)) << 16);
+    }
+    return d;
+}
+
+__device__ __forceinline__ uint32_t cvt2_bf16(float lo, float hi)
+{
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    const uint32_t ulo = __float_as_uint(lo), uhi = __float_as_uint(hi);
+    if ((ulo & 0x7fffffffu) > 0x7f800000u) {
+        d = (d & 0xffff0000u) | ((ulo >> 16) | 0x40u);
+    }
+    if ((uhi & 0x7fffffffu) > 0x7f800000u) {
+        d = (d & 0x0000ffffu) | (((uhi >> 16) | 0x40u) << 16);
+    }
+    return d;
+}
+
+template <bool kBf16>
+__device__ __forceinline__ uint32_t cvt2(float lo, float hi)
+{
+    return kBf16 ? cvt2_bf16(lo, hi) : cvt2_f16(lo, hi);
+}
+
+// 8 elements per thread per step: two 16-byte loads, one 16-byte store.
+template <bool kBf16>
+__global__ void __launch_bounds__(kThreads) tcvt_f32_to_16_kernel(const float *__restrict__ src,
+                                                                  uint16_t *__restrict__ dst, int64_t n)
+{
+    const int64_t nvec = n >> 3;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const float4 *s4 = reinterpret_cast<const float4 *>(src);
+    uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        const float4 a = ld_stream_f4(s4 + 2 * i);
+        const float4 b = ld_stream_f4(s4 + 2 * i + 1);
+        uint4 o;
+        o.x = cvt2<kBf16>(a.x, a.y);
+        o.y = cvt2<kBf16>(a.z, a.w);
+        o.z = cvt2<kBf16>(b.x, b.y);
+        o.w = cvt2<kBf16>(b.z, b.w);
+        st_stream_u4(d4 + i, o);
+    }
+    // ragged tail (< 8 elements), one thread
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        for (int64_t i = nvec << 3; i < n; ++i) {
+            dst[i] = static_cast<uint16_t>(cvt2<kBf16>(src[i], 0.0f) & 0xffffu);
+        }
+    }
+}
+
+// scalar variant for pointers that are not 16-byte aligned
+template <bool kBf16>
+__global__ void __launch_bounds__(kThreads) tcvt_f32_to_16_scalar_kernel(const float *__restrict__ src,
+                                                                         uint16_t *__restrict__ dst, int64_t n)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        dst[i] = static_cast<uint16_t>(cvt2<kBf16>(src[i], 0.0f) & 0xffffu);
+    }
+}
+
+__device__ __forceinline__ int32_t cvt_f32_i32_mode(float x, int mode)
+{
+    // the reference rounds in double then casts; every fp32 is exact in double and the rounded value
+    // of an in-range input is exactly representable, so the single-precision round is identical
+    const double v = static_cast<double>(x);
+    double r;
+    switch (mode) {
+        case 1: r = rint(v); break;
+        case 2: r = round(v); break;
+        case 3: r = floor(v); break;
+        case 4: r = ceil(v); break;
+        case 5: r = trunc(v); break;
+        case 6: {
+            const double f = floor(v), frac = v - f;
+            if (frac > 0.5) r = f + 1;
+            else if (frac < 0.5) r = f;
+            else r = (static_cast<long long>(f) & 1) ? f : f + 1;
+            break;
+        }
+        default: r = v; break;
+    }
+    return static_cast<int32_t>(r);
+}
+
+__global__ void __launch_bounds__(kThreads) tcvt_f32_i32_kernel(const float *__restrict__ src,
+                                                                int32_t *__restrict__ dst, int64_t n, int mode)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        dst[i] = cvt_f32_i32_mode(src[i], mode);
+    }
+}
+
+// ---------------------------------------------------------------- TGATHER (index form)
+// Four indices per thread: one 16-byte index load, four independent table loads (through L1/L2: the
+// table is re-read, duplicates hit), one 16-byte store.
+__global__ void __launch_bounds__(kThreads) tgather_b32_kernel(const uint32_t *__restrict__ src0, int64_t numel,
+                                                               const int32_t *__restrict__ idx,
+                                                               uint32_t *__restrict__ dst, int64_t n)
+{
+    const int64_t nvec = n >> 2;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const int4 *i4 = reinterpret_cast<const int4 *>(idx);
+    uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        const int4 r = ld_stream_i4(i4 + i);
+        uint4 o;
+        // unsigned compare folds the "negative" and ">= numel" tests into one
+        o.x = (static_cast<uint64_t>(static_cast<int64_t>(r.x)) < static_cast<uint64_t>(numel)) ? __ldg(src0 + r.x) : 0u;
+        o.y = (static_cast<uint64_t>(static_cast<int64_t>(r.y)) < static_cast<uint64_t>(numel)) ? __ldg(src0 + r.y) : 0u;
+        o.z = (static_cast<uint64_t>(static_cast<int64_t>(r.z)) < static_cast<uint64_t>(numel)) ? __ldg(src0 + r.z) : 0u;
+        o.w = (static_cast<uint64_t>(static_cast<int64_t>(r.w)) < static_cast<uint64_t>(numel)) ? __ldg(src0 + r.w) : 0u;
+        st_stream_u4(d4 + i, o);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        for (int64_t i = nvec << 2; i < n; ++i) {
+            const int32_t r = idx[i];
+            dst[i] = (static_cast<uint64_t>(static_cast<int64_t>(r)) < static_cast<uint64_t>(numel)) ? src0[r] : 0u;
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) tgather_scalar_kernel(const T *__restrict__ src0, int64_t numel,
+                                                                  const int32_t *__restrict__ idx,
+                                                                  T *__restrict__ dst, int64_t n)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const int32_t r = idx[i];
+        dst[i] = (static_cast<uint64_t>(static_cast<int64_t>(r)) < static_cast<uint64_t>(numel)) ? src0[r]
+                                                                                                 : static_cast<T>(0);
+    }
+}
+
+// ---------------------------------------------------------------- TGATHER (mask form)
+// Output element d of the packed result comes from row d / out_cols, column (d % out_cols) * div + off.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) tgather_mask_kernel(const T *__restrict__ src, T *__restrict__ dst,
+                                                                int64_t n_out, int cols, int out_cols, int div,
+                                                                int off)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t d = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; d < n_out; d += stride) {
+        const int64_t r = d / out_cols;
+        const int c = static_cast<int>(d - r * out_cols) * div + off;
+        dst[d] = src[r * cols + c];
+    }
+}
+
+// ---------------------------------------------------------------- row reductions
+// One warp per row; 128-bit loads when the row start and length allow it.
+template <bool kIsMax>
+__device__ __forceinline__ float red_op(float a, float b)
+{
+    return kIsMax ? fmaxf(a, b) : a + b;
+}
+
+template <bool kIsMax>
+__global__ void __launch_bounds__(kThreads) trow_reduce_kernel(const float *__restrict__ src, float *__restrict__ dst,
+                                                               int rows, int cols, int64_t row_stride)
+{
+    const int warps_per_block = kThreads / 32;
+    const int lane = threadIdx.x & 31;
+    for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
+        const float *p = src + static_cast<int64_t>(row) * row_stride;
+        float acc = kIsMax ? -INFINITY : 0.0f;
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(p) & 15u) == 0);
+        int c = 0;
+        if (vec_ok) {
+            const int nvec = cols >> 2;
+            const float4 *p4 = reinterpret_cast<const float4 *>(p);
+            for (int i = lane; i < nvec; i += 32) {
+                const float4 v = ld_stream_f4(p4 + i);
+                acc = red_op<kIsMax>(acc, red_op<kIsMax>(red_op<kIsMax>(v.x, v.y), red_op<kIsMax>(v.z, v.w)));
+            }
+            c = nvec << 2;
+        }
+        for (int i = c + lane; i < cols; i += 32) {
+            acc = red_op<kIsMax>(acc, p[i]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            acc = red_op<kIsMax>(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+        }
+        if (lane == 0) {
+            dst[row] = acc;
+        }
+    }
+}
+
+// ---------------------------------------------------------------- elementwise
+enum UnaryOp { kOpExp = 0 };
+enum BinaryOp { kOpAdd = 0, kOpSub = 1, kOpMul = 2, kOpDiv = 3, kOpMax = 4, kOpMin = 5 };
+
+__device__ __forceinline__ float apply_bin(int op, float a, float b)
+{
+    switch (op) {
+        case kOpAdd: return a + b;
+        case kOpSub: return a - b;
+        case kOpMul: return a * b;
+        case kOpDiv: return a / b;
+        case kOpMax: return fmaxf(a, b);
+        default: return fminf(a, b);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) texp_kernel(const float *__restrict__ src, float *__restrict__ dst,
+                                                        int64_t n, bool vec_ok)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    int64_t done = 0;
+    if (vec_ok) {
+        const int64_t nvec = n >> 2;
+        const float4 *s4 = reinterpret_cast<const float4 *>(src);
+        float4 *d4 = reinterpret_cast<float4 *>(dst);
+        for (int64_t i = tid; i < nvec; i += stride) {
+            float4 v = ld_stream_f4(s4 + i);
+            v.x = expf(v.x);
+            v.y = expf(v.y);
+            v.z = expf(v.z);
+            v.w = expf(v.w);
+            st_stream_f4(d4 + i, v);
+        }
+        done = nvec << 2;
+    }
+    for (int64_t i = done + tid; i < n; i += stride) {
+        dst[i] = expf(src[i]);
+    }
+}
+
+// dst[i] = a[i] op b[i]
+__global__ void __launch_bounds__(kThreads) tbinary_kernel(const float *__restrict__ a, const float *__restrict__ b,
+                                                           float *__restrict__ dst, int64_t n, int op)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        dst[i] = apply_bin(op, a[i], b[i]);
+    }
+}
+
+// dst[i] = a[i] op s
+__global__ void __launch_bounds__(kThreads) tscalar_kernel(const float *__restrict__ a, float s,
+                                                           float *__restrict__ dst, int64_t n, int op)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        dst[i] = apply_bin(op, a[i], s);
+    }
+}
+
+// dst[r, c] = a[r, c] op row_scalar[r]
+__global__ void __launch_bounds__(kThreads) trowexpand_kernel(const float *__restrict__ a,
+                                                              const float *__restrict__ row_scalar,
+                                                              float *__restrict__ dst, int rows, int cols, int op)
+{
+    const int64_t n = static_cast<int64_t>(rows) * cols;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const int64_t r = i / cols;
+        dst[i] = apply_bin(op, a[i], row_scalar[r]);
+    }
+}
+
+int grid_for(int64_t work_items, int items_per_block)
+{
+    int64_t blocks = (work_items + items_per_block - 1) / items_per_block;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 32; // grid-stride beyond this
+    if (blocks > cap) {
+        blocks = cap;
+    }
+    if (blocks < 1) {
+        blocks = 1;
+    }
+    return static_cast<int>(blocks);
+}
+
+bool aligned16(const void *p)
+{
+    return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+} // namespace
+
+// ---------------------------------------------------------------- launchers (called from the C ABI)
+
+int launch_tcvt_f32_16(const float *src, uint16_t *dst, int64_t n, bool bf16, cudaStream_t stream)
+{
+    if (n == 0) {
+        return kOk;
+    }
+    if (aligned16(src) && aligned16(dst)) {
+        const int grid = grid_for(n >> 3, kThreads);
+        if (bf16) {
+            tcvt_f32_to_16_kernel<true><<<grid, kThreads, 0, stream>>>(src, dst, n);
+        } else {
+            tcvt_f32_to_16_kernel<false><<<grid, kThreads, 0, stream>>>(src, dst, n);
+        }
+    } else {
+        const int grid = grid_for(n, kThreads);
+        if (bf16) {
+            tcvt_f32_to_16_scalar_kernel<true><<<grid, kThreads, 0, stream>>>(src, dst, n);
+        } else {
+            tcvt_f32_to_16_scalar_kernel<false><<<grid, kThreads, 0, stream>>>(src, dst, n);
+        }
+    }
+    return check_launch();
+}
+
+int launch_tcvt_f32_i32(const float *src, int32_t *dst, int64_t n, int mode, cudaStream_t stream)
+{
+    if (n == 0) {
+        return kOk;
+    }
+    tcvt_f32_i32_kernel<<<grid_for(n, kThreads), kThreads, 0, stream>>>(src, dst, n, mode);
+    return check_launch();
+}
+
+int launch_tgather(const void *src0, int64_t numel, const int32_t *idx, void *dst, int64_t n, int elem_bytes,
+                   cudaStream_t stream)
+{
+    if (n == 0) {
+        return kOk;
+    }
+    if (elem_bytes == 4) {
+        if (aligned16(idx) && aligned16(dst)) {
+            tgather_b32_kernel<<<grid_for(n >> 2, kThreads), kThreads, 0, stream>>>(
+                static_cast<const uint32_t *>(src0), numel, idx, static_cast<uint32_t *>(dst), n);
+        } else {
+            tgather_scalar_kernel<uint32_t><<<grid_for(n, kThreads), kThreads, 0, stream>>>(
+                static_cast<const uint32_t *>(src0), numel, idx, static_cast<uint32_t *>(dst), n);
+        }
+    } else {
+        tgather_scalar_kernel<uint16_t><<<grid_for(n, kThreads), kThreads, 0, stream>>>(
+            static_cast<const uint16_t *>(src0), numel, idx, static_cast<uint16_t *>(dst), n);
+    }
+    return check_launch();
+}
+
+int launch_tgather_mask(const void *src, void *dst, int rows, int cols, int pattern, int elem_bytes,
+                        cudaStream_t stream)
+{
+    int div, off;
+    switch (pattern) {
+        case 1: div = 2; off = 0; break;
+        case 2: div = 2; off = 1; break;
+        case 3: div = 4; off = 0; break;
+        case 4: div = 4; off = 1; break;
+        case 5: div = 4; off = 2; break;
+        case 6: div = 4; off = 3; break;
+        case 7: div = 1; off = 0; break;
+        default: return kErrBadArgument;
+    }
+    // columns selected per row: those c in [0, cols) with c % div == off
+    const int out_cols = (cols - off + div - 1) / div;
+    const int64_t n_out = static_cast<int64_t>(rows) * out_cols;
+    if (n_out <= 0) {
+        return kOk;
+    }
+    const int grid = grid_for(n_out, kThreads);
+    if (elem_bytes == 4) {
+        tgather_mask_kernel<uint32_t><<<grid, kThreads, 0, stream>>>(static_cast<const uint32_t *>(src),
+                                                                     static_cast<uint32_t *>(dst), n_out, cols,
+                                                                     out_cols, div, off);
+    } else {
+        tgather_mask_kernel<uint16_t><<<grid, kThreads, 0, stream>>>(static_cast<const uint16_t *>(src),
+                                                                     static_cast<uint16_t *>(dst), n_out, cols,
+                                                                     out_cols, div, off);
+    }
+    return check_launch();
+}
+
+int launch_trow_reduce(const float *src, float *dst, int rows, int cols, int64_t row_stride, bool is_max,
+                       cudaStream_t stream)
+{
+    if (rows == 0) {
+        return kOk;
+    }
+    const int grid = grid_for(rows, kThreads / 32);
+    if (is_max) {
+        trow_reduce_kernel<true><<<grid, kThreads, 0, stream>>>(src, dst, rows, cols, row_stride);
+    } else {
+        trow_reduce_kernel<false><<<grid, kThreads, 0, stream>>>(src, dst, rows, cols, row_stride);
+    }
+    return check_launch();
+}
+
+int launch_texp(const float *src, float *dst, int64_t n, cudaStream_t stream)
+{
+    if (n == 0) {
+        return kOk;
+    }
+    const bool vec_ok = aligned16(src) && aligned16(dst);
+    texp_kernel<<<grid_for(vec_ok ? (n >> 2) + 1 : n, kThreads), kThreads, 0, stream>>>(src, dst, n, vec_ok);
+    return check_launch();
+}
+
+int launch_tbinary(const float *a, const float *b, float *dst, int64_t n, int op, cudaStream_t stream)
+{
+    if (n == 0) {
+        return kOk;
+    }
+    tbinary_kernel<<<grid_for(n, kThreads), kThreads, 0, stream>>>(a, b, dst, n, op);
+    return check_launch();
+}
+
+int launch_tscalar(const float *a, float s, float *dst, int64_t n, int op, cudaStream_t stream)
+{
+    if (n == 0) {
+        return kOk;
+    }
+    tscalar_kernel<<<grid_for(n, kThreads), kThreads, 0, stream>>>(a, s, dst, n, op);
+    return check_launch();
+}
+
+int launch_trowexpand(const float *a, const float *row_scalar, float *dst, int rows, int cols, int op,
+                      cudaStream_t stream)
+{
+    if (rows == 0 || cols == 0) {
+        return kOk;
+    }
+    trowexpand_kernel<<<grid_for(static_cast<int64_t>(rows) * cols, kThreads), kThreads, 0, stream>>>(
+        a, row_scalar, dst, rows, cols, op);
+    return check_launch();
+}
+
+} // namespace pto_b200

@@ -1,0 +1,244 @@
+"""The PTO operator names of the hot path over torch CUDA tensors (host side of the C ABI).
+
+Names and argument meaning follow the reference's instruction surface (include/pto/common/pto_instr.hpp,
+paths relative to the reference root): TCVT :864, TGATHER :800/:824, TROWMAX :990, TROWSUM :942, TEXP :1129,
+TROWEXPANDSUB/MUL/DIV :1057-1073, TADD/TSUB/TMAX :56-120, TMULS :1188, TADDS :1161; `gemm` stands for
+LaunchGEMME2E (kernels/manual/a2a3/gemm_performance/gemm_performance_kernel.cpp:243) and `flash_attn_fwd` for
+LaunchTFA (kernels/manual/common/flash_atten/fa_performance_kernel.cpp:970).  A whole tensor plays the role of
+the tile: destination first is replaced by a returned (or `out=`) tensor.  Everything runs on the current
+CUDA stream of the tensors' device; nothing is computed by torch.
+"""
+import ctypes
+
+import torch
+
+from ._lib import PtoB200Error, check, lib
+
+CAST_RINT, CAST_ROUND, CAST_FLOOR, CAST_CEIL, CAST_TRUNC, CAST_ODD = 1, 2, 3, 4, 5, 6
+P0101, P1010, P0001, P0010, P0100, P1000, P1111 = 1, 2, 3, 4, 5, 6, 7
+OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_MAX, OP_MIN = 0, 1, 2, 3, 4, 5
+
+
+def _stream(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if not t.is_cuda:
+            raise PtoB200Error("operands must be CUDA tensors (there is no CPU path)")
+        if not t.is_contiguous():
+            raise PtoB200Error("operands must be contiguous")
+
+
+def TCVT(src, dtype, round_mode=CAST_RINT, out=None):
+    """Elementwise cast of an fp32 tensor to torch.float16, torch.bfloat16 or torch.int32."""
+    _need_cuda(src)
+    if src.dtype != torch.float32:
+        raise PtoB200Error("TCVT: source must be float32")
+    out = torch.empty(src.shape, dtype=dtype, device=src.device) if out is None else out
+    _need_cuda(out)
+    with torch.cuda.device(src.device):
+        if dtype == torch.float16:
+            rc = lib().pto_b200_tcvt_f32_f16(_ptr(src), _ptr(out), src.numel(), _stream(src))
+        elif dtype == torch.bfloat16:
+            rc = lib().pto_b200_tcvt_f32_bf16(_ptr(src), _ptr(out), src.numel(), _stream(src))
+        elif dtype == torch.int32:
+            rc = lib().pto_b200_tcvt_f32_i32(_ptr(src), _ptr(out), src.numel(), int(round_mode), _stream(src))
+        else:
+            raise PtoB200Error(f"TCVT: unsupported destination type {dtype}")
+    check(rc, "TCVT")
+    return out
+
+
+def TGATHER(src0, idx, out=None):
+    """out[i] = src0.flatten()[idx[i]]; an index outside [0, src0.numel()) gives 0.  4- or 2-byte elements."""
+    _need_cuda(src0, idx)
+    if idx.dtype != torch.int32:
+        raise PtoB200Error("TGATHER: indices must be int32")
+    if src0.element_size() not in (2, 4):
+        raise PtoB200Error("TGATHER: 16- or 32-bit elements only")
+    out = torch.empty(idx.shape, dtype=src0.dtype, device=src0.device) if out is None else out
+    with torch.cuda.device(src0.device):
+        rc = lib().pto_b200_tgather(_ptr(src0), src0.numel(), _ptr(idx), _ptr(out), idx.numel(), src0.element_size(),
+                                    _stream(src0))
+    check(rc, "TGATHER")
+    return out
+
+
+def TGATHER_MASK(src, pattern, out=None):
+    """Keeps the columns of a 2-D tensor that `pattern` selects, packed contiguously (1-D result)."""
+    _need_cuda(src)
+    if src.dim() != 2:
+        raise PtoB200Error("TGATHER_MASK: expects a 2-D tensor")
+    rows, cols = src.shape
+    div, off = {1: (2, 0), 2: (2, 1), 3: (4, 0), 4: (4, 1), 5: (4, 2), 6: (4, 3), 7: (1, 0)}[int(pattern)]
+    out_cols = (cols - off + div - 1) // div
+    out = torch.empty(rows * out_cols, dtype=src.dtype, device=src.device) if out is None else out
+    with torch.cuda.device(src.device):
+        rc = lib().pto_b200_tgather_mask(_ptr(src), _ptr(out), rows, cols, int(pattern), src.element_size(),
+                                         _stream(src))
+    check(rc, "TGATHER_MASK")
+    return out
+
+
+def _row_reduce(fn_name, src, out):
+    _need_cuda(src)
+    if src.dim() != 2 or src.dtype != torch.float32:
+        raise PtoB200Error(f"{fn_name}: expects a 2-D float32 tensor")
+    rows, cols = src.shape
+    out = torch.empty(rows, dtype=torch.float32, device=src.device) if out is None else out
+    with torch.cuda.device(src.device):
+        rc = getattr(lib(), fn_name)(_ptr(src), _ptr(out), rows, cols, cols, _stream(src))
+    check(rc, fn_name)
+    return out
+
+
+def TROWMAX(src, out=None):
+    return _row_reduce("pto_b200_trowmax_f32", src, out)
+
+
+def TROWSUM(src, out=None):
+    return _row_reduce("pto_b200_trowsum_f32", src, out)
+
+
+def TEXP(src, out=None):
+    _need_cuda(src)
+    out = torch.empty_like(src) if out is None else out
+    with torch.cuda.device(src.device):
+        rc = lib().pto_b200_texp_f32(_ptr(src), _ptr(out), src.numel(), _stream(src))
+    check(rc, "TEXP")
+    return out
+
+
+def _binary(a, b, op, out):
+    _need_cuda(a, b)
+    if a.shape != b.shape or a.dtype != torch.float32 or b.dtype != torch.float32:
+        raise PtoB200Error("binary tile op: operands must be float32 of the same shape")
+    out = torch.empty_like(a) if out is None else out
+    with torch.cuda.device(a.device):
+        rc = lib().pto_b200_tbinary_f32(_ptr(a), _ptr(b), _ptr(out), a.numel(), op, _stream(a))
+    check(rc, "binary tile op")
+    return out
+
+
+def TADD(a, b, out=None):
+    return _binary(a, b, OP_ADD, out)
+
+
+def TSUB(a, b, out=None):
+    return _binary(a, b, OP_SUB, out)
+
+
+def TMAX(a, b, out=None):
+    return _binary(a, b, OP_MAX, out)
+
+
+def _scalar(a, s, op, out):
+    _need_cuda(a)
+    out = torch.empty_like(a) if out is None else out
+    with torch.cuda.device(a.device):
+        rc = lib().pto_b200_tscalar_f32(_ptr(a), float(s), _ptr(out), a.numel(), op, _stream(a))
+    check(rc, "scalar tile op")
+    return out
+
+
+def TMULS(a, s, out=None):
+    return _scalar(a, s, OP_MUL, out)
+
+
+def TADDS(a, s, out=None):
+    return _scalar(a, s, OP_ADD, out)
+
+
+def _rowexpand(a, row_scalar, op, out):
+    _need_cuda(a, row_scalar)
+    if a.dim() != 2 or row_scalar.numel() != a.shape[0]:
+        raise PtoB200Error("row-expand tile op: expects a 2-D tile and one scalar per row")
+    out = torch.empty_like(a) if out is None else out
+    with torch.cuda.device(a.device):
+        rc = lib().pto_b200_trowexpand_f32(_ptr(a), _ptr(row_scalar), _ptr(out), a.shape[0], a.shape[1], op,
+                                           _stream(a))
+    check(rc, "row-expand tile op")
+    return out
+
+
+def TROWEXPANDSUB(a, row_scalar, out=None):
+    return _rowexpand(a, row_scalar, OP_SUB, out)
+
+
+def TROWEXPANDMUL(a, row_scalar, out=None):
+    return _rowexpand(a, row_scalar, OP_MUL, out)
+
+
+def TROWEXPANDDIV(a, row_scalar, out=None):
+    return _rowexpand(a, row_scalar, OP_DIV, out)
+
+
+def gemm(a, b, b_layout=1, out=None):
+    """C[m,n] fp32 = A[m,k] fp16 @ B.  b_layout 0: b is (k, n); 1: b is (n, k), the reference kernel's layout.
+    A 3-D `a` (batch, m, k) with 3-D `b` runs `batch` independent problems."""
+    _need_cuda(a, b)
+    if a.dtype != torch.float16 or b.dtype != torch.float16:
+        raise PtoB200Error("gemm: operands must be float16")
+    batched = a.dim() == 3
+    m, k = a.shape[-2:]
+    n = b.shape[-1] if b_layout == 0 else b.shape[-2]
+    shape = (a.shape[0], m, n) if batched else (m, n)
+    out = torch.empty(shape, dtype=torch.float32, device=a.device) if out is None else out
+    with torch.cuda.device(a.device):
+        if batched:
+            rc = lib().pto_b200_gemm_f16f32_batched(_ptr(a), _ptr(b), _ptr(out), m, n, k, int(b_layout), a.shape[0],
+                                                    m * k, n * k, m * n, _stream(a))
+        else:
+            rc = lib().pto_b200_gemm_f16f32(_ptr(a), _ptr(b), _ptr(out), m, n, k, int(b_layout), _stream(a))
+    check(rc, "gemm")
+    return out
+
+
+def gemm_host(a, b, c, b_layout=1):
+    """Same product over HOST tensors (pinned or pageable): copies in, computes, copies out, synchronises."""
+    m, k = a.shape
+    n = b.shape[1] if b_layout == 0 else b.shape[0]
+    rc = lib().pto_b200_gemm_f16f32_host(_ptr(a), _ptr(b), _ptr(c), m, n, k, int(b_layout))
+    check(rc, "gemm_host")
+    return c
+
+
+def flash_attn_fwd(q, k, v, causal=False, scale=None, out_dtype=torch.float16, out=None):
+    """q: (..., sq, d), k / v: (..., sk, d) fp16 with the same leading (batch, heads) dims.  Returns O like q."""
+    _need_cuda(q, k, v)
+    if q.dtype != torch.float16 or k.dtype != torch.float16 or v.dtype != torch.float16:
+        raise PtoB200Error("flash_attn_fwd: operands must be float16")
+    sq, d = q.shape[-2:]
+    sk = k.shape[-2]
+    bh = q.numel() // (sq * d)
+    scale = (1.0 / d ** 0.5) if scale is None else float(scale)
+    out = torch.empty(q.shape, dtype=out_dtype, device=q.device) if out is None else out
+    with torch.cuda.device(q.device):
+        rc = lib().pto_b200_flash_attn_fwd_f16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), bh, sq, sk, d, int(bool(causal)),
+                                               scale, 1 if out_dtype == torch.float16 else 0, _stream(q))
+    check(rc, "flash_attn_fwd")
+    return out
+
+
+def flash_attn_fwd_host(q, k, v, o, causal=False, scale=None):
+    sq, d = q.shape[-2:]
+    sk = k.shape[-2]
+    bh = q.numel() // (sq * d)
+    scale = (1.0 / d ** 0.5) if scale is None else float(scale)
+    rc = lib().pto_b200_flash_attn_fwd_f16_host(_ptr(q), _ptr(k), _ptr(v), _ptr(o), bh, sq, sk, d,
+                                                int(bool(causal)), scale, 1 if o.dtype == torch.float16 else 0)
+    check(rc, "flash_attn_fwd_host")
+    return o
+
+
+def device_status(device=None):
+    """Reads and clears the device-side status record (synchronises the current stream)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        return lib().pto_b200_device_status(ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))

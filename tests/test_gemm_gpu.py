@@ -1,0 +1,110 @@
+"""GPU parity of the fp16 -> fp32 GEMM against the CPU oracle (the reference's tile program arithmetic).
+
+Tolerance: max relative error <= 2e-3 with the denominator floored at rms(expected), i.e.
+|got - want| <= 2e-3 * max(|want|, rms(want)) for every element (outputs that cancel to ~0 are judged
+against the typical magnitude).  The reference's own self-check rule (ResultCmp eps 1e-3,
+kernels/manual/a2a3/gemm_performance/main.cpp:72) is applied as well."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import pto_isa_b200 as pto
+from util import dev, host, rel_err_ok, result_cmp
+
+pytestmark = pytest.mark.gpu
+port = oracle.port
+
+
+def make(m, n, k, b_layout, seed):
+    r = np.random.default_rng(seed)
+    a = r.uniform(-1, 1, (m, k)).astype(np.float32).astype(np.float16)
+    b = r.uniform(-1, 1, (k, n) if b_layout == 0 else (n, k)).astype(np.float32).astype(np.float16)
+    return a, b
+
+
+@pytest.mark.parametrize("b_layout", [1, 0])
+@pytest.mark.parametrize("mnk", [(128, 256, 64), (128, 256, 256), (256, 512, 320), (384, 256, 1024),
+                                 (1536, 1536, 1536)])
+def test_gemm_matches_oracle(mnk, b_layout):
+    m, n, k = mnk
+    a, b = make(m, n, k, b_layout, seed=0)
+    want = port.gemm_f16f32(a, b, b_layout)
+    got = host(pto.gemm(dev(a), dev(b), b_layout))
+    ok, worst = rel_err_ok(got, want, 2e-3)
+    assert ok, f"max relative error {worst:.3e}"
+    assert result_cmp(want, got, 1e-3)
+    assert pto.device_status() == 0
+
+
+@pytest.mark.parametrize("b_layout", [1, 0])
+@pytest.mark.parametrize("mnk", [(100, 200, 72), (129, 264, 520), (1, 8, 8), (300, 40, 136)])
+def test_gemm_ragged_shapes(mnk, b_layout):
+    """m, n not multiples of the 128 x 256 tile and k not a multiple of 64: edges are zero-filled by TMA
+    on the way in and masked on the way out."""
+    m, n, k = mnk
+    a, b = make(m, n, k, b_layout, seed=1)
+    bf = b.astype(np.float64) if b_layout == 0 else b.astype(np.float64).T
+    want = a.astype(np.float64) @ bf
+    c = torch.full((m + 1, n), 7.0, device="cuda")  # guard row must stay untouched
+    pto.gemm(dev(a), dev(b), b_layout, out=c[:m])
+    got = host(c)
+    ok, worst = rel_err_ok(got[:m], want, 2e-3)
+    assert ok, f"max relative error {worst:.3e}"
+    assert (got[m] == 7.0).all()
+
+
+def test_gemm_golden(golden_dir):
+    z = np.load(os.path.join(golden_dir, "gemm.npz"))
+    got = host(pto.gemm(dev(z["a"]), dev(z["b_dn"]), 1))
+    assert result_cmp(z["golden"], got, 1e-3)
+
+
+def test_gemm_unsupported_shapes_are_errors():
+    a = torch.zeros(128, 68, dtype=torch.float16, device="cuda")  # k not a multiple of 8
+    b = torch.zeros(256, 68, dtype=torch.float16, device="cuda")
+    with pytest.raises(pto.PtoB200Error):
+        pto.gemm(a, b, 1)
+
+
+def test_gemm_batched_and_linearity():
+    a, b = make(256, 256, 128, 1, seed=3)
+    a2, _ = make(256, 256, 128, 1, seed=4)
+    da = torch.stack([dev(a), dev(a2)])
+    db = torch.stack([dev(b), dev(b)])
+    c = host(pto.gemm(da, db, 1))
+    assert np.array_equal(c[0], host(pto.gemm(dev(a), dev(b), 1)))
+    assert np.array_equal(c[1], host(pto.gemm(dev(a2), dev(b), 1)))
+    # exactness property: scaling A by 2 scales C by exactly 2 (powers of two commute with rounding)
+    c2 = host(pto.gemm(dev((a.astype(np.float32) * 2).astype(np.float16)), dev(b), 1))
+    assert np.array_equal(c2, 2 * c[0])
+
+
+def test_gemm_full_size_sampled_tiles():
+    """6144^3 (the headline size): the whole product runs on the GPU; sampled 128 x 256 C tiles are
+    recomputed by the oracle at full K, and a row/column checksum identity is checked on everything."""
+    m = n = k = 6144
+    a, b = make(m, n, k, 1, seed=6144)
+    da, db = dev(a), dev(b)
+    c = pto.gemm(da, db, 1)
+    assert pto.device_status() == 0
+    r = np.random.default_rng(0)
+    for _ in range(6):
+        ti, tj = int(r.integers(0, m // 128)), int(r.integers(0, n // 256))
+        r0, c0 = ti * 128, tj * 256
+        want = np.zeros((128, 256), np.float32)
+        import ctypes
+        P = lambda x: x.ctypes.data_as(ctypes.c_void_p)
+        asub = np.ascontiguousarray(a[r0:r0 + 128])
+        bsub = np.ascontiguousarray(b[c0:c0 + 256])
+        assert port.lib.pto_oracle_gemm_f16f32(P(asub), P(bsub), P(want), 128, 256, k, 1) == 0
+        got = host(c[r0:r0 + 128, c0:c0 + 256])
+        ok, worst = rel_err_ok(got, want, 2e-3)
+        assert ok, f"tile ({ti},{tj}) max relative error {worst:.3e}"
+    # checksum of checksums: sum_j C[i, j] == A[i, :] . (sum_j B[j, :]) for every row i (float64 on host)
+    colsum_b = b.astype(np.float64).sum(axis=0)
+    want_rows = a.astype(np.float64) @ colsum_b
+    got_rows = host(c.double().sum(dim=1))
+    assert np.abs(got_rows - want_rows).max() <= 1e-3 * np.sqrt(n * k / 9.0)
