@@ -1,10 +1,472 @@
+// Flash-attention forward for sm_100a (head size 128, fp16 Q/K/V, fp32 softmax, fp32 or fp16 O).
+//
+// The reference (kernels/manual/common/flash_atten/fa_performance_kernel.cpp:607-963, paths relative to the
+// reference root) runs a cube core and two vector cores per 128 query rows and passes every QK tile, P tile
+// and PV tile through global-memory FIFOs (TPUSH/TPOP, :782-821).  Here one CTA owns 256 query rows (two
+// 128-row tiles) of one head and all of those hand-offs stay on chip:
+//   compute_qk  (:280-352, TLOAD K + pto_macro_matmul)  -> TMA loads of K into swizzled shared memory,
+//                                                          S = Q K^T by tcgen05.mma into tensor memory
+//   compute_p   (:452-552, pto_macro_fa_softmax)        -> one thread per query row reads its S row from
+//                                                          tensor memory, updates the running max and sum,
+//                                                          writes P = exp(scale*(S - max)) as fp16 back into
+//                                                          tensor memory over S
+//   compute_pv  (:357-447)                              -> O += P V by tcgen05.mma with P read from tensor
+//                                                          memory and V (MN-major) from shared memory
+//   compute_gu  (:557-605, pto_macro_fa_gu)             -> O lives in tensor memory; it is rescaled there when
+//                                                          a row's max grows, and divided by the row sum on
+//                                                          the way out
+// Softmax conventions are the reference's (pto_macro_fa_softmax.hpp:81-97,141-184): the max is taken on
+// the raw logits, p = exp(scale * (x - max)) in fp32, the row sum accumulates the fp32 p, p is rounded to
+// fp16 for the second product, the causal mask hides keys beyond the query's own index, fully masked key
+// tiles are skipped.  The running max is only moved when it grows by more than 8 in the log2 domain; the
+// result O / l does not depend on which reference value is used (both carry the same factor).
+//
+// Warp roles (320 threads): warps 0-3 softmax of query tile 0, warps 4-7 softmax of query tile 1 (each thread
+// owns one query row, so row reductions need no shuffles), warp 8 TMA producer, warp 9 MMA issuer.  While
+// the softmax warps of one tile work, the tensor core runs the products of the other tile.
 #include "ptx.cuh"
 #include "internal.h"
+
+#include <cuda_fp16.h>
+
 namespace pto_b200 {
-int launch_flash_attn_fwd(const uint16_t *, const uint16_t *, const uint16_t *, void *, int, int, int, int, int, float,
-                          int, cudaStream_t)
+
+namespace {
+
+constexpr int kD = 128;           // head size
+constexpr int kTileQ = 128;       // query rows per tile (two tiles per CTA)
+constexpr int kTileKV = 128;      // keys per step
+constexpr int kStagesKV = 2;
+constexpr int kTileBytes = kTileQ * kD * 2; // 32 KiB: a 128 x 128 fp16 tile as two 64-column swizzled halves
+constexpr int kHalfBytes = kTileBytes / 2;  // 16 KiB
+constexpr int kThreads = 320;
+constexpr int kTmemCols = 512;
+constexpr int kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+
+struct Control {
+    uint64_t q_full;
+    uint64_t k_full[kStagesKV], k_empty[kStagesKV];
+    uint64_t v_full[kStagesKV], v_empty[kStagesKV];
+    uint64_t s_full[2]; // S tile ready for the softmax warps
+    uint64_t p_full[2]; // P tile written (and O rescaled) by the softmax warps
+    uint64_t o_full[2]; // last PV product complete
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+constexpr int kSmemBytes = 2 * kTileBytes + 2 * kStagesKV * kTileBytes + sizeof(Control) + 1024;
+
+__device__ __forceinline__ float ex2_approx(float x)
 {
-    set_error_text("flash attention: not built yet");
-    return kErrUnsupportedShape;
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
+
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi)
+{
+    uint32_t d;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
+template <bool kCausal, bool kOutF16>
+__global__ void __launch_bounds__(kThreads, 1)
+flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                      const __grid_constant__ CUtensorMap tmap_v, void *__restrict__ o_ptr, int sq, int sk,
+                      float scale_log2, DeviceStatus *status)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *smem_q = smem;                                   // 2 tiles
+    uint8_t *smem_k = smem + 2 * kTileBytes;                  // kStagesKV tiles
+    uint8_t *smem_v = smem_k + kStagesKV * kTileBytes;        // kStagesKV tiles
+    Control *ctl = reinterpret_cast<Control *>(smem_v + kStagesKV * kTileBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // work assignment: consecutive CTAs share a head (K/V stay in L2); within a head the query blocks
+    // with the most key tiles (causal) come first
+    const int q_blocks = (sq + 2 * kTileQ - 1) / (2 * kTileQ);
+    const int bh = blockIdx.x / q_blocks;
+    const int qb = q_blocks - 1 - (blockIdx.x % q_blocks);
+    const int kv_tiles = sk / kTileKV;
+    int n_kv[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int q0 = (2 * qb + t) * kTileQ;
+        if (q0 >= sq) {
+            n_kv[t] = 0;
+        } else if (kCausal) {
+            const int lim = q0 / kTileKV + 1; // tiles that hold at least one key <= the tile's last query
+            n_kv[t] = lim < kv_tiles ? lim : kv_tiles;
+        } else {
+            n_kv[t] = kv_tiles;
+        }
+    }
+    const int n_max = n_kv[0] > n_kv[1] ? n_kv[0] : n_kv[1];
+
+    if (threadIdx.x == 0) {
+        mbar_init(&ctl->q_full, 1);
+        for (int s = 0; s < kStagesKV; ++s) {
+            mbar_init(&ctl->k_full[s], 1);
+            mbar_init(&ctl->k_empty[s], 1);
+            mbar_init(&ctl->v_full[s], 1);
+            mbar_init(&ctl->v_empty[s], 1);
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&ctl->s_full[t], 1);
+            mbar_init(&ctl->p_full[t], kTileQ);
+            mbar_init(&ctl->o_full[t], 1);
+        }
+        ctl->abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_q);
+        tma_prefetch_desc(&tmap_k);
+        tma_prefetch_desc(&tmap_v);
+    }
+    if (warp == 9) {
+        tmem_alloc(&ctl->tmem_base, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+    volatile int *abort_flag = &ctl->abort_flag;
+
+    if (warp == 8) {
+        // ------------------------------------------------------------ TMA producer (TLOAD of Q, K, V)
+        if (lane == 0) {
+            int q_bytes = 0;
+            for (int t = 0; t < 2; ++t) {
+                q_bytes += (n_kv[t] > 0) ? kTileBytes : 0;
+            }
+            mbar_arrive_expect_tx(&ctl->q_full, q_bytes);
+            for (int t = 0; t < 2; ++t) {
+                if (n_kv[t] > 0) {
+                    const int q0 = (2 * qb + t) * kTileQ;
+                    tma_load_3d(smem_q + t * kTileBytes, &tmap_q, &ctl->q_full, 0, q0, bh);
+                    tma_load_3d(smem_q + t * kTileBytes + kHalfBytes, &tmap_q, &ctl->q_full, 64, q0, bh);
+                }
+            }
+            for (int j = 0; j < n_max; ++j) {
+                const int s = j % kStagesKV;
+                const uint32_t ph = (j / kStagesKV) & 1;
+                if (!mbar_wait(&ctl->k_empty[s], ph ^ 1u, abort_flag)) {
+                    break;
+                }
+                mbar_arrive_expect_tx(&ctl->k_full[s], kTileBytes);
+                tma_load_3d(smem_k + s * kTileBytes, &tmap_k, &ctl->k_full[s], 0, j * kTileKV, bh);
+                tma_load_3d(smem_k + s * kTileBytes + kHalfBytes, &tmap_k, &ctl->k_full[s], 64, j * kTileKV, bh);
+                if (!mbar_wait(&ctl->v_empty[s], ph ^ 1u, abort_flag)) {
+                    break;
+                }
+                mbar_arrive_expect_tx(&ctl->v_full[s], kTileBytes);
+                tma_load_3d(smem_v + s * kTileBytes, &tmap_v, &ctl->v_full[s], 0, j * kTileKV, bh);
+                tma_load_3d(smem_v + s * kTileBytes + kHalfBytes, &tmap_v, &ctl->v_full[s], 64, j * kTileKV, bh);
+            }
+        }
+    } else if (warp == 9) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc_f16(kTileQ, kTileKV, 0, 0); // Q (K-major) x K (K-major)
+            constexpr uint32_t idesc_o = make_idesc_f16(kTileQ, kD, 0, 1);      // P (tmem)   x V (MN-major)
+            const uint32_t q_base = smem_u32(smem_q);
+            const uint32_t k_base = smem_u32(smem_k);
+            const uint32_t v_base = smem_u32(smem_v);
+            bool ok = mbar_wait(&ctl->q_full, 0, abort_flag);
+
+            // S_t(j) = Q_t K_j^T : 8 steps of 16 along the head dimension (two 64-wide swizzled halves)
+            auto issue_s = [&](int t, int j) {
+                const int s = j % kStagesKV;
+                const uint32_t qa = q_base + t * kTileBytes;
+                const uint32_t kb = k_base + s * kTileBytes;
+                const uint32_t d_tmem = tmem_base + (t == 0 ? kColS0 : kColS1);
+#pragma unroll
+                for (int kk = 0; kk < kD / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
+                    tc_mma_f16_ss(d_tmem, make_sw128_desc(qa + off, 16, 1024), make_sw128_desc(kb + off, 16, 1024),
+                                  idesc_s, kk != 0 ? 1u : 0u);
+                }
+                tc_commit(&ctl->s_full[t]);
+            };
+            // O_t (+)= P_t(j) V_j : 8 steps of 16 keys; P from tensor memory (8 columns per step)
+            auto issue_pv = [&](int t, int j) {
+                const int s = j % kStagesKV;
+                const uint32_t vb = v_base + s * kTileBytes;
+                const uint32_t d_tmem = tmem_base + (t == 0 ? kColO0 : kColO1);
+                const uint32_t p_tmem = tmem_base + (t == 0 ? kColS0 : kColS1);
+#pragma unroll
+                for (int kk = 0; kk < kTileKV / 16; ++kk) {
+                    tc_mma_f16_ts(d_tmem, p_tmem + kk * 8, make_sw128_desc(vb + kk * (16 * 128), kHalfBytes, 1024),
+                                  idesc_o, (j | kk) != 0 ? 1u : 0u);
+                }
+            };
+
+            // prologue: first S tile of both query tiles
+            if (ok && n_max > 0) {
+                ok = mbar_wait(&ctl->k_full[0], 0, abort_flag);
+                if (ok) {
+                    tc_fence_after();
+                    for (int t = 0; t < 2; ++t) {
+                        if (n_kv[t] > 0) {
+                            issue_s(t, 0);
+                        }
+                    }
+                    tc_commit(&ctl->k_empty[0]);
+                }
+            }
+            for (int j = 0; j < n_max && ok; ++j) {
+                const int s = j % kStagesKV;
+                const uint32_t ph = (j / kStagesKV) & 1;
+                const int sn = (j + 1) % kStagesKV;
+                const uint32_t phn = ((j + 1) / kStagesKV) & 1;
+                bool v_ready = false, k_ready = false;
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (j >= n_kv[t]) {
+                        continue;
+                    }
+                    ok = mbar_wait(&ctl->p_full[t], j & 1, abort_flag);
+                    if (ok && !v_ready) {
+                        ok = mbar_wait(&ctl->v_full[s], ph, abort_flag);
+                        v_ready = true;
+                    }
+                    if (!ok) {
+                        break;
+                    }
+                    tc_fence_after();
+                    issue_pv(t, j);
+                    if (j == n_kv[t] - 1) {
+                        tc_commit(&ctl->o_full[t]);
+                    }
+                    if (j + 1 < n_kv[t]) {
+                        if (!k_ready) {
+                            ok = mbar_wait(&ctl->k_full[sn], phn, abort_flag);
+                            k_ready = true;
+                            if (!ok) {
+                                break;
+                            }
+                            tc_fence_after();
+                        }
+                        issue_s(t, j + 1);
+                    }
+                }
+                if (!ok) {
+                    break;
+                }
+                tc_commit(&ctl->v_empty[s]);
+                if (k_ready) {
+                    tc_commit(&ctl->k_empty[sn]);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax / rescale / output warps
+        const int t = warp >> 2;               // query tile of this warpgroup
+        const int quarter = warp & 3;          // TMEM lanes [32*quarter, +32)
+        const int row_in_tile = quarter * 32 + lane;
+        const int q_row = (2 * qb + t) * kTileQ + row_in_tile;
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        const uint32_t s_addr = lane_addr + (t == 0 ? kColS0 : kColS1);
+        const uint32_t o_addr = lane_addr + (t == 0 ? kColO0 : kColO1);
+        const int n = n_kv[t];
+        float m_run = -INFINITY; // running reference max (raw logits)
+        float l_run = 0.0f;      // running sum of p
+        bool ok = true;
+
+        for (int j = 0; j < n; ++j) {
+            if (!mbar_wait(&ctl->s_full[t], j & 1, abort_flag)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            uint32_t sr[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld_32x32(s_addr + c * 32, sr[c]);
+            }
+            tmem_ld_wait();
+            const bool diag = kCausal && (j * kTileKV + kTileKV - 1 > (2 * qb + t) * kTileQ);
+            float mx = -INFINITY;
+            if (diag) {
+                const int kv0 = j * kTileKV;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float x = __uint_as_float(sr[c][i]);
+                        x = (kv0 + c * 32 + i > q_row) ? -INFINITY : x;
+                        sr[c][i] = __float_as_uint(x);
+                        mx = fmaxf(mx, x);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        mx = fmaxf(mx, __uint_as_float(sr[c][i]));
+                    }
+                }
+            }
+            // move the reference max only when some row of this warp grew by more than 2^8
+            const float m_new = fmaxf(m_run, mx);
+            const bool grow = (m_new - m_run) * scale_log2 > 8.0f; // also true on the first tile (m_run = -inf)
+            if (__any_sync(0xffffffffu, grow)) {
+                if (j > 0) {
+                    const float alpha = ex2_approx((m_run - m_new) * scale_log2);
+                    l_run *= alpha;
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t orow[32];
+                        tmem_ld_32x32(o_addr + c * 32, orow);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                        }
+                        tmem_st_32x32(o_addr + c * 32, orow);
+                    }
+                }
+                m_run = m_new;
+            }
+            const float neg_m = -m_run * scale_log2;
+            float sum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c][i]), scale_log2, neg_m));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, neg_m));
+                    sum += p0 + p1;
+                    pk[i >> 1] = pack_f16x2(p0, p1);
+                }
+                // fp16 P over the first 64 columns of S: 16 packed columns per 32 keys
+                tmem_st_32x16(s_addr + c * 16, pk);
+            }
+            l_run += sum;
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&ctl->p_full[t]);
+        }
+
+        // output: O / l
+        if (ok && n > 0) {
+            if (mbar_wait(&ctl->o_full[t], 0, abort_flag)) {
+                tc_fence_after();
+                const float inv_l = 1.0f / l_run;
+                const int64_t row_off = (static_cast<int64_t>(bh) * sq + q_row) * kD;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t orow[32];
+                    tmem_ld_32x32(o_addr + c * 32, orow);
+                    tmem_ld_wait();
+                    if (kOutF16) {
+                        uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__half *>(o_ptr) + row_off + c * 32);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint4 v;
+                            v.x = pack_f16x2(__uint_as_float(orow[8 * i + 0]) * inv_l, __uint_as_float(orow[8 * i + 1]) * inv_l);
+                            v.y = pack_f16x2(__uint_as_float(orow[8 * i + 2]) * inv_l, __uint_as_float(orow[8 * i + 3]) * inv_l);
+                            v.z = pack_f16x2(__uint_as_float(orow[8 * i + 4]) * inv_l, __uint_as_float(orow[8 * i + 5]) * inv_l);
+                            v.w = pack_f16x2(__uint_as_float(orow[8 * i + 6]) * inv_l, __uint_as_float(orow[8 * i + 7]) * inv_l);
+                            dst[i] = v;
+                        }
+                    } else {
+                        float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(o_ptr) + row_off + c * 32);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            dst[i] = make_float4(__uint_as_float(orow[4 * i + 0]) * inv_l, __uint_as_float(orow[4 * i + 1]) * inv_l,
+                                                 __uint_as_float(orow[4 * i + 2]) * inv_l, __uint_as_float(orow[4 * i + 3]) * inv_l);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (ctl->abort_flag) {
+        for (int i = 0; i < 1024; ++i) {
+            __nanosleep(1000);
+        }
+        if (threadIdx.x == 0 && atomicCAS(&status->code, 0, kErrDeviceWaitTimeout) == 0) {
+            status->block = blockIdx.x;
+            status->where = 2;
+        }
+        __syncthreads();
+    }
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+template <bool kCausal, bool kOutF16>
+int launch_variant(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, void *o, int bh, int sq, int sk,
+                   float scale_log2, DeviceStatus *status, cudaStream_t stream)
+{
+    static bool attr_set = false;
+    if (!attr_set) {
+        const int rc = check_cuda(cudaFuncSetAttribute(flash_attn_fwd_kernel<kCausal, kOutF16>,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+                                  "cudaFuncSetAttribute(flash_attn)");
+        if (rc != kOk) {
+            return rc;
+        }
+        attr_set = true;
+    }
+    const int q_blocks = (sq + 2 * kTileQ - 1) / (2 * kTileQ);
+    flash_attn_fwd_kernel<kCausal, kOutF16>
+        <<<bh * q_blocks, kThreads, kSmemBytes, stream>>>(tq, tk, tv, o, sq, sk, scale_log2, status);
+    return check_launch();
+}
+
+} // namespace
+
+int launch_flash_attn_fwd(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o, int bh, int sq, int sk,
+                          int d, int causal, float scale, int out_f16, cudaStream_t stream)
+{
+    if (d != kD) {
+        set_error_text("flash attention: head size must be 128");
+        return kErrUnsupportedShape;
+    }
+    if ((sq % kTileQ) != 0 || (sk % kTileKV) != 0) {
+        set_error_text("flash attention: sequence lengths must be multiples of 128");
+        return kErrUnsupportedShape;
+    }
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+         reinterpret_cast<uintptr_t>(o)) & 15u) {
+        set_error_text("flash attention: operands must be 16-byte aligned");
+        return kErrUnsupportedShape;
+    }
+    CUtensorMap tq, tk, tv;
+    int rc = make_tmap_3d(&tq, q, 2, bh, sq, d, d, static_cast<uint64_t>(sq) * d, kTileQ, 64, true);
+    if (rc == kOk) {
+        rc = make_tmap_3d(&tk, k, 2, bh, sk, d, d, static_cast<uint64_t>(sk) * d, kTileKV, 64, true);
+    }
+    if (rc == kOk) {
+        rc = make_tmap_3d(&tv, v, 2, bh, sk, d, d, static_cast<uint64_t>(sk) * d, kTileKV, 64, true);
+    }
+    if (rc != kOk) {
+        return rc;
+    }
+    DeviceStatus *status = device_status_ptr();
+    if (status == nullptr) {
+        return kErrCuda;
+    }
+    const float scale_log2 = scale * 1.4426950408889634f;
+    if (causal) {
+        return out_f16 ? launch_variant<true, true>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream)
+                       : launch_variant<true, false>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
+    }
+    return out_f16 ? launch_variant<false, true>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream)
+                   : launch_variant<false, false>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
+}
+
 } // namespace pto_b200
