@@ -1,0 +1,426 @@
+#!/usr/bin/env python3
+"""Benchmark of the PTO hot path on B200: fp16 -> fp32 GEMM at m = n = k = 6144 (headline), with
+flash-attention forward and the vector tile ops measured in the same run as extras.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A step is one pass over one batch of independent problems: PROBLEMS_PER_RANK (8) GEMMs of 6144^3 per
+GPU, each with its own A, B and C (the batch's inputs, 1.2 GB, exceed the 126 MB L2, so operands come
+from HBM every time).  At 8 GPUs that is the 64-problem configuration; work per GPU is fixed (weak
+scaling) and no collective is on the data path; the all-gather of the outputs is timed separately and
+reported as `with_allgather`.  Under torchrun every rank runs its own problems; the time of the timed
+region is the maximum over ranks.
+
+One JSON line is printed by rank 0.  `value` is whole-job TFLOP/s with operands resident in HBM;
+`e2e` is the same metric through the C ABI's host-buffer entry point (pinned host operands, copies in
+and out inside the timed region); `roofline` describes the GEMM kernel (tensor bound) from CUDA-event
+launch durations measured inside the timed loop; `cpu_baseline` is the reference's CPU-simulation tile
+program timed on this box's host cores on a bounded sample of the same problem.
+
+`--impl reference` times that CPU-simulation program alone (all host threads), on the same metric.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M = N = K = 6144
+PROBLEMS_PER_RANK = 8
+FLOPS_PER_PROBLEM = 2.0 * M * N * K
+TILE_M, TILE_N = 128, 256
+TILE_FLOPS = 2.0 * TILE_M * TILE_N * K
+# dram__bytes_read.sum + dram__bytes_write.sum of one 6144^3 launch, from the ncu capture summarised in
+# profiles/gemm_f16f32_6144_ncu.md
+GEMM_DRAM_TRAFFIC_BYTES = 820.7e6
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {k: float(p[k]) for k in FALLBACK_PEAKS}, "measured"
+    except Exception:
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ------------------------------------------------------------------ clock sampling during the timed region
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx.append(float(s[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------ CPU side (reference arm / cpu_baseline)
+
+def cpu_gemm_sample(budget_s, min_tiles=1, max_tiles=64):
+    """Runs the CPU tile program on C tiles of the 6144^3 problem for about `budget_s` seconds.
+    Returns (tflops, info dict).  Uses the reference's own CPU simulation when its build is present."""
+    import ctypes
+
+    import numpy as np
+
+    import oracle
+    use_ref = oracle.ref is not None
+    lib = oracle.ref if use_ref else oracle.port
+    P = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    r = np.random.default_rng(0)
+    # a strip of the problem: the A rows of one tile row and the B rows (n x k layout) of `max_tiles` tile columns
+    tiles_n = min(max_tiles, N // TILE_N)
+    a = r.uniform(-1, 1, (TILE_M, K)).astype(np.float16)
+    b = r.uniform(-1, 1, (tiles_n * TILE_N, K)).astype(np.float16)
+    c = np.zeros((TILE_M, tiles_n * TILE_N), np.float32)
+
+    def run(n_tiles):
+        t0 = time.perf_counter()
+        if use_ref:
+            rc = lib.lib.pto_ref_gemm_f16f32_tiles(P(a), P(b), P(c), TILE_M, tiles_n * TILE_N, K, 1, 0, n_tiles)
+        else:
+            rc = lib.lib.pto_oracle_gemm_f16f32_window(P(a), P(b), P(c), TILE_M, tiles_n * TILE_N, K, 1, 0, TILE_M, 0,
+                                                       n_tiles * TILE_N)
+        assert rc == 0
+        return time.perf_counter() - t0
+
+    t1 = run(1)  # calibration (also warms the thread pool / page faults)
+    n_tiles = int(max(min_tiles, min(tiles_n, budget_s / max(t1, 1e-6))))
+    dt = run(n_tiles)
+    cores = (lib.lib.pto_ref_hardware_threads() if use_ref else lib.lib.pto_oracle_threads())
+    info = {"kind": "reference" if use_ref else "port", "cores": int(cores),
+            "sample": f"{n_tiles} C tiles of 128x256 at full k=6144 of the 6144^3 problem ({dt:.2f} s)",
+            "tiles": n_tiles, "seconds": dt}
+    return n_tiles * TILE_FLOPS / dt / 1e12, info
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    total_steps = args.steps + args.warmup
+    per_step_budget = max(0.5, min(10.0, 150.0 / max(total_steps, 1)))
+    vals, info = [], None
+    for i in range(total_steps):
+        v, info = cpu_gemm_sample(per_step_budget)
+        if i >= args.warmup:
+            vals.append((v, info["seconds"], info["tiles"]))
+    flops = sum(t * TILE_FLOPS for _, _, t in vals)
+    secs = sum(s for _, s, _ in vals)
+    value = flops / secs / 1e12
+    line = {
+        "impl": "reference", "metric": "fp16 GEMM TFLOPS (m=n=k=6144, fp32 accumulate and output)", "value": value,
+        "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * secs / max(len(vals), 1), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "gemm_f16f32 m=n=k=6144, B stored n x k (Layout::DN), uniform[-1,1) seeded",
+                   "note": "CPU simulation of the reference's tile program (TLOAD/TEXTRACT/TMATMUL/TSTORE, base "
+                           "128x256, k step 64) on host cores; each step is a bounded sample of C tiles"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"],
+                         "sample": info["sample"]},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ------------------------------------------------------------------ GPU arm
+
+def timed_events(torch, fn, iters):
+    """Per-launch durations (ms) with CUDA events on the current (launching) stream."""
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for s, e in evs:
+        s.record()
+        fn()
+        e.record()
+    torch.cuda.synchronize()
+    return [s.elapsed_time(e) for s, e in evs]
+
+
+def extras(torch, pto, peaks, peak_kind):
+    """Attention and vector tile ops, rank 0 only, short.  Buffers are rotated so inputs come from HBM."""
+    out = []
+
+    def bench(fn, warm, iters):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        s = torch.cuda.Event(enable_timing=True)
+        e = torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / iters
+
+    g = torch.Generator(device="cuda").manual_seed(5)
+    B, H, S, D = 4, 32, 4096, 128
+    q = (torch.randn(B * H, S, D, device="cuda", generator=g) / D ** 0.5).half()
+    k = torch.randn(B * H, S, D, device="cuda", generator=g).half()
+    v = torch.randn(B * H, S, D, device="cuda", generator=g).half()
+    o = torch.empty_like(q)
+    for causal in (False, True):
+        ms = bench(lambda: pto.flash_attn_fwd(q, k, v, causal=causal, scale=1.0, out=o), 3, 10)
+        flops = 4.0 * B * H * S * S * D if not causal else 4.0 * B * H * D * S * (S + 1) / 2
+        tf = flops / ms / 1e9
+        out.append({"workload": f"flash_attn_fwd f16 B=4 H=32 S=4096 D=128 causal={causal}", "value": tf,
+                    "unit": "TFLOP/s", "ms": ms,
+                    "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                 "frac": tf / peaks["bf16_tflops"], "peak_kind": peak_kind + " burst",
+                                 "frac_of_nominal_2250": tf / 2250.0}})
+    del q, k, v, o
+    n = 1 << 24
+    sets = 6
+    xs = [torch.randn(n, device="cuda", generator=g) for _ in range(sets)]
+    o16 = [torch.empty(n, dtype=torch.float16, device="cuda") for _ in range(sets)]
+    ob16 = [torch.empty(n, dtype=torch.bfloat16, device="cuda") for _ in range(sets)]
+    idx = [torch.randint(0, n, (n,), device="cuda", dtype=torch.int32, generator=g) for _ in range(sets)]
+    for ix in idx:  # >= 10 % duplicates
+        pos = torch.randint(0, n, (n // 10,), device="cuda", generator=g)
+        ix[pos] = ix[(pos * 2654435761) % n]
+    og = [torch.empty(n, device="cuda") for _ in range(sets)]
+    ctr = [0]
+
+    def rot(f):
+        def g_():
+            j = ctr[0] % sets
+            ctr[0] += 1
+            f(j)
+        return g_
+
+    cases = [
+        ("TCVT f32->f16 16M elements", 6.0, rot(lambda j: pto.TCVT(xs[j], torch.float16, out=o16[j]))),
+        ("TCVT f32->bf16 16M elements", 6.0, rot(lambda j: pto.TCVT(xs[j], torch.bfloat16, out=ob16[j]))),
+        ("TGATHER f32 by int32 index, 16M of 16M, 10% duplicates", 12.0,
+         rot(lambda j: pto.TGATHER(xs[j], idx[j], out=og[j]))),
+    ]
+    for name, bytes_per_elem, fn in cases:
+        ms = bench(fn, 2 * sets, 5 * sets)
+        gbs = n * bytes_per_elem / ms / 1e6
+        out.append({"workload": name, "value": gbs, "unit": "GB/s", "ms": ms,
+                    "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                 "frac": gbs / peaks["hbm_gbs"], "peak_kind": peak_kind,
+                                 "note": f"{sets} rotating buffer sets (> L2)"}})
+    return out
+
+
+def run_gpu_arm(args):
+    import torch
+
+    import pto_isa_b200 as pto
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the CUDA kernels are the only implementation")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    peaks, peak_kind = load_peaks()
+
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    P = PROBLEMS_PER_RANK
+    a = [(torch.rand(M, K, device="cuda", generator=g) * 2 - 1).half() for _ in range(P)]
+    b = [(torch.rand(N, K, device="cuda", generator=g) * 2 - 1).half() for _ in range(P)]  # n x k (Layout::DN)
+    c = torch.empty(P, M, N, device="cuda")
+
+    def step():
+        for i in range(P):
+            pto.gemm(a[i], b[i], 1, out=c[i])
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    launch_ms = []
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        # per-launch events on the launching stream: the roofline's kernel duration comes from these
+        evs = []
+        for i in range(P):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            pto.gemm(a[i], b[i], 1, out=c[i])
+            e.record()
+            evs.append((s, e))
+        launch_ms.append(evs)
+    ev1.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    elapsed_ms = ev0.elapsed_time(ev1)
+    if pto.device_status() != 0:
+        raise SystemExit("a kernel reported a device-side wait timeout")
+    t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(t.item())
+    total_flops = world * args.steps * P * FLOPS_PER_PROBLEM
+    value = total_flops / elapsed_ms / 1e9
+    per_launch = [s.elapsed_time(e) for evs in launch_ms for s, e in evs]
+    avg_launch_ms = sum(per_launch) / len(per_launch)
+
+    # all-gather of the outputs (every GPU ends up with every C), timed separately
+    with_allgather = None
+    if dist is not None:
+        full = torch.empty(world * P, M, N, device="cuda")
+        dist.all_gather_into_tensor(full, c)  # warm-up (communicator set-up)
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        dist.all_gather_into_tensor(full, c)
+        g1.record()
+        barrier()
+        tg = torch.tensor([g0.elapsed_time(g1)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        ag_ms = float(tg.item())
+        step_ms = elapsed_ms / args.steps
+        with_allgather = {"allgather_ms_per_step": ag_ms, "bytes_gathered_per_gpu": int(world * P * M * N * 4),
+                          "value": world * P * FLOPS_PER_PROBLEM / (step_ms + ag_ms) / 1e9, "unit": "TFLOP/s"}
+        del full
+
+    # end to end through the C ABI's host-buffer entry point, pinned host operands
+    e2e_steps = max(1, min(args.steps, 2))
+    ha = [torch.empty(M, K, dtype=torch.float16).pin_memory() for _ in range(2)]
+    hb = [torch.empty(N, K, dtype=torch.float16).pin_memory() for _ in range(2)]
+    hc = [torch.empty(M, N, dtype=torch.float32).pin_memory() for _ in range(2)]
+    for i in range(2):
+        ha[i].copy_(a[i])
+        hb[i].copy_(b[i])
+    pto.gemm_host(ha[0], hb[0], hc[0], 1)  # warm-up: staging buffers are allocated on first use
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        for i in range(P):
+            pto.gemm_host(ha[i % 2], hb[i % 2], hc[i % 2], 1)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    te = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_s = float(te.item())
+    e2e_value = world * e2e_steps * P * FLOPS_PER_PROBLEM / e2e_s / 1e12
+    e2e_check = bool(torch.equal(hc[1].cuda(), c[1]))  # host path of problem 1 equals its device path
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return 0
+
+    achieved = FLOPS_PER_PROBLEM / avg_launch_ms / 1e9
+    peak = peaks["bf16_tflops_sustained"]
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": GEMM_DRAM_TRAFFIC_BYTES, "peak_kind": f"{peak_kind} cuBLAS bf16 8192^3, sustained loop "
+                "(launches timed inside a long step)", "frac_of_burst": achieved / peaks["bf16_tflops"],
+                "frac_of_nominal_2250": achieved / 2250.0, "kernel": "gemm_f16f32_kernel<1>",
+                "avg_launch_ms": avg_launch_ms, "algorithmic_flops_per_launch": FLOPS_PER_PROBLEM}
+    cpu = None
+    extra = None
+    if world == 1:
+        cpu_tf, info = cpu_gemm_sample(12.0)
+        cpu = {"value": cpu_tf, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"],
+               "sample": info["sample"]}
+        extra = extras(torch, pto, peaks, peak_kind)
+    line = {
+        "metric": "fp16 GEMM TFLOPS (m=n=k=6144, fp32 accumulate and output)", "value": value, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": f"gemm_f16f32 m=n=k=6144, {P} independent problems per GPU per step "
+                               f"({world * P} in total), B stored n x k (Layout::DN), uniform[-1,1) seeded",
+                   "l2": "each step reads 1.2 GB of distinct operands per GPU (> 126 MB L2)",
+                   "parallelism": f"{world} GPU(s), problems sharded, no data-path collective"},
+        "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": int(P * (M * K + N * K) * 2),
+                "d2h_bytes_per_step": int(P * M * N * 4), "steps": e2e_steps, "matches_device_path": e2e_check,
+                "api": "pto_b200_gemm_f16f32_host (C ABI, pinned host buffers)"},
+        "gpu_launches": args.steps * P, "with_allgather": with_allgather, "extras": extra,
+    }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
