@@ -118,6 +118,19 @@ int pto_b200_gemm_f16f32_batched(const uint16_t *a, const uint16_t *b, float *c,
 /* Same product with HOST buffers: copies A and B in, runs the kernel, copies C out, synchronises. */
 int pto_b200_gemm_f16f32_host(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout);
 
+/* Host-buffer GEMM for callers that must not allocate device memory at call time: processes whose device memory
+ * is wholly owned by another allocator, plugins barred from allocation calls after start-up, or paths that cannot
+ * afford an allocation's implicit synchronisation.  It has no counterpart in the reference.  It calls no
+ * cudaMalloc / cudaFree or other allocating routine: the device copies of A, B and C and the kernel's status record
+ * live in a 36 MiB array built into the library, held by every GPU that loads it until the process exits.
+ * Problems whose operands need more than that (about m = n = k = 2048) return PTO_B200_ERR_TOO_LARGE.
+ * The first call on a device also looks up the array's device address; make that first call before any stream
+ * capture starts.  Calls run on the legacy default stream and return after C has been copied out; all calls share
+ * the array (it keeps the previous call's contents, the status record is cleared per call), so calls that overlap
+ * on the GPU would race - do not issue them concurrently. */
+int pto_b200_gemm_f16f32_host_static(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k,
+                                     int b_layout);
+
 /* ---- flash attention forward -------------------------------------------------------------------- */
 
 /* O = softmax(scale * Q K^T [+ causal mask]) V for batch*heads independent heads.

@@ -245,6 +245,11 @@ int pto_b200_gemm_f16f32_host(const uint16_t *a, const uint16_t *b, float *c, in
     return check_cuda(cudaStreamSynchronize(s), "cudaStreamSynchronize");
 }
 
+int pto_b200_gemm_f16f32_host_static(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout)
+{
+    return gemm_f16f32_host_static(a, b, c, m, n, k, b_layout);
+}
+
 // ------------------------------------------------------------------ flash attention
 
 int pto_b200_flash_attn_fwd_f16(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o, int batch_heads,

@@ -300,4 +300,142 @@ int launch_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, in
     return check_launch();
 }
 
+// ======================================================================================================
+// Host-buffer GEMM that allocates nothing.
+//
+// For callers that must not (or cannot) allocate device memory at call time: a host process whose device
+// memory is entirely owned by another allocator, so that a cudaMalloc of even a few bytes fails or
+// fragments its pool; a plugin running under a policy that forbids allocation calls after start-up; or a
+// latency-critical path where an allocation's implicit device synchronisation is not acceptable.  The
+// regular entry points allocate on first use (the status record; the host variants also their staging
+// buffers).  This one keeps everything it needs - the status record and the device copies of A, B and C -
+// in one file-scope array that every GPU loading the library holds from module load until exit.
+//
+// Layout of the array: [0, 4096) header (the status record the kernel's bounded waits report into),
+// then A, B and C, each rounded up to 256 bytes.  Problems that do not fit are rejected.
+// All calls share the array and it keeps the previous call's contents: the status record is cleared at
+// the start of every call, A and B are overwritten by the copies in, and every element of C that is
+// copied out is written by the kernel.  Two calls that overlap on the GPU (from two threads or
+// processes' worth of streams) would race on it; calls are serialised on the legacy default stream and
+// the function returns only after its result has been copied out.
+namespace {
+
+constexpr size_t kStaticScratchBytes = 36u << 20; // 36 MiB per GPU
+constexpr size_t kStaticHeaderBytes = 4096;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address; the address is
+// looked up once per device (with that device current) and cached here.
+constexpr int kMaxDevicesStatic = 64;
+unsigned char *g_static_scratch_addr[kMaxDevicesStatic] = {nullptr};
+
+size_t round256(size_t x)
+{
+    return (x + 255u) & ~static_cast<size_t>(255u);
+}
+
+} // namespace
+
+size_t gemm_static_scratch_bytes()
+{
+    return kStaticScratchBytes;
+}
+
+int gemm_f16f32_host_static(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout)
+{
+    if (a == nullptr || b == nullptr || c == nullptr || m <= 0 || n <= 0 || k <= 0 || (b_layout != 0 && b_layout != 1)) {
+        set_error_text("gemm_host_static: bad argument");
+        return kErrBadArgument;
+    }
+    if ((k % 8) != 0 || (b_layout == 0 && (n % 8) != 0)) {
+        set_error_text("gemm_host_static: k (and n for a k x n B) must be multiples of 8");
+        return kErrUnsupportedShape;
+    }
+    const size_t a_bytes = static_cast<size_t>(m) * k * 2, b_bytes = static_cast<size_t>(n) * k * 2,
+                 c_bytes = static_cast<size_t>(m) * n * 4;
+    const size_t need = kStaticHeaderBytes + round256(a_bytes) + round256(b_bytes) + round256(c_bytes);
+    if (need > kStaticScratchBytes) {
+        set_error_text("gemm_host_static: A, B and C need %zu bytes of device staging but the built-in scratch holds "
+                       "%zu (about m = n = k = 2048); use pto_b200_gemm_f16f32_host for larger problems",
+                       need, kStaticScratchBytes);
+        return kErrTooLarge;
+    }
+    int dev = 0;
+    int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc != kOk) {
+        return rc;
+    }
+    if (dev < 0 || dev >= kMaxDevicesStatic) {
+        set_error_text("gemm_host_static: device ordinal %d out of range", dev);
+        return kErrBadArgument;
+    }
+    if (g_static_scratch_addr[dev] == nullptr) {
+        // one-time set-up for this device: resolve the array's device address and raise the kernels'
+        // dynamic shared-memory limit (neither allocates)
+        unsigned char *p = nullptr;
+        rc = check_cuda(cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_static_scratch),
+                        "cudaGetSymbolAddress(static scratch)");
+        if (rc != kOk) {
+            return rc;
+        }
+        rc = check_cuda(cudaFuncSetAttribute(gemm_f16f32_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kSmemBytes),
+                        "cudaFuncSetAttribute(gemm)");
+        if (rc == kOk) {
+            rc = check_cuda(cudaFuncSetAttribute(gemm_f16f32_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 kSmemBytes),
+                            "cudaFuncSetAttribute(gemm)");
+        }
+        if (rc != kOk) {
+            return rc;
+        }
+        g_static_scratch_addr[dev] = p;
+    }
+    unsigned char *base = g_static_scratch_addr[dev];
+    DeviceStatus *status = reinterpret_cast<DeviceStatus *>(base);
+    uint16_t *da = reinterpret_cast<uint16_t *>(base + kStaticHeaderBytes);
+    uint16_t *db = reinterpret_cast<uint16_t *>(base + kStaticHeaderBytes + round256(a_bytes));
+    float *dc = reinterpret_cast<float *>(base + kStaticHeaderBytes + round256(a_bytes) + round256(b_bytes));
+    cudaStream_t s = nullptr; // legacy default stream: serialises the calls that share the array
+
+    // the status record must start at zero; everything else is overwritten before it is read
+    if ((rc = check_cuda(cudaMemsetAsync(status, 0, sizeof(DeviceStatus), s), "cudaMemsetAsync(status)")) != kOk ||
+        (rc = check_cuda(cudaMemcpyAsync(da, a, a_bytes, cudaMemcpyHostToDevice, s), "H2D A")) != kOk ||
+        (rc = check_cuda(cudaMemcpyAsync(db, b, b_bytes, cudaMemcpyHostToDevice, s), "H2D B")) != kOk) {
+        return rc;
+    }
+    CUtensorMap tmap_a, tmap_b;
+    rc = make_tmap_2d(&tmap_a, da, 2, m, k, k, BM, BK, true);
+    if (rc == kOk) {
+        rc = (b_layout == 1) ? make_tmap_2d(&tmap_b, db, 2, n, k, k, BN, BK, true)
+                             : make_tmap_2d(&tmap_b, db, 2, k, n, n, BK, 64, true);
+    }
+    if (rc != kOk) {
+        return rc;
+    }
+    const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    if (b_layout == 1) {
+        gemm_f16f32_kernel<1><<<grid, kThreads, kSmemBytes, s>>>(tmap_a, tmap_b, dc, m, n, k, status);
+    } else {
+        gemm_f16f32_kernel<0><<<grid, kThreads, kSmemBytes, s>>>(tmap_a, tmap_b, dc, m, n, k, status);
+    }
+    if ((rc = check_launch()) != kOk) {
+        return rc;
+    }
+    DeviceStatus host_status;
+    if ((rc = check_cuda(cudaMemcpyAsync(c, dc, c_bytes, cudaMemcpyDeviceToHost, s), "D2H C")) != kOk ||
+        (rc = check_cuda(cudaMemcpyAsync(&host_status, status, sizeof(DeviceStatus), cudaMemcpyDeviceToHost, s),
+                         "D2H status")) != kOk ||
+        (rc = check_cuda(cudaStreamSynchronize(s), "cudaStreamSynchronize")) != kOk) {
+        return rc;
+    }
+    if (host_status.code != 0) {
+        set_error_text("gemm_host_static: device-side wait gave up (code %d, block %d)", host_status.code,
+                       host_status.block);
+        return host_status.code;
+    }
+    return kOk;
+}
+
 } // namespace pto_b200

@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdint.h>
 
 namespace pto_b200 {
@@ -55,6 +56,10 @@ int launch_trowexpand(const float *a, const float *row_scalar, float *dst, int r
 // GEMM: C[m x n] fp32 = A[m x k] fp16 * B, B given k x n row-major (b_layout 0) or n x k row-major (1)
 int launch_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
                        cudaStream_t stream);
+
+// host-buffer GEMM whose device staging and status record live in a built-in static device array (no allocation)
+int gemm_f16f32_host_static(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout);
+size_t gemm_static_scratch_bytes();
 
 // flash attention forward; q/k/v/o are [batch*heads, seq, d] contiguous; out_f16 selects the output type
 int launch_flash_attn_fwd(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o, int bh, int sq, int sk,
