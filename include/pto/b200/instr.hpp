@@ -1,0 +1,629 @@
+// PTO instructions on B200.  Call shapes follow the reference's instruction wrappers
+// (include/pto/common/pto_instr.hpp, paths relative to the reference root): TASSIGN :24-41, TLOAD :127,
+// TSTORE :159, TMATMUL :464, TMATMUL_ACC :481, TEXTRACT :624, TGATHER :800 / :824, TCVT :864, TMOV :882,
+// TROWSUM :942, TROWMAX :990, TROWEXPAND{DIV,MUL,SUB} :1057-1073, TEXP :1129, TADDS :1161, TMULS :1188,
+// TADD / TSUB / TMUL / TMAX :56-120; results follow the CPU simulation (include/pto/cpu/*.hpp).
+//
+// How each instruction runs on a thread block (see runtime.hpp for the block context):
+//   TLOAD  -> Mat : every thread issues 16-byte asynchronous copies (cp.async) into the 128-byte-swizzled
+//                   layout the tensor core reads; completion is observed through set_flag(PIPE_MTE2, ...)
+//   TLOAD  -> Vec : cooperative copy into a plain row- or column-major tile in shared memory
+//   TEXTRACT / TMOV (Mat -> Left / Right) : shared-memory staging: the window of the staged tile is copied,
+//                   16 bytes per thread and step, into the operand tile in the swizzled layout the tensor core
+//                   reads (so the Mat tile may be reloaded as soon as the copy is done, as on the NPU)
+//   TMATMUL[_ACC] : one thread issues tcgen05.mma (M = 128, N = Right::Cols, K = 16 per instruction) with
+//                   shared-memory descriptors built from the two views; the accumulator is an Acc tile in
+//                   tensor memory; completion is observed through set_flag(PIPE_M, ...)
+//   TSTORE <- Acc : tcgen05.ld, each thread owns one accumulator row, 16 columns at a time
+//   vector instructions : the block sweeps the tile's valid region, one warp per row for reductions
+#pragma once
+
+#include <math.h>
+
+#include "runtime.hpp"
+
+namespace pto {
+
+// ---------------------------------------------------------------- helpers
+namespace b200 {
+
+template <typename TileT>
+PTO_INTERNAL int vec_offset(int r, int c)
+{
+    static_assert(TileT::SFractal == SLayout::NoneBox, "vector instructions work on plain (NoneBox) tiles");
+    return TileT::isRowMajor ? r * TileT::Cols + c : c * TileT::Rows + r;
+}
+
+#if PTO_B200_DEVICE_CODE
+__device__ __forceinline__ void block_sync()
+{
+    __syncthreads();
+}
+
+__device__ __forceinline__ uint64_t sw128_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 16-byte asynchronous copy global -> shared; `valid_bytes` < 16 zero-fills the remainder
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void *gsrc, int valid_bytes)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(valid_bytes)
+                 : "memory");
+}
+#endif
+
+// scalar conversions with the CPU simulation's semantics (include/pto/cpu/TCvt.hpp:28-92)
+template <typename D, typename S>
+PTO_INTERNAL D convert(S x, RoundMode mode)
+{
+#if PTO_B200_DEVICE_CODE
+    if constexpr (std::is_same_v<D, S>) {
+        return x;
+    } else if constexpr (std::is_same_v<S, float> && std::is_same_v<D, __half>) {
+        const uint32_t u = __float_as_uint(x);
+        if ((u & 0x7fffffffu) > 0x7f800000u) { // NaN keeps sign and top payload bits, quiet bit set
+            return __ushort_as_half(static_cast<unsigned short>(((u >> 16) & 0x8000u) | 0x7e00u | ((u >> 13) & 0x3ffu)));
+        }
+        return __float2half_rn(x);
+    } else if constexpr (std::is_same_v<S, float> && std::is_same_v<D, __nv_bfloat16>) {
+        const uint32_t u = __float_as_uint(x);
+        if ((u & 0x7fffffffu) > 0x7f800000u) {
+            return __ushort_as_bfloat16(static_cast<unsigned short>((u >> 16) | 0x40u));
+        }
+        return __float2bfloat16_rn(x);
+    } else if constexpr (std::is_same_v<S, __half> && std::is_same_v<D, float>) {
+        return __half2float(x);
+    } else if constexpr (std::is_same_v<S, __nv_bfloat16> && std::is_same_v<D, float>) {
+        return __bfloat162float(x);
+    } else if constexpr ((std::is_same_v<S, float> || std::is_same_v<S, __half>)&&std::is_integral_v<D>) {
+        double v;
+        if constexpr (std::is_same_v<S, float>) {
+            v = static_cast<double>(x);
+        } else {
+            v = static_cast<double>(__half2float(x));
+        }
+        double r;
+        switch (mode) {
+            case RoundMode::CAST_RINT: r = rint(v); break;
+            case RoundMode::CAST_ROUND: r = round(v); break;
+            case RoundMode::CAST_FLOOR: r = floor(v); break;
+            case RoundMode::CAST_CEIL: r = ceil(v); break;
+            case RoundMode::CAST_TRUNC: r = trunc(v); break;
+            case RoundMode::CAST_ODD: {
+                const double f = floor(v), frac = v - f;
+                r = (frac > 0.5) ? f + 1 : ((frac < 0.5) ? f : ((static_cast<long long>(f) & 1) ? f : f + 1));
+                break;
+            }
+            default: r = v; break;
+        }
+        return static_cast<D>(r);
+    } else if constexpr (std::is_integral_v<S> && std::is_same_v<D, __half>) {
+        return __float2half_rn(static_cast<float>(x));
+    } else {
+        return static_cast<D>(x);
+    }
+#else
+    (void)mode;
+    return D(x);
+#endif
+}
+
+} // namespace b200
+
+// ---------------------------------------------------------------- Tile::data
+template <TileType L, typename E, const int R, const int C, const BLayout B, const int RV, const int CV, const SLayout S,
+          const int SS, const PadValue P, const CompactMode CM>
+PTO_INTERNAL typename Tile<L, E, R, C, B, RV, CV, S, SS, P, CM>::TileDType Tile<L, E, R, C, B, RV, CV, S, SS, P, CM>::data()
+    const
+{
+#if PTO_B200_DEVICE_CODE
+    return reinterpret_cast<E *>(b200::arena_of<L>() + addr_);
+#else
+    return nullptr;
+#endif
+}
+
+// ---------------------------------------------------------------- TASSIGN
+template <typename T, typename AddrType>
+PTO_INST void TASSIGN(T &obj, AddrType addr)
+{
+    if constexpr (is_tile<T>::value) {
+        if constexpr (std::is_pointer_v<AddrType>) {
+#if PTO_B200_DEVICE_CODE
+            obj.addr_ = static_cast<uint32_t>(reinterpret_cast<const uint8_t *>(addr) - b200::arena_of<T::Loc>());
+#endif
+        } else {
+            if constexpr (T::Loc == TileType::Acc) {
+                // an L0C byte address: one tensor-memory column holds 128 rows x 4 bytes
+                obj.addr_ = static_cast<uint32_t>(addr) / 512u;
+            } else {
+                obj.addr_ = static_cast<uint32_t>(addr);
+            }
+        }
+    } else {
+        obj.SetAddr(reinterpret_cast<typename T::DType *>(addr));
+    }
+}
+
+// ---------------------------------------------------------------- TLOAD
+template <typename TileData, typename GlobalData, typename... WaitEvents>
+PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... events)
+{
+    static_assert(sizeof(typename TileData::DType) == sizeof(typename GlobalData::DType),
+                  "TLOAD: source and destination element sizes differ");
+    static_assert(GlobalData::layout == Layout::ND || GlobalData::layout == Layout::DN,
+                  "TLOAD: ND and DN global tensors are supported");
+#if PTO_B200_DEVICE_CODE
+    using T = typename TileData::DType;
+    const T *g = reinterpret_cast<const T *>(src.data());
+    const int64_t s3 = src.GetStride(3), s4 = src.GetStride(4);
+    if constexpr (TileData::Loc == TileType::Mat) {
+        static_assert(sizeof(T) == 2, "Mat tiles feed the tensor core: 16-bit elements");
+        // the global tensor's unit-stride dimension decides the staged layout
+        const bool cols_contig = (s4 == 1);
+        const int vr = dst.GetValidRow(), vc = dst.GetValidCol();
+        const int lines = cols_contig ? TileData::Rows : TileData::Cols;  // index of the strided dimension
+        const int span = cols_contig ? TileData::Cols : TileData::Rows;   // extent of the contiguous dimension
+        const int v_lines = cols_contig ? vr : vc, v_span = cols_contig ? vc : vr;
+        const int64_t line_stride = cols_contig ? s3 : s4;
+        const int chunks_per_line = span / 8;
+        const uint32_t base = b200::smem_u32(b200::arena() + dst.addr_);
+        const uint32_t pitch = static_cast<uint32_t>(lines) * 128u;
+        for (int q = threadIdx.x; q < lines * chunks_per_line; q += blockDim.x) {
+            const int l = q / chunks_per_line, ch = q - l * chunks_per_line;
+            const int e0 = ch * 8; // first element of this 16-byte chunk along the contiguous dimension
+            int valid = (l < v_lines) ? (v_span - e0) * 2 : 0;
+            valid = valid < 0 ? 0 : (valid > 16 ? 16 : valid);
+            const uint32_t off = (ch >> 3) * pitch + l * 128u + (((ch & 7) ^ (l & 7)) << 4);
+            b200::cp_async16(base + off, valid > 0 ? g + l * line_stride + e0 : g, valid);
+        }
+        dst.pitch_ = pitch;
+        dst.major_ = cols_contig ? b200::kColsContiguous : b200::kRowsContiguous;
+    } else {
+        static_assert(TileData::Loc == TileType::Vec, "TLOAD: destination must be a Vec or Mat tile");
+        T *t = dst.data();
+        const int vr = dst.GetValidRow(), vc = dst.GetValidCol();
+        const int64_t n0 = src.GetShape(0), n1 = src.GetShape(1), n2 = src.GetShape(2), n3 = src.GetShape(3),
+                      n4 = src.GetShape(4);
+        if (vr < TileData::Rows || vc < TileData::Cols) { // padding of the invalid region
+            for (int i = threadIdx.x; i < TileData::Numel; i += blockDim.x) {
+                t[i] = T(0);
+            }
+            __syncthreads();
+        }
+        if (n0 * n1 * n2 == 1) {
+            for (int i = threadIdx.x; i < vr * vc; i += blockDim.x) {
+                const int r = i / vc, c = i - r * vc;
+                t[b200::vec_offset<TileData>(r, c)] = g[r * s3 + c * s4];
+            }
+        } else {
+            // outer dimensions fold into tile rows (row-major tiles), as include/pto/cpu/TLoad.hpp:74-95 does
+            const int64_t rows = n0 * n1 * n2 * n3;
+            for (int64_t i = threadIdx.x; i < rows * n4; i += blockDim.x) {
+                const int64_t R = i / n4, c = i - R * n4;
+                const int64_t r = R % n3, o = R / n3, i2 = o % n2, i1 = (o / n2) % n1, i0 = o / (n2 * n1);
+                t[b200::vec_offset<TileData>(static_cast<int>(R), static_cast<int>(c))] =
+                    g[i0 * src.GetStride(0) + i1 * src.GetStride(1) + i2 * src.GetStride(2) + r * s3 + c * s4];
+            }
+        }
+        __syncthreads();
+    }
+#endif
+    return {};
+}
+
+// ---------------------------------------------------------------- TEXTRACT / TMOV into matrix operands
+// Window of `src` starting at (indexRow, indexCol) with the destination's shape
+// (docs/isa/TEXTRACT.md:14-18 in the reference).  Both tiles use the same kind of layout: "lines" along the
+// strided dimension, 128 bytes (64 elements) of the contiguous dimension per line and block, 16-byte chunks
+// XOR-swizzled with the line number inside each group of 8 lines.  The offset along the contiguous dimension
+// must be a multiple of 8 elements.
+template <typename DstTileData, typename SrcTileData, typename... WaitEvents>
+PTO_INST RecordEvent TEXTRACT(DstTileData &dst, SrcTileData &src, uint16_t indexRow = 0, uint16_t indexCol = 0,
+                              WaitEvents &... events)
+{
+    static_assert(SrcTileData::Loc == TileType::Mat, "TEXTRACT: source must be a Mat tile");
+    static_assert(DstTileData::Loc == TileType::Left || DstTileData::Loc == TileType::Right,
+                  "TEXTRACT: destination must be a Left or Right tile");
+    static_assert(sizeof(typename DstTileData::DType) == 2 && sizeof(typename SrcTileData::DType) == 2,
+                  "TEXTRACT: 16-bit elements");
+#if PTO_B200_DEVICE_CODE
+    const bool cols_contig = (src.major_ == b200::kColsContiguous);
+    const int line0 = cols_contig ? indexRow : indexCol;
+    const int chunk0 = (cols_contig ? indexCol : indexRow) >> 3;
+    const int lines = cols_contig ? DstTileData::Rows : DstTileData::Cols;
+    const int chunks_per_line = (cols_contig ? DstTileData::Cols : DstTileData::Rows) / 8;
+    const uint32_t dst_pitch = static_cast<uint32_t>(lines) * 128u;
+    const uint8_t *s = b200::arena_of<TileType::Mat>() + src.addr_;
+    uint8_t *d = b200::arena_of<DstTileData::Loc>() + dst.addr_;
+    for (int q = threadIdx.x; q < lines * chunks_per_line; q += blockDim.x) {
+        const int l = q / chunks_per_line, ch = q - l * chunks_per_line;
+        const int sl = line0 + l, sch = chunk0 + ch;
+        const uint32_t s_off = (sch >> 3) * src.pitch_ + sl * 128u + (((sch & 7) ^ (sl & 7)) << 4);
+        const uint32_t d_off = (ch >> 3) * dst_pitch + l * 128u + (((ch & 7) ^ (l & 7)) << 4);
+        *reinterpret_cast<uint4 *>(d + d_off) = *reinterpret_cast<const uint4 *>(s + s_off);
+    }
+    dst.pitch_ = dst_pitch;
+    // Left [M x K] is a K-major operand when its columns are contiguous; Right [K x N] when its rows are
+    const bool k_major = (DstTileData::Loc == TileType::Left) ? cols_contig : !cols_contig;
+    dst.major_ = k_major ? 0 : 1;
+    if (DstTileData::ValidRow == DYNAMIC) {
+        dst.RowMaskInternal = src.GetValidRow() - indexRow;
+    }
+    if (DstTileData::ValidCol == DYNAMIC) {
+        dst.ColMaskInternal = src.GetValidCol() - indexCol;
+    }
+#endif
+    return {};
+}
+
+// ---------------------------------------------------------------- TMATMUL / TMATMUL_ACC
+namespace b200 {
+template <typename TileAccT, typename TileLeftT, typename TileRightT>
+PTO_INTERNAL void matmul_issue(TileAccT &c, TileLeftT &a, TileRightT &b, bool accumulate)
+{
+    using AT = typename TileLeftT::DType;
+    static_assert(std::is_same_v<AT, typename TileRightT::DType>, "TMATMUL: operand types differ");
+    static_assert(std::is_same_v<AT, __half> || std::is_same_v<AT, __nv_bfloat16>, "TMATMUL: fp16 / bf16 operands");
+    static_assert(std::is_same_v<typename TileAccT::DType, float>, "TMATMUL: fp32 accumulator");
+    static_assert(TileLeftT::Loc == TileType::Left && TileRightT::Loc == TileType::Right &&
+                      TileAccT::Loc == TileType::Acc,
+                  "TMATMUL: expects (Acc, Left, Right)");
+    static_assert(TileLeftT::Rows <= 128 && TileLeftT::Cols % 16 == 0 && TileLeftT::Cols == TileRightT::Rows,
+                  "TMATMUL: m <= 128, k a multiple of 16");
+    static_assert(TileRightT::Cols % 16 == 0 && TileRightT::Cols <= 256 && TileAccT::Cols == TileRightT::Cols,
+                  "TMATMUL: n a multiple of 16, at most 256");
+#if PTO_B200_DEVICE_CODE
+    if (threadIdx.x == 0) {
+        constexpr uint32_t kBf16 = std::is_same_v<AT, __nv_bfloat16> ? 1u : 0u;
+        const uint32_t idesc = (1u << 4) | (kBf16 << 7) | (kBf16 << 10) | (static_cast<uint32_t>(a.major_) << 15) |
+                               (static_cast<uint32_t>(b.major_) << 16) |
+                               (static_cast<uint32_t>(TileRightT::Cols >> 3) << 17) | (8u << 24); // M = 128
+        const uint32_t d_tmem = control()->tmem_base + c.addr_;
+        const uint32_t a_addr = smem_u32(arena_of<TileType::Left>() + a.addr_);
+        const uint32_t b_addr = smem_u32(arena_of<TileType::Right>() + b.addr_);
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < TileLeftT::Cols / 16; ++kk) {
+            const uint32_t k0 = kk * 16;
+            // K-major view: 16 k-values are 32 bytes inside a 128-byte line, blocks of 64 k are `pitch` apart;
+            // MN-major view: 16 k-values are 16 lines of 128 bytes, 64-element blocks of M/N are `pitch` apart
+            const uint64_t a_desc = (a.major_ == 0)
+                                        ? sw128_desc(a_addr + (k0 >> 6) * a.pitch_ + (k0 & 63u) * 2u, 16, 1024)
+                                        : sw128_desc(a_addr + k0 * 128u, a.pitch_, 1024);
+            const uint64_t b_desc = (b.major_ == 0)
+                                        ? sw128_desc(b_addr + (k0 >> 6) * b.pitch_ + (k0 & 63u) * 2u, 16, 1024)
+                                        : sw128_desc(b_addr + k0 * 128u, b.pitch_, 1024);
+            mma_f16(d_tmem, a_desc, b_desc, idesc, (accumulate || kk != 0) ? 1u : 0u);
+        }
+    }
+#endif
+}
+} // namespace b200
+
+template <typename TileAccT, typename TileLeftT, typename TileRightT, typename... WaitEvents>
+PTO_INST RecordEvent TMATMUL(TileAccT &cMatrix, TileLeftT &aMatrix, TileRightT &bMatrix, WaitEvents &... events)
+{
+    b200::matmul_issue(cMatrix, aMatrix, bMatrix, false);
+    return {};
+}
+
+template <typename TileAccT, typename TileLeftT, typename TileRightT, typename... WaitEvents>
+PTO_INST RecordEvent TMATMUL_ACC(TileAccT &cOutMatrix, TileAccT &cInMatrix, TileLeftT &aMatrix, TileRightT &bMatrix,
+                                 WaitEvents &... events)
+{
+    // the accumulator is updated in place (the reference's kernels pass the same tile twice)
+    (void)cInMatrix;
+    b200::matmul_issue(cOutMatrix, aMatrix, bMatrix, true);
+    return {};
+}
+
+// ---------------------------------------------------------------- TSTORE
+template <typename GlobalData, typename TileData, typename... WaitEvents>
+PTO_INST RecordEvent TSTORE(GlobalData &dst, TileData &src, WaitEvents &... events)
+{
+#if PTO_B200_DEVICE_CODE
+    using GT = typename GlobalData::DType;
+    GT *g = dst.data();
+    const int64_t s3 = dst.GetStride(3), s4 = dst.GetStride(4);
+    const int vr = src.GetValidRow(), vc = src.GetValidCol();
+    if constexpr (TileData::Loc == TileType::Acc) {
+        static_assert(std::is_same_v<typename TileData::DType, float>, "TSTORE: fp32 accumulator tiles");
+        static_assert(TileData::Cols % 16 == 0, "TSTORE: accumulator width must be a multiple of 16");
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int quarter = warp & 3;   // tensor-memory lanes [32 * quarter, +32) are readable by this warp
+        const int group = warp >> 2, groups = blockDim.x >> 7;
+        const int row = quarter * 32 + lane;
+        const uint32_t taddr = b200::control()->tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + src.addr_;
+        b200::tc_fence_after();
+        for (int c0 = group * 16; c0 < TileData::Cols; c0 += groups * 16) {
+            uint32_t r[16];
+            b200::tmem_ld16(taddr + c0, r);
+            if (row < vr) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (c0 + j < vc) {
+                        const float v = __uint_as_float(r[j]);
+                        if constexpr (std::is_same_v<GT, float>) {
+                            g[row * s3 + (c0 + j) * s4] = v;
+                        } else {
+                            g[row * s3 + (c0 + j) * s4] = b200::convert<GT, float>(v, RoundMode::CAST_RINT);
+                        }
+                    }
+                }
+            }
+        }
+        b200::tc_fence_before();
+    } else {
+        static_assert(TileData::Loc == TileType::Vec, "TSTORE: source must be a Vec or Acc tile");
+        static_assert(sizeof(typename TileData::DType) == sizeof(GT), "TSTORE: element sizes differ");
+        using T = typename TileData::DType;
+        const T *t = src.data();
+        T *gt = reinterpret_cast<T *>(g);
+        for (int i = threadIdx.x; i < vr * vc; i += blockDim.x) {
+            const int r = i / vc, c = i - r * vc;
+            gt[r * s3 + c * s4] = t[b200::vec_offset<TileData>(r, c)];
+        }
+    }
+#endif
+    return {};
+}
+
+// ---------------------------------------------------------------- TMOV
+template <typename DstTileData, typename SrcTileData, typename... WaitEvents>
+PTO_INST RecordEvent TMOV(DstTileData &dst, SrcTileData &src, WaitEvents &... events)
+{
+    if constexpr (SrcTileData::Loc == TileType::Mat) {
+        return TEXTRACT(dst, src, 0, 0);
+    } else {
+#if PTO_B200_DEVICE_CODE
+        if constexpr (SrcTileData::Loc == TileType::Acc) {
+            static_assert(DstTileData::Loc == TileType::Vec, "TMOV from an Acc tile goes to a Vec tile");
+            const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quarter = warp & 3;
+            const int group = warp >> 2, groups = blockDim.x >> 7;
+            const int row = quarter * 32 + lane;
+            const uint32_t taddr = b200::control()->tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + src.addr_;
+            typename DstTileData::DType *t = dst.data();
+            b200::tc_fence_after();
+            for (int c0 = group * 16; c0 < SrcTileData::Cols; c0 += groups * 16) {
+                uint32_t r[16];
+                b200::tmem_ld16(taddr + c0, r);
+                if (row < src.GetValidRow()) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (c0 + j < src.GetValidCol()) {
+                            t[b200::vec_offset<DstTileData>(row, c0 + j)] =
+                                b200::convert<typename DstTileData::DType, float>(__uint_as_float(r[j]),
+                                                                                  RoundMode::CAST_RINT);
+                        }
+                    }
+                }
+            }
+            b200::tc_fence_before();
+        } else {
+            const int vr = src.GetValidRow(), vc = src.GetValidCol();
+            for (int i = threadIdx.x; i < vr * vc; i += blockDim.x) {
+                const int r = i / vc, c = i - r * vc;
+                dst.data()[b200::vec_offset<DstTileData>(r, c)] = src.data()[b200::vec_offset<SrcTileData>(r, c)];
+            }
+        }
+        __syncthreads();
+#endif
+        return {};
+    }
+}
+
+// ---------------------------------------------------------------- elementwise vector instructions
+namespace b200 {
+template <typename DstT, typename SrcT, typename F>
+PTO_INTERNAL void for_each_valid(DstT &dst, SrcT &src, F f)
+{
+#if PTO_B200_DEVICE_CODE
+    const int vr = src.GetValidRow(), vc = src.GetValidCol();
+    for (int i = threadIdx.x; i < vr * vc; i += blockDim.x) {
+        const int r = i / vc, c = i - r * vc;
+        f(dst.data()[vec_offset<DstT>(r, c)], r, c);
+    }
+    __syncthreads();
+#endif
+}
+} // namespace b200
+
+template <typename TileDataD, typename TileDataS, typename... WaitEvents>
+PTO_INST RecordEvent TCVT(TileDataD &dst, TileDataS &src, RoundMode mode, WaitEvents &... events)
+{
+    b200::for_each_valid(dst, src, [&](typename TileDataD::DType &d, int r, int c) {
+        d = b200::convert<typename TileDataD::DType, typename TileDataS::DType>(
+            src.data()[b200::vec_offset<TileDataS>(r, c)], mode);
+    });
+    return {};
+}
+
+template <typename TileDataD, typename TileDataS, typename... WaitEvents>
+PTO_INST RecordEvent TCVT(TileDataD &dst, TileDataS &src, RoundMode mode, SaturationMode, WaitEvents &... events)
+{
+    return TCVT(dst, src, mode);
+}
+
+template <typename TileData, typename... WaitEvents>
+PTO_INST RecordEvent TEXP(TileData &dst, TileData &src, WaitEvents &... events)
+{
+    b200::for_each_valid(dst, dst, [&](typename TileData::DType &d, int r, int c) {
+#if PTO_B200_DEVICE_CODE
+        d = b200::convert<typename TileData::DType, float>(
+            expf(b200::convert<float, typename TileData::DType>(src.data()[b200::vec_offset<TileData>(r, c)],
+                                                                RoundMode::CAST_RINT)),
+            RoundMode::CAST_RINT);
+#endif
+    });
+    return {};
+}
+
+#define PTO_B200_BINARY(NAME, EXPR)                                                                              \
+    template <typename TileData, typename... WaitEvents>                                                         \
+    PTO_INST RecordEvent NAME(TileData &dst, TileData &src0, TileData &src1, WaitEvents &... events)             \
+    {                                                                                                            \
+        b200::for_each_valid(dst, dst, [&](typename TileData::DType &d, int r, int c) {                          \
+            const auto a = src0.data()[b200::vec_offset<TileData>(r, c)];                                        \
+            const auto b = src1.data()[b200::vec_offset<TileData>(r, c)];                                        \
+            d = (EXPR);                                                                                          \
+        });                                                                                                      \
+        return {};                                                                                               \
+    }
+PTO_B200_BINARY(TADD, a + b)
+PTO_B200_BINARY(TSUB, a - b)
+PTO_B200_BINARY(TMUL, a *b)
+PTO_B200_BINARY(TDIV, a / b)
+PTO_B200_BINARY(TMAX, (a < b) ? b : a)
+PTO_B200_BINARY(TMIN, (b < a) ? b : a)
+#undef PTO_B200_BINARY
+
+#define PTO_B200_SCALAR(NAME, EXPR)                                                                              \
+    template <typename TileData, typename... WaitEvents>                                                         \
+    PTO_INST RecordEvent NAME(TileData &dst, TileData &src0, typename TileData::DType s, WaitEvents &... events)  \
+    {                                                                                                            \
+        b200::for_each_valid(dst, dst, [&](typename TileData::DType &d, int r, int c) {                          \
+            const auto a = src0.data()[b200::vec_offset<TileData>(r, c)];                                        \
+            d = (EXPR);                                                                                          \
+        });                                                                                                      \
+        return {};                                                                                               \
+    }
+PTO_B200_SCALAR(TADDS, a + s)
+PTO_B200_SCALAR(TMULS, a *s)
+#undef PTO_B200_SCALAR
+
+// dst[r, c] = src0[r, c] op src1[r, 0]  (include/pto/cpu/TRowExpandOp.hpp:38-76)
+#define PTO_B200_ROWEXPAND(NAME, EXPR)                                                                           \
+    template <typename TileDst, typename TileSrc1, typename... WaitEvents>                                       \
+    PTO_INST RecordEvent NAME(TileDst &dst, TileDst &src0, TileSrc1 &src1, WaitEvents &... events)               \
+    {                                                                                                            \
+        b200::for_each_valid(dst, dst, [&](typename TileDst::DType &d, int r, int c) {                           \
+            const auto a = src0.data()[b200::vec_offset<TileDst>(r, c)];                                         \
+            const auto s = static_cast<typename TileDst::DType>(src1.data()[b200::vec_offset<TileSrc1>(r, 0)]);  \
+            d = (EXPR);                                                                                          \
+        });                                                                                                      \
+        return {};                                                                                               \
+    }
+PTO_B200_ROWEXPAND(TROWEXPANDSUB, a - s)
+PTO_B200_ROWEXPAND(TROWEXPANDMUL, a *s)
+PTO_B200_ROWEXPAND(TROWEXPANDDIV, a / s)
+PTO_B200_ROWEXPAND(TROWEXPANDADD, a + s)
+#undef PTO_B200_ROWEXPAND
+
+// ---------------------------------------------------------------- row reductions (one warp per row)
+namespace b200 {
+template <bool kIsMax, typename TileOut, typename TileIn>
+PTO_INTERNAL void row_reduce(TileOut &dst, TileIn &src)
+{
+#if PTO_B200_DEVICE_CODE
+    using AccT = float;
+    const int vr = src.GetValidRow(), vc = src.GetValidCol();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int r = warp; r < vr; r += warps) {
+        AccT acc = kIsMax ? -INFINITY : 0.0f;
+        for (int c = lane; c < vc; c += 32) {
+            const AccT v = convert<float, typename TileIn::DType>(src.data()[vec_offset<TileIn>(r, c)],
+                                                                  RoundMode::CAST_RINT);
+            acc = kIsMax ? fmaxf(acc, v) : acc + v;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const AccT other = __shfl_xor_sync(0xffffffffu, acc, o);
+            acc = kIsMax ? fmaxf(acc, other) : acc + other;
+        }
+        if (lane == 0) {
+            dst.data()[vec_offset<TileOut>(r, 0)] = convert<typename TileOut::DType, float>(acc, RoundMode::CAST_RINT);
+        }
+    }
+    __syncthreads();
+#endif
+}
+} // namespace b200
+
+template <typename TileOut, typename TileIn, typename TileTmp, typename... WaitEvents>
+PTO_INST RecordEvent TROWMAX(TileOut &dst, TileIn &src, TileTmp &tmp, WaitEvents &... events)
+{
+    b200::row_reduce<true>(dst, src);
+    return {};
+}
+
+template <typename TileOut, typename TileIn, typename TileTmp, typename... WaitEvents>
+PTO_INST RecordEvent TROWSUM(TileOut &dst, TileIn &src, TileTmp &tmp, WaitEvents &... events)
+{
+    b200::row_reduce<false>(dst, src);
+    return {};
+}
+
+// ---------------------------------------------------------------- TGATHER
+// index form (include/pto/cpu/TGather.hpp:68-100): out-of-range and negative indices give 0
+template <typename TileDataD, typename TileDataS0, typename TileDataS1, typename... WaitEvents>
+PTO_INST RecordEvent TGATHER(TileDataD &dst, TileDataS0 &src0, TileDataS1 &src1, WaitEvents &... events)
+{
+    static_assert(sizeof(typename TileDataS1::DType) == 4, "TGATHER: 32-bit indices");
+    static_assert(std::is_same_v<typename TileDataD::DType, typename TileDataS0::DType>, "TGATHER: types differ");
+    b200::for_each_valid(dst, dst, [&](typename TileDataD::DType &d, int r, int c) {
+        const int64_t raw = static_cast<int64_t>(src1.data()[b200::vec_offset<TileDataS1>(r, c)]);
+        if (raw < 0 || raw >= static_cast<int64_t>(TileDataS0::Numel)) {
+            d = typename TileDataD::DType(0);
+        } else {
+            const int sr = static_cast<int>(raw / TileDataS0::Cols), sc = static_cast<int>(raw % TileDataS0::Cols);
+            d = src0.data()[b200::vec_offset<TileDataS0>(sr, sc)];
+        }
+    });
+    return {};
+}
+
+// mask form (include/pto/cpu/TGather.hpp:102-129): selected columns of every row, packed contiguously
+template <typename DstTileData, typename SrcTileData, MaskPattern maskPattern, typename... WaitEvents>
+PTO_INST RecordEvent TGATHER(DstTileData &dst, SrcTileData &src, WaitEvents &... events)
+{
+    static_assert(DstTileData::isRowMajor && SrcTileData::isRowMajor, "TGATHER (mask): row-major tiles");
+#if PTO_B200_DEVICE_CODE
+    constexpr int div = (maskPattern == MaskPattern::P1111) ? 1
+                        : ((maskPattern == MaskPattern::P0101 || maskPattern == MaskPattern::P1010) ? 2 : 4);
+    constexpr int off = (maskPattern == MaskPattern::P1010 || maskPattern == MaskPattern::P0010)   ? 1
+                        : (maskPattern == MaskPattern::P0100)                                      ? 2
+                        : (maskPattern == MaskPattern::P1000)                                      ? 3
+                                                                                                   : 0;
+    const int vr = src.GetValidRow(), vc = src.GetValidCol();
+    const int per_row = (vc - off + div - 1) / div;
+    for (int i = threadIdx.x; i < vr * per_row; i += blockDim.x) {
+        const int r = i / per_row, k = i - r * per_row;
+        dst.data()[i] = src.data()[b200::vec_offset<SrcTileData>(r, k * div + off)];
+    }
+    __syncthreads();
+#endif
+    return {};
+}
+
+} // namespace pto

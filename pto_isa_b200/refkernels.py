@@ -1,0 +1,86 @@
+"""Builds the reference's own tile programs against this repository's PTO headers (include/pto/) with nvcc.
+
+The device code of the reference kernels is compiled unchanged.  One thing is not C++ that nvcc accepts:
+Ascend's launch statement `kernel<<<blocks, l2ctrl, stream>>>(args)` (the second launch argument is an L2
+control pointer there, a block shape in CUDA).  `rewrite_launches` turns exactly those statements into
+`PTO_B200_LAUNCH((kernel), blocks, stream, args)`; nothing else in the file is touched.  The rewritten
+text only ever exists in the build directory.
+
+The result, pto_isa_b200/libpto_b200_refkernels.so, is built where the reference tree is available and
+travels with the package; tests that need it skip when it is absent.
+"""
+import os
+import re
+import shutil
+import subprocess
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+OUT = os.path.join(HERE, "libpto_b200_refkernels.so")
+WRAPPER = os.path.join(HERE, "csrc", "refkernels", "wrappers.cu.in")
+
+_LAUNCH = re.compile(r"<<<\s*([^,<>]+?)\s*,\s*nullptr\s*,\s*([^,<>]+?)\s*>>>\s*\(")
+
+
+def rewrite_launches(text):
+    """`callee<<<blocks, nullptr, stream>>>(args);` -> `PTO_B200_LAUNCH((callee), blocks, stream, args);`"""
+    out = []
+    pos = 0
+    while True:
+        m = _LAUNCH.search(text, pos)
+        if not m:
+            out.append(text[pos:])
+            break
+        # the callee expression runs back to the previous statement / block boundary
+        start = max(text.rfind(";", pos, m.start()), text.rfind("{", pos, m.start()), text.rfind("}", pos, m.start())) + 1
+        callee = text[start:m.start()]
+        lead = callee[: len(callee) - len(callee.lstrip())]
+        # the argument list runs to the matching parenthesis
+        depth, i = 1, m.end()
+        while depth:
+            depth += {"(": 1, ")": -1}.get(text[i], 0)
+            i += 1
+        args = text[m.end(): i - 1].strip()
+        out.append(text[pos:start])
+        out.append(f"{lead}PTO_B200_LAUNCH(({callee.strip()}), {m.group(1)}, {m.group(2)}"
+                   + (f", {args}" if args else "") + ")")
+        pos = i
+    return "".join(out)
+
+
+def build(reference="/root/reference", force=False, verbose=False):
+    """Returns the path of the built library, or None when the reference tree is not present."""
+    if not os.path.isdir(os.path.join(reference, "kernels")):
+        return OUT if os.path.exists(OUT) else None
+    if not force and os.path.exists(OUT) and os.path.getmtime(OUT) >= max(
+            os.path.getmtime(os.path.join(dp, f)) for dp, _, fs in os.walk(os.path.join(ROOT, "include", "pto"))
+            for f in fs) and os.path.getmtime(OUT) >= os.path.getmtime(WRAPPER):
+        return OUT
+    build_dir = os.path.join(HERE, "build", "refkernels")
+    os.makedirs(build_dir, exist_ok=True)
+    sources = {
+        "gemm_performance_kernel.inc": "kernels/manual/a2a3/gemm_performance/gemm_performance_kernel.cpp",
+    }
+    for name, rel in sources.items():
+        with open(os.path.join(reference, rel)) as f:
+            text = rewrite_launches(f.read())
+        with open(os.path.join(build_dir, name), "w") as f:
+            f.write(text)
+    tu = os.path.join(build_dir, "wrappers.cu")
+    with open(WRAPPER) as f:
+        body = f.read().replace("@REFERENCE@", reference)
+    with open(tu, "w") as f:
+        f.write(body)
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--extended-lambda",
+           "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", build_dir, "-shared", "-o", OUT, tu]
+    if verbose:
+        cmd[1:1] = ["-Xptxas", "-v"]
+        print(" ".join(cmd))
+    subprocess.check_call(cmd)
+    return OUT
+
+
+if __name__ == "__main__":
+    import sys
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

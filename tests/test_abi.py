@@ -86,3 +86,16 @@ def test_cpu_tensors_are_rejected():
         p.TCVT(torch.zeros(8), torch.float16)
     with pytest.raises(p.PtoB200Error):
         p.gemm(torch.zeros(128, 64, dtype=torch.float16), torch.zeros(256, 64, dtype=torch.float16))
+
+
+def test_ascend_launch_statements_are_rewritten():
+    """The one non-C++-for-nvcc construct of the reference kernels: `k<<<blocks, l2ctrl, stream>>>(args)`."""
+    from pto_isa_b200.refkernels import rewrite_launches
+    src = ("void f() {\n    Kern<T, a,\n         b><<<blockDim, nullptr, stream>>>(out, src0, src1);\n"
+           "    warm<<<24, nullptr, stream>>>();\n    g(x);\n}\n")
+    out = rewrite_launches(src)
+    assert "<<<" not in out
+    assert "PTO_B200_LAUNCH((Kern<T, a,\n         b>), blockDim, stream, out, src0, src1);" in out
+    assert "PTO_B200_LAUNCH((warm), 24, stream);" in out
+    assert out.endswith("    g(x);\n}\n")
+    assert rewrite_launches("no launches here;") == "no launches here;"
