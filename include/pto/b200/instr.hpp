@@ -400,6 +400,10 @@ PTO_INST RecordEvent TSTORE(GlobalData &dst, TileData &src, WaitEvents &... even
 }
 
 // ---------------------------------------------------------------- TMOV
+//   Mat -> Left / Right : the whole-tile form of TEXTRACT
+//   Vec -> Left / Right : staging of a plain 16-bit tile into the swizzled operand layout
+//   Acc -> Vec          : tensor memory to shared memory (with conversion to the destination type)
+//   Vec -> Vec          : copy of the valid region
 template <typename DstTileData, typename SrcTileData, typename... WaitEvents>
 PTO_INST RecordEvent TMOV(DstTileData &dst, SrcTileData &src, WaitEvents &... events)
 {
@@ -430,6 +434,29 @@ PTO_INST RecordEvent TMOV(DstTileData &dst, SrcTileData &src, WaitEvents &... ev
                 }
             }
             b200::tc_fence_before();
+        } else if constexpr (DstTileData::Loc == TileType::Left || DstTileData::Loc == TileType::Right) {
+            static_assert(SrcTileData::Loc == TileType::Vec && SrcTileData::SFractal == SLayout::NoneBox,
+                          "TMOV into a matrix operand: from a Mat tile or a plain Vec tile");
+            static_assert(sizeof(typename SrcTileData::DType) == 2, "matrix operands are 16-bit");
+            static_assert(SrcTileData::Rows == DstTileData::Rows && SrcTileData::Cols == DstTileData::Cols,
+                          "TMOV: shapes differ");
+            constexpr bool cols_contig = SrcTileData::isRowMajor;
+            constexpr int lines = cols_contig ? DstTileData::Rows : DstTileData::Cols;
+            constexpr int span = cols_contig ? DstTileData::Cols : DstTileData::Rows;
+            static_assert(span % 8 == 0, "TMOV: the contiguous extent must be a multiple of 8 elements");
+            constexpr int chunks_per_line = span / 8;
+            constexpr uint32_t dst_pitch = static_cast<uint32_t>(lines) * 128u;
+            const uint8_t *s = reinterpret_cast<const uint8_t *>(src.data());
+            uint8_t *d = b200::arena_of<DstTileData::Loc>() + dst.addr_;
+            for (int q = threadIdx.x; q < lines * chunks_per_line; q += blockDim.x) {
+                const int l = q / chunks_per_line, ch = q - l * chunks_per_line;
+                const uint32_t d_off = (ch >> 3) * dst_pitch + l * 128u + (((ch & 7) ^ (l & 7)) << 4);
+                *reinterpret_cast<uint4 *>(d + d_off) =
+                    *reinterpret_cast<const uint4 *>(s + (static_cast<uint32_t>(l) * span + ch * 8) * 2u);
+            }
+            dst.pitch_ = dst_pitch;
+            const bool k_major = (DstTileData::Loc == TileType::Left) ? cols_contig : !cols_contig;
+            dst.major_ = k_major ? 0 : 1;
         } else {
             const int vr = src.GetValidRow(), vc = src.GetValidCol();
             for (int i = threadIdx.x; i < vr * vc; i += blockDim.x) {

@@ -49,6 +49,13 @@ def build(force=False, verbose=False):
         if verbose:
             print(" ".join(cmd))
         subprocess.check_call(cmd)
+    # tile programs written against include/pto/ (the PTO surface on this backend)
+    prog_src = os.path.join(CSRC, "pto_programs", "programs.cu")
+    prog_out = os.path.join(HERE, "libpto_b200_programs.so")
+    pto_headers = [os.path.join(dp, f) for dp, _, fs in os.walk(os.path.join(HERE, "..", "include", "pto")) for f in fs]
+    if force or _stale(prog_out, [prog_src] + pto_headers):
+        subprocess.check_call([_nvcc()] + flags + ["--extended-lambda", "-I", os.path.join(HERE, "..", "include"),
+                                                  "-shared", "-o", prog_out, prog_src])
     for so, src in SHIMS.items():
         src_path = os.path.join(CSRC, src)
         out = os.path.join(HERE, so)

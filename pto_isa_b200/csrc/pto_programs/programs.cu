@@ -1,0 +1,296 @@
+// Tile programs written against the PTO surface of this repository (include/pto/), in the style of the
+// reference's unit-test kernels (tests/cpu/st/testcase/*/*_kernel.cpp in the reference): they exercise the
+// instructions of the attention and vector path that the GEMM tile program does not - TGATHER (both forms),
+// the softmax chain TROWMAX / TROWEXPANDSUB / TMULS / TEXP / TROWSUM / TROWEXPANDDIV, TCVT, TMOV between
+// tensor memory, vector tiles and matrix operands, and both operand layouts of TMATMUL.
+// Built into libpto_b200_programs.so; used by tests/test_pto_programs_gpu.py.
+// Windows of the shared-memory arena for this translation unit: 116 KiB for Vec / Mat tiles (the attention
+// program below needs 113 KiB), 32 KiB for Left tiles, the rest (73 KiB) for Right tiles.
+#define PTO_B200_L0A_OFFSET (116 * 1024)
+#define PTO_B200_L0B_OFFSET (148 * 1024)
+#include <pto/pto-inst.hpp>
+
+using namespace pto;
+
+// ---------------------------------------------------------------- TGATHER, index form
+template <typename T, int kSrcRows, int kSrcCols, int kDstRows, int kDstCols>
+AICORE inline void ProgGatherIndex(__gm__ T *out, __gm__ T *src0, __gm__ int32_t *idx)
+{
+    using G0 = GlobalTensor<T, Shape<1, 1, 1, kSrcRows, kSrcCols>, Stride<1, 1, 1, kSrcCols, 1>>;
+    using G1 = GlobalTensor<int32_t, Shape<1, 1, 1, kDstRows, kDstCols>, Stride<1, 1, 1, kDstCols, 1>>;
+    using GD = GlobalTensor<T, Shape<1, 1, 1, kDstRows, kDstCols>, Stride<1, 1, 1, kDstCols, 1>>;
+    using Src0Tile = Tile<TileType::Vec, T, kSrcRows, kSrcCols, BLayout::RowMajor, -1, -1>;
+    using IdxTile = Tile<TileType::Vec, int32_t, kDstRows, kDstCols, BLayout::RowMajor, -1, -1>;
+    using DstTile = Tile<TileType::Vec, T, kDstRows, kDstCols, BLayout::RowMajor, -1, -1>;
+    Src0Tile s0(kSrcRows, kSrcCols);
+    IdxTile it(kDstRows, kDstCols);
+    DstTile dt(kDstRows, kDstCols);
+    TASSIGN(s0, 0x0);
+    TASSIGN(it, kSrcRows * kSrcCols * sizeof(T));
+    TASSIGN(dt, kSrcRows * kSrcCols * sizeof(T) + kDstRows * kDstCols * sizeof(int32_t));
+    G0 g0(src0);
+    G1 g1(idx);
+    GD gd(out);
+    TLOAD(s0, g0);
+    TLOAD(it, g1);
+    set_flag(PIPE_MTE2, PIPE_V, EVENT_ID0);
+    wait_flag(PIPE_MTE2, PIPE_V, EVENT_ID0);
+    TGATHER(dt, s0, it);
+    set_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    wait_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    TSTORE(gd, dt);
+}
+
+// ---------------------------------------------------------------- TGATHER, mask form
+template <typename T, int kRows, int kCols, MaskPattern kPattern, int kDiv>
+AICORE inline void ProgGatherMask(__gm__ T *out, __gm__ T *src)
+{
+    using GS = GlobalTensor<T, Shape<1, 1, 1, kRows, kCols>, Stride<1, 1, 1, kCols, 1>>;
+    using GD = GlobalTensor<T, Shape<1, 1, 1, kRows, kCols / kDiv>, Stride<1, 1, 1, kCols / kDiv, 1>>;
+    using SrcTile = Tile<TileType::Vec, T, kRows, kCols, BLayout::RowMajor>;
+    using DstTile = Tile<TileType::Vec, T, kRows, kCols / kDiv, BLayout::RowMajor>;
+    SrcTile st;
+    DstTile dt;
+    TASSIGN(st, 0x0);
+    TASSIGN(dt, kRows * kCols * sizeof(T));
+    GS gs(src);
+    GD gd(out);
+    TLOAD(st, gs);
+    set_flag(PIPE_MTE2, PIPE_V, EVENT_ID0);
+    wait_flag(PIPE_MTE2, PIPE_V, EVENT_ID0);
+    TGATHER<DstTile, SrcTile, kPattern>(dt, st);
+    set_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    wait_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    TSTORE(gd, dt);
+}
+
+// ---------------------------------------------------------------- row softmax of a fp32 tile
+template <int kRows, int kCols>
+AICORE inline void ProgRowSoftmax(__gm__ float *out, __gm__ float *rowmax_out, __gm__ float *rowsum_out,
+                                  __gm__ float *in, float scale)
+{
+    using G = GlobalTensor<float, Shape<1, 1, 1, kRows, kCols>, Stride<1, 1, 1, kCols, 1>>;
+    using GR = GlobalTensor<float, Shape<1, 1, 1, kRows, 1>, Stride<1, 1, 1, 1, kRows>, Layout::DN>;
+    using X = Tile<TileType::Vec, float, kRows, kCols, BLayout::RowMajor>;
+    using R = Tile<TileType::Vec, float, kRows, 1, BLayout::ColMajor>;
+    X x, p;
+    R mx, sm;
+    TASSIGN(x, 0x0);
+    TASSIGN(p, kRows * kCols * sizeof(float));
+    TASSIGN(mx, 2 * kRows * kCols * sizeof(float));
+    TASSIGN(sm, 2 * kRows * kCols * sizeof(float) + kRows * sizeof(float));
+    G gin(in), gout(out);
+    GR gmx(rowmax_out), gsm(rowsum_out);
+    TLOAD(x, gin);
+    set_flag(PIPE_MTE2, PIPE_V, EVENT_ID0);
+    wait_flag(PIPE_MTE2, PIPE_V, EVENT_ID0);
+    TROWMAX(mx, x, p);
+    TROWEXPANDSUB(p, x, mx);
+    TMULS(p, p, scale);
+    TEXP(p, p);
+    TROWSUM(sm, p, x);
+    TROWEXPANDDIV(p, p, sm);
+    set_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    wait_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    TSTORE(gout, p);
+    TSTORE(gmx, mx);
+    TSTORE(gsm, sm);
+}
+
+// ---------------------------------------------------------------- one TMATMUL with B given k x n (Layout::ND)
+template <int M, int K, int N>
+AICORE inline void ProgMatmulND(__gm__ float *out, __gm__ half *a, __gm__ half *b)
+{
+    using GA = GlobalTensor<half, Shape<1, 1, 1, M, K>, Stride<M * K, M * K, M * K, K, 1>>;
+    using GB = GlobalTensor<half, Shape<1, 1, 1, K, N>, Stride<K * N, K * N, K * N, N, 1>>;
+    using GC = GlobalTensor<float, Shape<1, 1, 1, M, N>, Stride<M * N, M * N, M * N, N, 1>>;
+    using MatA = Tile<TileType::Mat, half, M, K, BLayout::ColMajor, M, K, SLayout::RowMajor>;
+    using MatB = Tile<TileType::Mat, half, K, N, BLayout::RowMajor, K, N, SLayout::ColMajor>;
+    MatA am;
+    MatB bm;
+    TileLeft<half, M, K> al;
+    TileRight<half, K, N> br;
+    TileAcc<float, M, N> acc;
+    TASSIGN(am, 0x0);
+    TASSIGN(bm, M * K * sizeof(half));
+    TASSIGN(al, 0x0);
+    TASSIGN(br, 0x0);
+    TASSIGN(acc, 0x0);
+    GA ga(a);
+    GB gb(b);
+    GC gc(out);
+    TLOAD(am, ga);
+    TLOAD(bm, gb);
+    set_flag(PIPE_MTE2, PIPE_MTE1, EVENT_ID0);
+    wait_flag(PIPE_MTE2, PIPE_MTE1, EVENT_ID0);
+    TMOV(al, am);
+    TMOV(br, bm);
+    set_flag(PIPE_MTE1, PIPE_M, EVENT_ID0);
+    wait_flag(PIPE_MTE1, PIPE_M, EVENT_ID0);
+    TMATMUL(acc, al, br);
+    set_flag(PIPE_M, PIPE_FIX, EVENT_ID0);
+    wait_flag(PIPE_M, PIPE_FIX, EVENT_ID0);
+    TSTORE(gc, acc);
+}
+
+// ---------------------------------------------------------------- attention for one head, one key tile
+// The instruction sequence of the reference's attention test (tests/cpu/st/testcase/tflashattn/tflashattn_kernel.cpp:
+// 84-105) with the flash-attention kernel's conventions: fp16 Q / K / V, max on the raw logits,
+// p = exp(scale * (x - max)), fp32 row sum, fp16 P for the second product, division at the end.
+// Q: S0 x D, K, V: S1 x D (row-major), O: S0 x D fp32.  S0 = 128, S1 = 128, D = 64.
+template <int S0, int S1, int D>
+AICORE inline void ProgAttentionHead(__gm__ float *o, __gm__ half *q, __gm__ half *k, __gm__ half *v, float scale)
+{
+    using GQ = GlobalTensor<half, Shape<1, 1, 1, S0, D>, Stride<S0 * D, S0 * D, S0 * D, D, 1>>;
+    using GKT = GlobalTensor<half, Shape<1, 1, 1, D, S1>, Stride<S1 * D, S1 * D, S1 * D, 1, D>, Layout::DN>;
+    using GV = GlobalTensor<half, Shape<1, 1, 1, S1, D>, Stride<S1 * D, S1 * D, S1 * D, D, 1>>;
+    using GO = GlobalTensor<float, Shape<1, 1, 1, S0, D>, Stride<S0 * D, S0 * D, S0 * D, D, 1>>;
+    using QMat = Tile<TileType::Mat, half, S0, D, BLayout::ColMajor, S0, D, SLayout::RowMajor>;
+    using KTMat = Tile<TileType::Mat, half, D, S1, BLayout::RowMajor, D, S1, SLayout::ColMajor>;
+    using VMat = Tile<TileType::Mat, half, S1, D, BLayout::RowMajor, S1, D, SLayout::ColMajor>;
+    using Scores = Tile<TileType::Vec, float, S0, S1, BLayout::RowMajor>;
+    using Probs = Tile<TileType::Vec, half, S0, S1, BLayout::RowMajor>;
+    using RowRed = Tile<TileType::Vec, float, S0, 1, BLayout::ColMajor>;
+    using OutVec = Tile<TileType::Vec, float, S0, D, BLayout::RowMajor>;
+
+    QMat qm;
+    KTMat km;
+    VMat vm;
+    TileLeft<half, S0, D> ql;
+    TileRight<half, D, S1> kr;
+    TileAcc<float, S0, S1> sacc;
+    Scores x;
+    Probs ph;
+    RowRed mx, sm;
+    TileLeft<half, S0, S1> pl;
+    TileRight<half, S1, D> vr;
+    TileAcc<float, S0, D> oacc;
+    OutVec ov;
+
+    // Vec / Mat window: [Q | K^T | V] staging, later reused by the fp16 P tile; [scores], later reused by O; row state
+    constexpr uint32_t kQ = 0, kK = kQ + S0 * D * 2, kV = kK + D * S1 * 2, kX = kV + S1 * D * 2;
+    constexpr uint32_t kP = 0, kMx = kX + S0 * S1 * 4, kSm = kMx + S0 * 4;
+    static_assert(S0 * S1 * 2 <= kX, "the fp16 P tile must fit in the staging area it reuses");
+    TASSIGN(qm, kQ);
+    TASSIGN(km, kK);
+    TASSIGN(vm, kV);
+    TASSIGN(x, kX);
+    TASSIGN(ph, kP);
+    TASSIGN(mx, kMx);
+    TASSIGN(sm, kSm);
+    TASSIGN(ov, kX); // reuses the score tile's space once P has been written
+    TASSIGN(ql, 0x0);
+    TASSIGN(pl, 0x0);
+    TASSIGN(kr, 0x0);
+    TASSIGN(vr, 0x8000);
+    TASSIGN(sacc, 0x0);
+    TASSIGN(oacc, S1 * 512); // tensor-memory columns after the score accumulator
+
+    GQ gq(q);
+    GKT gk(k);
+    GV gv(v);
+    GO go(o);
+    TLOAD(qm, gq);
+    TLOAD(km, gk);
+    TLOAD(vm, gv);
+    set_flag(PIPE_MTE2, PIPE_MTE1, EVENT_ID0);
+    wait_flag(PIPE_MTE2, PIPE_MTE1, EVENT_ID0);
+    TMOV(ql, qm);
+    TMOV(kr, km);
+    TMOV(vr, vm);
+    set_flag(PIPE_MTE1, PIPE_M, EVENT_ID0);
+    wait_flag(PIPE_MTE1, PIPE_M, EVENT_ID0);
+    TMATMUL(sacc, ql, kr);
+    set_flag(PIPE_M, PIPE_V, EVENT_ID0);
+    wait_flag(PIPE_M, PIPE_V, EVENT_ID0);
+    TMOV(x, sacc);
+    TROWMAX(mx, x, x);
+    TROWEXPANDSUB(x, x, mx);
+    TMULS(x, x, scale);
+    TEXP(x, x);
+    TROWSUM(sm, x, x);
+    TCVT(ph, x, RoundMode::CAST_ROUND);
+    TMOV(pl, ph);
+    set_flag(PIPE_MTE1, PIPE_M, EVENT_ID1);
+    wait_flag(PIPE_MTE1, PIPE_M, EVENT_ID1);
+    TMATMUL(oacc, pl, vr);
+    set_flag(PIPE_M, PIPE_V, EVENT_ID1);
+    wait_flag(PIPE_M, PIPE_V, EVENT_ID1);
+    TMOV(ov, oacc);
+    TROWEXPANDDIV(ov, ov, sm);
+    set_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    wait_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    TSTORE(go, ov);
+}
+
+// ---------------------------------------------------------------- host entry points
+#pragma GCC visibility push(default)
+extern "C" {
+
+int pto_prog_tgather_index_f32(float *out, const float *src0, const int32_t *idx, void *stream)
+{
+    return pto::b200::launch(1, stream, [=] __device__() {
+               ProgGatherIndex<float, 32, 1024, 16, 64>(out, const_cast<float *>(src0), const_cast<int32_t *>(idx));
+           }) == cudaSuccess
+               ? 0
+               : 3;
+}
+
+int pto_prog_tgather_index_b16(int16_t *out, const int16_t *src0, const int32_t *idx, void *stream)
+{
+    return pto::b200::launch(1, stream, [=] __device__() {
+               ProgGatherIndex<int16_t, 16, 1024, 16, 128>(out, const_cast<int16_t *>(src0),
+                                                           const_cast<int32_t *>(idx));
+           }) == cudaSuccess
+               ? 0
+               : 3;
+}
+
+int pto_prog_tgather_mask_f32(float *out, const float *src, int pattern, void *stream)
+{
+    float *s = const_cast<float *>(src);
+    cudaError_t e;
+    switch (pattern) {
+        case 1: e = pto::b200::launch(1, stream, [=] __device__() { ProgGatherMask<float, 64, 256, MaskPattern::P0101, 2>(out, s); }); break;
+        case 2: e = pto::b200::launch(1, stream, [=] __device__() { ProgGatherMask<float, 64, 256, MaskPattern::P1010, 2>(out, s); }); break;
+        case 3: e = pto::b200::launch(1, stream, [=] __device__() { ProgGatherMask<float, 64, 256, MaskPattern::P0001, 4>(out, s); }); break;
+        case 4: e = pto::b200::launch(1, stream, [=] __device__() { ProgGatherMask<float, 64, 256, MaskPattern::P0010, 4>(out, s); }); break;
+        case 5: e = pto::b200::launch(1, stream, [=] __device__() { ProgGatherMask<float, 64, 256, MaskPattern::P0100, 4>(out, s); }); break;
+        case 6: e = pto::b200::launch(1, stream, [=] __device__() { ProgGatherMask<float, 64, 256, MaskPattern::P1000, 4>(out, s); }); break;
+        case 7: e = pto::b200::launch(1, stream, [=] __device__() { ProgGatherMask<float, 64, 256, MaskPattern::P1111, 1>(out, s); }); break;
+        default: return 1;
+    }
+    return e == cudaSuccess ? 0 : 3;
+}
+
+int pto_prog_row_softmax_64x256(float *out, float *rowmax, float *rowsum, const float *in, float scale, void *stream)
+{
+    return pto::b200::launch(1, stream, [=] __device__() {
+               ProgRowSoftmax<64, 256>(out, rowmax, rowsum, const_cast<float *>(in), scale);
+           }) == cudaSuccess
+               ? 0
+               : 3;
+}
+
+int pto_prog_matmul_nd_128x128x256(float *out, const __half *a, const __half *b, void *stream)
+{
+    return pto::b200::launch(1, stream, [=] __device__() {
+               ProgMatmulND<128, 128, 256>(out, const_cast<__half *>(a), const_cast<__half *>(b));
+           }) == cudaSuccess
+               ? 0
+               : 3;
+}
+
+int pto_prog_attention_head_128x128x64(float *o, const __half *q, const __half *k, const __half *v, float scale,
+                                       void *stream)
+{
+    return pto::b200::launch(1, stream, [=] __device__() {
+               ProgAttentionHead<128, 128, 64>(o, const_cast<__half *>(q), const_cast<__half *>(k),
+                                               const_cast<__half *>(v), scale);
+           }) == cudaSuccess
+               ? 0
+               : 3;
+}
+
+} // extern "C"
+#pragma GCC visibility pop

@@ -1,0 +1,106 @@
+"""Tile programs written against this repository's PTO headers (pto_isa_b200/csrc/pto_programs/programs.cu),
+run on the GPU and checked against the CPU oracle: TGATHER (index and mask forms), the softmax instruction
+chain, TMATMUL with a k x n (Layout::ND) second operand, and a whole attention head built from PTO
+instructions (TLOAD / TMOV / TMATMUL / TROWMAX / TROWEXPANDSUB / TMULS / TEXP / TROWSUM / TCVT / TROWEXPANDDIV /
+TSTORE)."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from util import attn_err_ok, dev, host, rel_err_ok
+
+pytestmark = pytest.mark.gpu
+port = oracle.port
+_SO = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "pto_isa_b200",
+                   "libpto_b200_programs.so")
+
+
+@pytest.fixture(scope="module")
+def prog():
+    lib = ctypes.CDLL(_SO)  # built by pto_isa_b200.build; its absence is an error, not a skip
+    return lib
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def test_tgather_index_program(prog):
+    r = np.random.default_rng(1)
+    src = r.standard_normal((32, 1024)).astype(np.float32)
+    idx = r.integers(-50, 32 * 1024 + 50, (16, 64)).astype(np.int32)
+    out = torch.full((16, 64), 7.0, device="cuda")
+    assert prog.pto_prog_tgather_index_f32(_ptr(out), _ptr(dev(src)), _ptr(dev(idx)), _stream()) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(host(out), port.tgather(src, idx))
+    s16 = r.integers(0, 65536, (16, 1024)).astype(np.uint16)
+    i16 = r.integers(-5, 16 * 1024 + 5, (16, 128)).astype(np.int32)
+    o16 = torch.zeros(16, 128, dtype=torch.int16, device="cuda")
+    assert prog.pto_prog_tgather_index_b16(_ptr(o16), _ptr(dev(s16.view(np.int16))), _ptr(dev(i16)), _stream()) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(host(o16).view(np.uint16), port.tgather(s16, i16))
+
+
+def test_tgather_mask_program(prog):
+    r = np.random.default_rng(2)
+    src = r.standard_normal((64, 256)).astype(np.float32)
+    d = dev(src)
+    for pat in range(1, 8):
+        want = port.tgather_mask(src, pat)
+        out = torch.zeros(want.size, device="cuda")
+        assert prog.pto_prog_tgather_mask_f32(_ptr(out), _ptr(d), pat, _stream()) == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(host(out), want), pat
+
+
+def test_row_softmax_program(prog):
+    r = np.random.default_rng(3)
+    x = (r.standard_normal((64, 256)) * 3).astype(np.float32)
+    out = torch.zeros(64, 256, device="cuda")
+    mx = torch.zeros(64, device="cuda")
+    sm = torch.zeros(64, device="cuda")
+    scale = np.float32(0.125)
+    assert prog.pto_prog_row_softmax_64x256(_ptr(out), _ptr(mx), _ptr(sm), _ptr(dev(x)), ctypes.c_float(scale),
+                                            _stream()) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(host(mx), port.trowmax_f32(x))
+    p = port.texp_f32(((x - x.max(axis=1, keepdims=True)) * scale).astype(np.float32))
+    s = port.trowsum_f32(p)
+    assert np.abs(host(sm) - s).max() <= 1e-5 * s.max()
+    assert np.abs(host(out) - p / s[:, None]).max() <= 1e-6
+
+
+def test_matmul_nd_program(prog):
+    r = np.random.default_rng(4)
+    a = r.uniform(-1, 1, (128, 128)).astype(np.float16)
+    b = r.uniform(-1, 1, (128, 256)).astype(np.float16)
+    out = torch.full((128, 256), float("nan"), device="cuda")
+    assert prog.pto_prog_matmul_nd_128x128x256(_ptr(out), _ptr(dev(a)), _ptr(dev(b)), _stream()) == 0
+    torch.cuda.synchronize()
+    want = port.gemm_f16f32(a, b, 0)
+    ok, worst = rel_err_ok(host(out), want, 2e-3)
+    assert ok, f"max relative error {worst:.3e}"
+
+
+def test_attention_head_program(prog):
+    r = np.random.default_rng(5)
+    s0, s1, d = 128, 128, 64
+    q = r.standard_normal((s0, d)).astype(np.float16)
+    k = r.standard_normal((s1, d)).astype(np.float16)
+    v = r.standard_normal((s1, d)).astype(np.float16)
+    scale = 1.0 / np.sqrt(d)
+    o = torch.full((s0, d), float("nan"), device="cuda")
+    assert prog.pto_prog_attention_head_128x128x64(_ptr(o), _ptr(dev(q)), _ptr(dev(k)), _ptr(dev(v)),
+                                                   ctypes.c_float(scale), _stream()) == 0
+    torch.cuda.synchronize()
+    want = port.attn_head_f16(q, k, v, 0, scale)
+    ok, worst, frac = attn_err_ok(host(o), want)
+    assert ok, f"max relative error {worst:.3e}, {frac:.5f} within tolerance"
