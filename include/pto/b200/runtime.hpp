@@ -33,7 +33,7 @@ constexpr int kBlockThreads = 256;
 constexpr int kNumPipes = 8;
 constexpr int kNumFlags = kNumPipes * kNumPipes * EVENT_ID_MAX; // 512
 constexpr int kTmemCols = 512;
-constexpr uint32_t kSpinLimit = 1u << 26;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
 struct Control {
     uint32_t tmem_base;
@@ -104,13 +104,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
 {
     volatile int *abort_flag = &control()->abort_flag;
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) {
             return true;
         }
-        if ((i & 0xff) == 0xff) {
+        if ((i & 0x3f) == 0x3f) {
             if (*abort_flag) {
                 return false;
+            }
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kWaitLimitNs) {
+                break; // two seconds on the global timer: give up instead of hanging the device
             }
             if (i > 4096) {
                 __nanosleep(64);

@@ -20,6 +20,9 @@
 #include "ptx.cuh"
 #include "internal.h"
 
+#include <cstdlib>
+#include <cstring>
+
 namespace pto_b200 {
 
 namespace {
@@ -253,6 +256,15 @@ int launch_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, in
         (reinterpret_cast<uintptr_t>(b) & 15u)) {
         set_error_text("gemm: k (and n for a k x n B) must be multiples of 8 and operands 16-byte aligned");
         return kErrUnsupportedShape;
+    }
+    // default: the kernel that puts two thread blocks on one 256 x 256 tile (gemm_2cta.cu);
+    // PTO_B200_GEMM_MODE=1cta selects the one-block-per-tile kernel of this file
+    static const bool one_block = [] {
+        const char *e = getenv("PTO_B200_GEMM_MODE");
+        return e != nullptr && strcmp(e, "1cta") == 0;
+    }();
+    if (!one_block) {
+        return launch_gemm2_f16f32(a, b, c, m, n, k, b_layout, stream);
     }
     CUtensorMap tmap_a, tmap_b;
     int rc = make_tmap_2d(&tmap_a, a, 2, m, k, k, BM, BK, true);

@@ -1,0 +1,362 @@
+// fp16 x fp16 -> fp32 GEMM for sm_100a on CTA pairs (tcgen05 cta_group::2): the same mapping of the reference's
+// GEMM tile program as gemm.cu (TLOAD -> TMA, TEXTRACT -> descriptor window, TMATMUL -> tcgen05.mma, TSTORE ->
+// tcgen05.ld + stores, flags -> mbarrier rings), with two thread blocks of a cluster working on one
+// 256 x 256 C tile.  Each block stages its own 128 rows of A and only *half* of the B tile per k step
+// (32 KiB instead of 48 KiB), the MMA of the pair reads both halves, so the shared-memory ring is 6 stages
+// deep and the L2 -> SM traffic per FLOP drops by a third.  Each block ends up with 128 rows x 256 columns
+// of the accumulator in its own tensor memory and stores them itself.
+//
+// Cross-block signalling (no multicast anywhere):
+//   full[s]   lives in the leader (rank 0): both blocks' TMA loads complete their bytes on it
+//   empty[s]  one per block: the leader commits the MMAs of a stage to its own and to the peer's barrier
+//   acc_full  one per block, committed the same way; acc_empty lives in the leader, the peer's epilogue
+//             warps arrive on it remotely.
+#include "ptx.cuh"
+#include "internal.h"
+
+namespace pto_b200 {
+
+namespace {
+
+constexpr int BM = 128;       // rows of A / C per block (256 per pair)
+constexpr int BN = 256;       // columns of C per pair
+constexpr int BNH = 128;      // columns of B staged per block
+constexpr int BK = 64;
+constexpr int kStages = 6;
+constexpr int kABytes = BM * BK * 2;  // 16 KiB
+constexpr int kBBytes = BNH * BK * 2; // 16 KiB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kThreads = 192; // warp 0 TMA, warp 1 MMA (leader only), warps 2..5 epilogue
+constexpr int kTmemCols = 512;
+
+struct Control {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+constexpr int kSmemBytes = kStages * kStageBytes + sizeof(Control) + 1024;
+
+// C tiles are walked in bands of kGroupN tile columns, tile rows fastest inside a band, so that the tiles in
+// flight at any time (one per block pair) form a roughly square patch: their A and B panels stay in L2.
+constexpr int kGroupN = 8;
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &tm, int &tn)
+{
+    const int band = t / (kGroupN * tiles_m);
+    const int first_n = band * kGroupN;
+    const int width = (tiles_n - first_n) < kGroupN ? (tiles_n - first_n) : kGroupN;
+    const int in_band = t - band * kGroupN * tiles_m;
+    tm = in_band / width;
+    tn = first_n + in_band % width;
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ void cluster_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// shared::cluster address of `p` (a location in this block's shared memory) in block `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_rank(const void *p, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+    return r;
+}
+
+__device__ __forceinline__ void remote_arrive(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// commit of the pair's MMAs to a barrier given by its shared::cluster address
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+                 : "memory");
+}
+
+// TMA load whose completion bytes are counted on a barrier of the pair's leader
+__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *map, uint32_t leader_bar, int c0,
+                                                 int c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        :
+        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                   uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+template <int kBLayout>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    float *__restrict__ c, int m, int n, int k, DeviceStatus *status)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    Control *ctl = reinterpret_cast<Control *>(smem + kStages * kStageBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank(); // 0 = leader
+    const int pair = blockIdx.x >> 1;
+    const int pairs = gridDim.x >> 1;
+    const int tiles_m = (m + 2 * BM - 1) / (2 * BM);
+    const int tiles_n = (n + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int kblocks = (k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&ctl->full[s], 1);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&ctl->acc_full[a], 1);
+            mbar_init(&ctl->acc_empty[a], 8); // four epilogue warps in each of the two blocks
+        }
+        ctl->abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync(); // both blocks' barriers exist before anything is signalled across blocks
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+    volatile int *abort_flag = &ctl->abort_flag;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TLOAD: TMA producer (both blocks)
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += pairs) {
+                int tm, tn;
+                tile_coords(t, tiles_m, tiles_n, tm, tn);
+                const int row0 = tm * 2 * BM + static_cast<int>(rank) * BM; // this block's rows of A and C
+                const int col0 = tn * BN + static_cast<int>(rank) * BNH;    // this block's half of the B tile
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *sa = smem + stage * kStageBytes;
+                    uint8_t *sb = sa + kABytes;
+                    const uint32_t leader_full = map_to_rank(&ctl->full[stage], 0);
+                    if (rank == 0) {
+                        mbar_arrive_expect_tx(&ctl->full[stage], 2 * kStageBytes); // bytes of both blocks
+                    }
+                    tma_load_2d_pair(sa, &tmap_a, leader_full, kb * BK, row0);
+                    if (kBLayout == 1) {
+                        tma_load_2d_pair(sb, &tmap_b, leader_full, kb * BK, col0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BNH / 64; ++j) {
+                            tma_load_2d_pair(sb + j * (64 * BK * 2), &tmap_b, leader_full, col0 + j * 64, kb * BK);
+                        }
+                    }
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ TEXTRACT + TMATMUL: MMA issuer (leader only)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_f16(2 * BM, BN, 0, kBLayout == 0 ? 1 : 0);
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += pairs) {
+                if (!mbar_wait(&ctl->acc_empty[acc], acc_phase ^ 1u, abort_flag)) {
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(&ctl->full[stage], phase, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_base = smem_u32(smem + stage * kStageBytes);
+                    const uint32_t b_base = a_base + kABytes;
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk) {
+                        const uint64_t a_desc = make_sw128_desc(a_base + kk * 32, 16, 1024);
+                        const uint64_t b_desc = (kBLayout == 1)
+                                                    ? make_sw128_desc(b_base + kk * 32, 16, 1024)
+                                                    : make_sw128_desc(b_base + kk * (16 * 128), 64 * BK * 2, 1024);
+                        tc_mma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    // the stage is reusable in both blocks once these MMAs have read it
+                    tc_commit_pair(map_to_rank(&ctl->empty[stage], 0));
+                    tc_commit_pair(map_to_rank(&ctl->empty[stage], 1));
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) {
+                    break;
+                }
+                tc_commit_pair(map_to_rank(&ctl->acc_full[acc], 0));
+                tc_commit_pair(map_to_rank(&ctl->acc_full[acc], 1));
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ TSTORE: epilogue warps (both blocks)
+        const int quarter = warp & 3;
+        uint32_t acc = 0, acc_phase = 0;
+        const bool vec_ok = ((n & 3) == 0) && ((reinterpret_cast<uintptr_t>(c) & 15u) == 0);
+        for (int t = pair; t < num_tiles; t += pairs) {
+            int tm, tn;
+            tile_coords(t, tiles_m, tiles_n, tm, tn);
+            if (!mbar_wait(&ctl->acc_full[acc], acc_phase, abort_flag)) {
+                break;
+            }
+            tc_fence_after();
+            const int row = tm * 2 * BM + static_cast<int>(rank) * BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+            float *crow = c + static_cast<int64_t>(row) * n + static_cast<int64_t>(tn) * BN;
+#pragma unroll 1
+            for (int cb = 0; cb < BN / 32; ++cb) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + cb * 32, r);
+                tmem_ld_wait();
+                const int col0 = tn * BN + cb * 32;
+                if (row < m) {
+                    if (vec_ok && col0 + 32 <= n) {
+                        float4 *dst = reinterpret_cast<float4 *>(crow + cb * 32);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (col0 + j < n) {
+                                crow[cb * 32 + j] = __uint_as_float(r[j]);
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                remote_arrive(map_to_rank(&ctl->acc_empty[acc], 0)); // the leader's MMA warp owns the accumulators
+            }
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (ctl->abort_flag) {
+        for (int i = 0; i < 1024; ++i) {
+            __nanosleep(1000);
+        }
+        if (threadIdx.x == 0 && atomicCAS(&status->code, 0, kErrDeviceWaitTimeout) == 0) {
+            status->block = blockIdx.x;
+            status->where = 3;
+        }
+        __syncthreads();
+    }
+    cluster_sync(); // neither block leaves while the other may still signal it or read its shared memory
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+} // namespace
+
+int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
+                        cudaStream_t stream)
+{
+    CUtensorMap tmap_a, tmap_b;
+    int rc = make_tmap_2d(&tmap_a, a, 2, m, k, k, BM, BK, true);
+    if (rc != kOk) {
+        return rc;
+    }
+    if (b_layout == 1) {
+        rc = make_tmap_2d(&tmap_b, b, 2, n, k, k, BNH, BK, true);
+    } else {
+        rc = make_tmap_2d(&tmap_b, b, 2, k, n, n, BK, 64, true);
+    }
+    if (rc != kOk) {
+        return rc;
+    }
+    const int tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
+    int pairs = sm_count() / 2;
+    if (tiles < pairs) {
+        pairs = tiles;
+    }
+    DeviceStatus *status = device_status_ptr();
+    if (status == nullptr) {
+        return kErrCuda;
+    }
+    static bool attr_set[2] = {false, false};
+    if (!attr_set[b_layout]) {
+        rc = check_cuda(b_layout == 1 ? cudaFuncSetAttribute(gemm2_f16f32_kernel<1>,
+                                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)
+                                      : cudaFuncSetAttribute(gemm2_f16f32_kernel<0>,
+                                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+                        "cudaFuncSetAttribute(gemm, 2 blocks per tile)");
+        if (rc != kOk) {
+            return rc;
+        }
+        attr_set[b_layout] = true;
+    }
+    if (b_layout == 1) {
+        gemm2_f16f32_kernel<1><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c, m, n, k, status);
+    } else {
+        gemm2_f16f32_kernel<0><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c, m, n, k, status);
+    }
+    return check_launch();
+}
+
+} // namespace pto_b200

@@ -57,6 +57,9 @@ int launch_trowexpand(const float *a, const float *row_scalar, float *dst, int r
 int launch_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
                        cudaStream_t stream);
 
+// the same product on pairs of thread blocks (cta_group::2); arguments already validated by the caller
+int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
+                        cudaStream_t stream);
 // host-buffer GEMM whose device staging and status record live in a built-in static device array (no allocation)
 int gemm_f16f32_host_static(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout);
 size_t gemm_static_scratch_bytes();

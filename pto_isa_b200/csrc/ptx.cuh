@@ -96,22 +96,36 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 }
 
 // Bounded wait.  `abort_flag` is a shared-memory word any role sets when it gives up, so that
-// the other roles stop waiting too.  Returns false on give-up.  The limit is generous (seconds)
-// for a healthy kernel and only exists so that a broken one returns.
-constexpr uint32_t kSpinLimit = 1u << 26;
+// the other roles stop waiting too.  Returns false on give-up.  The limit is wall-clock (two seconds on
+// the global timer): no healthy wait in these kernels lasts longer than a few milliseconds.
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long global_timer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag)
 {
     if (mbar_try_wait(bar, parity)) {
         return true;
     }
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) {
             return true;
         }
-        if ((i & 0xff) == 0xff) {
+        if ((i & 0x3f) == 0x3f) {
             if (*abort_flag) {
                 return false;
+            }
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kWaitLimitNs) {
+                break;
             }
             if (i > 4096) {
                 __nanosleep(64);
