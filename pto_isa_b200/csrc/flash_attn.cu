@@ -21,9 +21,12 @@
 // tiles are skipped.  The running max is only moved when it grows by more than 8 in the log2 domain; the
 // result O / l does not depend on which reference value is used (both carry the same factor).
 //
-// Warp roles (320 threads): warps 0-3 softmax of query tile 0, warps 4-7 softmax of query tile 1 (each thread
-// owns one query row, so row reductions need no shuffles), warp 8 TMA producer, warp 9 MMA issuer.  While
-// the softmax warps of one tile work, the tensor core runs the products of the other tile.
+// Warp roles (384 threads = 3 warpgroups): warps 0-3 softmax of query tile 0, warps 4-7 softmax of query tile 1
+// (each thread owns one query row, so row reductions need no shuffles), warp 8 TMA producer, warp 9 MMA
+// issuer, warps 10-11 idle.  The softmax warpgroups raise their register budget with setmaxnreg and the third
+// warpgroup lowers its own.  While the softmax warps of one tile work, the tensor core runs the products of
+// the other tile; P is handed over in two halves of 64 keys so the PV product starts before the second
+// half of the exponentials is done.
 #include "ptx.cuh"
 #include "internal.h"
 
@@ -39,7 +42,9 @@ constexpr int kTileKV = 128;      // keys per step
 constexpr int kStagesKV = 2;
 constexpr int kTileBytes = kTileQ * kD * 2; // 32 KiB: a 128 x 128 fp16 tile as two 64-column swizzled halves
 constexpr int kHalfBytes = kTileBytes / 2;  // 16 KiB
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;     // warps 0-3 / 4-7 softmax of query tile 0 / 1, warp 8 TMA, warp 9 MMA, warps 10-11 idle
+constexpr int kRegsSoftmax = 224; // per-thread register budgets after the warpgroups rebalance (setmaxnreg);
+constexpr int kRegsOther = 56;      // 256 * 224 + 128 * 56 = 64512 = 384 * 168, the pool the block was launched with
 constexpr int kTmemCols = 512;
 constexpr int kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
 
@@ -48,7 +53,7 @@ struct Control {
     uint64_t k_full[kStagesKV], k_empty[kStagesKV];
     uint64_t v_full[kStagesKV], v_empty[kStagesKV];
     uint64_t s_full[2]; // S tile ready for the softmax warps
-    uint64_t p_full[2]; // P tile written (and O rescaled) by the softmax warps
+    uint64_t p_full[2][2]; // first / second half (64 keys each) of the P tile written by the softmax warps
     uint64_t o_full[2]; // last PV product complete
     uint32_t tmem_base;
     int abort_flag;
@@ -117,7 +122,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(&ctl->s_full[t], 1);
-            mbar_init(&ctl->p_full[t], kTileQ);
+            mbar_init(&ctl->p_full[t][0], kTileQ);
+            mbar_init(&ctl->p_full[t][1], kTileQ);
             mbar_init(&ctl->o_full[t], 1);
         }
         ctl->abort_flag = 0;
@@ -136,6 +142,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const uint32_t tmem_base = ctl->tmem_base;
     volatile int *abort_flag = &ctl->abort_flag;
 
+    if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
     if (warp == 8) {
         // ------------------------------------------------------------ TMA producer (TLOAD of Q, K, V)
         if (lane == 0) {
@@ -192,14 +200,16 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 }
                 tc_commit(&ctl->s_full[t]);
             };
-            // O_t (+)= P_t(j) V_j : 8 steps of 16 keys; P from tensor memory (8 columns per step)
-            auto issue_pv = [&](int t, int j) {
+            // O_t (+)= P_t(j) V_j : 8 steps of 16 keys; P from tensor memory (8 columns per step); `half` selects
+            // keys [0, 64) or [64, 128)
+            auto issue_pv_half = [&](int t, int j, int half) {
                 const int s = j % kStagesKV;
                 const uint32_t vb = v_base + s * kTileBytes;
                 const uint32_t d_tmem = tmem_base + (t == 0 ? kColO0 : kColO1);
                 const uint32_t p_tmem = tmem_base + (t == 0 ? kColS0 : kColS1);
 #pragma unroll
-                for (int kk = 0; kk < kTileKV / 16; ++kk) {
+                for (int kq = 0; kq < kTileKV / 32; ++kq) {
+                    const int kk = half * (kTileKV / 32) + kq;
                     tc_mma_f16_ts(d_tmem, p_tmem + kk * 8, make_sw128_desc(vb + kk * (16 * 128), kHalfBytes, 1024),
                                   idesc_o, (j | kk) != 0 ? 1u : 0u);
                 }
@@ -228,7 +238,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                     if (j >= n_kv[t]) {
                         continue;
                     }
-                    ok = mbar_wait(&ctl->p_full[t], j & 1, abort_flag);
+                    ok = mbar_wait(&ctl->p_full[t][0], j & 1, abort_flag);
                     if (ok && !v_ready) {
                         ok = mbar_wait(&ctl->v_full[s], ph, abort_flag);
                         v_ready = true;
@@ -237,7 +247,13 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                         break;
                     }
                     tc_fence_after();
-                    issue_pv(t, j);
+                    issue_pv_half(t, j, 0);
+                    ok = mbar_wait(&ctl->p_full[t][1], j & 1, abort_flag);
+                    if (!ok) {
+                        break;
+                    }
+                    tc_fence_after();
+                    issue_pv_half(t, j, 1);
                     if (j == n_kv[t] - 1) {
                         tc_commit(&ctl->o_full[t]);
                     }
@@ -262,7 +278,9 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 }
             }
         }
+    }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
         // ------------------------------------------------------------ softmax / rescale / output warps
         const int t = warp >> 2;               // query tile of this warpgroup
         const int quarter = warp & 3;          // TMEM lanes [32*quarter, +32)
@@ -289,28 +307,36 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             }
             tmem_ld_wait();
             const bool diag = kCausal && (j * kTileKV + kTileKV - 1 > (2 * qb + t) * kTileQ);
-            float mx = -INFINITY;
             if (diag) {
                 const int kv0 = j * kTileKV;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        float x = __uint_as_float(sr[c][i]);
-                        x = (kv0 + c * 32 + i > q_row) ? -INFINITY : x;
-                        sr[c][i] = __float_as_uint(x);
-                        mx = fmaxf(mx, x);
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        mx = fmaxf(mx, __uint_as_float(sr[c][i]));
+                        if (kv0 + c * 32 + i > q_row) {
+                            sr[c][i] = 0xff800000u; // -inf
+                        }
                     }
                 }
             }
+            // row maximum with eight independent chains
+            float mx8[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                mx8[u] = -INFINITY;
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        mx8[u] = fmaxf(mx8[u], __uint_as_float(sr[c][i + u]));
+                    }
+                }
+            }
+            const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                                   fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             // move the reference max only when some row of this warp grew by more than 2^8
             const float m_new = fmaxf(m_run, mx);
             const bool grow = (m_new - m_run) * scale_log2 > 8.0f; // also true on the first tile (m_run = -inf)
@@ -333,7 +359,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 m_run = m_new;
             }
             const float neg_m = -m_run * scale_log2;
-            float sum = 0.0f;
+            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t pk[16];
@@ -341,16 +367,23 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 for (int i = 0; i < 32; i += 2) {
                     const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c][i]), scale_log2, neg_m));
                     const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, neg_m));
-                    sum += p0 + p1;
+                    sum4[(i >> 1) & 3] += p0 + p1;
                     pk[i >> 1] = pack_f16x2(p0, p1);
+                }
+                if (c == 2) {
+                    // the first half of the tile (64 keys) was stored one chunk of arithmetic ago: its stores have
+                    // landed by now, hand it to the MMA warp so that the PV product can start
+                    tmem_st_wait();
+                    tc_fence_before();
+                    mbar_arrive(&ctl->p_full[t][0]);
                 }
                 // fp16 P over the first 64 columns of S: 16 packed columns per 32 keys
                 tmem_st_32x16(s_addr + c * 16, pk);
             }
-            l_run += sum;
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(&ctl->p_full[t]);
+            mbar_arrive(&ctl->p_full[t][1]);
+            l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         }
 
         // output: O / l
