@@ -7,14 +7,18 @@
 //   compute_qk  (:280-352, TLOAD K + pto_macro_matmul)  -> TMA loads of K into swizzled shared memory,
 //                                                          S = Q K^T by tcgen05.mma into tensor memory
 //   compute_p   (:452-552, pto_macro_fa_softmax)        -> one thread per query row reads its S row from
-//                                                          tensor memory, updates the running max and sum,
-//                                                          writes P = exp(scale*(S - max)) as fp16 back into
-//                                                          tensor memory over S
-//   compute_pv  (:357-447)                              -> O += P V by tcgen05.mma with P read from tensor
-//                                                          memory and V (MN-major) from shared memory
+//                                                          tensor memory, updates the running max and sum and
+//                                                          writes P = exp(scale*(S - max)) as fp16 into shared
+//                                                          memory in the tensor core's operand layout
+//   compute_pv  (:357-447)                              -> O += P V by tcgen05.mma, P and V (MN-major) from
+//                                                          shared memory
 //   compute_gu  (:557-605, pto_macro_fa_gu)             -> O lives in tensor memory; it is rescaled there when
 //                                                          a row's max grows, and divided by the row sum on
 //                                                          the way out
+// Because P does not live where S does, the product S(j+1) = Q K(j+1)^T is issued as soon as the softmax
+// warps have *read* S(j), i.e. it runs on the tensor core while the exponentials of step j are computed;
+// the reference's QK_PRELOAD look-ahead (fa_performance_kernel.h:18-26) plays the same role.
+//
 // Softmax conventions are the reference's (pto_macro_fa_softmax.hpp:81-97,141-184): the max is taken on
 // the raw logits, p = exp(scale * (x - max)) in fp32, the row sum accumulates the fp32 p, p is rounded to
 // fp16 for the second product, the causal mask hides keys beyond the query's own index, fully masked key
@@ -22,11 +26,9 @@
 // result O / l does not depend on which reference value is used (both carry the same factor).
 //
 // Warp roles (384 threads = 3 warpgroups): warps 0-3 softmax of query tile 0, warps 4-7 softmax of query tile 1
-// (each thread owns one query row, so row reductions need no shuffles), warp 8 TMA producer, warp 9 MMA
-// issuer, warps 10-11 idle.  The softmax warpgroups raise their register budget with setmaxnreg and the third
-// warpgroup lowers its own.  While the softmax warps of one tile work, the tensor core runs the products of
-// the other tile; P is handed over in two halves of 64 keys so the PV product starts before the second
-// half of the exponentials is done.
+// (each thread owns one query row, so row reductions need no shuffles), warp 8 TMA producer, warps 9 and 10
+// MMA issuers (one per query tile), warp 11 idle.  The softmax warpgroups raise their register budget with setmaxnreg and the third
+// warpgroup lowers its own.
 #include "ptx.cuh"
 #include "internal.h"
 
@@ -39,27 +41,28 @@ namespace {
 constexpr int kD = 128;           // head size
 constexpr int kTileQ = 128;       // query rows per tile (two tiles per CTA)
 constexpr int kTileKV = 128;      // keys per step
-constexpr int kStagesKV = 2;
+constexpr int kRing = 3;          // K / V tiles in flight, in the order the tensor core consumes them
 constexpr int kTileBytes = kTileQ * kD * 2; // 32 KiB: a 128 x 128 fp16 tile as two 64-column swizzled halves
 constexpr int kHalfBytes = kTileBytes / 2;  // 16 KiB
-constexpr int kThreads = 384;     // warps 0-3 / 4-7 softmax of query tile 0 / 1, warp 8 TMA, warp 9 MMA, warps 10-11 idle
-constexpr int kRegsSoftmax = 224; // per-thread register budgets after the warpgroups rebalance (setmaxnreg);
-constexpr int kRegsOther = 56;      // 256 * 224 + 128 * 56 = 64512 = 384 * 168, the pool the block was launched with
+constexpr int kThreads = 384;
+constexpr int kRegsSoftmax = 224; // per-thread register budgets after the warpgroups rebalance (setmaxnreg):
+constexpr int kRegsOther = 56;    // 256 * 224 + 128 * 56 = 64512 = 384 * 168, the pool the block was launched with
 constexpr int kTmemCols = 512;
 constexpr int kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
 
 struct Control {
     uint64_t q_full;
-    uint64_t k_full[kStagesKV], k_empty[kStagesKV];
-    uint64_t v_full[kStagesKV], v_empty[kStagesKV];
-    uint64_t s_full[2]; // S tile ready for the softmax warps
-    uint64_t p_full[2][2]; // first / second half (64 keys each) of the P tile written by the softmax warps
-    uint64_t o_full[2]; // last PV product complete
+    uint64_t ring_full[kRing], ring_empty[kRing];
+    uint64_t s_full[2];  // S tile complete in tensor memory
+    uint64_t s_free[2];  // S tile copied to registers by all 128 softmax threads: S(j+1) may overwrite it
+    uint64_t p_full[2];  // P tile written to shared memory (and O rescaled) by all 128 softmax threads
+    uint64_t pv_done[2]; // PV product of the step complete: P buffer reusable, O consistent
     uint32_t tmem_base;
     int abort_flag;
 };
 
-constexpr int kSmemBytes = 2 * kTileBytes + 2 * kStagesKV * kTileBytes + sizeof(Control) + 1024;
+// Q (2 tiles) + K/V ring (3 tiles) + P (2 tiles)
+constexpr int kSmemBytes = (2 + kRing + 2) * kTileBytes + sizeof(Control) + 1024;
 
 __device__ __forceinline__ float ex2_approx(float x)
 {
@@ -75,6 +78,11 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi)
     return d;
 }
 
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 template <bool kCausal, bool kOutF16>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -83,10 +91,10 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *smem_q = smem;                                   // 2 tiles
-    uint8_t *smem_k = smem + 2 * kTileBytes;                  // kStagesKV tiles
-    uint8_t *smem_v = smem_k + kStagesKV * kTileBytes;        // kStagesKV tiles
-    Control *ctl = reinterpret_cast<Control *>(smem_v + kStagesKV * kTileBytes);
+    uint8_t *smem_q = smem;                                // 2 tiles
+    uint8_t *smem_ring = smem + 2 * kTileBytes;            // kRing tiles
+    uint8_t *smem_p = smem_ring + kRing * kTileBytes;      // 2 tiles
+    Control *ctl = reinterpret_cast<Control *>(smem_p + 2 * kTileBytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -97,34 +105,37 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const int bh = blockIdx.x / q_blocks;
     const int qb = q_blocks - 1 - (blockIdx.x % q_blocks);
     const int kv_tiles = sk / kTileKV;
-    int n_kv[2];
+    int n_kv0, n_kv1;
+    {
+        int n[2];
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
-        const int q0 = (2 * qb + t) * kTileQ;
-        if (q0 >= sq) {
-            n_kv[t] = 0;
-        } else if (kCausal) {
-            const int lim = q0 / kTileKV + 1; // tiles that hold at least one key <= the tile's last query
-            n_kv[t] = lim < kv_tiles ? lim : kv_tiles;
-        } else {
-            n_kv[t] = kv_tiles;
+        for (int t = 0; t < 2; ++t) {
+            const int q0 = (2 * qb + t) * kTileQ;
+            if (q0 >= sq) {
+                n[t] = 0;
+            } else if (kCausal) {
+                const int lim = q0 / kTileKV + 1; // tiles that hold at least one key <= the tile's last query
+                n[t] = lim < kv_tiles ? lim : kv_tiles;
+            } else {
+                n[t] = kv_tiles;
+            }
         }
+        n_kv0 = n[0];
+        n_kv1 = n[1];
     }
-    const int n_max = n_kv[0] > n_kv[1] ? n_kv[0] : n_kv[1];
+    const int n_max = n_kv0 > n_kv1 ? n_kv0 : n_kv1;
 
     if (threadIdx.x == 0) {
         mbar_init(&ctl->q_full, 1);
-        for (int s = 0; s < kStagesKV; ++s) {
-            mbar_init(&ctl->k_full[s], 1);
-            mbar_init(&ctl->k_empty[s], 1);
-            mbar_init(&ctl->v_full[s], 1);
-            mbar_init(&ctl->v_empty[s], 1);
+        for (int s = 0; s < kRing; ++s) {
+            mbar_init(&ctl->ring_full[s], 1);
+            mbar_init(&ctl->ring_empty[s], 2); // both MMA issuers release a slot
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(&ctl->s_full[t], 1);
-            mbar_init(&ctl->p_full[t][0], kTileQ);
-            mbar_init(&ctl->p_full[t][1], kTileQ);
-            mbar_init(&ctl->o_full[t], 1);
+            mbar_init(&ctl->s_free[t], kTileQ);
+            mbar_init(&ctl->p_full[t], kTileQ);
+            mbar_init(&ctl->pv_done[t], 1);
         }
         ctl->abort_flag = 0;
         fence_mbar_init();
@@ -143,142 +154,140 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     volatile int *abort_flag = &ctl->abort_flag;
 
     if (warp >= 8) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-    if (warp == 8) {
-        // ------------------------------------------------------------ TMA producer (TLOAD of Q, K, V)
-        if (lane == 0) {
-            int q_bytes = 0;
-            for (int t = 0; t < 2; ++t) {
-                q_bytes += (n_kv[t] > 0) ? kTileBytes : 0;
-            }
-            mbar_arrive_expect_tx(&ctl->q_full, q_bytes);
-            for (int t = 0; t < 2; ++t) {
-                if (n_kv[t] > 0) {
-                    const int q0 = (2 * qb + t) * kTileQ;
-                    tma_load_3d(smem_q + t * kTileBytes, &tmap_q, &ctl->q_full, 0, q0, bh);
-                    tma_load_3d(smem_q + t * kTileBytes + kHalfBytes, &tmap_q, &ctl->q_full, 64, q0, bh);
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+        if (warp == 8) {
+            // -------------------------------------------------------- TMA producer (TLOAD of Q, K, V)
+            // ring items in consumption order: K(0), then for every step j: K(j+1) (if any), V(j)
+            if (lane == 0) {
+                int q_bytes = 0;
+                q_bytes += (n_kv0 > 0) ? kTileBytes : 0;
+                q_bytes += (n_kv1 > 0) ? kTileBytes : 0;
+                mbar_arrive_expect_tx(&ctl->q_full, q_bytes);
+                for (int t = 0; t < 2; ++t) {
+                    if ((t == 0 ? n_kv0 : n_kv1) > 0) {
+                        const int q0 = (2 * qb + t) * kTileQ;
+                        tma_load_3d(smem_q + t * kTileBytes, &tmap_q, &ctl->q_full, 0, q0, bh);
+                        tma_load_3d(smem_q + t * kTileBytes + kHalfBytes, &tmap_q, &ctl->q_full, 64, q0, bh);
+                    }
+                }
+                int item = 0;
+                bool ok = true;
+                auto load_item = [&](const CUtensorMap *map, int tile) {
+                    const int s = item % kRing;
+                    const uint32_t ph = (item / kRing) & 1;
+                    if (!mbar_wait(&ctl->ring_empty[s], ph ^ 1u, abort_flag)) {
+                        ok = false;
+                        return;
+                    }
+                    uint8_t *dst = smem_ring + s * kTileBytes;
+                    mbar_arrive_expect_tx(&ctl->ring_full[s], kTileBytes);
+                    tma_load_3d(dst, map, &ctl->ring_full[s], 0, tile * kTileKV, bh);
+                    tma_load_3d(dst + kHalfBytes, map, &ctl->ring_full[s], 64, tile * kTileKV, bh);
+                    ++item;
+                };
+                if (n_max > 0) {
+                    load_item(&tmap_k, 0);
+                }
+                for (int j = 0; j < n_max && ok; ++j) {
+                    if (j + 1 < n_max) {
+                        load_item(&tmap_k, j + 1);
+                    }
+                    if (ok) {
+                        load_item(&tmap_v, j);
+                    }
                 }
             }
-            for (int j = 0; j < n_max; ++j) {
-                const int s = j % kStagesKV;
-                const uint32_t ph = (j / kStagesKV) & 1;
-                if (!mbar_wait(&ctl->k_empty[s], ph ^ 1u, abort_flag)) {
-                    break;
-                }
-                mbar_arrive_expect_tx(&ctl->k_full[s], kTileBytes);
-                tma_load_3d(smem_k + s * kTileBytes, &tmap_k, &ctl->k_full[s], 0, j * kTileKV, bh);
-                tma_load_3d(smem_k + s * kTileBytes + kHalfBytes, &tmap_k, &ctl->k_full[s], 64, j * kTileKV, bh);
-                if (!mbar_wait(&ctl->v_empty[s], ph ^ 1u, abort_flag)) {
-                    break;
-                }
-                mbar_arrive_expect_tx(&ctl->v_full[s], kTileBytes);
-                tma_load_3d(smem_v + s * kTileBytes, &tmap_v, &ctl->v_full[s], 0, j * kTileKV, bh);
-                tma_load_3d(smem_v + s * kTileBytes + kHalfBytes, &tmap_v, &ctl->v_full[s], 64, j * kTileKV, bh);
-            }
-        }
-    } else if (warp == 9) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc_s = make_idesc_f16(kTileQ, kTileKV, 0, 0); // Q (K-major) x K (K-major)
-            constexpr uint32_t idesc_o = make_idesc_f16(kTileQ, kD, 0, 1);      // P (tmem)   x V (MN-major)
-            const uint32_t q_base = smem_u32(smem_q);
-            const uint32_t k_base = smem_u32(smem_k);
-            const uint32_t v_base = smem_u32(smem_v);
-            bool ok = mbar_wait(&ctl->q_full, 0, abort_flag);
+        } else if (warp == 9 || warp == 10) {
+            // -------------------------------------------------------- MMA issuers: warp 9 for query tile 0,
+            // warp 10 for query tile 1.  One thread sustains about one tcgen05.mma per 80 cycles, a 128 x 128 x 16
+            // MMA takes 64: two issuing threads keep the tensor core fed.  Both walk the K/V ring in the same
+            // order and both release every slot (the ring's empty barriers count two arrivals).
+            if (lane == 0) {
+                const int t = warp - 9;
+                const int n_t = (t == 0) ? n_kv0 : n_kv1;
+                constexpr uint32_t idesc_s = make_idesc_f16(kTileQ, kTileKV, 0, 0); // Q (K-major) x K (K-major)
+                constexpr uint32_t idesc_o = make_idesc_f16(kTileQ, kD, 0, 1);      // P (K-major) x V (MN-major)
+                const uint32_t ring_base = smem_u32(smem_ring);
+                const uint32_t s_tmem = tmem_base + (t == 0 ? kColS0 : kColS1);
+                const uint32_t o_tmem = tmem_base + (t == 0 ? kColO0 : kColO1);
+                // descriptors of the operands that never move (Q_t, P_t): built once
+                const uint64_t q_desc = make_sw128_desc(smem_u32(smem_q) + t * kTileBytes, 16, 1024);
+                const uint64_t p_desc = make_sw128_desc(smem_u32(smem_p) + t * kTileBytes, 16, 1024);
+                bool ok = mbar_wait(&ctl->q_full, 0, abort_flag);
+                int item = 0;
 
-            // S_t(j) = Q_t K_j^T : 8 steps of 16 along the head dimension (two 64-wide swizzled halves)
-            auto issue_s = [&](int t, int j) {
-                const int s = j % kStagesKV;
-                const uint32_t qa = q_base + t * kTileBytes;
-                const uint32_t kb = k_base + s * kTileBytes;
-                const uint32_t d_tmem = tmem_base + (t == 0 ? kColS0 : kColS1);
+                // a k step of 16 inside a K-major tile: +32 bytes, and +16 KiB when crossing into the second
+                // 64-wide half; in descriptor units (16 bytes) that is +2 and +1024
+                auto kmajor_step = [](int kk) -> uint64_t {
+                    return static_cast<uint64_t>((kk >> 2) * (kHalfBytes >> 4) + (kk & 3) * 2);
+                };
+                auto issue_s = [&](uint32_t kb) {
+                    const uint64_t k_desc = make_sw128_desc(kb, 16, 1024);
 #pragma unroll
-                for (int kk = 0; kk < kD / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-                    tc_mma_f16_ss(d_tmem, make_sw128_desc(qa + off, 16, 1024), make_sw128_desc(kb + off, 16, 1024),
-                                  idesc_s, kk != 0 ? 1u : 0u);
-                }
-                tc_commit(&ctl->s_full[t]);
-            };
-            // O_t (+)= P_t(j) V_j : 8 steps of 16 keys; P from tensor memory (8 columns per step); `half` selects
-            // keys [0, 64) or [64, 128)
-            auto issue_pv_half = [&](int t, int j, int half) {
-                const int s = j % kStagesKV;
-                const uint32_t vb = v_base + s * kTileBytes;
-                const uint32_t d_tmem = tmem_base + (t == 0 ? kColO0 : kColO1);
-                const uint32_t p_tmem = tmem_base + (t == 0 ? kColS0 : kColS1);
+                    for (int kk = 0; kk < kD / 16; ++kk) {
+                        tc_mma_f16_ss(s_tmem, q_desc + kmajor_step(kk), k_desc + kmajor_step(kk), idesc_s,
+                                      kk != 0 ? 1u : 0u);
+                    }
+                    tc_commit(&ctl->s_full[t]);
+                };
+                auto issue_pv = [&](uint32_t vb, bool accumulate) {
+                    const uint64_t v_desc = make_sw128_desc(vb, kHalfBytes, 1024); // MN-major: 16 keys = 2 KiB
 #pragma unroll
-                for (int kq = 0; kq < kTileKV / 32; ++kq) {
-                    const int kk = half * (kTileKV / 32) + kq;
-                    tc_mma_f16_ts(d_tmem, p_tmem + kk * 8, make_sw128_desc(vb + kk * (16 * 128), kHalfBytes, 1024),
-                                  idesc_o, (j | kk) != 0 ? 1u : 0u);
-                }
-            };
+                    for (int kk = 0; kk < kTileKV / 16; ++kk) {
+                        tc_mma_f16_ss(o_tmem, p_desc + kmajor_step(kk), v_desc + static_cast<uint64_t>(kk * 128),
+                                      idesc_o, (accumulate || kk != 0) ? 1u : 0u);
+                    }
+                    tc_commit(&ctl->pv_done[t]);
+                };
+                auto ring_wait = [&](uint32_t &addr, int &slot) {
+                    slot = item % kRing;
+                    const uint32_t ph = (item / kRing) & 1;
+                    addr = ring_base + slot * kTileBytes;
+                    ++item;
+                    return mbar_wait(&ctl->ring_full[slot], ph, abort_flag);
+                };
 
-            // prologue: first S tile of both query tiles
-            if (ok && n_max > 0) {
-                ok = mbar_wait(&ctl->k_full[0], 0, abort_flag);
-                if (ok) {
-                    tc_fence_after();
-                    for (int t = 0; t < 2; ++t) {
-                        if (n_kv[t] > 0) {
-                            issue_s(t, 0);
+                uint32_t addr = 0;
+                int slot = 0;
+                if (ok && n_max > 0) {
+                    ok = ring_wait(addr, slot); // K(0)
+                    if (ok) {
+                        if (n_t > 0) {
+                            issue_s(addr);
                         }
+                        tc_commit(&ctl->ring_empty[slot]);
                     }
-                    tc_commit(&ctl->k_empty[0]);
                 }
-            }
-            for (int j = 0; j < n_max && ok; ++j) {
-                const int s = j % kStagesKV;
-                const uint32_t ph = (j / kStagesKV) & 1;
-                const int sn = (j + 1) % kStagesKV;
-                const uint32_t phn = ((j + 1) / kStagesKV) & 1;
-                bool v_ready = false, k_ready = false;
-                for (int t = 0; t < 2 && ok; ++t) {
-                    if (j >= n_kv[t]) {
-                        continue;
-                    }
-                    ok = mbar_wait(&ctl->p_full[t][0], j & 1, abort_flag);
-                    if (ok && !v_ready) {
-                        ok = mbar_wait(&ctl->v_full[s], ph, abort_flag);
-                        v_ready = true;
-                    }
-                    if (!ok) {
-                        break;
-                    }
-                    tc_fence_after();
-                    issue_pv_half(t, j, 0);
-                    ok = mbar_wait(&ctl->p_full[t][1], j & 1, abort_flag);
-                    if (!ok) {
-                        break;
-                    }
-                    tc_fence_after();
-                    issue_pv_half(t, j, 1);
-                    if (j == n_kv[t] - 1) {
-                        tc_commit(&ctl->o_full[t]);
-                    }
-                    if (j + 1 < n_kv[t]) {
-                        if (!k_ready) {
-                            ok = mbar_wait(&ctl->k_full[sn], phn, abort_flag);
-                            k_ready = true;
-                            if (!ok) {
-                                break;
+                for (int j = 0; j < n_max && ok; ++j) {
+                    if (j + 1 < n_max) {
+                        ok = ring_wait(addr, slot); // K(j+1)
+                        if (ok && j + 1 < n_t) {
+                            ok = mbar_wait(&ctl->s_free[t], j & 1, abort_flag); // S_t(j) has been read
+                            if (ok) {
+                                tc_fence_after();
+                                issue_s(addr);
                             }
-                            tc_fence_after();
                         }
-                        issue_s(t, j + 1);
+                        if (!ok) {
+                            break;
+                        }
+                        tc_commit(&ctl->ring_empty[slot]);
                     }
-                }
-                if (!ok) {
-                    break;
-                }
-                tc_commit(&ctl->v_empty[s]);
-                if (k_ready) {
-                    tc_commit(&ctl->k_empty[sn]);
+                    ok = ring_wait(addr, slot); // V(j)
+                    if (ok && j < n_t) {
+                        ok = mbar_wait(&ctl->p_full[t], j & 1, abort_flag);
+                        if (ok) {
+                            tc_fence_after();
+                            issue_pv(addr, j != 0);
+                        }
+                    }
+                    if (!ok) {
+                        break;
+                    }
+                    tc_commit(&ctl->ring_empty[slot]);
                 }
             }
         }
-    }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
         // ------------------------------------------------------------ softmax / rescale / output warps
@@ -289,7 +298,10 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         const uint32_t s_addr = lane_addr + (t == 0 ? kColS0 : kColS1);
         const uint32_t o_addr = lane_addr + (t == 0 ? kColO0 : kColO1);
-        const int n = n_kv[t];
+        // this row of the P tile: two halves of 64 keys, 128 bytes per row and half, 16-byte chunks swizzled
+        const uint32_t p_row = smem_u32(smem_p) + t * kTileBytes + row_in_tile * 128;
+        const uint32_t swz = static_cast<uint32_t>(row_in_tile & 7);
+        const int n = (t == 0) ? n_kv0 : n_kv1;
         float m_run = -INFINITY; // running reference max (raw logits)
         float l_run = 0.0f;      // running sum of p
         bool ok = true;
@@ -306,6 +318,9 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 tmem_ld_32x32(s_addr + c * 32, sr[c]);
             }
             tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(&ctl->s_free[t]); // the tensor core may start S(j+1) into the same columns
+
             const bool diag = kCausal && (j * kTileKV + kTileKV - 1 > (2 * qb + t) * kTileQ);
             if (diag) {
                 const int kv0 = j * kTileKV;
@@ -340,8 +355,18 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             // move the reference max only when some row of this warp grew by more than 2^8
             const float m_new = fmaxf(m_run, mx);
             const bool grow = (m_new - m_run) * scale_log2 > 8.0f; // also true on the first tile (m_run = -inf)
-            if (__any_sync(0xffffffffu, grow)) {
+            const bool rescale = __any_sync(0xffffffffu, grow);
+            // The previous PV product must be complete before O is rescaled or P's buffer is rewritten.  The
+            // rescale is rare, so normally this wait sits after the exponentials: they overlap that product.
+            bool pv_waited = (j == 0);
+            if (rescale) {
                 if (j > 0) {
+                    if (!mbar_wait(&ctl->pv_done[t], (j - 1) & 1, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    pv_waited = true;
+                    tc_fence_after();
                     const float alpha = ex2_approx((m_run - m_new) * scale_log2);
                     l_run *= alpha;
 #pragma unroll 1
@@ -355,40 +380,48 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                         }
                         tmem_st_32x32(o_addr + c * 32, orow);
                     }
+                    tmem_st_wait();
+                    tc_fence_before();
                 }
                 m_run = m_new;
             }
             const float neg_m = -m_run * scale_log2;
             float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            uint32_t pk[4][16];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c][i]), scale_log2, neg_m));
                     const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, neg_m));
                     sum4[(i >> 1) & 3] += p0 + p1;
-                    pk[i >> 1] = pack_f16x2(p0, p1);
+                    pk[c][i >> 1] = pack_f16x2(p0, p1);
                 }
-                if (c == 2) {
-                    // the first half of the tile (64 keys) was stored one chunk of arithmetic ago: its stores have
-                    // landed by now, hand it to the MMA warp so that the PV product can start
-                    tmem_st_wait();
-                    tc_fence_before();
-                    mbar_arrive(&ctl->p_full[t][0]);
-                }
-                // fp16 P over the first 64 columns of S: 16 packed columns per 32 keys
-                tmem_st_32x16(s_addr + c * 16, pk);
             }
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(&ctl->p_full[t][1]);
+            if (!pv_waited) {
+                if (!mbar_wait(&ctl->pv_done[t], (j - 1) & 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                // 32 keys = four 16-byte chunks of this row; chunk index within the 64-key half: (c & 1) * 4 + q
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t chunk = static_cast<uint32_t>((c & 1) * 4 + q);
+                    st_shared_v4(p_row + (c >> 1) * kHalfBytes + ((chunk ^ swz) << 4), pk[c][4 * q], pk[c][4 * q + 1],
+                                 pk[c][4 * q + 2], pk[c][4 * q + 3]);
+                }
+            }
             l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            fence_proxy_async_smem(); // the tensor core reads P through the asynchronous proxy
+            mbar_arrive(&ctl->p_full[t]);
         }
 
         // output: O / l
         if (ok && n > 0) {
-            if (mbar_wait(&ctl->o_full[t], 0, abort_flag)) {
+            if (mbar_wait(&ctl->pv_done[t], (n - 1) & 1, abort_flag)) {
                 tc_fence_after();
                 const float inv_l = 1.0f / l_run;
                 const int64_t row_off = (static_cast<int64_t>(bh) * sq + q_row) * kD;
