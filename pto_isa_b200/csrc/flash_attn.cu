@@ -34,6 +34,8 @@
 
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 namespace pto_b200 {
 
 namespace {
@@ -78,12 +80,69 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi)
     return d;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// ---- packed fp32 pairs (two lanes per 64-bit register; one issue slot per pair of operations)
+__device__ __forceinline__ uint64_t pack2(float lo, float hi)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// 2^x for a pair of arguments on the FMA pipe instead of the special-function unit (which bounds the
+// exponential phase of the softmax): x is clamped to >= -126, split into round(x) + f with f in [-0.5, 0.5]
+// by the 1.5 * 2^23 trick, 2^f is a degree-4 minimax polynomial (max relative error 2.7e-6, far below the
+// fp16 rounding P undergoes), and round(x) is added to the exponent field.
+__device__ __forceinline__ void exp2_poly_pair(float x0, float x1, float &p0, float &p1)
+{
+    const float kMagic = 12582912.0f; // 1.5 * 2^23
+    x0 = fmaxf(x0, -126.0f);
+    x1 = fmaxf(x1, -126.0f);
+    const uint64_t x = pack2(x0, x1);
+    const uint64_t t = add2(x, pack2(kMagic, kMagic));       // integer part lands in the low mantissa bits
+    const uint64_t r = add2(t, pack2(-kMagic, -kMagic));     // round(x) as a float
+    const uint64_t f = fma2(r, pack2(-1.0f, -1.0f), x);      // x - round(x)
+    uint64_t p = pack2(0.009570101276040077f, 0.009570101276040077f);
+    p = fma2(p, f, pack2(0.05591785907745361f, 0.05591785907745361f));
+    p = fma2(p, f, pack2(0.240247443318367f, 0.240247443318367f));
+    p = fma2(p, f, pack2(0.6931217908859253f, 0.6931217908859253f));
+    p = fma2(p, f, pack2(0.9999992847442627f, 0.9999992847442627f));
+    float t0, t1, q0, q1;
+    unpack2(t, t0, t1);
+    unpack2(p, q0, q1);
+    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
+
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
 {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-template <bool kCausal, bool kOutF16>
+// kPolyOf8: of every 8 pairs of probabilities, this many are exponentiated on the FMA pipe
+template <bool kCausal, bool kOutF16, int kPolyOf8>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, void *__restrict__ o_ptr, int sq, int sk,
@@ -334,24 +393,21 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                     }
                 }
             }
-            // row maximum with eight independent chains
+            // row maximum: eight independent chains of three-input maxima
             float mx8[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                mx8[u] = -INFINITY;
+                mx8[u] = fmaxf(__uint_as_float(sr[0][u]), __uint_as_float(sr[0][8 + u]));
             }
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int i = 16; i < 128; i += 16) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        mx8[u] = fmaxf(mx8[u], __uint_as_float(sr[c][i + u]));
-                    }
+                for (int u = 0; u < 8; ++u) {
+                    mx8[u] = max3(mx8[u], __uint_as_float(sr[i >> 5][(i & 31) + u]),
+                                  __uint_as_float(sr[i >> 5][(i & 31) + 8 + u]));
                 }
             }
-            const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                                   fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+            const float mx = fmaxf(max3(mx8[0], mx8[1], mx8[2]), max3(max3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
             // move the reference max only when some row of this warp grew by more than 2^8
             const float m_new = fmaxf(m_run, mx);
             const bool grow = (m_new - m_run) * scale_log2 > 8.0f; // also true on the first tile (m_run = -inf)
@@ -387,32 +443,39 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             }
             const float neg_m = -m_run * scale_log2;
             float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint32_t pk[4][16];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
+                uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c][i]), scale_log2, neg_m));
-                    const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, neg_m));
+                    const float a0 = fmaf(__uint_as_float(sr[c][i]), scale_log2, neg_m);
+                    const float a1 = fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, neg_m);
+                    float p0, p1;
+                    if (((i >> 1) & 7) < kPolyOf8) {
+                        exp2_poly_pair(a0, a1, p0, p1);
+                    } else {
+                        p0 = ex2_approx(a0);
+                        p1 = ex2_approx(a1);
+                    }
                     sum4[(i >> 1) & 3] += p0 + p1;
-                    pk[c][i >> 1] = pack_f16x2(p0, p1);
+                    pk[i >> 1] = pack_f16x2(p0, p1);
                 }
-            }
-            if (!pv_waited) {
-                if (!mbar_wait(&ctl->pv_done[t], (j - 1) & 1, abort_flag)) {
-                    ok = false;
-                    break;
+                if (c == 0 && !pv_waited) {
+                    // first store into P's buffer: the previous product must have finished reading it
+                    if (!mbar_wait(&ctl->pv_done[t], (j - 1) & 1, abort_flag)) {
+                        ok = false;
+                    }
                 }
-            }
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
                 // 32 keys = four 16-byte chunks of this row; chunk index within the 64-key half: (c & 1) * 4 + q
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const uint32_t chunk = static_cast<uint32_t>((c & 1) * 4 + q);
-                    st_shared_v4(p_row + (c >> 1) * kHalfBytes + ((chunk ^ swz) << 4), pk[c][4 * q], pk[c][4 * q + 1],
-                                 pk[c][4 * q + 2], pk[c][4 * q + 3]);
+                    st_shared_v4(p_row + (c >> 1) * kHalfBytes + ((chunk ^ swz) << 4), pk[4 * q], pk[4 * q + 1],
+                                 pk[4 * q + 2], pk[4 * q + 3]);
                 }
+            }
+            if (!ok) {
+                break;
             }
             l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             fence_proxy_async_smem(); // the tensor core reads P through the asynchronous proxy
@@ -473,13 +536,13 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     }
 }
 
-template <bool kCausal, bool kOutF16>
+template <bool kCausal, bool kOutF16, int kPolyOf8>
 int launch_variant(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, void *o, int bh, int sq, int sk,
                    float scale_log2, DeviceStatus *status, cudaStream_t stream)
 {
     static bool attr_set = false;
     if (!attr_set) {
-        const int rc = check_cuda(cudaFuncSetAttribute(flash_attn_fwd_kernel<kCausal, kOutF16>,
+        const int rc = check_cuda(cudaFuncSetAttribute(flash_attn_fwd_kernel<kCausal, kOutF16, kPolyOf8>,
                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
                                   "cudaFuncSetAttribute(flash_attn)");
         if (rc != kOk) {
@@ -488,9 +551,21 @@ int launch_variant(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorM
         attr_set = true;
     }
     const int q_blocks = (sq + 2 * kTileQ - 1) / (2 * kTileQ);
-    flash_attn_fwd_kernel<kCausal, kOutF16>
+    flash_attn_fwd_kernel<kCausal, kOutF16, kPolyOf8>
         <<<bh * q_blocks, kThreads, kSmemBytes, stream>>>(tq, tk, tv, o, sq, sk, scale_log2, status);
     return check_launch();
+}
+
+template <int kPolyOf8>
+int launch_mode(bool causal, bool out_f16, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, void *o,
+                int bh, int sq, int sk, float scale_log2, DeviceStatus *status, cudaStream_t stream)
+{
+    if (causal) {
+        return out_f16 ? launch_variant<true, true, kPolyOf8>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream)
+                       : launch_variant<true, false, kPolyOf8>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
+    }
+    return out_f16 ? launch_variant<false, true, kPolyOf8>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream)
+                   : launch_variant<false, false, kPolyOf8>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
 }
 
 } // namespace
@@ -527,12 +602,19 @@ int launch_flash_attn_fwd(const uint16_t *q, const uint16_t *k, const uint16_t *
         return kErrCuda;
     }
     const float scale_log2 = scale * 1.4426950408889634f;
-    if (causal) {
-        return out_f16 ? launch_variant<true, true>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream)
-                       : launch_variant<true, false>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
+    // share of the exponentials moved from the special-function unit to the FMA pipe (pairs out of every 8);
+    // PTO_B200_FA_POLY overrides the default for experiments
+    static const int poly = [] {
+        const char *e = getenv("PTO_B200_FA_POLY");
+        return e != nullptr ? atoi(e) : 1;
+    }();
+    switch (poly) {
+        case 0: return launch_mode<0>(causal != 0, out_f16 != 0, tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
+        case 2: return launch_mode<2>(causal != 0, out_f16 != 0, tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
+        case 3: return launch_mode<3>(causal != 0, out_f16 != 0, tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
+        case 4: return launch_mode<4>(causal != 0, out_f16 != 0, tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
+        default: return launch_mode<1>(causal != 0, out_f16 != 0, tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
     }
-    return out_f16 ? launch_variant<false, true>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream)
-                   : launch_variant<false, false>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
 }
 
 } // namespace pto_b200
