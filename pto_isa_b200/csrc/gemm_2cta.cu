@@ -21,8 +21,12 @@ namespace {
 constexpr int BM = 128;       // rows of A / C per block (256 per pair)
 constexpr int BN = 256;       // columns of C per pair
 constexpr int BNH = 128;      // columns of B staged per block
-constexpr int BK = 64;
-constexpr int kStages = 6;
+#ifndef PTO_B200_GEMM2_BK
+#define PTO_B200_GEMM2_BK 128
+#endif
+constexpr int BK = PTO_B200_GEMM2_BK; // k extent of a stage: BK / 16 MMAs per full/empty barrier round trip
+constexpr int kBoxK = 64;             // k extent of one TMA box (128 bytes, the swizzle span)
+constexpr int kStages = (192 * 1024) / ((BM + BNH) * BK * 2);
 constexpr int kABytes = BM * BK * 2;  // 16 KiB
 constexpr int kBBytes = BNH * BK * 2; // 16 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
@@ -38,7 +42,12 @@ struct Control {
     int abort_flag;
 };
 
-constexpr int kSmemBytes = kStages * kStageBytes + sizeof(Control) + 1024;
+// TSTORE staging: each epilogue warp owns two 32 x 32 fp32 slabs (4 KiB, 128-byte rows, 128-byte swizzle) that it
+// fills from tensor memory and hands to a TMA store, so that the accumulator leaves the SM as full 128-byte
+// lines issued by one instruction instead of 32 row-strided stores per register.
+constexpr int kSlabBytes = 32 * 32 * 4;
+constexpr int kStagingBytes = 4 * 2 * kSlabBytes;
+constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + sizeof(Control) + 1024;
 
 // C tiles are walked in bands of kGroupN tile columns, tile rows fastest inside a band, so that the tiles in
 // flight at any time (one per block pair) form a roughly square patch: their A and B panels stay in L2.
@@ -113,11 +122,13 @@ __device__ __forceinline__ void tc_mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_d
 template <int kBLayout>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    float *__restrict__ c, int m, int n, int k, DeviceStatus *status)
+                    const __grid_constant__ CUtensorMap tmap_c, int c_by_tma, float *__restrict__ c, int m, int n,
+                    int k, DeviceStatus *status)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    Control *ctl = reinterpret_cast<Control *>(smem + kStages * kStageBytes);
+    uint8_t *staging = smem + kStages * kStageBytes;
+    Control *ctl = reinterpret_cast<Control *>(staging + kStagingBytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -142,6 +153,9 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         fence_mbar_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
+        if (c_by_tma) {
+            tma_prefetch_desc(&tmap_c);
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
@@ -177,9 +191,16 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (rank == 0) {
                         mbar_arrive_expect_tx(&ctl->full[stage], 2 * kStageBytes); // bytes of both blocks
                     }
-                    tma_load_2d_pair(sa, &tmap_a, leader_full, kb * BK, row0);
+#pragma unroll
+                    for (int h = 0; h < BK / kBoxK; ++h) {
+                        tma_load_2d_pair(sa + h * (BM * kBoxK * 2), &tmap_a, leader_full, kb * BK + h * kBoxK, row0);
+                    }
                     if (kBLayout == 1) {
-                        tma_load_2d_pair(sb, &tmap_b, leader_full, kb * BK, col0);
+#pragma unroll
+                        for (int h = 0; h < BK / kBoxK; ++h) {
+                            tma_load_2d_pair(sb + h * (BNH * kBoxK * 2), &tmap_b, leader_full, kb * BK + h * kBoxK,
+                                             col0);
+                        }
                     } else {
 #pragma unroll
                         for (int j = 0; j < BNH / 64; ++j) {
@@ -199,6 +220,13 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             constexpr uint32_t idesc = make_idesc_f16(2 * BM, BN, 0, kBLayout == 0 ? 1 : 0);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
+            // descriptors of stage 0; a stage or a k step further on only moves the 16-byte-unit address field
+            const uint64_t a_desc0 = make_sw128_desc(smem_u32(smem), 16, 1024);
+            const uint64_t b_desc0 = (kBLayout == 1) ? make_sw128_desc(smem_u32(smem) + kABytes, 16, 1024)
+                                                     : make_sw128_desc(smem_u32(smem) + kABytes, 64 * BK * 2, 1024);
+            constexpr uint32_t kBStep = (kBLayout == 1) ? (32 >> 4) : ((16 * 128) >> 4);
+            const uint32_t empty_mine = map_to_rank(&ctl->empty[0], 0);
+            const uint32_t empty_peer = map_to_rank(&ctl->empty[0], 1);
             for (int t = pair; t < num_tiles && ok; t += pairs) {
                 if (!mbar_wait(&ctl->acc_empty[acc], acc_phase ^ 1u, abort_flag)) {
                     break;
@@ -211,19 +239,20 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_base = smem_u32(smem + stage * kStageBytes);
-                    const uint32_t b_base = a_base + kABytes;
+                    const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage * (kStageBytes >> 4));
+                    const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(stage * (kStageBytes >> 4));
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; ++kk) {
-                        const uint64_t a_desc = make_sw128_desc(a_base + kk * 32, 16, 1024);
-                        const uint64_t b_desc = (kBLayout == 1)
-                                                    ? make_sw128_desc(b_base + kk * 32, 16, 1024)
-                                                    : make_sw128_desc(b_base + kk * (16 * 128), 64 * BK * 2, 1024);
-                        tc_mma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        // K-major operands: 64-element boxes side by side, 32 bytes per k step inside a box
+                        const uint32_t a_off = ((kk >> 2) * (BM * kBoxK * 2) + (kk & 3) * 32) >> 4;
+                        const uint32_t b_off =
+                            (kBLayout == 1) ? (((kk >> 2) * (BNH * kBoxK * 2) + (kk & 3) * 32) >> 4) : kk * kBStep;
+                        tc_mma_f16_ss_pair(d_tmem, a_desc + static_cast<uint64_t>(a_off),
+                                           b_desc + static_cast<uint64_t>(b_off), idesc, (kb | kk) != 0 ? 1u : 0u);
                     }
                     // the stage is reusable in both blocks once these MMAs have read it
-                    tc_commit_pair(map_to_rank(&ctl->empty[stage], 0));
-                    tc_commit_pair(map_to_rank(&ctl->empty[stage], 1));
+                    tc_commit_pair(empty_mine + stage * 8);
+                    tc_commit_pair(empty_peer + stage * 8);
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -245,6 +274,8 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int quarter = warp & 3;
         uint32_t acc = 0, acc_phase = 0;
         const bool vec_ok = ((n & 3) == 0) && ((reinterpret_cast<uintptr_t>(c) & 15u) == 0);
+        uint8_t *slabs = staging + (warp - 2) * 2 * kSlabBytes;
+        uint32_t slab = 0;
         for (int t = pair; t < num_tiles; t += pairs) {
             int tm, tn;
             tile_coords(t, tiles_m, tiles_n, tm, tn);
@@ -261,7 +292,29 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 tmem_ld_32x32(taddr + cb * 32, r);
                 tmem_ld_wait();
                 const int col0 = tn * BN + cb * 32;
-                if (row < m) {
+                if (c_by_tma) {
+                    // the store that last read this slab (two chunks ago) has finished reading it
+                    if (lane == 0) {
+                        tma_store_wait_read<1>();
+                    }
+                    __syncwarp();
+                    uint8_t *dst = slabs + slab * kSlabBytes + lane * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        *reinterpret_cast<uint4 *>(dst + ((j ^ (lane & 7)) << 4)) =
+                            make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int slab_row0 = row - lane;
+                        if (slab_row0 < m && col0 < n) {
+                            tma_store_2d(&tmap_c, slabs + slab * kSlabBytes, col0, slab_row0);
+                        }
+                        tma_store_commit();
+                    }
+                    slab ^= 1u;
+                } else if (row < m) {
                     if (vec_ok && col0 + 32 <= n) {
                         float4 *dst = reinterpret_cast<float4 *>(crow + cb * 32);
 #pragma unroll
@@ -288,6 +341,9 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 acc = 0;
                 acc_phase ^= 1u;
             }
+        }
+        if (c_by_tma && lane == 0) {
+            tma_store_wait_all<0>(); // the slabs are read, and C is written, before the block retires
         }
     }
 
@@ -317,13 +373,23 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
                         cudaStream_t stream)
 {
-    CUtensorMap tmap_a, tmap_b;
-    int rc = make_tmap_2d(&tmap_a, a, 2, m, k, k, BM, BK, true);
+    CUtensorMap tmap_a, tmap_b, tmap_c;
+    int rc = make_tmap_2d(&tmap_a, a, 2, m, k, k, BM, kBoxK, true);
     if (rc != kOk) {
         return rc;
     }
+    // C leaves through TMA stores when its rows are 16-byte aligned; otherwise the epilogue stores directly
+    const int c_by_tma = ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0) ? 1 : 0;
+    if (c_by_tma) {
+        rc = make_tmap_2d(&tmap_c, c, 4, m, n, n, 32, 32, true);
+        if (rc != kOk) {
+            return rc;
+        }
+    } else {
+        tmap_c = tmap_a; // never dereferenced
+    }
     if (b_layout == 1) {
-        rc = make_tmap_2d(&tmap_b, b, 2, n, k, k, BNH, BK, true);
+        rc = make_tmap_2d(&tmap_b, b, 2, n, k, k, BNH, kBoxK, true);
     } else {
         rc = make_tmap_2d(&tmap_b, b, 2, k, n, n, BK, 64, true);
     }
@@ -352,9 +418,9 @@ int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, i
         attr_set[b_layout] = true;
     }
     if (b_layout == 1) {
-        gemm2_f16f32_kernel<1><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c, m, n, k, status);
+        gemm2_f16f32_kernel<1><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, m, n, k, status);
     } else {
-        gemm2_f16f32_kernel<0><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c, m, n, k, status);
+        gemm2_f16f32_kernel<0><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, m, n, k, status);
     }
     return check_launch();
 }
