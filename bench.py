@@ -56,16 +56,47 @@ def load_peaks():
 # ------------------------------------------------------------------ clock sampling during the timed region
 
 class ClockSampler:
+    """Samples the SM clock and the clock event reasons of one GPU while the timed region runs: NVML polled from a
+    thread every few milliseconds (read-only queries), or an `nvidia-smi -lms` child when NVML cannot be loaded."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+                   0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, index):
+    def __init__(self, index, uuid=None):
         self.index = index
-        self.samples = []
+        self.uuid = uuid
+        self.samples = []      # (sm_mhz, reasons bitmask) from NVML, or csv fields from nvidia-smi
+        self.max_mhz = None
         self.proc = None
         self.thread = None
+        self.nvml = None
+        self.handle = None
+        self.stop_flag = threading.Event()
+
+    def _open_nvml(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = None
+            if self.uuid:
+                try:
+                    handle = pynvml.nvmlDeviceGetHandleByUUID(self.uuid)
+                except Exception:
+                    handle = None
+            if handle is None:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self.nvml, self.handle = pynvml, handle
+            return True
+        except Exception:
+            return False
 
     def start(self):
+        if self._open_nvml():
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -76,6 +107,17 @@ class ClockSampler:
         self.thread = threading.Thread(target=self._read, daemon=True)
         self.thread.start()
 
+    def _poll_nvml(self):
+        n = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                mhz = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                bits = int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                self.samples.append((mhz, bits))
+            except Exception:
+                pass
+            time.sleep(0.003)
+
     def _read(self):
         for line in self.proc.stdout:
             parts = [x.strip() for x in line.split(",")]
@@ -83,6 +125,16 @@ class ClockSampler:
                 self.samples.append(parts)
 
     def stop(self):
+        if self.nvml is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            sm = [s[0] for s in self.samples]
+            bits = 0
+            for s in self.samples:
+                bits |= s[1]
+            reasons = sorted(name for bit, name in self.REASON_BITS.items() if bits & bit)
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz, "samples": len(sm),
+                    "sm_mhz_min": min(sm) if sm else None, "reasons": reasons, "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -104,7 +156,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi"}
 
 
 # ------------------------------------------------------------------ CPU side (reference arm / cpu_baseline)
@@ -296,7 +348,12 @@ def run_gpu_arm(args):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    gpu_uuid = None
+    try:
+        gpu_uuid = "GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid)
+    except Exception:
+        pass
+    sampler = ClockSampler(local_rank, gpu_uuid) if rank == 0 else None
     if sampler:
         sampler.start()
     launch_ms = []
@@ -413,7 +470,7 @@ def run_gpu_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     args = ap.parse_args()

@@ -56,8 +56,8 @@ struct Control {
     uint64_t q_full;
     uint64_t ring_full[kRing], ring_empty[kRing];
     uint64_t s_full[2];  // S tile complete in tensor memory
-    uint64_t s_free[2];  // S tile copied to registers by all 128 softmax threads: S(j+1) may overwrite it
-    uint64_t p_full[2];  // P tile written to shared memory (and O rescaled) by all 128 softmax threads
+    uint64_t s_free[2];  // S tile copied to registers by all four softmax warps: S(j+1) may overwrite it
+    uint64_t p_full[2];  // P tile written to shared memory (and O rescaled) by all four softmax warps
     uint64_t pv_done[2]; // PV product of the step complete: P buffer reusable, O consistent
     uint32_t tmem_base;
     int abort_flag;
@@ -192,8 +192,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(&ctl->s_full[t], 1);
-            mbar_init(&ctl->s_free[t], kTileQ);
-            mbar_init(&ctl->p_full[t], kTileQ);
+            mbar_init(&ctl->s_free[t], kTileQ / 32); // one arrival per softmax warp
+            mbar_init(&ctl->p_full[t], kTileQ / 32);
             mbar_init(&ctl->pv_done[t], 1);
         }
         ctl->abort_flag = 0;
@@ -378,7 +378,9 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             }
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(&ctl->s_free[t]); // the tensor core may start S(j+1) into the same columns
+            if (lane == 0) {
+                mbar_arrive(&ctl->s_free[t]); // the tensor core may start S(j+1) into the same columns
+            }
 
             const bool diag = kCausal && (j * kTileKV + kTileKV - 1 > (2 * qb + t) * kTileQ);
             if (diag) {
@@ -479,7 +481,10 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             }
             l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             fence_proxy_async_smem(); // the tensor core reads P through the asynchronous proxy
-            mbar_arrive(&ctl->p_full[t]);
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&ctl->p_full[t]);
+            }
         }
 
         // output: O / l
