@@ -38,8 +38,8 @@ FLOPS_PER_PROBLEM = 2.0 * M * N * K
 TILE_M, TILE_N = 128, 256
 TILE_FLOPS = 2.0 * TILE_M * TILE_N * K
 # dram__bytes_read.sum + dram__bytes_write.sum of one 6144^3 launch, from the ncu capture summarised in
-# profiles/gemm_f16f32_6144_ncu.md
-GEMM_DRAM_TRAFFIC_BYTES = 820.7e6
+# profiles/gemm2_f16f32_6144_ncu.md
+GEMM_DRAM_TRAFFIC_BYTES = 571.3e6
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -437,7 +437,7 @@ def run_gpu_arm(args):
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "traffic": GEMM_DRAM_TRAFFIC_BYTES, "peak_kind": f"{peak_kind} cuBLAS bf16 8192^3, sustained loop "
                 "(launches timed inside a long step)", "frac_of_burst": achieved / peaks["bf16_tflops"],
-                "frac_of_nominal_2250": achieved / 2250.0, "kernel": "gemm_f16f32_kernel<1>",
+                "frac_of_nominal_2250": achieved / 2250.0, "kernel": "gemm2_f16f32_kernel<1>",
                 "avg_launch_ms": avg_launch_ms, "algorithmic_flops_per_launch": FLOPS_PER_PROBLEM}
     cpu = None
     extra = None
