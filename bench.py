@@ -243,6 +243,53 @@ def timed_events(torch, fn, iters):
     return [s.elapsed_time(e) for s, e in evs]
 
 
+def sharded_attention(torch, pto, dist, world, rank, barrier, iters=3):
+    from pto_isa_b200 import shard
+    heads, S, D = 32 * 32, 8192, 128
+    b, e = shard.unit_range(heads, world, rank)
+    mine = e - b
+    g = torch.Generator(device="cuda").manual_seed(900 + rank)
+    q = (torch.randn(mine, S, D, device="cuda", generator=g) / D ** 0.5).half()
+    k = torch.randn(mine, S, D, device="cuda", generator=g).half()
+    v = torch.randn(mine, S, D, device="cuda", generator=g).half()
+    o = torch.empty_like(q)
+    for _ in range(2):
+        pto.flash_attn_fwd(q, k, v, causal=True, scale=1.0, out=o)
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(iters):
+        pto.flash_attn_fwd(q, k, v, causal=True, scale=1.0, out=o)
+    s1.record()
+    barrier()
+    t = torch.tensor([s0.elapsed_time(s1) / iters], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    flops = 4.0 * heads * D * S * (S + 1) / 2
+    res = {"workload": "flash_attn_fwd f16 batch 32 x 32 heads, S=8192, D=128, causal, fp16 O; heads sharded",
+           "value": flops / ms / 1e9, "unit": "TFLOP/s", "ms": ms, "scaling": "strong", "heads_per_gpu": mine,
+           "n_gpus": world, "gpu_launches": iters}
+    if dist is not None:
+        full = shard.all_gather_units(o, heads)  # warm-up
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        full = shard.all_gather_units(o, heads)
+        g1.record()
+        barrier()
+        tg = torch.tensor([g0.elapsed_time(g1)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        ag = float(tg.item())
+        res["allgather_ms"] = ag
+        res["bytes_gathered_per_gpu"] = int(full.numel() * 2)
+        res["value_with_allgather"] = flops / (ms + ag) / 1e9
+        del full
+    del q, k, v, o
+    torch.cuda.empty_cache()
+    return res
+
+
 def extras(torch, pto, peaks, peak_kind):
     """Attention and vector tile ops, rank 0 only, short.  Buffers are rotated so inputs come from HBM."""
     out = []
@@ -327,9 +374,19 @@ def run_gpu_arm(args):
         import torch.distributed as dist_mod
         dist = dist_mod
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # NCCL writes its banner and debug lines to stdout by default; stdout carries the one JSON line
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # NCCL prints its version banner (and debug lines) on stdout while the communicator is created; stdout
+        # carries the one JSON line, so file descriptor 1 points at stderr until the first collective is through
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
     peaks, peak_kind = load_peaks()
 
     g = torch.Generator(device="cuda").manual_seed(100 + rank)
@@ -406,6 +463,10 @@ def run_gpu_arm(args):
                           "value": world * P * FLOPS_PER_PROBLEM / (step_ms + ag_ms) / 1e9, "unit": "TFLOP/s"}
         del full
 
+    # multi-head attention of the sharding config (batch 32 x 32 heads, S 8192, D 128, causal, fp16 O): the 1024
+    # heads are split over the ranks (fixed total work: strong scaling), then every rank gathers all outputs
+    sharded_attn = sharded_attention(torch, pto, dist, world, rank, barrier)
+
     # end to end through the C ABI's host-buffer entry point, pinned host operands
     e2e_steps = max(1, min(args.steps, 2))
     ha = [torch.empty(M, K, dtype=torch.float16).pin_memory() for _ in range(2)]
@@ -461,7 +522,8 @@ def run_gpu_arm(args):
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": int(P * (M * K + N * K) * 2),
                 "d2h_bytes_per_step": int(P * M * N * 4), "steps": e2e_steps, "matches_device_path": e2e_check,
                 "api": "pto_b200_gemm_f16f32_host (C ABI, pinned host buffers)"},
-        "gpu_launches": args.steps * P, "with_allgather": with_allgather, "extras": extra,
+        "gpu_launches": args.steps * P, "with_allgather": with_allgather, "sharded_attention": sharded_attn,
+        "extras": extra,
     }
     print(json.dumps(line), flush=True)
     if dist is not None:
