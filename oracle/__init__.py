@@ -25,7 +25,9 @@ def build(force=False):
     if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(os.path.join(_HERE, "pto_oracle.c")):
         subprocess.check_call(["make", "-C", _HERE, "liboracle.so"], stdout=subprocess.DEVNULL)
     ref_so = os.path.join(_HERE, "_ref", "libpto_ref.so")
-    if os.path.isdir("/root/reference/include/pto") and (force or not os.path.exists(ref_so)):
+    ref_srcs = [os.path.join(_HERE, f) for f in os.listdir(_HERE) if f.startswith("ref_") and f.endswith(".cpp")]
+    stale = os.path.exists(ref_so) and any(os.path.getmtime(f) > os.path.getmtime(ref_so) for f in ref_srcs)
+    if os.path.isdir("/root/reference/include/pto") and (force or stale or not os.path.exists(ref_so)):
         subprocess.check_call(["make", "-C", _HERE, "ref"], stdout=subprocess.DEVNULL)
 
 
@@ -101,6 +103,96 @@ class _Lib:
         out = np.empty(x.shape[0], np.float32)
         rc = self._f("trowsum_f32")(_p(x), _p(out), x.shape[0], x.shape[1])
         assert rc == 0
+        return out
+
+    # -- second batch of vector ops (op codes as in include/pto_b200.h)
+    def trowexpand_f32(self, a, s, op):
+        """dst[r, c] = a[r, c] op s[r]; op 7 ignores `a` (plain TROWEXPAND, pass the wanted shape as zeros)."""
+        a = np.ascontiguousarray(a, np.float32)
+        s = np.ascontiguousarray(s, np.float32)
+        out = np.empty_like(a)
+        rc = self._f("trowexpand_f32")(_p(a), _p(s), _p(out), a.shape[0], a.shape[1], int(op))
+        if rc != 0:
+            raise ValueError("trowexpand: unsupported shape or operator")
+        return out
+
+    def trowmin_f32(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape[0], np.float32)
+        rc = self._f("trowmin_f32")(_p(x), _p(out), x.shape[0], x.shape[1])
+        if rc != 0:
+            raise ValueError("trowmin: unsupported shape")
+        return out
+
+    def tcolreduce_f32(self, x, op):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape[1], np.float32)
+        rc = self._f("tcolreduce_f32")(_p(x), _p(out), x.shape[0], x.shape[1], int(op))
+        if rc != 0:
+            raise ValueError("tcolreduce: unsupported shape or operator")
+        return out
+
+    def tfillpad_f32(self, src, valid_rows, valid_cols, pad_kind):
+        """pad_kind 1 zero, 2 max (+inf), 3 min (-inf).  The reference build takes dense 64 x 256 tiles only."""
+        src = np.ascontiguousarray(src, np.float32)
+        out = np.empty_like(src)
+        if self.prefix == "pto_ref_":
+            assert src.shape == (64, 256)
+            rc = self._f("tfillpad_f32")(_p(src), _p(out), int(valid_rows), int(valid_cols), int(pad_kind))
+        else:
+            pad = {1: 0, 2: 0x7f800000, 3: 0xff800000}[int(pad_kind)]
+            rc = self._f("tfillpad_b32")(_p(src), _p(out), src.shape[0], src.shape[1], int(valid_rows),
+                                         int(valid_cols), ctypes.c_uint32(pad))
+        if rc != 0:
+            raise ValueError("tfillpad: unsupported shape")
+        return out
+
+    def ttrans(self, src):
+        src = np.ascontiguousarray(src)
+        out = np.empty((src.shape[1], src.shape[0]), src.dtype)
+        if self.prefix == "pto_ref_":
+            assert src.shape == (64, 128) and src.dtype == np.float32
+            rc = self._f("ttrans_f32_64x128")(_p(src), _p(out))
+        else:
+            name = "ttrans_b32" if src.itemsize == 4 else "ttrans_b16"
+            rc = self._f(name)(_p(src), _p(out), src.shape[0], src.shape[1])
+        assert rc == 0
+        return out
+
+    def tsel(self, mask, a, b):
+        """mask: uint8, one bit per element of the row-major operands, least significant bit first."""
+        a = np.ascontiguousarray(a, np.float32)
+        b = np.ascontiguousarray(b, np.float32)
+        mask = np.ascontiguousarray(mask, np.uint8)
+        out = np.empty_like(a)
+        name = "tsel_f32" if self.prefix == "pto_ref_" else "tsel_b32"
+        rc = self._f(name)(_p(mask), _p(a), _p(b), _p(out), a.shape[0], a.shape[1])
+        if rc != 0:
+            raise ValueError("tsel: unsupported shape")
+        return out
+
+    def tcmps_f32(self, x, scalar, mode):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.zeros(x.size // 8, np.uint8)
+        if self.prefix == "pto_ref_":
+            assert x.shape == (64, 256)
+            rc = self._f("tcmps_f32")(_p(x), ctypes.c_float(scalar), _p(out), int(mode))
+        else:
+            rc = self._f("tcmps_f32")(_p(x), ctypes.c_float(scalar), _p(out), x.shape[0], x.shape[1], int(mode))
+        if rc != 0:
+            raise ValueError("tcmps: unsupported shape")
+        return out
+
+    def tcmp_f32(self, a, b, mode):
+        a = np.ascontiguousarray(a, np.float32)
+        b = np.ascontiguousarray(b, np.float32)
+        out = np.empty_like(a)
+        if self.prefix == "pto_ref_":
+            rc = self._f("tcmp_f32")(_p(a), _p(b), _p(out), a.shape[0], a.shape[1], int(mode))
+        else:
+            rc = self._f("tcmp_f32")(_p(a), _p(b), _p(out), _i64(a.size), int(mode))
+        if rc != 0:
+            raise ValueError("tcmp: unsupported shape")
         return out
 
     # -- GEMM

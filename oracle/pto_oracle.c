@@ -664,3 +664,180 @@ int pto_oracle_attn_head_f32_plain(const float *q, const float *k, const float *
     free(x);
     return 0;
 }
+
+/* ------------------------------------------------------------------ FA-adjacent vector ops (second batch)
+ * Row-expand family, column reductions, TROWMIN, TFILLPAD, TTRANS, TSEL, TCMP / TCMPS.
+ * All tensors are dense row-major; `cols` is both the valid width and the row pitch. */
+
+/* ElementOpCal of include/pto/cpu/ElementOp.h: ADD :85-95, SUB :98-108, MUL, DIV, MAX :201-211 (std::max),
+ * MIN :214-224 (std::min), EXPDIF :265-270 (float(exp(double(a - b)))).  Codes as in include/pto_b200.h. */
+static inline float elem_op(int op, float a, float b)
+{
+    switch (op) {
+        case 0: return a + b;
+        case 1: return a - b;
+        case 2: return a * b;
+        case 3: return a / b;
+        case 4: return (a < b) ? b : a; /* std::max(a, b) */
+        case 5: return (b < a) ? b : a; /* std::min(a, b) */
+        case 6: return (float)exp((double)(a - b));
+        default: return b;              /* 7: plain TROWEXPAND, include/pto/cpu/TRowExpand.hpp:22-37 */
+    }
+}
+
+/* TROWEXPAND{ADD,SUB,MUL,DIV,MAX,MIN,EXPDIF} and TROWEXPAND: dst[r, c] = a[r, c] op s[r]
+ * (include/pto/cpu/TRowExpandOp.hpp:38-57; s read from column 0 of an R x 1 tile, :22-33). */
+int pto_oracle_trowexpand_f32(const float *a, const float *s, float *dst, int rows, int cols, int op)
+{
+    if (op < 0 || op > 7) {
+        return -1;
+    }
+    for (int r = 0; r < rows; ++r) {
+        for (int c = 0; c < cols; ++c) {
+            const int64_t i = (int64_t)r * cols + c;
+            dst[i] = elem_op(op, op == 7 ? 0.0f : a[i], s[r]);
+        }
+    }
+    return 0;
+}
+
+/* TROWMIN (include/pto/cpu/TRowMin.hpp:21-41): first element, then std::min left to right. */
+int pto_oracle_trowmin_f32(const float *src, float *dst, int rows, int cols)
+{
+    for (int r = 0; r < rows; ++r) {
+        float m = src[(int64_t)r * cols];
+        for (int c = 1; c < cols; ++c) {
+            const float x = src[(int64_t)r * cols + c];
+            m = (x < m) ? x : m;
+        }
+        dst[r] = m;
+    }
+    return 0;
+}
+
+/* TCOLSUM / TCOLMAX / TCOLMIN: dst[c] over the rows, top to bottom (include/pto/cpu/TColSum.hpp:19-30 sequential
+ * fp32 sum from 0; TColMax.hpp:19-33 and TColMin.hpp start from row 0 and replace on strict > / <).
+ * op: 0 = sum, 4 = max, 5 = min. */
+int pto_oracle_tcolreduce_f32(const float *src, float *dst, int rows, int cols, int op)
+{
+    if (op != 0 && op != 4 && op != 5) {
+        return -1;
+    }
+    for (int c = 0; c < cols; ++c) {
+        float acc = (op == 0) ? 0.0f : src[c];
+        for (int r = (op == 0) ? 0 : 1; r < rows; ++r) {
+            const float x = src[(int64_t)r * cols + c];
+            if (op == 0) {
+                acc += x;
+            } else if (op == 4) {
+                acc = (x > acc) ? x : acc;
+            } else {
+                acc = (x < acc) ? x : acc;
+            }
+        }
+        dst[c] = acc;
+    }
+    return 0;
+}
+
+/* TFILLPAD (include/pto/cpu/TFillPad.hpp:19-49): dst is rows x cols; the valid_rows x valid_cols corner is copied
+ * from src (same pitch), everything else becomes the pad value.  Elements are 32-bit patterns; the caller picks
+ * the pattern that PadValue::Zero / Max / Min mean for its type (:24-36: +inf / -inf for floating types). */
+int pto_oracle_tfillpad_b32(const uint32_t *src, uint32_t *dst, int rows, int cols, int valid_rows, int valid_cols,
+                            uint32_t pad)
+{
+    for (int r = 0; r < rows; ++r) {
+        for (int c = 0; c < cols; ++c) {
+            const int64_t i = (int64_t)r * cols + c;
+            dst[i] = (r < valid_rows && c < valid_cols) ? src[i] : pad;
+        }
+    }
+    return 0;
+}
+
+/* TTRANS (include/pto/cpu/TTrans.hpp:17-45, plain layouts): dst[c, r] = src[r, c]; src rows x cols, dst cols x rows. */
+int pto_oracle_ttrans_b32(const uint32_t *src, uint32_t *dst, int rows, int cols)
+{
+    for (int r = 0; r < rows; ++r) {
+        for (int c = 0; c < cols; ++c) {
+            dst[(int64_t)c * rows + r] = src[(int64_t)r * cols + c];
+        }
+    }
+    return 0;
+}
+int pto_oracle_ttrans_b16(const uint16_t *src, uint16_t *dst, int rows, int cols)
+{
+    for (int r = 0; r < rows; ++r) {
+        for (int c = 0; c < cols; ++c) {
+            dst[(int64_t)c * rows + r] = src[(int64_t)r * cols + c];
+        }
+    }
+    return 0;
+}
+
+/* TSEL (include/pto/cpu/TSel.hpp:22-46): the mask bytes are consumed bit by bit, least significant first, in
+ * row-major order over the valid region: element i = r * cols + c takes src0 when bit (i & 7) of byte (i >> 3)
+ * is set, else src1. */
+int pto_oracle_tsel_b32(const uint8_t *mask, const uint32_t *src0, const uint32_t *src1, uint32_t *dst, int rows,
+                        int cols)
+{
+    const int64_t n = (int64_t)rows * cols;
+    for (int64_t i = 0; i < n; ++i) {
+        dst[i] = ((mask[i >> 3] >> (i & 7)) & 1) ? src0[i] : src1[i];
+    }
+    return 0;
+}
+
+/* CmpCall of include/pto/cpu/TCmps.hpp:23-52: EQ / NE compare |a - b| in double against 1e-9, the others are the
+ * plain operators.  Modes: EQ 0, NE 1, LT 2, LE 3, GT 4, GE 5 (include/pto/common/type.hpp:131-139). */
+static inline int cmp_call(float a, float b, int mode)
+{
+    const double diff = (double)a - (double)b;
+    switch (mode) {
+        case 0: return fabs(diff) < 1e-9;
+        case 1: return fabs(diff) > 1e-9;
+        case 2: return a < b;
+        case 3: return a <= b;
+        case 4: return a > b;
+        case 5: return a >= b;
+        default: return fabs(diff) < 1e-9;
+    }
+}
+
+/* TCMPS (include/pto/cpu/TCmps.hpp:54-91): one result bit per element, packed least significant bit first,
+ * cols / 8 bytes per row, rows back to back.  cols must be a multiple of 8. */
+int pto_oracle_tcmps_f32(const float *src, float scalar, uint8_t *dst, int rows, int cols, int mode)
+{
+    if (cols % 8 != 0) {
+        return -1;
+    }
+    const int64_t n = (int64_t)rows * cols;
+    for (int64_t b = 0; b < n / 8; ++b) {
+        uint8_t v = 0;
+        for (int bit = 0; bit < 8; ++bit) {
+            v |= (uint8_t)(cmp_call(src[b * 8 + bit], scalar, mode) << bit);
+        }
+        dst[b] = v;
+    }
+    return 0;
+}
+
+/* TCMP in the CPU simulation (include/pto/cpu/ElementTileOp.h:177-184, ElementOp.h:227-254): the result tile has
+ * the operands' type and holds 1 or 0 from the plain C++ operators. */
+int pto_oracle_tcmp_f32(const float *a, const float *b, float *dst, int64_t n, int mode)
+{
+    for (int64_t i = 0; i < n; ++i) {
+        int r;
+        switch (mode) {
+            case 0: r = a[i] == b[i]; break;
+            case 1: r = a[i] != b[i]; break;
+            case 2: r = a[i] < b[i]; break;
+            case 3: r = a[i] <= b[i]; break;
+            case 4: r = a[i] > b[i]; break;
+            case 5: r = a[i] >= b[i]; break;
+            default: r = a[i] == b[i]; break;
+        }
+        dst[i] = (float)r;
+    }
+    return 0;
+}

@@ -198,6 +198,114 @@ def gen_gemm(ref, tmp, out):
                         golden=read(os.path.join(d, "output/golden.bin"), np.float32, (m, n)))
 
 
+def gen_vector2(ref, tmp, out):
+    """Row-expand family, TROWMIN, column reductions, TTRANS, TSEL, TCMPS, TCMP: the float32 cases of the
+    reference's generators (each module seeds np.random with 19 when it is loaded; cases run in its own order,
+    the non-float32 ones too, so that the random stream matches)."""
+    keep = {}
+    base = os.path.join(ref, "tests/cpu/st/testcase")
+
+    # trowexpand/gen_data.py:61-63 (case list), :19-25 (generator)
+    mod = load(os.path.join(base, "trowexpand/gen_data.py"), "ref_trowexpand_gen")
+    d = in_case_dir(tmp, "trowexpand_0")
+    mod.gen_expand()
+    keep["trowexpand_src"] = read(os.path.join(d, "input.bin"), np.float32, (64, 64))
+    keep["trowexpand_golden"] = read(os.path.join(d, "golden.bin"), np.float32, (64, 64))
+
+    # trowexpandop/gen_data.py:66-73 (case list x operations), :19-45 (generator)
+    mod = load(os.path.join(base, "trowexpandop/gen_data.py"), "ref_trowexpandop_gen")
+    P = mod.TRowExpandOpParams
+    for pi, prm in enumerate([P(np.float32, 64, 64), P(np.float16, 16, 256)]):
+        for op in ["div", "mul", "sub", "add", "min", "max", "expdif"]:
+            d = in_case_dir(tmp, f"trowexpandop_{pi}_{op}")
+            mod.gen_golden_data_trowexpandop(prm, op)
+            if prm.dtype == np.float32:
+                keep[f"trowexpandop_{op}_a"] = read(os.path.join(d, "input1.bin"), np.float32, (64, 64))
+                keep[f"trowexpandop_{op}_s"] = read(os.path.join(d, "input2.bin"), np.float32, (64,))
+                keep[f"trowexpandop_{op}_golden"] = read(os.path.join(d, "golden.bin"), np.float32, (64, 64))
+
+    # trowmin/gen_data.py:59-65 (case list), :19-31 (generator)
+    mod = load(os.path.join(base, "trowmin/gen_data.py"), "ref_trowmin_gen")
+    P = mod.TRowminParams
+    for i, prm in enumerate([P(np.float32, 64, 64, 64, 64, 64, 64), P(np.float16, 64, 64, 64, 64, 64, 64),
+                             P(np.float16, 161, 161, 32, 32, 161, 161), P(np.float32, 77, 81, 32, 16, 77, 81),
+                             P(np.float32, 32, 32, 32, 16, 32, 32)]):
+        d = in_case_dir(tmp, f"trowmin_{i}")
+        mod.gen_golden_data_trowmin(prm)
+        if prm.dtype == np.float32:
+            keep[f"trowmin{i}_src"] = read(os.path.join(d, "input1.bin"), np.float32, (prm.tile_row, prm.tile_col))
+            keep[f"trowmin{i}_golden"] = read(os.path.join(d, "golden.bin"), np.float32)
+
+    # tcolmax/gen_data.py:80-83 (case list), :17-43; tcolsum/gen_data.py:72-75, :17-36; tcolmin/gen_data.py:59-63, :19-31
+    mod = load(os.path.join(base, "tcolmax/gen_data.py"), "ref_tcolmax_gen")
+    P = mod.tcolmaxParams
+    for i, prm in enumerate([P(np.float32, 64, 64, 64, 64, 64, 64), P(np.float16, 16, 256, 16, 256, 16, 256)]):
+        in_case_dir(tmp, f"tcolmax_{i}")
+        _, src, golden = mod.gen_golden_data_tcolmax("", prm)
+        if prm.dtype == np.float32:
+            keep["tcolmax_src"], keep["tcolmax_golden"] = src, golden[0].copy()
+    mod = load(os.path.join(base, "tcolsum/gen_data.py"), "ref_tcolsum_gen")
+    P = mod.TColsumParams
+    for i, prm in enumerate([P(np.float32, 64, 64, 64, 64, 64, 64), P(np.float16, 16, 256, 16, 256, 16, 256)]):
+        in_case_dir(tmp, f"tcolsum_{i}")
+        src, golden = mod.gen_golden_data_tcolsum("", prm)
+        if prm.dtype == np.float32:
+            keep["tcolsum_src"], keep["tcolsum_golden"] = src, golden[0].copy()
+    mod = load(os.path.join(base, "tcolmin/gen_data.py"), "ref_tcolmin_gen")
+    P = mod.TColminParams
+    for i, prm in enumerate([P(np.float32, 64, 64, 64, 64, 64, 64), P(np.float16, 64, 64, 64, 64, 64, 64),
+                             P(np.float32, 32, 32, 32, 16, 32, 32)]):
+        d = in_case_dir(tmp, f"tcolmin_{i}")
+        mod.gen_golden_data_tcolmin(prm)
+        if prm.dtype == np.float32:
+            keep[f"tcolmin{i}_src"] = read(os.path.join(d, "input1.bin"), np.float32, (prm.tile_row, prm.tile_col))
+            keep[f"tcolmin{i}_golden"] = read(os.path.join(d, "golden.bin"), np.float32)
+
+    # ttrans/gen_data.py:41-43 (case list), :19-27 (generator)
+    mod = load(os.path.join(base, "ttrans/gen_data.py"), "ref_ttrans_gen")
+    d = in_case_dir(tmp, "ttrans_0")
+    mod.gen_golden("", mod.TTransParams(np.float32, 128, 128))
+    keep["ttrans_src"] = read(os.path.join(d, "x1_gm.bin"), np.float32, (128, 128))
+    keep["ttrans_golden"] = read(os.path.join(d, "golden.bin"), np.float32, (128, 128))
+
+    # tsel/gen_data.py:62-72 (case list), :28-51 (generator); the float32 cases come first
+    mod = load(os.path.join(base, "tsel/gen_data.py"), "ref_tsel_gen")
+    P = mod.TSelParams
+    for i, prm in enumerate([P("c1", np.float32, 2, 128, 2, 128), P("c2", np.float32, 2, 32, 2, 32),
+                             P("c3", np.float32, 2, 160, 2, 160)]):
+        d = in_case_dir(tmp, f"tsel_{i}")
+        mod.gen_golden_data_tsel(prm)
+        shape = (prm.validRows, prm.validCols)
+        keep[f"tsel{i}_a"] = read(os.path.join(d, "input0.bin"), np.float32, shape)
+        keep[f"tsel{i}_b"] = read(os.path.join(d, "input1.bin"), np.float32, shape)
+        keep[f"tsel{i}_mask"] = read(os.path.join(d, "mask.bin"), np.uint8)
+        keep[f"tsel{i}_golden"] = read(os.path.join(d, "golden.bin"), np.float32, shape)
+
+    # tcmps/gen_data.py:95-106 (case list), :17-64 (generator); float32 cases whose tile is the whole tensor
+    mod = load(os.path.join(base, "tcmps/gen_data.py"), "ref_tcmps_gen")
+    P = mod.tcmpsParams
+    modes = {"CmpMode::EQ": 0, "CmpMode::NE": 1, "CmpMode::LT": 2, "CmpMode::LE": 3, "CmpMode::GT": 4, "CmpMode::GE": 5}
+    cases = [P(np.float16, 32, 32, 32, 32, 32, 32, "CmpMode::GE"), P(np.float32, 1, 64, 1, 64, 1, 64, "CmpMode::EQ"),
+             P(np.float32, 8, 64, 8, 64, 8, 64, "CmpMode::GT"), P(np.float32, 4, 64, 4, 64, 4, 64, "CmpMode::NE"),
+             P(np.float32, 128, 128, 64, 64, 128, 128, "CmpMode::LT"), P(np.int32, 64, 64, 32, 32, 64, 64, "CmpMode::EQ"),
+             P(np.int32, 16, 32, 16, 32, 16, 32, "CmpMode::EQ"), P(np.float32, 128, 128, 128, 128, 128, 128, "CmpMode::LE")]
+    for i, prm in enumerate(cases):
+        d = in_case_dir(tmp, f"tcmps_{i}")
+        mod.gen_golden_data_tcmps("", prm)
+        if prm.dtype == np.float32 and prm.tile_row == prm.global_row:
+            keep[f"tcmps{i}_src"] = read(os.path.join(d, "input1.bin"), np.float32, (prm.tile_row, prm.tile_col))
+            keep[f"tcmps{i}_scalar"] = read(os.path.join(d, "input2.bin"), np.float32)
+            keep[f"tcmps{i}_mode"] = np.array(modes[prm.mode])
+            keep[f"tcmps{i}_golden"] = read(os.path.join(d, "golden.bin"), np.uint8)
+
+    # tcmp/gen_data.py:92-97 (case list), :18-56 (generator)
+    mod = load(os.path.join(base, "tcmp/gen_data.py"), "ref_tcmp_gen")
+    _, a, b, golden = mod.gen_golden_data_tcmp("", mod.TCmpParams(np.float32, 64, 64, 64, 64, 64, 64, "EQ")) \
+        if in_case_dir(tmp, "tcmp_0") else (None, None, None, None)
+    keep["tcmp_a"], keep["tcmp_b"], keep["tcmp_golden"] = a, b, golden
+    np.savez_compressed(os.path.join(out, "vector2.npz"), **keep)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -205,7 +313,7 @@ def main():
     cwd = os.getcwd()
     with tempfile.TemporaryDirectory() as tmp:
         try:
-            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm):
+            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm, gen_vector2):
                 os.chdir(tmp)
                 fn(args.reference, tmp, HERE)
         finally:

@@ -232,3 +232,77 @@ def test_reference_unit_test_kernel(golden_dir):
     port.lib.pto_oracle_attn_head_f32_plain(P(q), P(k), P(v), P(o2), 64, 32)
     assert result_cmp(g, o1, 2e-4)
     assert np.array_equal(o1, o2)
+
+
+# ------------------------------------------------------------------ second batch of vector ops
+
+OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3, "max": 4, "min": 5, "expdif": 6}
+
+
+def test_vector2_golden(golden_dir):
+    """Goldens of the reference's generators (numpy): exact for copies, selections and comparisons; the
+    arithmetic ones within the reference test mains' eps 1e-3 (ResultCmp), in practice bit-equal except expdif."""
+    z = load(golden_dir, "vector2.npz")
+    x = z["trowexpand_src"]
+    assert np.array_equal(port.trowexpand_f32(np.zeros_like(x), x[:, 0].copy(), 7), z["trowexpand_golden"])
+    for name, op in OPS.items():
+        got = port.trowexpand_f32(z[f"trowexpandop_{name}_a"], z[f"trowexpandop_{name}_s"], op)
+        if name == "expdif":
+            assert result_cmp(z[f"trowexpandop_{name}_golden"], got, 1e-3)
+        else:
+            assert np.array_equal(got, z[f"trowexpandop_{name}_golden"]), name
+    for i in (0, 3, 4):  # float32 cases; 3 and 4: the tile is narrower than the tensor, the golden covers min(tile, valid)
+        src, golden = z[f"trowmin{i}_src"], z[f"trowmin{i}_golden"]
+        assert np.array_equal(port.trowmin_f32(src)[: golden.size], golden)
+    assert np.array_equal(port.tcolreduce_f32(z["tcolmax_src"], 4), z["tcolmax_golden"])
+    assert np.array_equal(port.tcolreduce_f32(z["tcolsum_src"], 0), z["tcolsum_golden"])  # small integers: exact
+    for i in (0, 2):
+        src, golden = z[f"tcolmin{i}_src"], z[f"tcolmin{i}_golden"]
+        assert np.array_equal(port.tcolreduce_f32(src, 5)[: golden.size], golden)
+    assert np.array_equal(port.ttrans(z["ttrans_src"]), z["ttrans_golden"])
+    for i in range(3):
+        assert np.array_equal(port.tsel(z[f"tsel{i}_mask"], z[f"tsel{i}_a"], z[f"tsel{i}_b"]), z[f"tsel{i}_golden"])
+    n_cmps = 0
+    for i in range(8):
+        if f"tcmps{i}_src" in z:
+            got = port.tcmps_f32(z[f"tcmps{i}_src"], float(z[f"tcmps{i}_scalar"][0]), int(z[f"tcmps{i}_mode"]))
+            assert np.array_equal(got, z[f"tcmps{i}_golden"]), i
+            n_cmps += 1
+    assert n_cmps == 4
+    assert np.array_equal(port.tcmp_f32(z["tcmp_a"], z["tcmp_b"], 0), z["tcmp_golden"])
+
+
+@needs_ref
+def test_vector2_matches_reference_bits():
+    r = np.random.default_rng(77)
+    bits = lambda a: np.ascontiguousarray(a).view(np.uint32)
+    for rows, cols in ((64, 256), (37, 200), (1, 8), (64, 1)):
+        a = r.standard_normal((rows, cols)).astype(np.float32) * 3
+        s = (r.standard_normal(rows).astype(np.float32) + 2.5)
+        for op in range(8):
+            assert np.array_equal(bits(port.trowexpand_f32(a, s, op)), bits(ref.trowexpand_f32(a, s, op))), (rows, cols, op)
+        assert np.array_equal(bits(port.trowmin_f32(a)), bits(ref.trowmin_f32(a)))
+        for op in (0, 4, 5):
+            assert np.array_equal(bits(port.tcolreduce_f32(a, op)), bits(ref.tcolreduce_f32(a, op))), (rows, cols, op)
+        b = np.round(a)
+        c = np.round(r.standard_normal((rows, cols)).astype(np.float32) * 3)
+        for mode in range(6):
+            assert np.array_equal(port.tcmp_f32(b, c, mode), ref.tcmp_f32(b, c, mode))
+    t = r.standard_normal((64, 256)).astype(np.float32)
+    for kind in (1, 2, 3):
+        for vr, vc in ((64, 256), (40, 100), (1, 1)):
+            assert np.array_equal(bits(port.tfillpad_f32(t, vr, vc, kind)), bits(ref.tfillpad_f32(t, vr, vc, kind)))
+    u = r.standard_normal((64, 128)).astype(np.float32)
+    assert np.array_equal(port.ttrans(u), ref.ttrans(u))
+    for rows in (1, 50, 64):
+        m = r.integers(0, 256, rows * 256 // 8, dtype=np.uint8)
+        a = r.standard_normal((rows, 256)).astype(np.float32)
+        b = r.standard_normal((rows, 256)).astype(np.float32)
+        assert np.array_equal(port.tsel(m, a, b), ref.tsel(m, a, b))
+    t2 = np.round(t * 2) / 2
+    for mode in range(6):
+        assert np.array_equal(port.tcmps_f32(t2, 0.5, mode), ref.tcmps_f32(t2, 0.5, mode))
+        # EQ / NE use a 1e-9 window in double (include/pto/cpu/TCmps.hpp:27-33): values 1e-10 apart count as equal
+    near = np.full((64, 256), 1.0, np.float32)
+    assert np.array_equal(port.tcmps_f32(near, float(np.nextafter(np.float32(1.0), np.float32(2.0))), 0),
+                          ref.tcmps_f32(near, float(np.nextafter(np.float32(1.0), np.float32(2.0))), 0))
