@@ -55,6 +55,16 @@ extern "C" {
 #define PTO_B200_OP_DIV 3
 #define PTO_B200_OP_MAX 4
 #define PTO_B200_OP_MIN 5
+#define PTO_B200_OP_EXPDIF 6 /* exp(a - b); pto_b200_trowexpand_f32 only */
+#define PTO_B200_OP_EXPAND 7 /* the row scalar itself (plain TROWEXPAND); pto_b200_trowexpand_f32 only */
+
+/* CmpMode values of the reference (include/pto/common/type.hpp:131-139). */
+#define PTO_B200_CMP_EQ 0
+#define PTO_B200_CMP_NE 1
+#define PTO_B200_CMP_LT 2
+#define PTO_B200_CMP_LE 3
+#define PTO_B200_CMP_GT 4
+#define PTO_B200_CMP_GE 5
 
 /* ---- library state ------------------------------------------------------------------------------ */
 
@@ -98,10 +108,40 @@ int pto_b200_texp_f32(const float *src, float *dst, int64_t n, void *stream);
 int pto_b200_tbinary_f32(const float *a, const float *b, float *dst, int64_t n, int op, void *stream);
 /* TADDS / TMULS / ...: dst = a op scalar (include/pto/common/pto_instr.hpp:1161, :1188). */
 int pto_b200_tscalar_f32(const float *a, float scalar, float *dst, int64_t n, int op, void *stream);
-/* TROWEXPANDSUB / MUL / DIV / ADD / MAX / MIN: dst[r, c] = a[r, c] op row_scalar[r]
- * (include/pto/common/pto_instr.hpp:1057-1073, include/pto/cpu/TRowExpandOp.hpp:38-76). */
+/* TROWEXPANDSUB / MUL / DIV / ADD / MAX / MIN / EXPDIF: dst[r, c] = a[r, c] op row_scalar[r], and with
+ * PTO_B200_OP_EXPAND the plain TROWEXPAND dst[r, c] = row_scalar[r] (`a` is not read and may be NULL)
+ * (include/pto/common/pto_instr.hpp:1049-1108; include/pto/cpu/TRowExpandOp.hpp:38-98, TRowExpand.hpp:22-37).
+ * max / min are std::max / std::min; EXPDIF is exp evaluated in double and rounded to float. */
 int pto_b200_trowexpand_f32(const float *a, const float *row_scalar, float *dst, int rows, int cols, int op,
                             void *stream);
+/* TROWMIN: dst[r] = min over the `cols` valid columns of row r (include/pto/common/pto_instr.hpp:1007-1012,
+ * include/pto/cpu/TRowMin.hpp:21-41). */
+int pto_b200_trowmin_f32(const float *src, float *dst, int rows, int cols, int64_t row_stride, void *stream);
+/* TCOLSUM / TCOLMAX / TCOLMIN: dst[c] = sum / max / min over the `rows` valid rows of column c; `op` is
+ * PTO_B200_OP_ADD, _MAX or _MIN (include/pto/common/pto_instr.hpp:959-988, :1305-1310; include/pto/cpu/TColSum.hpp:19-30,
+ * TColMax.hpp:19-33, TColMin.hpp).  The sum is a fixed-order tree in fp32 (the reference sums top to bottom). */
+int pto_b200_tcolreduce_f32(const float *src, float *dst, int rows, int cols, int64_t row_stride, int op, void *stream);
+/* TFILLPAD: dst is rows x cols; its valid_rows x valid_cols corner is copied from src (same shape and pitch, read
+ * only inside that corner), every other element becomes `pad_bits` (the low 16 bits for 2-byte elements): the
+ * caller passes the pattern PadValue::Zero / Max / Min mean for its element type, e.g. 0x7f800000 / 0xff800000 for
+ * float Max / Min (include/pto/common/pto_instr.hpp:754-782, include/pto/cpu/TFillPad.hpp:19-49). */
+int pto_b200_tfillpad(const void *src, void *dst, int rows, int cols, int valid_rows, int valid_cols, uint32_t pad_bits,
+                      int elem_bytes, void *stream);
+/* TTRANS: dst[c, r] = src[r, c]; src is rows x cols, dst cols x rows, both dense; elem_bytes 4 or 2
+ * (include/pto/common/pto_instr.hpp:1032-1037, include/pto/cpu/TTrans.hpp:17-45). */
+int pto_b200_ttrans(const void *src, void *dst, int rows, int cols, int elem_bytes, void *stream);
+/* TSEL: dst[i] = bit i of `mask` ? src0[i] : src1[i] over n elements of a dense row-major tile; the mask is read
+ * one bit per element, least significant bit of byte 0 first, (n + 7) / 8 bytes; elem_bytes 4 or 2
+ * (include/pto/common/pto_instr.hpp:1024-1029, include/pto/cpu/TSel.hpp:22-46). */
+int pto_b200_tsel(const uint8_t *mask, const void *src0, const void *src1, void *dst, int64_t n, int elem_bytes,
+                  void *stream);
+/* TCMPS: one result bit per element of src compared with `scalar`, packed least significant bit first into n / 8
+ * bytes (n a multiple of 8).  EQ / NE compare |a - b| in double against 1e-9 like the reference
+ * (include/pto/common/pto_instr.hpp:143-148, include/pto/cpu/TCmps.hpp:23-91). */
+int pto_b200_tcmps_f32(const float *src, float scalar, uint8_t *dst_bits, int64_t n, int mode, void *stream);
+/* TCMP as the CPU simulation defines it: dst[i] = 1.0f or 0.0f from the plain comparison of a[i] and b[i]
+ * (include/pto/common/pto_instr.hpp:151-157, include/pto/cpu/ElementTileOp.h:177-184, ElementOp.h:227-254). */
+int pto_b200_tcmp_f32(const float *a, const float *b, float *dst, int64_t n, int mode, void *stream);
 
 /* ---- GEMM --------------------------------------------------------------------------------------- */
 

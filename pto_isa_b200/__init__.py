@@ -10,5 +10,6 @@ from ._lib import PtoB200Error, lib, lib_path  # noqa: F401
 from . import ops  # noqa: F401
 from .ops import (  # noqa: F401
     TCVT, TGATHER, TGATHER_MASK, TROWMAX, TROWSUM, TEXP, TROWEXPANDSUB, TROWEXPANDMUL, TROWEXPANDDIV,
-    TADD, TSUB, TMAX, TMULS, TADDS, gemm, gemm_host, flash_attn_fwd, flash_attn_fwd_host, device_status,
+    TROWEXPAND, TROWEXPANDADD, TROWEXPANDMAX, TROWEXPANDMIN, TROWEXPANDEXPDIF, TROWMIN, TCOLSUM, TCOLMAX, TCOLMIN,
+    TFILLPAD, TTRANS, TSEL, TCMPS, TCMP, TADD, TSUB, TMUL, TDIV, TMAX, TMIN, TMULS, TADDS, gemm, gemm_host, flash_attn_fwd, flash_attn_fwd_host, device_status,
 )

@@ -33,6 +33,13 @@ SIGNATURES = {
     "pto_b200_tbinary_f32": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "pto_b200_tscalar_f32": (_i, [_vp, _f, _vp, _i64, _i, _vp]),
     "pto_b200_trowexpand_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "pto_b200_trowmin_f32": (_i, [_vp, _vp, _i, _i, _i64, _vp]),
+    "pto_b200_tcolreduce_f32": (_i, [_vp, _vp, _i, _i, _i64, _i, _vp]),
+    "pto_b200_tfillpad": (_i, [_vp, _vp, _i, _i, _i, _i, _u32, _i, _vp]),
+    "pto_b200_ttrans": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "pto_b200_tsel": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _vp]),
+    "pto_b200_tcmps_f32": (_i, [_vp, _f, _vp, _i64, _i, _vp]),
+    "pto_b200_tcmp_f32": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "pto_b200_gemm_f16f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "pto_b200_gemm_f16f32_batched": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i64, _i64, _i64, _vp]),
     "pto_b200_gemm_f16f32_host": (_i, [_vp, _vp, _vp, _i, _i, _i, _i]),

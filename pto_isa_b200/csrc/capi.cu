@@ -185,11 +185,76 @@ int pto_b200_tscalar_f32(const float *a, float scalar, float *dst, int64_t n, in
 int pto_b200_trowexpand_f32(const float *a, const float *row_scalar, float *dst, int rows, int cols, int op,
                             void *stream)
 {
-    if (rows < 0 || cols < 0 || op < 0 || op > 5 ||
-        (rows > 0 && cols > 0 && (a == nullptr || row_scalar == nullptr || dst == nullptr))) {
+    if (rows < 0 || cols < 0 || op < 0 || op > 7 ||
+        (rows > 0 && cols > 0 && ((a == nullptr && op != 7) || row_scalar == nullptr || dst == nullptr))) {
         return bad("trowexpand: bad argument");
     }
     return launch_trowexpand(a, row_scalar, dst, rows, cols, op, as_stream(stream));
+}
+
+int pto_b200_trowmin_f32(const float *src, float *dst, int rows, int cols, int64_t row_stride, void *stream)
+{
+    if (rows < 0 || cols <= 0 || row_stride < cols || (rows > 0 && (src == nullptr || dst == nullptr))) {
+        return bad("trowmin: bad argument");
+    }
+    return launch_trowmin(src, dst, rows, cols, row_stride, as_stream(stream));
+}
+
+int pto_b200_tcolreduce_f32(const float *src, float *dst, int rows, int cols, int64_t row_stride, int op, void *stream)
+{
+    if (rows <= 0 || cols < 0 || row_stride < cols || (op != 0 && op != 4 && op != 5) ||
+        (cols > 0 && (src == nullptr || dst == nullptr))) {
+        return bad("tcolreduce: bad argument (op must be PTO_B200_OP_ADD, _MAX or _MIN; at least one row)");
+    }
+    return launch_tcolreduce(src, dst, rows, cols, row_stride, op, as_stream(stream));
+}
+
+int pto_b200_tfillpad(const void *src, void *dst, int rows, int cols, int valid_rows, int valid_cols, uint32_t pad_bits,
+                      int elem_bytes, void *stream)
+{
+    if (rows < 0 || cols < 0 || valid_rows < 0 || valid_cols < 0 || valid_rows > rows || valid_cols > cols ||
+        (elem_bytes != 4 && elem_bytes != 2) || (rows > 0 && cols > 0 && dst == nullptr) ||
+        (valid_rows > 0 && valid_cols > 0 && src == nullptr)) {
+        return bad("tfillpad: bad argument");
+    }
+    return launch_tfillpad(src, dst, rows, cols, valid_rows, valid_cols, pad_bits, elem_bytes, as_stream(stream));
+}
+
+int pto_b200_ttrans(const void *src, void *dst, int rows, int cols, int elem_bytes, void *stream)
+{
+    if (rows < 0 || cols < 0 || (elem_bytes != 4 && elem_bytes != 2) ||
+        (rows > 0 && cols > 0 && (src == nullptr || dst == nullptr)) || src == dst) {
+        if (!(rows == 0 || cols == 0)) {
+            return bad("ttrans: bad argument (in-place transposition is not supported)");
+        }
+    }
+    return launch_ttrans(src, dst, rows, cols, elem_bytes, as_stream(stream));
+}
+
+int pto_b200_tsel(const uint8_t *mask, const void *src0, const void *src1, void *dst, int64_t n, int elem_bytes,
+                  void *stream)
+{
+    if (n < 0 || (elem_bytes != 4 && elem_bytes != 2) ||
+        (n > 0 && (mask == nullptr || src0 == nullptr || src1 == nullptr || dst == nullptr))) {
+        return bad("tsel: bad argument");
+    }
+    return launch_tsel(mask, src0, src1, dst, n, elem_bytes, as_stream(stream));
+}
+
+int pto_b200_tcmps_f32(const float *src, float scalar, uint8_t *dst_bits, int64_t n, int mode, void *stream)
+{
+    if (n < 0 || (n & 7) != 0 || mode < 0 || mode > 5 || (n > 0 && (src == nullptr || dst_bits == nullptr))) {
+        return bad("tcmps: bad argument (n must be a multiple of 8)");
+    }
+    return launch_tcmps(src, scalar, dst_bits, n, mode, as_stream(stream));
+}
+
+int pto_b200_tcmp_f32(const float *a, const float *b, float *dst, int64_t n, int mode, void *stream)
+{
+    if (n < 0 || mode < 0 || mode > 5 || (n > 0 && (a == nullptr || b == nullptr || dst == nullptr))) {
+        return bad("tcmp: bad argument");
+    }
+    return launch_tcmp(a, b, dst, n, mode, as_stream(stream));
 }
 
 // ------------------------------------------------------------------ GEMM

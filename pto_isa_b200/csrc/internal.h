@@ -52,6 +52,17 @@ int launch_tbinary(const float *a, const float *b, float *dst, int64_t n, int op
 int launch_tscalar(const float *a, float s, float *dst, int64_t n, int op, cudaStream_t stream);
 int launch_trowexpand(const float *a, const float *row_scalar, float *dst, int rows, int cols, int op,
                       cudaStream_t stream);
+int launch_trowmin(const float *src, float *dst, int rows, int cols, int64_t row_stride, cudaStream_t stream);
+int launch_tcolreduce(const float *src, float *dst, int rows, int cols, int64_t row_stride, int op, cudaStream_t stream);
+int launch_tfillpad(const void *src, void *dst, int rows, int cols, int valid_rows, int valid_cols, uint32_t pad,
+                    int elem_bytes, cudaStream_t stream);
+int launch_ttrans(const void *src, void *dst, int rows, int cols, int elem_bytes, cudaStream_t stream);
+int launch_tsel(const uint8_t *mask, const void *src0, const void *src1, void *dst, int64_t n, int elem_bytes,
+                cudaStream_t stream);
+int launch_tcmps(const float *src, float scalar, uint8_t *dst, int64_t n, int mode, cudaStream_t stream);
+int launch_tcmp(const float *a, const float *b, float *dst, int64_t n, int mode, cudaStream_t stream);
+// blocks for a grid-stride kernel over `work_items` items, `items_per_block` per block per pass (capped at 32 per SM)
+int grid_for(int64_t work_items, int items_per_block);
 
 // GEMM: C[m x n] fp32 = A[m x k] fp16 * B, B given k x n row-major (b_layout 0) or n x k row-major (1)
 int launch_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,

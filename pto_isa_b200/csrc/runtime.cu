@@ -202,4 +202,17 @@ int make_tmap_3d(CUtensorMap *map, const void *base, int elem_bytes, uint64_t ou
     return kOk;
 }
 
+int grid_for(int64_t work_items, int items_per_block)
+{
+    int64_t blocks = (work_items + items_per_block - 1) / items_per_block;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 32; // grid-stride beyond this
+    if (blocks > cap) {
+        blocks = cap;
+    }
+    if (blocks < 1) {
+        blocks = 1;
+    }
+    return static_cast<int>(blocks);
+}
+
 } // namespace pto_b200

@@ -1,6 +1,6 @@
 // Vector tile ops of the PTO surface as HBM-streaming kernels for sm_100a:
 // TCVT (fp32 -> fp16 / bf16 / int32), TGATHER (index and mask forms), TROWMAX, TROWSUM, TEXP,
-// TROWEXPAND{SUB,MUL,DIV}, and the elementwise binary / scalar ops of the attention softmax.
+// and the elementwise binary / scalar ops of the attention softmax (the row-expand family lives in vector_ops2.cu).
 //
 // All of them are memory-bound: 128-bit streaming loads that bypass L1, 128-bit streaming stores,
 // one warp per row with shuffle reductions for the row ops, grids sized from the element count.
@@ -241,8 +241,8 @@ __device__ __forceinline__ float apply_bin(int op, float a, float b)
         case kOpSub: return a - b;
         case kOpMul: return a * b;
         case kOpDiv: return a / b;
-        case kOpMax: return fmaxf(a, b);
-        default: return fminf(a, b);
+        case kOpMax: return (a < b) ? b : a; // std::max, as the reference's ElementOp
+        default: return (b < a) ? b : a;     // std::min
     }
 }
 
@@ -289,32 +289,6 @@ __global__ void __launch_bounds__(kThreads) tscalar_kernel(const float *__restri
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         dst[i] = apply_bin(op, a[i], s);
     }
-}
-
-// dst[r, c] = a[r, c] op row_scalar[r]
-__global__ void __launch_bounds__(kThreads) trowexpand_kernel(const float *__restrict__ a,
-                                                              const float *__restrict__ row_scalar,
-                                                              float *__restrict__ dst, int rows, int cols, int op)
-{
-    const int64_t n = static_cast<int64_t>(rows) * cols;
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const int64_t r = i / cols;
-        dst[i] = apply_bin(op, a[i], row_scalar[r]);
-    }
-}
-
-int grid_for(int64_t work_items, int items_per_block)
-{
-    int64_t blocks = (work_items + items_per_block - 1) / items_per_block;
-    const int64_t cap = static_cast<int64_t>(sm_count()) * 32; // grid-stride beyond this
-    if (blocks > cap) {
-        blocks = cap;
-    }
-    if (blocks < 1) {
-        blocks = 1;
-    }
-    return static_cast<int>(blocks);
 }
 
 bool aligned16(const void *p)
@@ -452,17 +426,6 @@ int launch_tscalar(const float *a, float s, float *dst, int64_t n, int op, cudaS
         return kOk;
     }
     tscalar_kernel<<<grid_for(n, kThreads), kThreads, 0, stream>>>(a, s, dst, n, op);
-    return check_launch();
-}
-
-int launch_trowexpand(const float *a, const float *row_scalar, float *dst, int rows, int cols, int op,
-                      cudaStream_t stream)
-{
-    if (rows == 0 || cols == 0) {
-        return kOk;
-    }
-    trowexpand_kernel<<<grid_for(static_cast<int64_t>(rows) * cols, kThreads), kThreads, 0, stream>>>(
-        a, row_scalar, dst, rows, cols, op);
     return check_launch();
 }
 

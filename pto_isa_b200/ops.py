@@ -2,7 +2,9 @@
 
 Names and argument meaning follow the reference's instruction surface (include/pto/common/pto_instr.hpp,
 paths relative to the reference root): TCVT :864, TGATHER :800/:824, TROWMAX :990, TROWSUM :942, TEXP :1129,
-TROWEXPANDSUB/MUL/DIV :1057-1073, TADD/TSUB/TMAX :56-120, TMULS :1188, TADDS :1161; `gemm` stands for
+TROWEXPAND :1049 and TROWEXPANDSUB/MUL/DIV/ADD/MAX/MIN/EXPDIF :1057-1108, TROWMIN :1007, TCOLSUM/TCOLMAX/TCOLMIN
+:959-988/:1305, TFILLPAD :754, TTRANS :1032, TSEL :1024, TCMPS :143, TCMP :151, TADD/TSUB/TMUL/TDIV/TMAX/TMIN :56-120
+and :238, TMULS :1188, TADDS :1161; `gemm` stands for
 LaunchGEMME2E (kernels/manual/a2a3/gemm_performance/gemm_performance_kernel.cpp:243) and `flash_attn_fwd` for
 LaunchTFA (kernels/manual/common/flash_atten/fa_performance_kernel.cpp:970).  A whole tensor plays the role of
 the tile: destination first is replaced by a returned (or `out=`) tensor.  Everything runs on the current
@@ -16,7 +18,9 @@ from ._lib import PtoB200Error, check, lib
 
 CAST_RINT, CAST_ROUND, CAST_FLOOR, CAST_CEIL, CAST_TRUNC, CAST_ODD = 1, 2, 3, 4, 5, 6
 P0101, P1010, P0001, P0010, P0100, P1000, P1111 = 1, 2, 3, 4, 5, 6, 7
-OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_MAX, OP_MIN = 0, 1, 2, 3, 4, 5
+OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_MAX, OP_MIN, OP_EXPDIF, OP_EXPAND = 0, 1, 2, 3, 4, 5, 6, 7
+CMP_EQ, CMP_NE, CMP_LT, CMP_LE, CMP_GT, CMP_GE = 0, 1, 2, 3, 4, 5
+PAD_ZERO, PAD_MAX, PAD_MIN = 1, 2, 3  # PadValue::Zero / Max / Min (include/pto/common/type.hpp:204-210)
 
 
 def _stream(t):
@@ -138,6 +142,18 @@ def TMAX(a, b, out=None):
     return _binary(a, b, OP_MAX, out)
 
 
+def TMUL(a, b, out=None):
+    return _binary(a, b, OP_MUL, out)
+
+
+def TDIV(a, b, out=None):
+    return _binary(a, b, OP_DIV, out)
+
+
+def TMIN(a, b, out=None):
+    return _binary(a, b, OP_MIN, out)
+
+
 def _scalar(a, s, op, out):
     _need_cuda(a)
     out = torch.empty_like(a) if out is None else out
@@ -177,6 +193,138 @@ def TROWEXPANDMUL(a, row_scalar, out=None):
 
 def TROWEXPANDDIV(a, row_scalar, out=None):
     return _rowexpand(a, row_scalar, OP_DIV, out)
+
+
+def TROWEXPANDADD(a, row_scalar, out=None):
+    return _rowexpand(a, row_scalar, OP_ADD, out)
+
+
+def TROWEXPANDMAX(a, row_scalar, out=None):
+    return _rowexpand(a, row_scalar, OP_MAX, out)
+
+
+def TROWEXPANDMIN(a, row_scalar, out=None):
+    return _rowexpand(a, row_scalar, OP_MIN, out)
+
+
+def TROWEXPANDEXPDIF(a, row_scalar, out=None):
+    return _rowexpand(a, row_scalar, OP_EXPDIF, out)
+
+
+def TROWEXPAND(row_scalar, cols, out=None):
+    """dst[r, c] = row_scalar[r] for `cols` columns."""
+    _need_cuda(row_scalar)
+    if row_scalar.dtype != torch.float32:
+        raise PtoB200Error("TROWEXPAND: expects float32")
+    rows = row_scalar.numel()
+    out = torch.empty(rows, cols, dtype=torch.float32, device=row_scalar.device) if out is None else out
+    with torch.cuda.device(row_scalar.device):
+        rc = lib().pto_b200_trowexpand_f32(None, _ptr(row_scalar), _ptr(out), rows, cols, OP_EXPAND, _stream(row_scalar))
+    check(rc, "TROWEXPAND")
+    return out
+
+
+def TROWMIN(src, out=None):
+    return _row_reduce("pto_b200_trowmin_f32", src, out)
+
+
+def _col_reduce(src, op, out, what):
+    _need_cuda(src)
+    if src.dim() != 2 or src.dtype != torch.float32:
+        raise PtoB200Error(f"{what}: expects a 2-D float32 tensor")
+    rows, cols = src.shape
+    out = torch.empty(cols, dtype=torch.float32, device=src.device) if out is None else out
+    with torch.cuda.device(src.device):
+        rc = lib().pto_b200_tcolreduce_f32(_ptr(src), _ptr(out), rows, cols, cols, op, _stream(src))
+    check(rc, what)
+    return out
+
+
+def TCOLSUM(src, out=None):
+    return _col_reduce(src, OP_ADD, out, "TCOLSUM")
+
+
+def TCOLMAX(src, out=None):
+    return _col_reduce(src, OP_MAX, out, "TCOLMAX")
+
+
+def TCOLMIN(src, out=None):
+    return _col_reduce(src, OP_MIN, out, "TCOLMIN")
+
+
+def _pad_bits(dtype, pad):
+    """The bit pattern PadValue::Zero / Max / Min mean for `dtype` (include/pto/cpu/TFillPad.hpp:24-36): infinities
+    for floating types, the type's max / min for integers."""
+    if pad == PAD_ZERO:
+        return 0
+    if dtype.is_floating_point:
+        inf = torch.tensor([float("inf") if pad == PAD_MAX else float("-inf")], dtype=dtype)
+        return int(inf.view(torch.int32 if dtype.itemsize == 4 else torch.int16).item()) & (0xffffffff if dtype.itemsize == 4 else 0xffff)
+    info = torch.iinfo(dtype)
+    return int(info.max if pad == PAD_MAX else info.min) & (0xffffffff if dtype.itemsize == 4 else 0xffff)
+
+
+def TFILLPAD(src, valid_rows, valid_cols, pad=PAD_ZERO, out=None):
+    """Copies the valid_rows x valid_cols corner of the 2-D tile `src` and fills the rest with the pad value."""
+    _need_cuda(src)
+    if src.dim() != 2 or src.dtype.itemsize not in (2, 4):
+        raise PtoB200Error("TFILLPAD: expects a 2-D tensor of 2- or 4-byte elements")
+    out = torch.empty_like(src) if out is None else out
+    with torch.cuda.device(src.device):
+        rc = lib().pto_b200_tfillpad(_ptr(src), _ptr(out), src.shape[0], src.shape[1], int(valid_rows), int(valid_cols),
+                                     _pad_bits(src.dtype, pad), src.dtype.itemsize, _stream(src))
+    check(rc, "TFILLPAD")
+    return out
+
+
+def TTRANS(src, out=None):
+    _need_cuda(src)
+    if src.dim() != 2 or src.dtype.itemsize not in (2, 4):
+        raise PtoB200Error("TTRANS: expects a 2-D tensor of 2- or 4-byte elements")
+    out = torch.empty(src.shape[1], src.shape[0], dtype=src.dtype, device=src.device) if out is None else out
+    with torch.cuda.device(src.device):
+        rc = lib().pto_b200_ttrans(_ptr(src), _ptr(out), src.shape[0], src.shape[1], src.dtype.itemsize, _stream(src))
+    check(rc, "TTRANS")
+    return out
+
+
+def TSEL(mask, src0, src1, out=None):
+    """mask: uint8 tensor, one bit per element of the operands in row-major order, least significant bit first."""
+    _need_cuda(mask, src0, src1)
+    if src0.shape != src1.shape or src0.dtype != src1.dtype or src0.dtype.itemsize not in (2, 4):
+        raise PtoB200Error("TSEL: operands must have the same shape and a 2- or 4-byte element type")
+    if mask.dtype != torch.uint8 or mask.numel() * 8 < src0.numel():
+        raise PtoB200Error("TSEL: the mask must be uint8 with one bit per element")
+    out = torch.empty_like(src0) if out is None else out
+    with torch.cuda.device(src0.device):
+        rc = lib().pto_b200_tsel(_ptr(mask), _ptr(src0), _ptr(src1), _ptr(out), src0.numel(), src0.dtype.itemsize,
+                                 _stream(src0))
+    check(rc, "TSEL")
+    return out
+
+
+def TCMPS(src, scalar, mode, out=None):
+    """Packed comparison bits of `src` against a scalar: numel / 8 bytes, least significant bit first."""
+    _need_cuda(src)
+    if src.dtype != torch.float32 or src.numel() % 8 != 0:
+        raise PtoB200Error("TCMPS: expects float32 with a multiple of 8 elements")
+    out = torch.empty(src.numel() // 8, dtype=torch.uint8, device=src.device) if out is None else out
+    with torch.cuda.device(src.device):
+        rc = lib().pto_b200_tcmps_f32(_ptr(src), float(scalar), _ptr(out), src.numel(), int(mode), _stream(src))
+    check(rc, "TCMPS")
+    return out
+
+
+def TCMP(a, b, mode, out=None):
+    """1.0 / 0.0 per element, the form the reference's CPU simulation gives TCMP."""
+    _need_cuda(a, b)
+    if a.shape != b.shape or a.dtype != torch.float32 or b.dtype != torch.float32:
+        raise PtoB200Error("TCMP: operands must be float32 of the same shape")
+    out = torch.empty_like(a) if out is None else out
+    with torch.cuda.device(a.device):
+        rc = lib().pto_b200_tcmp_f32(_ptr(a), _ptr(b), _ptr(out), a.numel(), int(mode), _stream(a))
+    check(rc, "TCMP")
+    return out
 
 
 def gemm(a, b, b_layout=1, out=None):

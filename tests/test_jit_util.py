@@ -51,8 +51,8 @@ def test_loaders_reject_cpu_tensors():
 def test_operator_on_the_reference_shape():
     import pto_isa_b200 as pto
     g = torch.Generator(device="cuda").manual_seed(3)
-    a = (torch.rand(512, 2048, device=dev(), generator=g) * 2 - 1).half()
-    b_dn = (torch.rand(1536, 2048, device=dev(), generator=g) * 2 - 1).half()
+    a = (torch.rand(512, 2048, device="cuda", generator=g) * 2 - 1).half()
+    b_dn = (torch.rand(1536, 2048, device="cuda", generator=g) * 2 - 1).half()
     out = jit_util.pto_gemm_basic(a, b_dn)
     assert out.shape == (512, 1536) and out.dtype == torch.float32
     assert torch.equal(out, pto.gemm(a, b_dn, 1))
@@ -65,9 +65,9 @@ def test_gemm_loader_equals_the_abi_entry_point():
     import pto_isa_b200 as pto
     g = torch.Generator(device="cuda").manual_seed(4)
     n = jit_util.GEMM_JIT_M
-    a = (torch.rand(n, n, device=dev(), generator=g) * 2 - 1).half()
-    b = (torch.rand(n, n, device=dev(), generator=g) * 2 - 1).half()
-    c = torch.zeros(n, n, device=dev())
+    a = (torch.rand(n, n, device="cuda", generator=g) * 2 - 1).half()
+    b = (torch.rand(n, n, device="cuda", generator=g) * 2 - 1).half()
+    c = torch.zeros(n, n, device="cuda")
     gemm = jit_util.load_lib()
     gemm(c, a, b)
     torch.cuda.synchronize()
@@ -81,10 +81,10 @@ def test_flash_loader_equals_the_abi_entry_point(causal):
     import pto_isa_b200 as pto
     g = torch.Generator(device="cuda").manual_seed(5)
     s0, s1, d = 512, 512, 128
-    q = torch.randn(s0, d, device=dev(), generator=g).half()
-    k = torch.randn(s1, d, device=dev(), generator=g).half()
-    v = torch.randn(s1, d, device=dev(), generator=g).half()
-    o = torch.zeros(s0, d, device=dev())
+    q = torch.randn(s0, d, device="cuda", generator=g).half()
+    k = torch.randn(s1, d, device="cuda", generator=g).half()
+    v = torch.randn(s1, d, device="cuda", generator=g).half()
+    o = torch.zeros(s0, d, device="cuda")
     flash = jit_util.load_flash_lib()
     flash(q, k, v, o, is_causal=causal)
     torch.cuda.synchronize()
