@@ -342,11 +342,26 @@ def extras(torch, pto, peaks, peak_kind):
             f(j)
         return g_
 
+    side = 4096  # the same 16 M elements as a 4096 x 4096 tile for the 2-D ops
+    x2 = [x.view(side, side) for x in xs]
+    o2 = [o.view(side, side) for o in og]
+    rowv = [torch.randn(side, device="cuda", generator=g) for _ in range(sets)]
+    colv = [torch.empty(side, device="cuda") for _ in range(sets)]
+    maskb = [torch.randint(0, 256, (n // 8,), device="cuda", dtype=torch.uint8, generator=g) for _ in range(sets)]
+    bitsb = [torch.empty(n // 8, device="cuda", dtype=torch.uint8) for _ in range(sets)]
     cases = [
         ("TCVT f32->f16 16M elements", 6.0, rot(lambda j: pto.TCVT(xs[j], torch.float16, out=o16[j]))),
         ("TCVT f32->bf16 16M elements", 6.0, rot(lambda j: pto.TCVT(xs[j], torch.bfloat16, out=ob16[j]))),
         ("TGATHER f32 by int32 index, 16M of 16M, 10% duplicates", 12.0,
          rot(lambda j: pto.TGATHER(xs[j], idx[j], out=og[j]))),
+        ("TROWEXPANDSUB f32 4096x4096", 8.0, rot(lambda j: pto.TROWEXPANDSUB(x2[j], rowv[j], out=o2[j]))),
+        ("TROWMAX f32 4096x4096", 4.0, rot(lambda j: pto.TROWMAX(x2[j], out=colv[j]))),
+        ("TCOLSUM f32 4096x4096", 4.0, rot(lambda j: pto.TCOLSUM(x2[j], out=colv[j]))),
+        ("TTRANS f32 4096x4096", 8.0, rot(lambda j: pto.TTRANS(x2[j], out=o2[j]))),
+        ("TSEL f32 16M elements, bit mask", 12.125, rot(lambda j: pto.TSEL(maskb[j], xs[j], xs[(j + 1) % sets], out=og[j]))),
+        ("TCMPS f32 16M elements -> bits", 4.125, rot(lambda j: pto.TCMPS(xs[j], 0.0, 4, out=bitsb[j]))),
+        ("TFILLPAD f32 4096x4096, valid 3000x3000", 4.0 * (3000 * 3000 / n) + 4.0,
+         rot(lambda j: pto.TFILLPAD(x2[j], 3000, 3000, 3, out=o2[j]))),
     ]
     for name, bytes_per_elem, fn in cases:
         ms = bench(fn, 2 * sets, 5 * sets)

@@ -20,6 +20,8 @@
 
 #include <math.h>
 
+#include <limits>
+
 #include "runtime.hpp"
 
 namespace pto {
@@ -549,14 +551,30 @@ PTO_B200_SCALAR(TADDS, a + s)
 PTO_B200_SCALAR(TMULS, a *s)
 #undef PTO_B200_SCALAR
 
-// dst[r, c] = src0[r, c] op src1[r, 0]  (include/pto/cpu/TRowExpandOp.hpp:38-76)
+// dst[r, c] = src0[r, c] op s(r), s(r) read from src1 as the reference's load_row_scalar does: a 1 x R row tile, an
+// R x 1 column tile, or element r of the storage otherwise (include/pto/cpu/TRowExpandOp.hpp:21-57)
+namespace b200 {
+template <typename TileVec>
+PTO_INTERNAL typename TileVec::DType row_scalar(TileVec &src1, int r)
+{
+    const int vr = src1.GetValidRow(), vc = src1.GetValidCol();
+    if (vr == 1 && r < vc) {
+        return src1.data()[vec_offset<TileVec>(0, r)];
+    }
+    if (vc == 1 && r < vr) {
+        return src1.data()[vec_offset<TileVec>(r, 0)];
+    }
+    return src1.data()[r % TileVec::Numel];
+}
+} // namespace b200
+
 #define PTO_B200_ROWEXPAND(NAME, EXPR)                                                                           \
     template <typename TileDst, typename TileSrc1, typename... WaitEvents>                                       \
     PTO_INST RecordEvent NAME(TileDst &dst, TileDst &src0, TileSrc1 &src1, WaitEvents &... events)               \
     {                                                                                                            \
         b200::for_each_valid(dst, dst, [&](typename TileDst::DType &d, int r, int c) {                           \
             const auto a = src0.data()[b200::vec_offset<TileDst>(r, c)];                                         \
-            const auto s = static_cast<typename TileDst::DType>(src1.data()[b200::vec_offset<TileSrc1>(r, 0)]);  \
+            const auto s = static_cast<typename TileDst::DType>(b200::row_scalar(src1, r));                      \
             d = (EXPR);                                                                                          \
         });                                                                                                      \
         return {};                                                                                               \
@@ -565,11 +583,24 @@ PTO_B200_ROWEXPAND(TROWEXPANDSUB, a - s)
 PTO_B200_ROWEXPAND(TROWEXPANDMUL, a *s)
 PTO_B200_ROWEXPAND(TROWEXPANDDIV, a / s)
 PTO_B200_ROWEXPAND(TROWEXPANDADD, a + s)
+PTO_B200_ROWEXPAND(TROWEXPANDMAX, (a < s) ? s : a)
+PTO_B200_ROWEXPAND(TROWEXPANDMIN, (s < a) ? s : a)
+PTO_B200_ROWEXPAND(TROWEXPANDEXPDIF, static_cast<typename TileDst::DType>(exp(static_cast<double>(a - s))))
 #undef PTO_B200_ROWEXPAND
+
+// dst[r, c] = src[r, 0]  (include/pto/cpu/TRowExpand.hpp:22-37)
+template <typename TileDataDst, typename TileDataSrc, typename... WaitEvents>
+PTO_INST RecordEvent TROWEXPAND(TileDataDst &dst, TileDataSrc &src, WaitEvents &... events)
+{
+    b200::for_each_valid(dst, dst, [&](typename TileDataDst::DType &d, int r, int) {
+        d = static_cast<typename TileDataDst::DType>(src.data()[b200::vec_offset<TileDataSrc>(r, 0)]);
+    });
+    return {};
+}
 
 // ---------------------------------------------------------------- row reductions (one warp per row)
 namespace b200 {
-template <bool kIsMax, typename TileOut, typename TileIn>
+template <int kMode, typename TileOut, typename TileIn> // 0 sum, 1 max, 2 min
 PTO_INTERNAL void row_reduce(TileOut &dst, TileIn &src)
 {
 #if PTO_B200_DEVICE_CODE
@@ -577,16 +608,16 @@ PTO_INTERNAL void row_reduce(TileOut &dst, TileIn &src)
     const int vr = src.GetValidRow(), vc = src.GetValidCol();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     for (int r = warp; r < vr; r += warps) {
-        AccT acc = kIsMax ? -INFINITY : 0.0f;
+        AccT acc = kMode == 1 ? -INFINITY : (kMode == 2 ? INFINITY : 0.0f);
         for (int c = lane; c < vc; c += 32) {
             const AccT v = convert<float, typename TileIn::DType>(src.data()[vec_offset<TileIn>(r, c)],
                                                                   RoundMode::CAST_RINT);
-            acc = kIsMax ? fmaxf(acc, v) : acc + v;
+            acc = kMode == 1 ? fmaxf(acc, v) : (kMode == 2 ? fminf(acc, v) : acc + v);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const AccT other = __shfl_xor_sync(0xffffffffu, acc, o);
-            acc = kIsMax ? fmaxf(acc, other) : acc + other;
+            acc = kMode == 1 ? fmaxf(acc, other) : (kMode == 2 ? fminf(acc, other) : acc + other);
         }
         if (lane == 0) {
             dst.data()[vec_offset<TileOut>(r, 0)] = convert<typename TileOut::DType, float>(acc, RoundMode::CAST_RINT);
@@ -600,14 +631,254 @@ PTO_INTERNAL void row_reduce(TileOut &dst, TileIn &src)
 template <typename TileOut, typename TileIn, typename TileTmp, typename... WaitEvents>
 PTO_INST RecordEvent TROWMAX(TileOut &dst, TileIn &src, TileTmp &tmp, WaitEvents &... events)
 {
-    b200::row_reduce<true>(dst, src);
+    b200::row_reduce<1>(dst, src);
     return {};
 }
 
 template <typename TileOut, typename TileIn, typename TileTmp, typename... WaitEvents>
 PTO_INST RecordEvent TROWSUM(TileOut &dst, TileIn &src, TileTmp &tmp, WaitEvents &... events)
 {
-    b200::row_reduce<false>(dst, src);
+    b200::row_reduce<0>(dst, src);
+    return {};
+}
+
+template <typename TileOut, typename TileIn, typename TileTmp, typename... WaitEvents>
+PTO_INST RecordEvent TROWMIN(TileOut &dst, TileIn &src, TileTmp &tmp, WaitEvents &... events)
+{
+    b200::row_reduce<2>(dst, src);
+    return {};
+}
+
+// ---------------------------------------------------------------- column reductions (one thread per column)
+// Rows are visited top to bottom, so TCOLSUM adds in the reference's order (include/pto/cpu/TColSum.hpp:19-30,
+// TColMax.hpp:19-33, TColMin.hpp); the result goes to row 0 of dst.
+namespace b200 {
+template <int kMode, typename TileOut, typename TileIn> // 0 sum, 1 max, 2 min
+PTO_INTERNAL void col_reduce(TileOut &dst, TileIn &src)
+{
+#if PTO_B200_DEVICE_CODE
+    using T = typename TileOut::DType;
+    const int vr = src.GetValidRow(), vc = src.GetValidCol();
+    for (int c = threadIdx.x; c < vc; c += blockDim.x) {
+        T acc = kMode == 0 ? T(0) : static_cast<T>(src.data()[vec_offset<TileIn>(0, c)]);
+        for (int r = (kMode == 0 ? 0 : 1); r < vr; ++r) {
+            const T v = static_cast<T>(src.data()[vec_offset<TileIn>(r, c)]);
+            if (kMode == 0) {
+                acc += v;
+            } else if (kMode == 1) {
+                acc = (v > acc) ? v : acc;
+            } else {
+                acc = (v < acc) ? v : acc;
+            }
+        }
+        dst.data()[vec_offset<TileOut>(0, c)] = acc;
+    }
+    __syncthreads();
+#endif
+}
+} // namespace b200
+
+template <typename TileOut, typename TileIn, typename... WaitEvents>
+PTO_INST RecordEvent TCOLSUM(TileOut &dst, TileIn &src, WaitEvents &... events)
+{
+    b200::col_reduce<0>(dst, src);
+    return {};
+}
+template <typename TileOut, typename TileIn, typename TileTmp, typename... WaitEvents>
+PTO_INST RecordEvent TCOLSUM(TileOut &dst, TileIn &src, TileTmp &tmp, bool isBinary, WaitEvents &... events)
+{
+    b200::col_reduce<0>(dst, src);
+    return {};
+}
+template <typename TileOut, typename TileIn, typename... WaitEvents>
+PTO_INST RecordEvent TCOLMAX(TileOut &dst, TileIn &src, WaitEvents &... events)
+{
+    b200::col_reduce<1>(dst, src);
+    return {};
+}
+template <typename TileOut, typename TileIn, typename... WaitEvents>
+PTO_INST RecordEvent TCOLMIN(TileOut &dst, TileIn &src, WaitEvents &... events)
+{
+    b200::col_reduce<2>(dst, src);
+    return {};
+}
+
+// ---------------------------------------------------------------- TFILLPAD (include/pto/cpu/TFillPad.hpp:19-104)
+// every element of dst: the source's valid corner is copied, the rest becomes the pad value of dst's type
+namespace b200 {
+template <typename T, PadValue P>
+PTO_INTERNAL T pad_value()
+{
+    if constexpr (std::is_floating_point_v<T> || std::is_same_v<T, half> || std::is_same_v<T, bfloat16_t>) {
+        if constexpr (P == PadValue::Max) {
+            return convert<T, float>(INFINITY, RoundMode::CAST_RINT);
+        } else if constexpr (P == PadValue::Min) {
+            return convert<T, float>(-INFINITY, RoundMode::CAST_RINT);
+        } else {
+            return convert<T, float>(0.0f, RoundMode::CAST_RINT);
+        }
+    } else {
+        if constexpr (P == PadValue::Max) {
+            return std::numeric_limits<T>::max();
+        } else if constexpr (P == PadValue::Min) {
+            return std::numeric_limits<T>::min();
+        } else {
+            return T(0);
+        }
+    }
+}
+template <typename TileDataDst, typename TileDataSrc>
+PTO_INTERNAL void fill_pad(TileDataDst &dst, TileDataSrc &src)
+{
+    static_assert(TileDataDst::PadVal != PadValue::Null, "TFILLPAD: the destination tile needs a pad value");
+    static_assert(sizeof(typename TileDataDst::DType) == sizeof(typename TileDataSrc::DType), "TFILLPAD: element sizes");
+#if PTO_B200_DEVICE_CODE
+    const int vr = src.GetValidRow(), vc = src.GetValidCol();
+    const auto pad = pad_value<typename TileDataDst::DType, TileDataDst::PadVal>();
+    if (dst.GetValidRow() != 0 && dst.GetValidCol() != 0) {
+        for (int i = threadIdx.x; i < TileDataDst::Rows * TileDataDst::Cols; i += blockDim.x) {
+            const int r = i / TileDataDst::Cols, c = i - r * TileDataDst::Cols;
+            dst.data()[vec_offset<TileDataDst>(r, c)] =
+                (r < vr && c < vc) ? static_cast<typename TileDataDst::DType>(src.data()[vec_offset<TileDataSrc>(r, c)]) : pad;
+        }
+    }
+    __syncthreads();
+#endif
+}
+} // namespace b200
+
+template <typename DstTileData, typename SrcTileData, typename... WaitEvents>
+PTO_INST RecordEvent TFILLPAD(DstTileData &dst, SrcTileData &src, WaitEvents &... events)
+{
+    static_assert(DstTileData::Cols == SrcTileData::Cols && DstTileData::Rows == SrcTileData::Rows,
+                  "TFILLPAD: dst and src have the same rows and columns");
+    b200::fill_pad(dst, src);
+    return {};
+}
+template <typename DstTileData, typename SrcTileData, typename... WaitEvents>
+PTO_INST RecordEvent TFILLPAD_INPLACE(DstTileData &dst, SrcTileData &src, WaitEvents &... events)
+{
+    static_assert(DstTileData::Cols == SrcTileData::Cols && DstTileData::Rows == SrcTileData::Rows,
+                  "TFILLPAD_INPLACE: dst and src have the same rows and columns");
+    b200::fill_pad(dst, src);
+    return {};
+}
+template <typename DstTileData, typename SrcTileData, typename... WaitEvents>
+PTO_INST RecordEvent TFILLPAD_EXPAND(DstTileData &dst, SrcTileData &src, WaitEvents &... events)
+{
+    static_assert(DstTileData::Cols >= SrcTileData::Cols && DstTileData::Rows >= SrcTileData::Rows,
+                  "TFILLPAD_EXPAND: dst is at least as large as src");
+    b200::fill_pad(dst, src);
+    return {};
+}
+
+// ---------------------------------------------------------------- TTRANS (include/pto/cpu/TTrans.hpp:17-58)
+template <typename TileDataDst, typename TileDataSrc, typename TileDataTmp, typename... WaitEvents>
+PTO_INST RecordEvent TTRANS(TileDataDst &dst, TileDataSrc &src, TileDataTmp &tmp, WaitEvents &... events)
+{
+    static_assert(TileDataSrc::ValidRow == TileDataDst::ValidCol && TileDataSrc::ValidCol == TileDataDst::ValidRow,
+                  "TTRANS: the valid extents of dst are those of src exchanged");
+#if PTO_B200_DEVICE_CODE
+    const int vr = src.GetValidRow(), vc = src.GetValidCol();
+    for (int i = threadIdx.x; i < vr * vc; i += blockDim.x) {
+        const int c = i / vr, r = i - c * vr; // consecutive threads write consecutive elements of a dst row
+        dst.data()[b200::vec_offset<TileDataDst>(c, r)] = src.data()[b200::vec_offset<TileDataSrc>(r, c)];
+    }
+    __syncthreads();
+#endif
+    return {};
+}
+
+// ---------------------------------------------------------------- TSEL (include/pto/cpu/TSel.hpp:22-57)
+// the mask tile's bytes are consumed bit by bit, least significant first, row-major over dst's valid region; the
+// mask bytes themselves are walked row by row over the mask tile's valid columns
+template <typename TileData, typename MaskTile, typename... WaitEvents>
+PTO_INST RecordEvent TSEL(TileData &dst, MaskTile &selMask, TileData &src0, TileData &src1, WaitEvents &... events)
+{
+    const int mask_cols = selMask.GetValidCol();
+    const int vc = dst.GetValidCol();
+    b200::for_each_valid(dst, dst, [&](typename TileData::DType &d, int r, int c) {
+        const int bit_index = r * vc + c;
+        const int byte_index = bit_index >> 3;
+        const auto byte = static_cast<uint8_t>(
+            selMask.data()[b200::vec_offset<MaskTile>(byte_index / mask_cols, byte_index % mask_cols)]);
+        const auto off = b200::vec_offset<TileData>(r, c);
+        d = ((byte >> (bit_index & 7)) & 1) ? src0.data()[off] : src1.data()[off];
+    });
+    return {};
+}
+
+// ---------------------------------------------------------------- TCMPS / TCMP
+namespace b200 {
+// include/pto/cpu/TCmps.hpp:23-52: EQ / NE look at |a - b| in double against 1e-9
+template <typename T>
+PTO_INTERNAL uint8_t cmps_call(T a, T b, CmpMode mode)
+{
+    const double diff = static_cast<double>(convert<float, T>(a, RoundMode::CAST_RINT)) -
+                        static_cast<double>(convert<float, T>(b, RoundMode::CAST_RINT));
+    const double mag = diff < 0 ? -diff : diff;
+    switch (mode) {
+        case CmpMode::NE: return mag > 1e-9;
+        case CmpMode::LT: return a < b;
+        case CmpMode::GT: return a > b;
+        case CmpMode::GE: return a >= b;
+        case CmpMode::LE: return a <= b;
+        default: return mag < 1e-9;
+    }
+}
+} // namespace b200
+
+// One bit per element of src0's whole tile (zero outside its valid region), eight to a byte, least significant first,
+// Cols / 8 bytes per tile row; byte number i * dstValidCol + j of that stream lands at element offset
+// i * SrcCols + j of dst's storage, exactly as the simulation writes it (include/pto/cpu/TCmps.hpp:54-91).
+template <typename TileDataDst, typename TileDataSrc, typename T, typename... WaitEvents>
+PTO_INST RecordEvent TCMPS(TileDataDst &dst, TileDataSrc &src0, T src1, CmpMode cmpMode, WaitEvents &... events)
+{
+#if PTO_B200_DEVICE_CODE
+    constexpr int H = TileDataSrc::Rows, W = TileDataSrc::Cols;
+    constexpr int bytes_per_row = W / 8;
+    const int svr = src0.GetValidRow(), svc = src0.GetValidCol();
+    const int dvr = dst.GetValidRow(), dvc = dst.GetValidCol();
+    const auto scalar = static_cast<typename TileDataSrc::DType>(src1);
+    for (int n = threadIdx.x; n < dvr * dvc; n += blockDim.x) {
+        if (n >= H * bytes_per_row) {
+            break;
+        }
+        const int h = n / bytes_per_row, k = n - h * bytes_per_row;
+        uint32_t byte = 0;
+        for (int bit = 0; bit < 8; ++bit) {
+            const int c = k * 8 + bit;
+            if (h < svr && c < svc) {
+                byte |= static_cast<uint32_t>(b200::cmps_call(src0.data()[h * TileDataSrc::RowStride + c], scalar, cmpMode))
+                        << bit;
+            }
+        }
+        const int i = n / dvc, j = n - i * dvc;
+        dst.data()[i * W + j] = static_cast<typename TileDataDst::DType>(byte);
+    }
+    __syncthreads();
+#endif
+    return {};
+}
+
+// the simulation's TCMP: 1 or 0 in the operands' type (include/pto/cpu/ElementTileOp.h:177-184, ElementOp.h:227-254)
+template <typename TileDataDst, typename TileDataSrc, typename... WaitEvents>
+PTO_INST RecordEvent TCMP(TileDataDst &dst, TileDataSrc &src0, TileDataSrc &src1, CmpMode cmpMode, WaitEvents &... events)
+{
+    b200::for_each_valid(dst, dst, [&](typename TileDataDst::DType &d, int r, int c) {
+        const auto a = src0.data()[b200::vec_offset<TileDataSrc>(r, c)];
+        const auto b = src1.data()[b200::vec_offset<TileDataSrc>(r, c)];
+        bool res;
+        switch (cmpMode) {
+            case CmpMode::NE: res = a != b; break;
+            case CmpMode::GT: res = a > b; break;
+            case CmpMode::LT: res = a < b; break;
+            case CmpMode::GE: res = a >= b; break;
+            case CmpMode::LE: res = a <= b; break;
+            default: res = a == b; break;
+        }
+        d = static_cast<typename TileDataDst::DType>(res ? 1 : 0);
+    });
     return {};
 }
 

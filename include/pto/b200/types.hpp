@@ -90,6 +90,8 @@ enum class RoundMode : uint8_t {
 };
 
 enum class PadValue { Null, Zero, Max, Min };
+// include/pto/common/type.hpp:131-139
+enum class CmpMode : uint8_t { EQ = 0, NE = 1, LT = 2, LE = 3, GT = 4, GE = 5 };
 enum class CompactMode { Null, Normal };
 enum class SaturationMode : uint8_t { ON = 0, OFF = 1 };
 enum class AtomicType : uint8_t { AtomicNone = 0, AtomicAdd = 1 };

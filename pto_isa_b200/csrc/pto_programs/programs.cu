@@ -223,6 +223,158 @@ AICORE inline void ProgAttentionHead(__gm__ float *o, __gm__ half *q, __gm__ hal
     TSTORE(go, ov);
 }
 
+// ---------------------------------------------------------------- the row-softmax tutorial and the second batch
+// Row softmax in the decomposition of the reference's tutorial (docs/coding/tutorials/row-softmax.md:14-45):
+// TROWMAX, TROWEXPAND + TSUB, TEXP, TROWSUM, TROWEXPAND + TDIV.
+template <int M, int N>
+AICORE inline void ProgRowSoftmaxTutorial(__gm__ float *out, __gm__ float *in)
+{
+    using GT = GlobalTensor<float, Shape<1, 1, 1, M, N>, Stride<1, 1, 1, N, 1>>;
+    using XTile = Tile<TileType::Vec, float, M, N, BLayout::RowMajor, DYNAMIC, DYNAMIC>;
+    using Col1 = Tile<TileType::Vec, float, M, 1, BLayout::ColMajor, DYNAMIC, 1>;
+    GT gin(in), gout(out);
+    XTile x(M, N), tmp(M, N);
+    Col1 row_max(M), row_sum(M);
+    TASSIGN(x, 0x0);
+    TASSIGN(tmp, M * N * sizeof(float));
+    TASSIGN(row_max, 2 * M * N * sizeof(float));
+    TASSIGN(row_sum, 2 * M * N * sizeof(float) + M * sizeof(float));
+    TLOAD(x, gin);
+    set_flag(PIPE_MTE2, PIPE_V, EVENT_ID0);
+    wait_flag(PIPE_MTE2, PIPE_V, EVENT_ID0);
+    TROWMAX(row_max, x, tmp);
+    TROWEXPAND(tmp, row_max);
+    TSUB(x, x, tmp);
+    TEXP(x, x);
+    TROWSUM(row_sum, x, tmp);
+    TROWEXPAND(tmp, row_sum);
+    TDIV(x, x, tmp);
+    set_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    wait_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    TSTORE(gout, x);
+}
+
+// TFILLPAD, TROWMIN, TCOLMAX / TCOLSUM / TCOLMIN, TTRANS, TCMPS + TSEL, TROWEXPAND{MAX,MIN,EXPDIF}, TROWEXPAND, TCMP
+// on one 64 x 128 fp32 tile pair.  Every result goes to its own output array.
+struct Vector2Out {
+    float *fill, *rowmin, *colmax, *colsum, *colmin, *trans, *sel, *emax, *emin, *edif, *expand, *cmp;
+    uint8_t *bits;
+};
+
+AICORE inline void ProgVector2(Vector2Out o, __gm__ float *a_in, __gm__ float *b_in, __gm__ float *s_in, int valid_rows,
+                               int valid_cols)
+{
+    constexpr int R = 64, C = 128;
+    using G = GlobalTensor<float, Shape<1, 1, 1, R, C>, Stride<1, 1, 1, C, 1>>;
+    using GTr = GlobalTensor<float, Shape<1, 1, 1, C, R>, Stride<1, 1, 1, R, 1>>;
+    using GCol = GlobalTensor<float, Shape<1, 1, 1, R, 1>, Stride<1, 1, 1, 1, R>, Layout::DN>;
+    using GRow = GlobalTensor<float, Shape<1, 1, 1, 1, C>, Stride<1, 1, 1, C, 1>>;
+    using GBits = GlobalTensor<uint8_t, Shape<1, 1, 1, R, C>, Stride<1, 1, 1, C, 1>>;
+    using X = Tile<TileType::Vec, float, R, C, BLayout::RowMajor, DYNAMIC, DYNAMIC>;
+    using XPad = Tile<TileType::Vec, float, R, C, BLayout::RowMajor, DYNAMIC, DYNAMIC, SLayout::NoneBox,
+                      TileConfig::fractalABSize, PadValue::Max>;
+    using XT = Tile<TileType::Vec, float, C, R, BLayout::RowMajor>;
+    using XFull = Tile<TileType::Vec, float, R, C, BLayout::RowMajor>;
+    using Col1 = Tile<TileType::Vec, float, R, 1, BLayout::ColMajor, DYNAMIC, 1>;
+    using Row1 = Tile<TileType::Vec, float, 1, C, BLayout::RowMajor, 1, DYNAMIC>;
+    using Bits = Tile<TileType::Vec, uint8_t, R, C, BLayout::RowMajor, DYNAMIC, DYNAMIC>;
+
+    constexpr uint32_t kTile = R * C * sizeof(float);
+    X a(R, C), b(R, C), w(R, C), part(valid_rows, valid_cols);
+    XPad padded(R, C);
+    XFull a_full, unused;
+    XT tr;
+    Col1 s(R), rmin(R);
+    Row1 cred(C);
+    Bits bits(R, C); // as in the reference's own test kernel the byte tile has the source's shape: the packed stream is contiguous
+    TASSIGN(a, 0x0);
+    TASSIGN(a_full, 0x0);
+    TASSIGN(part, 0x0);
+    TASSIGN(b, kTile);
+    TASSIGN(w, 2 * kTile);
+    TASSIGN(padded, 2 * kTile);
+    TASSIGN(tr, 2 * kTile);
+    TASSIGN(unused, 2 * kTile);
+    TASSIGN(bits, 3 * kTile);
+    TASSIGN(s, 3 * kTile + R * C);
+    TASSIGN(rmin, 3 * kTile + R * C + R * sizeof(float));
+    TASSIGN(cred, 3 * kTile + R * C + 2 * R * sizeof(float));
+
+    G ga(a_in), gb(b_in);
+    GCol gs(s_in);
+    TLOAD(a, ga);
+    TLOAD(b, gb);
+    TLOAD(s, gs);
+    set_flag(PIPE_MTE2, PIPE_V, EVENT_ID0);
+    wait_flag(PIPE_MTE2, PIPE_V, EVENT_ID0);
+
+    auto store_w = [&](__gm__ float *dst) {
+        G g(dst);
+        set_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+        wait_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+        TSTORE(g, w);
+        set_flag(PIPE_MTE3, PIPE_V, EVENT_ID0);
+        wait_flag(PIPE_MTE3, PIPE_V, EVENT_ID0);
+    };
+    auto store_row = [&](__gm__ float *dst) {
+        GRow g(dst);
+        set_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+        wait_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+        TSTORE(g, cred);
+        set_flag(PIPE_MTE3, PIPE_V, EVENT_ID0);
+        wait_flag(PIPE_MTE3, PIPE_V, EVENT_ID0);
+    };
+
+    // pad everything outside the valid corner of `a` with +inf, then the row minima of the padded tile
+    TFILLPAD(padded, part);
+    TROWMIN(rmin, padded, unused);
+    {
+        G g(o.fill);
+        GCol gm(o.rowmin);
+        set_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+        wait_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+        TSTORE(g, padded);
+        TSTORE(gm, rmin);
+        set_flag(PIPE_MTE3, PIPE_V, EVENT_ID0);
+        wait_flag(PIPE_MTE3, PIPE_V, EVENT_ID0);
+    }
+    TCOLMAX(cred, a);
+    store_row(o.colmax);
+    TCOLSUM(cred, a);
+    store_row(o.colsum);
+    TCOLMIN(cred, a);
+    store_row(o.colmin);
+    TTRANS(tr, a_full, unused);
+    {
+        GTr g(o.trans);
+        set_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+        wait_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+        TSTORE(g, tr);
+        set_flag(PIPE_MTE3, PIPE_V, EVENT_ID0);
+        wait_flag(PIPE_MTE3, PIPE_V, EVENT_ID0);
+    }
+    // relu-like selection: a where a > 0.25, else b
+    TCMPS(bits, a, 0.25f, CmpMode::GT);
+    TSEL(w, bits, a, b);
+    store_w(o.sel);
+    {
+        GBits g(o.bits);
+        Bits flat(R * C / 8 / C, C); // the packed stream sits at the start of the byte tile's storage
+        TASSIGN(flat, 3 * kTile);
+        TSTORE(g, flat);
+    }
+    TROWEXPANDMAX(w, a, s);
+    store_w(o.emax);
+    TROWEXPANDMIN(w, a, s);
+    store_w(o.emin);
+    TROWEXPANDEXPDIF(w, a, s);
+    store_w(o.edif);
+    TROWEXPAND(w, s);
+    store_w(o.expand);
+    TCMP(w, a, b, CmpMode::LT);
+    store_w(o.cmp);
+}
+
 // ---------------------------------------------------------------- host entry points
 #pragma GCC visibility push(default)
 extern "C" {
@@ -287,6 +439,33 @@ int pto_prog_attention_head_128x128x64(float *o, const __half *q, const __half *
     return pto::b200::launch(1, stream, [=] __device__() {
                ProgAttentionHead<128, 128, 64>(o, const_cast<__half *>(q), const_cast<__half *>(k),
                                                const_cast<__half *>(v), scale);
+           }) == cudaSuccess
+               ? 0
+               : 3;
+}
+
+int pto_prog_row_softmax_tutorial_64x256(float *out, const float *in, void *stream)
+{
+    return pto::b200::launch(1, stream, [=] __device__() {
+               ProgRowSoftmaxTutorial<64, 256>(out, const_cast<float *>(in));
+           }) == cudaSuccess
+               ? 0
+               : 3;
+}
+
+// outs: 13 device pointers in the order of Vector2Out (the last one the packed comparison bits)
+int pto_prog_vector2_64x128(void *const *outs, const float *a, const float *b, const float *s, int valid_rows,
+                            int valid_cols, void *stream)
+{
+    Vector2Out o;
+    float **f = reinterpret_cast<float **>(&o);
+    for (int i = 0; i < 12; ++i) {
+        f[i] = static_cast<float *>(outs[i]);
+    }
+    o.bits = static_cast<uint8_t *>(outs[12]);
+    return pto::b200::launch(1, stream, [=] __device__() {
+               ProgVector2(o, const_cast<float *>(a), const_cast<float *>(b), const_cast<float *>(s), valid_rows,
+                           valid_cols);
            }) == cudaSuccess
                ? 0
                : 3;

@@ -104,3 +104,53 @@ def test_attention_head_program(prog):
     want = port.attn_head_f16(q, k, v, 0, scale)
     ok, worst, frac = attn_err_ok(host(o), want)
     assert ok, f"max relative error {worst:.3e}, {frac:.5f} within tolerance"
+
+
+def test_row_softmax_tutorial_program(prog):
+    """The tutorial's decomposition (TROWMAX, TROWEXPAND + TSUB, TEXP, TROWSUM, TROWEXPAND + TDIV)."""
+    r = np.random.default_rng(21)
+    x = (r.standard_normal((64, 256)) * 4).astype(np.float32)
+    out = torch.zeros(64, 256, device="cuda")
+    assert prog.pto_prog_row_softmax_tutorial_64x256(_ptr(out), _ptr(dev(x)), _stream()) == 0
+    torch.cuda.synchronize()
+    mx = port.trowmax_f32(x)
+    e = port.texp_f32(port.trowexpand_f32(x, mx, 1))
+    want = e / port.trowsum_f32(e)[:, None]
+    ok, worst = rel_err_ok(host(out), want, 2e-6)  # expf and the row sum's order differ from the CPU's in the last bits
+    assert ok, worst
+    assert np.allclose(host(out).sum(axis=1), 1.0, atol=1e-5)
+
+
+@pytest.mark.parametrize("valid", [(64, 128), (40, 100), (1, 1)])
+def test_vector2_program(prog, valid):
+    """TFILLPAD, TROWMIN, TCOLMAX / TCOLSUM / TCOLMIN, TTRANS, TCMPS + TSEL, TROWEXPAND{MAX,MIN,EXPDIF}, TROWEXPAND, TCMP
+    issued as PTO instructions on shared-memory tiles: bit-equal to the oracle (EXPDIF: one ulp)."""
+    vr, vc = valid
+    r = np.random.default_rng(22)
+    a = r.standard_normal((64, 128)).astype(np.float32)
+    b = r.standard_normal((64, 128)).astype(np.float32)
+    s = (r.standard_normal(64) * 0.5).astype(np.float32)
+    names = ["fill", "rowmin", "colmax", "colsum", "colmin", "trans", "sel", "emax", "emin", "edif", "expand", "cmp"]
+    shapes = {"rowmin": (64,), "colmax": (128,), "colsum": (128,), "colmin": (128,), "trans": (128, 64)}
+    outs = {n: torch.full(shapes.get(n, (64, 128)), -7.0, device="cuda") for n in names}
+    bits = torch.zeros(64 * 128 // 8, dtype=torch.uint8, device="cuda")
+    ptrs = (ctypes.c_void_p * 13)(*[outs[n].data_ptr() for n in names], bits.data_ptr())
+    assert prog.pto_prog_vector2_64x128(ptrs, _ptr(dev(a)), _ptr(dev(b)), _ptr(dev(s)), vr, vc, _stream()) == 0
+    torch.cuda.synchronize()
+    u32 = lambda x: np.ascontiguousarray(x).view(np.uint32)
+    fill = port.tfillpad_f32(a, vr, vc, 2)
+    assert np.array_equal(u32(host(outs["fill"])), u32(fill))
+    assert np.array_equal(u32(host(outs["rowmin"])), u32(port.trowmin_f32(fill)))
+    assert np.array_equal(u32(host(outs["colmax"])), u32(port.tcolreduce_f32(a, 4)))
+    assert np.array_equal(u32(host(outs["colsum"])), u32(port.tcolreduce_f32(a, 0)))  # same top-to-bottom order
+    assert np.array_equal(u32(host(outs["colmin"])), u32(port.tcolreduce_f32(a, 5)))
+    assert np.array_equal(host(outs["trans"]), port.ttrans(a))
+    want_bits = port.tcmps_f32(a, 0.25, 4)
+    assert np.array_equal(host(bits), want_bits)
+    assert np.array_equal(host(outs["sel"]), port.tsel(want_bits, a, b))
+    assert np.array_equal(u32(host(outs["emax"])), u32(port.trowexpand_f32(a, s, 4)))
+    assert np.array_equal(u32(host(outs["emin"])), u32(port.trowexpand_f32(a, s, 5)))
+    got, want = u32(host(outs["edif"])).astype(np.int64), u32(port.trowexpand_f32(a, s, 6)).astype(np.int64)
+    assert np.all(np.abs(got - want) <= 1)
+    assert np.array_equal(u32(host(outs["expand"])), u32(port.trowexpand_f32(a, s, 7)))
+    assert np.array_equal(host(outs["cmp"]), port.tcmp_f32(a, b, 2))
