@@ -349,6 +349,7 @@ def extras(torch, pto, peaks, peak_kind):
     colv = [torch.empty(side, device="cuda") for _ in range(sets)]
     maskb = [torch.randint(0, 256, (n // 8,), device="cuda", dtype=torch.uint8, generator=g) for _ in range(sets)]
     bitsb = [torch.empty(n // 8, device="cuda", dtype=torch.uint8) for _ in range(sets)]
+    col_ws = torch.empty(max(1, pto.lib().pto_b200_tcolreduce_workspace_bytes(side, side) // 4), device="cuda")
     cases = [
         ("TCVT f32->f16 16M elements", 6.0, rot(lambda j: pto.TCVT(xs[j], torch.float16, out=o16[j]))),
         ("TCVT f32->bf16 16M elements", 6.0, rot(lambda j: pto.TCVT(xs[j], torch.bfloat16, out=ob16[j]))),
@@ -356,7 +357,7 @@ def extras(torch, pto, peaks, peak_kind):
          rot(lambda j: pto.TGATHER(xs[j], idx[j], out=og[j]))),
         ("TROWEXPANDSUB f32 4096x4096", 8.0, rot(lambda j: pto.TROWEXPANDSUB(x2[j], rowv[j], out=o2[j]))),
         ("TROWMAX f32 4096x4096", 4.0, rot(lambda j: pto.TROWMAX(x2[j], out=colv[j]))),
-        ("TCOLSUM f32 4096x4096", 4.0, rot(lambda j: pto.TCOLSUM(x2[j], out=colv[j]))),
+        ("TCOLSUM f32 4096x4096", 4.0, rot(lambda j: pto.TCOLSUM(x2[j], out=colv[j], workspace=col_ws))),
         ("TTRANS f32 4096x4096", 8.0, rot(lambda j: pto.TTRANS(x2[j], out=o2[j]))),
         ("TSEL f32 16M elements, bit mask", 12.125, rot(lambda j: pto.TSEL(maskb[j], xs[j], xs[(j + 1) % sets], out=og[j]))),
         ("TCMPS f32 16M elements -> bits", 4.125, rot(lambda j: pto.TCMPS(xs[j], 0.0, 4, out=bitsb[j]))),

@@ -119,8 +119,14 @@ int pto_b200_trowexpand_f32(const float *a, const float *row_scalar, float *dst,
 int pto_b200_trowmin_f32(const float *src, float *dst, int rows, int cols, int64_t row_stride, void *stream);
 /* TCOLSUM / TCOLMAX / TCOLMIN: dst[c] = sum / max / min over the `rows` valid rows of column c; `op` is
  * PTO_B200_OP_ADD, _MAX or _MIN (include/pto/common/pto_instr.hpp:959-988, :1305-1310; include/pto/cpu/TColSum.hpp:19-30,
- * TColMax.hpp:19-33, TColMin.hpp).  The sum is a fixed-order tree in fp32 (the reference sums top to bottom). */
-int pto_b200_tcolreduce_f32(const float *src, float *dst, int rows, int cols, int64_t row_stride, int op, void *stream);
+ * TColMax.hpp:19-33, TColMin.hpp).  The sum is a fixed-order tree in fp32 (the reference sums top to bottom).
+ * `workspace` is optional scratch in device memory: with at least pto_b200_tcolreduce_workspace_bytes(rows, cols)
+ * bytes of it (16-byte aligned) a large tile is reduced in two passes that use the whole GPU; with NULL, or for small
+ * tiles (the query returns 0), one block per strip of 32 columns does the whole column.  The result does not depend
+ * on which form ran for max / min; for the sum both orders are fixed but differ in the last bits. */
+int64_t pto_b200_tcolreduce_workspace_bytes(int rows, int cols);
+int pto_b200_tcolreduce_f32(const float *src, float *dst, int rows, int cols, int64_t row_stride, int op, void *workspace,
+                            int64_t workspace_bytes, void *stream);
 /* TFILLPAD: dst is rows x cols; its valid_rows x valid_cols corner is copied from src (same shape and pitch, read
  * only inside that corner), every other element becomes `pad_bits` (the low 16 bits for 2-byte elements): the
  * caller passes the pattern PadValue::Zero / Max / Min mean for its element type, e.g. 0x7f800000 / 0xff800000 for

@@ -34,7 +34,8 @@ SIGNATURES = {
     "pto_b200_tscalar_f32": (_i, [_vp, _f, _vp, _i64, _i, _vp]),
     "pto_b200_trowexpand_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "pto_b200_trowmin_f32": (_i, [_vp, _vp, _i, _i, _i64, _vp]),
-    "pto_b200_tcolreduce_f32": (_i, [_vp, _vp, _i, _i, _i64, _i, _vp]),
+    "pto_b200_tcolreduce_workspace_bytes": (_i64, [_i, _i]),
+    "pto_b200_tcolreduce_f32": (_i, [_vp, _vp, _i, _i, _i64, _i, _vp, _i64, _vp]),
     "pto_b200_tfillpad": (_i, [_vp, _vp, _i, _i, _i, _i, _u32, _i, _vp]),
     "pto_b200_ttrans": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "pto_b200_tsel": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _vp]),

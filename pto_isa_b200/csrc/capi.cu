@@ -65,7 +65,7 @@ extern "C" {
 
 int pto_b200_version(void)
 {
-    return 1;
+    return 2; // 2: second batch of vector ops (row-expand family, column reductions, TFILLPAD, TTRANS, TSEL, TCMP*)
 }
 
 const char *pto_b200_last_error(void)
@@ -200,13 +200,24 @@ int pto_b200_trowmin_f32(const float *src, float *dst, int rows, int cols, int64
     return launch_trowmin(src, dst, rows, cols, row_stride, as_stream(stream));
 }
 
-int pto_b200_tcolreduce_f32(const float *src, float *dst, int rows, int cols, int64_t row_stride, int op, void *stream)
+int64_t pto_b200_tcolreduce_workspace_bytes(int rows, int cols)
 {
-    if (rows <= 0 || cols < 0 || row_stride < cols || (op != 0 && op != 4 && op != 5) ||
+    if (rows <= 0 || cols <= 0) {
+        return 0;
+    }
+    const int segs = tcolreduce_segments(rows, cols);
+    return segs > 1 ? static_cast<int64_t>(segs) * cols * static_cast<int64_t>(sizeof(float)) : 0;
+}
+
+int pto_b200_tcolreduce_f32(const float *src, float *dst, int rows, int cols, int64_t row_stride, int op, void *workspace,
+                            int64_t workspace_bytes, void *stream)
+{
+    if (rows <= 0 || cols < 0 || row_stride < cols || (op != 0 && op != 4 && op != 5) || workspace_bytes < 0 ||
         (cols > 0 && (src == nullptr || dst == nullptr))) {
         return bad("tcolreduce: bad argument (op must be PTO_B200_OP_ADD, _MAX or _MIN; at least one row)");
     }
-    return launch_tcolreduce(src, dst, rows, cols, row_stride, op, as_stream(stream));
+    return launch_tcolreduce(src, dst, rows, cols, row_stride, op, static_cast<float *>(workspace),
+                             static_cast<size_t>(workspace_bytes), as_stream(stream));
 }
 
 int pto_b200_tfillpad(const void *src, void *dst, int rows, int cols, int valid_rows, int valid_cols, uint32_t pad_bits,

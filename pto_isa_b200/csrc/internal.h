@@ -53,7 +53,9 @@ int launch_tscalar(const float *a, float s, float *dst, int64_t n, int op, cudaS
 int launch_trowexpand(const float *a, const float *row_scalar, float *dst, int rows, int cols, int op,
                       cudaStream_t stream);
 int launch_trowmin(const float *src, float *dst, int rows, int cols, int64_t row_stride, cudaStream_t stream);
-int launch_tcolreduce(const float *src, float *dst, int rows, int cols, int64_t row_stride, int op, cudaStream_t stream);
+int launch_tcolreduce(const float *src, float *dst, int rows, int cols, int64_t row_stride, int op, float *workspace,
+                      size_t workspace_bytes, cudaStream_t stream);
+int tcolreduce_segments(int rows, int cols);
 int launch_tfillpad(const void *src, void *dst, int rows, int cols, int valid_rows, int valid_cols, uint32_t pad,
                     int elem_bytes, cudaStream_t stream);
 int launch_ttrans(const void *src, void *dst, int rows, int cols, int elem_bytes, cudaStream_t stream);

@@ -211,7 +211,16 @@ __global__ void __launch_bounds__(kThreads) trow_reduce_kernel(const float *__re
         if (vec_ok) {
             const int nvec = cols >> 2;
             const float4 *p4 = reinterpret_cast<const float4 *>(p);
-            for (int i = lane; i < nvec; i += 32) {
+            int i = lane;
+            for (; i + 96 < nvec; i += 128) { // four 16-byte loads in flight per lane
+                const float4 v0 = ld_stream_f4(p4 + i), v1 = ld_stream_f4(p4 + i + 32);
+                const float4 v2 = ld_stream_f4(p4 + i + 64), v3 = ld_stream_f4(p4 + i + 96);
+                acc = red_op<kIsMax>(acc, red_op<kIsMax>(red_op<kIsMax>(v0.x, v0.y), red_op<kIsMax>(v0.z, v0.w)));
+                acc = red_op<kIsMax>(acc, red_op<kIsMax>(red_op<kIsMax>(v1.x, v1.y), red_op<kIsMax>(v1.z, v1.w)));
+                acc = red_op<kIsMax>(acc, red_op<kIsMax>(red_op<kIsMax>(v2.x, v2.y), red_op<kIsMax>(v2.z, v2.w)));
+                acc = red_op<kIsMax>(acc, red_op<kIsMax>(red_op<kIsMax>(v3.x, v3.y), red_op<kIsMax>(v3.z, v3.w)));
+            }
+            for (; i < nvec; i += 32) {
                 const float4 v = ld_stream_f4(p4 + i);
                 acc = red_op<kIsMax>(acc, red_op<kIsMax>(red_op<kIsMax>(v.x, v.y), red_op<kIsMax>(v.z, v.w)));
             }

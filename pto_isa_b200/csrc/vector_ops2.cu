@@ -50,17 +50,31 @@ __global__ void __launch_bounds__(kThreads) trowexpand_kernel(const float *__res
     if (kVec) {
         const int vcols = cols >> 2;
         const int64_t nvec = static_cast<int64_t>(rows) * vcols;
-        for (int64_t i = tid; i < nvec; i += stride) {
-            const float sv = __ldg(s + i / vcols);
-            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        // two independent 16-byte loads in flight per thread
+        for (int64_t i = tid; i < nvec; i += 2 * stride) {
+            const int64_t j = i + stride;
+            const bool two = j < nvec;
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f), w = v;
             if (op != 7) {
                 v = ld_stream_f4(reinterpret_cast<const float4 *>(a) + i);
+                if (two) {
+                    w = ld_stream_f4(reinterpret_cast<const float4 *>(a) + j);
+                }
             }
+            const float sv = __ldg(s + i / vcols);
+            const float sw = two ? __ldg(s + j / vcols) : 0.0f;
             v.x = elem_op(op, v.x, sv);
             v.y = elem_op(op, v.y, sv);
             v.z = elem_op(op, v.z, sv);
             v.w = elem_op(op, v.w, sv);
             st_stream_f4(reinterpret_cast<float4 *>(dst) + i, v);
+            if (two) {
+                w.x = elem_op(op, w.x, sw);
+                w.y = elem_op(op, w.y, sw);
+                w.z = elem_op(op, w.z, sw);
+                w.w = elem_op(op, w.w, sw);
+                st_stream_f4(reinterpret_cast<float4 *>(dst) + j, w);
+            }
         }
     } else {
         const int64_t n = static_cast<int64_t>(rows) * cols;
@@ -82,7 +96,16 @@ __global__ void __launch_bounds__(kThreads) trowmin_kernel(const float *__restri
         int c = 0;
         if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
             const int nvec = cols >> 2;
-            for (int i = lane; i < nvec; i += 32) {
+            int i = lane;
+            for (; i + 96 < nvec; i += 128) { // four 16-byte loads in flight per lane
+                const float4 v0 = ld_stream_f4(reinterpret_cast<const float4 *>(p) + i);
+                const float4 v1 = ld_stream_f4(reinterpret_cast<const float4 *>(p) + i + 32);
+                const float4 v2 = ld_stream_f4(reinterpret_cast<const float4 *>(p) + i + 64);
+                const float4 v3 = ld_stream_f4(reinterpret_cast<const float4 *>(p) + i + 96);
+                acc = fminf(acc, fminf(fminf(fminf(v0.x, v0.y), fminf(v0.z, v0.w)), fminf(fminf(v1.x, v1.y), fminf(v1.z, v1.w))));
+                acc = fminf(acc, fminf(fminf(fminf(v2.x, v2.y), fminf(v2.z, v2.w)), fminf(fminf(v3.x, v3.y), fminf(v3.z, v3.w))));
+            }
+            for (; i < nvec; i += 32) {
                 const float4 v = ld_stream_f4(reinterpret_cast<const float4 *>(p) + i);
                 acc = fminf(acc, fminf(fminf(v.x, v.y), fminf(v.z, v.w)));
             }
@@ -156,6 +179,76 @@ __global__ void __launch_bounds__(kColWarps * 32) tcolreduce_kernel(const float 
             dst[c] = t;
         }
         __syncthreads();
+    }
+}
+
+// Two-pass form for large tiles (needs a caller-provided workspace of segments * cols floats): the rows are cut
+// into segments so that strips x segments blocks fill the GPU; a block of 8 warps reduces 128 columns (one 512-byte
+// row piece per warp load, four in flight) of one segment and writes a partial row, the second pass combines the
+// segments top to bottom.  Deterministic; the sum's order is fixed but not the reference's.
+constexpr int kSegWarps = 8;
+constexpr int kSegUnroll = 4;
+
+template <int kOp>
+__device__ __forceinline__ float4 col_op4(float4 a, float4 b)
+{
+    return make_float4(col_op<kOp>(a.x, b.x), col_op<kOp>(a.y, b.y), col_op<kOp>(a.z, b.z), col_op<kOp>(a.w, b.w));
+}
+
+template <int kOp>
+__global__ void __launch_bounds__(kSegWarps * 32) tcolreduce_seg_kernel(const float *__restrict__ src,
+                                                                         float *__restrict__ partial, int rows, int cols,
+                                                                         int64_t row_stride, int rows_per_seg)
+{
+    __shared__ float4 part[kSegWarps][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float id1 = kOp == 0 ? 0.0f : (kOp == 4 ? -INFINITY : INFINITY);
+    const float4 ident = make_float4(id1, id1, id1, id1);
+    const int c = (blockIdx.x * 32 + lane) * 4; // cols is a multiple of 4
+    const int r_begin = blockIdx.y * rows_per_seg;
+    const int r_end = min(rows, r_begin + rows_per_seg);
+    float4 acc[kSegUnroll];
+#pragma unroll
+    for (int u = 0; u < kSegUnroll; ++u) {
+        acc[u] = ident;
+    }
+    if (c < cols) {
+        const float *p = src + c;
+        for (int r = r_begin + warp; r < r_end; r += kSegWarps * kSegUnroll) {
+#pragma unroll
+            for (int u = 0; u < kSegUnroll; ++u) {
+                const int rr = r + u * kSegWarps;
+                if (rr < r_end) {
+                    acc[u] = col_op4<kOp>(acc[u], ld_stream_f4(reinterpret_cast<const float4 *>(
+                                                      p + static_cast<int64_t>(rr) * row_stride)));
+                }
+            }
+        }
+    }
+    float4 v = col_op4<kOp>(col_op4<kOp>(acc[0], acc[1]), col_op4<kOp>(acc[2], acc[3]));
+    part[warp][lane] = v;
+    __syncthreads();
+    if (warp == 0 && c < cols) {
+        float4 t = part[0][lane];
+#pragma unroll
+        for (int w = 1; w < kSegWarps; ++w) {
+            t = col_op4<kOp>(t, part[w][lane]);
+        }
+        *reinterpret_cast<float4 *>(partial + static_cast<int64_t>(blockIdx.y) * cols + c) = t;
+    }
+}
+
+template <int kOp>
+__global__ void __launch_bounds__(kThreads) tcolreduce_final_kernel(const float *__restrict__ partial,
+                                                                    float *__restrict__ dst, int cols, int segments)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < cols) {
+        float t = partial[c];
+        for (int s = 1; s < segments; ++s) {
+            t = col_op<kOp>(t, partial[static_cast<int64_t>(s) * cols + c]);
+        }
+        dst[c] = t;
     }
 }
 
@@ -356,7 +449,7 @@ int launch_trowexpand(const float *a, const float *row_scalar, float *dst, int r
     }
     const bool vec = (cols % 4 == 0) && aligned16(dst) && (op == 7 || aligned16(a));
     if (vec) {
-        trowexpand_kernel<true><<<grid_for(static_cast<int64_t>(rows) * (cols >> 2), kThreads), kThreads, 0, stream>>>(
+        trowexpand_kernel<true><<<grid_for(static_cast<int64_t>(rows) * (cols >> 3) + 1, kThreads), kThreads, 0, stream>>>(
             a, row_scalar, dst, rows, cols, op);
     } else {
         trowexpand_kernel<false><<<grid_for(static_cast<int64_t>(rows) * cols, kThreads), kThreads, 0, stream>>>(
@@ -374,10 +467,51 @@ int launch_trowmin(const float *src, float *dst, int rows, int cols, int64_t row
     return check_launch();
 }
 
-int launch_tcolreduce(const float *src, float *dst, int rows, int cols, int64_t row_stride, int op, cudaStream_t stream)
+// segments the two-pass form cuts `rows` into (1: the single-pass kernel is used)
+int tcolreduce_segments(int rows, int cols)
+{
+    if ((cols & 3) != 0 || rows < 256) {
+        return 1;
+    }
+    const int strips = (cols + 127) / 128;
+    int segs = (8 * sm_count() + strips - 1) / strips;
+    const int max_segs = rows / 64; // at least 64 rows per segment
+    if (segs > max_segs) {
+        segs = max_segs;
+    }
+    return segs < 2 ? 1 : segs;
+}
+
+int launch_tcolreduce(const float *src, float *dst, int rows, int cols, int64_t row_stride, int op, float *workspace,
+                      size_t workspace_bytes, cudaStream_t stream)
 {
     if (cols == 0) {
         return kOk;
+    }
+    const int segs = tcolreduce_segments(rows, cols);
+    const bool two_pass = segs > 1 && workspace != nullptr &&
+                          workspace_bytes >= static_cast<size_t>(segs) * cols * sizeof(float) && aligned16(src) &&
+                          aligned16(workspace) && (row_stride & 3) == 0;
+    if (two_pass) {
+        const int rows_per_seg = (rows + segs - 1) / segs;
+        const dim3 grid((cols + 127) / 128, segs);
+        const int fgrid = (cols + kThreads - 1) / kThreads;
+        switch (op) {
+            case 0:
+                tcolreduce_seg_kernel<0><<<grid, kSegWarps * 32, 0, stream>>>(src, workspace, rows, cols, row_stride, rows_per_seg);
+                tcolreduce_final_kernel<0><<<fgrid, kThreads, 0, stream>>>(workspace, dst, cols, segs);
+                break;
+            case 4:
+                tcolreduce_seg_kernel<4><<<grid, kSegWarps * 32, 0, stream>>>(src, workspace, rows, cols, row_stride, rows_per_seg);
+                tcolreduce_final_kernel<4><<<fgrid, kThreads, 0, stream>>>(workspace, dst, cols, segs);
+                break;
+            case 5:
+                tcolreduce_seg_kernel<5><<<grid, kSegWarps * 32, 0, stream>>>(src, workspace, rows, cols, row_stride, rows_per_seg);
+                tcolreduce_final_kernel<5><<<fgrid, kThreads, 0, stream>>>(workspace, dst, cols, segs);
+                break;
+            default: return kErrBadArgument;
+        }
+        return check_launch();
     }
     const int strips = (cols + 31) / 32;
     const int grid = strips < 4 * sm_count() ? strips : 4 * sm_count();

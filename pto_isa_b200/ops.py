@@ -228,28 +228,32 @@ def TROWMIN(src, out=None):
     return _row_reduce("pto_b200_trowmin_f32", src, out)
 
 
-def _col_reduce(src, op, out, what):
+def _col_reduce(src, op, out, what, workspace=None):
     _need_cuda(src)
     if src.dim() != 2 or src.dtype != torch.float32:
         raise PtoB200Error(f"{what}: expects a 2-D float32 tensor")
     rows, cols = src.shape
     out = torch.empty(cols, dtype=torch.float32, device=src.device) if out is None else out
+    ws_bytes = lib().pto_b200_tcolreduce_workspace_bytes(rows, cols) if workspace is None else workspace.numel() * workspace.element_size()
+    if workspace is None and ws_bytes > 0:
+        workspace = torch.empty(ws_bytes // 4, dtype=torch.float32, device=src.device)  # torch's caching allocator
     with torch.cuda.device(src.device):
-        rc = lib().pto_b200_tcolreduce_f32(_ptr(src), _ptr(out), rows, cols, cols, op, _stream(src))
+        rc = lib().pto_b200_tcolreduce_f32(_ptr(src), _ptr(out), rows, cols, cols, op,
+                                           _ptr(workspace) if workspace is not None else None, ws_bytes, _stream(src))
     check(rc, what)
     return out
 
 
-def TCOLSUM(src, out=None):
-    return _col_reduce(src, OP_ADD, out, "TCOLSUM")
+def TCOLSUM(src, out=None, workspace=None):
+    return _col_reduce(src, OP_ADD, out, "TCOLSUM", workspace)
 
 
-def TCOLMAX(src, out=None):
-    return _col_reduce(src, OP_MAX, out, "TCOLMAX")
+def TCOLMAX(src, out=None, workspace=None):
+    return _col_reduce(src, OP_MAX, out, "TCOLMAX", workspace)
 
 
-def TCOLMIN(src, out=None):
-    return _col_reduce(src, OP_MIN, out, "TCOLMIN")
+def TCOLMIN(src, out=None, workspace=None):
+    return _col_reduce(src, OP_MIN, out, "TCOLMIN", workspace)
 
 
 def _pad_bits(dtype, pad):

@@ -47,7 +47,7 @@ def test_only_the_c_abi_is_exported(built_lib):
 def test_python_signature_table_matches_header(built_lib):
     from pto_isa_b200 import _lib
     assert sorted(_lib.SIGNATURES) == header_symbols()
-    assert _lib.lib().pto_b200_version() == 1
+    assert _lib.lib().pto_b200_version() == 2
 
 
 def test_call_kernel_shims_export_the_reference_symbol(built_lib):

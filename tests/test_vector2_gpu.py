@@ -92,6 +92,23 @@ def test_fillpad_trans_sel_cmp(rows, cols):
             assert np.array_equal(host(pto.TCMPS(cuda(ai), 1.0, mode)), port.tcmps_f32(ai, 1.0, mode)), mode
 
 
+def test_column_reduction_forms_agree():
+    """The two-pass form (caller workspace) and the single-pass form give the same max / min and sums within the
+    order tolerance; a workspace that is too small falls back to the single pass."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randn(1000, 2052, device="cuda", generator=g)
+    need = pto.lib().pto_b200_tcolreduce_workspace_bytes(1000, 2052)
+    assert need > 0 and pto.lib().pto_b200_tcolreduce_workspace_bytes(100, 2052) == 0
+    small = torch.empty(4, device="cuda")
+    for fn in (pto.TCOLMAX, pto.TCOLMIN):
+        assert torch.equal(fn(a), fn(a, workspace=small))
+        assert torch.equal(fn(a), getattr(a, "max" if fn is pto.TCOLMAX else "min")(dim=0).values)
+    s2, s1 = pto.TCOLSUM(a), pto.TCOLSUM(a, workspace=small)
+    assert (s2 - s1).abs().max().item() <= 2e-6 * a.abs().sum(dim=0).max().item()
+    want = port.tcolreduce_f32(host(a), 0)
+    assert np.all(np.abs(host(s2) - want) <= 2e-6 * np.abs(host(a)).sum(axis=0))
+
+
 def test_tcmps_equality_window():
     # EQ / NE compare |a - b| in double against 1e-9 (include/pto/cpu/TCmps.hpp:27-33)
     x = np.array([1.0, 1.0 + 2 ** -23, 1e-10, -1e-10, 0.0, 5e-10, 2e-9, 3.0], np.float32)
