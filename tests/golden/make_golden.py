@@ -306,6 +306,25 @@ def gen_vector2(ref, tmp, out):
     np.savez_compressed(os.path.join(out, "vector2.npz"), **keep)
 
 
+def gen_harness(ref, tmp, out):
+    """The case list files of the flash-attention harness, written by the reference's own generator
+    (kernels/manual/common/flash_atten/scripts/generate_cases.py:168-232) for its default cases and for an explicit
+    list: kept as text fixtures so that the B200 replay tool's reader / writer can be compared byte for byte."""
+    import subprocess
+    script = os.path.join(ref, "kernels/manual/common/flash_atten/scripts/generate_cases.py")
+    for tag, extra in (("default", []), ("explicit", ["--cases", "128,128,512,128", "--cases", "128,512,2048,128,512",
+                                                      "--qk-preload", "2"])):
+        d = in_case_dir(tmp, f"harness_{tag}")
+        subprocess.check_call([sys.executable, script, "--output-header", os.path.join(d, "generated_cases.h"),
+                               "--output-json", os.path.join(d, "generated_cases.json")] + extra,
+                              stdout=subprocess.DEVNULL)
+        for name in ("generated_cases.h", "generated_cases.json"):
+            with open(os.path.join(d, name)) as f:
+                text = f.read()
+            with open(os.path.join(out, f"harness_{tag}_{name}"), "w") as f:
+                f.write(text)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -313,13 +332,13 @@ def main():
     cwd = os.getcwd()
     with tempfile.TemporaryDirectory() as tmp:
         try:
-            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm, gen_vector2):
+            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm, gen_vector2, gen_harness):
                 os.chdir(tmp)
                 fn(args.reference, tmp, HERE)
         finally:
             os.chdir(cwd)
     for f in sorted(os.listdir(HERE)):
-        if f.endswith(".npz"):
+        if f.endswith(".npz") or f.startswith("harness_"):
             print(f, os.path.getsize(os.path.join(HERE, f)))
 
 
