@@ -238,17 +238,31 @@ __global__ void __launch_bounds__(kSegWarps * 32) tcolreduce_seg_kernel(const fl
     }
 }
 
+// second pass: a block per 32 columns, warp w folds segments w, w + 8, ... (independent loads), then the eight
+// warps' values are folded in warp order: a fixed order for every column
 template <int kOp>
 __global__ void __launch_bounds__(kThreads) tcolreduce_final_kernel(const float *__restrict__ partial,
                                                                     float *__restrict__ dst, int cols, int segments)
 {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    __shared__ float part[kThreads / 32][33];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * 32 + lane;
+    float t = kOp == 0 ? 0.0f : (kOp == 4 ? -INFINITY : INFINITY);
     if (c < cols) {
-        float t = partial[c];
-        for (int s = 1; s < segments; ++s) {
-            t = col_op<kOp>(t, partial[static_cast<int64_t>(s) * cols + c]);
+#pragma unroll 4
+        for (int sgm = warp; sgm < segments; sgm += kThreads / 32) {
+            t = col_op<kOp>(t, __ldg(partial + static_cast<int64_t>(sgm) * cols + c));
         }
-        dst[c] = t;
+    }
+    part[warp][lane] = t;
+    __syncthreads();
+    if (warp == 0 && c < cols) {
+        float v = part[0][lane];
+#pragma unroll
+        for (int w = 1; w < kThreads / 32; ++w) {
+            v = col_op<kOp>(v, part[w][lane]);
+        }
+        dst[c] = v;
     }
 }
 
@@ -495,7 +509,7 @@ int launch_tcolreduce(const float *src, float *dst, int rows, int cols, int64_t 
     if (two_pass) {
         const int rows_per_seg = (rows + segs - 1) / segs;
         const dim3 grid((cols + 127) / 128, segs);
-        const int fgrid = (cols + kThreads - 1) / kThreads;
+        const int fgrid = (cols + 31) / 32;
         switch (op) {
             case 0:
                 tcolreduce_seg_kernel<0><<<grid, kSegWarps * 32, 0, stream>>>(src, workspace, rows, cols, row_stride, rows_per_seg);
