@@ -163,6 +163,11 @@ int pto_b200_gemm_f16f32_batched(const uint16_t *a, const uint16_t *b, float *c,
                                  int batch, int64_t a_stride, int64_t b_stride, int64_t c_stride, void *stream);
 /* Same product with HOST buffers: copies A and B in, runs the kernel, copies C out, synchronises. */
 int pto_b200_gemm_f16f32_host(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout);
+/* `batch` problems from HOST buffers, operands `*_stride` elements apart: the copy in of problem i + 1, the kernel of
+ * problem i and the copy out of problem i - 1 overlap (three streams over two staging sets; pinned host buffers are
+ * needed for the copies to overlap).  Returns after the last C has arrived. */
+int pto_b200_gemm_f16f32_host_batched(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
+                                      int batch, int64_t a_stride, int64_t b_stride, int64_t c_stride);
 
 /* Host-buffer GEMM for callers that must not allocate device memory at call time: processes whose device memory
  * is wholly owned by another allocator, plugins barred from allocation calls after start-up, or paths that cannot

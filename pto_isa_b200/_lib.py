@@ -44,6 +44,7 @@ SIGNATURES = {
     "pto_b200_gemm_f16f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "pto_b200_gemm_f16f32_batched": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i64, _i64, _i64, _vp]),
     "pto_b200_gemm_f16f32_host": (_i, [_vp, _vp, _vp, _i, _i, _i, _i]),
+    "pto_b200_gemm_f16f32_host_batched": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i64, _i64, _i64]),
     "pto_b200_gemm_f16f32_host_static": (_i, [_vp, _vp, _vp, _i, _i, _i, _i]),
     "pto_b200_flash_attn_fwd_f16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp]),
     "pto_b200_flash_attn_fwd_f16_host": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i]),

@@ -22,9 +22,12 @@ int bad(const char *what)
 
 // Device scratch for the *_host entry points: grown on demand, kept for reuse, one set per process.
 struct HostArena {
-    void *ptr[4] = {nullptr, nullptr, nullptr, nullptr};
-    size_t cap[4] = {0, 0, 0, 0};
+    void *ptr[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    size_t cap[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     cudaStream_t stream = nullptr;
+    // the batched host GEMM pipelines copies in, kernels and copies out on three streams over two staging sets
+    cudaStream_t pipe[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t h2d_done[2] = {nullptr, nullptr}, comp_done[2] = {nullptr, nullptr}, d2h_done[2] = {nullptr, nullptr};
 };
 HostArena g_arena;
 
@@ -55,6 +58,30 @@ int arena_stream(cudaStream_t *s)
         }
     }
     *s = g_arena.stream;
+    return kOk;
+}
+
+int arena_pipeline()
+{
+    for (int i = 0; i < 3; ++i) {
+        if (g_arena.pipe[i] == nullptr) {
+            int rc = check_cuda(cudaStreamCreateWithFlags(&g_arena.pipe[i], cudaStreamNonBlocking), "cudaStreamCreate");
+            if (rc != kOk) {
+                return rc;
+            }
+        }
+    }
+    for (int i = 0; i < 2; ++i) {
+        cudaEvent_t *evs[3] = {&g_arena.h2d_done[i], &g_arena.comp_done[i], &g_arena.d2h_done[i]};
+        for (cudaEvent_t *e : evs) {
+            if (*e == nullptr) {
+                int rc = check_cuda(cudaEventCreateWithFlags(e, cudaEventDisableTiming), "cudaEventCreate");
+                if (rc != kOk) {
+                    return rc;
+                }
+            }
+        }
+    }
     return kOk;
 }
 
@@ -319,6 +346,60 @@ int pto_b200_gemm_f16f32_host(const uint16_t *a, const uint16_t *b, float *c, in
         return rc;
     }
     return check_cuda(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+}
+
+int pto_b200_gemm_f16f32_host_batched(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
+                                      int batch, int64_t a_stride, int64_t b_stride, int64_t c_stride)
+{
+    if (m <= 0 || n <= 0 || k <= 0 || batch < 0 || a_stride < 0 || b_stride < 0 || c_stride < 0 ||
+        (batch > 0 && (a == nullptr || b == nullptr || c == nullptr))) {
+        return bad("gemm_host_batched: bad argument");
+    }
+    if (batch == 0) {
+        return kOk;
+    }
+    const size_t a_bytes = static_cast<size_t>(m) * k * 2, b_bytes = static_cast<size_t>(n) * k * 2,
+                 c_bytes = static_cast<size_t>(m) * n * 4;
+    void *da[2], *db[2], *dc[2];
+    int rc = arena_pipeline();
+    for (int s = 0; s < 2 && rc == kOk; ++s) {
+        if ((rc = arena_get(2 + 3 * s, a_bytes, &da[s])) == kOk && (rc = arena_get(3 + 3 * s, b_bytes, &db[s])) == kOk) {
+            rc = arena_get(4 + 3 * s, c_bytes, &dc[s]);
+        }
+    }
+    if (rc != kOk) {
+        return rc;
+    }
+    cudaStream_t in = g_arena.pipe[0], run = g_arena.pipe[1], out = g_arena.pipe[2];
+    for (int i = 0; i < batch && rc == kOk; ++i) {
+        const int s = i & 1;
+        const uint16_t *ha = a + static_cast<int64_t>(i) * a_stride, *hb = b + static_cast<int64_t>(i) * b_stride;
+        float *hc = c + static_cast<int64_t>(i) * c_stride;
+        // copies in: the kernel of problem i - 2 has consumed this set's A and B
+        if (i >= 2) {
+            rc = check_cuda(cudaStreamWaitEvent(in, g_arena.comp_done[s], 0), "cudaStreamWaitEvent");
+        }
+        if (rc == kOk) rc = check_cuda(cudaMemcpyAsync(da[s], ha, a_bytes, cudaMemcpyHostToDevice, in), "H2D A");
+        if (rc == kOk) rc = check_cuda(cudaMemcpyAsync(db[s], hb, b_bytes, cudaMemcpyHostToDevice, in), "H2D B");
+        if (rc == kOk) rc = check_cuda(cudaEventRecord(g_arena.h2d_done[s], in), "cudaEventRecord");
+        // kernel: operands are in, and the copy out of problem i - 2 has read this set's C
+        if (rc == kOk) rc = check_cuda(cudaStreamWaitEvent(run, g_arena.h2d_done[s], 0), "cudaStreamWaitEvent");
+        if (rc == kOk && i >= 2) rc = check_cuda(cudaStreamWaitEvent(run, g_arena.d2h_done[s], 0), "cudaStreamWaitEvent");
+        if (rc == kOk) {
+            rc = launch_gemm_f16f32(static_cast<const uint16_t *>(da[s]), static_cast<const uint16_t *>(db[s]),
+                                    static_cast<float *>(dc[s]), m, n, k, b_layout, run);
+        }
+        if (rc == kOk) rc = check_cuda(cudaEventRecord(g_arena.comp_done[s], run), "cudaEventRecord");
+        // copy out
+        if (rc == kOk) rc = check_cuda(cudaStreamWaitEvent(out, g_arena.comp_done[s], 0), "cudaStreamWaitEvent");
+        if (rc == kOk) rc = check_cuda(cudaMemcpyAsync(hc, dc[s], c_bytes, cudaMemcpyDeviceToHost, out), "D2H C");
+        if (rc == kOk) rc = check_cuda(cudaEventRecord(g_arena.d2h_done[s], out), "cudaEventRecord");
+    }
+    // drain all three streams even after an error so that no copy is left in flight on the caller's buffers
+    const int r0 = check_cuda(cudaStreamSynchronize(in), "cudaStreamSynchronize");
+    const int r1 = check_cuda(cudaStreamSynchronize(run), "cudaStreamSynchronize");
+    const int r2 = check_cuda(cudaStreamSynchronize(out), "cudaStreamSynchronize");
+    return rc != kOk ? rc : (r0 != kOk ? r0 : (r1 != kOk ? r1 : r2));
 }
 
 int pto_b200_gemm_f16f32_host_static(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout)

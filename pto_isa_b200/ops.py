@@ -361,6 +361,20 @@ def gemm_host(a, b, c, b_layout=1):
     return c
 
 
+def gemm_host_batched(a, b, c, b_layout=1):
+    """`batch` products over HOST tensors a (batch, m, k), b (batch, n, k) or (batch, k, n), c (batch, m, n): copies in,
+    kernels and copies out of consecutive problems overlap (pin the tensors for that)."""
+    if a.dim() != 3 or b.dim() != 3 or c.dim() != 3 or a.is_cuda or b.is_cuda or c.is_cuda:
+        raise PtoB200Error("gemm_host_batched: expects 3-D host tensors")
+    if not (a.is_contiguous() and b.is_contiguous() and c.is_contiguous()):
+        raise PtoB200Error("gemm_host_batched: operands must be contiguous")
+    batch, m, k = a.shape
+    n = b.shape[2] if b_layout == 0 else b.shape[1]
+    rc = lib().pto_b200_gemm_f16f32_host_batched(_ptr(a), _ptr(b), _ptr(c), m, n, k, int(b_layout), batch, m * k, n * k, m * n)
+    check(rc, "gemm_host_batched")
+    return c
+
+
 def flash_attn_fwd(q, k, v, causal=False, scale=None, out_dtype=torch.float16, out=None):
     """q: (..., sq, d), k / v: (..., sk, d) fp16 with the same leading (batch, heads) dims.  Returns O like q."""
     _need_cuda(q, k, v)

@@ -108,3 +108,21 @@ def test_gemm_full_size_sampled_tiles():
     want_rows = a.astype(np.float64) @ colsum_b
     got_rows = host(c.double().sum(dim=1))
     assert np.abs(got_rows - want_rows).max() <= 1e-3 * np.sqrt(n * k / 9.0)
+
+
+def test_host_batched_pipeline_equals_device_path():
+    """Pipelined host-buffer entry point: every problem of the batch (odd count: both staging sets, a tail) equals the
+    device-pointer entry point bit for bit; pinned and pageable host memory."""
+    g = torch.Generator().manual_seed(8)
+    batch, m, n, k = 5, 256, 384, 512
+    a = (torch.rand(batch, m, k, generator=g) * 2 - 1).half()
+    b = (torch.rand(batch, n, k, generator=g) * 2 - 1).half()
+    for pin in (False, True):
+        ha, hb = (a.pin_memory(), b.pin_memory()) if pin else (a, b)
+        hc = torch.zeros(batch, m, n)
+        hc = hc.pin_memory() if pin else hc
+        pto.gemm_host_batched(ha, hb, hc, 1)
+        for i in range(batch):
+            assert torch.equal(hc[i], pto.gemm(a[i].cuda(), b[i].cuda(), 1).cpu()), (pin, i)
+    assert pto.gemm_host_batched(a[:0], b[:0], torch.zeros(0, m, n), 1).shape[0] == 0
+    assert pto.device_status() == 0
