@@ -145,7 +145,7 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 template <bool kCausal, bool kOutF16, int kPolyOf8>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                      const __grid_constant__ CUtensorMap tmap_v, void *__restrict__ o_ptr, int sq, int sk,
+                      const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o, int sq, int sk,
                       float scale_log2, DeviceStatus *status)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -198,9 +198,28 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
         ctl->abort_flag = 0;
         fence_mbar_init();
-        tma_prefetch_desc(&tmap_q);
-        tma_prefetch_desc(&tmap_k);
+        // The first loads (both Q tiles and K(0), ring item 0) leave right here, before the tensor-memory allocation
+        // and the block-wide barrier: their latency is the start-up cost of every block.
+        {
+            int q_bytes = 0;
+            q_bytes += (n_kv0 > 0) ? kTileBytes : 0;
+            q_bytes += (n_kv1 > 0) ? kTileBytes : 0;
+            mbar_arrive_expect_tx(&ctl->q_full, q_bytes);
+            for (int t = 0; t < 2; ++t) {
+                if ((t == 0 ? n_kv0 : n_kv1) > 0) {
+                    const int q0 = (2 * qb + t) * kTileQ;
+                    tma_load_3d(smem_q + t * kTileBytes, &tmap_q, &ctl->q_full, 0, q0, bh);
+                    tma_load_3d(smem_q + t * kTileBytes + kHalfBytes, &tmap_q, &ctl->q_full, 64, q0, bh);
+                }
+            }
+            if (n_max > 0) {
+                mbar_arrive_expect_tx(&ctl->ring_full[0], kTileBytes);
+                tma_load_3d(smem_ring, &tmap_k, &ctl->ring_full[0], 0, 0, bh);
+                tma_load_3d(smem_ring + kHalfBytes, &tmap_k, &ctl->ring_full[0], 64, 0, bh);
+            }
+        }
         tma_prefetch_desc(&tmap_v);
+        tma_prefetch_desc(&tmap_o);
     }
     if (warp == 9) {
         tmem_alloc(&ctl->tmem_base, kTmemCols);
@@ -218,18 +237,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             // -------------------------------------------------------- TMA producer (TLOAD of Q, K, V)
             // ring items in consumption order: K(0), then for every step j: K(j+1) (if any), V(j)
             if (lane == 0) {
-                int q_bytes = 0;
-                q_bytes += (n_kv0 > 0) ? kTileBytes : 0;
-                q_bytes += (n_kv1 > 0) ? kTileBytes : 0;
-                mbar_arrive_expect_tx(&ctl->q_full, q_bytes);
-                for (int t = 0; t < 2; ++t) {
-                    if ((t == 0 ? n_kv0 : n_kv1) > 0) {
-                        const int q0 = (2 * qb + t) * kTileQ;
-                        tma_load_3d(smem_q + t * kTileBytes, &tmap_q, &ctl->q_full, 0, q0, bh);
-                        tma_load_3d(smem_q + t * kTileBytes + kHalfBytes, &tmap_q, &ctl->q_full, 64, q0, bh);
-                    }
-                }
-                int item = 0;
+                int item = 1; // item 0, K(0), was issued with the Q tiles before the block-wide barrier
                 bool ok = true;
                 auto load_item = [&](const CUtensorMap *map, int tile) {
                     const int s = item % kRing;
@@ -244,9 +252,6 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                     tma_load_3d(dst + kHalfBytes, map, &ctl->ring_full[s], 64, tile * kTileKV, bh);
                     ++item;
                 };
-                if (n_max > 0) {
-                    load_item(&tmap_k, 0);
-                }
                 for (int j = 0; j < n_max && ok; ++j) {
                     if (j + 1 < n_max) {
                         load_item(&tmap_k, j + 1);
@@ -487,36 +492,60 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             }
         }
 
-        // output: O / l
+        // output: O / l.  The rows go through shared memory - the P tile's buffer (free once the last product is
+        // complete) and, for fp32 output, the Q tile's buffer as well - in 128-byte-swizzled column groups, and each
+        // warp hands its 32 rows to TMA stores: full 128-byte lines instead of one row-strided 16-byte store per lane.
         if (ok && n > 0) {
             if (mbar_wait(&ctl->pv_done[t], (n - 1) & 1, abort_flag)) {
                 tc_fence_after();
                 const float inv_l = 1.0f / l_run;
-                const int64_t row_off = (static_cast<int64_t>(bh) * sq + q_row) * kD;
+                const uint32_t q_row_smem = smem_u32(smem_q) + t * kTileBytes + row_in_tile * 128;
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
                     uint32_t orow[32];
                     tmem_ld_32x32(o_addr + c * 32, orow);
                     tmem_ld_wait();
                     if (kOutF16) {
-                        uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__half *>(o_ptr) + row_off + c * 32);
+                        // 32 columns = four 16-byte chunks of the 64-column group c >> 1
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            uint4 v;
-                            v.x = pack_f16x2(__uint_as_float(orow[8 * i + 0]) * inv_l, __uint_as_float(orow[8 * i + 1]) * inv_l);
-                            v.y = pack_f16x2(__uint_as_float(orow[8 * i + 2]) * inv_l, __uint_as_float(orow[8 * i + 3]) * inv_l);
-                            v.z = pack_f16x2(__uint_as_float(orow[8 * i + 4]) * inv_l, __uint_as_float(orow[8 * i + 5]) * inv_l);
-                            v.w = pack_f16x2(__uint_as_float(orow[8 * i + 6]) * inv_l, __uint_as_float(orow[8 * i + 7]) * inv_l);
-                            dst[i] = v;
+                            const uint32_t chunk = static_cast<uint32_t>((c & 1) * 4 + i);
+                            st_shared_v4(p_row + (c >> 1) * kHalfBytes + ((chunk ^ swz) << 4),
+                                         pack_f16x2(__uint_as_float(orow[8 * i + 0]) * inv_l, __uint_as_float(orow[8 * i + 1]) * inv_l),
+                                         pack_f16x2(__uint_as_float(orow[8 * i + 2]) * inv_l, __uint_as_float(orow[8 * i + 3]) * inv_l),
+                                         pack_f16x2(__uint_as_float(orow[8 * i + 4]) * inv_l, __uint_as_float(orow[8 * i + 5]) * inv_l),
+                                         pack_f16x2(__uint_as_float(orow[8 * i + 6]) * inv_l, __uint_as_float(orow[8 * i + 7]) * inv_l));
                         }
                     } else {
-                        float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(o_ptr) + row_off + c * 32);
+                        // 32 columns = one 128-byte group: groups 0, 1 in P's buffer, 2, 3 in Q's
+                        const uint32_t base = ((c < 2) ? p_row : q_row_smem) + (c & 1) * kHalfBytes;
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
-                            dst[i] = make_float4(__uint_as_float(orow[4 * i + 0]) * inv_l, __uint_as_float(orow[4 * i + 1]) * inv_l,
-                                                 __uint_as_float(orow[4 * i + 2]) * inv_l, __uint_as_float(orow[4 * i + 3]) * inv_l);
+                            st_shared_v4(base + ((static_cast<uint32_t>(i) ^ swz) << 4),
+                                         __float_as_uint(__uint_as_float(orow[4 * i + 0]) * inv_l),
+                                         __float_as_uint(__uint_as_float(orow[4 * i + 1]) * inv_l),
+                                         __float_as_uint(__uint_as_float(orow[4 * i + 2]) * inv_l),
+                                         __float_as_uint(__uint_as_float(orow[4 * i + 3]) * inv_l));
                         }
                     }
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    const int row0 = (2 * qb + t) * kTileQ + quarter * 32; // this warp's 32 rows
+                    uint8_t *p_src = smem_p + t * kTileBytes + quarter * 32 * 128;
+                    uint8_t *q_src = smem_q + t * kTileBytes + quarter * 32 * 128;
+                    if (kOutF16) {
+                        tma_store_3d(&tmap_o, p_src, 0, row0, bh);
+                        tma_store_3d(&tmap_o, p_src + kHalfBytes, 64, row0, bh);
+                    } else {
+                        tma_store_3d(&tmap_o, p_src, 0, row0, bh);
+                        tma_store_3d(&tmap_o, p_src + kHalfBytes, 32, row0, bh);
+                        tma_store_3d(&tmap_o, q_src, 64, row0, bh);
+                        tma_store_3d(&tmap_o, q_src + kHalfBytes, 96, row0, bh);
+                    }
+                    tma_store_commit();
+                    tma_store_wait_all<0>(); // the buffers are read and O is written before the block retires
                 }
             }
         }
@@ -542,7 +571,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 }
 
 template <bool kCausal, bool kOutF16, int kPolyOf8>
-int launch_variant(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, void *o, int bh, int sq, int sk,
+int launch_variant(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const CUtensorMap &to, int bh, int sq, int sk,
                    float scale_log2, DeviceStatus *status, cudaStream_t stream)
 {
     static bool attr_set = false;
@@ -557,20 +586,20 @@ int launch_variant(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorM
     }
     const int q_blocks = (sq + 2 * kTileQ - 1) / (2 * kTileQ);
     flash_attn_fwd_kernel<kCausal, kOutF16, kPolyOf8>
-        <<<bh * q_blocks, kThreads, kSmemBytes, stream>>>(tq, tk, tv, o, sq, sk, scale_log2, status);
+        <<<bh * q_blocks, kThreads, kSmemBytes, stream>>>(tq, tk, tv, to, sq, sk, scale_log2, status);
     return check_launch();
 }
 
 template <int kPolyOf8>
-int launch_mode(bool causal, bool out_f16, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, void *o,
+int launch_mode(bool causal, bool out_f16, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const CUtensorMap &to,
                 int bh, int sq, int sk, float scale_log2, DeviceStatus *status, cudaStream_t stream)
 {
     if (causal) {
-        return out_f16 ? launch_variant<true, true, kPolyOf8>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream)
-                       : launch_variant<true, false, kPolyOf8>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
+        return out_f16 ? launch_variant<true, true, kPolyOf8>(tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream)
+                       : launch_variant<true, false, kPolyOf8>(tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream);
     }
-    return out_f16 ? launch_variant<false, true, kPolyOf8>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream)
-                   : launch_variant<false, false, kPolyOf8>(tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
+    return out_f16 ? launch_variant<false, true, kPolyOf8>(tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream)
+                   : launch_variant<false, false, kPolyOf8>(tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream);
 }
 
 } // namespace
@@ -591,13 +620,17 @@ int launch_flash_attn_fwd(const uint16_t *q, const uint16_t *k, const uint16_t *
         set_error_text("flash attention: operands must be 16-byte aligned");
         return kErrUnsupportedShape;
     }
-    CUtensorMap tq, tk, tv;
+    CUtensorMap tq, tk, tv, to;
     int rc = make_tmap_3d(&tq, q, 2, bh, sq, d, d, static_cast<uint64_t>(sq) * d, kTileQ, 64, true);
     if (rc == kOk) {
         rc = make_tmap_3d(&tk, k, 2, bh, sk, d, d, static_cast<uint64_t>(sk) * d, kTileKV, 64, true);
     }
     if (rc == kOk) {
         rc = make_tmap_3d(&tv, v, 2, bh, sk, d, d, static_cast<uint64_t>(sk) * d, kTileKV, 64, true);
+    }
+    if (rc == kOk) {
+        // O leaves in boxes of 32 rows x 128 bytes (64 fp16 or 32 fp32 columns), one set per softmax warp
+        rc = make_tmap_3d(&to, o, out_f16 ? 2 : 4, bh, sq, d, d, static_cast<uint64_t>(sq) * d, 32, out_f16 ? 64 : 32, true);
     }
     if (rc != kOk) {
         return rc;
@@ -614,11 +647,11 @@ int launch_flash_attn_fwd(const uint16_t *q, const uint16_t *k, const uint16_t *
         return e != nullptr ? atoi(e) : 1;
     }();
     switch (poly) {
-        case 0: return launch_mode<0>(causal != 0, out_f16 != 0, tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
-        case 2: return launch_mode<2>(causal != 0, out_f16 != 0, tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
-        case 3: return launch_mode<3>(causal != 0, out_f16 != 0, tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
-        case 4: return launch_mode<4>(causal != 0, out_f16 != 0, tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
-        default: return launch_mode<1>(causal != 0, out_f16 != 0, tq, tk, tv, o, bh, sq, sk, scale_log2, status, stream);
+        case 0: return launch_mode<0>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream);
+        case 2: return launch_mode<2>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream);
+        case 3: return launch_mode<3>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream);
+        case 4: return launch_mode<4>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream);
+        default: return launch_mode<1>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream);
     }
 }
 
