@@ -375,6 +375,156 @@ AICORE inline void ProgVector2(Vector2Out o, __gm__ float *a_in, __gm__ float *b
     store_w(o.cmp);
 }
 
+// ---------------------------------------------------------------- a multi-latent-attention head
+// The instruction sequence of the reference's MLA demo (demos/cpu/mla_attention_demo/mla_attention_demo.cpp:326-376:
+// latent projections, K_lat^T by TTRANS, scaled scores, row softmax, context, output projection) with fp16 matrix
+// operands: every accumulator goes Acc -> Vec (fp32, TMOV) -> fp16 (TCVT) -> Left / Right (TMOV).
+template <int S, int D, int R>
+AICORE inline void ProgMlaHead(__gm__ float *out, __gm__ half *q, __gm__ half *k, __gm__ half *v, __gm__ half *wq,
+                               __gm__ half *wk, __gm__ half *wv, __gm__ half *wo, float scale)
+{
+    using GSD = GlobalTensor<half, Shape<1, 1, 1, S, D>, Stride<S * D, S * D, S * D, D, 1>>;
+    using GDR = GlobalTensor<half, Shape<1, 1, 1, D, R>, Stride<D * R, D * R, D * R, R, 1>>;
+    using GRD = GlobalTensor<half, Shape<1, 1, 1, R, D>, Stride<R * D, R * D, R * D, D, 1>>;
+    using GO = GlobalTensor<float, Shape<1, 1, 1, S, D>, Stride<S * D, S * D, S * D, D, 1>>;
+    using SDh = Tile<TileType::Vec, half, S, D, BLayout::RowMajor>;
+    using DRh = Tile<TileType::Vec, half, D, R, BLayout::RowMajor>;
+    using RDh = Tile<TileType::Vec, half, R, D, BLayout::RowMajor>;
+    using SRh = Tile<TileType::Vec, half, S, R, BLayout::RowMajor>;
+    using RSh = Tile<TileType::Vec, half, R, S, BLayout::RowMajor>;
+    using SRf = Tile<TileType::Vec, float, S, R, BLayout::RowMajor>;
+    using SSf = Tile<TileType::Vec, float, S, S, BLayout::RowMajor>;
+    using SSh = Tile<TileType::Vec, half, S, S, BLayout::RowMajor>;
+    using RowRed = Tile<TileType::Vec, float, S, 1, BLayout::ColMajor>;
+    static_assert(S == 128 && D == 64 && R == 64, "the arena plan below is for S 128, D 64, R 64");
+
+    constexpr uint32_t K = 1024;
+    SDh qv, kv, vv;
+    DRh wqv, wkv, wvv;
+    RDh wov;
+    SRh qlat, klat, vlat, ctx16;
+    RSh klat_t;
+    SRf tmp32;
+    SSf scores;
+    SSh probs;
+    RowRed mx, sm;
+    TASSIGN(qv, 0);
+    TASSIGN(kv, 16 * K);
+    TASSIGN(vv, 32 * K);
+    TASSIGN(wqv, 48 * K);
+    TASSIGN(wkv, 56 * K);
+    TASSIGN(wvv, 64 * K);
+    TASSIGN(tmp32, 72 * K);   // 72..104 KiB
+    TASSIGN(qlat, 0);         // over Q once it sits in the Left window
+    TASSIGN(klat, 16 * K);    // over K
+    TASSIGN(vlat, 32 * K);    // over V
+    TASSIGN(klat_t, 48 * K);  // over Wq, Wk
+    TASSIGN(scores, 48 * K);  // 48..112 KiB, over K_lat^T, Wv and the fp32 scratch, all consumed by then
+    TASSIGN(probs, 0);        // 0..32 KiB, over Q_lat and K_lat
+    TASSIGN(ctx16, 80 * K);
+    TASSIGN(wov, 96 * K);
+    TASSIGN(mx, 114 * K);
+    TASSIGN(sm, 114 * K + S * 4);
+
+    TileLeft<half, S, D> l_sd;
+    TileLeft<half, S, R> l_sr;
+    TileLeft<half, S, S> l_ss;
+    TileRight<half, D, R> r_wq, r_wk, r_wv;
+    TileRight<half, R, D> r_wo;
+    TileRight<half, R, S> r_klat_t;
+    TileRight<half, S, R> r_vlat;
+    TileAcc<float, S, R> acc_sr;
+    TileAcc<float, S, S> acc_ss;
+    TileAcc<float, S, D> acc_sd;
+    TASSIGN(l_sd, 0x0);
+    TASSIGN(l_sr, 0x0);
+    TASSIGN(l_ss, 0x0);
+    TASSIGN(r_wq, 0);
+    TASSIGN(r_wk, 8 * K);
+    TASSIGN(r_wv, 16 * K);
+    TASSIGN(r_wo, 24 * K);
+    TASSIGN(r_klat_t, 32 * K);
+    TASSIGN(r_vlat, 48 * K);
+    TASSIGN(acc_sr, 0x0);
+    TASSIGN(acc_ss, R * 512);         // tensor-memory columns after the S x R accumulator
+    TASSIGN(acc_sd, (R + S) * 512);
+
+    GSD gq(q), gk(k), gv(v);
+    GDR gwq(wq), gwk(wk), gwv(wv);
+    GRD gwo(wo);
+    GO go(out);
+    TLOAD(qv, gq);
+    TLOAD(kv, gk);
+    TLOAD(vv, gv);
+    TLOAD(wqv, gwq);
+    TLOAD(wkv, gwk);
+    TLOAD(wvv, gwv);
+    set_flag(PIPE_MTE2, PIPE_MTE1, EVENT_ID0);
+    wait_flag(PIPE_MTE2, PIPE_MTE1, EVENT_ID0);
+    TMOV(r_wq, wqv);
+    TMOV(r_wk, wkv);
+    TMOV(r_wv, wvv);
+
+    // latent projections (S x D) * (D x R) -> (S x R), each brought back as an fp16 Vec tile
+    auto project = [&](SDh &x, TileRight<half, D, R> &w, SRh &dst, event_t ev) {
+        TMOV(l_sd, x);
+        set_flag(PIPE_MTE1, PIPE_M, ev);
+        wait_flag(PIPE_MTE1, PIPE_M, ev);
+        TMATMUL(acc_sr, l_sd, w);
+        set_flag(PIPE_M, PIPE_V, ev);
+        wait_flag(PIPE_M, PIPE_V, ev);
+        TMOV(tmp32, acc_sr);
+        TCVT(dst, tmp32, RoundMode::CAST_RINT);
+    };
+    project(qv, r_wq, qlat, EVENT_ID0);
+    project(kv, r_wk, klat, EVENT_ID1);
+    project(vv, r_wv, vlat, EVENT_ID2);
+
+    // scores = Q_lat * K_lat^T, the transpose made by TTRANS
+    TTRANS(klat_t, klat, klat);
+    TMOV(r_klat_t, klat_t);
+    TMOV(r_vlat, vlat);
+    TMOV(l_sr, qlat);
+    set_flag(PIPE_MTE1, PIPE_M, EVENT_ID3);
+    wait_flag(PIPE_MTE1, PIPE_M, EVENT_ID3);
+    TMATMUL(acc_ss, l_sr, r_klat_t);
+    set_flag(PIPE_M, PIPE_V, EVENT_ID3);
+    wait_flag(PIPE_M, PIPE_V, EVENT_ID3);
+    TMOV(scores, acc_ss);
+    TMULS(scores, scores, scale);
+
+    // row softmax
+    TROWMAX(mx, scores, scores);
+    TROWEXPANDSUB(scores, scores, mx);
+    TEXP(scores, scores);
+    TROWSUM(sm, scores, scores);
+    TROWEXPANDDIV(scores, scores, sm);
+    TCVT(probs, scores, RoundMode::CAST_RINT);
+
+    // context = P * V_lat, output = context * Wo
+    TMOV(l_ss, probs);
+    set_flag(PIPE_MTE1, PIPE_M, EVENT_ID4);
+    wait_flag(PIPE_MTE1, PIPE_M, EVENT_ID4);
+    TMATMUL(acc_sr, l_ss, r_vlat);
+    set_flag(PIPE_M, PIPE_V, EVENT_ID4);
+    wait_flag(PIPE_M, PIPE_V, EVENT_ID4);
+    SRf ctx32;
+    TASSIGN(ctx32, 48 * K); // the score tile is dead
+    TMOV(ctx32, acc_sr);
+    TCVT(ctx16, ctx32, RoundMode::CAST_RINT);
+    TLOAD(wov, gwo);
+    set_flag(PIPE_MTE2, PIPE_MTE1, EVENT_ID1);
+    wait_flag(PIPE_MTE2, PIPE_MTE1, EVENT_ID1);
+    TMOV(r_wo, wov);
+    TMOV(l_sr, ctx16);
+    set_flag(PIPE_MTE1, PIPE_M, EVENT_ID5);
+    wait_flag(PIPE_MTE1, PIPE_M, EVENT_ID5);
+    TMATMUL(acc_sd, l_sr, r_wo);
+    set_flag(PIPE_M, PIPE_FIX, EVENT_ID0);
+    wait_flag(PIPE_M, PIPE_FIX, EVENT_ID0);
+    TSTORE(go, acc_sd);
+}
+
 // ---------------------------------------------------------------- host entry points
 #pragma GCC visibility push(default)
 extern "C" {
@@ -466,6 +616,18 @@ int pto_prog_vector2_64x128(void *const *outs, const float *a, const float *b, c
     return pto::b200::launch(1, stream, [=] __device__() {
                ProgVector2(o, const_cast<float *>(a), const_cast<float *>(b), const_cast<float *>(s), valid_rows,
                            valid_cols);
+           }) == cudaSuccess
+               ? 0
+               : 3;
+}
+
+int pto_prog_mla_head_128x64x64(float *out, const __half *q, const __half *k, const __half *v, const __half *wq,
+                                const __half *wk, const __half *wv, const __half *wo, float scale, void *stream)
+{
+    auto c = [](const __half *p) { return const_cast<__half *>(p); };
+    __half *q_ = c(q), *k_ = c(k), *v_ = c(v), *wq_ = c(wq), *wk_ = c(wk), *wv_ = c(wv), *wo_ = c(wo);
+    return pto::b200::launch(1, stream, [=] __device__() {
+               ProgMlaHead<128, 64, 64>(out, q_, k_, v_, wq_, wk_, wv_, wo_, scale);
            }) == cudaSuccess
                ? 0
                : 3;

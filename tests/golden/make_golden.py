@@ -325,6 +325,28 @@ def gen_harness(ref, tmp, out):
                 f.write(text)
 
 
+def gen_mla(ref, tmp, out):
+    """One multi-latent-attention head (S 128, D 64, R 64, fp16 operands): seeded inputs and the output of the
+    reference's CPU simulation running the instruction sequence of demos/cpu/mla_attention_demo/mla_attention_demo.cpp:326-376
+    (oracle/ref_mla.cpp, compiled against the reference headers as oracle/_ref/libpto_ref.so)."""
+    import ctypes
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    import oracle
+    if oracle.ref is None:
+        raise SystemExit("oracle/_ref/libpto_ref.so is needed for the MLA fixture")
+    r = np.random.default_rng(20260)
+    S, D, R = 128, 64, 64
+    q, k, v = (r.standard_normal((S, D)).astype(np.float16) for _ in range(3))
+    wq, wk, wv = ((r.standard_normal((D, R)) / np.sqrt(D)).astype(np.float16) for _ in range(3))
+    wo = (r.standard_normal((R, D)) / np.sqrt(R)).astype(np.float16)
+    o = np.zeros((S, D), np.float32)
+    P = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    scale = 1.0 / np.sqrt(R)
+    rc = oracle.ref.lib.pto_ref_mla_head_f16_128x64x64(P(q), P(k), P(v), P(wq), P(wk), P(wv), P(wo), P(o), ctypes.c_float(scale))
+    assert rc == 0
+    np.savez_compressed(os.path.join(out, "mla.npz"), q=q, k=k, v=v, wq=wq, wk=wk, wv=wv, wo=wo, o=o, scale=np.float32(scale))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -332,7 +354,7 @@ def main():
     cwd = os.getcwd()
     with tempfile.TemporaryDirectory() as tmp:
         try:
-            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm, gen_vector2, gen_harness):
+            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm, gen_vector2, gen_harness, gen_mla):
                 os.chdir(tmp)
                 fn(args.reference, tmp, HERE)
         finally:

@@ -82,16 +82,17 @@ def test_gemm_batched_and_linearity():
     assert np.array_equal(c2, 2 * c[0])
 
 
-def test_gemm_full_size_sampled_tiles():
-    """6144^3 (the headline size): the whole product runs on the GPU; sampled 128 x 256 C tiles are
-    recomputed by the oracle at full K, and a row/column checksum identity is checked on everything."""
-    m = n = k = 6144
-    a, b = make(m, n, k, 1, seed=6144)
+@pytest.mark.parametrize("size", [3072, 6144, 7680])
+def test_gemm_full_size_sampled_tiles(size):
+    """The square sweep (6144^3 is the headline size): the whole product runs on the GPU; sampled 128 x 256 C tiles
+    are recomputed by the oracle at full K, and a row/column checksum identity is checked on everything."""
+    m = n = k = size
+    a, b = make(m, n, k, 1, seed=size)
     da, db = dev(a), dev(b)
     c = pto.gemm(da, db, 1)
     assert pto.device_status() == 0
     r = np.random.default_rng(0)
-    for _ in range(6):
+    for _ in range(4):
         ti, tj = int(r.integers(0, m // 128)), int(r.integers(0, n // 256))
         r0, c0 = ti * 128, tj * 256
         want = np.zeros((128, 256), np.float32)

@@ -154,3 +154,26 @@ def test_vector2_program(prog, valid):
     assert np.all(np.abs(got - want) <= 1)
     assert np.array_equal(u32(host(outs["expand"])), u32(port.trowexpand_f32(a, s, 7)))
     assert np.array_equal(host(outs["cmp"]), port.tcmp_f32(a, b, 2))
+
+
+def test_mla_head_program(prog, golden_dir):
+    """The instruction sequence of the reference's multi-latent-attention demo (latent projections, TTRANS of K_lat,
+    scaled scores, row softmax, context, output projection) on the GPU against the same sequence run by the
+    reference's CPU simulation (tests/golden/mla.npz).  Five chained fp16 products with fp16 hand-offs: tolerance 2e-3
+    of max(|x|, rms), as for the GEMM and attention."""
+    import os
+    z = np.load(os.path.join(golden_dir, "mla.npz"))
+    out = torch.zeros(128, 64, device="cuda")
+    h = lambda name: dev(z[name].view(np.int16))
+    ops = [h(n) for n in ("q", "k", "v", "wq", "wk", "wv", "wo")]
+    rc = prog.pto_prog_mla_head_128x64x64(_ptr(out), *[_ptr(t) for t in ops], ctypes.c_float(float(z["scale"])), _stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    ok, worst = rel_err_ok(host(out), z["o"], 2e-3)
+    assert ok, worst
+    if oracle.ref is not None:  # the reference build itself, when it travelled along
+        P = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+        o2 = np.zeros((128, 64), np.float32)
+        arrs = [np.ascontiguousarray(z[n]) for n in ("q", "k", "v", "wq", "wk", "wv", "wo")]
+        assert oracle.ref.lib.pto_ref_mla_head_f16_128x64x64(*[P(a) for a in arrs], P(o2), ctypes.c_float(float(z["scale"]))) == 0
+        assert np.array_equal(o2, z["o"])
