@@ -125,3 +125,29 @@ def test_attention_full_size_sampled_heads(causal):
     of = o.float()
     assert bool((of <= vmax + 2e-3 * vmax.abs() + 1e-3).all()) and bool((of >= vmin - 2e-3 * vmin.abs() - 1e-3).all())
     assert bool(torch.isfinite(of).all())
+
+
+def test_attention_long_sequence_causal_sampled_rows():
+    """S = 8192, causal (the sequence length of the multi-GPU sharding configuration), 6 heads: the last 128 queries
+    (they see all 8192 keys, 64 key tiles) and the first 256 of two heads are recomputed by the oracle, which is
+    given the same rows as a rectangular problem (s0 rows against the keys they may see)."""
+    bh, s, d = 6, 8192, 128
+    g = torch.Generator(device="cuda").manual_seed(8192)
+    q = (torch.randn(bh, s, d, device="cuda", generator=g) / d ** 0.5).half()
+    k = torch.randn(bh, s, d, device="cuda", generator=g).half()
+    v = torch.randn(bh, s, d, device="cuda", generator=g).half()
+    o = pto.flash_attn_fwd(q, k, v, causal=True, scale=1.0, out_dtype=torch.float32)
+    assert pto.device_status() == 0
+    for h in (0, 5):
+        # first 256 queries: a square causal problem of its own
+        want = port.attn_head_f16(host(q[h, :256]), host(k[h, :256]), host(v[h, :256]), 1, 1.0)
+        ok, worst, _ = attn_err_ok(host(o[h, :256]), want)
+        assert ok, f"head {h} first rows: max relative error {worst:.3e}"
+        # last 128 queries against all keys: row i of the block may see keys 0 .. s - 128 + i; the oracle's causal mask
+        # works on square problems, so every row is checked as the last row of the problem made of keys 0 .. its own
+        for row in (s - 128, s - 65, s - 1):
+            qi = host(q[h, row:row + 1]).repeat(128, axis=0)  # 128 copies: the oracle's tile height
+            want_row = port.attn_head_f16(qi, host(k[h, :row + 1]), host(v[h, :row + 1]), 0, 1.0)[0]
+            got_row = host(o[h, row])
+            assert np.abs(got_row - want_row).max() <= 3e-3 * max(np.abs(want_row).max(), 1e-3), (h, row)
+    assert bool(torch.isfinite(o).all())
