@@ -207,7 +207,10 @@ int grid_for(int64_t work_items, int items_per_block)
     int64_t blocks = (work_items + items_per_block - 1) / items_per_block;
     const int64_t cap = static_cast<int64_t>(sm_count()) * 32; // grid-stride beyond this
     if (blocks > cap) {
-        blocks = cap;
+        // every block makes the same number of passes (the last one possibly short): a grid of exactly `cap` blocks
+        // would leave some blocks with one pass more than others and a tail in which most of the GPU idles
+        const int64_t passes = (blocks + cap - 1) / cap;
+        blocks = (blocks + passes - 1) / passes;
     }
     if (blocks < 1) {
         blocks = 1;

@@ -262,8 +262,8 @@ def _pad_bits(dtype, pad):
     if pad == PAD_ZERO:
         return 0
     if dtype.is_floating_point:
-        inf = torch.tensor([float("inf") if pad == PAD_MAX else float("-inf")], dtype=dtype)
-        return int(inf.view(torch.int32 if dtype.itemsize == 4 else torch.int16).item()) & (0xffffffff if dtype.itemsize == 4 else 0xffff)
+        bits = {torch.float32: 0x7f800000, torch.float16: 0x7c00, torch.bfloat16: 0x7f80}[dtype]  # +infinity
+        return bits | ((0x80000000 if dtype.itemsize == 4 else 0x8000) if pad == PAD_MIN else 0)
     info = torch.iinfo(dtype)
     return int(info.max if pad == PAD_MAX else info.min) & (0xffffffff if dtype.itemsize == 4 else 0xffff)
 
