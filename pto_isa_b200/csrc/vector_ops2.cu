@@ -337,6 +337,46 @@ __global__ void __launch_bounds__(256) ttrans_kernel(const T *__restrict__ src, 
     }
 }
 
+// 4-byte elements, rows and cols multiples of 4, 16-byte aligned operands: 64 x 64 tiles, every thread moves a 4 x 4
+// block.  It loads four 16-byte row pieces (256-byte row segments per half warp, 16 KB in flight per block),
+// transposes the block in registers, writes the four transposed pieces into shared memory whose 16-byte chunks are
+// XOR-swizzled by (row / 4) % 8 - the stores of a quarter warp go to rows 4 apart, the loads to one row, both hit eight
+// different bank groups - and stores 16-byte pieces of the transposed rows, again 256-byte segments.
+__global__ void __launch_bounds__(256) ttrans4_vec_kernel(const float *__restrict__ src, float *__restrict__ dst,
+                                                          int rows, int cols)
+{
+    __shared__ float4 tile[64][16]; // [transposed row][swizzled chunk]
+    const int cg = threadIdx.x & 15, rg = threadIdx.x >> 4; // column group / row group of the 4 x 4 block
+    const int tiles_c = (cols + 63) / 64;
+    const int tiles_r = (rows + 63) / 64;
+    for (int64_t t = blockIdx.x; t < static_cast<int64_t>(tiles_r) * tiles_c; t += gridDim.x) {
+        const int r0 = static_cast<int>(t / tiles_c) * 64, c0 = static_cast<int>(t % tiles_c) * 64;
+        const int r = r0 + 4 * rg, c = c0 + 4 * cg;
+        float4 in[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            in[j] = (r + j < rows && c < cols)
+                        ? ld_stream_f4(reinterpret_cast<const float4 *>(src + static_cast<int64_t>(r + j) * cols + c))
+                        : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+        tile[4 * cg + 0][rg ^ (cg & 7)] = make_float4(in[0].x, in[1].x, in[2].x, in[3].x);
+        tile[4 * cg + 1][rg ^ (cg & 7)] = make_float4(in[0].y, in[1].y, in[2].y, in[3].y);
+        tile[4 * cg + 2][rg ^ (cg & 7)] = make_float4(in[0].z, in[1].z, in[2].z, in[3].z);
+        tile[4 * cg + 3][rg ^ (cg & 7)] = make_float4(in[0].w, in[1].w, in[2].w, in[3].w);
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int tr = rg + 16 * j;                   // transposed row inside the tile = source column
+            const int out_r = c0 + tr, out_c = r0 + 4 * cg; // dst[out_r, out_c .. out_c + 3]
+            if (out_r < cols && out_c < rows) {
+                st_stream_f4(reinterpret_cast<float4 *>(dst + static_cast<int64_t>(out_r) * rows + out_c),
+                             tile[tr][cg ^ ((tr >> 2) & 7)]);
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // ---------------------------------------------------------------- TSEL: one mask byte (8 elements) per thread
 template <typename T>
 __global__ void __launch_bounds__(kThreads) tsel_kernel(const uint8_t *__restrict__ mask, const T *__restrict__ a,
@@ -582,7 +622,12 @@ int launch_ttrans(const void *src, void *dst, int rows, int cols, int elem_bytes
     const int64_t tiles = static_cast<int64_t>((rows + tile - 1) / tile) * ((cols + tile - 1) / tile);
     const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
     const int grid = static_cast<int>(tiles < cap ? tiles : cap);
-    if (elem_bytes == 4) {
+    if (elem_bytes == 4 && (rows & 3) == 0 && (cols & 3) == 0 && aligned16(src) && aligned16(dst)) {
+        const int64_t tiles64 = static_cast<int64_t>((rows + 63) / 64) * ((cols + 63) / 64);
+        const int64_t cap64 = static_cast<int64_t>(sm_count()) * 8;
+        ttrans4_vec_kernel<<<static_cast<int>(tiles64 < cap64 ? tiles64 : cap64), 256, 0, stream>>>(
+            static_cast<const float *>(src), static_cast<float *>(dst), rows, cols);
+    } else if (elem_bytes == 4) {
         ttrans_kernel<uint32_t><<<grid, 256, 0, stream>>>(static_cast<const uint32_t *>(src), static_cast<uint32_t *>(dst),
                                                           rows, cols);
     } else {

@@ -143,6 +143,16 @@ def test_goldens_of_the_reference_generators(golden_dir):
     assert np.array_equal(host(pto.TCMP(cuda(z["tcmp_a"]), cuda(z["tcmp_b"]), 0)), z["tcmp_golden"])
 
 
+@pytest.mark.parametrize("rows,cols", [(4, 4), (64, 64), (68, 132), (1024, 192), (260, 64), (8, 4100)])
+def test_ttrans_vector_path_shapes(rows, cols):
+    """Shapes the 16-byte path takes (rows and cols multiples of 4), with partial 64 x 64 edge tiles."""
+    a = np.arange(rows * cols, dtype=np.float32).reshape(rows, cols)
+    guard = torch.full((cols + 1, rows), -1.0, device="cuda")
+    pto.TTRANS(cuda(a), out=guard[:cols])
+    got = host(guard)
+    assert np.array_equal(got[:cols], port.ttrans(a)) and (got[cols] == -1.0).all()
+
+
 def test_full_size_properties():
     """4096 x 4096 (the vector-op config's 16 M elements): identities that need no CPU pass."""
     g = torch.Generator(device="cuda").manual_seed(11)
