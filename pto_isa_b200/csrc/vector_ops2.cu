@@ -183,11 +183,12 @@ __global__ void __launch_bounds__(kColWarps * 32) tcolreduce_kernel(const float 
 }
 
 // Two-pass form for large tiles (needs a caller-provided workspace of segments * cols floats): the rows are cut
-// into segments so that strips x segments blocks fill the GPU; a block of 8 warps reduces 128 columns (one 512-byte
+// into segments so that strips x segments blocks fill the GPU in one wave; a block of 8 warps reduces 128 columns (one 512-byte
 // row piece per warp load, four in flight) of one segment and writes a partial row, the second pass combines the
 // segments top to bottom.  Deterministic; the sum's order is fixed but not the reference's.
 constexpr int kSegWarps = 8;
 constexpr int kSegUnroll = 4;
+constexpr int kSegBlocksPerSm = 6; // 40 registers x 256 threads: six blocks fit the register file, not eight
 
 template <int kOp>
 __device__ __forceinline__ float4 col_op4(float4 a, float4 b)
@@ -196,11 +197,14 @@ __device__ __forceinline__ float4 col_op4(float4 a, float4 b)
 }
 
 template <int kOp>
-__global__ void __launch_bounds__(kSegWarps * 32) tcolreduce_seg_kernel(const float *__restrict__ src,
+__global__ void __launch_bounds__(kSegWarps * 32, kSegBlocksPerSm) tcolreduce_seg_kernel(const float *__restrict__ src,
                                                                          float *__restrict__ partial, int rows, int cols,
                                                                          int64_t row_stride, int rows_per_seg)
 {
     __shared__ float4 part[kSegWarps][32];
+    // the second pass may be scheduled as soon as this grid's blocks are all resident; it waits for this grid's
+    // completion (and its writes) before it reads a partial
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float id1 = kOp == 0 ? 0.0f : (kOp == 4 ? -INFINITY : INFINITY);
     const float4 ident = make_float4(id1, id1, id1, id1);
@@ -248,6 +252,7 @@ __global__ void __launch_bounds__(kThreads) tcolreduce_final_kernel(const float 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c = blockIdx.x * 32 + lane;
     float t = kOp == 0 ? 0.0f : (kOp == 4 ? -INFINITY : INFINITY);
+    asm volatile("griddepcontrol.wait;" ::: "memory"); // first pass complete and visible (no-op in a plain launch)
     if (c < cols) {
 #pragma unroll 4
         for (int sgm = warp; sgm < segments; sgm += kThreads / 32) {
@@ -528,7 +533,7 @@ int tcolreduce_segments(int rows, int cols)
         return 1;
     }
     const int strips = (cols + 127) / 128;
-    int segs = (8 * sm_count() + strips - 1) / strips;
+    int segs = kSegBlocksPerSm * sm_count() / strips; // rounded down: all blocks resident at once, no second wave
     const int max_segs = rows / 64; // at least 64 rows per segment
     if (segs > max_segs) {
         segs = max_segs;
@@ -550,20 +555,37 @@ int launch_tcolreduce(const float *src, float *dst, int rows, int cols, int64_t 
         const int rows_per_seg = (rows + segs - 1) / segs;
         const dim3 grid((cols + 127) / 128, segs);
         const int fgrid = (cols + 31) / 32;
+        // the second pass is launched with programmatic stream serialization: its blocks are scheduled while the
+        // first pass drains and wait on the device for its completion, which hides the launch latency between the two
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(fgrid);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = stream;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        const float *partial = workspace;
+        cudaError_t err = cudaSuccess;
         switch (op) {
             case 0:
                 tcolreduce_seg_kernel<0><<<grid, kSegWarps * 32, 0, stream>>>(src, workspace, rows, cols, row_stride, rows_per_seg);
-                tcolreduce_final_kernel<0><<<fgrid, kThreads, 0, stream>>>(workspace, dst, cols, segs);
+                err = cudaLaunchKernelEx(&cfg, tcolreduce_final_kernel<0>, partial, dst, cols, segs);
                 break;
             case 4:
                 tcolreduce_seg_kernel<4><<<grid, kSegWarps * 32, 0, stream>>>(src, workspace, rows, cols, row_stride, rows_per_seg);
-                tcolreduce_final_kernel<4><<<fgrid, kThreads, 0, stream>>>(workspace, dst, cols, segs);
+                err = cudaLaunchKernelEx(&cfg, tcolreduce_final_kernel<4>, partial, dst, cols, segs);
                 break;
             case 5:
                 tcolreduce_seg_kernel<5><<<grid, kSegWarps * 32, 0, stream>>>(src, workspace, rows, cols, row_stride, rows_per_seg);
-                tcolreduce_final_kernel<5><<<fgrid, kThreads, 0, stream>>>(workspace, dst, cols, segs);
+                err = cudaLaunchKernelEx(&cfg, tcolreduce_final_kernel<5>, partial, dst, cols, segs);
                 break;
             default: return kErrBadArgument;
+        }
+        if (err != cudaSuccess) {
+            return check_cuda(err, "cudaLaunchKernelEx");
         }
         return check_launch();
     }
