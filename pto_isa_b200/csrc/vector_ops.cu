@@ -22,6 +22,7 @@ namespace pto_b200 {
 namespace {
 
 constexpr int kThreads = 256;
+constexpr int kRowWarps = 4; // rows (one warp each) per block of the row reductions
 
 // ---------------------------------------------------------------- TCVT
 
@@ -201,7 +202,7 @@ template <bool kIsMax>
 __global__ void __launch_bounds__(kThreads) trow_reduce_kernel(const float *__restrict__ src, float *__restrict__ dst,
                                                                int rows, int cols, int64_t row_stride)
 {
-    const int warps_per_block = kThreads / 32;
+    const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
         const float *p = src + static_cast<int64_t>(row) * row_stride;
@@ -401,11 +402,12 @@ int launch_trow_reduce(const float *src, float *dst, int rows, int cols, int64_t
     if (rows == 0) {
         return kOk;
     }
-    const int grid = grid_for(rows, kThreads / 32);
+    // four rows (warps) per block: with eight, 4096 rows make 512 blocks = 3.5 per SM, a 4-against-3 imbalance
+    const int grid = grid_for(rows, kRowWarps);
     if (is_max) {
-        trow_reduce_kernel<true><<<grid, kThreads, 0, stream>>>(src, dst, rows, cols, row_stride);
+        trow_reduce_kernel<true><<<grid, kRowWarps * 32, 0, stream>>>(src, dst, rows, cols, row_stride);
     } else {
-        trow_reduce_kernel<false><<<grid, kThreads, 0, stream>>>(src, dst, rows, cols, row_stride);
+        trow_reduce_kernel<false><<<grid, kRowWarps * 32, 0, stream>>>(src, dst, rows, cols, row_stride);
     }
     return check_launch();
 }

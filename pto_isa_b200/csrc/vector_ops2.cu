@@ -18,6 +18,7 @@ namespace pto_b200 {
 namespace {
 
 constexpr int kThreads = 256;
+constexpr int kRowWarps = 4; // rows (one warp each) per block of the row reductions
 
 bool aligned16(const void *p)
 {
@@ -88,7 +89,7 @@ __global__ void __launch_bounds__(kThreads) trowexpand_kernel(const float *__res
 __global__ void __launch_bounds__(kThreads) trowmin_kernel(const float *__restrict__ src, float *__restrict__ dst, int rows,
                                                            int cols, int64_t row_stride)
 {
-    const int warps_per_block = kThreads / 32;
+    const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
         const float *p = src + static_cast<int64_t>(row) * row_stride;
@@ -522,7 +523,7 @@ int launch_trowmin(const float *src, float *dst, int rows, int cols, int64_t row
     if (rows == 0) {
         return kOk;
     }
-    trowmin_kernel<<<grid_for(rows, kThreads / 32), kThreads, 0, stream>>>(src, dst, rows, cols, row_stride);
+    trowmin_kernel<<<grid_for(rows, kRowWarps), kRowWarps * 32, 0, stream>>>(src, dst, rows, cols, row_stride);
     return check_launch();
 }
 
