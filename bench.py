@@ -323,6 +323,30 @@ def extras(torch, pto, peaks, peak_kind):
                                  "frac": tf / peaks["bf16_tflops"], "peak_kind": peak_kind + " burst",
                                  "frac_of_nominal_2250": tf / 2250.0}})
     del q, k, v, o
+    # MX block-scaled fp8 GEMM at the reference's MxMatmul configuration (6144^3, float8_e5m2 operands, e8m0 scales per
+    # 32 k, bfloat16 output); four operand sets in rotation (4 x 75 MB of fp8 > L2); scale packing is inside the timing
+    mm = 6144
+    sets_mx = 4
+    mxa = [torch.randint(0, 256, (mm, mm), device="cuda", dtype=torch.uint8, generator=g) & 0x7b | 0x30 for _ in range(sets_mx)]
+    mxb = [torch.randint(0, 256, (mm, mm), device="cuda", dtype=torch.uint8, generator=g) & 0xfb | 0x30 for _ in range(sets_mx)]
+    mxsa = [torch.randint(127, 130, (mm, mm // 32), device="cuda", dtype=torch.uint8, generator=g) for _ in range(sets_mx)]
+    mxsb = [torch.randint(127, 130, (mm, mm // 32), device="cuda", dtype=torch.uint8, generator=g) for _ in range(sets_mx)]
+    mxc = torch.empty(mm, mm, device="cuda", dtype=torch.bfloat16)
+    mx_i = [0]
+
+    def mx_step():
+        j = mx_i[0] % sets_mx
+        mx_i[0] += 1
+        pto.mx_gemm(mxa[j], mxb[j], mxsa[j], mxsb[j], torch.bfloat16, out=mxc, fmt=pto.ops.FP8_E5M2)
+
+    ms = bench(mx_step, 4, 20)
+    tf = 2.0 * mm ** 3 / ms / 1e9
+    out.append({"workload": "MX fp8 GEMM (e5m2 x e5m2, e8m0 scales per 32 k, bf16 out) 6144^3", "value": tf,
+                "unit": "TFLOP/s", "ms": ms,
+                "roofline": {"bound": "tensor", "achieved": tf, "peak": 4500.0, "unit": "TFLOP/s", "frac": tf / 4500.0,
+                             "peak_kind": "nominal dense fp8 (no fp8 peak was measured on this pool)",
+                             "vs_measured_bf16_burst": tf / peaks["bf16_tflops"]}})
+    del mxa, mxb, mxsa, mxsb, mxc
     n = 1 << 24
     sets = 6
     xs = [torch.randn(n, device="cuda", generator=g) for _ in range(sets)]

@@ -158,6 +158,19 @@ int pto_b200_tcmp_f32(const float *a, const float *b, float *dst, int64_t n, int
  * (k a multiple of 8; n a multiple of 8 when b_layout is 0). */
 int pto_b200_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
                          void *stream);
+/* MX block-scaled fp8 GEMM: C[m x n] = (scale_a (x) A) * (scale_b (x) B)^T, the MxMatmul of
+ * kernels/manual/a5/matmul_mxfp8_performance (README.md "C = (scaleA (x) A) * (scaleB (x) B)"; kernel entry
+ * LaunchMxMatmul, mxmatmul_performance_kernel.cpp; instruction TMATMUL_MX, include/pto/common/pto_instr.hpp:403-460).
+ * A is m x k and B is n x k (the reference's transposed second operand), both fp8: format 0 = float8_e4m3fn,
+ * 1 = float8_e5m2.  scale_a is m x (k / 32) and scale_b is n x (k / 32) float8_e8m0 bytes (value 2^(byte - 127)), one
+ * per 32 consecutive k of a row, row-major - the files x1_scale_gm.bin / x2_scale_gm.bin of scripts/gen_data.py:56-64.
+ * C is bfloat16 (out_f32 0, the reference's output type) or float (1); products are accumulated in fp32.
+ * k must be a multiple of 32.  `workspace` (device memory, 128-byte aligned, pto_b200_mxgemm_workspace_bytes(m, n, k)
+ * bytes) receives the scales rearranged for the tensor core; it can be reused by the next call on the same stream. */
+int64_t pto_b200_mxgemm_workspace_bytes(int m, int n, int k);
+int pto_b200_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *scale_a, const uint8_t *scale_b, void *c, int m,
+                        int n, int k, int a_format, int b_format, int out_f32, void *workspace, int64_t workspace_bytes,
+                        void *stream);
 /* `batch` independent problems of the same shape, operands `*_stride` elements apart. */
 int pto_b200_gemm_f16f32_batched(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
                                  int batch, int64_t a_stride, int64_t b_stride, int64_t c_stride, void *stream);

@@ -221,6 +221,22 @@ class _Lib:
         assert rc == 0
         return c[r0:r1, c0:c1].copy()
 
+    # -- MX block-scaled fp8 GEMM
+    def mxgemm_fp8(self, a, b, sfa, sfb, a_fmt=1, b_fmt=1, window=None):
+        """a: (m,k), b: (n,k) fp8 bytes; sfa: (m,k/32), sfb: (n,k/32) e8m0 bytes.  Returns the exact sums as fp32 (m,n);
+        with window=(r0, r1, c0, c1) only that part of C is computed (the rest stays 0)."""
+        a, b = np.ascontiguousarray(a, np.uint8), np.ascontiguousarray(b, np.uint8)
+        sfa, sfb = np.ascontiguousarray(sfa, np.uint8), np.ascontiguousarray(sfb, np.uint8)
+        (m, k), n = a.shape, b.shape[0]
+        assert b.shape[1] == k and sfa.shape == (m, k // 32) and sfb.shape == (n, k // 32)
+        r0, r1, c0, c1 = window if window is not None else (0, m, 0, n)
+        c = np.zeros((m, n), np.float32)
+        rc = self._f("mxgemm_fp8_window")(_p(a), _p(b), _p(sfa), _p(sfb), _p(c), m, n, k, int(a_fmt), int(b_fmt), r0, r1,
+                                          c0, c1)
+        if rc != 0:
+            raise ValueError("mxgemm: unsupported shape or format")
+        return c
+
     # -- attention (one head)
     def attn_head_f16(self, q, k, v, causal, scale):
         q = np.ascontiguousarray(q, np.float16)

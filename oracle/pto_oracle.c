@@ -411,6 +411,78 @@ int pto_oracle_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m
     return pto_oracle_gemm_f16f32_window(a, b, c, m, n, k, b_layout, 0, m, 0, n);
 }
 
+/* ------------------------------------------------------------------ MX block-scaled fp8 GEMM
+ * C = (scaleA (x) A) * (scaleB (x) B)^T as kernels/manual/a5/matmul_mxfp8_performance/scripts/gen_data.py:27-52
+ * computes its golden: every fp8 element is multiplied by 2^(scale byte - 127) of its 32-element k block, the
+ * products are summed (here exactly, in double) and the sum is returned as float; the caller rounds to bfloat16.
+ * a: m x k, b: n x k fp8 bytes (format 0 = float8_e4m3fn, 1 = float8_e5m2); sfa: m x k/32, sfb: n x k/32 e8m0. */
+static double fp8_value(uint8_t v, int fmt)
+{
+    int sign = v >> 7;
+    double r;
+    if (fmt == 1) { /* e5m2: the upper byte of an IEEE half */
+        r = (double)half_to_f32((uint16_t)((uint16_t)v << 8));
+        return r;
+    }
+    int e = (v >> 3) & 15, mnt = v & 7;
+    if (e == 15 && mnt == 7) {
+        return NAN; /* e4m3fn: the only non-finite code */
+    }
+    r = e == 0 ? ldexp((double)mnt, -9) : ldexp((double)(8 + mnt), e - 10);
+    return sign ? -r : r;
+}
+
+typedef struct {
+    const uint8_t *a, *b, *sfa, *sfb;
+    float *c;
+    int m, n, k, c0, c1;
+    const double *lut_a, *lut_b;
+} mx_ctx;
+
+static void mx_rows(int64_t begin, int64_t end, void *ctx)
+{
+    const mx_ctx *g = (const mx_ctx *)ctx;
+    int ks = g->k / 32;
+    for (int64_t i = begin; i < end; ++i) {
+        for (int j = g->c0; j < g->c1; ++j) {
+            double sum = 0.0;
+            for (int blk = 0; blk < ks; ++blk) {
+                double part = 0.0;
+                const uint8_t *pa = g->a + i * g->k + blk * 32, *pb = g->b + (int64_t)j * g->k + blk * 32;
+                for (int t = 0; t < 32; ++t) {
+                    part += g->lut_a[pa[t]] * g->lut_b[pb[t]];
+                }
+                int ea = g->sfa[i * ks + blk], eb = g->sfb[(int64_t)j * ks + blk];
+                sum += (ea == 255 || eb == 255) ? NAN : ldexp(part, ea + eb - 254);
+            }
+            g->c[i * g->n + j] = (float)sum;
+        }
+    }
+}
+
+int pto_oracle_mxgemm_fp8_window(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, const uint8_t *sfb, float *c, int m,
+                                 int n, int k, int a_fmt, int b_fmt, int r0, int r1, int c0, int c1)
+{
+    if (k % 32 || a_fmt < 0 || a_fmt > 1 || b_fmt < 0 || b_fmt > 1 || r0 < 0 || r1 > m || c0 < 0 || c1 > n) {
+        return -1;
+    }
+    double lut[2][256];
+    for (int f = 0; f < 2; ++f) {
+        for (int v = 0; v < 256; ++v) {
+            lut[f][v] = fp8_value((uint8_t)v, f);
+        }
+    }
+    mx_ctx g = {a, b, sfa, sfb, c, m, n, k, c0, c1, lut[a_fmt], lut[b_fmt]};
+    parallel_range(r0, r1, mx_rows, &g);
+    return 0;
+}
+
+int pto_oracle_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, const uint8_t *sfb, float *c, int m, int n,
+                          int k, int a_fmt, int b_fmt)
+{
+    return pto_oracle_mxgemm_fp8_window(a, b, sfa, sfb, c, m, n, k, a_fmt, b_fmt, 0, m, 0, n);
+}
+
 /* Single TMATMUL over the whole k extent (no k stepping): tests/cpu/st/testcase/tmatmul cases. */
 int pto_oracle_tmatmul_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int k, int n)
 {

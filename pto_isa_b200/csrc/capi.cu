@@ -303,6 +303,35 @@ int pto_b200_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, 
     return launch_gemm_f16f32(a, b, c, m, n, k, b_layout, as_stream(stream));
 }
 
+int64_t pto_b200_mxgemm_workspace_bytes(int m, int n, int k)
+{
+    if (m <= 0 || n <= 0 || k <= 0) {
+        return 0;
+    }
+    return static_cast<int64_t>(mxgemm_workspace_bytes(m, n, k));
+}
+
+int pto_b200_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *scale_a, const uint8_t *scale_b, void *c, int m,
+                        int n, int k, int a_format, int b_format, int out_f32, void *workspace, int64_t workspace_bytes,
+                        void *stream)
+{
+    if (a == nullptr || b == nullptr || scale_a == nullptr || scale_b == nullptr || c == nullptr || m <= 0 || n <= 0 ||
+        k <= 0) {
+        return bad("mxgemm: bad argument");
+    }
+    if ((k % 32) != 0) {
+        return bad("mxgemm: k must be a multiple of the 32-element scale block");
+    }
+    if (a_format < 0 || a_format > 1 || b_format < 0 || b_format > 1) {
+        return bad("mxgemm: formats are 0 (e4m3) or 1 (e5m2)");
+    }
+    if ((reinterpret_cast<uintptr_t>(a) & 15u) != 0 || (reinterpret_cast<uintptr_t>(b) & 15u) != 0) {
+        return bad("mxgemm: A and B must be 16-byte aligned");
+    }
+    return launch_mxgemm_fp8(a, b, scale_a, scale_b, c, m, n, k, a_format, b_format, out_f32 ? 1 : 0, workspace,
+                             workspace_bytes < 0 ? 0 : static_cast<size_t>(workspace_bytes), as_stream(stream));
+}
+
 int pto_b200_gemm_f16f32_batched(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
                                  int batch, int64_t a_stride, int64_t b_stride, int64_t c_stride, void *stream)
 {

@@ -73,6 +73,12 @@ int launch_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, in
 // the same product on pairs of thread blocks (cta_group::2); arguments already validated by the caller
 int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
                         cudaStream_t stream);
+// MX block-scaled fp8 GEMM (kind::mxf8f6f4): C[m x n] bf16 (or fp32) = (sfa (x) A[m x k]) * (sfb (x) B[n x k])^T, one e8m0
+// scale per 32 k; a_fmt / b_fmt 0 = e4m3, 1 = e5m2.  The workspace receives the scales in the tensor core's atoms.
+size_t mxgemm_workspace_bytes(int m, int n, int k);
+int launch_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, const uint8_t *sfb, void *c, int m, int n,
+                      int k, int a_fmt, int b_fmt, int out_f32, void *workspace, size_t workspace_bytes,
+                      cudaStream_t stream);
 // host-buffer GEMM whose device staging and status record live in a built-in static device array (no allocation)
 int gemm_f16f32_host_static(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout);
 size_t gemm_static_scratch_bytes();

@@ -1,0 +1,509 @@
+// MX block-scaled fp8 GEMM for sm_100a on CTA pairs: C[m x n] (bf16 or fp32) = (scaleA (x) A) * (scaleB (x) B)^T with
+// A [m x k] and B [n x k] in fp8 (e4m3 or e5m2), one e8m0 scale per 32 consecutive k of a row.  It stands for the
+// reference's MxMatmul tile program (kernels/manual/a5/matmul_mxfp8_performance/mxmatmul_performance_kernel.cpp:
+// TLOAD of data and scale tiles, TEXTRACT, TMATMUL_MX, TSTORE) and maps it to tcgen05.mma kind::mxf8f6f4 with
+// block scaling: the data tiles arrive by TMA in the 128-byte swizzle, the scale tiles arrive by TMA in the
+// 32-row x 16-byte atoms the tensor core reads, are copied into tensor memory (tcgen05.cp) by the MMA thread and are
+// consumed from there by the four k = 32 MMAs of a stage.
+//
+// The block pair works on a 256 x 256 C tile as in gemm_2cta.cu (each block stages its own 128 rows of A and half of
+// the B tile; full[] lives in the leader, empty[] in both blocks).  Tensor memory holds one 256-column accumulator
+// and a ring of scale slots, so the epilogue of a tile does not overlap the next tile's MMAs; the TMA producer does
+// run ahead by the whole ring during the epilogue.
+#include "ptx.cuh"
+#include "internal.h"
+
+#include <cuda_bf16.h>
+
+namespace pto_b200 {
+
+namespace {
+
+constexpr int BM = 128;  // rows of A / C per block (256 per pair)
+constexpr int BN = 256;  // columns of C per pair
+constexpr int BNH = 128; // rows of B staged per block
+constexpr int BK = 128;  // k extent of a stage: one 128-byte swizzle span of fp8, four MMAs, four scales per row
+constexpr int kStages = 5;
+constexpr int kABytes = BM * BK;          // 16 KiB
+constexpr int kBBytes = BNH * BK;         // 16 KiB
+constexpr int kSfaBytes = 512;            // 128 rows x 4 scales
+constexpr int kSfbBytes = 1024;           // 256 rows x 4 scales (each block needs the scales of the whole B tile)
+constexpr int kSfaOff = kABytes + kBBytes;
+constexpr int kSfbOff = kSfaOff + kSfaBytes;
+constexpr int kStageBytes = 34 * 1024;    // 32 KiB of data + 1.5 KiB of scales, rounded up to the swizzle alignment
+constexpr int kTxBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes; // per block and stage
+constexpr int kThreads = 192;             // warp 0 TMA, warp 1 MMA (leader only), warps 2..5 epilogue
+constexpr int kTmemCols = 512;
+constexpr int kSfTmemBase = BN;           // scale slots start after the accumulator
+constexpr int kSfTmemStride = 16;         // columns per slot: 4 for A, 8 for B
+
+struct Control {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t acc_full;
+    uint64_t acc_empty;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+constexpr int kSlabBytes = 32 * 128; // 32 rows x 128 bytes (64 bf16 or 32 fp32), 128-byte swizzle
+constexpr int kStagingBytes = 4 * 2 * kSlabBytes;
+constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + sizeof(Control) + 1024;
+
+constexpr int kGroupN = 8;
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &tm, int &tn)
+{
+    const int band = t / (kGroupN * tiles_m);
+    const int first_n = band * kGroupN;
+    const int width = (tiles_n - first_n) < kGroupN ? (tiles_n - first_n) : kGroupN;
+    const int in_band = t - band * kGroupN * tiles_m;
+    tm = in_band / width;
+    tn = first_n + in_band % width;
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ void cluster_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t map_to_rank(const void *p, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+    return r;
+}
+
+__device__ __forceinline__ void remote_arrive(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *map, uint32_t leader_bar, int c0,
+                                                 int c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        :
+        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+// Shared-memory descriptor of a scale atom: 32 rows of 16 bytes, no swizzle; 8-row groups are 128 bytes apart
+__device__ __forceinline__ uint64_t make_scale_desc(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu);
+    d |= static_cast<uint64_t>(128 >> 4) << 32; // stride between 8-row groups
+    d |= 1ull << 46;                            // descriptor version for sm_100
+    return d;
+}
+
+// 32 rows x 16 bytes of shared memory (in both blocks of the pair: each from its own) -> tensor memory columns
+// [taddr, taddr + 4), the same 32 rows repeated in the four 32-lane quarters
+__device__ __forceinline__ void tc_copy_scales_pair(uint32_t taddr, uint64_t desc)
+{
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+
+// Instruction descriptor of kind::mxf8f6f4 with block scaling: fp32 accumulation, K-major operands, e8m0 scales.
+// Formats: 0 = e4m3, 1 = e5m2.  The scale ids (which byte of the 4-byte scale column an MMA uses) are added per MMA.
+__device__ __forceinline__ uint32_t make_idesc_mx(int m, int n, int a_fmt, int b_fmt)
+{
+    return (static_cast<uint32_t>(a_fmt) << 7) | (static_cast<uint32_t>(b_fmt) << 10) |
+           (static_cast<uint32_t>(n >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void tc_mma_mx_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+        "}\n"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+
+// ---------------------------------------------------------------- scale packing
+// scale[rows x kscales] (row-major e8m0 bytes) -> [row tile][k block][rows_per_tile / 128][32][4][4]: for every
+// (tile of rows_per_tile rows, block of 128 k) the 512-byte atoms the tensor core reads, byte
+// (r % 32) * 16 + ((r % 128) / 32) * 4 + j for row r and the j-th scale of the k block.  Rows and scales outside the
+// matrix are written as 127 (2^0): the matching data are zero-filled by TMA, but an arbitrary byte could be the NaN
+// code.  One thread per (row, k block).
+__global__ void __launch_bounds__(256) mx_pack_scales_kernel(const uint8_t *__restrict__ sfa, const uint8_t *__restrict__ sfb,
+                                                             uint8_t *__restrict__ packed_a, uint8_t *__restrict__ packed_b,
+                                                             int m, int n, int kscales, int kblocks, int rows_a_padded,
+                                                             int rows_b_padded)
+{
+    const int64_t total_a = static_cast<int64_t>(rows_a_padded) * kblocks;
+    const int64_t total = total_a + static_cast<int64_t>(rows_b_padded) * kblocks;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const bool is_a = i < total_a;
+        const int64_t j = is_a ? i : i - total_a;
+        const int r = static_cast<int>(j / kblocks), kb = static_cast<int>(j % kblocks);
+        const uint8_t *src = is_a ? sfa : sfb;
+        const int rows = is_a ? m : n;
+        const int rows_per_tile = is_a ? 128 : 256;
+        uint32_t word = 0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int ks = kb * 4 + q;
+            const uint32_t v = (r < rows && ks < kscales) ? src[static_cast<int64_t>(r) * kscales + ks] : 127u;
+            word |= v << (8 * q);
+        }
+        const int tile = r / rows_per_tile, in_tile = r % rows_per_tile;
+        const int64_t atom = (static_cast<int64_t>(tile) * kblocks + kb) * (rows_per_tile / 128) + in_tile / 128;
+        uint8_t *dst = (is_a ? packed_a : packed_b) + atom * 512 + (in_tile % 32) * 16 + ((in_tile % 128) / 32) * 4;
+        *reinterpret_cast<uint32_t *>(dst) = word;
+    }
+}
+
+template <bool kOutF32>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                   const __grid_constant__ CUtensorMap tmap_c, int c_by_tma, void *__restrict__ c, int m, int n, int k,
+                   int a_fmt, int b_fmt, DeviceStatus *status)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *staging = smem + kStages * kStageBytes;
+    Control *ctl = reinterpret_cast<Control *>(staging + kStagingBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank(); // 0 = leader
+    const int pair = blockIdx.x >> 1;
+    const int pairs = gridDim.x >> 1;
+    const int tiles_m = (m + 2 * BM - 1) / (2 * BM);
+    const int tiles_n = (n + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int kblocks = (k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&ctl->full[s], 1);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        mbar_init(&ctl->acc_full, 1);
+        mbar_init(&ctl->acc_empty, 8); // four epilogue warps in each of the two blocks
+        ctl->abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_sfa);
+        tma_prefetch_desc(&tmap_sfb);
+        if (c_by_tma) {
+            tma_prefetch_desc(&tmap_c);
+        }
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync(); // both blocks' barriers exist before anything is signalled across blocks
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+    volatile int *abort_flag = &ctl->abort_flag;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TLOAD: TMA producer (both blocks)
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += pairs) {
+                int tm, tn;
+                tile_coords(t, tiles_m, tiles_n, tm, tn);
+                const int row0 = tm * 2 * BM + static_cast<int>(rank) * BM; // this block's rows of A and C
+                const int col0 = tn * BN + static_cast<int>(rank) * BNH;    // this block's half of the B tile
+                const int sfa_row0 = (tm * 2 + static_cast<int>(rank)) * kblocks;
+                const int sfb_row0 = tn * kblocks;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *sa = smem + stage * kStageBytes;
+                    const uint32_t leader_full = map_to_rank(&ctl->full[stage], 0);
+                    if (rank == 0) {
+                        mbar_arrive_expect_tx(&ctl->full[stage], 2 * kTxBytes); // bytes of both blocks
+                    }
+                    tma_load_2d_pair(sa, &tmap_a, leader_full, kb * BK, row0);
+                    tma_load_2d_pair(sa + kABytes, &tmap_b, leader_full, kb * BK, col0);
+                    tma_load_2d_pair(sa + kSfaOff, &tmap_sfa, leader_full, 0, sfa_row0 + kb);
+                    tma_load_2d_pair(sa + kSfbOff, &tmap_sfb, leader_full, 0, sfb_row0 + kb);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ TEXTRACT + TMATMUL_MX: MMA issuer (leader only)
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = make_idesc_mx(2 * BM, BN, a_fmt, b_fmt);
+            uint32_t stage = 0, phase = 0, acc_phase = 0;
+            bool ok = true;
+            const uint64_t a_desc0 = make_sw128_desc(smem_u32(smem), 16, 1024);
+            const uint64_t b_desc0 = make_sw128_desc(smem_u32(smem) + kABytes, 16, 1024);
+            const uint64_t sfa_desc0 = make_scale_desc(smem_u32(smem) + kSfaOff);
+            const uint64_t sfb_desc0 = make_scale_desc(smem_u32(smem) + kSfbOff);
+            const uint32_t empty_mine = map_to_rank(&ctl->empty[0], 0);
+            const uint32_t empty_peer = map_to_rank(&ctl->empty[0], 1);
+            const uint32_t acc_full_mine = map_to_rank(&ctl->acc_full, 0);
+            const uint32_t acc_full_peer = map_to_rank(&ctl->acc_full, 1);
+            const uint32_t d_tmem = tmem_base;
+            for (int t = pair; t < num_tiles && ok; t += pairs) {
+                // the epilogue warps of both blocks have drained the previous tile's accumulator
+                if (!mbar_wait(&ctl->acc_empty, acc_phase ^ 1u, abort_flag)) {
+                    break;
+                }
+                tc_fence_after();
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(&ctl->full[stage], phase, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t stage_off = static_cast<uint64_t>(stage * (kStageBytes >> 4));
+                    const uint32_t sfa_tmem = tmem_base + kSfTmemBase + stage * kSfTmemStride;
+                    const uint32_t sfb_tmem = sfa_tmem + 4;
+                    // the stage's scales: one atom for this block's 128 rows of A, two for the 256 rows of B
+                    tc_copy_scales_pair(sfa_tmem, sfa_desc0 + stage_off);
+                    tc_copy_scales_pair(sfb_tmem, sfb_desc0 + stage_off);
+                    tc_copy_scales_pair(sfb_tmem + 4, sfb_desc0 + stage_off + (512 >> 4));
+#pragma unroll
+                    for (int kk = 0; kk < BK / 32; ++kk) {
+                        // 32 bytes of k per MMA inside the 128-byte span; scale byte kk of the slot's columns
+                        const uint32_t id = idesc | (static_cast<uint32_t>(kk) << 29) | (static_cast<uint32_t>(kk) << 4);
+                        tc_mma_mx_pair(d_tmem, a_desc0 + stage_off + static_cast<uint64_t>(kk * 2),
+                                       b_desc0 + stage_off + static_cast<uint64_t>(kk * 2), id, sfa_tmem, sfb_tmem,
+                                       (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    tc_commit_pair(empty_mine + stage * 8);
+                    tc_commit_pair(empty_peer + stage * 8);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) {
+                    break;
+                }
+                tc_commit_pair(acc_full_mine);
+                tc_commit_pair(acc_full_peer);
+                acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ TSTORE: epilogue warps (both blocks)
+        const int quarter = warp & 3;
+        uint32_t acc_phase = 0;
+        constexpr int kSlabCols = kOutF32 ? 32 : 64; // 128 bytes of output per row and slab
+        constexpr int kElem = kOutF32 ? 4 : 2;
+        uint8_t *slabs = staging + (warp - 2) * 2 * kSlabBytes;
+        uint32_t slab = 0;
+        const uint32_t acc_empty_leader = map_to_rank(&ctl->acc_empty, 0);
+        for (int t = pair; t < num_tiles; t += pairs) {
+            int tm, tn;
+            tile_coords(t, tiles_m, tiles_n, tm, tn);
+            if (!mbar_wait(&ctl->acc_full, acc_phase, abort_flag)) {
+                break;
+            }
+            tc_fence_after();
+            const int row = tm * 2 * BM + static_cast<int>(rank) * BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            uint8_t *crow = static_cast<uint8_t *>(c) + (static_cast<int64_t>(row) * n + static_cast<int64_t>(tn) * BN) * kElem;
+#pragma unroll 1
+            for (int cb = 0; cb < BN / kSlabCols; ++cb) {
+                uint32_t w[32]; // 128 bytes of this row's output
+                if (kOutF32) {
+                    tmem_ld_32x32(taddr + cb * 32, w);
+                    tmem_ld_wait();
+                } else {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld_32x32(taddr + cb * 64, r0);
+                    tmem_ld_32x32(taddr + cb * 64 + 32, r1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+                        const __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+                        w[j] = *reinterpret_cast<const uint32_t *>(&p0);
+                        w[16 + j] = *reinterpret_cast<const uint32_t *>(&p1);
+                    }
+                }
+                const int col0 = tn * BN + cb * kSlabCols;
+                if (c_by_tma) {
+                    if (lane == 0) {
+                        tma_store_wait_read<1>(); // the store that last read this slab has finished reading it
+                    }
+                    __syncwarp();
+                    uint8_t *dst = slabs + slab * kSlabBytes + lane * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        *reinterpret_cast<uint4 *>(dst + ((j ^ (lane & 7)) << 4)) =
+                            make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int slab_row0 = row - lane;
+                        if (slab_row0 < m && col0 < n) {
+                            tma_store_2d(&tmap_c, slabs + slab * kSlabBytes, col0, slab_row0);
+                        }
+                        tma_store_commit();
+                    }
+                    slab ^= 1u;
+                } else if (row < m) {
+                    // unaligned C: element stores
+#pragma unroll
+                    for (int j = 0; j < kSlabCols; ++j) {
+                        if (col0 + j < n) {
+                            if (kOutF32) {
+                                reinterpret_cast<uint32_t *>(crow)[cb * kSlabCols + j] = w[j];
+                            } else {
+                                reinterpret_cast<uint16_t *>(crow)[cb * kSlabCols + j] =
+                                    static_cast<uint16_t>((j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu));
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                remote_arrive(acc_empty_leader); // the leader's MMA warp owns the accumulator
+            }
+            acc_phase ^= 1u;
+        }
+        if (c_by_tma && lane == 0) {
+            tma_store_wait_all<0>(); // the slabs are read, and C is written, before the block retires
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (ctl->abort_flag) {
+        for (int i = 0; i < 1024; ++i) {
+            __nanosleep(1000);
+        }
+        if (threadIdx.x == 0 && atomicCAS(&status->code, 0, kErrDeviceWaitTimeout) == 0) {
+            status->block = blockIdx.x;
+            status->where = 5;
+        }
+        __syncthreads();
+    }
+    cluster_sync(); // neither block leaves while the other may still signal it or read its shared memory
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+} // namespace
+
+size_t mxgemm_workspace_bytes(int m, int n, int k)
+{
+    const size_t kblocks = static_cast<size_t>((k + BK - 1) / BK);
+    const size_t atoms_a = static_cast<size_t>((m + 127) / 128) * kblocks;
+    const size_t atoms_b = static_cast<size_t>((n + 255) / 256) * 2 * kblocks;
+    return (atoms_a + atoms_b) * 512;
+}
+
+int launch_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, const uint8_t *sfb, void *c, int m, int n,
+                      int k, int a_fmt, int b_fmt, int out_f32, void *workspace, size_t workspace_bytes,
+                      cudaStream_t stream)
+{
+    if (workspace == nullptr || workspace_bytes < mxgemm_workspace_bytes(m, n, k) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 127u) != 0) {
+        set_error_text("mxgemm: the workspace must be 128-byte aligned and hold mxgemm_workspace_bytes(m, n, k) bytes");
+        return kErrBadArgument;
+    }
+    const int kblocks = (k + BK - 1) / BK;
+    const int rows_a_padded = ((m + 127) / 128) * 128;
+    const int rows_b_padded = ((n + 255) / 256) * 256;
+    uint8_t *packed_a = static_cast<uint8_t *>(workspace);
+    uint8_t *packed_b = packed_a + static_cast<size_t>(rows_a_padded / 128) * kblocks * 512;
+    const int64_t pack_items = static_cast<int64_t>(rows_a_padded + rows_b_padded) * kblocks;
+    mx_pack_scales_kernel<<<grid_for(pack_items, 256), 256, 0, stream>>>(sfa, sfb, packed_a, packed_b, m, n, k / 32, kblocks,
+                                                                        rows_a_padded, rows_b_padded);
+    int rc = check_launch();
+    if (rc != kOk) {
+        return rc;
+    }
+    CUtensorMap tmap_a, tmap_b, tmap_sfa, tmap_sfb, tmap_c;
+    if ((rc = make_tmap_2d(&tmap_a, a, 1, m, k, k, BM, BK, true)) != kOk ||
+        (rc = make_tmap_2d(&tmap_b, b, 1, n, k, k, BNH, BK, true)) != kOk ||
+        (rc = make_tmap_2d(&tmap_sfa, packed_a, 4, static_cast<uint64_t>(rows_a_padded / 128) * kblocks, 128, 128, 1, 128,
+                           false)) != kOk ||
+        (rc = make_tmap_2d(&tmap_sfb, packed_b, 4, static_cast<uint64_t>(rows_b_padded / 256) * kblocks, 256, 256, 1, 256,
+                           false)) != kOk) {
+        return rc;
+    }
+    const int elem = out_f32 ? 4 : 2;
+    const int c_by_tma = ((n * elem) % 16 == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0) ? 1 : 0;
+    if (c_by_tma) {
+        rc = make_tmap_2d(&tmap_c, c, elem, m, n, n, 32, out_f32 ? 32 : 64, true);
+        if (rc != kOk) {
+            return rc;
+        }
+    } else {
+        tmap_c = tmap_a; // never dereferenced
+    }
+    const int tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
+    int pairs = sm_count() / 2;
+    if (tiles < pairs) {
+        pairs = tiles;
+    }
+    DeviceStatus *status = device_status_ptr();
+    if (status == nullptr) {
+        return kErrCuda;
+    }
+    static bool attr_set = false;
+    if (!attr_set) {
+        if ((rc = check_cuda(cudaFuncSetAttribute(mxgemm2_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  kSmemBytes),
+                             "cudaFuncSetAttribute(mxgemm)")) != kOk ||
+            (rc = check_cuda(cudaFuncSetAttribute(mxgemm2_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  kSmemBytes),
+                             "cudaFuncSetAttribute(mxgemm)")) != kOk) {
+            return rc;
+        }
+        attr_set = true;
+    }
+    if (out_f32) {
+        mxgemm2_fp8_kernel<true><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_sfa, tmap_sfb, tmap_c,
+                                                                             c_by_tma, c, m, n, k, a_fmt, b_fmt, status);
+    } else {
+        mxgemm2_fp8_kernel<false><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_sfa, tmap_sfb, tmap_c,
+                                                                              c_by_tma, c, m, n, k, a_fmt, b_fmt, status);
+    }
+    return check_launch();
+}
+
+} // namespace pto_b200

@@ -148,7 +148,8 @@ EncodeTiledFn encode_tiled_fn()
 
 static CUtensorMapDataType dtype_of(int elem_bytes)
 {
-    return elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
+    return elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                           : (elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32);
 }
 
 int make_tmap_2d(CUtensorMap *map, const void *base, int elem_bytes, uint64_t rows, uint64_t cols,

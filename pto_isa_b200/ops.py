@@ -331,6 +331,52 @@ def TCMP(a, b, mode, out=None):
     return out
 
 
+FP8_E4M3, FP8_E5M2 = 0, 1
+_mx_workspaces = {}
+
+
+def _fp8_format(t, fmt):
+    if t.dtype == torch.float8_e5m2:
+        return FP8_E5M2
+    if t.dtype == torch.float8_e4m3fn:
+        return FP8_E4M3
+    if t.dtype == torch.uint8 and fmt in (FP8_E4M3, FP8_E5M2):
+        return fmt
+    raise PtoB200Error("mx_gemm: operands must be float8_e5m2 / float8_e4m3fn, or uint8 with fmt=FP8_E4M3 / FP8_E5M2")
+
+
+def mx_gemm(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, out=None, fmt=FP8_E5M2, workspace=None):
+    """C[m,n] = (scale_a (x) A[m,k]) @ (scale_b (x) B[n,k])^T, the reference's MxMatmul
+    (kernels/manual/a5/matmul_mxfp8_performance): fp8 operands, one float8_e8m0 scale (uint8 bytes, 2^(byte - 127)) per
+    32 consecutive k of a row: scale_a (m, k/32), scale_b (n, k/32).  Output bfloat16 (the reference's) or float32."""
+    _need_cuda(a, b, scale_a, scale_b)
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
+        raise PtoB200Error("mx_gemm: a is (m, k) and b is (n, k)")
+    (m, k), n = a.shape, b.shape[0]
+    if k % 32 != 0 or tuple(scale_a.shape) != (m, k // 32) or tuple(scale_b.shape) != (n, k // 32):
+        raise PtoB200Error("mx_gemm: k must be a multiple of 32 and the scales (m, k/32) and (n, k/32)")
+    if scale_a.dtype.itemsize != 1 or scale_b.dtype.itemsize != 1:
+        raise PtoB200Error("mx_gemm: scales are one byte each (float8_e8m0)")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise PtoB200Error("mx_gemm: the output is bfloat16 or float32")
+    fa, fb = _fp8_format(a, fmt), _fp8_format(b, fmt)
+    out = torch.empty(m, n, dtype=out_dtype, device=a.device) if out is None else out
+    _need_cuda(out)
+    need = lib().pto_b200_mxgemm_workspace_bytes(m, n, k)
+    if workspace is None:
+        key = (a.device.index, torch.cuda.current_stream(a.device).cuda_stream)
+        workspace = _mx_workspaces.get(key)
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+            _mx_workspaces[key] = workspace
+    with torch.cuda.device(a.device):
+        rc = lib().pto_b200_mxgemm_fp8(_ptr(a), _ptr(b), _ptr(scale_a), _ptr(scale_b), _ptr(out), m, n, k, fa, fb,
+                                       1 if out_dtype == torch.float32 else 0, _ptr(workspace), workspace.numel(),
+                                       _stream(a))
+    check(rc, "mx_gemm")
+    return out
+
+
 def gemm(a, b, b_layout=1, out=None):
     """C[m,n] fp32 = A[m,k] fp16 @ B.  b_layout 0: b is (k, n); 1: b is (n, k), the reference kernel's layout.
     A 3-D `a` (batch, m, k) with 3-D `b` runs `batch` independent problems."""

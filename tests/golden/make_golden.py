@@ -347,6 +347,25 @@ def gen_mla(ref, tmp, out):
     np.savez_compressed(os.path.join(out, "mla.npz"), q=q, k=k, v=v, wq=wq, wk=wk, wv=wv, wo=wo, o=o, scale=np.float32(scale))
 
 
+def gen_mxgemm(ref, tmp, out):
+    """MX block-scaled fp8 GEMM: inputs, e8m0 scales and golden written by the reference's own generator
+    (kernels/manual/a5/matmul_mxfp8_performance/scripts/gen_data.py:27-70; it needs ml_dtypes), called for two small
+    problems instead of its 6144^3: float8_e5m2 at 256 x 384 x 256 (m, k, n) and float8_e4m3fn at 128 x 128 x 256.
+    Files as the generator writes them: A m x k, B transposed to n x k, scaleA m x k/32, scaleB transposed to n x k/32,
+    golden m x n bfloat16 (stored here as its 16-bit patterns)."""
+    mod = load(os.path.join(ref, "kernels/manual/a5/matmul_mxfp8_performance/scripts/gen_data.py"), "ref_mx_gen")
+    saved = {}
+    for tag, dtype, (m, k, n) in (("e5m2", mod.fp8_e5m2, (256, 384, 256)), ("e4m3", mod.fp8_e4m3fn, (128, 128, 256))):
+        d = in_case_dir(tmp, f"mxgemm_{tag}")
+        mod.gen_golden_data(mod.MxMatmulParams(dtype, dtype, mod.bfloat16, m, k, n, False))
+        saved[f"{tag}_a"] = read(os.path.join(d, "input/x1_gm.bin"), np.uint8, (m, k))
+        saved[f"{tag}_b"] = read(os.path.join(d, "input/x2_gm.bin"), np.uint8, (n, k))
+        saved[f"{tag}_scale_a"] = read(os.path.join(d, "input/x1_scale_gm.bin"), np.uint8, (m, k // 32))
+        saved[f"{tag}_scale_b"] = read(os.path.join(d, "input/x2_scale_gm.bin"), np.uint8, (n, k // 32))
+        saved[f"{tag}_golden_bf16_bits"] = read(os.path.join(d, "output/golden.bin"), np.uint16, (m, n))
+    np.savez_compressed(os.path.join(out, "mxgemm.npz"), **saved)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -354,7 +373,7 @@ def main():
     cwd = os.getcwd()
     with tempfile.TemporaryDirectory() as tmp:
         try:
-            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm, gen_vector2, gen_harness, gen_mla):
+            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm, gen_vector2, gen_harness, gen_mla, gen_mxgemm):
                 os.chdir(tmp)
                 fn(args.reference, tmp, HERE)
         finally:

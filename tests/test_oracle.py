@@ -306,3 +306,32 @@ def test_vector2_matches_reference_bits():
     near = np.full((64, 256), 1.0, np.float32)
     assert np.array_equal(port.tcmps_f32(near, float(np.nextafter(np.float32(1.0), np.float32(2.0))), 0),
                           ref.tcmps_f32(near, float(np.nextafter(np.float32(1.0), np.float32(2.0))), 0))
+
+
+def test_mxgemm_oracle_matches_reference_generator(golden_dir):
+    """The restatement of the MX block-scaled fp8 GEMM reproduces, bit for bit after rounding to bfloat16, the golden
+    the reference's own generator wrote (kernels/manual/a5/matmul_mxfp8_performance/scripts/gen_data.py)."""
+    z = np.load(os.path.join(golden_dir, "mxgemm.npz"))
+    for tag, fmt in (("e5m2", 1), ("e4m3", 0)):
+        c = port.mxgemm_fp8(z[f"{tag}_a"], z[f"{tag}_b"], z[f"{tag}_scale_a"], z[f"{tag}_scale_b"], fmt, fmt)
+        u = c.view(np.uint32).astype(np.uint64)
+        bits = ((u + 0x7fff + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+        assert np.array_equal(bits, z[f"{tag}_golden_bf16_bits"]), tag
+
+
+def test_mxgemm_oracle_fp8_decoding_against_torch():
+    """All 256 codes of both fp8 formats, through a one-element product with unit scales."""
+    import torch
+    codes = np.arange(256, dtype=np.uint8)
+    one = {1: 0x3c, 0: 0x38}  # 1.0 in e5m2 / e4m3
+    for fmt, tdt in ((1, torch.float8_e5m2), (0, torch.float8_e4m3fn)):
+        a = np.zeros((256, 32), np.uint8)
+        a[:, 0] = codes
+        b = np.zeros((1, 32), np.uint8)
+        b[0, 0] = one[fmt]
+        s = np.full((256, 1), 127, np.uint8)
+        got = port.mxgemm_fp8(a, b, s, s[:1], fmt, fmt)[:, 0]
+        want = torch.from_numpy(codes).view(tdt).float().numpy()
+        assert np.array_equal(np.isnan(got), np.isnan(want))
+        ok = ~np.isnan(want)
+        assert np.array_equal(got[ok], want[ok])
