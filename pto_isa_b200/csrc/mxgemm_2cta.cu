@@ -22,20 +22,25 @@ namespace {
 constexpr int BM = 128;  // rows of A / C per block (256 per pair)
 constexpr int BN = 256;  // columns of C per pair
 constexpr int BNH = 128; // rows of B staged per block
-constexpr int BK = 128;  // k extent of a stage: one 128-byte swizzle span of fp8, four MMAs, four scales per row
-constexpr int kStages = 5;
-constexpr int kABytes = BM * BK;          // 16 KiB
-constexpr int kBBytes = BNH * BK;         // 16 KiB
-constexpr int kSfaBytes = 512;            // 128 rows x 4 scales
+constexpr int kSpan = 128; // k extent of one 128-byte swizzle span of fp8: four MMAs, four scales per row
+#ifndef PTO_B200_MX_SPANS
+#define PTO_B200_MX_SPANS 2
+#endif
+constexpr int kSpans = PTO_B200_MX_SPANS; // spans per stage
+constexpr int BK = kSpan * kSpans;        // k extent of a stage
+constexpr int kStages = kSpans == 2 ? 3 : 6;
+constexpr int kABytes = BM * BK;          // 16 KiB per span
+constexpr int kBBytes = BNH * BK;         // 16 KiB per span
+constexpr int kSfaBytes = 512;            // 128 rows x 4 scales (one span)
 constexpr int kSfbBytes = 1024;           // 256 rows x 4 scales (each block needs the scales of the whole B tile)
-constexpr int kSfaOff = kABytes + kBBytes;
-constexpr int kSfbOff = kSfaOff + kSfaBytes;
-constexpr int kStageBytes = 34 * 1024;    // 32 KiB of data + 1.5 KiB of scales, rounded up to the swizzle alignment
-constexpr int kTxBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes; // per block and stage
+constexpr int kSfOff = kABytes + kBBytes; // per span: the A atom, then the two B atoms
+constexpr int kSfSpanBytes = kSfaBytes + kSfbBytes;
+constexpr int kStageBytes = ((kSfOff + kSpans * kSfSpanBytes + 1023) / 1024) * 1024;
+constexpr int kTxBytes = kABytes + kBBytes + kSpans * kSfSpanBytes; // per block and stage
 constexpr int kThreads = 192;             // warp 0 TMA, warp 1 MMA (leader only), warps 2..5 epilogue
 constexpr int kTmemCols = 512;
 constexpr int kSfTmemBase = BN;           // scale slots start after the accumulator
-constexpr int kSfTmemStride = 16;         // columns per slot: 4 for A, 8 for B
+constexpr int kSfTmemStride = 16;         // columns per span slot: 4 for A, 8 for B
 
 struct Control {
     uint64_t full[kStages];
@@ -47,7 +52,8 @@ struct Control {
 };
 
 constexpr int kSlabBytes = 32 * 128; // 32 rows x 128 bytes (64 bf16 or 32 fp32), 128-byte swizzle
-constexpr int kStagingBytes = 4 * 2 * kSlabBytes;
+constexpr int kSlabsPerWarp = 1;
+constexpr int kStagingBytes = 4 * kSlabsPerWarp * kSlabBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + sizeof(Control) + 1024;
 
 constexpr int kGroupN = 8;
@@ -85,10 +91,14 @@ __device__ __forceinline__ void remote_arrive(uint32_t cluster_addr)
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
-__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr)
+// one commit of the pair's MMAs and copies, delivered to the barrier at the same shared-memory offset in both blocks
+__device__ __forceinline__ void tc_commit_both(uint32_t local_addr)
 {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
-                 : "memory");
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            local_addr),
+        "h"(static_cast<uint16_t>(3))
+        : "memory");
 }
 
 __device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *map, uint32_t leader_bar, int c0,
@@ -196,6 +206,7 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const int tiles_n = (n + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
     const int kblocks = (k + BK - 1) / BK;
+    const int kspans = kblocks * kSpans; // scale atoms along k (padded to whole stages by the packing kernel)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -237,8 +248,8 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 tile_coords(t, tiles_m, tiles_n, tm, tn);
                 const int row0 = tm * 2 * BM + static_cast<int>(rank) * BM; // this block's rows of A and C
                 const int col0 = tn * BN + static_cast<int>(rank) * BNH;    // this block's half of the B tile
-                const int sfa_row0 = (tm * 2 + static_cast<int>(rank)) * kblocks;
-                const int sfb_row0 = tn * kblocks;
+                const int sfa_row0 = (tm * 2 + static_cast<int>(rank)) * kspans;
+                const int sfb_row0 = tn * kspans;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) {
                         ok = false;
@@ -249,10 +260,15 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     if (rank == 0) {
                         mbar_arrive_expect_tx(&ctl->full[stage], 2 * kTxBytes); // bytes of both blocks
                     }
-                    tma_load_2d_pair(sa, &tmap_a, leader_full, kb * BK, row0);
-                    tma_load_2d_pair(sa + kABytes, &tmap_b, leader_full, kb * BK, col0);
-                    tma_load_2d_pair(sa + kSfaOff, &tmap_sfa, leader_full, 0, sfa_row0 + kb);
-                    tma_load_2d_pair(sa + kSfbOff, &tmap_sfb, leader_full, 0, sfb_row0 + kb);
+#pragma unroll
+                    for (int sp = 0; sp < kSpans; ++sp) {
+                        tma_load_2d_pair(sa + sp * (BM * kSpan), &tmap_a, leader_full, kb * BK + sp * kSpan, row0);
+                        tma_load_2d_pair(sa + kABytes + sp * (BNH * kSpan), &tmap_b, leader_full, kb * BK + sp * kSpan,
+                                         col0);
+                        uint8_t *sf = sa + kSfOff + sp * kSfSpanBytes;
+                        tma_load_2d_pair(sf, &tmap_sfa, leader_full, 0, sfa_row0 + kb * kSpans + sp);
+                        tma_load_2d_pair(sf + kSfaBytes, &tmap_sfb, leader_full, 0, sfb_row0 + kb * kSpans + sp);
+                    }
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -262,58 +278,75 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ TEXTRACT + TMATMUL_MX: MMA issuer (leader only)
-        if (lane == 0 && rank == 0) {
+        // The whole warp walks the loops (lane 0 waits and issues, the result of every wait is broadcast), so that the
+        // control flow stays warp-uniform and the descriptors of the tcgen05 instructions can be kept in uniform
+        // registers instead of being moved there one by one in front of every instruction.
+        if (rank == 0) {
             const uint32_t idesc = make_idesc_mx(2 * BM, BN, a_fmt, b_fmt);
             uint32_t stage = 0, phase = 0, acc_phase = 0;
-            bool ok = true;
             const uint64_t a_desc0 = make_sw128_desc(smem_u32(smem), 16, 1024);
             const uint64_t b_desc0 = make_sw128_desc(smem_u32(smem) + kABytes, 16, 1024);
-            const uint64_t sfa_desc0 = make_scale_desc(smem_u32(smem) + kSfaOff);
-            const uint64_t sfb_desc0 = make_scale_desc(smem_u32(smem) + kSfbOff);
-            const uint32_t empty_mine = map_to_rank(&ctl->empty[0], 0);
-            const uint32_t empty_peer = map_to_rank(&ctl->empty[0], 1);
-            const uint32_t acc_full_mine = map_to_rank(&ctl->acc_full, 0);
-            const uint32_t acc_full_peer = map_to_rank(&ctl->acc_full, 1);
+            const uint64_t sfa_desc0 = make_scale_desc(smem_u32(smem) + kSfOff);
+            const uint64_t sfb_desc0 = make_scale_desc(smem_u32(smem) + kSfOff + kSfaBytes);
+            const uint32_t empty_addr = smem_u32(&ctl->empty[0]);
+            const uint32_t acc_full_addr = smem_u32(&ctl->acc_full);
             const uint32_t d_tmem = tmem_base;
-            for (int t = pair; t < num_tiles && ok; t += pairs) {
+            for (int t = pair; t < num_tiles; t += pairs) {
                 // the epilogue warps of both blocks have drained the previous tile's accumulator
-                if (!mbar_wait(&ctl->acc_empty, acc_phase ^ 1u, abort_flag)) {
+                int ok = 1;
+                if (lane == 0) {
+                    ok = mbar_wait(&ctl->acc_empty, acc_phase ^ 1u, abort_flag) ? 1 : 0;
+                }
+                if (__shfl_sync(0xffffffffu, ok, 0) == 0) {
                     break;
                 }
                 tc_fence_after();
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(&ctl->full[stage], phase, abort_flag)) {
-                        ok = false;
+                    if (lane == 0) {
+                        ok = mbar_wait(&ctl->full[stage], phase, abort_flag) ? 1 : 0;
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (ok == 0) {
                         break;
                     }
                     tc_fence_after();
                     const uint64_t stage_off = static_cast<uint64_t>(stage * (kStageBytes >> 4));
-                    const uint32_t sfa_tmem = tmem_base + kSfTmemBase + stage * kSfTmemStride;
-                    const uint32_t sfb_tmem = sfa_tmem + 4;
-                    // the stage's scales: one atom for this block's 128 rows of A, two for the 256 rows of B
-                    tc_copy_scales_pair(sfa_tmem, sfa_desc0 + stage_off);
-                    tc_copy_scales_pair(sfb_tmem, sfb_desc0 + stage_off);
-                    tc_copy_scales_pair(sfb_tmem + 4, sfb_desc0 + stage_off + (512 >> 4));
+                    if (lane == 0) {
 #pragma unroll
-                    for (int kk = 0; kk < BK / 32; ++kk) {
-                        // 32 bytes of k per MMA inside the 128-byte span; scale byte kk of the slot's columns
-                        const uint32_t id = idesc | (static_cast<uint32_t>(kk) << 29) | (static_cast<uint32_t>(kk) << 4);
-                        tc_mma_mx_pair(d_tmem, a_desc0 + stage_off + static_cast<uint64_t>(kk * 2),
-                                       b_desc0 + stage_off + static_cast<uint64_t>(kk * 2), id, sfa_tmem, sfb_tmem,
-                                       (kb | kk) != 0 ? 1u : 0u);
+                        for (int sp = 0; sp < kSpans; ++sp) {
+                            const uint32_t sfa_tmem = tmem_base + kSfTmemBase + (stage * kSpans + sp) * kSfTmemStride;
+                            const uint32_t sfb_tmem = sfa_tmem + 4;
+                            const uint64_t sf_off = stage_off + static_cast<uint64_t>((sp * kSfSpanBytes) >> 4);
+                            // the span's scales: one atom for this block's 128 rows of A, two for the 256 rows of B
+                            tc_copy_scales_pair(sfa_tmem, sfa_desc0 + sf_off);
+                            tc_copy_scales_pair(sfb_tmem, sfb_desc0 + sf_off);
+                            tc_copy_scales_pair(sfb_tmem + 4, sfb_desc0 + sf_off + (512 >> 4));
+#pragma unroll
+                            for (int kk = 0; kk < kSpan / 32; ++kk) {
+                                // 32 bytes of k per MMA inside the 128-byte span; scale byte kk of the slot's columns
+                                const uint32_t id =
+                                    idesc | (static_cast<uint32_t>(kk) << 29) | (static_cast<uint32_t>(kk) << 4);
+                                const uint64_t a_off = stage_off + static_cast<uint64_t>((sp * (BM * kSpan) + kk * 32) >> 4);
+                                const uint64_t b_off = stage_off + static_cast<uint64_t>((sp * (BNH * kSpan) + kk * 32) >> 4);
+                                tc_mma_mx_pair(d_tmem, a_desc0 + a_off, b_desc0 + b_off, id, sfa_tmem, sfb_tmem,
+                                               (kb | sp | kk) != 0 ? 1u : 0u);
+                            }
+                        }
+                        // the stage is reusable in both blocks once these MMAs have read it: one commit, delivered to
+                        // the barrier at this offset in both blocks
+                        tc_commit_both(empty_addr + stage * 8);
                     }
-                    tc_commit_pair(empty_mine + stage * 8);
-                    tc_commit_pair(empty_peer + stage * 8);
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
-                if (!ok) {
+                if (ok == 0) {
                     break;
                 }
-                tc_commit_pair(acc_full_mine);
-                tc_commit_pair(acc_full_peer);
+                if (lane == 0) {
+                    tc_commit_both(acc_full_addr);
+                }
                 acc_phase ^= 1u;
             }
         }
@@ -323,7 +356,7 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         uint32_t acc_phase = 0;
         constexpr int kSlabCols = kOutF32 ? 32 : 64; // 128 bytes of output per row and slab
         constexpr int kElem = kOutF32 ? 4 : 2;
-        uint8_t *slabs = staging + (warp - 2) * 2 * kSlabBytes;
+        uint8_t *slabs = staging + (warp - 2) * kSlabsPerWarp * kSlabBytes;
         uint32_t slab = 0;
         const uint32_t acc_empty_leader = map_to_rank(&ctl->acc_empty, 0);
         for (int t = pair; t < num_tiles; t += pairs) {
@@ -358,7 +391,7 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 const int col0 = tn * BN + cb * kSlabCols;
                 if (c_by_tma) {
                     if (lane == 0) {
-                        tma_store_wait_read<1>(); // the store that last read this slab has finished reading it
+                        tma_store_wait_read<kSlabsPerWarp - 1>(); // the store that last read this slab has finished reading it
                     }
                     __syncwarp();
                     uint8_t *dst = slabs + slab * kSlabBytes + lane * 128;
@@ -376,7 +409,7 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                         }
                         tma_store_commit();
                     }
-                    slab ^= 1u;
+                    slab = (slab + 1) % kSlabsPerWarp;
                 } else if (row < m) {
                     // unaligned C: element stores
 #pragma unroll
@@ -429,7 +462,7 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 
 size_t mxgemm_workspace_bytes(int m, int n, int k)
 {
-    const size_t kblocks = static_cast<size_t>((k + BK - 1) / BK);
+    const size_t kblocks = static_cast<size_t>((k + BK - 1) / BK) * kSpans; // 128-k scale atoms, whole stages
     const size_t atoms_a = static_cast<size_t>((m + 127) / 128) * kblocks;
     const size_t atoms_b = static_cast<size_t>((n + 255) / 256) * 2 * kblocks;
     return (atoms_a + atoms_b) * 512;
@@ -444,7 +477,7 @@ int launch_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, co
         set_error_text("mxgemm: the workspace must be 128-byte aligned and hold mxgemm_workspace_bytes(m, n, k) bytes");
         return kErrBadArgument;
     }
-    const int kblocks = (k + BK - 1) / BK;
+    const int kblocks = ((k + BK - 1) / BK) * kSpans; // 128-k scale atoms along k, padded to whole stages
     const int rows_a_padded = ((m + 127) / 128) * 128;
     const int rows_b_padded = ((n + 255) / 256) * 256;
     uint8_t *packed_a = static_cast<uint8_t *>(workspace);
@@ -457,8 +490,8 @@ int launch_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, co
         return rc;
     }
     CUtensorMap tmap_a, tmap_b, tmap_sfa, tmap_sfb, tmap_c;
-    if ((rc = make_tmap_2d(&tmap_a, a, 1, m, k, k, BM, BK, true)) != kOk ||
-        (rc = make_tmap_2d(&tmap_b, b, 1, n, k, k, BNH, BK, true)) != kOk ||
+    if ((rc = make_tmap_2d(&tmap_a, a, 1, m, k, k, BM, kSpan, true)) != kOk ||
+        (rc = make_tmap_2d(&tmap_b, b, 1, n, k, k, BNH, kSpan, true)) != kOk ||
         (rc = make_tmap_2d(&tmap_sfa, packed_a, 4, static_cast<uint64_t>(rows_a_padded / 128) * kblocks, 128, 128, 1, 128,
                            false)) != kOk ||
         (rc = make_tmap_2d(&tmap_sfb, packed_b, 4, static_cast<uint64_t>(rows_b_padded / 256) * kblocks, 256, 256, 1, 256,
