@@ -39,8 +39,17 @@ constexpr int kStageBytes = ((kSfOff + kSpans * kSfSpanBytes + 1023) / 1024) * 1
 constexpr int kTxBytes = kABytes + kBBytes + kSpans * kSfSpanBytes; // per block and stage
 constexpr int kThreads = 192;             // warp 0 TMA, warp 1 MMA (leader only), warps 2..5 epilogue
 constexpr int kTmemCols = 512;
-constexpr int kSfTmemBase = BN;           // scale slots start after the accumulator
-constexpr int kSfTmemStride = 16;         // columns per span slot: 4 for A, 8 for B
+// Tensor memory: two accumulators that share 64 columns, [0, 256) and [192, 448), then four scale slots of 16 columns
+// (4 for A, 8 for B).  The epilogue drains the shared columns of a tile first and releases the accumulator to the MMA
+// warp at that point, so the next tile's MMAs run under the rest of the epilogue.  The scale slots are reused every
+// four spans: the copy into a slot is issued after the MMAs that read it, by the same thread, which the tensor pipe
+// executes in issue order.
+constexpr int kAccStride = 192;
+constexpr int kAccShared = BN - kAccStride; // 64 columns belong to both accumulators
+constexpr int kSfTmemBase = kAccStride + BN;
+constexpr int kSfSlots = 4;
+constexpr int kSfTmemStride = 16;
+static_assert(kSfTmemBase + kSfSlots * kSfTmemStride <= kTmemCols, "tensor memory layout");
 
 struct Control {
     uint64_t full[kStages];
@@ -290,9 +299,10 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             const uint64_t sfb_desc0 = make_scale_desc(smem_u32(smem) + kSfOff + kSfaBytes);
             const uint32_t empty_addr = smem_u32(&ctl->empty[0]);
             const uint32_t acc_full_addr = smem_u32(&ctl->acc_full);
-            const uint32_t d_tmem = tmem_base;
+            uint32_t local_tile = 0, span_ctr = 0;
             for (int t = pair; t < num_tiles; t += pairs) {
-                // the epilogue warps of both blocks have drained the previous tile's accumulator
+                // the epilogue warps of both blocks have drained the columns the previous tile shares with this one
+                // (and all of the tile before that, which used this accumulator)
                 int ok = 1;
                 if (lane == 0) {
                     ok = mbar_wait(&ctl->acc_empty, acc_phase ^ 1u, abort_flag) ? 1 : 0;
@@ -301,6 +311,8 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     break;
                 }
                 tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (local_tile & 1u) * kAccStride;
+                ++local_tile;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (lane == 0) {
                         ok = mbar_wait(&ctl->full[stage], phase, abort_flag) ? 1 : 0;
@@ -314,7 +326,8 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     if (lane == 0) {
 #pragma unroll
                         for (int sp = 0; sp < kSpans; ++sp) {
-                            const uint32_t sfa_tmem = tmem_base + kSfTmemBase + (stage * kSpans + sp) * kSfTmemStride;
+                            const uint32_t sfa_tmem =
+                                tmem_base + kSfTmemBase + ((span_ctr + sp) % kSfSlots) * kSfTmemStride;
                             const uint32_t sfb_tmem = sfa_tmem + 4;
                             const uint64_t sf_off = stage_off + static_cast<uint64_t>((sp * kSfSpanBytes) >> 4);
                             // the span's scales: one atom for this block's 128 rows of A, two for the 256 rows of B
@@ -336,6 +349,7 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                         // the barrier at this offset in both blocks
                         tc_commit_both(empty_addr + stage * 8);
                     }
+                    span_ctr += kSpans;
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -353,7 +367,7 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     } else {
         // ------------------------------------------------------------ TSTORE: epilogue warps (both blocks)
         const int quarter = warp & 3;
-        uint32_t acc_phase = 0;
+        uint32_t acc_phase = 0, local_tile = 0;
         constexpr int kSlabCols = kOutF32 ? 32 : 64; // 128 bytes of output per row and slab
         constexpr int kElem = kOutF32 ? 4 : 2;
         uint8_t *slabs = staging + (warp - 2) * kSlabsPerWarp * kSlabBytes;
@@ -367,10 +381,16 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             }
             tc_fence_after();
             const int row = tm * 2 * BM + static_cast<int>(rank) * BM + quarter * 32 + lane;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            const uint32_t buf = local_tile & 1u;
+            ++local_tile;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kAccStride;
+            constexpr int kSlabs = BN / kSlabCols;
+            constexpr int kEarly = kAccShared / kSlabCols; // slabs in the columns shared with the other accumulator
             uint8_t *crow = static_cast<uint8_t *>(c) + (static_cast<int64_t>(row) * n + static_cast<int64_t>(tn) * BN) * kElem;
 #pragma unroll 1
-            for (int cb = 0; cb < BN / kSlabCols; ++cb) {
+            for (int i = 0; i < kSlabs; ++i) {
+                // the shared columns first: the last ones of accumulator 0, the first ones of accumulator 1
+                const int cb = (buf == 0) ? (i + kSlabs - kEarly) % kSlabs : i;
                 uint32_t w[32]; // 128 bytes of this row's output
                 if (kOutF32) {
                     tmem_ld_32x32(taddr + cb * 32, w);
@@ -386,6 +406,14 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                         const __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
                         w[j] = *reinterpret_cast<const uint32_t *>(&p0);
                         w[16 + j] = *reinterpret_cast<const uint32_t *>(&p1);
+                    }
+                }
+                if (i == kEarly - 1) {
+                    // the shared columns are in registers: the next tile's MMAs may overwrite them
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        remote_arrive(acc_empty_leader); // the leader's MMA warp owns the accumulators
                     }
                 }
                 const int col0 = tn * BN + cb * kSlabCols;
@@ -424,11 +452,6 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                         }
                     }
                 }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                remote_arrive(acc_empty_leader); // the leader's MMA warp owns the accumulator
             }
             acc_phase ^= 1u;
         }
