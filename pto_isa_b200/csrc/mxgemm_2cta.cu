@@ -165,32 +165,52 @@ __device__ __forceinline__ void tc_mma_mx_pair(uint32_t d_tmem, uint64_t a_desc,
 // (r % 32) * 16 + ((r % 128) / 32) * 4 + j for row r and the j-th scale of the k block.  Rows and scales outside the
 // matrix are written as 127 (2^0): the matching data are zero-filled by TMA, but an arbitrary byte could be the NaN
 // code.  One thread per (row, k block).
+__device__ __forceinline__ uint8_t *mx_atom_word(uint8_t *packed, int rows_per_tile, int kblocks, int r, int kb)
+{
+    const int tile = r / rows_per_tile, in_tile = r % rows_per_tile;
+    const int64_t atom = (static_cast<int64_t>(tile) * kblocks + kb) * (rows_per_tile / 128) + in_tile / 128;
+    return packed + atom * 512 + (in_tile % 32) * 16 + ((in_tile % 128) / 32) * 4;
+}
+
+// kQuad: one thread per (row, four k blocks) with one 16-byte load (kscales a multiple of 16, aligned sources, kblocks a
+// multiple of 4); otherwise one thread per (row, k block) with byte loads.
+template <bool kQuad>
 __global__ void __launch_bounds__(256) mx_pack_scales_kernel(const uint8_t *__restrict__ sfa, const uint8_t *__restrict__ sfb,
                                                              uint8_t *__restrict__ packed_a, uint8_t *__restrict__ packed_b,
                                                              int m, int n, int kscales, int kblocks, int rows_a_padded,
                                                              int rows_b_padded)
 {
-    const int64_t total_a = static_cast<int64_t>(rows_a_padded) * kblocks;
-    const int64_t total = total_a + static_cast<int64_t>(rows_b_padded) * kblocks;
+    const int per_row = kQuad ? kblocks / 4 : kblocks;
+    const int64_t total_a = static_cast<int64_t>(rows_a_padded) * per_row;
+    const int64_t total = total_a + static_cast<int64_t>(rows_b_padded) * per_row;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
          i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const bool is_a = i < total_a;
         const int64_t j = is_a ? i : i - total_a;
-        const int r = static_cast<int>(j / kblocks), kb = static_cast<int>(j % kblocks);
+        const int r = static_cast<int>(j / per_row), q = static_cast<int>(j % per_row);
         const uint8_t *src = is_a ? sfa : sfb;
+        uint8_t *packed = is_a ? packed_a : packed_b;
         const int rows = is_a ? m : n;
         const int rows_per_tile = is_a ? 128 : 256;
-        uint32_t word = 0;
+        if (kQuad) {
+            uint4 v = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+            if (r < rows && q * 16 < kscales) {
+                v = *reinterpret_cast<const uint4 *>(src + static_cast<int64_t>(r) * kscales + q * 16);
+            }
+            *reinterpret_cast<uint32_t *>(mx_atom_word(packed, rows_per_tile, kblocks, r, 4 * q + 0)) = v.x;
+            *reinterpret_cast<uint32_t *>(mx_atom_word(packed, rows_per_tile, kblocks, r, 4 * q + 1)) = v.y;
+            *reinterpret_cast<uint32_t *>(mx_atom_word(packed, rows_per_tile, kblocks, r, 4 * q + 2)) = v.z;
+            *reinterpret_cast<uint32_t *>(mx_atom_word(packed, rows_per_tile, kblocks, r, 4 * q + 3)) = v.w;
+        } else {
+            uint32_t word = 0;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int ks = kb * 4 + q;
-            const uint32_t v = (r < rows && ks < kscales) ? src[static_cast<int64_t>(r) * kscales + ks] : 127u;
-            word |= v << (8 * q);
+            for (int b = 0; b < 4; ++b) {
+                const int ks = q * 4 + b;
+                const uint32_t v = (r < rows && ks < kscales) ? src[static_cast<int64_t>(r) * kscales + ks] : 127u;
+                word |= v << (8 * b);
+            }
+            *reinterpret_cast<uint32_t *>(mx_atom_word(packed, rows_per_tile, kblocks, r, q)) = word;
         }
-        const int tile = r / rows_per_tile, in_tile = r % rows_per_tile;
-        const int64_t atom = (static_cast<int64_t>(tile) * kblocks + kb) * (rows_per_tile / 128) + in_tile / 128;
-        uint8_t *dst = (is_a ? packed_a : packed_b) + atom * 512 + (in_tile % 32) * 16 + ((in_tile % 128) / 32) * 4;
-        *reinterpret_cast<uint32_t *>(dst) = word;
     }
 }
 
@@ -505,9 +525,17 @@ int launch_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, co
     const int rows_b_padded = ((n + 255) / 256) * 256;
     uint8_t *packed_a = static_cast<uint8_t *>(workspace);
     uint8_t *packed_b = packed_a + static_cast<size_t>(rows_a_padded / 128) * kblocks * 512;
-    const int64_t pack_items = static_cast<int64_t>(rows_a_padded + rows_b_padded) * kblocks;
-    mx_pack_scales_kernel<<<grid_for(pack_items, 256), 256, 0, stream>>>(sfa, sfb, packed_a, packed_b, m, n, k / 32, kblocks,
-                                                                        rows_a_padded, rows_b_padded);
+    const int kscales = k / 32;
+    const bool quad = (kscales % 16 == 0) && (kblocks % 4 == 0) && (reinterpret_cast<uintptr_t>(sfa) & 15u) == 0 &&
+                      (reinterpret_cast<uintptr_t>(sfb) & 15u) == 0;
+    const int64_t pack_items = static_cast<int64_t>(rows_a_padded + rows_b_padded) * (quad ? kblocks / 4 : kblocks);
+    if (quad) {
+        mx_pack_scales_kernel<true><<<grid_for(pack_items, 256), 256, 0, stream>>>(sfa, sfb, packed_a, packed_b, m, n, kscales,
+                                                                                  kblocks, rows_a_padded, rows_b_padded);
+    } else {
+        mx_pack_scales_kernel<false><<<grid_for(pack_items, 256), 256, 0, stream>>>(sfa, sfb, packed_a, packed_b, m, n, kscales,
+                                                                                   kblocks, rows_a_padded, rows_b_padded);
+    }
     int rc = check_launch();
     if (rc != kOk) {
         return rc;
