@@ -171,6 +171,10 @@ int64_t pto_b200_mxgemm_workspace_bytes(int m, int n, int k);
 int pto_b200_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *scale_a, const uint8_t *scale_b, void *c, int m,
                         int n, int k, int a_format, int b_format, int out_f32, void *workspace, int64_t workspace_bytes,
                         void *stream);
+/* TMATMUL_BIAS (include/pto/common/pto_instr.hpp:509-527, include/pto/cpu/TMatmul.hpp:99-116): the same product with
+ * bias[j] (n floats) added to every element of column j. */
+int pto_b200_gemm_f16f32_bias(const uint16_t *a, const uint16_t *b, const float *bias, float *c, int m, int n, int k,
+                              int b_layout, void *stream);
 /* `batch` independent problems of the same shape, operands `*_stride` elements apart. */
 int pto_b200_gemm_f16f32_batched(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
                                  int batch, int64_t a_stride, int64_t b_stride, int64_t c_stride, void *stream);

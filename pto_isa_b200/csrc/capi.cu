@@ -332,6 +332,15 @@ int pto_b200_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *scale
                              workspace_bytes < 0 ? 0 : static_cast<size_t>(workspace_bytes), as_stream(stream));
 }
 
+int pto_b200_gemm_f16f32_bias(const uint16_t *a, const uint16_t *b, const float *bias, float *c, int m, int n, int k,
+                              int b_layout, void *stream)
+{
+    if (bias == nullptr) {
+        return bad("gemm_bias: bias is null");
+    }
+    return launch_gemm_f16f32(a, b, c, m, n, k, b_layout, as_stream(stream), bias);
+}
+
 int pto_b200_gemm_f16f32_batched(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
                                  int batch, int64_t a_stride, int64_t b_stride, int64_t c_stride, void *stream)
 {

@@ -245,7 +245,7 @@ gemm_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 } // namespace
 
 int launch_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
-                       cudaStream_t stream)
+                       cudaStream_t stream, const float *bias)
 {
     if (a == nullptr || b == nullptr || c == nullptr || m <= 0 || n <= 0 || k <= 0 || (b_layout != 0 && b_layout != 1)) {
         set_error_text("gemm: bad argument");
@@ -264,7 +264,11 @@ int launch_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, in
         return e != nullptr && strcmp(e, "1cta") == 0;
     }();
     if (!one_block) {
-        return launch_gemm2_f16f32(a, b, c, m, n, k, b_layout, stream);
+        return launch_gemm2_f16f32(a, b, c, m, n, k, b_layout, stream, bias);
+    }
+    if (bias != nullptr) {
+        set_error_text("gemm: the bias form runs on the default kernel only (unset PTO_B200_GEMM_MODE)");
+        return kErrUnsupportedShape;
     }
     CUtensorMap tmap_a, tmap_b;
     int rc = make_tmap_2d(&tmap_a, a, 2, m, k, k, BM, BK, true);

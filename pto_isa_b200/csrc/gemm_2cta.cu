@@ -119,12 +119,15 @@ __device__ __forceinline__ void tc_mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_d
         : "memory");
 }
 
-template <int kBLayout>
+// kMode: bit 0 = layout of B (0: k x n, 1: n x k), bit 1 = the TMATMUL_BIAS epilogue
+template <int kMode>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const __grid_constant__ CUtensorMap tmap_c, int c_by_tma, float *__restrict__ c, int m, int n,
-                    int k, DeviceStatus *status)
+                    const __grid_constant__ CUtensorMap tmap_c, int c_by_tma, float *__restrict__ c,
+                    const float *__restrict__ bias, int m, int n, int k, DeviceStatus *status)
 {
+    constexpr int kBLayout = kMode & 1;
+    constexpr bool kBias = (kMode & 2) != 0;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *staging = smem + kStages * kStageBytes;
@@ -292,6 +295,14 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 tmem_ld_32x32(taddr + cb * 32, r);
                 tmem_ld_wait();
                 const int col0 = tn * BN + cb * 32;
+                if (kBias) {
+                    // TMATMUL_BIAS: one bias value per column, the same for every row (uniform loads)
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float bv = (col0 + j < n) ? __ldg(bias + col0 + j) : 0.0f;
+                        r[j] = __float_as_uint(__uint_as_float(r[j]) + bv);
+                    }
+                }
                 if (c_by_tma) {
                     // the store that last read this slab (two chunks ago) has finished reading it
                     if (lane == 0) {
@@ -371,7 +382,7 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 } // namespace
 
 int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
-                        cudaStream_t stream)
+                        cudaStream_t stream, const float *bias)
 {
     CUtensorMap tmap_a, tmap_b, tmap_c;
     int rc = make_tmap_2d(&tmap_a, a, 2, m, k, k, BM, kBoxK, true);
@@ -405,22 +416,27 @@ int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, i
     if (status == nullptr) {
         return kErrCuda;
     }
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[b_layout]) {
-        rc = check_cuda(b_layout == 1 ? cudaFuncSetAttribute(gemm2_f16f32_kernel<1>,
-                                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)
-                                      : cudaFuncSetAttribute(gemm2_f16f32_kernel<0>,
-                                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
-                        "cudaFuncSetAttribute(gemm, 2 blocks per tile)");
-        if (rc != kOk) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        if ((rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm, 2 blocks per tile)")) != kOk ||
+            (rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm, 2 blocks per tile)")) != kOk ||
+            (rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm, 2 blocks per tile)")) != kOk ||
+            (rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm, 2 blocks per tile)")) != kOk) {
             return rc;
         }
-        attr_set[b_layout] = true;
+        attr_set = true;
     }
-    if (b_layout == 1) {
-        gemm2_f16f32_kernel<1><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, m, n, k, status);
+    const dim3 grid(2 * pairs);
+    if (bias == nullptr) {
+        if (b_layout == 1) {
+            gemm2_f16f32_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, bias, m, n, k, status);
+        } else {
+            gemm2_f16f32_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, bias, m, n, k, status);
+        }
+    } else if (b_layout == 1) {
+        gemm2_f16f32_kernel<3><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, bias, m, n, k, status);
     } else {
-        gemm2_f16f32_kernel<0><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, m, n, k, status);
+        gemm2_f16f32_kernel<2><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, bias, m, n, k, status);
     }
     return check_launch();
 }

@@ -67,12 +67,13 @@ int launch_tcmp(const float *a, const float *b, float *dst, int64_t n, int mode,
 int grid_for(int64_t work_items, int items_per_block);
 
 // GEMM: C[m x n] fp32 = A[m x k] fp16 * B, B given k x n row-major (b_layout 0) or n x k row-major (1)
+// `bias` (optional): n floats added to every row of C (TMATMUL_BIAS)
 int launch_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
-                       cudaStream_t stream);
+                       cudaStream_t stream, const float *bias = nullptr);
 
 // the same product on pairs of thread blocks (cta_group::2); arguments already validated by the caller
 int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
-                        cudaStream_t stream);
+                        cudaStream_t stream, const float *bias = nullptr);
 // MX block-scaled fp8 GEMM (kind::mxf8f6f4): C[m x n] bf16 (or fp32) = (sfa (x) A[m x k]) * (sfb (x) B[n x k])^T, one e8m0
 // scale per 32 k; a_fmt / b_fmt 0 = e4m3, 1 = e5m2.  The workspace receives the scales in the tensor core's atoms.
 size_t mxgemm_workspace_bytes(int m, int n, int k);

@@ -377,13 +377,25 @@ def mx_gemm(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, out=None, fmt=FP8_
     return out
 
 
-def gemm(a, b, b_layout=1, out=None):
+def gemm(a, b, b_layout=1, out=None, bias=None):
     """C[m,n] fp32 = A[m,k] fp16 @ B.  b_layout 0: b is (k, n); 1: b is (n, k), the reference kernel's layout.
-    A 3-D `a` (batch, m, k) with 3-D `b` runs `batch` independent problems."""
+    A 3-D `a` (batch, m, k) with 3-D `b` runs `batch` independent problems.  `bias` (n floats, 2-D problems only) is
+    added to every row: TMATMUL_BIAS."""
     _need_cuda(a, b)
     if a.dtype != torch.float16 or b.dtype != torch.float16:
         raise PtoB200Error("gemm: operands must be float16")
     batched = a.dim() == 3
+    if bias is not None:
+        _need_cuda(bias)
+        n_ = b.shape[-1] if b_layout == 0 else b.shape[-2]
+        if batched or bias.dtype != torch.float32 or bias.numel() != n_:
+            raise PtoB200Error("gemm: bias is n float32 values, for a single problem")
+        out = torch.empty(a.shape[0], n_, dtype=torch.float32, device=a.device) if out is None else out
+        with torch.cuda.device(a.device):
+            rc = lib().pto_b200_gemm_f16f32_bias(_ptr(a), _ptr(b), _ptr(bias), _ptr(out), a.shape[0], n_, a.shape[1],
+                                                 int(b_layout), _stream(a))
+        check(rc, "gemm (bias)")
+        return out
     m, k = a.shape[-2:]
     n = b.shape[-1] if b_layout == 0 else b.shape[-2]
     shape = (a.shape[0], m, n) if batched else (m, n)

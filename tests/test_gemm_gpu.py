@@ -127,3 +127,18 @@ def test_host_batched_pipeline_equals_device_path():
             assert torch.equal(hc[i], pto.gemm(a[i].cuda(), b[i].cuda(), 1).cpu()), (pin, i)
     assert pto.gemm_host_batched(a[:0], b[:0], torch.zeros(0, m, n), 1).shape[0] == 0
     assert pto.device_status() == 0
+
+
+@pytest.mark.parametrize("mnk", [(256, 512, 320), (129, 264, 520), (16, 16, 16)])
+def test_gemm_bias_form(mnk):
+    """TMATMUL_BIAS (include/pto/cpu/TMatmul.hpp:99-116): the product plus one bias value per column; against the
+    oracle's product with the bias added in fp32, and exactly equal to the plain kernel's output plus the bias."""
+    m, n, k = mnk
+    a, b = make(m, n, k, 1, seed=11)
+    bias = np.random.default_rng(5).uniform(-10, 10, n).astype(np.float32)
+    got = host(pto.gemm(dev(a), dev(b), 1, bias=dev(bias)))
+    plain = host(pto.gemm(dev(a), dev(b), 1))
+    assert np.array_equal(got, plain + bias[None, :])
+    want = a.astype(np.float64) @ b.astype(np.float64).T + bias[None, :]
+    ok, worst = rel_err_ok(got, want, 2e-3)
+    assert ok, f"max relative error {worst:.3e}"
