@@ -171,6 +171,11 @@ int64_t pto_b200_mxgemm_workspace_bytes(int m, int n, int k);
 int pto_b200_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *scale_a, const uint8_t *scale_b, void *c, int m,
                         int n, int k, int a_format, int b_format, int out_f32, void *workspace, int64_t workspace_bytes,
                         void *stream);
+/* The same product with packed fp4 operands, the MxMatmul of kernels/manual/a5/matmul_mxfp4_performance: A is m x k and
+ * B is n x k float4_e2m1 values, two per byte with the lower k index in the low nibble (pack_two_fp4,
+ * scripts/gen_data.py:24-34), k / 2 bytes per row; scales, output, workspace and k % 32 == 0 as for the fp8 form. */
+int pto_b200_mxgemm_fp4(const uint8_t *a, const uint8_t *b, const uint8_t *scale_a, const uint8_t *scale_b, void *c, int m,
+                        int n, int k, int out_f32, void *workspace, int64_t workspace_bytes, void *stream);
 /* TMATMUL_BIAS (include/pto/common/pto_instr.hpp:509-527, include/pto/cpu/TMatmul.hpp:99-116): the same product with
  * bias[j] (n floats) added to every element of column j. */
 int pto_b200_gemm_f16f32_bias(const uint16_t *a, const uint16_t *b, const float *bias, float *c, int m, int n, int k,

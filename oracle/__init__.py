@@ -237,6 +237,19 @@ class _Lib:
             raise ValueError("mxgemm: unsupported shape or format")
         return c
 
+    def mxgemm_fp4(self, a, b, sfa, sfb, window=None):
+        """a: (m,k/2), b: (n,k/2) bytes of packed float4_e2m1 (low nibble first); scales as mxgemm_fp8.  Exact sums, fp32."""
+        a, b = np.ascontiguousarray(a, np.uint8), np.ascontiguousarray(b, np.uint8)
+        sfa, sfb = np.ascontiguousarray(sfa, np.uint8), np.ascontiguousarray(sfb, np.uint8)
+        m, n, k = a.shape[0], b.shape[0], 2 * a.shape[1]
+        assert b.shape[1] == a.shape[1] and sfa.shape == (m, k // 32) and sfb.shape == (n, k // 32)
+        r0, r1, c0, c1 = window if window is not None else (0, m, 0, n)
+        c = np.zeros((m, n), np.float32)
+        rc = self._f("mxgemm_fp4_window")(_p(a), _p(b), _p(sfa), _p(sfb), _p(c), m, n, k, r0, r1, c0, c1)
+        if rc != 0:
+            raise ValueError("mxgemm_fp4: unsupported shape")
+        return c
+
     # -- attention (one head)
     def attn_head_f16(self, q, k, v, causal, scale):
         q = np.ascontiguousarray(q, np.float16)

@@ -477,6 +477,38 @@ int pto_oracle_mxgemm_fp8_window(const uint8_t *a, const uint8_t *b, const uint8
     return 0;
 }
 
+/* Packed fp4 form (kernels/manual/a5/matmul_mxfp4_performance/scripts/gen_data.py:24-34,37-66): two float4_e2m1 values per
+ * byte, element 2i in the low nibble and element 2i + 1 in the high nibble; a: m x k/2, b: n x k/2 bytes.
+ * e2m1 codes 0..7 are 0, 0.5, 1, 1.5, 2, 3, 4, 6; bit 3 is the sign. */
+int pto_oracle_mxgemm_fp4_window(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, const uint8_t *sfb, float *c, int m,
+                                 int n, int k, int r0, int r1, int c0, int c1)
+{
+    static const double mag[8] = {0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0};
+    if (k % 32 || r0 < 0 || r1 > m || c0 < 0 || c1 > n) {
+        return -1;
+    }
+    int ks = k / 32, kb = k / 2;
+    for (int i = r0; i < r1; ++i) {
+        for (int j = c0; j < c1; ++j) {
+            double sum = 0.0;
+            for (int blk = 0; blk < ks; ++blk) {
+                double part = 0.0;
+                for (int t = 0; t < 32; ++t) {
+                    int e = blk * 32 + t;
+                    uint8_t ba = a[(int64_t)i * kb + e / 2], bb = b[(int64_t)j * kb + e / 2];
+                    int va = (e & 1) ? (ba >> 4) : (ba & 15), vb = (e & 1) ? (bb >> 4) : (bb & 15);
+                    double x = (va & 8) ? -mag[va & 7] : mag[va & 7], y = (vb & 8) ? -mag[vb & 7] : mag[vb & 7];
+                    part += x * y;
+                }
+                int ea = sfa[(int64_t)i * ks + blk], eb = sfb[(int64_t)j * ks + blk];
+                sum += (ea == 255 || eb == 255) ? NAN : ldexp(part, ea + eb - 254);
+            }
+            c[(int64_t)i * n + j] = (float)sum;
+        }
+    }
+    return 0;
+}
+
 int pto_oracle_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, const uint8_t *sfb, float *c, int m, int n,
                           int k, int a_fmt, int b_fmt)
 {

@@ -332,6 +332,23 @@ int pto_b200_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *scale
                              workspace_bytes < 0 ? 0 : static_cast<size_t>(workspace_bytes), as_stream(stream));
 }
 
+int pto_b200_mxgemm_fp4(const uint8_t *a, const uint8_t *b, const uint8_t *scale_a, const uint8_t *scale_b, void *c, int m,
+                        int n, int k, int out_f32, void *workspace, int64_t workspace_bytes, void *stream)
+{
+    if (a == nullptr || b == nullptr || scale_a == nullptr || scale_b == nullptr || c == nullptr || m <= 0 || n <= 0 ||
+        k <= 0) {
+        return bad("mxgemm_fp4: bad argument");
+    }
+    if ((k % 32) != 0) {
+        return bad("mxgemm_fp4: k must be a multiple of the 32-element scale block");
+    }
+    if ((reinterpret_cast<uintptr_t>(a) & 15u) != 0 || (reinterpret_cast<uintptr_t>(b) & 15u) != 0) {
+        return bad("mxgemm_fp4: A and B must be 16-byte aligned");
+    }
+    return launch_mxgemm_fp4(a, b, scale_a, scale_b, c, m, n, k, out_f32 ? 1 : 0, workspace,
+                             workspace_bytes < 0 ? 0 : static_cast<size_t>(workspace_bytes), as_stream(stream));
+}
+
 int pto_b200_gemm_f16f32_bias(const uint16_t *a, const uint16_t *b, const float *bias, float *c, int m, int n, int k,
                               int b_layout, void *stream)
 {

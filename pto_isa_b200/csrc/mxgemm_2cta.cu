@@ -31,12 +31,13 @@ constexpr int BK = kSpan * kSpans;        // k extent of a stage
 constexpr int kStages = kSpans == 2 ? 3 : 6;
 constexpr int kABytes = BM * BK;          // 16 KiB per span
 constexpr int kBBytes = BNH * BK;         // 16 KiB per span
-constexpr int kSfaBytes = 512;            // 128 rows x 4 scales (one span)
-constexpr int kSfbBytes = 1024;           // 256 rows x 4 scales (each block needs the scales of the whole B tile)
-constexpr int kSfOff = kABytes + kBBytes; // per span: the A atom, then the two B atoms
-constexpr int kSfSpanBytes = kSfaBytes + kSfbBytes;
-constexpr int kStageBytes = ((kSfOff + kSpans * kSfSpanBytes + 1023) / 1024) * 1024;
-constexpr int kTxBytes = kABytes + kBBytes + kSpans * kSfSpanBytes; // per block and stage
+constexpr int kSfOff = kABytes + kBBytes; // per span: the A atoms, then the B atoms
+// A scale atom holds the scales of 128 rows x 128 k (4 per row).  A 128-byte span is 128 k of fp8 = one atom per 128 rows,
+// or 256 k of packed fp4 = two atoms: kAtoms below.
+__host__ __device__ constexpr int sfa_bytes(int atoms) { return 512 * atoms; }        // this block's 128 rows of A
+__host__ __device__ constexpr int sf_span_bytes(int atoms) { return 1536 * atoms; }
+__host__ __device__ constexpr int stage_bytes(int atoms) { return ((kSfOff + kSpans * sf_span_bytes(atoms) + 1023) / 1024) * 1024; }
+__host__ __device__ constexpr int tx_bytes(int atoms) { return kABytes + kBBytes + kSpans * sf_span_bytes(atoms); }
 constexpr int kThreads = 192;             // warp 0 TMA, warp 1 MMA (leader only), warps 2..5 epilogue
 constexpr int kTmemCols = 512;
 // Tensor memory: two accumulators that share 64 columns, [0, 256) and [192, 448), then four scale slots of 16 columns
@@ -47,9 +48,7 @@ constexpr int kTmemCols = 512;
 constexpr int kAccStride = 192;
 constexpr int kAccShared = BN - kAccStride; // 64 columns belong to both accumulators
 constexpr int kSfTmemBase = kAccStride + BN;
-constexpr int kSfSlots = 4;
-constexpr int kSfTmemStride = 16;
-static_assert(kSfTmemBase + kSfSlots * kSfTmemStride <= kTmemCols, "tensor memory layout");
+constexpr int kSfTmemCols = kTmemCols - kSfTmemBase; // 64: four 16-column slots (fp8) or two 32-column slots (fp4)
 
 struct Control {
     uint64_t full[kStages];
@@ -63,7 +62,12 @@ struct Control {
 constexpr int kSlabBytes = 32 * 128; // 32 rows x 128 bytes (64 bf16 or 32 fp32), 128-byte swizzle
 constexpr int kSlabsPerWarp = 1;
 constexpr int kStagingBytes = 4 * kSlabsPerWarp * kSlabBytes;
-constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + sizeof(Control) + 1024;
+__host__ __device__ constexpr int smem_bytes(int atoms)
+{
+    // the fp4 layout fills the 227 KB to the last kilobyte: its buffer is declared 1024-byte aligned instead of being
+    // aligned by hand inside a larger allocation
+    return kStages * stage_bytes(atoms) + kStagingBytes + static_cast<int>(sizeof(Control)) + (atoms == 1 ? 1024 : 0);
+}
 
 constexpr int kGroupN = 8;
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &tm, int &tn)
@@ -145,18 +149,31 @@ __device__ __forceinline__ uint32_t make_idesc_mx(int m, int n, int a_fmt, int b
            (static_cast<uint32_t>(n >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+template <int kAtoms>
 __device__ __forceinline__ void tc_mma_mx_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                                uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate)
 {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
-        "}\n"
-        :
-        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-        : "memory");
+    if (kAtoms == 1) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+            "}\n"
+            :
+            : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+            "}\n"
+            :
+            : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+            : "memory");
+    }
 }
 
 // ---------------------------------------------------------------- scale packing
@@ -214,15 +231,30 @@ __global__ void __launch_bounds__(256) mx_pack_scales_kernel(const uint8_t *__re
     }
 }
 
-template <bool kOutF32>
+// kAtoms 1: fp8 operands (kind::mxf8f6f4, k = 32 per MMA, one scale per row and MMA); 2: packed fp4 e2m1 operands
+// (kind::mxf4, k = 64 per MMA, two scales per row and MMA).  `k` is the row length of A and B in bytes.
+template <bool kOutF32, int kAtoms>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+mxgemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                    const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                    const __grid_constant__ CUtensorMap tmap_c, int c_by_tma, void *__restrict__ c, int m, int n, int k,
                    int a_fmt, int b_fmt, DeviceStatus *status)
 {
-    extern __shared__ uint8_t smem_raw[];
+    constexpr int kStageBytes = stage_bytes(kAtoms);
+    constexpr int kSfaBytes = sfa_bytes(kAtoms);
+    constexpr int kSfSpanBytes = sf_span_bytes(kAtoms);
+    constexpr int kSlotCols = 16 * kAtoms; // 4 columns per atom of A, 8 per atom of B
+    constexpr int kSfSlots = kSfTmemCols / kSlotCols;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    if (kAtoms == 2 && smem != smem_raw) {
+        // no room to realign: report instead of running over the end of the allocation
+        if (threadIdx.x == 0 && atomicCAS(&status->code, 0, kErrCuda) == 0) {
+            status->block = blockIdx.x;
+            status->where = 6;
+        }
+        return;
+    }
     uint8_t *staging = smem + kStages * kStageBytes;
     Control *ctl = reinterpret_cast<Control *>(staging + kStagingBytes);
 
@@ -235,7 +267,7 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const int tiles_n = (n + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
     const int kblocks = (k + BK - 1) / BK;
-    const int kspans = kblocks * kSpans; // scale atoms along k (padded to whole stages by the packing kernel)
+    const int katoms = kblocks * kSpans * kAtoms; // scale atoms along k (padded to whole stages by the packing kernel)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -277,8 +309,8 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 tile_coords(t, tiles_m, tiles_n, tm, tn);
                 const int row0 = tm * 2 * BM + static_cast<int>(rank) * BM; // this block's rows of A and C
                 const int col0 = tn * BN + static_cast<int>(rank) * BNH;    // this block's half of the B tile
-                const int sfa_row0 = (tm * 2 + static_cast<int>(rank)) * kspans;
-                const int sfb_row0 = tn * kspans;
+                const int sfa_row0 = (tm * 2 + static_cast<int>(rank)) * katoms;
+                const int sfb_row0 = tn * katoms;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) {
                         ok = false;
@@ -287,7 +319,7 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     uint8_t *sa = smem + stage * kStageBytes;
                     const uint32_t leader_full = map_to_rank(&ctl->full[stage], 0);
                     if (rank == 0) {
-                        mbar_arrive_expect_tx(&ctl->full[stage], 2 * kTxBytes); // bytes of both blocks
+                        mbar_arrive_expect_tx(&ctl->full[stage], 2 * tx_bytes(kAtoms)); // bytes of both blocks
                     }
 #pragma unroll
                     for (int sp = 0; sp < kSpans; ++sp) {
@@ -295,8 +327,8 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                         tma_load_2d_pair(sa + kABytes + sp * (BNH * kSpan), &tmap_b, leader_full, kb * BK + sp * kSpan,
                                          col0);
                         uint8_t *sf = sa + kSfOff + sp * kSfSpanBytes;
-                        tma_load_2d_pair(sf, &tmap_sfa, leader_full, 0, sfa_row0 + kb * kSpans + sp);
-                        tma_load_2d_pair(sf + kSfaBytes, &tmap_sfb, leader_full, 0, sfb_row0 + kb * kSpans + sp);
+                        tma_load_2d_pair(sf, &tmap_sfa, leader_full, 0, sfa_row0 + (kb * kSpans + sp) * kAtoms);
+                        tma_load_2d_pair(sf + kSfaBytes, &tmap_sfb, leader_full, 0, sfb_row0 + (kb * kSpans + sp) * kAtoms);
                     }
                     if (++stage == kStages) {
                         stage = 0;
@@ -311,7 +343,7 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         // control flow stays warp-uniform and the descriptors of the tcgen05 instructions can be kept in uniform
         // registers instead of being moved there one by one in front of every instruction.
         if (rank == 0) {
-            const uint32_t idesc = make_idesc_mx(2 * BM, BN, a_fmt, b_fmt);
+            const uint32_t idesc = kAtoms == 1 ? make_idesc_mx(2 * BM, BN, a_fmt, b_fmt) : make_idesc_mx(2 * BM, BN, 1, 1);
             uint32_t stage = 0, phase = 0, acc_phase = 0;
             const uint64_t a_desc0 = make_sw128_desc(smem_u32(smem), 16, 1024);
             const uint64_t b_desc0 = make_sw128_desc(smem_u32(smem) + kABytes, 16, 1024);
@@ -346,23 +378,29 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     if (lane == 0) {
 #pragma unroll
                         for (int sp = 0; sp < kSpans; ++sp) {
-                            const uint32_t sfa_tmem =
-                                tmem_base + kSfTmemBase + ((span_ctr + sp) % kSfSlots) * kSfTmemStride;
-                            const uint32_t sfb_tmem = sfa_tmem + 4;
+                            const uint32_t sfa_tmem = tmem_base + kSfTmemBase + ((span_ctr + sp) % kSfSlots) * kSlotCols;
+                            const uint32_t sfb_tmem = sfa_tmem + 4 * kAtoms;
                             const uint64_t sf_off = stage_off + static_cast<uint64_t>((sp * kSfSpanBytes) >> 4);
-                            // the span's scales: one atom for this block's 128 rows of A, two for the 256 rows of B
-                            tc_copy_scales_pair(sfa_tmem, sfa_desc0 + sf_off);
-                            tc_copy_scales_pair(sfb_tmem, sfb_desc0 + sf_off);
-                            tc_copy_scales_pair(sfb_tmem + 4, sfb_desc0 + sf_off + (512 >> 4));
+                            // the span's scales: per atom one copy for this block's 128 rows of A, two for the 256 rows
+                            // of B
+#pragma unroll
+                            for (int at = 0; at < kAtoms; ++at) {
+                                tc_copy_scales_pair(sfa_tmem + at * 4, sfa_desc0 + sf_off + static_cast<uint64_t>((at * 512) >> 4));
+                                tc_copy_scales_pair(sfb_tmem + at * 8, sfb_desc0 + sf_off + static_cast<uint64_t>((at * 1024) >> 4));
+                                tc_copy_scales_pair(sfb_tmem + at * 8 + 4,
+                                                    sfb_desc0 + sf_off + static_cast<uint64_t>((at * 1024 + 512) >> 4));
+                            }
 #pragma unroll
                             for (int kk = 0; kk < kSpan / 32; ++kk) {
-                                // 32 bytes of k per MMA inside the 128-byte span; scale byte kk of the slot's columns
-                                const uint32_t id =
-                                    idesc | (static_cast<uint32_t>(kk) << 29) | (static_cast<uint32_t>(kk) << 4);
+                                // 32 bytes of k per MMA inside the 128-byte span.  fp8: scale byte kk of the atom's
+                                // columns; fp4: atom kk / 2, scale bytes {0, 1} or {2, 3}
+                                const uint32_t sf_id = kAtoms == 1 ? static_cast<uint32_t>(kk) : static_cast<uint32_t>((kk & 1) * 2);
+                                const uint32_t atom = kAtoms == 1 ? 0u : static_cast<uint32_t>(kk >> 1);
+                                const uint32_t id = idesc | (sf_id << 29) | (sf_id << 4);
                                 const uint64_t a_off = stage_off + static_cast<uint64_t>((sp * (BM * kSpan) + kk * 32) >> 4);
                                 const uint64_t b_off = stage_off + static_cast<uint64_t>((sp * (BNH * kSpan) + kk * 32) >> 4);
-                                tc_mma_mx_pair(d_tmem, a_desc0 + a_off, b_desc0 + b_off, id, sfa_tmem, sfb_tmem,
-                                               (kb | sp | kk) != 0 ? 1u : 0u);
+                                tc_mma_mx_pair<kAtoms>(d_tmem, a_desc0 + a_off, b_desc0 + b_off, id, sfa_tmem + atom * 4,
+                                                       sfb_tmem + atom * 8, (kb | sp | kk) != 0 ? 1u : 0u);
                             }
                         }
                         // the stage is reusable in both blocks once these MMAs have read it: one commit, delivered to
@@ -503,24 +541,55 @@ mxgemm2_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 
 } // namespace
 
+// scale atoms (128 k each) along k, padded to whole stages; `fp4`: a stage is 512 k (two spans of 256), else 256 k
+static int mx_atoms_along_k(int k, bool fp4)
+{
+    const int stage_k = fp4 ? 2 * BK : BK;
+    return ((k + stage_k - 1) / stage_k) * (stage_k / 128);
+}
+
 size_t mxgemm_workspace_bytes(int m, int n, int k)
 {
-    const size_t kblocks = static_cast<size_t>((k + BK - 1) / BK) * kSpans; // 128-k scale atoms, whole stages
-    const size_t atoms_a = static_cast<size_t>((m + 127) / 128) * kblocks;
-    const size_t atoms_b = static_cast<size_t>((n + 255) / 256) * 2 * kblocks;
+    // sized for the fp4 form, whose stages are longer (its padding along k is the larger one)
+    const size_t atoms_k = static_cast<size_t>(mx_atoms_along_k(k, true));
+    const size_t atoms_a = static_cast<size_t>((m + 127) / 128) * atoms_k;
+    const size_t atoms_b = static_cast<size_t>((n + 255) / 256) * 2 * atoms_k;
     return (atoms_a + atoms_b) * 512;
 }
 
-int launch_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, const uint8_t *sfb, void *c, int m, int n,
-                      int k, int a_fmt, int b_fmt, int out_f32, void *workspace, size_t workspace_bytes,
-                      cudaStream_t stream)
+template <bool kOutF32, int kAtoms>
+static int launch_mx_kernel(int pairs, cudaStream_t stream, const CUtensorMap &tmap_a, const CUtensorMap &tmap_b,
+                            const CUtensorMap &tmap_sfa, const CUtensorMap &tmap_sfb, const CUtensorMap &tmap_c,
+                            int c_by_tma, void *c, int m, int n, int k_bytes, int a_fmt, int b_fmt, DeviceStatus *status)
+{
+    static bool attr_set = false;
+    if (!attr_set) {
+        const int rc = check_cuda(cudaFuncSetAttribute(mxgemm2_kernel<kOutF32, kAtoms>,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(kAtoms)),
+                                  "cudaFuncSetAttribute(mxgemm)");
+        if (rc != kOk) {
+            return rc;
+        }
+        attr_set = true;
+    }
+    mxgemm2_kernel<kOutF32, kAtoms><<<2 * pairs, kThreads, smem_bytes(kAtoms), stream>>>(
+        tmap_a, tmap_b, tmap_sfa, tmap_sfb, tmap_c, c_by_tma, c, m, n, k_bytes, a_fmt, b_fmt, status);
+    return check_launch();
+}
+
+// `fp4`: A and B hold two e2m1 values per byte (the lower k index in the low nibble), k / 2 bytes per row
+int launch_mxgemm(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, const uint8_t *sfb, void *c, int m, int n, int k,
+                  bool fp4, int a_fmt, int b_fmt, int out_f32, void *workspace, size_t workspace_bytes,
+                  cudaStream_t stream)
 {
     if (workspace == nullptr || workspace_bytes < mxgemm_workspace_bytes(m, n, k) ||
         (reinterpret_cast<uintptr_t>(workspace) & 127u) != 0) {
         set_error_text("mxgemm: the workspace must be 128-byte aligned and hold mxgemm_workspace_bytes(m, n, k) bytes");
         return kErrBadArgument;
     }
-    const int kblocks = ((k + BK - 1) / BK) * kSpans; // 128-k scale atoms along k, padded to whole stages
+    const int kblocks = mx_atoms_along_k(k, fp4); // 128-k scale atoms along k, padded to whole stages
+    const int k_bytes = fp4 ? k / 2 : k;
+    const int atoms = fp4 ? 2 : 1;
     const int rows_a_padded = ((m + 127) / 128) * 128;
     const int rows_b_padded = ((n + 255) / 256) * 256;
     uint8_t *packed_a = static_cast<uint8_t *>(workspace);
@@ -541,12 +610,13 @@ int launch_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, co
         return rc;
     }
     CUtensorMap tmap_a, tmap_b, tmap_sfa, tmap_sfb, tmap_c;
-    if ((rc = make_tmap_2d(&tmap_a, a, 1, m, k, k, BM, kSpan, true)) != kOk ||
-        (rc = make_tmap_2d(&tmap_b, b, 1, n, k, k, BNH, kSpan, true)) != kOk ||
-        (rc = make_tmap_2d(&tmap_sfa, packed_a, 4, static_cast<uint64_t>(rows_a_padded / 128) * kblocks, 128, 128, 1, 128,
-                           false)) != kOk ||
-        (rc = make_tmap_2d(&tmap_sfb, packed_b, 4, static_cast<uint64_t>(rows_b_padded / 256) * kblocks, 256, 256, 1, 256,
-                           false)) != kOk) {
+    // scales: one row of the map per atom (A: 512 bytes) or atom pair (B: 1024 bytes), `atoms` rows per copy
+    if ((rc = make_tmap_2d(&tmap_a, a, 1, m, k_bytes, k_bytes, BM, kSpan, true)) != kOk ||
+        (rc = make_tmap_2d(&tmap_b, b, 1, n, k_bytes, k_bytes, BNH, kSpan, true)) != kOk ||
+        (rc = make_tmap_2d(&tmap_sfa, packed_a, 4, static_cast<uint64_t>(rows_a_padded / 128) * kblocks, 128, 128, atoms,
+                           128, false)) != kOk ||
+        (rc = make_tmap_2d(&tmap_sfb, packed_b, 4, static_cast<uint64_t>(rows_b_padded / 256) * kblocks, 256, 256, atoms,
+                           256, false)) != kOk) {
         return rc;
     }
     const int elem = out_f32 ? 4 : 2;
@@ -568,26 +638,29 @@ int launch_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, co
     if (status == nullptr) {
         return kErrCuda;
     }
-    static bool attr_set = false;
-    if (!attr_set) {
-        if ((rc = check_cuda(cudaFuncSetAttribute(mxgemm2_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                  kSmemBytes),
-                             "cudaFuncSetAttribute(mxgemm)")) != kOk ||
-            (rc = check_cuda(cudaFuncSetAttribute(mxgemm2_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                  kSmemBytes),
-                             "cudaFuncSetAttribute(mxgemm)")) != kOk) {
-            return rc;
-        }
-        attr_set = true;
+    if (fp4) {
+        return out_f32 ? launch_mx_kernel<true, 2>(pairs, stream, tmap_a, tmap_b, tmap_sfa, tmap_sfb, tmap_c, c_by_tma, c, m, n,
+                                                   k_bytes, a_fmt, b_fmt, status)
+                       : launch_mx_kernel<false, 2>(pairs, stream, tmap_a, tmap_b, tmap_sfa, tmap_sfb, tmap_c, c_by_tma, c, m,
+                                                    n, k_bytes, a_fmt, b_fmt, status);
     }
-    if (out_f32) {
-        mxgemm2_fp8_kernel<true><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_sfa, tmap_sfb, tmap_c,
-                                                                             c_by_tma, c, m, n, k, a_fmt, b_fmt, status);
-    } else {
-        mxgemm2_fp8_kernel<false><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_sfa, tmap_sfb, tmap_c,
-                                                                              c_by_tma, c, m, n, k, a_fmt, b_fmt, status);
-    }
-    return check_launch();
+    return out_f32 ? launch_mx_kernel<true, 1>(pairs, stream, tmap_a, tmap_b, tmap_sfa, tmap_sfb, tmap_c, c_by_tma, c, m, n,
+                                               k_bytes, a_fmt, b_fmt, status)
+                   : launch_mx_kernel<false, 1>(pairs, stream, tmap_a, tmap_b, tmap_sfa, tmap_sfb, tmap_c, c_by_tma, c, m, n,
+                                                k_bytes, a_fmt, b_fmt, status);
+}
+
+int launch_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, const uint8_t *sfb, void *c, int m, int n,
+                      int k, int a_fmt, int b_fmt, int out_f32, void *workspace, size_t workspace_bytes,
+                      cudaStream_t stream)
+{
+    return launch_mxgemm(a, b, sfa, sfb, c, m, n, k, false, a_fmt, b_fmt, out_f32, workspace, workspace_bytes, stream);
+}
+
+int launch_mxgemm_fp4(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, const uint8_t *sfb, void *c, int m, int n,
+                      int k, int out_f32, void *workspace, size_t workspace_bytes, cudaStream_t stream)
+{
+    return launch_mxgemm(a, b, sfa, sfb, c, m, n, k, true, 1, 1, out_f32, workspace, workspace_bytes, stream);
 }
 
 } // namespace pto_b200

@@ -377,6 +377,35 @@ def mx_gemm(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, out=None, fmt=FP8_
     return out
 
 
+def mx_gemm_fp4(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, out=None, workspace=None):
+    """C[m,n] = (scale_a (x) A[m,k]) @ (scale_b (x) B[n,k])^T with packed float4_e2m1 operands: a is (m, k/2) and b is
+    (n, k/2) uint8, two values per byte, the lower k index in the low nibble (the reference's MXFP4 MxMatmul,
+    kernels/manual/a5/matmul_mxfp4_performance); scales as for mx_gemm."""
+    _need_cuda(a, b, scale_a, scale_b)
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1] or a.dtype.itemsize != 1 or b.dtype.itemsize != 1:
+        raise PtoB200Error("mx_gemm_fp4: a is (m, k/2) and b is (n, k/2) bytes")
+    m, n, k = a.shape[0], b.shape[0], 2 * a.shape[1]
+    if k % 32 != 0 or tuple(scale_a.shape) != (m, k // 32) or tuple(scale_b.shape) != (n, k // 32):
+        raise PtoB200Error("mx_gemm_fp4: k must be a multiple of 32 and the scales (m, k/32) and (n, k/32)")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise PtoB200Error("mx_gemm_fp4: the output is bfloat16 or float32")
+    out = torch.empty(m, n, dtype=out_dtype, device=a.device) if out is None else out
+    _need_cuda(out)
+    need = lib().pto_b200_mxgemm_workspace_bytes(m, n, k)
+    if workspace is None:
+        key = (a.device.index, torch.cuda.current_stream(a.device).cuda_stream)
+        workspace = _mx_workspaces.get(key)
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+            _mx_workspaces[key] = workspace
+    with torch.cuda.device(a.device):
+        rc = lib().pto_b200_mxgemm_fp4(_ptr(a), _ptr(b), _ptr(scale_a), _ptr(scale_b), _ptr(out), m, n, k,
+                                       1 if out_dtype == torch.float32 else 0, _ptr(workspace), workspace.numel(),
+                                       _stream(a))
+    check(rc, "mx_gemm_fp4")
+    return out
+
+
 def gemm(a, b, b_layout=1, out=None, bias=None):
     """C[m,n] fp32 = A[m,k] fp16 @ B.  b_layout 0: b is (k, n); 1: b is (n, k), the reference kernel's layout.
     A 3-D `a` (batch, m, k) with 3-D `b` runs `batch` independent problems.  `bias` (n floats, 2-D problems only) is

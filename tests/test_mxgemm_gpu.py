@@ -135,3 +135,52 @@ def test_mxgemm_full_size_sampled_tiles():
     c32 = pto.mx_gemm(da, db, dsa, dsb, torch.float32)
     assert torch.equal(pto.mx_gemm(da, db, dsa, dev(sb + 1), torch.float32), 2 * c32)
     assert torch.equal(c32.bfloat16(), c)
+
+
+# ---------------------------------------------------------------- packed fp4 (float4_e2m1) operands
+def make_fp4(m, n, k, seed, full_range=True):
+    """Packed e2m1 bytes.  full_range: all 16 codes; otherwise the reference generator's values {-1, 0, 1}
+    (kernels/manual/a5/matmul_mxfp4_performance/scripts/gen_data.py:44-45)."""
+    r = np.random.default_rng(seed)
+    if full_range:
+        a = r.integers(0, 256, (m, k // 2)).astype(np.uint8)
+        b = r.integers(0, 256, (n, k // 2)).astype(np.uint8)
+    else:
+        code = np.array([0xA, 0x0, 0x2], np.uint8)  # -1, 0, 1
+        ea, eb = code[r.integers(0, 3, (m, k))], code[r.integers(0, 3, (n, k))]
+        a = (ea[:, 0::2] | (ea[:, 1::2] << 4)).astype(np.uint8)
+        b = (eb[:, 0::2] | (eb[:, 1::2] << 4)).astype(np.uint8)
+    sa = r.integers(127, 130, (m, k // 32)).astype(np.uint8)
+    sb = r.integers(127, 130, (n, k // 32)).astype(np.uint8)
+    sa[:, (k // 64):] = r.integers(120, 134, sa[:, (k // 64):].shape).astype(np.uint8)
+    return a, b, sa, sb
+
+
+@pytest.mark.parametrize("full_range", [False, True])
+@pytest.mark.parametrize("mnk", [(256, 256, 512), (256, 256, 256), (128, 256, 1024), (512, 768, 2048), (300, 200, 1184), (1, 8, 32)])
+def test_mxgemm_fp4_matches_oracle(mnk, full_range):
+    """Positions matter here: every k block carries its own pair of scales, so a wrong nibble order, scale byte or
+    scale atom shows as an error far above the tolerance."""
+    m, n, k = mnk
+    a, b, sa, sb = make_fp4(m, n, k, seed=m + n + k, full_range=full_range)
+    want = port.mxgemm_fp4(a, b, sa, sb)
+    got32 = host(pto.mx_gemm_fp4(dev(a), dev(b), dev(sa), dev(sb), torch.float32))
+    ok, worst = rel_err_ok(got32, want, 2e-3)
+    assert ok, f"max relative error {worst:.3e}"
+    got16 = host(pto.mx_gemm_fp4(dev(a), dev(b), dev(sa), dev(sb), torch.bfloat16).view(torch.int16)).view(np.uint16)
+    check_bf16(got16, want)
+    assert pto.device_status() == 0
+
+
+def test_mxgemm_fp4_full_size_sampled_tiles():
+    """6144^3 (the reference's MXFP4 configuration): sampled 64 x 64 windows against the oracle at full k."""
+    m = n = k = 6144
+    a, b, sa, sb = make_fp4(m, n, k, seed=61, full_range=True)
+    c = pto.mx_gemm_fp4(dev(a), dev(b), dev(sa), dev(sb), torch.bfloat16)
+    assert pto.device_status() == 0
+    r = np.random.default_rng(2)
+    for _ in range(3):
+        r0, c0 = int(r.integers(0, m // 64)) * 64, int(r.integers(0, n // 64)) * 64
+        want = port.mxgemm_fp4(a, b, sa, sb, window=(r0, r0 + 64, c0, c0 + 64))[r0:r0 + 64, c0:c0 + 64]
+        got = host(c[r0:r0 + 64, c0:c0 + 64].contiguous().view(torch.int16)).view(np.uint16)
+        check_bf16(got, want)
