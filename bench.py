@@ -346,7 +346,23 @@ def extras(torch, pto, peaks, peak_kind):
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": 4500.0, "unit": "TFLOP/s", "frac": tf / 4500.0,
                              "peak_kind": "nominal dense fp8 (no fp8 peak was measured on this pool)",
                              "vs_measured_bf16_burst": tf / peaks["bf16_tflops"]}})
-    del mxa, mxb, mxsa, mxsb, mxc
+    # the same with packed fp4 (e2m1) operands: the reference's MXFP4 MxMatmul configuration (6144^3, bf16 output)
+    fa = [x[:, : mm // 2].contiguous() for x in mxa]
+    fb = [x[:, : mm // 2].contiguous() for x in mxb]
+
+    def mx4_step():
+        j = mx_i[0] % sets_mx
+        mx_i[0] += 1
+        pto.mx_gemm_fp4(fa[j], fb[j], mxsa[j], mxsb[j], torch.bfloat16, out=mxc)
+
+    ms = bench(mx4_step, 4, 20)
+    tf = 2.0 * mm ** 3 / ms / 1e9
+    out.append({"workload": "MX fp4 GEMM (packed e2m1, e8m0 scales per 32 k, bf16 out) 6144^3", "value": tf,
+                "unit": "TFLOP/s", "ms": ms,
+                "roofline": {"bound": "tensor", "achieved": tf, "peak": 9000.0, "unit": "TFLOP/s", "frac": tf / 9000.0,
+                             "peak_kind": "nominal dense fp4 (no fp4 peak was measured on this pool)",
+                             "vs_measured_bf16_burst": tf / peaks["bf16_tflops"]}})
+    del mxa, mxb, mxsa, mxsb, mxc, fa, fb
     n = 1 << 24
     sets = 6
     xs = [torch.randn(n, device="cuda", generator=g) for _ in range(sets)]

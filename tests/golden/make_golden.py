@@ -366,6 +366,29 @@ def gen_mxgemm(ref, tmp, out):
     np.savez_compressed(os.path.join(out, "mxgemm.npz"), **saved)
 
 
+def gen_mxgemm_fp4(ref, tmp, out):
+    """MXFP4 form: packed inputs, scales and golden written by the reference's generator
+    (kernels/manual/a5/matmul_mxfp4_performance/scripts/gen_data.py:24-80) for a 128 x 512 x 256 (m, k, n) problem.
+    The generator imports the `en_dtypes` package for its float4 types; that package is not in this image, so the
+    module name is bound to a stand-in whose float4_e2m1 is ml_dtypes.float4_e2m1fn - the same E2M1 format, one value
+    per byte in the low four bits, which is all pack_two_fp4 (:24-34) relies on."""
+    import types
+
+    import ml_dtypes
+    sys.modules.setdefault("en_dtypes", types.SimpleNamespace(float4_e2m1=ml_dtypes.float4_e2m1fn,
+                                                              float4_e1m2=ml_dtypes.float4_e2m1fn))
+    mod = load(os.path.join(ref, "kernels/manual/a5/matmul_mxfp4_performance/scripts/gen_data.py"), "ref_mx4_gen")
+    m, k, n = 128, 512, 256
+    d = in_case_dir(tmp, "mxgemm_fp4")
+    mod.gen_golden_data(mod.MxMatmulParams(mod.fp4_e2m1x2, mod.fp4_e2m1x2, mod.bfloat16, m, k, n, False))
+    np.savez_compressed(os.path.join(out, "mxgemm_fp4.npz"),
+                        a=read(os.path.join(d, "input/x1_gm.bin"), np.uint8, (m, k // 2)),
+                        b=read(os.path.join(d, "input/x2_gm.bin"), np.uint8, (n, k // 2)),
+                        scale_a=read(os.path.join(d, "input/x1_scale_gm.bin"), np.uint8, (m, k // 32)),
+                        scale_b=read(os.path.join(d, "input/x2_scale_gm.bin"), np.uint8, (n, k // 32)),
+                        golden_bf16_bits=read(os.path.join(d, "output/golden.bin"), np.uint16, (m, n)))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -373,7 +396,7 @@ def main():
     cwd = os.getcwd()
     with tempfile.TemporaryDirectory() as tmp:
         try:
-            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm, gen_vector2, gen_harness, gen_mla, gen_mxgemm):
+            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm, gen_vector2, gen_harness, gen_mla, gen_mxgemm, gen_mxgemm_fp4):
                 os.chdir(tmp)
                 fn(args.reference, tmp, HERE)
         finally:

@@ -184,3 +184,26 @@ def test_mxgemm_fp4_full_size_sampled_tiles():
         want = port.mxgemm_fp4(a, b, sa, sb, window=(r0, r0 + 64, c0, c0 + 64))[r0:r0 + 64, c0:c0 + 64]
         got = host(c[r0:r0 + 64, c0:c0 + 64].contiguous().view(torch.int16)).view(np.uint16)
         check_bf16(got, want)
+
+
+def test_mxgemm_fp4_reference_golden(golden_dir):
+    z = np.load(os.path.join(golden_dir, "mxgemm_fp4.npz"))
+    got = pto.mx_gemm_fp4(dev(z["a"]), dev(z["b"]), dev(z["scale_a"]), dev(z["scale_b"]), torch.bfloat16)
+    bits = host(got.view(torch.int16)).view(np.uint16)
+    assert result_cmp(bf16_bits_to_f32(z["golden_bf16_bits"]), bf16_bits_to_f32(bits), 1e-3)
+    assert (bits != z["golden_bf16_bits"]).mean() <= 5e-3
+
+
+def test_mxgemm_fp4_reference_shape_sampled_windows():
+    """m 2040, k 8192, n 8100: the ragged configuration of the reference's MXFP4 example (scripts/gen_data.py:100);
+    windows that include the last rows and columns, and a guard row."""
+    m, k, n = 2040, 8192, 8100
+    a, b, sa, sb = make_fp4(m, n, k, seed=2040, full_range=False)
+    c = torch.full((m + 1, n), 7.0, device="cuda", dtype=torch.bfloat16)
+    pto.mx_gemm_fp4(dev(a), dev(b), dev(sa), dev(sb), torch.bfloat16, out=c[:m])
+    assert pto.device_status() == 0 and bool((c[m] == 7.0).all())
+    for r0, c0 in ((0, 0), (m - 40, n - 36), (1024, 4096)):
+        r1, c1 = min(m, r0 + 40), min(n, c0 + 36)
+        want = port.mxgemm_fp4(a, b, sa, sb, window=(r0, r1, c0, c1))[r0:r1, c0:c1]
+        got = host(c[r0:r1, c0:c1].contiguous().view(torch.int16)).view(np.uint16)
+        check_bf16(got, want)

@@ -335,3 +335,28 @@ def test_mxgemm_oracle_fp8_decoding_against_torch():
         assert np.array_equal(np.isnan(got), np.isnan(want))
         ok = ~np.isnan(want)
         assert np.array_equal(got[ok], want[ok])
+
+
+def test_mxgemm_fp4_oracle_matches_reference_generator(golden_dir):
+    """Packed fp4 form: nibble order, e2m1 decoding and scale handling of the restatement against the golden of the
+    reference's generator (kernels/manual/a5/matmul_mxfp4_performance/scripts/gen_data.py), bit for bit in bfloat16."""
+    z = np.load(os.path.join(golden_dir, "mxgemm_fp4.npz"))
+    c = port.mxgemm_fp4(z["a"], z["b"], z["scale_a"], z["scale_b"])
+    u = c.view(np.uint32).astype(np.uint64)
+    bits = ((u + 0x7fff + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    assert np.array_equal(bits, z["golden_bf16_bits"])
+
+
+def test_mxgemm_fp4_oracle_decodes_all_codes():
+    """All 16 e2m1 codes in both nibble positions against ml_dtypes' float4_e2m1fn."""
+    ml_dtypes = pytest.importorskip("ml_dtypes")
+    codes = np.arange(16, dtype=np.uint8)
+    want = codes.view(ml_dtypes.float4_e2m1fn).astype(np.float32)
+    one = np.zeros((1, 16), np.uint8)
+    s = np.full((16, 1), 127, np.uint8)
+    for pos in (0, 1):
+        a = np.zeros((16, 16), np.uint8)
+        a[:, 0] = codes << (4 * pos)
+        one[0, 0] = 0x2 << (4 * pos)  # 1.0 in the same position
+        got = port.mxgemm_fp4(a, one, s, s[:1])[:, 0]
+        assert np.array_equal(got, want), pos
