@@ -789,6 +789,53 @@ PTO_INST RecordEvent TTRANS(TileDataDst &dst, TileDataSrc &src, TileDataTmp &tmp
     return {};
 }
 
+// ---------------------------------------------------------------- TTRI (include/pto/cpu/TTRI.hpp:30-77)
+// isUpperOrLower 0: one where c <= r + diagonal; 1: one where c >= r + diagonal; zero elsewhere in the valid region
+template <typename TileData, int isUpperOrLower, typename... WaitEvents>
+PTO_INST RecordEvent TTRI(TileData &dst, int diagonal, WaitEvents &... events)
+{
+    static_assert(isUpperOrLower == 0 || isUpperOrLower == 1, "TTRI: isUpperOrLower must be 0 or 1");
+    static_assert(TileData::isRowMajor, "TTRI: row-major tiles only");
+#if PTO_B200_DEVICE_CODE
+    using T = typename TileData::DType;
+    const int vr = dst.GetValidRow(), vc = dst.GetValidCol();
+    for (int i = threadIdx.x; i < vr * vc; i += blockDim.x) {
+        const int r = i / vc, c = i - r * vc;
+        const bool in = isUpperOrLower ? (c >= r + diagonal) : (c <= r + diagonal);
+        dst.data()[b200::vec_offset<TileData>(r, c)] = in ? b200::convert<T, float>(1.0f, RoundMode::CAST_RINT)
+                                                          : b200::convert<T, float>(0.0f, RoundMode::CAST_RINT);
+    }
+    __syncthreads();
+#endif
+    return {};
+}
+
+// ---------------------------------------------------------------- TRESHAPE (include/pto/cpu/TReshape.hpp:18-56)
+// The same bytes under another tile type of the same location and total size.  The simulation copies the storage; here
+// both tiles are handles into one arena, so the bytes are copied only when the handles differ.
+template <typename TileDataOut, typename TileDataIn, typename... WaitEvents>
+PTO_INST RecordEvent TRESHAPE(TileDataOut &dst, TileDataIn &src, WaitEvents &... events)
+{
+    static_assert(TileDataOut::Loc == TileDataIn::Loc, "TRESHAPE: source and target TileType must be the same");
+    static_assert(sizeof(typename TileDataOut::DType) * TileDataOut::Rows * TileDataOut::Cols ==
+                      sizeof(typename TileDataIn::DType) * TileDataIn::Rows * TileDataIn::Cols,
+                  "TRESHAPE: total byte size must match");
+    static_assert(TileDataOut::Loc == TileType::Vec, "TRESHAPE: vector tiles");
+#if PTO_B200_DEVICE_CODE
+    constexpr int kBytes = sizeof(typename TileDataIn::DType) * TileDataIn::Rows * TileDataIn::Cols;
+    static_assert(kBytes % 4 == 0, "TRESHAPE: tile storage is a multiple of 4 bytes");
+    const uint32_t *s = reinterpret_cast<const uint32_t *>(src.data());
+    uint32_t *d = reinterpret_cast<uint32_t *>(dst.data());
+    if (s != d) {
+        for (int i = threadIdx.x; i < kBytes / 4; i += blockDim.x) {
+            d[i] = s[i];
+        }
+    }
+    __syncthreads();
+#endif
+    return {};
+}
+
 // ---------------------------------------------------------------- TSEL (include/pto/cpu/TSel.hpp:22-57)
 // the mask tile's bytes are consumed bit by bit, least significant first, row-major over dst's valid region; the
 // mask bytes themselves are walked row by row over the mask tile's valid columns

@@ -68,7 +68,9 @@ extern "C" {
 
 /* ---- library state ------------------------------------------------------------------------------ */
 
-/* ABI version of this header. */
+/* ABI version of this header (2: second batch of vector ops; 3: MX block-scaled GEMM, TMATMUL_BIAS form, TTRI);
+ * pto_b200_version() returns the version the library was built from. */
+#define PTO_B200_ABI_VERSION 3
 int pto_b200_version(void);
 /* Text of the last error raised on the calling thread ("" if none). */
 const char *pto_b200_last_error(void);
@@ -148,6 +150,16 @@ int pto_b200_tcmps_f32(const float *src, float scalar, uint8_t *dst_bits, int64_
 /* TCMP as the CPU simulation defines it: dst[i] = 1.0f or 0.0f from the plain comparison of a[i] and b[i]
  * (include/pto/common/pto_instr.hpp:151-157, include/pto/cpu/ElementTileOp.h:177-184, ElementOp.h:227-254). */
 int pto_b200_tcmp_f32(const float *a, const float *b, float *dst, int64_t n, int mode, void *stream);
+
+/* TTRI<Tile, isUpperOrLower>(dst, diagonal) (include/pto/common/pto_instr.hpp:817-823, include/pto/cpu/TTRI.hpp:30-77):
+ * a rows x cols row-major tile of ones and zeros; lower (upper 0): one where c <= r + diagonal; upper (1): one where
+ * c >= r + diagonal.  dtype: the element type whose "one" is written.  (TRESHAPE, pto_instr.hpp:999-1004, moves no data:
+ * it is the same bytes under another tile shape, i.e. the same device pointer.) */
+#define PTO_B200_DTYPE_F32 0
+#define PTO_B200_DTYPE_I32 1
+#define PTO_B200_DTYPE_F16 2
+#define PTO_B200_DTYPE_I16 3
+int pto_b200_ttri(void *dst, int rows, int cols, int diagonal, int upper, int dtype, void *stream);
 
 /* ---- GEMM --------------------------------------------------------------------------------------- */
 

@@ -195,6 +195,16 @@ class _Lib:
             raise ValueError("tcmp: unsupported shape")
         return out
 
+    def ttri_f32(self, rows, cols, diagonal, upper):
+        out = np.empty((rows, cols), np.float32)
+        if self.prefix == "pto_ref_":
+            rc = self._f("ttri_f32")(_p(out), rows, cols, int(diagonal), int(upper))
+        else:
+            rc = self._f("ttri_b32")(_p(out), rows, cols, int(diagonal), int(upper), ctypes.c_uint32(0x3f800000))
+        if rc != 0:
+            raise ValueError("ttri: unsupported shape")
+        return out
+
     # -- GEMM
     def gemm_f16f32(self, a, b, b_layout):
         """a: (m,k) fp16; b: (k,n) fp16 when b_layout == 0, (n,k) when 1.  Returns (m,n) fp32."""

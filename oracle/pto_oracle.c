@@ -411,6 +411,20 @@ int pto_oracle_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m
     return pto_oracle_gemm_f16f32_window(a, b, c, m, n, k, b_layout, 0, m, 0, n);
 }
 
+/* ------------------------------------------------------------------ TTRI
+ * include/pto/cpu/TTRI.hpp:30-77: lower (upper == 0): dst[r, c] = 1 for c <= r + diagonal, else 0; upper: dst[r, c] = 1
+ * for c >= r + diagonal, else 0.  "1" is the element type's one: 32-bit words (float 1.0f or integer 1) are passed in. */
+int pto_oracle_ttri_b32(uint32_t *dst, int rows, int cols, int diagonal, int upper, uint32_t one)
+{
+    for (int r = 0; r < rows; ++r) {
+        for (int c = 0; c < cols; ++c) {
+            int in = upper ? (c >= r + diagonal) : (c <= r + diagonal);
+            dst[(int64_t)r * cols + c] = in ? one : 0u;
+        }
+    }
+    return 0;
+}
+
 /* ------------------------------------------------------------------ MX block-scaled fp8 GEMM
  * C = (scaleA (x) A) * (scaleB (x) B)^T as kernels/manual/a5/matmul_mxfp8_performance/scripts/gen_data.py:27-52
  * computes its golden: every fp8 element is multiplied by 2^(scale byte - 127) of its 32-element k block, the

@@ -208,4 +208,20 @@ int pto_ref_tcmp_f32(const float *a, const float *b, float *dst, int rows, int c
     return 0;
 }
 
+// TTRI on a rows x cols valid corner of the 64 x 256 float tile (tests/cpu/st/testcase/ttri/ttri_kernel.cpp pattern)
+int pto_ref_ttri_f32(float *dst, int rows, int cols, int diagonal, int upper)
+{
+    if (!fits(rows, cols) || rows == 0 || cols == 0) {
+        return -1;
+    }
+    auto z = std::make_unique<MatTile>(rows, cols);
+    if (upper) {
+        TTRI<MatTile, 1>(*z, diagonal);
+    } else {
+        TTRI<MatTile, 0>(*z, diagonal);
+    }
+    drain(dst, *z, rows, cols);
+    return 0;
+}
+
 } // extern "C"

@@ -92,7 +92,7 @@ extern "C" {
 
 int pto_b200_version(void)
 {
-    return 2; // 2: second batch of vector ops (row-expand family, column reductions, TFILLPAD, TTRANS, TSEL, TCMP*)
+    return PTO_B200_ABI_VERSION;
 }
 
 const char *pto_b200_last_error(void)
@@ -330,6 +330,23 @@ int pto_b200_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *scale
     }
     return launch_mxgemm_fp8(a, b, scale_a, scale_b, c, m, n, k, a_format, b_format, out_f32 ? 1 : 0, workspace,
                              workspace_bytes < 0 ? 0 : static_cast<size_t>(workspace_bytes), as_stream(stream));
+}
+
+int pto_b200_ttri(void *dst, int rows, int cols, int diagonal, int upper, int dtype, void *stream)
+{
+    if (dst == nullptr || rows < 0 || cols < 0 || (upper != 0 && upper != 1)) {
+        return bad("ttri: bad argument");
+    }
+    uint32_t one;
+    int bytes;
+    switch (dtype) {
+        case PTO_B200_DTYPE_F32: one = 0x3f800000u; bytes = 4; break;
+        case PTO_B200_DTYPE_I32: one = 1u; bytes = 4; break;
+        case PTO_B200_DTYPE_F16: one = 0x3c00u; bytes = 2; break;
+        case PTO_B200_DTYPE_I16: one = 1u; bytes = 2; break;
+        default: return bad("ttri: dtype is one of PTO_B200_DTYPE_F32 / I32 / F16 / I16");
+    }
+    return launch_ttri(dst, rows, cols, diagonal, upper, one, bytes, as_stream(stream));
 }
 
 int pto_b200_mxgemm_fp4(const uint8_t *a, const uint8_t *b, const uint8_t *scale_a, const uint8_t *scale_b, void *c, int m,

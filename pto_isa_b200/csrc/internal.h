@@ -74,6 +74,10 @@ int launch_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, in
 // the same product on pairs of thread blocks (cta_group::2); arguments already validated by the caller
 int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
                         cudaStream_t stream, const float *bias = nullptr);
+// TTRI: rows x cols tile of `one_bits` (the element type's one) inside the lower / upper triangle, zero outside
+int launch_ttri(void *dst, int rows, int cols, int diagonal, int upper, uint32_t one_bits, int elem_bytes,
+                cudaStream_t stream);
+
 // MX block-scaled fp8 GEMM (kind::mxf8f6f4): C[m x n] bf16 (or fp32) = (sfa (x) A[m x k]) * (sfb (x) B[n x k])^T, one e8m0
 // scale per 32 k; a_fmt / b_fmt 0 = e4m3, 1 = e5m2.  The workspace receives the scales in the tensor core's atoms.
 size_t mxgemm_workspace_bytes(int m, int n, int k);

@@ -375,6 +375,55 @@ AICORE inline void ProgVector2(Vector2Out o, __gm__ float *a_in, __gm__ float *b
     store_w(o.cmp);
 }
 
+// ---------------------------------------------------------------- causal mask by TTRI, TRESHAPE
+// The mask construction of the reference's streaming softmax (kernels/manual/common/flash_atten/pto_macro_fa_softmax.hpp:
+// 64-79: an upper-triangular tile of ones times the lowest float, added to the logits), a lower-triangular tile, and the
+// masked tile seen as 128 x 64 by TRESHAPE with its row maxima.
+AICORE inline void ProgTriReshape(__gm__ float *masked_out, __gm__ float *tril_out, __gm__ float *rowmax_out,
+                                  __gm__ float *x_in, int diagonal)
+{
+    constexpr int R = 64, C = 128;
+    using G = GlobalTensor<float, Shape<1, 1, 1, R, C>, Stride<1, 1, 1, C, 1>>;
+    using GCol = GlobalTensor<float, Shape<1, 1, 1, 2 * R, 1>, Stride<1, 1, 1, 1, 2 * R>, Layout::DN>;
+    using X = Tile<TileType::Vec, float, R, C, BLayout::RowMajor>;
+    using XR = Tile<TileType::Vec, float, 2 * R, C / 2, BLayout::RowMajor>;
+    using Col1 = Tile<TileType::Vec, float, 2 * R, 1, BLayout::ColMajor, DYNAMIC, 1>;
+    constexpr uint32_t kTile = R * C * sizeof(float);
+    X x, mask, w;
+    XR reshaped, tmp;
+    Col1 rmax(2 * R);
+    TASSIGN(x, 0x0);
+    TASSIGN(mask, kTile);
+    TASSIGN(w, 2 * kTile);
+    TASSIGN(reshaped, 3 * kTile);
+    TASSIGN(tmp, kTile); // the mask tile's storage is free again when the row maxima are taken
+    TASSIGN(rmax, 4 * kTile);
+    G gx(x_in), gw(masked_out), gt(tril_out);
+    GCol gm(rowmax_out);
+    TLOAD(x, gx);
+    set_flag(PIPE_MTE2, PIPE_V, EVENT_ID0);
+    wait_flag(PIPE_MTE2, PIPE_V, EVENT_ID0);
+    TTRI<X, 1>(mask, diagonal);
+    TMULS(mask, mask, -3.40282e38f);
+    TADD(w, x, mask);
+    set_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    wait_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    TSTORE(gw, w);
+    set_flag(PIPE_MTE3, PIPE_V, EVENT_ID0);
+    wait_flag(PIPE_MTE3, PIPE_V, EVENT_ID0);
+    TTRI<X, 0>(mask, -2);
+    set_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    wait_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    TSTORE(gt, mask);
+    set_flag(PIPE_MTE3, PIPE_V, EVENT_ID0);
+    wait_flag(PIPE_MTE3, PIPE_V, EVENT_ID0);
+    TRESHAPE(reshaped, w);
+    TROWMAX(rmax, reshaped, tmp);
+    set_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    wait_flag(PIPE_V, PIPE_MTE3, EVENT_ID0);
+    TSTORE(gm, rmax);
+}
+
 // ---------------------------------------------------------------- a multi-latent-attention head
 // The instruction sequence of the reference's MLA demo (demos/cpu/mla_attention_demo/mla_attention_demo.cpp:326-376:
 // latent projections, K_lat^T by TTRANS, scaled scores, row softmax, context, output projection) with fp16 matrix
@@ -616,6 +665,15 @@ int pto_prog_vector2_64x128(void *const *outs, const float *a, const float *b, c
     return pto::b200::launch(1, stream, [=] __device__() {
                ProgVector2(o, const_cast<float *>(a), const_cast<float *>(b), const_cast<float *>(s), valid_rows,
                            valid_cols);
+           }) == cudaSuccess
+               ? 0
+               : 3;
+}
+
+int pto_prog_tri_reshape_64x128(float *masked, float *tril, float *rowmax, const float *x, int diagonal, void *stream)
+{
+    return pto::b200::launch(1, stream, [=] __device__() {
+               ProgTriReshape(masked, tril, rowmax, const_cast<float *>(x), diagonal);
            }) == cudaSuccess
                ? 0
                : 3;

@@ -383,6 +383,21 @@ __global__ void __launch_bounds__(256) ttrans4_vec_kernel(const float *__restric
     }
 }
 
+// ---------------------------------------------------------------- TTRI: triangular 0 / 1 tile
+// lower: one for c <= r + diagonal; upper: one for c >= r + diagonal (include/pto/cpu/TTRI.hpp:30-77)
+template <typename T>
+__global__ void __launch_bounds__(kThreads) ttri_kernel(T *__restrict__ dst, int rows, int cols, int diagonal, int upper,
+                                                        T one)
+{
+    const int64_t n = static_cast<int64_t>(rows) * cols;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const int r = static_cast<int>(i / cols), c = static_cast<int>(i - static_cast<int64_t>(r) * cols);
+        const bool in = upper ? (c >= r + diagonal) : (c <= r + diagonal);
+        dst[i] = in ? one : T(0);
+    }
+}
+
 // ---------------------------------------------------------------- TSEL: one mask byte (8 elements) per thread
 template <typename T>
 __global__ void __launch_bounds__(kThreads) tsel_kernel(const uint8_t *__restrict__ mask, const T *__restrict__ a,
@@ -656,6 +671,22 @@ int launch_ttrans(const void *src, void *dst, int rows, int cols, int elem_bytes
     } else {
         ttrans_kernel<uint16_t><<<grid, 256, 0, stream>>>(static_cast<const uint16_t *>(src), static_cast<uint16_t *>(dst),
                                                           rows, cols);
+    }
+    return check_launch();
+}
+
+int launch_ttri(void *dst, int rows, int cols, int diagonal, int upper, uint32_t one_bits, int elem_bytes,
+                cudaStream_t stream)
+{
+    if (rows == 0 || cols == 0) {
+        return kOk;
+    }
+    const int grid = grid_for(static_cast<int64_t>(rows) * cols, kThreads);
+    if (elem_bytes == 4) {
+        ttri_kernel<uint32_t><<<grid, kThreads, 0, stream>>>(static_cast<uint32_t *>(dst), rows, cols, diagonal, upper, one_bits);
+    } else {
+        ttri_kernel<uint16_t><<<grid, kThreads, 0, stream>>>(static_cast<uint16_t *>(dst), rows, cols, diagonal, upper,
+                                                             static_cast<uint16_t>(one_bits));
     }
     return check_launch();
 }

@@ -331,6 +331,30 @@ def TCMP(a, b, mode, out=None):
     return out
 
 
+_TRI_DTYPES = {torch.float32: 0, torch.int32: 1, torch.float16: 2, torch.int16: 3}
+
+
+def TTRI(rows, cols, diagonal=0, upper=False, dtype=torch.float32, device="cuda", out=None):
+    """rows x cols tile of ones inside the lower (c <= r + diagonal) or upper (c >= r + diagonal) triangle, zeros outside."""
+    if dtype not in _TRI_DTYPES:
+        raise PtoB200Error("TTRI: float32, int32, float16 or int16")
+    out = torch.empty(rows, cols, dtype=dtype, device=device) if out is None else out
+    _need_cuda(out)
+    with torch.cuda.device(out.device):
+        rc = lib().pto_b200_ttri(_ptr(out), int(rows), int(cols), int(diagonal), 1 if upper else 0, _TRI_DTYPES[dtype],
+                                 _stream(out))
+    check(rc, "TTRI")
+    return out
+
+
+def TRESHAPE(src, rows, cols):
+    """The same bytes under another 2-D shape (include/pto/cpu/TReshape.hpp:18-56): a view, no kernel."""
+    _need_cuda(src)
+    if src.numel() != rows * cols:
+        raise PtoB200Error("TRESHAPE: the total size must match")
+    return src.view(rows, cols)
+
+
 FP8_E4M3, FP8_E5M2 = 0, 1
 _mx_workspaces = {}
 

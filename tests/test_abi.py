@@ -47,7 +47,9 @@ def test_only_the_c_abi_is_exported(built_lib):
 def test_python_signature_table_matches_header(built_lib):
     from pto_isa_b200 import _lib
     assert sorted(_lib.SIGNATURES) == header_symbols()
-    assert _lib.lib().pto_b200_version() == 2
+    import re
+    header = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "pto_b200.h")).read()
+    assert _lib.lib().pto_b200_version() == int(re.search(r"#define PTO_B200_ABI_VERSION (\d+)", header).group(1)) == 3
 
 
 def test_call_kernel_shims_export_the_reference_symbol(built_lib):
@@ -99,3 +101,9 @@ def test_ascend_launch_statements_are_rewritten():
     assert "PTO_B200_LAUNCH((warm), 24, stream);" in out
     assert out.endswith("    g(x);\n}\n")
     assert rewrite_launches("no launches here;") == "no launches here;"
+
+
+def test_build_entry_version_check():
+    """The check build() ends with (library version == header version) holds for the library in the tree."""
+    import __graft_entry__
+    __graft_entry__.check_library_version()

@@ -360,3 +360,17 @@ def test_mxgemm_fp4_oracle_decodes_all_codes():
         one[0, 0] = 0x2 << (4 * pos)  # 1.0 in the same position
         got = port.mxgemm_fp4(a, one, s, s[:1])[:, 0]
         assert np.array_equal(got, want), pos
+
+
+@pytest.mark.parametrize("diagonal", [-70, -2, 0, 1, 5, 300])
+@pytest.mark.parametrize("upper", [0, 1])
+def test_ttri_restatement_against_reference_build_and_numpy(diagonal, upper):
+    """TTRI (include/pto/cpu/TTRI.hpp:30-77): the restatement equals numpy's tril / triu of ones and, where the
+    reference build is present, the reference's own implementation on a 64 x 256 tile and a 40 x 100 corner."""
+    for rows, cols in ((64, 256), (40, 100), (1, 1)):
+        got = port.ttri_f32(rows, cols, diagonal, upper)
+        ones = np.ones((rows, cols), np.float32)
+        want = np.triu(ones, diagonal) if upper else np.tril(ones, diagonal)
+        assert np.array_equal(got, want)
+        if oracle.ref is not None:
+            assert np.array_equal(oracle.ref.ttri_f32(rows, cols, diagonal, upper), want), (rows, cols)

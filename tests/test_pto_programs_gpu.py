@@ -156,6 +156,25 @@ def test_vector2_program(prog, valid):
     assert np.array_equal(host(outs["cmp"]), port.tcmp_f32(a, b, 2))
 
 
+@pytest.mark.parametrize("diagonal", [1, 0, -5, 40, 200])
+def test_tri_reshape_program(prog, diagonal):
+    """TTRI (upper, times the lowest float, added to the logits: the causal mask of the reference's streaming softmax),
+    TTRI (lower), TRESHAPE 64 x 128 -> 128 x 64 and the row maxima of the reshaped tile, as PTO instructions."""
+    r = np.random.default_rng(7)
+    x = r.standard_normal((64, 128)).astype(np.float32)
+    masked = torch.full((64, 128), 5.0, device="cuda")
+    tril = torch.full((64, 128), 5.0, device="cuda")
+    rowmax = torch.full((128,), 5.0, device="cuda")
+    assert prog.pto_prog_tri_reshape_64x128(_ptr(masked), _ptr(tril), _ptr(rowmax), _ptr(dev(x)), diagonal, _stream()) == 0
+    torch.cuda.synchronize()
+    mask = port.ttri_f32(64, 128, diagonal, 1) * np.float32(-3.40282e38)
+    want = x + mask
+    u32 = lambda a: np.ascontiguousarray(a).view(np.uint32)
+    assert np.array_equal(u32(host(masked)), u32(want))
+    assert np.array_equal(host(tril), port.ttri_f32(64, 128, -2, 0))
+    assert np.array_equal(host(rowmax), want.reshape(128, 64).max(axis=1))
+
+
 def test_mla_head_program(prog, golden_dir):
     """The instruction sequence of the reference's multi-latent-attention demo (latent projections, TTRANS of K_lat,
     scaled scores, row softmax, context, output projection) on the GPU against the same sequence run by the

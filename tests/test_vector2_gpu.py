@@ -191,3 +191,19 @@ def test_argument_errors():
     with pytest.raises(pto.PtoB200Error):
         pto.TCOLSUM(torch.zeros(0, 8, device="cuda"))
     assert pto.TROWMIN(torch.zeros(0, 8, device="cuda")).numel() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.int32, torch.float16, torch.int16])
+def test_ttri_and_treshape(dtype):
+    """TTRI against the oracle for lower / upper triangles, diagonals outside the tile included; TRESHAPE is a view."""
+    for rows, cols in ((64, 256), (37, 200), (1, 1), (300, 1028)):
+        for diagonal in (-400, -3, 0, 1, 7, 2000):
+            for upper in (False, True):
+                got = pto.TTRI(rows, cols, diagonal, upper, dtype)
+                want = port.ttri_f32(rows, cols, diagonal, int(upper))
+                assert np.array_equal(host(got.float()), want), (rows, cols, diagonal, upper)
+    t = pto.TTRI(64, 256, 3, True, dtype)
+    r = pto.TRESHAPE(t, 128, 128)
+    assert r.data_ptr() == t.data_ptr() and torch.equal(r.reshape(-1), t.reshape(-1))
+    with pytest.raises(pto.PtoB200Error):
+        pto.TRESHAPE(t, 100, 100)
