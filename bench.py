@@ -362,7 +362,23 @@ def extras(torch, pto, peaks, peak_kind):
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": 9000.0, "unit": "TFLOP/s", "frac": tf / 9000.0,
                              "peak_kind": "nominal dense fp4 (no fp4 peak was measured on this pool)",
                              "vs_measured_bf16_burst": tf / peaks["bf16_tflops"]}})
-    del mxa, mxb, mxsa, mxsb, mxc, fa, fb
+    # TMATMUL's (int8, int8 -> int32) form at the same size: kind::i8 on the CTA-pair GEMM kernel
+    ia = [x.view(torch.int8) for x in mxa]
+    ib = [x.view(torch.int8) for x in mxb]
+    ic = torch.empty(mm, mm, device="cuda", dtype=torch.int32)
+
+    def i8_step():
+        j = mx_i[0] % sets_mx
+        mx_i[0] += 1
+        pto.gemm_i8(ia[j], ib[j], out=ic)
+
+    ms = bench(i8_step, 4, 20)
+    tf = 2.0 * mm ** 3 / ms / 1e9
+    out.append({"workload": "int8 GEMM (int32 accumulate and output) 6144^3", "value": tf, "unit": "TOP/s", "ms": ms,
+                "roofline": {"bound": "tensor", "achieved": tf, "peak": 4500.0, "unit": "TOP/s", "frac": tf / 4500.0,
+                             "peak_kind": "nominal dense int8 (no int8 peak was measured on this pool)",
+                             "vs_measured_bf16_burst": tf / peaks["bf16_tflops"]}})
+    del mxa, mxb, mxsa, mxsb, mxc, fa, fb, ia, ib, ic
     n = 1 << 24
     sets = 6
     xs = [torch.randn(n, device="cuda", generator=g) for _ in range(sets)]

@@ -188,6 +188,9 @@ int pto_b200_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *scale
  * scripts/gen_data.py:24-34), k / 2 bytes per row; scales, output, workspace and k % 32 == 0 as for the fp8 form. */
 int pto_b200_mxgemm_fp4(const uint8_t *a, const uint8_t *b, const uint8_t *scale_a, const uint8_t *scale_b, void *c, int m,
                         int n, int k, int out_f32, void *workspace, int64_t workspace_bytes, void *stream);
+/* TMATMUL's (int8, int8 -> int32) form (include/pto/cpu/TMatmul.hpp:46-51; tests/cpu/st/testcase/tmatmul case2):
+ * C[m x n] int32 = A[m x k] int8 * B^T with B stored n x k; exact integer arithmetic.  k a multiple of 16. */
+int pto_b200_gemm_i8i32(const int8_t *a, const int8_t *b, int32_t *c, int m, int n, int k, void *stream);
 /* TMATMUL_BIAS (include/pto/common/pto_instr.hpp:509-527, include/pto/cpu/TMatmul.hpp:99-116): the same product with
  * bias[j] (n floats) added to every element of column j. */
 int pto_b200_gemm_f16f32_bias(const uint16_t *a, const uint16_t *b, const float *bias, float *c, int m, int n, int k,

@@ -260,6 +260,14 @@ class _Lib:
             raise ValueError("mxgemm_fp4: unsupported shape")
         return c
 
+    def tmatmul_i8i32(self, a, b):
+        """a: (m,k) int8, b: (k,n) int8 -> (m,n) int32, exact."""
+        a, b = np.ascontiguousarray(a, np.int8), np.ascontiguousarray(b, np.int8)
+        (m, k), n = a.shape, b.shape[1]
+        c = np.empty((m, n), np.int32)
+        assert self._f("tmatmul_i8i32")(_p(a), _p(b), _p(c), m, k, n) == 0
+        return c
+
     # -- attention (one head)
     def attn_head_f16(self, q, k, v, causal, scale):
         q = np.ascontiguousarray(q, np.float16)

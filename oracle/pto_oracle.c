@@ -544,6 +544,22 @@ int pto_oracle_tmatmul_f16f32(const uint16_t *a, const uint16_t *b, float *c, in
     return 0;
 }
 
+/* (int8, int8 -> int32) form of the same instruction (include/pto/cpu/TMatmul.hpp:22-37,46-51): exact integer sums.
+ * a: m x k, b: k x n, row-major. */
+int pto_oracle_tmatmul_i8i32(const int8_t *a, const int8_t *b, int32_t *c, int m, int k, int n)
+{
+    for (int i = 0; i < m; ++i) {
+        for (int j = 0; j < n; ++j) {
+            int32_t s = 0;
+            for (int kk = 0; kk < k; ++kk) {
+                s += (int32_t)a[(int64_t)i * k + kk] * (int32_t)b[(int64_t)kk * n + j];
+            }
+            c[(int64_t)i * n + j] = s;
+        }
+    }
+    return 0;
+}
+
 int pto_oracle_tmatmul_f32(const float *a, const float *b, float *c, int m, int k, int n)
 {
     for (int i = 0; i < m; ++i) {

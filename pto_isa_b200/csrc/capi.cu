@@ -366,6 +366,11 @@ int pto_b200_mxgemm_fp4(const uint8_t *a, const uint8_t *b, const uint8_t *scale
                              workspace_bytes < 0 ? 0 : static_cast<size_t>(workspace_bytes), as_stream(stream));
 }
 
+int pto_b200_gemm_i8i32(const int8_t *a, const int8_t *b, int32_t *c, int m, int n, int k, void *stream)
+{
+    return launch_gemm2_i8i32(a, b, c, m, n, k, as_stream(stream));
+}
+
 int pto_b200_gemm_f16f32_bias(const uint16_t *a, const uint16_t *b, const float *bias, float *c, int m, int n, int k,
                               int b_layout, void *stream)
 {

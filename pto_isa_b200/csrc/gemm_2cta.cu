@@ -119,7 +119,33 @@ __device__ __forceinline__ void tc_mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_d
         : "memory");
 }
 
-// kMode: bit 0 = layout of B (0: k x n, 1: n x k), bit 1 = the TMATMUL_BIAS epilogue
+// the same instruction on signed 8-bit operands with 32-bit integer accumulation (k = 32 per instruction)
+__device__ __forceinline__ void tc_mma_i8_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                  uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// instruction descriptor of kind::i8: signed 8-bit A and B (K-major), 32-bit integer accumulator
+__host__ __device__ constexpr uint32_t make_idesc_i8(int m, int n)
+{
+    return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+           (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// kMode: bit 0 = layout of B (0: k x n, 1: n x k), bit 1 = the TMATMUL_BIAS epilogue, bit 2 = int8 operands with an
+// int32 result (TMATMUL's (int8, int8 -> int32) form, include/pto/cpu/TMatmul.hpp:46-51).  In the int8 form the rows
+// of A and B are handed to TMA as 16-bit elements, two int8 each, so `k` and every k coordinate below count pairs:
+// a 128-byte box is 64 of them, and an MMA still advances 32 bytes (32 int8, its k extent) inside the box.  The
+// accumulator words go out bit for bit, as in the float form.
 template <int kMode>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -128,6 +154,8 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 {
     constexpr int kBLayout = kMode & 1;
     constexpr bool kBias = (kMode & 2) != 0;
+    constexpr bool kInt8 = (kMode & 4) != 0;
+    static_assert(!kInt8 || (kBLayout == 1 && !kBias), "int8: B is n x k, no bias");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *staging = smem + kStages * kStageBytes;
@@ -220,7 +248,8 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     } else if (warp == 1) {
         // ------------------------------------------------------------ TEXTRACT + TMATMUL: MMA issuer (leader only)
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = make_idesc_f16(2 * BM, BN, 0, kBLayout == 0 ? 1 : 0);
+            constexpr uint32_t idesc =
+                kInt8 ? make_idesc_i8(2 * BM, BN) : make_idesc_f16(2 * BM, BN, 0, kBLayout == 0 ? 1 : 0);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             // descriptors of stage 0; a stage or a k step further on only moves the 16-byte-unit address field
@@ -250,8 +279,13 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         const uint32_t a_off = ((kk >> 2) * (BM * kBoxK * 2) + (kk & 3) * 32) >> 4;
                         const uint32_t b_off =
                             (kBLayout == 1) ? (((kk >> 2) * (BNH * kBoxK * 2) + (kk & 3) * 32) >> 4) : kk * kBStep;
-                        tc_mma_f16_ss_pair(d_tmem, a_desc + static_cast<uint64_t>(a_off),
-                                           b_desc + static_cast<uint64_t>(b_off), idesc, (kb | kk) != 0 ? 1u : 0u);
+                        if (kInt8) {
+                            tc_mma_i8_ss_pair(d_tmem, a_desc + static_cast<uint64_t>(a_off),
+                                              b_desc + static_cast<uint64_t>(b_off), idesc, (kb | kk) != 0 ? 1u : 0u);
+                        } else {
+                            tc_mma_f16_ss_pair(d_tmem, a_desc + static_cast<uint64_t>(a_off),
+                                               b_desc + static_cast<uint64_t>(b_off), idesc, (kb | kk) != 0 ? 1u : 0u);
+                        }
                     }
                     // the stage is reusable in both blocks once these MMAs have read it
                     tc_commit_pair(empty_mine + stage * 8);
@@ -438,6 +472,56 @@ int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, i
     } else {
         gemm2_f16f32_kernel<2><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, bias, m, n, k, status);
     }
+    return check_launch();
+}
+
+// C[m x n] int32 = A[m x k] int8 * B[n x k]^T int8 on the same kernel (see kMode bit 2)
+int launch_gemm2_i8i32(const int8_t *a, const int8_t *b, int32_t *c, int m, int n, int k, cudaStream_t stream)
+{
+    if (a == nullptr || b == nullptr || c == nullptr || m <= 0 || n <= 0 || k <= 0) {
+        set_error_text("gemm_i8: bad argument");
+        return kErrBadArgument;
+    }
+    if ((k % 16) != 0 || (reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(b) & 15u)) {
+        set_error_text("gemm_i8: k must be a multiple of 16 and the operands 16-byte aligned");
+        return kErrUnsupportedShape;
+    }
+    const int k2 = k / 2; // rows as 16-bit elements
+    CUtensorMap tmap_a, tmap_b, tmap_c;
+    int rc;
+    if ((rc = make_tmap_2d(&tmap_a, a, 2, m, k2, k2, BM, kBoxK, true)) != kOk ||
+        (rc = make_tmap_2d(&tmap_b, b, 2, n, k2, k2, BNH, kBoxK, true)) != kOk) {
+        return rc;
+    }
+    const int c_by_tma = ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0) ? 1 : 0;
+    if (c_by_tma) {
+        if ((rc = make_tmap_2d(&tmap_c, c, 4, m, n, n, 32, 32, true)) != kOk) {
+            return rc;
+        }
+    } else {
+        tmap_c = tmap_a; // never dereferenced
+    }
+    const int tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
+    int pairs = sm_count() / 2;
+    if (tiles < pairs) {
+        pairs = tiles;
+    }
+    DeviceStatus *status = device_status_ptr();
+    if (status == nullptr) {
+        return kErrCuda;
+    }
+    static bool attr_set = false;
+    if (!attr_set) {
+        if ((rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  kSmemBytes),
+                             "cudaFuncSetAttribute(gemm int8)")) != kOk) {
+            return rc;
+        }
+        attr_set = true;
+    }
+    gemm2_f16f32_kernel<5><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma,
+                                                                        reinterpret_cast<float *>(c), nullptr, m, n, k2,
+                                                                        status);
     return check_launch();
 }
 

@@ -463,6 +463,20 @@ def gemm(a, b, b_layout=1, out=None, bias=None):
     return out
 
 
+def gemm_i8(a, b, out=None):
+    """C[m,n] int32 = A[m,k] int8 @ B[n,k]^T int8, exact (TMATMUL's int8 form).  k a multiple of 16."""
+    _need_cuda(a, b)
+    if a.dtype != torch.int8 or b.dtype != torch.int8 or a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
+        raise PtoB200Error("gemm_i8: a is (m, k) and b is (n, k), both int8")
+    m, k = a.shape
+    n = b.shape[0]
+    out = torch.empty(m, n, dtype=torch.int32, device=a.device) if out is None else out
+    with torch.cuda.device(a.device):
+        rc = lib().pto_b200_gemm_i8i32(_ptr(a), _ptr(b), _ptr(out), m, n, k, _stream(a))
+    check(rc, "gemm_i8")
+    return out
+
+
 def gemm_host(a, b, c, b_layout=1):
     """Same product over HOST tensors (pinned or pageable): copies in, computes, copies out, synchronises."""
     m, k = a.shape

@@ -126,6 +126,21 @@ def gen_tmatmul(ref, tmp, out):
     np.savez_compressed(os.path.join(out, "tmatmul.npz"), **keep)
 
 
+def gen_tmatmul_i8(ref, tmp, out):
+    """The int8 -> int32 case of the same generator (tests/cpu/st/testcase/tmatmul/gen_data.py:34-59; its own case2 is
+    6 x 7 x 8) at 128 x 64 x 256 and 256 x 320 x 512, shapes whose rows a TMA descriptor accepts."""
+    mod = load(os.path.join(ref, "tests/cpu/st/testcase/tmatmul/gen_data.py"), "ref_tmatmul_gen_i8")
+    keep = {}
+    for name, (m, k, n) in (("small", (128, 64, 256)), ("mid", (256, 320, 512))):
+        p = mod.tmatmulParams(np.int8, np.int8, np.int32, m, k, n, False)
+        d = in_case_dir(tmp, "tmatmul_i8_" + name)
+        mod.gen_golden_data(name, p)
+        keep[f"{name}_a"] = read(os.path.join(d, "x1_gm.bin"), np.int8, (m, k))
+        keep[f"{name}_b"] = read(os.path.join(d, "x2_gm.bin"), np.int8, (k, n))
+        keep[f"{name}_golden"] = read(os.path.join(d, "golden.bin"), np.int32, (m, n))
+    np.savez_compressed(os.path.join(out, "tmatmul_i8.npz"), **keep)
+
+
 def gen_rowops(ref, tmp, out):
     keep = {}
     # tests/cpu/st/testcase/trowmax/gen_data.py:79-85 (case list), :17-35 (generator)
@@ -396,7 +411,7 @@ def main():
     cwd = os.getcwd()
     with tempfile.TemporaryDirectory() as tmp:
         try:
-            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm, gen_vector2, gen_harness, gen_mla, gen_mxgemm, gen_mxgemm_fp4):
+            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm, gen_vector2, gen_harness, gen_mla, gen_mxgemm, gen_mxgemm_fp4, gen_tmatmul_i8):
                 os.chdir(tmp)
                 fn(args.reference, tmp, HERE)
         finally:

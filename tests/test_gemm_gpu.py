@@ -142,3 +142,28 @@ def test_gemm_bias_form(mnk):
     want = a.astype(np.float64) @ b.astype(np.float64).T + bias[None, :]
     ok, worst = rel_err_ok(got, want, 2e-3)
     assert ok, f"max relative error {worst:.3e}"
+
+
+@pytest.mark.parametrize("mnk", [(128, 256, 64), (256, 512, 320), (300, 200, 112), (1, 4, 16), (1024, 768, 2048)])
+def test_gemm_int8_exact(mnk):
+    """TMATMUL's (int8, int8 -> int32) form on kind::i8: bit-exact against the oracle over the full int8 range, ragged
+    m and n included, with a guard row."""
+    m, n, k = mnk
+    r = np.random.default_rng(m + k)
+    a = r.integers(-128, 128, (m, k)).astype(np.int8)
+    b = r.integers(-128, 128, (n, k)).astype(np.int8)
+    want = port.tmatmul_i8i32(a, np.ascontiguousarray(b.T))
+    c = torch.full((m + 1, n), 7, device="cuda", dtype=torch.int32)
+    pto.gemm_i8(dev(a), dev(b), out=c[:m])
+    got = host(c)
+    assert np.array_equal(got[:m], want) and (got[m] == 7).all()
+    assert pto.device_status() == 0
+
+
+def test_gemm_int8_reference_golden(golden_dir):
+    z = np.load(os.path.join(golden_dir, "tmatmul_i8.npz"))
+    for name in ("small", "mid"):
+        got = host(pto.gemm_i8(dev(z[name + "_a"]), dev(np.ascontiguousarray(z[name + "_b"].T))))
+        assert np.array_equal(got, z[name + "_golden"])
+    with pytest.raises(pto.PtoB200Error):
+        pto.gemm_i8(torch.zeros(16, 24, dtype=torch.int8, device="cuda"), torch.zeros(16, 24, dtype=torch.int8, device="cuda"))

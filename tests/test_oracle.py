@@ -374,3 +374,10 @@ def test_ttri_restatement_against_reference_build_and_numpy(diagonal, upper):
         assert np.array_equal(got, want)
         if oracle.ref is not None:
             assert np.array_equal(oracle.ref.ttri_f32(rows, cols, diagonal, upper), want), (rows, cols)
+
+
+def test_tmatmul_i8_oracle_matches_reference_generator(golden_dir):
+    """(int8, int8 -> int32): exact equality with the golden of tests/cpu/st/testcase/tmatmul/gen_data.py."""
+    z = np.load(os.path.join(golden_dir, "tmatmul_i8.npz"))
+    for name in ("small", "mid"):
+        assert np.array_equal(port.tmatmul_i8i32(z[name + "_a"], z[name + "_b"]), z[name + "_golden"])
