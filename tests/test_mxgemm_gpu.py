@@ -207,3 +207,23 @@ def test_mxgemm_fp4_reference_shape_sampled_windows():
         want = port.mxgemm_fp4(a, b, sa, sb, window=(r0, r1, c0, c1))[r0:r1, c0:c1]
         got = host(c[r0:r1, c0:c1].contiguous().view(torch.int16)).view(np.uint16)
         check_bf16(got, want)
+
+
+@pytest.mark.parametrize("mnk", [(130, 36, 160), (64, 7, 64), (257, 260, 96)])
+def test_mxgemm_unaligned_output_rows(mnk):
+    """Output rows that are not multiples of 16 bytes (bf16 n = 36, 7; fp32 n = 7) leave through element stores instead
+    of TMA stores; an output that starts at an odd element too."""
+    m, n, k = mnk
+    a, b, sa, sb = make(m, n, k, 0, seed=n)
+    want = port.mxgemm_fp8(a, b, sa, sb, 0, 0)
+    for dt in (torch.bfloat16, torch.float32):
+        flat = torch.full(((m + 1) * n + 1,), 7.0, device="cuda", dtype=dt)
+        out = flat[1:1 + m * n].view(m, n)  # starts one element into the allocation
+        pto.mx_gemm(dev(a), dev(b), dev(sa), dev(sb), dt, out=out, fmt=0)
+        assert float(flat[0]) == 7.0 and bool((flat[1 + m * n:] == 7.0).all())
+        if dt == torch.float32:
+            ok, worst = rel_err_ok(host(out), want, 2e-3)
+            assert ok, f"max relative error {worst:.3e}"
+        else:
+            check_bf16(host(out.contiguous().view(torch.int16)).view(np.uint16), want)
+    assert pto.device_status() == 0
