@@ -346,6 +346,25 @@ def extras(torch, pto, peaks, peak_kind):
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": 4500.0, "unit": "TFLOP/s", "frac": tf / 4500.0,
                              "peak_kind": "nominal dense fp8 (no fp8 peak was measured on this pool)",
                              "vs_measured_bf16_burst": tf / peaks["bf16_tflops"]}})
+    # the vendor library's MXFP8 GEMM on the same box and operand bits (cuBLASLt through torch._scaled_mm, e4m3, unit scales):
+    # a denominator measured live, in the role MEASURED_PEAKS.json's cuBLAS figure plays for the fp16 GEMM
+    try:
+        ones = torch.full((mm, mm // 32), 127, device="cuda", dtype=torch.uint8).view(torch.float8_e8m0fnu)
+        la = [x.view(torch.float8_e4m3fn) for x in mxa]
+        lb = [x.view(torch.float8_e4m3fn).t() for x in mxb]
+
+        def lib_step():
+            j = mx_i[0] % sets_mx
+            mx_i[0] += 1
+            torch._scaled_mm(la[j], lb[j], scale_a=ones, scale_b=ones, out_dtype=torch.bfloat16)
+
+        lib_ms = bench(lib_step, 4, 20)
+        out[-1]["roofline"]["library_mxfp8_tflops"] = 2.0 * mm ** 3 / lib_ms / 1e9
+        out[-1]["roofline"]["frac_of_library"] = tf / out[-1]["roofline"]["library_mxfp8_tflops"]
+        del ones, la, lb
+    except Exception as exc:  # an older torch or cuBLASLt without block-scaled GEMMs: the comparison is left out
+        out[-1]["roofline"]["library_mxfp8_tflops"] = None
+        out[-1]["roofline"]["library_note"] = str(exc)[:120]
     # the same with packed fp4 (e2m1) operands: the reference's MXFP4 MxMatmul configuration (6144^3, bf16 output)
     fa = [x[:, : mm // 2].contiguous() for x in mxa]
     fb = [x[:, : mm // 2].contiguous() for x in mxb]
