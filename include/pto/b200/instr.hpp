@@ -76,6 +76,17 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // 16-byte asynchronous copy global -> shared; `valid_bytes` < 16 zero-fills the remainder
 __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void *gsrc, int valid_bytes)
 {
@@ -212,7 +223,8 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
         dst.pitch_ = pitch;
         dst.major_ = cols_contig ? b200::kColsContiguous : b200::kRowsContiguous;
     } else {
-        static_assert(TileData::Loc == TileType::Vec, "TLOAD: destination must be a Vec or Mat tile");
+        static_assert(TileData::Loc == TileType::Vec || TileData::Loc == TileType::Bias,
+                      "TLOAD: destination must be a Vec, Bias or Mat tile");
         T *t = dst.data();
         const int vr = dst.GetValidRow(), vc = dst.GetValidCol();
         const int64_t n0 = src.GetShape(0), n1 = src.GetShape(1), n2 = src.GetShape(2), n3 = src.GetShape(3),
@@ -347,6 +359,40 @@ PTO_INST RecordEvent TMATMUL_ACC(TileAccT &cOutMatrix, TileAccT &cInMatrix, Tile
     // the accumulator is updated in place (the reference's kernels pass the same tile twice)
     (void)cInMatrix;
     b200::matmul_issue(cOutMatrix, aMatrix, bMatrix, true);
+    return {};
+}
+
+// TMATMUL_BIAS (include/pto/cpu/TMatmul.hpp:99-116): C = A * B + bias, one bias value per column.  The bias row is
+// written into every lane of the accumulator's tensor-memory columns first, then the product is accumulated onto it.
+template <typename TileAccT, typename TileLeftT, typename TileRightT, typename TileBiasT, typename... WaitEvents>
+PTO_INST RecordEvent TMATMUL_BIAS(TileAccT &cMatrix, TileLeftT &aMatrix, TileRightT &bMatrix, TileBiasT &biasData,
+                                  WaitEvents &... events)
+{
+    static_assert(TileBiasT::Loc == TileType::Bias && TileBiasT::Rows == 1 && TileBiasT::Cols == TileAccT::Cols,
+                  "TMATMUL_BIAS: the bias is a 1 x N tile of TileType::Bias");
+    static_assert(std::is_same_v<typename TileBiasT::DType, float>, "TMATMUL_BIAS: fp32 bias");
+    static_assert(TileAccT::Cols % 16 == 0, "TMATMUL_BIAS: accumulator width must be a multiple of 16");
+#if PTO_B200_DEVICE_CODE
+    {
+        const int warp = threadIdx.x >> 5;
+        const int quarter = warp & 3; // tensor-memory lanes [32 * quarter, +32) are writable by this warp
+        const int group = warp >> 2, groups = blockDim.x >> 7;
+        const uint32_t taddr = b200::control()->tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + cMatrix.addr_;
+        const float *bias = biasData.data();
+        const int vc = biasData.GetValidCol();
+        for (int c0 = group * 16; c0 < TileAccT::Cols; c0 += groups * 16) {
+            uint32_t r[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                r[j] = (c0 + j < vc) ? __float_as_uint(bias[c0 + j]) : 0u;
+            }
+            b200::tmem_st16(taddr + c0, r);
+        }
+        b200::tc_fence_before();
+        __syncthreads();
+    }
+#endif
+    b200::matmul_issue(cMatrix, aMatrix, bMatrix, true);
     return {};
 }
 

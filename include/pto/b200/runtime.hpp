@@ -11,6 +11,7 @@
 //   Vec, Mat : [0, PTO_B200_L0A_OFFSET)            default 96 KiB  (two 128x64 + two 64x256 fp16 staging tiles)
 //   Left     : [PTO_B200_L0A_OFFSET, PTO_B200_L0B_OFFSET)   48 KiB  (ping at 0, pong at 32 KiB, 16 KiB each)
 //   Right    : [PTO_B200_L0B_OFFSET, end of arena)          64 KiB+ (ping at 0, pong at 32 KiB, 32 KiB each)
+//   Bias     : a 1 KiB table in the control block (one row of up to 256 floats for TMATMUL_BIAS)
 // Define the two macros before including the PTO headers to move the windows.
 // 512 tensor-memory columns are allocated per block for Acc tiles.
 #pragma once
@@ -42,9 +43,10 @@ struct Control {
     int pad;
     uint64_t flags[kNumFlags];
     uint32_t phase[kNumFlags / 32][kBlockThreads / 32]; // phase bit of every flag, per warp
+    uint8_t bias_table[1024];                            // the address space of TileType::Bias tiles (the NPU's bias table)
 };
 constexpr int kControlBytes = ((int)sizeof(Control) + 1023) / 1024 * 1024;
-constexpr int kDefaultSmemBytes = 227 * 1024; // 1 KiB alignment slack + control (5 KiB) + 221 KiB arena
+constexpr int kDefaultSmemBytes = 227 * 1024; // 1 KiB alignment slack + control (6 KiB) + 220 KiB arena
 
 #if PTO_B200_DEVICE_CODE
 __device__ __forceinline__ uint8_t *smem_base()
@@ -64,7 +66,11 @@ __device__ __forceinline__ uint8_t *arena()
 template <TileType Loc>
 __device__ __forceinline__ uint8_t *arena_of()
 {
-    return arena() + (Loc == TileType::Left ? PTO_B200_L0A_OFFSET : (Loc == TileType::Right ? PTO_B200_L0B_OFFSET : 0));
+    if constexpr (Loc == TileType::Bias) {
+        return control()->bias_table;
+    } else {
+        return arena() + (Loc == TileType::Left ? PTO_B200_L0A_OFFSET : (Loc == TileType::Right ? PTO_B200_L0B_OFFSET : 0));
+    }
 }
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {

@@ -133,6 +133,50 @@ AICORE inline void ProgMatmulND(__gm__ float *out, __gm__ half *a, __gm__ half *
     TSTORE(gc, acc);
 }
 
+// ---------------------------------------------------------------- TMATMUL_BIAS
+// The bias form of the reference's unit-test kernel (tests/cpu/st/testcase/tmatmul/tmatmul_kernel.cpp:26-98): the bias
+// row is loaded into a TileType::Bias tile and added by the instruction.
+template <int M, int K, int N>
+AICORE inline void ProgMatmulBias(__gm__ float *out, __gm__ half *a, __gm__ half *b, __gm__ float *bias)
+{
+    using GA = GlobalTensor<half, Shape<1, 1, 1, M, K>, Stride<M * K, M * K, M * K, K, 1>>;
+    using GB = GlobalTensor<half, Shape<1, 1, 1, K, N>, Stride<K * N, K * N, K * N, N, 1>>;
+    using GBias = GlobalTensor<float, Shape<1, 1, 1, 1, N>, Stride<N, N, N, N, 1>>;
+    using GC = GlobalTensor<float, Shape<1, 1, 1, M, N>, Stride<M * N, M * N, M * N, N, 1>>;
+    using MatA = Tile<TileType::Mat, half, M, K, BLayout::ColMajor, M, K, SLayout::RowMajor>;
+    using MatB = Tile<TileType::Mat, half, K, N, BLayout::RowMajor, K, N, SLayout::ColMajor>;
+    using BiasTile = Tile<TileType::Bias, float, 1, N, BLayout::RowMajor, 1, N>;
+    MatA am;
+    MatB bm;
+    TileLeft<half, M, K> al;
+    TileRight<half, K, N> br;
+    TileAcc<float, M, N> acc;
+    BiasTile bias_tile;
+    TASSIGN(am, 0x0);
+    TASSIGN(bm, M * K * sizeof(half));
+    TASSIGN(al, 0x0);
+    TASSIGN(br, 0x0);
+    TASSIGN(acc, 0x0);
+    TASSIGN(bias_tile, 0x0);
+    GA ga(a);
+    GB gb(b);
+    GBias gbias(bias);
+    GC gc(out);
+    TLOAD(am, ga);
+    TLOAD(bm, gb);
+    set_flag(PIPE_MTE2, PIPE_MTE1, EVENT_ID0);
+    wait_flag(PIPE_MTE2, PIPE_MTE1, EVENT_ID0);
+    TMOV(al, am);
+    TMOV(br, bm);
+    set_flag(PIPE_MTE1, PIPE_M, EVENT_ID0);
+    wait_flag(PIPE_MTE1, PIPE_M, EVENT_ID0);
+    TLOAD(bias_tile, gbias);
+    TMATMUL_BIAS(acc, al, br, bias_tile);
+    set_flag(PIPE_M, PIPE_FIX, EVENT_ID0);
+    wait_flag(PIPE_M, PIPE_FIX, EVENT_ID0);
+    TSTORE(gc, acc);
+}
+
 // ---------------------------------------------------------------- attention for one head, one key tile
 // The instruction sequence of the reference's attention test (tests/cpu/st/testcase/tflashattn/tflashattn_kernel.cpp:
 // 84-105) with the flash-attention kernel's conventions: fp16 Q / K / V, max on the raw logits,
@@ -665,6 +709,16 @@ int pto_prog_vector2_64x128(void *const *outs, const float *a, const float *b, c
     return pto::b200::launch(1, stream, [=] __device__() {
                ProgVector2(o, const_cast<float *>(a), const_cast<float *>(b), const_cast<float *>(s), valid_rows,
                            valid_cols);
+           }) == cudaSuccess
+               ? 0
+               : 3;
+}
+
+int pto_prog_tmatmul_bias_128x64x256(float *out, const __half *a, const __half *b, const float *bias, void *stream)
+{
+    return pto::b200::launch(1, stream, [=] __device__() {
+               ProgMatmulBias<128, 64, 256>(out, const_cast<__half *>(a), const_cast<__half *>(b),
+                                            const_cast<float *>(bias));
            }) == cudaSuccess
                ? 0
                : 3;

@@ -141,6 +141,21 @@ def gen_tmatmul_i8(ref, tmp, out):
     np.savez_compressed(os.path.join(out, "tmatmul_i8.npz"), **keep)
 
 
+def gen_tmatmul_bias(ref, tmp, out):
+    """The bias form of the tmatmul generator (tests/cpu/st/testcase/tmatmul/gen_data.py:34-59 with is_bias; the
+    reference's own case_bias_2 is fp16 16 x 15 x 16) at 128 x 64 x 256: A m x k, B k x n fp16, bias n fp32."""
+    mod = load(os.path.join(ref, "tests/cpu/st/testcase/tmatmul/gen_data.py"), "ref_tmatmul_gen_bias")
+    m, k, n = 128, 64, 256
+    p = mod.tmatmulParams(np.float16, np.float16, np.float32, m, k, n, True, np.float32)
+    d = in_case_dir(tmp, "tmatmul_bias")
+    mod.gen_golden_data("bias", p)
+    np.savez_compressed(os.path.join(out, "tmatmul_bias.npz"),
+                        a=read(os.path.join(d, "x1_gm.bin"), np.float16, (m, k)),
+                        b=read(os.path.join(d, "x2_gm.bin"), np.float16, (k, n)),
+                        bias=read(os.path.join(d, "bias_gm.bin"), np.float32, (n,)),
+                        golden=read(os.path.join(d, "golden.bin"), np.float32, (m, n)))
+
+
 def gen_rowops(ref, tmp, out):
     keep = {}
     # tests/cpu/st/testcase/trowmax/gen_data.py:79-85 (case list), :17-35 (generator)
@@ -411,7 +426,7 @@ def main():
     cwd = os.getcwd()
     with tempfile.TemporaryDirectory() as tmp:
         try:
-            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm, gen_vector2, gen_harness, gen_mla, gen_mxgemm, gen_mxgemm_fp4, gen_tmatmul_i8):
+            for fn in (gen_tcvt, gen_tgather, gen_tmatmul, gen_rowops, gen_attention, gen_gemm, gen_vector2, gen_harness, gen_mla, gen_mxgemm, gen_mxgemm_fp4, gen_tmatmul_i8, gen_tmatmul_bias):
                 os.chdir(tmp)
                 fn(args.reference, tmp, HERE)
         finally:

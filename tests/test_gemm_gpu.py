@@ -167,3 +167,10 @@ def test_gemm_int8_reference_golden(golden_dir):
         assert np.array_equal(got, z[name + "_golden"])
     with pytest.raises(pto.PtoB200Error):
         pto.gemm_i8(torch.zeros(16, 24, dtype=torch.int8, device="cuda"), torch.zeros(16, 24, dtype=torch.int8, device="cuda"))
+
+
+def test_gemm_bias_reference_golden(golden_dir):
+    """The bias case of the reference's tmatmul generator (integer-valued operands: the result is exact)."""
+    z = np.load(os.path.join(golden_dir, "tmatmul_bias.npz"))
+    got = host(pto.gemm(dev(z["a"]), dev(z["b"]), 0, bias=dev(z["bias"])))
+    assert np.array_equal(got, z["golden"])

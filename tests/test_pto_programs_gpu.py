@@ -156,6 +156,28 @@ def test_vector2_program(prog, valid):
     assert np.array_equal(host(outs["cmp"]), port.tcmp_f32(a, b, 2))
 
 
+def test_tmatmul_bias_program(prog, golden_dir):
+    """TMATMUL_BIAS as a PTO instruction (bias row in a TileType::Bias tile, written into tensor memory under the
+    product) in the sequence of the reference's unit-test kernel, against the golden of the reference's generator
+    (integer-valued operands: exact) and against the oracle product plus bias on random operands."""
+    z = np.load(os.path.join(golden_dir, "tmatmul_bias.npz"))
+    out = torch.zeros(128, 256, device="cuda")
+    assert prog.pto_prog_tmatmul_bias_128x64x256(_ptr(out), _ptr(dev(z["a"].view(np.int16))), _ptr(dev(z["b"].view(np.int16))),
+                                                 _ptr(dev(z["bias"])), _stream()) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(host(out), z["golden"])
+    r = np.random.default_rng(3)
+    a = r.uniform(-1, 1, (128, 64)).astype(np.float16)
+    b = r.uniform(-1, 1, (64, 256)).astype(np.float16)
+    bias = r.uniform(-10, 10, 256).astype(np.float32)
+    assert prog.pto_prog_tmatmul_bias_128x64x256(_ptr(out), _ptr(dev(a.view(np.int16))), _ptr(dev(b.view(np.int16))),
+                                                 _ptr(dev(bias)), _stream()) == 0
+    torch.cuda.synchronize()
+    want = a.astype(np.float64) @ b.astype(np.float64) + bias[None, :]
+    ok, worst = rel_err_ok(host(out), want, 2e-3)
+    assert ok, worst
+
+
 @pytest.mark.parametrize("diagonal", [1, 0, -5, 40, 200])
 def test_tri_reshape_program(prog, diagonal):
     """TTRI (upper, times the lowest float, added to the logits: the causal mask of the reference's streaming softmax),
