@@ -1,15 +1,17 @@
-// MX block-scaled fp8 GEMM for sm_100a on CTA pairs: C[m x n] (bf16 or fp32) = (scaleA (x) A) * (scaleB (x) B)^T with
-// A [m x k] and B [n x k] in fp8 (e4m3 or e5m2), one e8m0 scale per 32 consecutive k of a row.  It stands for the
-// reference's MxMatmul tile program (kernels/manual/a5/matmul_mxfp8_performance/mxmatmul_performance_kernel.cpp:
-// TLOAD of data and scale tiles, TEXTRACT, TMATMUL_MX, TSTORE) and maps it to tcgen05.mma kind::mxf8f6f4 with
-// block scaling: the data tiles arrive by TMA in the 128-byte swizzle, the scale tiles arrive by TMA in the
-// 32-row x 16-byte atoms the tensor core reads, are copied into tensor memory (tcgen05.cp) by the MMA thread and are
-// consumed from there by the four k = 32 MMAs of a stage.
+// MX block-scaled GEMM for sm_100a on CTA pairs: C[m x n] (bf16 or fp32) = (scaleA (x) A) * (scaleB (x) B)^T with
+// A [m x k] and B [n x k] in fp8 (e4m3 or e5m2) or packed fp4 (e2m1, two per byte), one e8m0 scale per 32 consecutive k
+// of a row.  It stands for the reference's MxMatmul tile programs (kernels/manual/a5/matmul_mxfp8_performance and
+// matmul_mxfp4_performance, mxmatmul_performance_kernel.cpp: TLOAD of data and scale tiles, TEXTRACT, TMATMUL_MX,
+// TSTORE) and maps them to tcgen05.mma kind::mxf8f6f4 / kind::mxf4 with block scaling: the data tiles arrive by TMA
+// in the 128-byte swizzle, the scale tiles arrive by TMA in the 32-row x 16-byte atoms the tensor core reads, are
+// copied into tensor memory (tcgen05.cp) by the MMA thread and are consumed from there by the four MMAs of a
+// 128-byte span of k.
 //
 // The block pair works on a 256 x 256 C tile as in gemm_2cta.cu (each block stages its own 128 rows of A and half of
-// the B tile; full[] lives in the leader, empty[] in both blocks).  Tensor memory holds one 256-column accumulator
-// and a ring of scale slots, so the epilogue of a tile does not overlap the next tile's MMAs; the TMA producer does
-// run ahead by the whole ring during the epilogue.
+// the B tile; full[] lives in the leader, empty[] in both blocks; one multicast commit per stage).  A stage is two
+// spans.  Tensor memory holds two accumulators that share 64 columns, and the scale slots behind them: the epilogue
+// drains the shared columns of a tile first and releases the accumulator then, so that the next tile's MMAs run under
+// the rest of the epilogue.
 #include "ptx.cuh"
 #include "internal.h"
 
