@@ -159,6 +159,7 @@ int pto_b200_tcmp_f32(const float *a, const float *b, float *dst, int64_t n, int
 #define PTO_B200_DTYPE_I32 1
 #define PTO_B200_DTYPE_F16 2
 #define PTO_B200_DTYPE_I16 3
+#define PTO_B200_DTYPE_BF16 4
 int pto_b200_ttri(void *dst, int rows, int cols, int diagonal, int upper, int dtype, void *stream);
 
 /* ---- GEMM --------------------------------------------------------------------------------------- */
@@ -188,6 +189,11 @@ int pto_b200_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *scale
  * scripts/gen_data.py:24-34), k / 2 bytes per row; scales, output, workspace and k % 32 == 0 as for the fp8 form. */
 int pto_b200_mxgemm_fp4(const uint8_t *a, const uint8_t *b, const uint8_t *scale_a, const uint8_t *scale_b, void *c, int m,
                         int n, int k, int out_f32, void *workspace, int64_t workspace_bytes, void *stream);
+/* The fp16 product with C rounded to fp16 or bfloat16 (nearest even) on the way out of the accumulator: the conversion
+ * TSTORE offers for accumulator tiles (include/pto/common/pto_instr.hpp:159-226, docs/isa/TSTORE.md:67-72).
+ * out_dtype: PTO_B200_DTYPE_F16 or PTO_B200_DTYPE_BF16.  Shapes as pto_b200_gemm_f16f32. */
+int pto_b200_gemm_f16_out16(const uint16_t *a, const uint16_t *b, uint16_t *c, int m, int n, int k, int b_layout,
+                            int out_dtype, void *stream);
 /* TMATMUL's (int8, int8 -> int32) form (include/pto/cpu/TMatmul.hpp:46-51; tests/cpu/st/testcase/tmatmul case2):
  * C[m x n] int32 = A[m x k] int8 * B^T with B stored n x k; exact integer arithmetic.  k a multiple of 16. */
 int pto_b200_gemm_i8i32(const int8_t *a, const int8_t *b, int32_t *c, int m, int n, int k, void *stream);

@@ -14,6 +14,9 @@
 #include "ptx.cuh"
 #include "internal.h"
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 namespace pto_b200 {
 
 namespace {
@@ -145,7 +148,9 @@ __host__ __device__ constexpr uint32_t make_idesc_i8(int m, int n)
 // int32 result (TMATMUL's (int8, int8 -> int32) form, include/pto/cpu/TMatmul.hpp:46-51).  In the int8 form the rows
 // of A and B are handed to TMA as 16-bit elements, two int8 each, so `k` and every k coordinate below count pairs:
 // a 128-byte box is 64 of them, and an MMA still advances 32 bytes (32 int8, its k extent) inside the box.  The
-// accumulator words go out bit for bit, as in the float form.
+// accumulator words go out bit for bit, as in the float form.  Bits 3-4 = 16-bit output: the accumulator is rounded
+// (nearest even) to fp16 (1) or bf16 (2) before it is stored, the conversion TSTORE offers on the way out of the
+// accumulator (docs/isa/TSTORE.md:67-72 in the reference).
 template <int kMode>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -155,6 +160,8 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     constexpr int kBLayout = kMode & 1;
     constexpr bool kBias = (kMode & 2) != 0;
     constexpr bool kInt8 = (kMode & 4) != 0;
+    constexpr int kOut16 = (kMode >> 3) & 3; // 0: fp32 C; 1: C rounded to fp16 on the way out; 2: to bf16 (TSTORE's conversion)
+    static_assert(kOut16 == 0 || (!kInt8 && !kBias), "16-bit output: plain fp16 product");
     static_assert(!kInt8 || (kBLayout == 1 && !kBias), "int8: B is n x k, no bias");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -323,6 +330,60 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int row = tm * 2 * BM + static_cast<int>(rank) * BM + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
             float *crow = c + static_cast<int64_t>(row) * n + static_cast<int64_t>(tn) * BN;
+            if constexpr (kOut16 != 0) {
+                uint16_t *crow16 = reinterpret_cast<uint16_t *>(c) + static_cast<int64_t>(row) * n + static_cast<int64_t>(tn) * BN;
+#pragma unroll 1
+                for (int cb = 0; cb < BN / 64; ++cb) {
+                    uint32_t r0[32], r1[32], w[32]; // 64 columns -> 128 bytes of this row
+                    tmem_ld_32x32(taddr + cb * 64, r0);
+                    tmem_ld_32x32(taddr + cb * 64 + 32, r1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (kOut16 == 1) {
+                            const __half2 p0 = __floats2half2_rn(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+                            const __half2 p1 = __floats2half2_rn(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+                            w[j] = *reinterpret_cast<const uint32_t *>(&p0);
+                            w[16 + j] = *reinterpret_cast<const uint32_t *>(&p1);
+                        } else {
+                            const __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+                            const __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+                            w[j] = *reinterpret_cast<const uint32_t *>(&p0);
+                            w[16 + j] = *reinterpret_cast<const uint32_t *>(&p1);
+                        }
+                    }
+                    const int col0 = tn * BN + cb * 64;
+                    if (c_by_tma) {
+                        if (lane == 0) {
+                            tma_store_wait_read<1>();
+                        }
+                        __syncwarp();
+                        uint8_t *dst = slabs + slab * kSlabBytes + lane * 128;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            *reinterpret_cast<uint4 *>(dst + ((j ^ (lane & 7)) << 4)) =
+                                make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            const int slab_row0 = row - lane;
+                            if (slab_row0 < m && col0 < n) {
+                                tma_store_2d(&tmap_c, slabs + slab * kSlabBytes, col0, slab_row0);
+                            }
+                            tma_store_commit();
+                        }
+                        slab ^= 1u;
+                    } else if (row < m) {
+#pragma unroll
+                        for (int j = 0; j < 64; ++j) {
+                            if (col0 + j < n) {
+                                crow16[cb * 64 + j] = static_cast<uint16_t>((j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu));
+                            }
+                        }
+                    }
+                }
+            } else {
 #pragma unroll 1
             for (int cb = 0; cb < BN / 32; ++cb) {
                 uint32_t r[32];
@@ -377,6 +438,7 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                 }
             }
+            } // fp32 / int32 output
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -471,6 +533,62 @@ int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, i
         gemm2_f16f32_kernel<3><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, bias, m, n, k, status);
     } else {
         gemm2_f16f32_kernel<2><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, bias, m, n, k, status);
+    }
+    return check_launch();
+}
+
+// C rounded to fp16 (out16 == 1) or bf16 (2): the same kernel with the converting epilogue (kMode bits 3-4)
+int launch_gemm2_f16_out16(const uint16_t *a, const uint16_t *b, uint16_t *c, int m, int n, int k, int b_layout, int out16,
+                           cudaStream_t stream)
+{
+    CUtensorMap tmap_a, tmap_b, tmap_c;
+    int rc = make_tmap_2d(&tmap_a, a, 2, m, k, k, BM, kBoxK, true);
+    if (rc != kOk) {
+        return rc;
+    }
+    const int c_by_tma = ((n & 7) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0) ? 1 : 0;
+    if (c_by_tma) {
+        if ((rc = make_tmap_2d(&tmap_c, c, 2, m, n, n, 32, 64, true)) != kOk) {
+            return rc;
+        }
+    } else {
+        tmap_c = tmap_a; // never dereferenced
+    }
+    rc = (b_layout == 1) ? make_tmap_2d(&tmap_b, b, 2, n, k, k, BNH, kBoxK, true) : make_tmap_2d(&tmap_b, b, 2, k, n, n, BK, 64, true);
+    if (rc != kOk) {
+        return rc;
+    }
+    const int tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
+    int pairs = sm_count() / 2;
+    if (tiles < pairs) {
+        pairs = tiles;
+    }
+    DeviceStatus *status = device_status_ptr();
+    if (status == nullptr) {
+        return kErrCuda;
+    }
+    static bool attr_set = false;
+    if (!attr_set) {
+        if ((rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm out16)")) != kOk ||
+            (rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<9>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm out16)")) != kOk ||
+            (rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm out16)")) != kOk ||
+            (rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<17>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm out16)")) != kOk) {
+            return rc;
+        }
+        attr_set = true;
+    }
+    const dim3 grid(2 * pairs);
+    float *cf = reinterpret_cast<float *>(c);
+    if (out16 == 1) {
+        if (b_layout == 1) {
+            gemm2_f16f32_kernel<9><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, cf, nullptr, m, n, k, status);
+        } else {
+            gemm2_f16f32_kernel<8><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, cf, nullptr, m, n, k, status);
+        }
+    } else if (b_layout == 1) {
+        gemm2_f16f32_kernel<17><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, cf, nullptr, m, n, k, status);
+    } else {
+        gemm2_f16f32_kernel<16><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, cf, nullptr, m, n, k, status);
     }
     return check_launch();
 }

@@ -87,6 +87,9 @@ int launch_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, co
 // the same with packed fp4 (e2m1) operands, two per byte, the lower k index in the low nibble (kind::mxf4, block 32)
 int launch_mxgemm_fp4(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, const uint8_t *sfb, void *c, int m, int n,
                       int k, int out_f32, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+// the fp16 product with C rounded to fp16 (out16 1) or bf16 (2) in the epilogue; arguments validated by the caller
+int launch_gemm2_f16_out16(const uint16_t *a, const uint16_t *b, uint16_t *c, int m, int n, int k, int b_layout, int out16,
+                           cudaStream_t stream);
 // C[m x n] int32 = A[m x k] int8 * B[n x k]^T int8 (kind::i8 on the CTA-pair kernel); k a multiple of 16
 int launch_gemm2_i8i32(const int8_t *a, const int8_t *b, int32_t *c, int m, int n, int k, cudaStream_t stream);
 // host-buffer GEMM whose device staging and status record live in a built-in static device array (no allocation)

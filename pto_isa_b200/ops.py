@@ -463,6 +463,23 @@ def gemm(a, b, b_layout=1, out=None, bias=None):
     return out
 
 
+def gemm_out16(a, b, b_layout=1, out_dtype=torch.float16, out=None):
+    """The fp16 product with C rounded to float16 or bfloat16 on the way out of the accumulator (TSTORE's conversion)."""
+    _need_cuda(a, b)
+    if a.dtype != torch.float16 or b.dtype != torch.float16 or a.dim() != 2 or b.dim() != 2:
+        raise PtoB200Error("gemm_out16: operands are 2-D float16")
+    if out_dtype not in (torch.float16, torch.bfloat16):
+        raise PtoB200Error("gemm_out16: the output is float16 or bfloat16")
+    m, k = a.shape
+    n = b.shape[1] if b_layout == 0 else b.shape[0]
+    out = torch.empty(m, n, dtype=out_dtype, device=a.device) if out is None else out
+    with torch.cuda.device(a.device):
+        rc = lib().pto_b200_gemm_f16_out16(_ptr(a), _ptr(b), _ptr(out), m, n, k, int(b_layout),
+                                           2 if out_dtype == torch.float16 else 4, _stream(a))
+    check(rc, "gemm_out16")
+    return out
+
+
 def gemm_i8(a, b, out=None):
     """C[m,n] int32 = A[m,k] int8 @ B[n,k]^T int8, exact (TMATMUL's int8 form).  k a multiple of 16."""
     _need_cuda(a, b)

@@ -174,3 +174,25 @@ def test_gemm_bias_reference_golden(golden_dir):
     z = np.load(os.path.join(golden_dir, "tmatmul_bias.npz"))
     got = host(pto.gemm(dev(z["a"]), dev(z["b"]), 0, bias=dev(z["bias"])))
     assert np.array_equal(got, z["golden"])
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("mnk_layout", [((256, 512, 320), 1), ((129, 264, 520), 1), ((300, 40, 136), 0), ((1, 8, 8), 1),
+                                        ((130, 36, 64), 1)])
+def test_gemm_16bit_output(mnk_layout, out_dtype):
+    """C rounded to fp16 / bf16 in the epilogue (TSTORE's conversion out of the accumulator): bit-equal to the fp32
+    kernel's output rounded by torch (same accumulator, round to nearest even), ragged shapes and an output whose rows
+    are not 16-byte multiples (n = 36) included; a guard row stays untouched."""
+    (m, n, k), b_layout = mnk_layout
+    a, b = make(m, n, k, b_layout, seed=21)
+    want = pto.gemm(dev(a), dev(b), b_layout).to(out_dtype)
+    c = torch.full((m + 1, n), 7.0, device="cuda", dtype=out_dtype)
+    pto.gemm_out16(dev(a), dev(b), b_layout, out_dtype, out=c[:m])
+    assert torch.equal(c[:m], want) and bool((c[m] == 7.0).all())
+    assert pto.device_status() == 0
+
+
+def test_gemm_16bit_output_full_size():
+    a, b = make(6144, 6144, 6144, 1, seed=6)
+    da, db = dev(a), dev(b)
+    assert torch.equal(pto.gemm_out16(da, db, 1, torch.bfloat16), pto.gemm(da, db, 1).bfloat16())
