@@ -189,6 +189,9 @@ int pto_b200_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *scale
  * scripts/gen_data.py:24-34), k / 2 bytes per row; scales, output, workspace and k % 32 == 0 as for the fp8 form. */
 int pto_b200_mxgemm_fp4(const uint8_t *a, const uint8_t *b, const uint8_t *scale_a, const uint8_t *scale_b, void *c, int m,
                         int n, int k, int out_f32, void *workspace, int64_t workspace_bytes, void *stream);
+/* The same product on bfloat16 operands (TMATMUL's bfloat16 form on the NPU back ends, include/pto/npu/a2a3/TMatmul.hpp),
+ * fp32 accumulate and output. */
+int pto_b200_gemm_bf16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout, void *stream);
 /* The fp16 product with C rounded to fp16 or bfloat16 (nearest even) on the way out of the accumulator: the conversion
  * TSTORE offers for accumulator tiles (include/pto/common/pto_instr.hpp:159-226, docs/isa/TSTORE.md:67-72).
  * out_dtype: PTO_B200_DTYPE_F16 or PTO_B200_DTYPE_BF16.  Shapes as pto_b200_gemm_f16f32. */

@@ -11,5 +11,5 @@ from . import ops  # noqa: F401
 from .ops import (  # noqa: F401
     TCVT, TGATHER, TGATHER_MASK, TROWMAX, TROWSUM, TEXP, TROWEXPANDSUB, TROWEXPANDMUL, TROWEXPANDDIV,
     TROWEXPAND, TROWEXPANDADD, TROWEXPANDMAX, TROWEXPANDMIN, TROWEXPANDEXPDIF, TROWMIN, TCOLSUM, TCOLMAX, TCOLMIN,
-    TFILLPAD, TTRANS, TTRI, TRESHAPE, TSEL, TCMPS, TCMP, TADD, TSUB, TMUL, TDIV, TMAX, TMIN, TMULS, TADDS, gemm, gemm_i8, gemm_out16, gemm_host, gemm_host_batched, mx_gemm, mx_gemm_fp4, flash_attn_fwd, flash_attn_fwd_host, device_status,
+    TFILLPAD, TTRANS, TTRI, TRESHAPE, TSEL, TCMPS, TCMP, TADD, TSUB, TMUL, TDIV, TMAX, TMIN, TMULS, TADDS, gemm, gemm_i8, gemm_out16, gemm_bf16, gemm_host, gemm_host_batched, mx_gemm, mx_gemm_fp4, flash_attn_fwd, flash_attn_fwd_host, device_status,
 )

@@ -46,6 +46,7 @@ SIGNATURES = {
     "pto_b200_mxgemm_fp8": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i64, _vp]),
     "pto_b200_ttri": (_i, [_vp, _i, _i, _i, _i, _i, _vp]),
     "pto_b200_mxgemm_fp4": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i64, _vp]),
+    "pto_b200_gemm_bf16f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "pto_b200_gemm_f16_out16": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "pto_b200_gemm_i8i32": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "pto_b200_gemm_f16f32_bias": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),

@@ -366,6 +366,19 @@ int pto_b200_mxgemm_fp4(const uint8_t *a, const uint8_t *b, const uint8_t *scale
                              workspace_bytes < 0 ? 0 : static_cast<size_t>(workspace_bytes), as_stream(stream));
 }
 
+int pto_b200_gemm_bf16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout, void *stream)
+{
+    if (a == nullptr || b == nullptr || c == nullptr || m <= 0 || n <= 0 || k <= 0 || (b_layout != 0 && b_layout != 1)) {
+        return bad("gemm_bf16: bad argument");
+    }
+    if ((k % 8) != 0 || (b_layout == 0 && (n % 8) != 0) || (reinterpret_cast<uintptr_t>(a) & 15u) ||
+        (reinterpret_cast<uintptr_t>(b) & 15u)) {
+        set_error_text("gemm_bf16: k (and n for a k x n B) must be multiples of 8 and operands 16-byte aligned");
+        return kErrUnsupportedShape;
+    }
+    return launch_gemm2_bf16f32(a, b, c, m, n, k, b_layout, as_stream(stream));
+}
+
 int pto_b200_gemm_f16_out16(const uint16_t *a, const uint16_t *b, uint16_t *c, int m, int n, int k, int b_layout,
                             int out_dtype, void *stream)
 {

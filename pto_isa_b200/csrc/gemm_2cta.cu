@@ -160,6 +160,7 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     constexpr int kBLayout = kMode & 1;
     constexpr bool kBias = (kMode & 2) != 0;
     constexpr bool kInt8 = (kMode & 4) != 0;
+    constexpr bool kBf16In = (kMode & 32) != 0; // bfloat16 operands (bit 5), fp32 accumulate and output
     constexpr int kOut16 = (kMode >> 3) & 3; // 0: fp32 C; 1: C rounded to fp16 on the way out; 2: to bf16 (TSTORE's conversion)
     static_assert(kOut16 == 0 || (!kInt8 && !kBias), "16-bit output: plain fp16 product");
     static_assert(!kInt8 || (kBLayout == 1 && !kBias), "int8: B is n x k, no bias");
@@ -256,7 +257,7 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // ------------------------------------------------------------ TEXTRACT + TMATMUL: MMA issuer (leader only)
         if (lane == 0 && rank == 0) {
             constexpr uint32_t idesc =
-                kInt8 ? make_idesc_i8(2 * BM, BN) : make_idesc_f16(2 * BM, BN, 0, kBLayout == 0 ? 1 : 0);
+                kInt8 ? make_idesc_i8(2 * BM, BN) : make_idesc_f16(2 * BM, BN, 0, kBLayout == 0 ? 1 : 0, kBf16In ? 1 : 0);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             // descriptors of stage 0; a stage or a k step further on only moves the 16-byte-unit address field
@@ -533,6 +534,53 @@ int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, i
         gemm2_f16f32_kernel<3><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, bias, m, n, k, status);
     } else {
         gemm2_f16f32_kernel<2><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, bias, m, n, k, status);
+    }
+    return check_launch();
+}
+
+// bfloat16 operands, fp32 accumulate and output: the plain kernel with the other operand format in its instruction
+// descriptor (kMode bit 5); arguments validated by the caller
+int launch_gemm2_bf16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
+                         cudaStream_t stream)
+{
+    CUtensorMap tmap_a, tmap_b, tmap_c;
+    int rc = make_tmap_2d(&tmap_a, a, 2, m, k, k, BM, kBoxK, true);
+    if (rc != kOk) {
+        return rc;
+    }
+    const int c_by_tma = ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0) ? 1 : 0;
+    if (c_by_tma) {
+        if ((rc = make_tmap_2d(&tmap_c, c, 4, m, n, n, 32, 32, true)) != kOk) {
+            return rc;
+        }
+    } else {
+        tmap_c = tmap_a; // never dereferenced
+    }
+    rc = (b_layout == 1) ? make_tmap_2d(&tmap_b, b, 2, n, k, k, BNH, kBoxK, true) : make_tmap_2d(&tmap_b, b, 2, k, n, n, BK, 64, true);
+    if (rc != kOk) {
+        return rc;
+    }
+    const int tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
+    int pairs = sm_count() / 2;
+    if (tiles < pairs) {
+        pairs = tiles;
+    }
+    DeviceStatus *status = device_status_ptr();
+    if (status == nullptr) {
+        return kErrCuda;
+    }
+    static bool attr_set = false;
+    if (!attr_set) {
+        if ((rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm bf16)")) != kOk ||
+            (rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<33>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm bf16)")) != kOk) {
+            return rc;
+        }
+        attr_set = true;
+    }
+    if (b_layout == 1) {
+        gemm2_f16f32_kernel<33><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, nullptr, m, n, k, status);
+    } else {
+        gemm2_f16f32_kernel<32><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, nullptr, m, n, k, status);
     }
     return check_launch();
 }

@@ -87,6 +87,9 @@ int launch_mxgemm_fp8(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, co
 // the same with packed fp4 (e2m1) operands, two per byte, the lower k index in the low nibble (kind::mxf4, block 32)
 int launch_mxgemm_fp4(const uint8_t *a, const uint8_t *b, const uint8_t *sfa, const uint8_t *sfb, void *c, int m, int n,
                       int k, int out_f32, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+// bfloat16 operands, fp32 accumulate and output; arguments validated by the caller
+int launch_gemm2_bf16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
+                         cudaStream_t stream);
 // the fp16 product with C rounded to fp16 (out16 1) or bf16 (2) in the epilogue; arguments validated by the caller
 int launch_gemm2_f16_out16(const uint16_t *a, const uint16_t *b, uint16_t *c, int m, int n, int k, int b_layout, int out16,
                            cudaStream_t stream);

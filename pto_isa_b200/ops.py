@@ -463,6 +463,20 @@ def gemm(a, b, b_layout=1, out=None, bias=None):
     return out
 
 
+def gemm_bf16(a, b, b_layout=1, out=None):
+    """C[m,n] fp32 = A[m,k] bfloat16 @ B (layouts as gemm)."""
+    _need_cuda(a, b)
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or a.dim() != 2 or b.dim() != 2:
+        raise PtoB200Error("gemm_bf16: operands are 2-D bfloat16")
+    m, k = a.shape
+    n = b.shape[1] if b_layout == 0 else b.shape[0]
+    out = torch.empty(m, n, dtype=torch.float32, device=a.device) if out is None else out
+    with torch.cuda.device(a.device):
+        rc = lib().pto_b200_gemm_bf16f32(_ptr(a), _ptr(b), _ptr(out), m, n, k, int(b_layout), _stream(a))
+    check(rc, "gemm_bf16")
+    return out
+
+
 def gemm_out16(a, b, b_layout=1, out_dtype=torch.float16, out=None):
     """The fp16 product with C rounded to float16 or bfloat16 on the way out of the accumulator (TSTORE's conversion)."""
     _need_cuda(a, b)

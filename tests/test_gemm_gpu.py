@@ -196,3 +196,20 @@ def test_gemm_16bit_output_full_size():
     a, b = make(6144, 6144, 6144, 1, seed=6)
     da, db = dev(a), dev(b)
     assert torch.equal(pto.gemm_out16(da, db, 1, torch.bfloat16), pto.gemm(da, db, 1).bfloat16())
+
+
+@pytest.mark.parametrize("b_layout", [1, 0])
+@pytest.mark.parametrize("mnk", [(256, 512, 320), (129, 264, 520), (1024, 768, 2048)])
+def test_gemm_bf16_operands(mnk, b_layout):
+    """bfloat16 operands, fp32 accumulate: against the exact (float64) product of the same bf16 values, tolerance 2e-3 of
+    max(|want|, rms(want)) as for fp16."""
+    m, n, k = mnk
+    g = torch.Generator().manual_seed(m + b_layout)
+    a = (torch.rand(m, k, generator=g) * 2 - 1).bfloat16()
+    b = (torch.rand((k, n) if b_layout == 0 else (n, k), generator=g) * 2 - 1).bfloat16()
+    bd = b.double() if b_layout == 0 else b.double().t()
+    want = (a.double() @ bd).numpy()
+    got = host(pto.gemm_bf16(a.cuda(), b.cuda(), b_layout))
+    ok, worst = rel_err_ok(got, want, 2e-3)
+    assert ok, f"max relative error {worst:.3e}"
+    assert pto.device_status() == 0
