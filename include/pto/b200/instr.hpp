@@ -22,7 +22,7 @@
 
 #include <limits>
 
-#include "runtime.hpp"
+#include "event.hpp"
 
 namespace pto {
 
@@ -181,6 +181,17 @@ PTO_INST void TASSIGN(T &obj, AddrType addr)
                 obj.addr_ = static_cast<uint32_t>(addr) / 512u;
             } else {
                 obj.addr_ = static_cast<uint32_t>(addr);
+#if PTO_B200_DEVICE_CODE
+                // `(uint64_t)tile.data() + bytes`, the reference's way of stepping a tile through its buffer, is a
+                // generic address inside this block's arena: turn it back into the window's offset
+                if constexpr (sizeof(AddrType) == 8) {
+                    const uint64_t a = static_cast<uint64_t>(addr);
+                    const uint64_t base = reinterpret_cast<uint64_t>(b200::arena_of<T::Loc>());
+                    if (a >= base && a - base < static_cast<uint64_t>(b200::kDefaultSmemBytes)) {
+                        obj.addr_ = static_cast<uint32_t>(a - base);
+                    }
+                }
+#endif
             }
         }
     } else {
@@ -188,10 +199,39 @@ PTO_INST void TASSIGN(T &obj, AddrType addr)
     }
 }
 
+// compile-time address form (include/pto/common/pto_instr.hpp:30-41 in the reference)
+template <std::size_t Addr, typename T>
+PTO_INST std::enable_if_t<is_tile<T>::value> TASSIGN(T &obj)
+{
+    static_assert(T::Loc == TileType::Acc || Addr % 32 == 0, "TASSIGN: tile addresses are 32-byte aligned");
+    TASSIGN(obj, static_cast<std::size_t>(Addr));
+}
+
 // ---------------------------------------------------------------- TLOAD
+// Results follow the CPU simulation (include/pto/cpu/TLoad.hpp:143-177 in the reference): the whole destination tile is
+// the pad value of its type (PadValue::Null and Zero: 0; Max / Min: +-infinity, or the integer limits) except where the
+// global tensor's elements land.  Row-major tiles: dimensions 0..3 of the global tensor fold into tile rows, dimension 4
+// runs along the columns; column-major tiles: dimension 3 runs along the rows, dimensions 0..2 and 4 fold into columns.
+namespace b200 {
+template <typename T, PadValue P>
+PTO_INTERNAL T pad_value();
+
+// where element (i0, i1, i2, r, c) of a five-dimensional global tensor lies in a plain Vec tile
+template <typename TileData>
+PTO_INTERNAL int folded_offset(int64_t outer, int64_t r, int64_t c, int64_t n3, int64_t n4)
+{
+    if constexpr (TileData::isRowMajor) {
+        return static_cast<int>((outer * n3 + r) * TileData::Cols + c);
+    } else {
+        return static_cast<int>((outer * n4 + c) * TileData::Rows + r);
+    }
+}
+} // namespace b200
+
 template <typename TileData, typename GlobalData, typename... WaitEvents>
 PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... events)
 {
+    TSYNC(events...);
     static_assert(sizeof(typename TileData::DType) == sizeof(typename GlobalData::DType),
                   "TLOAD: source and destination element sizes differ");
     static_assert(GlobalData::layout == Layout::ND || GlobalData::layout == Layout::DN,
@@ -200,9 +240,8 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
     using T = typename TileData::DType;
     const T *g = reinterpret_cast<const T *>(src.data());
     const int64_t s3 = src.GetStride(3), s4 = src.GetStride(4);
-    if constexpr (TileData::Loc == TileType::Mat) {
-        static_assert(sizeof(T) == 2, "Mat tiles feed the tensor core: 16-bit elements");
-        // the global tensor's unit-stride dimension decides the staged layout
+    if constexpr (TileData::Loc == TileType::Mat && sizeof(T) == 2) {
+        // 16-bit matrix tiles feed the tensor core: the global tensor's unit-stride dimension decides the staged layout
         const bool cols_contig = (s4 == 1);
         const int vr = dst.GetValidRow(), vc = dst.GetValidCol();
         const int lines = cols_contig ? TileData::Rows : TileData::Cols;  // index of the strided dimension
@@ -212,43 +251,69 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
         const int chunks_per_line = span / 8;
         const uint32_t base = b200::smem_u32(b200::arena() + dst.addr_);
         const uint32_t pitch = static_cast<uint32_t>(lines) * 128u;
+        // 16-byte asynchronous copies need 16-byte aligned sources; ragged rows are fetched element by element
+        const bool aligned = ((reinterpret_cast<uintptr_t>(g) | static_cast<uintptr_t>(line_stride * 2)) & 15u) == 0 &&
+                             !__isShared(g); // (a FIFO entry may lie in the block's own shared memory)
         for (int q = threadIdx.x; q < lines * chunks_per_line; q += blockDim.x) {
             const int l = q / chunks_per_line, ch = q - l * chunks_per_line;
             const int e0 = ch * 8; // first element of this 16-byte chunk along the contiguous dimension
             int valid = (l < v_lines) ? (v_span - e0) * 2 : 0;
             valid = valid < 0 ? 0 : (valid > 16 ? 16 : valid);
             const uint32_t off = (ch >> 3) * pitch + l * 128u + (((ch & 7) ^ (l & 7)) << 4);
-            b200::cp_async16(base + off, valid > 0 ? g + l * line_stride + e0 : g, valid);
+            if (aligned) {
+                b200::cp_async16(base + off, valid > 0 ? g + l * line_stride + e0 : g, valid);
+            } else {
+                uint4 v = make_uint4(0, 0, 0, 0);
+                unsigned short *h = reinterpret_cast<unsigned short *>(&v);
+                for (int e = 0; e < valid / 2; ++e) {
+                    h[e] = reinterpret_cast<const unsigned short *>(g)[l * line_stride + e0 + e];
+                }
+                *reinterpret_cast<uint4 *>(b200::arena() + dst.addr_ + off) = v;
+            }
         }
         dst.pitch_ = pitch;
         dst.major_ = cols_contig ? b200::kColsContiguous : b200::kRowsContiguous;
+    } else if constexpr (TileData::Loc == TileType::Mat) {
+        // matrix tiles of 8- and 32-bit elements are kept plain (row-major Rows x Cols, zero outside the valid region);
+        // TMATMUL on them runs on the CUDA cores with the simulation's arithmetic
+        T *t = reinterpret_cast<T *>(b200::arena() + dst.addr_);
+        const int vr = dst.GetValidRow(), vc = dst.GetValidCol();
+        for (int i = threadIdx.x; i < TileData::Numel; i += blockDim.x) {
+            const int r = i / TileData::Cols, c = i - r * TileData::Cols;
+            t[i] = (r < vr && c < vc) ? g[r * s3 + c * s4] : T(0);
+        }
+        dst.pitch_ = 0;
+        dst.major_ = b200::kPlain;
+        __syncthreads();
     } else {
         static_assert(TileData::Loc == TileType::Vec || TileData::Loc == TileType::Bias,
                       "TLOAD: destination must be a Vec, Bias or Mat tile");
+        static_assert(TileData::SFractal == SLayout::NoneBox, "TLOAD: plain (NoneBox) vector tiles");
         T *t = dst.data();
-        const int vr = dst.GetValidRow(), vc = dst.GetValidCol();
         const int64_t n0 = src.GetShape(0), n1 = src.GetShape(1), n2 = src.GetShape(2), n3 = src.GetShape(3),
                       n4 = src.GetShape(4);
-        if (vr < TileData::Rows || vc < TileData::Cols) { // padding of the invalid region
+        const int64_t outer = n0 * n1 * n2;
+        // rows x cols of the tile that the global tensor covers; everything else becomes the pad value
+        const int64_t cov_r = TileData::isRowMajor ? outer * n3 : n3;
+        const int64_t cov_c = TileData::isRowMajor ? n4 : outer * n4;
+        if (cov_r < TileData::Rows || cov_c < TileData::Cols) {
+            const T pad = b200::pad_value<T, TileData::PadVal>();
             for (int i = threadIdx.x; i < TileData::Numel; i += blockDim.x) {
-                t[i] = T(0);
+                const int r = TileData::isRowMajor ? i / TileData::Cols : i % TileData::Rows;
+                const int c = TileData::isRowMajor ? i % TileData::Cols : i / TileData::Rows;
+                if (r >= cov_r || c >= cov_c) {
+                    t[i] = pad;
+                }
             }
-            __syncthreads();
         }
-        if (n0 * n1 * n2 == 1) {
-            for (int i = threadIdx.x; i < vr * vc; i += blockDim.x) {
-                const int r = i / vc, c = i - r * vc;
-                t[b200::vec_offset<TileData>(r, c)] = g[r * s3 + c * s4];
-            }
-        } else {
-            // outer dimensions fold into tile rows (row-major tiles), as include/pto/cpu/TLoad.hpp:74-95 does
-            const int64_t rows = n0 * n1 * n2 * n3;
-            for (int64_t i = threadIdx.x; i < rows * n4; i += blockDim.x) {
-                const int64_t R = i / n4, c = i - R * n4;
-                const int64_t r = R % n3, o = R / n3, i2 = o % n2, i1 = (o / n2) % n1, i0 = o / (n2 * n1);
-                t[b200::vec_offset<TileData>(static_cast<int>(R), static_cast<int>(c))] =
-                    g[i0 * src.GetStride(0) + i1 * src.GetStride(1) + i2 * src.GetStride(2) + r * s3 + c * s4];
-            }
+        const int64_t per = n3 * n4;
+        for (int64_t i = threadIdx.x; i < outer * per; i += blockDim.x) {
+            const int64_t o = i / per, rc = i - o * per;
+            // consecutive threads walk the global tensor's unit-stride dimension
+            const int64_t r = (s4 == 1) ? rc / n4 : rc % n3, c = (s4 == 1) ? rc % n4 : rc / n3;
+            const int64_t i2 = o % n2, i1 = (o / n2) % n1, i0 = o / (n2 * n1);
+            t[b200::folded_offset<TileData>(o, r, c, n3, n4)] =
+                g[i0 * src.GetStride(0) + i1 * src.GetStride(1) + i2 * src.GetStride(2) + r * s3 + c * s4];
         }
         __syncthreads();
     }
@@ -266,31 +331,51 @@ template <typename DstTileData, typename SrcTileData, typename... WaitEvents>
 PTO_INST RecordEvent TEXTRACT(DstTileData &dst, SrcTileData &src, uint16_t indexRow = 0, uint16_t indexCol = 0,
                               WaitEvents &... events)
 {
+    TSYNC(events...);
     static_assert(SrcTileData::Loc == TileType::Mat, "TEXTRACT: source must be a Mat tile");
     static_assert(DstTileData::Loc == TileType::Left || DstTileData::Loc == TileType::Right,
                   "TEXTRACT: destination must be a Left or Right tile");
-    static_assert(sizeof(typename DstTileData::DType) == 2 && sizeof(typename SrcTileData::DType) == 2,
-                  "TEXTRACT: 16-bit elements");
+    static_assert(sizeof(typename DstTileData::DType) == sizeof(typename SrcTileData::DType),
+                  "TEXTRACT: element sizes differ");
 #if PTO_B200_DEVICE_CODE
-    const bool cols_contig = (src.major_ == b200::kColsContiguous);
-    const int line0 = cols_contig ? indexRow : indexCol;
-    const int chunk0 = (cols_contig ? indexCol : indexRow) >> 3;
-    const int lines = cols_contig ? DstTileData::Rows : DstTileData::Cols;
-    const int chunks_per_line = (cols_contig ? DstTileData::Cols : DstTileData::Rows) / 8;
-    const uint32_t dst_pitch = static_cast<uint32_t>(lines) * 128u;
-    const uint8_t *s = b200::arena_of<TileType::Mat>() + src.addr_;
-    uint8_t *d = b200::arena_of<DstTileData::Loc>() + dst.addr_;
-    for (int q = threadIdx.x; q < lines * chunks_per_line; q += blockDim.x) {
-        const int l = q / chunks_per_line, ch = q - l * chunks_per_line;
-        const int sl = line0 + l, sch = chunk0 + ch;
-        const uint32_t s_off = (sch >> 3) * src.pitch_ + sl * 128u + (((sch & 7) ^ (sl & 7)) << 4);
-        const uint32_t d_off = (ch >> 3) * dst_pitch + l * 128u + (((ch & 7) ^ (l & 7)) << 4);
-        *reinterpret_cast<uint4 *>(d + d_off) = *reinterpret_cast<const uint4 *>(s + s_off);
+    if constexpr (sizeof(typename SrcTileData::DType) != 2) {
+        // plain tiles (8- and 32-bit elements): the window, row by row; outside the source tile the operand is zero
+        using T = typename DstTileData::DType;
+        const T *s = reinterpret_cast<const T *>(b200::arena_of<TileType::Mat>() + src.addr_);
+        T *d = reinterpret_cast<T *>(b200::arena_of<DstTileData::Loc>() + dst.addr_);
+        for (int i = threadIdx.x; i < DstTileData::Numel; i += blockDim.x) {
+            const int r = i / DstTileData::Cols, c = i - r * DstTileData::Cols;
+            const int sr = r + indexRow, sc = c + indexCol;
+            d[i] = (sr < SrcTileData::Rows && sc < SrcTileData::Cols) ? s[sr * SrcTileData::Cols + sc] : T(0);
+        }
+        dst.pitch_ = 0;
+        dst.major_ = b200::kPlain;
+    } else {
+        const bool cols_contig = (src.major_ == b200::kColsContiguous);
+        const int line0 = cols_contig ? indexRow : indexCol;
+        const int chunk0 = (cols_contig ? indexCol : indexRow) >> 3;
+        const int lines = cols_contig ? DstTileData::Rows : DstTileData::Cols;
+        const int chunks_per_line = (cols_contig ? DstTileData::Cols : DstTileData::Rows) / 8;
+        // lines and chunks of the source tile's own storage; a window that reaches past them reads zeros
+        const int src_lines = cols_contig ? SrcTileData::Rows : SrcTileData::Cols;
+        const int src_chunks = (cols_contig ? SrcTileData::Cols : SrcTileData::Rows) / 8;
+        const uint32_t dst_pitch = static_cast<uint32_t>(lines) * 128u;
+        const uint8_t *s = b200::arena_of<TileType::Mat>() + src.addr_;
+        uint8_t *d = b200::arena_of<DstTileData::Loc>() + dst.addr_;
+        for (int q = threadIdx.x; q < lines * chunks_per_line; q += blockDim.x) {
+            const int l = q / chunks_per_line, ch = q - l * chunks_per_line;
+            const int sl = line0 + l, sch = chunk0 + ch;
+            const uint32_t s_off = (sch >> 3) * src.pitch_ + sl * 128u + (((sch & 7) ^ (sl & 7)) << 4);
+            const uint32_t d_off = (ch >> 3) * dst_pitch + l * 128u + (((ch & 7) ^ (l & 7)) << 4);
+            *reinterpret_cast<uint4 *>(d + d_off) = (sl < src_lines && sch < src_chunks)
+                                                        ? *reinterpret_cast<const uint4 *>(s + s_off)
+                                                        : make_uint4(0, 0, 0, 0);
+        }
+        dst.pitch_ = dst_pitch;
+        // Left [M x K] is a K-major operand when its columns are contiguous; Right [K x N] when its rows are
+        const bool k_major = (DstTileData::Loc == TileType::Left) ? cols_contig : !cols_contig;
+        dst.major_ = k_major ? 0 : 1;
     }
-    dst.pitch_ = dst_pitch;
-    // Left [M x K] is a K-major operand when its columns are contiguous; Right [K x N] when its rows are
-    const bool k_major = (DstTileData::Loc == TileType::Left) ? cols_contig : !cols_contig;
-    dst.major_ = k_major ? 0 : 1;
     if (DstTileData::ValidRow == DYNAMIC) {
         dst.RowMaskInternal = src.GetValidRow() - indexRow;
     }
@@ -301,22 +386,36 @@ PTO_INST RecordEvent TEXTRACT(DstTileData &dst, SrcTileData &src, uint16_t index
     return {};
 }
 
-// ---------------------------------------------------------------- TMATMUL / TMATMUL_ACC
+// ---------------------------------------------------------------- TMATMUL / TMATMUL_ACC / TMATMUL_BIAS
+// (half, half -> float) and (bfloat16, bfloat16 -> float) run on the tensor core; (float, float -> float) and
+// (int8, int8 -> int32), the two other operand types of the reference (include/pto/cpu/TMatmul.hpp:46-51), are plain
+// tiles multiplied on the CUDA cores in the simulation's order: one sum over k per output element, products and sums
+// rounded separately, added to the accumulator (or the bias) at the end (TMatmul.hpp:22-37,99-116).
 namespace b200 {
+template <typename TileAccT, typename TileLeftT, typename TileRightT>
+PTO_INTERNAL void matmul_check()
+{
+    using AT = typename TileLeftT::DType;
+    using CT = typename TileAccT::DType;
+    static_assert(std::is_same_v<AT, typename TileRightT::DType>, "TMATMUL: operand types differ");
+    static_assert(((std::is_same_v<AT, __half> || std::is_same_v<AT, __nv_bfloat16> || std::is_same_v<AT, float>)&&std::is_same_v<CT, float>) ||
+                      (std::is_same_v<AT, int8_t> && std::is_same_v<CT, int32_t>),
+                  "TMATMUL: (half | bfloat16 | float -> float) or (int8 -> int32)");
+    static_assert(TileLeftT::Loc == TileType::Left && TileRightT::Loc == TileType::Right &&
+                      TileAccT::Loc == TileType::Acc,
+                  "TMATMUL: expects (Acc, Left, Right)");
+    static_assert(TileLeftT::Rows <= 128 && TileLeftT::Cols == TileRightT::Rows && TileLeftT::Rows == TileAccT::Rows,
+                  "TMATMUL: m <= 128, inconsistent m / k");
+    static_assert(TileRightT::Cols % 16 == 0 && TileRightT::Cols <= 256 && TileAccT::Cols == TileRightT::Cols,
+                  "TMATMUL: n a multiple of 16, at most 256");
+}
+
+// tensor-core product; `accumulate` false: the accumulator is overwritten
 template <typename TileAccT, typename TileLeftT, typename TileRightT>
 PTO_INTERNAL void matmul_issue(TileAccT &c, TileLeftT &a, TileRightT &b, bool accumulate)
 {
     using AT = typename TileLeftT::DType;
-    static_assert(std::is_same_v<AT, typename TileRightT::DType>, "TMATMUL: operand types differ");
-    static_assert(std::is_same_v<AT, __half> || std::is_same_v<AT, __nv_bfloat16>, "TMATMUL: fp16 / bf16 operands");
-    static_assert(std::is_same_v<typename TileAccT::DType, float>, "TMATMUL: fp32 accumulator");
-    static_assert(TileLeftT::Loc == TileType::Left && TileRightT::Loc == TileType::Right &&
-                      TileAccT::Loc == TileType::Acc,
-                  "TMATMUL: expects (Acc, Left, Right)");
-    static_assert(TileLeftT::Rows <= 128 && TileLeftT::Cols % 16 == 0 && TileLeftT::Cols == TileRightT::Rows,
-                  "TMATMUL: m <= 128, k a multiple of 16");
-    static_assert(TileRightT::Cols % 16 == 0 && TileRightT::Cols <= 256 && TileAccT::Cols == TileRightT::Cols,
-                  "TMATMUL: n a multiple of 16, at most 256");
+    static_assert(TileLeftT::Cols % 16 == 0, "TMATMUL: k a multiple of 16");
 #if PTO_B200_DEVICE_CODE
     if (threadIdx.x == 0) {
         constexpr uint32_t kBf16 = std::is_same_v<AT, __nv_bfloat16> ? 1u : 0u;
@@ -343,37 +442,173 @@ PTO_INTERNAL void matmul_issue(TileAccT &c, TileLeftT &a, TileRightT &b, bool ac
     }
 #endif
 }
+
+// CUDA-core product of plain tiles.  mode 0: C = A B, 1: C += A B, 2: C = A B + bias (one value per column).
+// A thread owns one accumulator row (its tensor-memory lane), sixteen columns at a time.
+template <typename TileAccT, typename TileLeftT, typename TileRightT>
+PTO_INTERNAL void matmul_plain(TileAccT &c, TileLeftT &a, TileRightT &b, int mode, const typename TileAccT::DType *bias)
+{
+#if PTO_B200_DEVICE_CODE
+    using AT = typename TileLeftT::DType;
+    using CT = typename TileAccT::DType;
+    constexpr int K = TileLeftT::Cols, N = TileRightT::Cols;
+    const AT *pa = reinterpret_cast<const AT *>(arena_of<TileType::Left>() + a.addr_);
+    const AT *pb = reinterpret_cast<const AT *>(arena_of<TileType::Right>() + b.addr_);
+    const int m = a.GetValidRow(), kv = a.GetValidCol(), n = b.GetValidCol();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int quarter = warp & 3, group = warp >> 2, groups = blockDim.x >> 7;
+    const int row = quarter * 32 + lane;
+    const uint32_t taddr = control()->tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c.addr_;
+    __syncthreads();
+    tc_fence_after();
+    for (int c0 = group * 16; c0 < N; c0 += groups * 16) {
+        uint32_t r[16];
+        if (mode == 1) {
+            tmem_ld16(taddr + c0, r);
+        }
+#pragma unroll 1
+        for (int j = 0; j < 16; ++j) {
+            const int col = c0 + j;
+            CT acc = CT(0);
+            if (row < m && row < TileLeftT::Rows && col < n) {
+                for (int k = 0; k < kv; ++k) {
+                    if constexpr (std::is_same_v<CT, float>) {
+                        acc = __fadd_rn(acc, __fmul_rn(pa[row * K + k], pb[k * N + col]));
+                    } else {
+                        acc += static_cast<CT>(pa[row * K + k]) * static_cast<CT>(pb[k * N + col]);
+                    }
+                }
+                if (mode == 1) {
+                    CT prev;
+                    memcpy(&prev, &r[j], 4);
+                    if constexpr (std::is_same_v<CT, float>) {
+                        acc = __fadd_rn(prev, acc);
+                    } else {
+                        acc = prev + acc;
+                    }
+                } else if (mode == 2) {
+                    if constexpr (std::is_same_v<CT, float>) {
+                        acc = __fadd_rn(acc, bias[col]);
+                    } else {
+                        acc = acc + bias[col];
+                    }
+                }
+            }
+            memcpy(&r[j], &acc, 4);
+        }
+        tmem_st16(taddr + c0, r);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+#endif
+}
+
+template <typename TileAccT, typename TileLeftT, typename TileRightT>
+PTO_INTERNAL void matmul_dispatch(TileAccT &c, TileLeftT &a, TileRightT &b, bool accumulate)
+{
+    matmul_check<TileAccT, TileLeftT, TileRightT>();
+    if constexpr (sizeof(typename TileLeftT::DType) == 2) {
+        matmul_issue(c, a, b, accumulate);
+    } else {
+        matmul_plain(c, a, b, accumulate ? 1 : 0, nullptr);
+    }
+}
 } // namespace b200
 
+// The AccPhase argument selects the NPU's unit-flag handshake between the matrix pipe and the store that follows
+// (Partial: more products to come, Final: the accumulator is complete; include/pto/npu/a2a3/TMatmul.hpp:148-180 in the
+// reference).  Here completion is observed through set_flag(PIPE_M, ...) in every case, so the phase changes nothing.
 template <typename TileAccT, typename TileLeftT, typename TileRightT, typename... WaitEvents>
 PTO_INST RecordEvent TMATMUL(TileAccT &cMatrix, TileLeftT &aMatrix, TileRightT &bMatrix, WaitEvents &... events)
 {
-    b200::matmul_issue(cMatrix, aMatrix, bMatrix, false);
+    TSYNC(events...);
+    b200::matmul_dispatch(cMatrix, aMatrix, bMatrix, false);
     return {};
 }
+template <AccPhase Phase, typename TileAccT, typename TileLeftT, typename TileRightT, typename... WaitEvents>
+PTO_INST RecordEvent TMATMUL(TileAccT &cMatrix, TileLeftT &aMatrix, TileRightT &bMatrix, WaitEvents &... events)
+{
+    TSYNC(events...);
+    b200::matmul_dispatch(cMatrix, aMatrix, bMatrix, false);
+    return {};
+}
+
+// the accumulator is updated in place (the reference's kernels pass the same tile twice; a distinct input tile is
+// copied into the output's tensor-memory columns first)
+namespace b200 {
+template <typename TileAccT>
+PTO_INTERNAL void acc_copy(TileAccT &dst, TileAccT &src)
+{
+#if PTO_B200_DEVICE_CODE
+    if (dst.addr_ != src.addr_) {
+        const int warp = threadIdx.x >> 5, quarter = warp & 3, group = warp >> 2, groups = blockDim.x >> 7;
+        const uint32_t lane_base = control()->tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        __syncthreads();
+        tc_fence_after();
+        for (int c0 = group * 16; c0 < TileAccT::Cols; c0 += groups * 16) {
+            uint32_t r[16];
+            tmem_ld16(lane_base + src.addr_ + c0, r);
+            tmem_st16(lane_base + dst.addr_ + c0, r);
+        }
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+    }
+#endif
+}
+} // namespace b200
 
 template <typename TileAccT, typename TileLeftT, typename TileRightT, typename... WaitEvents>
 PTO_INST RecordEvent TMATMUL_ACC(TileAccT &cOutMatrix, TileAccT &cInMatrix, TileLeftT &aMatrix, TileRightT &bMatrix,
                                  WaitEvents &... events)
 {
-    // the accumulator is updated in place (the reference's kernels pass the same tile twice)
-    (void)cInMatrix;
-    b200::matmul_issue(cOutMatrix, aMatrix, bMatrix, true);
+    TSYNC(events...);
+    b200::acc_copy(cOutMatrix, cInMatrix);
+    b200::matmul_dispatch(cOutMatrix, aMatrix, bMatrix, true);
+    return {};
+}
+template <AccPhase Phase, typename TileAccT, typename TileLeftT, typename TileRightT, typename... WaitEvents>
+PTO_INST RecordEvent TMATMUL_ACC(TileAccT &cOutMatrix, TileAccT &cInMatrix, TileLeftT &aMatrix, TileRightT &bMatrix,
+                                 WaitEvents &... events)
+{
+    TSYNC(events...);
+    b200::acc_copy(cOutMatrix, cInMatrix);
+    b200::matmul_dispatch(cOutMatrix, aMatrix, bMatrix, true);
+    return {};
+}
+// shared accumulator tile (include/pto/common/pto_instr.hpp:498-507 in the reference)
+template <AccPhase Phase = AccPhase::Unspecified, typename TileAccT, typename TileLeftT, typename TileRightT,
+          typename... WaitEvents,
+          std::enable_if_t<TileLeftT::Loc == TileType::Left && TileRightT::Loc == TileType::Right, int> = 0>
+PTO_INST RecordEvent TMATMUL_ACC(TileAccT &cMatrix, TileLeftT &aMatrix, TileRightT &bMatrix, WaitEvents &... events)
+{
+    TSYNC(events...);
+    b200::matmul_dispatch(cMatrix, aMatrix, bMatrix, true);
     return {};
 }
 
-// TMATMUL_BIAS (include/pto/cpu/TMatmul.hpp:99-116): C = A * B + bias, one bias value per column.  The bias row is
-// written into every lane of the accumulator's tensor-memory columns first, then the product is accumulated onto it.
-template <typename TileAccT, typename TileLeftT, typename TileRightT, typename TileBiasT, typename... WaitEvents>
+// TMATMUL_BIAS (include/pto/cpu/TMatmul.hpp:99-116): C = A * B + bias, one bias value per column.  On the tensor core
+// the bias row is written into every lane of the accumulator's tensor-memory columns first, then the product is
+// accumulated onto it.
+template <typename TileAccT, typename TileLeftT, typename TileRightT, typename TileBiasT, typename... WaitEvents,
+          std::enable_if_t<TileBiasT::Loc == TileType::Bias, int> = 0>
 PTO_INST RecordEvent TMATMUL_BIAS(TileAccT &cMatrix, TileLeftT &aMatrix, TileRightT &bMatrix, TileBiasT &biasData,
                                   WaitEvents &... events)
 {
+    TSYNC(events...);
     static_assert(TileBiasT::Loc == TileType::Bias && TileBiasT::Rows == 1 && TileBiasT::Cols == TileAccT::Cols,
                   "TMATMUL_BIAS: the bias is a 1 x N tile of TileType::Bias");
-    static_assert(std::is_same_v<typename TileBiasT::DType, float>, "TMATMUL_BIAS: fp32 bias");
+    static_assert(std::is_same_v<typename TileBiasT::DType, typename TileAccT::DType>,
+                  "TMATMUL_BIAS: the bias has the accumulator's type");
     static_assert(TileAccT::Cols % 16 == 0, "TMATMUL_BIAS: accumulator width must be a multiple of 16");
+    b200::matmul_check<TileAccT, TileLeftT, TileRightT>();
+    if constexpr (sizeof(typename TileLeftT::DType) != 2) {
 #if PTO_B200_DEVICE_CODE
-    {
+        b200::matmul_plain(cMatrix, aMatrix, bMatrix, 2, biasData.data());
+#endif
+    } else {
+#if PTO_B200_DEVICE_CODE
         const int warp = threadIdx.x >> 5;
         const int quarter = warp & 3; // tensor-memory lanes [32 * quarter, +32) are writable by this warp
         const int group = warp >> 2, groups = blockDim.x >> 7;
@@ -390,15 +625,43 @@ PTO_INST RecordEvent TMATMUL_BIAS(TileAccT &cMatrix, TileLeftT &aMatrix, TileRig
         }
         b200::tc_fence_before();
         __syncthreads();
-    }
 #endif
-    b200::matmul_issue(cMatrix, aMatrix, bMatrix, true);
+        b200::matmul_issue(cMatrix, aMatrix, bMatrix, true);
+    }
     return {};
+}
+template <AccPhase Phase, typename TileAccT, typename TileLeftT, typename TileRightT, typename TileBiasT,
+          typename... WaitEvents, std::enable_if_t<TileBiasT::Loc == TileType::Bias, int> = 0>
+PTO_INST RecordEvent TMATMUL_BIAS(TileAccT &cMatrix, TileLeftT &aMatrix, TileRightT &bMatrix, TileBiasT &biasData,
+                                  WaitEvents &... events)
+{
+    return TMATMUL_BIAS(cMatrix, aMatrix, bMatrix, biasData, events...);
 }
 
 // ---------------------------------------------------------------- TSTORE
-template <typename GlobalData, typename TileData, typename... WaitEvents>
-PTO_INST RecordEvent TSTORE(GlobalData &dst, TileData &src, WaitEvents &... events)
+// Vec -> GM follows include/pto/cpu/TStore.hpp:121-150 in the reference (the mirror image of TLOAD's folding of the five
+// dimensions); Acc -> GM reads the accumulator out of tensor memory, converting fp32 to the global tensor's 16-bit type
+// where that differs (docs/isa/TSTORE.md:67-72).  AtomicType::AtomicAdd adds into the destination; ReluPreMode::
+// NormalRelu clamps negative accumulator values to zero before the store; the STPhase argument belongs to the NPU's
+// unit-flag handshake and changes nothing here (completion is observed through set_flag).
+namespace b200 {
+template <typename GT, AtomicType kAtomic>
+PTO_INTERNAL void store_elem(GT *p, GT v)
+{
+#if PTO_B200_DEVICE_CODE
+    if constexpr (kAtomic == AtomicType::AtomicAdd) {
+        static_assert(std::is_same_v<GT, float> || std::is_same_v<GT, int32_t> || std::is_same_v<GT, __half> ||
+                          std::is_same_v<GT, __nv_bfloat16>,
+                      "TSTORE<AtomicAdd>: float, int32, half or bfloat16 destinations");
+        atomicAdd(p, v);
+    } else {
+        *p = v;
+    }
+#endif
+}
+
+template <AtomicType kAtomic, ReluPreMode kRelu, typename GlobalData, typename TileData>
+PTO_INTERNAL void tstore(GlobalData &dst, TileData &src)
 {
 #if PTO_B200_DEVICE_CODE
     using GT = typename GlobalData::DType;
@@ -406,44 +669,130 @@ PTO_INST RecordEvent TSTORE(GlobalData &dst, TileData &src, WaitEvents &... even
     const int64_t s3 = dst.GetStride(3), s4 = dst.GetStride(4);
     const int vr = src.GetValidRow(), vc = src.GetValidCol();
     if constexpr (TileData::Loc == TileType::Acc) {
-        static_assert(std::is_same_v<typename TileData::DType, float>, "TSTORE: fp32 accumulator tiles");
+        using CT = typename TileData::DType;
+        static_assert(sizeof(CT) == 4, "TSTORE: 32-bit accumulator tiles");
         static_assert(TileData::Cols % 16 == 0, "TSTORE: accumulator width must be a multiple of 16");
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const int quarter = warp & 3;   // tensor-memory lanes [32 * quarter, +32) are readable by this warp
         const int group = warp >> 2, groups = blockDim.x >> 7;
         const int row = quarter * 32 + lane;
-        const uint32_t taddr = b200::control()->tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + src.addr_;
-        b200::tc_fence_after();
+        const uint32_t taddr = control()->tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + src.addr_;
+        tc_fence_after();
         for (int c0 = group * 16; c0 < TileData::Cols; c0 += groups * 16) {
             uint32_t r[16];
-            b200::tmem_ld16(taddr + c0, r);
+            tmem_ld16(taddr + c0, r);
             if (row < vr) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     if (c0 + j < vc) {
-                        const float v = __uint_as_float(r[j]);
-                        if constexpr (std::is_same_v<GT, float>) {
-                            g[row * s3 + (c0 + j) * s4] = v;
+                        CT v;
+                        memcpy(&v, &r[j], 4);
+                        if (kRelu == ReluPreMode::NormalRelu && v < CT(0)) {
+                            v = CT(0);
+                        }
+                        if constexpr (std::is_same_v<GT, CT>) {
+                            store_elem<GT, kAtomic>(&g[row * s3 + (c0 + j) * s4], v);
                         } else {
-                            g[row * s3 + (c0 + j) * s4] = b200::convert<GT, float>(v, RoundMode::CAST_RINT);
+                            static_assert(std::is_same_v<CT, float>, "TSTORE: only fp32 accumulators are converted");
+                            store_elem<GT, kAtomic>(&g[row * s3 + (c0 + j) * s4],
+                                                    convert<GT, float>(v, RoundMode::CAST_RINT));
                         }
                     }
                 }
             }
         }
-        b200::tc_fence_before();
+        tc_fence_before();
     } else {
         static_assert(TileData::Loc == TileType::Vec, "TSTORE: source must be a Vec or Acc tile");
+        static_assert(TileData::SFractal == SLayout::NoneBox, "TSTORE: plain (NoneBox) vector tiles");
         static_assert(sizeof(typename TileData::DType) == sizeof(GT), "TSTORE: element sizes differ");
         using T = typename TileData::DType;
         const T *t = src.data();
         T *gt = reinterpret_cast<T *>(g);
-        for (int i = threadIdx.x; i < vr * vc; i += blockDim.x) {
-            const int r = i / vc, c = i - r * vc;
-            gt[r * s3 + c * s4] = t[b200::vec_offset<TileData>(r, c)];
+        const int64_t n0 = dst.GetShape(0), n1 = dst.GetShape(1), n2 = dst.GetShape(2), n3 = dst.GetShape(3),
+                      n4 = dst.GetShape(4);
+        const int64_t outer = n0 * n1 * n2, per = n3 * n4;
+        for (int64_t i = threadIdx.x; i < outer * per; i += blockDim.x) {
+            const int64_t o = i / per, rc = i - o * per;
+            const int64_t r = (s4 == 1) ? rc / n4 : rc % n3, c = (s4 == 1) ? rc % n4 : rc / n3;
+            const int64_t i2 = o % n2, i1 = (o / n2) % n1, i0 = o / (n2 * n1);
+            const int off = folded_offset<TileData>(o, r, c, n3, n4);
+            const int tr = TileData::isRowMajor ? off / TileData::Cols : off % TileData::Rows;
+            const int tc = TileData::isRowMajor ? off % TileData::Cols : off / TileData::Rows;
+            if (tr < vr && tc < vc) {
+                store_elem<T, kAtomic>(&gt[i0 * dst.GetStride(0) + i1 * dst.GetStride(1) + i2 * dst.GetStride(2) +
+                                           r * s3 + c * s4],
+                                       t[off]);
+            }
         }
     }
 #endif
+}
+} // namespace b200
+
+template <typename TileData, typename GlobalData, typename... WaitEvents,
+          std::enable_if_t<is_global<GlobalData>::value && is_tile<TileData>::value, int> = 0>
+PTO_INST RecordEvent TSTORE(GlobalData &dst, TileData &src, WaitEvents &... events)
+{
+    TSYNC(events...);
+    b200::tstore<AtomicType::AtomicNone, ReluPreMode::NoRelu>(dst, src);
+    return {};
+}
+template <STPhase Phase, typename TileData, typename GlobalData, typename... WaitEvents,
+          std::enable_if_t<is_global<GlobalData>::value && is_tile<TileData>::value, int> = 0>
+PTO_INST RecordEvent TSTORE(GlobalData &dst, TileData &src, WaitEvents &... events)
+{
+    TSYNC(events...);
+    b200::tstore<AtomicType::AtomicNone, ReluPreMode::NoRelu>(dst, src);
+    return {};
+}
+template <typename TileData, typename GlobalData, AtomicType atomicType, typename... WaitEvents>
+PTO_INST RecordEvent TSTORE(GlobalData &dst, TileData &src, WaitEvents &... events)
+{
+    TSYNC(events...);
+    b200::tstore<atomicType, ReluPreMode::NoRelu>(dst, src);
+    return {};
+}
+template <STPhase Phase, typename TileData, typename GlobalData, AtomicType atomicType, typename... WaitEvents>
+PTO_INST RecordEvent TSTORE(GlobalData &dst, TileData &src, WaitEvents &... events)
+{
+    TSYNC(events...);
+    b200::tstore<atomicType, ReluPreMode::NoRelu>(dst, src);
+    return {};
+}
+template <typename TileData, typename GlobalData, AtomicType atomicType, ReluPreMode reluPreMode, typename... WaitEvents>
+PTO_INST RecordEvent TSTORE(GlobalData &dst, TileData &src, WaitEvents &... events)
+{
+    TSYNC(events...);
+    b200::tstore<atomicType, reluPreMode>(dst, src);
+    return {};
+}
+template <STPhase Phase, typename TileData, typename GlobalData, AtomicType atomicType, ReluPreMode reluPreMode,
+          typename... WaitEvents>
+PTO_INST RecordEvent TSTORE(GlobalData &dst, TileData &src, WaitEvents &... events)
+{
+    TSYNC(events...);
+    b200::tstore<atomicType, reluPreMode>(dst, src);
+    return {};
+}
+
+// the pre-quantisation scalar is accepted and, as in the simulation (include/pto/cpu/TStore.hpp:152-157), not applied
+template <typename TileData, typename GlobalData, AtomicType atomicType = AtomicType::AtomicNone,
+          ReluPreMode reluPreMode = ReluPreMode::NoRelu, typename... WaitEvents>
+PTO_INST RecordEvent TSTORE(GlobalData &dst, TileData &src, uint64_t preQuantScalar, WaitEvents &... events)
+{
+    TSYNC(events...);
+    (void)preQuantScalar;
+    b200::tstore<atomicType, reluPreMode>(dst, src);
+    return {};
+}
+template <STPhase Phase, typename TileData, typename GlobalData, AtomicType atomicType = AtomicType::AtomicNone,
+          ReluPreMode reluPreMode = ReluPreMode::NoRelu, typename... WaitEvents>
+PTO_INST RecordEvent TSTORE(GlobalData &dst, TileData &src, uint64_t preQuantScalar, WaitEvents &... events)
+{
+    TSYNC(events...);
+    (void)preQuantScalar;
+    b200::tstore<atomicType, reluPreMode>(dst, src);
     return {};
 }
 
@@ -455,6 +804,7 @@ PTO_INST RecordEvent TSTORE(GlobalData &dst, TileData &src, WaitEvents &... even
 template <typename DstTileData, typename SrcTileData, typename... WaitEvents>
 PTO_INST RecordEvent TMOV(DstTileData &dst, SrcTileData &src, WaitEvents &... events)
 {
+    TSYNC(events...);
     if constexpr (SrcTileData::Loc == TileType::Mat) {
         return TEXTRACT(dst, src, 0, 0);
     } else {
@@ -474,9 +824,13 @@ PTO_INST RecordEvent TMOV(DstTileData &dst, SrcTileData &src, WaitEvents &... ev
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         if (c0 + j < src.GetValidCol()) {
-                            t[b200::vec_offset<DstTileData>(row, c0 + j)] =
-                                b200::convert<typename DstTileData::DType, float>(__uint_as_float(r[j]),
-                                                                                  RoundMode::CAST_RINT);
+                            if constexpr (std::is_same_v<typename DstTileData::DType, typename SrcTileData::DType>) {
+                                memcpy(&t[b200::vec_offset<DstTileData>(row, c0 + j)], &r[j], 4);
+                            } else {
+                                t[b200::vec_offset<DstTileData>(row, c0 + j)] =
+                                    b200::convert<typename DstTileData::DType, float>(__uint_as_float(r[j]),
+                                                                                      RoundMode::CAST_RINT);
+                            }
                         }
                     }
                 }
@@ -537,6 +891,7 @@ PTO_INTERNAL void for_each_valid(DstT &dst, SrcT &src, F f)
 template <typename TileDataD, typename TileDataS, typename... WaitEvents>
 PTO_INST RecordEvent TCVT(TileDataD &dst, TileDataS &src, RoundMode mode, WaitEvents &... events)
 {
+    TSYNC(events...);
     b200::for_each_valid(dst, src, [&](typename TileDataD::DType &d, int r, int c) {
         d = b200::convert<typename TileDataD::DType, typename TileDataS::DType>(
             src.data()[b200::vec_offset<TileDataS>(r, c)], mode);
@@ -547,12 +902,14 @@ PTO_INST RecordEvent TCVT(TileDataD &dst, TileDataS &src, RoundMode mode, WaitEv
 template <typename TileDataD, typename TileDataS, typename... WaitEvents>
 PTO_INST RecordEvent TCVT(TileDataD &dst, TileDataS &src, RoundMode mode, SaturationMode, WaitEvents &... events)
 {
+    TSYNC(events...);
     return TCVT(dst, src, mode);
 }
 
 template <typename TileData, typename... WaitEvents>
 PTO_INST RecordEvent TEXP(TileData &dst, TileData &src, WaitEvents &... events)
 {
+    TSYNC(events...);
     b200::for_each_valid(dst, dst, [&](typename TileData::DType &d, int r, int c) {
 #if PTO_B200_DEVICE_CODE
         d = b200::convert<typename TileData::DType, float>(
@@ -565,12 +922,14 @@ PTO_INST RecordEvent TEXP(TileData &dst, TileData &src, WaitEvents &... events)
 }
 
 #define PTO_B200_BINARY(NAME, EXPR)                                                                              \
-    template <typename TileData, typename... WaitEvents>                                                         \
-    PTO_INST RecordEvent NAME(TileData &dst, TileData &src0, TileData &src1, WaitEvents &... events)             \
+    template <typename TileData, typename TileSrc0, typename TileSrc1, typename... WaitEvents,                   \
+              std::enable_if_t<is_tile<TileSrc0>::value && is_tile<TileSrc1>::value, int> = 0>                   \
+    PTO_INST RecordEvent NAME(TileData &dst, TileSrc0 &src0, TileSrc1 &src1, WaitEvents &... events)             \
     {                                                                                                            \
+        TSYNC(events...);                                                                                        \
         b200::for_each_valid(dst, dst, [&](typename TileData::DType &d, int r, int c) {                          \
-            const auto a = src0.data()[b200::vec_offset<TileData>(r, c)];                                        \
-            const auto b = src1.data()[b200::vec_offset<TileData>(r, c)];                                        \
+            const typename TileData::DType a = src0.data()[b200::vec_offset<TileSrc0>(r, c)];                    \
+            const typename TileData::DType b = src1.data()[b200::vec_offset<TileSrc1>(r, c)];                    \
             d = (EXPR);                                                                                          \
         });                                                                                                      \
         return {};                                                                                               \
@@ -587,6 +946,7 @@ PTO_B200_BINARY(TMIN, (b < a) ? b : a)
     template <typename TileData, typename... WaitEvents>                                                         \
     PTO_INST RecordEvent NAME(TileData &dst, TileData &src0, typename TileData::DType s, WaitEvents &... events)  \
     {                                                                                                            \
+        TSYNC(events...);          \
         b200::for_each_valid(dst, dst, [&](typename TileData::DType &d, int r, int c) {                          \
             const auto a = src0.data()[b200::vec_offset<TileData>(r, c)];                                        \
             d = (EXPR);                                                                                          \
@@ -618,6 +978,7 @@ PTO_INTERNAL typename TileVec::DType row_scalar(TileVec &src1, int r)
     template <typename TileDst, typename TileSrc1, typename... WaitEvents>                                       \
     PTO_INST RecordEvent NAME(TileDst &dst, TileDst &src0, TileSrc1 &src1, WaitEvents &... events)               \
     {                                                                                                            \
+        TSYNC(events...);          \
         b200::for_each_valid(dst, dst, [&](typename TileDst::DType &d, int r, int c) {                           \
             const auto a = src0.data()[b200::vec_offset<TileDst>(r, c)];                                         \
             const auto s = static_cast<typename TileDst::DType>(b200::row_scalar(src1, r));                      \
@@ -638,6 +999,7 @@ PTO_B200_ROWEXPAND(TROWEXPANDEXPDIF, static_cast<typename TileDst::DType>(exp(st
 template <typename TileDataDst, typename TileDataSrc, typename... WaitEvents>
 PTO_INST RecordEvent TROWEXPAND(TileDataDst &dst, TileDataSrc &src, WaitEvents &... events)
 {
+    TSYNC(events...);
     b200::for_each_valid(dst, dst, [&](typename TileDataDst::DType &d, int r, int) {
         d = static_cast<typename TileDataDst::DType>(src.data()[b200::vec_offset<TileDataSrc>(r, 0)]);
     });
@@ -677,6 +1039,7 @@ PTO_INTERNAL void row_reduce(TileOut &dst, TileIn &src)
 template <typename TileOut, typename TileIn, typename TileTmp, typename... WaitEvents>
 PTO_INST RecordEvent TROWMAX(TileOut &dst, TileIn &src, TileTmp &tmp, WaitEvents &... events)
 {
+    TSYNC(events...);
     b200::row_reduce<1>(dst, src);
     return {};
 }
@@ -684,6 +1047,7 @@ PTO_INST RecordEvent TROWMAX(TileOut &dst, TileIn &src, TileTmp &tmp, WaitEvents
 template <typename TileOut, typename TileIn, typename TileTmp, typename... WaitEvents>
 PTO_INST RecordEvent TROWSUM(TileOut &dst, TileIn &src, TileTmp &tmp, WaitEvents &... events)
 {
+    TSYNC(events...);
     b200::row_reduce<0>(dst, src);
     return {};
 }
@@ -691,6 +1055,7 @@ PTO_INST RecordEvent TROWSUM(TileOut &dst, TileIn &src, TileTmp &tmp, WaitEvents
 template <typename TileOut, typename TileIn, typename TileTmp, typename... WaitEvents>
 PTO_INST RecordEvent TROWMIN(TileOut &dst, TileIn &src, TileTmp &tmp, WaitEvents &... events)
 {
+    TSYNC(events...);
     b200::row_reduce<2>(dst, src);
     return {};
 }
@@ -727,24 +1092,28 @@ PTO_INTERNAL void col_reduce(TileOut &dst, TileIn &src)
 template <typename TileOut, typename TileIn, typename... WaitEvents>
 PTO_INST RecordEvent TCOLSUM(TileOut &dst, TileIn &src, WaitEvents &... events)
 {
+    TSYNC(events...);
     b200::col_reduce<0>(dst, src);
     return {};
 }
 template <typename TileOut, typename TileIn, typename TileTmp, typename... WaitEvents>
 PTO_INST RecordEvent TCOLSUM(TileOut &dst, TileIn &src, TileTmp &tmp, bool isBinary, WaitEvents &... events)
 {
+    TSYNC(events...);
     b200::col_reduce<0>(dst, src);
     return {};
 }
 template <typename TileOut, typename TileIn, typename... WaitEvents>
 PTO_INST RecordEvent TCOLMAX(TileOut &dst, TileIn &src, WaitEvents &... events)
 {
+    TSYNC(events...);
     b200::col_reduce<1>(dst, src);
     return {};
 }
 template <typename TileOut, typename TileIn, typename... WaitEvents>
 PTO_INST RecordEvent TCOLMIN(TileOut &dst, TileIn &src, WaitEvents &... events)
 {
+    TSYNC(events...);
     b200::col_reduce<2>(dst, src);
     return {};
 }
@@ -796,6 +1165,7 @@ PTO_INTERNAL void fill_pad(TileDataDst &dst, TileDataSrc &src)
 template <typename DstTileData, typename SrcTileData, typename... WaitEvents>
 PTO_INST RecordEvent TFILLPAD(DstTileData &dst, SrcTileData &src, WaitEvents &... events)
 {
+    TSYNC(events...);
     static_assert(DstTileData::Cols == SrcTileData::Cols && DstTileData::Rows == SrcTileData::Rows,
                   "TFILLPAD: dst and src have the same rows and columns");
     b200::fill_pad(dst, src);
@@ -804,6 +1174,7 @@ PTO_INST RecordEvent TFILLPAD(DstTileData &dst, SrcTileData &src, WaitEvents &..
 template <typename DstTileData, typename SrcTileData, typename... WaitEvents>
 PTO_INST RecordEvent TFILLPAD_INPLACE(DstTileData &dst, SrcTileData &src, WaitEvents &... events)
 {
+    TSYNC(events...);
     static_assert(DstTileData::Cols == SrcTileData::Cols && DstTileData::Rows == SrcTileData::Rows,
                   "TFILLPAD_INPLACE: dst and src have the same rows and columns");
     b200::fill_pad(dst, src);
@@ -812,6 +1183,7 @@ PTO_INST RecordEvent TFILLPAD_INPLACE(DstTileData &dst, SrcTileData &src, WaitEv
 template <typename DstTileData, typename SrcTileData, typename... WaitEvents>
 PTO_INST RecordEvent TFILLPAD_EXPAND(DstTileData &dst, SrcTileData &src, WaitEvents &... events)
 {
+    TSYNC(events...);
     static_assert(DstTileData::Cols >= SrcTileData::Cols && DstTileData::Rows >= SrcTileData::Rows,
                   "TFILLPAD_EXPAND: dst is at least as large as src");
     b200::fill_pad(dst, src);
@@ -822,6 +1194,7 @@ PTO_INST RecordEvent TFILLPAD_EXPAND(DstTileData &dst, SrcTileData &src, WaitEve
 template <typename TileDataDst, typename TileDataSrc, typename TileDataTmp, typename... WaitEvents>
 PTO_INST RecordEvent TTRANS(TileDataDst &dst, TileDataSrc &src, TileDataTmp &tmp, WaitEvents &... events)
 {
+    TSYNC(events...);
     static_assert(TileDataSrc::ValidRow == TileDataDst::ValidCol && TileDataSrc::ValidCol == TileDataDst::ValidRow,
                   "TTRANS: the valid extents of dst are those of src exchanged");
 #if PTO_B200_DEVICE_CODE
@@ -840,6 +1213,7 @@ PTO_INST RecordEvent TTRANS(TileDataDst &dst, TileDataSrc &src, TileDataTmp &tmp
 template <typename TileData, int isUpperOrLower, typename... WaitEvents>
 PTO_INST RecordEvent TTRI(TileData &dst, int diagonal, WaitEvents &... events)
 {
+    TSYNC(events...);
     static_assert(isUpperOrLower == 0 || isUpperOrLower == 1, "TTRI: isUpperOrLower must be 0 or 1");
     static_assert(TileData::isRowMajor, "TTRI: row-major tiles only");
 #if PTO_B200_DEVICE_CODE
@@ -856,29 +1230,25 @@ PTO_INST RecordEvent TTRI(TileData &dst, int diagonal, WaitEvents &... events)
     return {};
 }
 
-// ---------------------------------------------------------------- TRESHAPE (include/pto/cpu/TReshape.hpp:18-56)
-// The same bytes under another tile type of the same location and total size.  The simulation copies the storage; here
-// both tiles are handles into one arena, so the bytes are copied only when the handles differ.
+// ---------------------------------------------------------------- TRESHAPE
+// The same bytes under another tile type of the same location and total size.  As on the NPU
+// (include/pto/npu/a2a3/TReshape.hpp:21-51 in the reference) the destination is re-bound to the source's storage, so
+// that writes through either tile are seen through the other: the reference's streaming softmax relies on this
+// (kernels/manual/common/flash_atten/pto_macro_fa_softmax.hpp:141-165).  The CPU simulation copies the bytes instead
+// (include/pto/cpu/TReshape.hpp:18-56); a program that only reads the reshaped tile sees the same values either way.
 template <typename TileDataOut, typename TileDataIn, typename... WaitEvents>
 PTO_INST RecordEvent TRESHAPE(TileDataOut &dst, TileDataIn &src, WaitEvents &... events)
 {
+    TSYNC(events...);
     static_assert(TileDataOut::Loc == TileDataIn::Loc, "TRESHAPE: source and target TileType must be the same");
     static_assert(sizeof(typename TileDataOut::DType) * TileDataOut::Rows * TileDataOut::Cols ==
                       sizeof(typename TileDataIn::DType) * TileDataIn::Rows * TileDataIn::Cols,
                   "TRESHAPE: total byte size must match");
-    static_assert(TileDataOut::Loc == TileType::Vec, "TRESHAPE: vector tiles");
-#if PTO_B200_DEVICE_CODE
-    constexpr int kBytes = sizeof(typename TileDataIn::DType) * TileDataIn::Rows * TileDataIn::Cols;
-    static_assert(kBytes % 4 == 0, "TRESHAPE: tile storage is a multiple of 4 bytes");
-    const uint32_t *s = reinterpret_cast<const uint32_t *>(src.data());
-    uint32_t *d = reinterpret_cast<uint32_t *>(dst.data());
-    if (s != d) {
-        for (int i = threadIdx.x; i < kBytes / 4; i += blockDim.x) {
-            d[i] = s[i];
-        }
-    }
-    __syncthreads();
-#endif
+    static_assert((TileDataOut::SFractal == SLayout::NoneBox) == (TileDataIn::SFractal == SLayout::NoneBox),
+                  "TRESHAPE: cannot reshape between boxed and non-boxed layouts");
+    dst.addr_ = src.addr_;
+    dst.pitch_ = src.pitch_;
+    dst.major_ = src.major_;
     return {};
 }
 
@@ -888,6 +1258,7 @@ PTO_INST RecordEvent TRESHAPE(TileDataOut &dst, TileDataIn &src, WaitEvents &...
 template <typename TileData, typename MaskTile, typename... WaitEvents>
 PTO_INST RecordEvent TSEL(TileData &dst, MaskTile &selMask, TileData &src0, TileData &src1, WaitEvents &... events)
 {
+    TSYNC(events...);
     const int mask_cols = selMask.GetValidCol();
     const int vc = dst.GetValidCol();
     b200::for_each_valid(dst, dst, [&](typename TileData::DType &d, int r, int c) {
@@ -927,6 +1298,7 @@ PTO_INTERNAL uint8_t cmps_call(T a, T b, CmpMode mode)
 template <typename TileDataDst, typename TileDataSrc, typename T, typename... WaitEvents>
 PTO_INST RecordEvent TCMPS(TileDataDst &dst, TileDataSrc &src0, T src1, CmpMode cmpMode, WaitEvents &... events)
 {
+    TSYNC(events...);
 #if PTO_B200_DEVICE_CODE
     constexpr int H = TileDataSrc::Rows, W = TileDataSrc::Cols;
     constexpr int bytes_per_row = W / 8;
@@ -958,6 +1330,7 @@ PTO_INST RecordEvent TCMPS(TileDataDst &dst, TileDataSrc &src0, T src1, CmpMode 
 template <typename TileDataDst, typename TileDataSrc, typename... WaitEvents>
 PTO_INST RecordEvent TCMP(TileDataDst &dst, TileDataSrc &src0, TileDataSrc &src1, CmpMode cmpMode, WaitEvents &... events)
 {
+    TSYNC(events...);
     b200::for_each_valid(dst, dst, [&](typename TileDataDst::DType &d, int r, int c) {
         const auto a = src0.data()[b200::vec_offset<TileDataSrc>(r, c)];
         const auto b = src1.data()[b200::vec_offset<TileDataSrc>(r, c)];
@@ -980,6 +1353,7 @@ PTO_INST RecordEvent TCMP(TileDataDst &dst, TileDataSrc &src0, TileDataSrc &src1
 template <typename TileDataD, typename TileDataS0, typename TileDataS1, typename... WaitEvents>
 PTO_INST RecordEvent TGATHER(TileDataD &dst, TileDataS0 &src0, TileDataS1 &src1, WaitEvents &... events)
 {
+    TSYNC(events...);
     static_assert(sizeof(typename TileDataS1::DType) == 4, "TGATHER: 32-bit indices");
     static_assert(std::is_same_v<typename TileDataD::DType, typename TileDataS0::DType>, "TGATHER: types differ");
     b200::for_each_valid(dst, dst, [&](typename TileDataD::DType &d, int r, int c) {
@@ -998,6 +1372,7 @@ PTO_INST RecordEvent TGATHER(TileDataD &dst, TileDataS0 &src0, TileDataS1 &src1,
 template <typename DstTileData, typename SrcTileData, MaskPattern maskPattern, typename... WaitEvents>
 PTO_INST RecordEvent TGATHER(DstTileData &dst, SrcTileData &src, WaitEvents &... events)
 {
+    TSYNC(events...);
     static_assert(DstTileData::isRowMajor && SrcTileData::isRowMajor, "TGATHER (mask): row-major tiles");
 #if PTO_B200_DEVICE_CODE
     constexpr int div = (maskPattern == MaskPattern::P1111) ? 1

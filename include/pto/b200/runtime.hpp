@@ -12,8 +12,14 @@
 //   Left     : [PTO_B200_L0A_OFFSET, PTO_B200_L0B_OFFSET)   48 KiB  (ping at 0, pong at 32 KiB, 16 KiB each)
 //   Right    : [PTO_B200_L0B_OFFSET, end of arena)          64 KiB+ (ping at 0, pong at 32 KiB, 32 KiB each)
 //   Bias     : a 1 KiB table in the control block (one row of up to 256 floats for TMATMUL_BIAS)
-// Define the two macros before including the PTO headers to move the windows.
+// Define the two macros before including the PTO headers to move the windows for a whole translation unit, or give
+// the offsets per launch (LaunchOptions).
 // 512 tensor-memory columns are allocated per block for Acc tiles.
+//
+// Every wait of a tile program (wait_flag, wait_flag_dev, Event::Wait) is bounded: the launch carries a limit in
+// nanoseconds (two seconds unless the caller gives one); a wait that runs out records the flag it waited for,
+// raises the block's abort flag so that all later waits return at once, and the block epilogue writes
+// {code 4, block, flag index, source / destination pipes} into the caller's status record.  Nothing traps.
 #pragma once
 
 #include <cuda.h>
@@ -34,18 +40,37 @@ constexpr int kBlockThreads = 256;
 constexpr int kNumPipes = 8;
 constexpr int kNumFlags = kNumPipes * kNumPipes * EVENT_ID_MAX; // 512
 constexpr int kTmemCols = 512;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull; // default limit of a wait
+constexpr int kNumDevFlags = 16;   // cross-core flag ids (wait_flag_dev / ffts_cross_core_sync)
+constexpr int kNumCoreStatics = 2; // function-local statics of tile programs (see PTO_B200_CORE_STATIC)
+constexpr int kWarps = kBlockThreads / 32;
+
+// What a block reports when one of its waits ran out (same layout as the status record of libpto_b200.so).
+struct StatusRecord {
+    int code;   // 0 ok, 4 = a wait gave up
+    int block;  // block index that reported
+    int where;  // index of the flag waited for: ((src pipe * 8 + dst pipe) * 8 + event id); 512 + id for a cross-core flag
+    int detail; // src pipe * 16 + dst pipe
+};
 
 struct Control {
     uint32_t tmem_base;
     int abort_flag;
     int error_code;
-    int pad;
+    int fail_where;                 // flag index of the first wait that gave up
+    unsigned long long wait_limit_ns;
     uint64_t flags[kNumFlags];
-    uint32_t phase[kNumFlags / 32][kBlockThreads / 32]; // phase bit of every flag, per warp
+    uint32_t phase[kNumFlags / 32][kWarps];              // phase bit of every flag, per warp
     uint8_t bias_table[1024];                            // the address space of TileType::Bias tiles (the NPU's bias table)
+    int dev_flags[kNumDevFlags];                         // counting flags between the cube and vector roles of a core
+    uint32_t event_next[kWarps][kNumPipes * kNumPipes / 8]; // next automatic event id of a pipe pair (4 bits each), per warp
+    unsigned long long core_static[kNumCoreStatics][kWarps]; // function-local statics of tile programs, per warp
+    uint32_t core_static_init[kWarps];                   // bit s set: slot s of this warp holds a value
+    uint32_t l0a_offset;                                 // start of the Left window of the arena (bytes)
+    uint32_t l0b_offset;                                 // start of the Right window of the arena (bytes)
 };
 constexpr int kControlBytes = ((int)sizeof(Control) + 1023) / 1024 * 1024;
+static_assert(kControlBytes == 6 * 1024, "the control block is 6 KiB: the arena is the other 220 KiB");
 constexpr int kDefaultSmemBytes = 227 * 1024; // 1 KiB alignment slack + control (6 KiB) + 220 KiB arena
 
 #if PTO_B200_DEVICE_CODE
@@ -69,7 +94,13 @@ __device__ __forceinline__ uint8_t *arena_of()
     if constexpr (Loc == TileType::Bias) {
         return control()->bias_table;
     } else {
-        return arena() + (Loc == TileType::Left ? PTO_B200_L0A_OFFSET : (Loc == TileType::Right ? PTO_B200_L0B_OFFSET : 0));
+        if constexpr (Loc == TileType::Left) {
+            return arena() + control()->l0a_offset;
+        } else if constexpr (Loc == TileType::Right) {
+            return arena() + control()->l0b_offset;
+        } else {
+            return arena();
+        }
     }
 }
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
@@ -107,9 +138,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
+__device__ __forceinline__ unsigned long long global_timer_ns()
 {
-    volatile int *abort_flag = &control()->abort_flag;
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    return now;
+}
+// the first wait of a block that gives up records what it waited for; every later wait returns at once
+__device__ __forceinline__ void give_up(int where)
+{
+    Control *ctl = control();
+    if (atomicCAS(&ctl->abort_flag, 0, 1) == 0) {
+        ctl->fail_where = where;
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int where = -1)
+{
+    Control *ctl = control();
+    volatile int *abort_flag = &ctl->abort_flag;
     unsigned long long t0 = 0;
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) {
@@ -119,19 +165,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
             if (*abort_flag) {
                 return false;
             }
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            const unsigned long long now = global_timer_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > kWaitLimitNs) {
-                break; // two seconds on the global timer: give up instead of hanging the device
+            } else if (now - t0 > ctl->wait_limit_ns) {
+                break; // the launch's limit on the global timer: give up instead of hanging the device
             }
             if (i > 4096) {
                 __nanosleep(64);
             }
         }
     }
-    *abort_flag = 1;
+    give_up(where);
     return false;
 }
 
@@ -155,7 +200,7 @@ __device__ __forceinline__ void tc_commit(uint64_t *bar)
 }
 
 // Block prologue / epilogue (called by the launch trampoline, not by tile programs).
-__device__ __forceinline__ void block_begin()
+__device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, uint32_t l0a_offset, uint32_t l0b_offset)
 {
     Control *ctl = control();
     const int nthreads = blockDim.x;
@@ -170,9 +215,22 @@ __device__ __forceinline__ void block_begin()
             ctl->phase[w][threadIdx.x >> 5] = 0;
         }
     }
+    for (int i = threadIdx.x; i < kWarps * kNumPipes * kNumPipes / 8; i += nthreads) {
+        (&ctl->event_next[0][0])[i] = 0;
+    }
+    if (threadIdx.x < kNumDevFlags) {
+        ctl->dev_flags[threadIdx.x] = 0;
+    }
+    if (threadIdx.x < kWarps) {
+        ctl->core_static_init[threadIdx.x] = 0;
+    }
     if (threadIdx.x == 0) {
         ctl->abort_flag = 0;
         ctl->error_code = 0;
+        ctl->fail_where = -1;
+        ctl->wait_limit_ns = wait_limit_ns == 0 ? kWaitLimitNs : wait_limit_ns;
+        ctl->l0a_offset = l0a_offset;
+        ctl->l0b_offset = l0b_offset;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (threadIdx.x < 32) {
@@ -186,14 +244,20 @@ __device__ __forceinline__ void block_begin()
     tc_fence_after();
 }
 
-__device__ __forceinline__ void block_end(int *status)
+__device__ __forceinline__ void block_end(StatusRecord *status)
 {
     asm volatile("cp.async.wait_all;" ::: "memory");
     tc_fence_before();
     __syncthreads();
     Control *ctl = control();
     if (ctl->abort_flag && threadIdx.x == 0 && status != nullptr) {
-        atomicCAS(status, 0, 4); // a bounded wait gave up
+        if (atomicCAS(&status->code, 0, 4) == 0) { // a bounded wait gave up; the first block to report wins
+            const int where = ctl->fail_where;
+            status->block = static_cast<int>(blockIdx.x);
+            status->where = where;
+            status->detail = where >= 0 && where < kNumFlags ? ((where >> 6) & 7) * 16 + ((where >> 3) & 7) : -1;
+            __threadfence();
+        }
     }
     if (threadIdx.x < 32) {
         tc_fence_after();
@@ -205,28 +269,50 @@ __device__ __forceinline__ void block_end(int *status)
 
 // The real kernel that hosts a tile program.  It is declared here, before `__global__` loses its CUDA
 // meaning for the rest of the translation unit (see pto-inst.hpp).
+// What a launch may set beside the program: `status` is a device record (four ints, zero before the launch) that
+// receives {4, block, flag, pipes} when a block gave up on a wait; `wait_limit_ns` bounds every wait of the program
+// (0: two seconds); the two offsets place the Left and Right windows of the arena.
+struct LaunchOptions {
+    void *status = nullptr;
+    int smem_bytes = kDefaultSmemBytes;
+    unsigned long long wait_limit_ns = 0;
+    uint32_t l0a_offset = PTO_B200_L0A_OFFSET;
+    uint32_t l0b_offset = PTO_B200_L0B_OFFSET;
+};
+
 template <typename Program>
-__global__ void __launch_bounds__(kBlockThreads, 1) block_kernel(Program program, int *status)
+__global__ void __launch_bounds__(kBlockThreads, 1)
+    block_kernel(Program program, StatusRecord *status, unsigned long long wait_limit_ns, uint32_t l0a_offset,
+                 uint32_t l0b_offset)
 {
 #if PTO_B200_DEVICE_CODE
-    block_begin();
+    block_begin(wait_limit_ns, l0a_offset, l0b_offset);
     program();
     block_end(status);
 #endif
 }
 
-// Launches `program` (a __device__ callable) on `blocks` thread blocks of the stream.  `status`, if given,
-// is a device word that receives 4 when a block gave up on a flag wait.
+// Launches `program` (a __device__ callable) on `blocks` thread blocks of the stream.
 template <typename Program>
-inline cudaError_t launch(uint32_t blocks, void *stream, Program program, int *status = nullptr,
-                          int smem_bytes = kDefaultSmemBytes)
+inline cudaError_t launch(uint32_t blocks, void *stream, Program program, const LaunchOptions &opt)
 {
-    cudaError_t e = cudaFuncSetAttribute(block_kernel<Program>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    cudaError_t e =
+        cudaFuncSetAttribute(block_kernel<Program>, cudaFuncAttributeMaxDynamicSharedMemorySize, opt.smem_bytes);
     if (e != cudaSuccess) {
         return e;
     }
-    block_kernel<Program><<<blocks, kBlockThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(program, status);
+    block_kernel<Program><<<blocks, kBlockThreads, opt.smem_bytes, static_cast<cudaStream_t>(stream)>>>(
+        program, static_cast<StatusRecord *>(opt.status), opt.wait_limit_ns, opt.l0a_offset, opt.l0b_offset);
     return cudaGetLastError();
+}
+template <typename Program>
+inline cudaError_t launch(uint32_t blocks, void *stream, Program program, void *status = nullptr,
+                          int smem_bytes = kDefaultSmemBytes)
+{
+    LaunchOptions opt;
+    opt.status = status;
+    opt.smem_bytes = smem_bytes;
+    return launch(blocks, stream, program, opt);
 }
 
 } // namespace b200
@@ -236,6 +322,17 @@ inline cudaError_t launch(uint32_t blocks, void *stream, Program program, int *s
 // name (with its template arguments), followed by the block count, the stream and the kernel's arguments.
 #define PTO_B200_LAUNCH(kernel, blocks, stream, ...) \
     (void)pto::b200::launch((blocks), (stream), [=] __device__() { kernel(__VA_ARGS__); })
+
+// start of the block's arena (the address space of Vec and Mat tiles) for programs that place data there themselves,
+// e.g. the ring of an on-chip FIFO
+PTO_INTERNAL uint8_t *pto_b200_arena()
+{
+#if PTO_B200_DEVICE_CODE
+    return pto::b200::arena();
+#else
+    return nullptr;
+#endif
+}
 
 // ---------------------------------------------------------------- block id, flags
 PTO_INTERNAL uint32_t get_block_idx()
@@ -259,7 +356,7 @@ PTO_INTERNAL uint32_t get_block_num()
 //   PIPE_M    : tcgen05.commit by the issuing thread (covers all earlier tcgen05.mma)
 //   PIPE_MTE2 : every thread arrives when its own asynchronous copies have landed
 //   others    : their work is synchronous per thread, every thread arrives
-PTO_INTERNAL void set_flag(pipe_t src, pipe_t dst, event_t id)
+PTO_INTERNAL void set_flag(pipe_t src, pipe_t dst, int id)
 {
 #if PTO_B200_DEVICE_CODE
     uint64_t *bar = &pto::b200::control()->flags[pto::b200::flag_index(src, dst, id)];
@@ -283,7 +380,7 @@ PTO_INTERNAL void set_flag(pipe_t src, pipe_t dst, event_t id)
 }
 
 // wait_flag(src, dst, id): every thread waits for the matching set_flag (the n-th wait pairs with the n-th set).
-PTO_INTERNAL void wait_flag(pipe_t src, pipe_t dst, event_t id)
+PTO_INTERNAL void wait_flag(pipe_t src, pipe_t dst, int id)
 {
 #if PTO_B200_DEVICE_CODE
     pto::b200::Control *ctl = pto::b200::control();
@@ -292,7 +389,7 @@ PTO_INTERNAL void wait_flag(pipe_t src, pipe_t dst, event_t id)
     volatile uint32_t *word = &ctl->phase[f >> 5][threadIdx.x >> 5];
     const uint32_t bit = 1u << (f & 31);
     const uint32_t parity = (*word & bit) ? 1u : 0u;
-    pto::b200::mbar_wait(&ctl->flags[f], parity);
+    pto::b200::mbar_wait(&ctl->flags[f], parity, f);
     __syncwarp();
     if ((threadIdx.x & 31) == 0) {
         *word ^= bit;
@@ -314,3 +411,151 @@ PTO_INTERNAL void pipe_barrier(pipe_t pipe)
     __syncthreads();
 #endif
 }
+
+// ---------------------------------------------------------------- cross-core flags
+// On the NPU the cube core and the two vector cores of an AI core signal each other through FFTS flags
+// (include/pto/npu/a2a3/TPush.hpp:141-162 in the reference: ffts_cross_core_sync raises flag `id` once everything
+// issued so far on `pipe` is complete, wait_flag_dev(id) consumes one raise).  Here one thread block plays both roles
+// in program order, so a flag is a counter in the control block: the raise happens after the block's outstanding
+// copies and stores are complete, the wait is bounded like every other wait.
+PTO_INTERNAL void ffts_cross_core_sync(pipe_t pipe, uint64_t config)
+{
+#if PTO_B200_DEVICE_CODE
+    (void)pipe;
+    const int id = static_cast<int>((config >> 8) & 0xf);
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads(); // global and shared-memory writes of every thread are visible to the block from here on
+    if (threadIdx.x == 0) {
+        atomicAdd(&pto::b200::control()->dev_flags[id], 1);
+    }
+    __syncthreads();
+#else
+    (void)pipe;
+    (void)config;
+#endif
+}
+
+PTO_INTERNAL void wait_flag_dev(int id)
+{
+#if PTO_B200_DEVICE_CODE
+    pto::b200::Control *ctl = pto::b200::control();
+    volatile int *flag = &ctl->dev_flags[id & 0xf];
+    volatile int *abort_flag = &ctl->abort_flag;
+    __syncthreads();
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0; *flag <= 0; ++i) {
+        if ((i & 0x3f) == 0x3f) {
+            if (*abort_flag) {
+                break;
+            }
+            const unsigned long long now = pto::b200::global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > ctl->wait_limit_ns) {
+                pto::b200::give_up(pto::b200::kNumFlags + (id & 0xf));
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && *flag > 0) {
+        atomicSub(&ctl->dev_flags[id & 0xf], 1);
+    }
+    __syncthreads();
+#else
+    (void)id;
+#endif
+}
+PTO_INTERNAL void set_ffts_base_addr(uint64_t) {}
+// one block hosts the cube role and a single vector role
+PTO_INTERNAL uint32_t get_subblockid() { return 0; }
+PTO_INTERNAL uint32_t get_subblockdim() { return 1; }
+
+namespace pto {
+namespace b200 {
+
+// ---------------------------------------------------------------- function-local statics of tile programs
+// A `static` local in a device function is ONE variable for the whole grid in CUDA, where the reference's kernels
+// expect one per core (its instruction stream is scalar there).  PTO_B200_CORE_STATIC(T, name, init, slot) declares
+// the per-core replacement: the value lives in the block's control area, one copy per warp (every lane of a warp runs
+// the same scalar stream); reads and writes go through this proxy, which keeps the lanes of a warp in step.
+template <typename T, int Slot>
+struct CoreStatic {
+    static_assert(Slot >= 0 && Slot < kNumCoreStatics, "PTO_B200_CORE_STATIC: slot out of range");
+    static_assert(sizeof(T) <= 8 && std::is_integral_v<T>, "PTO_B200_CORE_STATIC: integral types of up to 8 bytes");
+#if PTO_B200_DEVICE_CODE
+    __device__ __forceinline__ explicit CoreStatic(T init)
+    {
+        Control *c = control();
+        const int warp = threadIdx.x >> 5;
+        __syncwarp();
+        const bool have = (c->core_static_init[warp] >> Slot) & 1u;
+        __syncwarp();
+        if (!have && (threadIdx.x & 31) == 0) {
+            c->core_static[Slot][warp] = static_cast<unsigned long long>(init);
+            c->core_static_init[warp] |= 1u << Slot;
+        }
+        __syncwarp();
+    }
+    __device__ __forceinline__ T get() const
+    {
+        __syncwarp();
+        const T v = static_cast<T>(control()->core_static[Slot][threadIdx.x >> 5]);
+        __syncwarp();
+        return v;
+    }
+    __device__ __forceinline__ void set(T v)
+    {
+        __syncwarp();
+        if ((threadIdx.x & 31) == 0) {
+            control()->core_static[Slot][threadIdx.x >> 5] = static_cast<unsigned long long>(v);
+        }
+        __syncwarp();
+    }
+#else
+    explicit CoreStatic(T init) : host_(init) {}
+    T get() const { return host_; }
+    void set(T v) { host_ = v; }
+    T host_;
+#endif
+    PTO_INTERNAL operator T() const { return get(); }
+    PTO_INTERNAL CoreStatic &operator=(T v)
+    {
+        set(v);
+        return *this;
+    }
+    PTO_INTERNAL CoreStatic &operator^=(T v) { return *this = static_cast<T>(get() ^ v); }
+    PTO_INTERNAL CoreStatic &operator+=(T v) { return *this = static_cast<T>(get() + v); }
+    PTO_INTERNAL CoreStatic &operator-=(T v) { return *this = static_cast<T>(get() - v); }
+};
+
+// next automatic event id of a (source pipe, destination pipe) pair, ids 0..7 in turn
+// (include/pto/common/event.hpp:112-135 in the reference keeps this counter in a function-local static)
+PTO_INTERNAL event_t next_event_id(pipe_t src, pipe_t dst)
+{
+#if PTO_B200_DEVICE_CODE
+    Control *c = control();
+    const int pair = (src & 7) * kNumPipes + (dst & 7);
+    uint32_t *word = &c->event_next[threadIdx.x >> 5][pair >> 3];
+    const int shift = (pair & 7) * 4;
+    __syncwarp();
+    const uint32_t w = *word;
+    __syncwarp();
+    const uint32_t id = (w >> shift) & 0xfu;
+    if ((threadIdx.x & 31) == 0) {
+        *word = (w & ~(0xfu << shift)) | (((id + 1) % EVENT_ID_MAX) << shift);
+    }
+    __syncwarp();
+    return static_cast<event_t>(id);
+#else
+    (void)src;
+    (void)dst;
+    return EVENT_ID0;
+#endif
+}
+
+} // namespace b200
+} // namespace pto
+
+#define PTO_B200_CORE_STATIC(T, name, init, slot) pto::b200::CoreStatic<T, slot> name(static_cast<T>(init))

@@ -24,6 +24,8 @@ struct DynCount {
 template <int64_t N1 = DYNAMIC, int64_t N2 = DYNAMIC, int64_t N3 = DYNAMIC, int64_t N4 = DYNAMIC, int64_t N5 = DYNAMIC>
 struct Shape {
     static constexpr int64_t staticShape[5] = {N1, N2, N3, N4, N5};
+    // (device code cannot index a static constexpr array at run time)
+    PTO_INTERNAL static constexpr int64_t static_at(int i) { return i == 0 ? N1 : i == 1 ? N2 : i == 2 ? N3 : i == 3 ? N4 : N5; }
     int64_t shape[5] = {N1 == DYNAMIC ? 1 : N1, N2 == DYNAMIC ? 1 : N2, N3 == DYNAMIC ? 1 : N3, N4 == DYNAMIC ? 1 : N4,
                         N5 == DYNAMIC ? 1 : N5};
 
@@ -32,7 +34,7 @@ struct Shape {
     {
         const int64_t v[5] = {a, b, c, d, e};
         for (int i = 0; i < 5; ++i) {
-            if (staticShape[i] == DYNAMIC) {
+            if (static_at(i) == DYNAMIC) {
                 shape[i] = v[i];
             }
         }
@@ -46,7 +48,7 @@ struct Shape {
         const int64_t v[sizeof...(Ts)] = {static_cast<int64_t>(vals)...};
         int k = 0;
         for (int i = 0; i < 5; ++i) {
-            if (staticShape[i] == DYNAMIC) {
+            if (static_at(i) == DYNAMIC) {
                 shape[i] = v[k++];
             }
         }
@@ -56,6 +58,7 @@ struct Shape {
 template <int64_t N1 = DYNAMIC, int64_t N2 = DYNAMIC, int64_t N3 = DYNAMIC, int64_t N4 = DYNAMIC, int64_t N5 = DYNAMIC>
 struct Stride {
     static constexpr int64_t staticStride[5] = {N1, N2, N3, N4, N5};
+    PTO_INTERNAL static constexpr int64_t static_at(int i) { return i == 0 ? N1 : i == 1 ? N2 : i == 2 ? N3 : i == 3 ? N4 : N5; }
     int64_t stride[5] = {N1 == DYNAMIC ? 1 : N1, N2 == DYNAMIC ? 1 : N2, N3 == DYNAMIC ? 1 : N3,
                          N4 == DYNAMIC ? 1 : N4, N5 == DYNAMIC ? 1 : N5};
 
@@ -64,7 +67,7 @@ struct Stride {
     {
         const int64_t v[5] = {a, b, c, d, e};
         for (int i = 0; i < 5; ++i) {
-            if (staticStride[i] == DYNAMIC) {
+            if (static_at(i) == DYNAMIC) {
                 stride[i] = v[i];
             }
         }
@@ -77,7 +80,7 @@ struct Stride {
         const int64_t v[sizeof...(Ts)] = {static_cast<int64_t>(vals)...};
         int k = 0;
         for (int i = 0; i < 5; ++i) {
-            if (staticStride[i] == DYNAMIC) {
+            if (static_at(i) == DYNAMIC) {
                 stride[i] = v[k++];
             }
         }
@@ -170,7 +173,8 @@ private:
 // ---------------------------------------------------------------- Tile
 namespace b200 {
 // how a staged Mat tile lies in shared memory (decided by TLOAD from the global tensor's contiguous dimension)
-enum : uint8_t { kColsContiguous = 0, kRowsContiguous = 1 };
+// kPlain: 8- and 32-bit matrix tiles, stored row-major Rows x Cols without swizzle (not read by the tensor core)
+enum : uint8_t { kColsContiguous = 0, kRowsContiguous = 1, kPlain = 2 };
 } // namespace b200
 
 template <TileType Loc_, typename Element_, const int Rows_, const int Cols_,

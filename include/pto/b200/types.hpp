@@ -97,6 +97,7 @@ enum class SaturationMode : uint8_t { ON = 0, OFF = 1 };
 enum class AtomicType : uint8_t { AtomicNone = 0, AtomicAdd = 1 };
 enum class AccPhase : uint8_t { Unspecified = 0x0, Unknown = Unspecified, Partial = 0x2, Final = 0x3 };
 enum class STPhase : uint8_t { Unspecified = 0x0, Partial = 0x2, Final = 0x3 };
+enum class ReluPreMode : uint8_t { NoRelu = 0, NormalRelu = 1 };
 
 namespace GlobalTensorDim {
 constexpr int DIM_0 = 0;
@@ -118,7 +119,7 @@ struct TileConfig {
     static constexpr int fractalMxSize = 32;
 };
 
-// Instructions return a RecordEvent; on this backend ordering is carried by set_flag / wait_flag.
+// What an instruction returns; assigning it to an Event raises that event's flag (event.hpp).
 struct RecordEvent {};
 
 // geometry constants of the ISA that tile programs refer to

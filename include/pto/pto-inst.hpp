@@ -16,7 +16,9 @@
 #include "b200/types.hpp"
 #include "b200/tile.hpp"
 #include "b200/runtime.hpp"
+#include "b200/event.hpp"
 #include "b200/instr.hpp"
+#include "b200/pipe.hpp"
 
 #define PTO_B200_CUDA_GLOBAL __attribute__((global))
 

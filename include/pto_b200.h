@@ -68,9 +68,10 @@ extern "C" {
 
 /* ---- library state ------------------------------------------------------------------------------ */
 
-/* ABI version of this header (2: second batch of vector ops; 3: MX block-scaled GEMM, TMATMUL_BIAS form, TTRI);
+/* ABI version of this header (2: second batch of vector ops; 3: MX block-scaled GEMM, TMATMUL_BIAS form, TTRI;
+ * 4: status record exports, per-block profile stamps, the random-read probe);
  * pto_b200_version() returns the version the library was built from. */
-#define PTO_B200_ABI_VERSION 3
+#define PTO_B200_ABI_VERSION 4
 int pto_b200_version(void);
 /* Text of the last error raised on the calling thread ("" if none). */
 const char *pto_b200_last_error(void);
@@ -79,6 +80,14 @@ int pto_b200_last_status(void);
 /* Reads (and clears) the device-side status record that kernels with bounded waits report into.
  * Synchronises `stream`.  Returns 0, or PTO_B200_ERR_DEVICE_WAIT_TIMEOUT if a kernel gave up on a wait. */
 int pto_b200_device_status(void *stream);
+/* The same, and copies the record out: record[0] the code, [1] the block that reported, [2] which wait gave up (for a
+ * tile program: the flag's index ((source pipe * 8 + destination pipe) * 8 + event id), 512 + id for a cross-core
+ * flag), [3] detail (for a tile program: source pipe * 16 + destination pipe).  The reference's waits are unbounded
+ * (include/pto/npu/a2a3/TPush.hpp:141-146, wait_flag / wait_flag_dev); every wait here carries a limit. */
+int pto_b200_device_status_ex(void *stream, int record[4]);
+/* Device address of the current device's status record (four ints), so that tile programs launched through
+ * pto::b200::launch (include/pto/b200/runtime.hpp) can report into the record pto_b200_device_status reads. */
+void *pto_b200_status_record(void);
 
 /* ---- vector tile ops ---------------------------------------------------------------------------- */
 
@@ -221,12 +230,30 @@ int pto_b200_gemm_f16f32_host_batched(const uint16_t *a, const uint16_t *b, floa
  * cudaMalloc / cudaFree or other allocating routine: the device copies of A, B and C and the kernel's status record
  * live in a 36 MiB array built into the library, held by every GPU that loads it until the process exits.
  * Problems whose operands need more than that (about m = n = k = 2048) return PTO_B200_ERR_TOO_LARGE.
- * The first call on a device also looks up the array's device address; make that first call before any stream
- * capture starts.  Calls run on the legacy default stream and return after C has been copied out; all calls share
- * the array (it keeps the previous call's contents, the status record is cleared per call), so calls that overlap
- * on the GPU would race - do not issue them concurrently. */
+ * The first call on a device also looks up the array's device address, and it is then that CUDA, which loads a
+ * library's device code and data on first use, takes the 36 MiB from that device: make one warm-up call per device
+ * at start-up, while the memory is still there to take and before any stream capture starts.  Calls run on the
+ * legacy default stream and return after C has been copied out; all calls share the array (it keeps the previous
+ * call's contents, the status record is cleared per call), so calls that overlap on the GPU would race - do not
+ * issue them concurrently. */
 int pto_b200_gemm_f16f32_host_static(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k,
                                      int b_layout);
+
+/* ---- measurement helpers ------------------------------------------------------------------------ */
+
+/* Per-block profile stamps, the counterpart of the reference kernel's get_sys_cnt() stamps per block
+ * (kernels/manual/common/flash_atten/fa_performance_kernel.cpp:615,728-738,950-953, reduced on the host to duration and
+ * TFLOPS in flash_atten/main.cpp:616-660).  With a buffer of 4 * capacity_blocks 64-bit words set for the current
+ * device, every block b < capacity_blocks of the GEMM pair kernel and of the attention kernel writes
+ * stamps[4 b + 0 / 1] = the global nanosecond timer at its start / end and stamps[4 b + 2 / 3] = its SM's cycle counter
+ * at its start / end (cycles / nanoseconds = the clock the block really ran at).  A null pointer switches the stamps
+ * off (the default).  Synchronises `stream`; kernels launched afterwards see the setting. */
+int pto_b200_set_profile_buffer(uint64_t *stamps, int64_t capacity_blocks, void *stream);
+
+/* `reads` random 4-byte reads spread over the first `table_bytes` (a power of two) of `table`, indices from a hash, no
+ * index or output stream: the rate at which this GPU serves random 32-byte sectors of a table of that size, which is
+ * what bounds TGATHER (include/pto/cpu/TGather.hpp:68-100) beside its two streams.  `sink` receives one word. */
+int pto_b200_probe_random_reads(const uint32_t *table, int64_t table_bytes, int64_t reads, uint32_t *sink, void *stream);
 
 /* ---- flash attention forward -------------------------------------------------------------------- */
 

@@ -22,6 +22,10 @@ SIGNATURES = {
     "pto_b200_last_error": (ctypes.c_char_p, []),
     "pto_b200_last_status": (_i, []),
     "pto_b200_device_status": (_i, [_vp]),
+    "pto_b200_device_status_ex": (_i, [_vp, _vp]),
+    "pto_b200_status_record": (_vp, []),
+    "pto_b200_set_profile_buffer": (_i, [_vp, _i64, _vp]),
+    "pto_b200_probe_random_reads": (_i, [_vp, _i64, _i64, _vp, _vp]),
     "pto_b200_tcvt_f32_f16": (_i, [_vp, _vp, _i64, _vp]),
     "pto_b200_tcvt_f32_bf16": (_i, [_vp, _vp, _i64, _vp]),
     "pto_b200_tcvt_f32_i32": (_i, [_vp, _vp, _i64, _i, _vp]),

@@ -56,6 +56,7 @@ def build(force=False, verbose=False):
     if force or _stale(prog_out, [prog_src] + pto_headers):
         subprocess.check_call([_nvcc()] + flags + ["--extended-lambda", "-I", os.path.join(HERE, "..", "include"),
                                                   "-shared", "-o", prog_out, prog_src])
+    build_host(force)
     for so, src in SHIMS.items():
         src_path = os.path.join(CSRC, src)
         out = os.path.join(HERE, so)
@@ -63,6 +64,32 @@ def build(force=False, verbose=False):
             subprocess.check_call(["g++", "-O2", "-fPIC", "-shared", "-o", out, src_path, "-L" + HERE, "-lpto_b200",
                                    "-Wl,-rpath,$ORIGIN"])
     return LIB
+
+
+def build_host(force=False):
+    """The C++ half of the boundary: the reference's host launcher templates over the C ABI
+    (libpto_b200_launchers.so, include/pto_b200_launchers.hpp) and a C++ host program in the shape of the
+    reference's kernel hosts (pto_b200_host).  Plain g++; the CUDA runtime supplies memory and streams."""
+    host_dir = os.path.join(CSRC, "host")
+    hdrs = [os.path.join(HERE, "..", "include", "pto_b200_launchers.hpp"), os.path.join(HERE, "..", "include", "pto_b200.h")]
+    lib_out = os.path.join(HERE, "libpto_b200_launchers.so")
+    refk = os.path.join(HERE, "libpto_b200_refkernels.so")
+    src = os.path.join(host_dir, "launchers.cpp")
+    deps = [src, LIB] + hdrs + ([refk] if os.path.exists(refk) else [])
+    if force or _stale(lib_out, deps):
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-o", lib_out, src, "-L" + HERE, "-lpto_b200",
+               "-Wl,-rpath,$ORIGIN"]
+        if os.path.exists(refk):  # LaunchTMATMUL<key> runs the reference's tile programs compiled for B200
+            cmd += ["-Wl,--no-as-needed", "-lpto_b200_refkernels", "-Wl,--as-needed"]  # (weak references only)
+        subprocess.check_call(cmd)
+    cuda_home = os.path.dirname(os.path.dirname(_nvcc()))
+    exe = os.path.join(HERE, "pto_b200_host")
+    main_src = os.path.join(host_dir, "host_main.cpp")
+    if force or _stale(exe, [main_src, lib_out] + hdrs):
+        subprocess.check_call(["g++", "-O2", "-std=c++17", "-o", exe, main_src, "-I" + os.path.join(cuda_home, "include"),
+                               "-L" + HERE, "-lpto_b200_launchers", "-lpto_b200", "-L" + os.path.join(cuda_home, "lib64"),
+                               "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(cuda_home, "lib64")])
+    return exe
 
 
 if __name__ == "__main__":

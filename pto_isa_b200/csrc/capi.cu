@@ -5,6 +5,8 @@
 #include "internal.h"
 #include "ptx.cuh"
 
+#include <mutex>
+
 using namespace pto_b200;
 
 namespace {
@@ -20,7 +22,8 @@ int bad(const char *what)
     return kErrBadArgument;
 }
 
-// Device scratch for the *_host entry points: grown on demand, kept for reuse, one set per process.
+// Device scratch for the *_host entry points: grown on demand, kept for reuse, one set per device.  A *_host call
+// holds g_host_mutex from its first use of the set to its last synchronisation, so concurrent callers take turns.
 struct HostArena {
     void *ptr[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     size_t cap[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -29,50 +32,63 @@ struct HostArena {
     cudaStream_t pipe[3] = {nullptr, nullptr, nullptr};
     cudaEvent_t h2d_done[2] = {nullptr, nullptr}, comp_done[2] = {nullptr, nullptr}, d2h_done[2] = {nullptr, nullptr};
 };
-HostArena g_arena;
+constexpr int kMaxHostDevices = 64;
+HostArena g_arenas[kMaxHostDevices];
+std::mutex g_host_mutex;
 
-int arena_get(int slot, size_t bytes, void **out)
+// the current device's set (nullptr, with the error text set, when there is no usable device)
+HostArena *arena_of_current_device()
 {
-    if (g_arena.cap[slot] < bytes) {
-        if (g_arena.ptr[slot] != nullptr) {
-            cudaFree(g_arena.ptr[slot]);
-            g_arena.ptr[slot] = nullptr;
-            g_arena.cap[slot] = 0;
+    const int dev = current_device_ordinal();
+    if (dev < 0 || dev >= kMaxHostDevices) {
+        set_error_text("no current CUDA device");
+        return nullptr;
+    }
+    return &g_arenas[dev];
+}
+
+int arena_get(HostArena &ar, int slot, size_t bytes, void **out)
+{
+    if (ar.cap[slot] < bytes) {
+        if (ar.ptr[slot] != nullptr) {
+            cudaFree(ar.ptr[slot]);
+            ar.ptr[slot] = nullptr;
+            ar.cap[slot] = 0;
         }
-        int rc = check_cuda(cudaMalloc(&g_arena.ptr[slot], bytes), "cudaMalloc(host-variant staging)");
+        int rc = check_cuda(cudaMalloc(&ar.ptr[slot], bytes), "cudaMalloc(host-variant staging)");
         if (rc != kOk) {
             return rc;
         }
-        g_arena.cap[slot] = bytes;
+        ar.cap[slot] = bytes;
     }
-    *out = g_arena.ptr[slot];
+    *out = ar.ptr[slot];
     return kOk;
 }
 
-int arena_stream(cudaStream_t *s)
+int arena_stream(HostArena &ar, cudaStream_t *s)
 {
-    if (g_arena.stream == nullptr) {
-        int rc = check_cuda(cudaStreamCreateWithFlags(&g_arena.stream, cudaStreamNonBlocking), "cudaStreamCreate");
+    if (ar.stream == nullptr) {
+        int rc = check_cuda(cudaStreamCreateWithFlags(&ar.stream, cudaStreamNonBlocking), "cudaStreamCreate");
         if (rc != kOk) {
             return rc;
         }
     }
-    *s = g_arena.stream;
+    *s = ar.stream;
     return kOk;
 }
 
-int arena_pipeline()
+int arena_pipeline(HostArena &ar)
 {
     for (int i = 0; i < 3; ++i) {
-        if (g_arena.pipe[i] == nullptr) {
-            int rc = check_cuda(cudaStreamCreateWithFlags(&g_arena.pipe[i], cudaStreamNonBlocking), "cudaStreamCreate");
+        if (ar.pipe[i] == nullptr) {
+            int rc = check_cuda(cudaStreamCreateWithFlags(&ar.pipe[i], cudaStreamNonBlocking), "cudaStreamCreate");
             if (rc != kOk) {
                 return rc;
             }
         }
     }
     for (int i = 0; i < 2; ++i) {
-        cudaEvent_t *evs[3] = {&g_arena.h2d_done[i], &g_arena.comp_done[i], &g_arena.d2h_done[i]};
+        cudaEvent_t *evs[3] = {&ar.h2d_done[i], &ar.comp_done[i], &ar.d2h_done[i]};
         for (cudaEvent_t *e : evs) {
             if (*e == nullptr) {
                 int rc = check_cuda(cudaEventCreateWithFlags(e, cudaEventDisableTiming), "cudaEventCreate");
@@ -83,6 +99,20 @@ int arena_pipeline()
         }
     }
     return kOk;
+}
+
+// end of a *_host call: wait for the stream (also after an error, so that no copy stays in flight on the caller's
+// buffers), then read the device status record: a kernel that gave up on a wait must not look like success
+int finish_host_call(int rc, cudaStream_t s)
+{
+    const int sync_rc = check_cuda(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    if (rc != kOk) {
+        return rc;
+    }
+    if (sync_rc != kOk) {
+        return sync_rc;
+    }
+    return fetch_device_status(s);
 }
 
 } // namespace
@@ -108,6 +138,24 @@ int pto_b200_last_status(void)
 int pto_b200_device_status(void *stream)
 {
     return fetch_device_status(as_stream(stream));
+}
+
+int pto_b200_device_status_ex(void *stream, int record[4])
+{
+    return fetch_device_status(as_stream(stream), record);
+}
+
+void *pto_b200_status_record(void)
+{
+    return device_status_ptr();
+}
+
+int pto_b200_set_profile_buffer(uint64_t *stamps, int64_t capacity_blocks, void *stream)
+{
+    if (stamps != nullptr && capacity_blocks <= 0) {
+        return bad("set_profile_buffer: capacity_blocks must be positive");
+    }
+    return set_profile_buffer(reinterpret_cast<unsigned long long *>(stamps), capacity_blocks, as_stream(stream));
 }
 
 // ------------------------------------------------------------------ vector ops
@@ -433,26 +481,25 @@ int pto_b200_gemm_f16f32_host(const uint16_t *a, const uint16_t *b, float *c, in
     }
     const size_t a_bytes = static_cast<size_t>(m) * k * 2, b_bytes = static_cast<size_t>(n) * k * 2,
                  c_bytes = static_cast<size_t>(m) * n * 4;
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    HostArena *ar = arena_of_current_device();
+    if (ar == nullptr) {
+        return kErrCuda;
+    }
     void *da, *db, *dc;
     cudaStream_t s;
     int rc;
-    if ((rc = arena_stream(&s)) != kOk || (rc = arena_get(0, a_bytes, &da)) != kOk ||
-        (rc = arena_get(1, b_bytes, &db)) != kOk || (rc = arena_get(2, c_bytes, &dc)) != kOk) {
+    if ((rc = arena_stream(*ar, &s)) != kOk || (rc = arena_get(*ar, 0, a_bytes, &da)) != kOk ||
+        (rc = arena_get(*ar, 1, b_bytes, &db)) != kOk || (rc = arena_get(*ar, 2, c_bytes, &dc)) != kOk) {
         return rc;
     }
-    if ((rc = check_cuda(cudaMemcpyAsync(da, a, a_bytes, cudaMemcpyHostToDevice, s), "H2D A")) != kOk ||
-        (rc = check_cuda(cudaMemcpyAsync(db, b, b_bytes, cudaMemcpyHostToDevice, s), "H2D B")) != kOk) {
-        return rc;
+    if ((rc = check_cuda(cudaMemcpyAsync(da, a, a_bytes, cudaMemcpyHostToDevice, s), "H2D A")) == kOk &&
+        (rc = check_cuda(cudaMemcpyAsync(db, b, b_bytes, cudaMemcpyHostToDevice, s), "H2D B")) == kOk &&
+        (rc = launch_gemm_f16f32(static_cast<const uint16_t *>(da), static_cast<const uint16_t *>(db),
+                                 static_cast<float *>(dc), m, n, k, b_layout, s)) == kOk) {
+        rc = check_cuda(cudaMemcpyAsync(c, dc, c_bytes, cudaMemcpyDeviceToHost, s), "D2H C");
     }
-    rc = launch_gemm_f16f32(static_cast<const uint16_t *>(da), static_cast<const uint16_t *>(db),
-                            static_cast<float *>(dc), m, n, k, b_layout, s);
-    if (rc != kOk) {
-        return rc;
-    }
-    if ((rc = check_cuda(cudaMemcpyAsync(c, dc, c_bytes, cudaMemcpyDeviceToHost, s), "D2H C")) != kOk) {
-        return rc;
-    }
-    return check_cuda(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    return finish_host_call(rc, s);
 }
 
 int pto_b200_gemm_f16f32_host_batched(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
@@ -467,51 +514,72 @@ int pto_b200_gemm_f16f32_host_batched(const uint16_t *a, const uint16_t *b, floa
     }
     const size_t a_bytes = static_cast<size_t>(m) * k * 2, b_bytes = static_cast<size_t>(n) * k * 2,
                  c_bytes = static_cast<size_t>(m) * n * 4;
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    HostArena *arp = arena_of_current_device();
+    if (arp == nullptr) {
+        return kErrCuda;
+    }
+    HostArena &ar = *arp;
     void *da[2], *db[2], *dc[2];
-    int rc = arena_pipeline();
+    int rc = arena_pipeline(ar);
     for (int s = 0; s < 2 && rc == kOk; ++s) {
-        if ((rc = arena_get(2 + 3 * s, a_bytes, &da[s])) == kOk && (rc = arena_get(3 + 3 * s, b_bytes, &db[s])) == kOk) {
-            rc = arena_get(4 + 3 * s, c_bytes, &dc[s]);
+        if ((rc = arena_get(ar, 2 + 3 * s, a_bytes, &da[s])) == kOk &&
+            (rc = arena_get(ar, 3 + 3 * s, b_bytes, &db[s])) == kOk) {
+            rc = arena_get(ar, 4 + 3 * s, c_bytes, &dc[s]);
         }
     }
     if (rc != kOk) {
         return rc;
     }
-    cudaStream_t in = g_arena.pipe[0], run = g_arena.pipe[1], out = g_arena.pipe[2];
+    cudaStream_t in = ar.pipe[0], run = ar.pipe[1], out = ar.pipe[2];
     for (int i = 0; i < batch && rc == kOk; ++i) {
         const int s = i & 1;
         const uint16_t *ha = a + static_cast<int64_t>(i) * a_stride, *hb = b + static_cast<int64_t>(i) * b_stride;
         float *hc = c + static_cast<int64_t>(i) * c_stride;
         // copies in: the kernel of problem i - 2 has consumed this set's A and B
         if (i >= 2) {
-            rc = check_cuda(cudaStreamWaitEvent(in, g_arena.comp_done[s], 0), "cudaStreamWaitEvent");
+            rc = check_cuda(cudaStreamWaitEvent(in, ar.comp_done[s], 0), "cudaStreamWaitEvent");
         }
         if (rc == kOk) rc = check_cuda(cudaMemcpyAsync(da[s], ha, a_bytes, cudaMemcpyHostToDevice, in), "H2D A");
         if (rc == kOk) rc = check_cuda(cudaMemcpyAsync(db[s], hb, b_bytes, cudaMemcpyHostToDevice, in), "H2D B");
-        if (rc == kOk) rc = check_cuda(cudaEventRecord(g_arena.h2d_done[s], in), "cudaEventRecord");
+        if (rc == kOk) rc = check_cuda(cudaEventRecord(ar.h2d_done[s], in), "cudaEventRecord");
         // kernel: operands are in, and the copy out of problem i - 2 has read this set's C
-        if (rc == kOk) rc = check_cuda(cudaStreamWaitEvent(run, g_arena.h2d_done[s], 0), "cudaStreamWaitEvent");
-        if (rc == kOk && i >= 2) rc = check_cuda(cudaStreamWaitEvent(run, g_arena.d2h_done[s], 0), "cudaStreamWaitEvent");
+        if (rc == kOk) rc = check_cuda(cudaStreamWaitEvent(run, ar.h2d_done[s], 0), "cudaStreamWaitEvent");
+        if (rc == kOk && i >= 2) rc = check_cuda(cudaStreamWaitEvent(run, ar.d2h_done[s], 0), "cudaStreamWaitEvent");
         if (rc == kOk) {
             rc = launch_gemm_f16f32(static_cast<const uint16_t *>(da[s]), static_cast<const uint16_t *>(db[s]),
                                     static_cast<float *>(dc[s]), m, n, k, b_layout, run);
         }
-        if (rc == kOk) rc = check_cuda(cudaEventRecord(g_arena.comp_done[s], run), "cudaEventRecord");
+        if (rc == kOk) rc = check_cuda(cudaEventRecord(ar.comp_done[s], run), "cudaEventRecord");
         // copy out
-        if (rc == kOk) rc = check_cuda(cudaStreamWaitEvent(out, g_arena.comp_done[s], 0), "cudaStreamWaitEvent");
+        if (rc == kOk) rc = check_cuda(cudaStreamWaitEvent(out, ar.comp_done[s], 0), "cudaStreamWaitEvent");
         if (rc == kOk) rc = check_cuda(cudaMemcpyAsync(hc, dc[s], c_bytes, cudaMemcpyDeviceToHost, out), "D2H C");
-        if (rc == kOk) rc = check_cuda(cudaEventRecord(g_arena.d2h_done[s], out), "cudaEventRecord");
+        if (rc == kOk) rc = check_cuda(cudaEventRecord(ar.d2h_done[s], out), "cudaEventRecord");
     }
     // drain all three streams even after an error so that no copy is left in flight on the caller's buffers
     const int r0 = check_cuda(cudaStreamSynchronize(in), "cudaStreamSynchronize");
     const int r1 = check_cuda(cudaStreamSynchronize(run), "cudaStreamSynchronize");
     const int r2 = check_cuda(cudaStreamSynchronize(out), "cudaStreamSynchronize");
-    return rc != kOk ? rc : (r0 != kOk ? r0 : (r1 != kOk ? r1 : r2));
+    if (rc != kOk || r0 != kOk || r1 != kOk || r2 != kOk) {
+        return rc != kOk ? rc : (r0 != kOk ? r0 : (r1 != kOk ? r1 : r2));
+    }
+    return fetch_device_status(run); // a kernel that gave up on a wait must not look like success
 }
 
 int pto_b200_gemm_f16f32_host_static(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout)
 {
     return gemm_f16f32_host_static(a, b, c, m, n, k, b_layout);
+}
+
+// ------------------------------------------------------------------ measurement helpers
+
+int pto_b200_probe_random_reads(const uint32_t *table, int64_t table_bytes, int64_t reads, uint32_t *sink, void *stream)
+{
+    if (table == nullptr || sink == nullptr || reads <= 0 || table_bytes < 1024 || (table_bytes & (table_bytes - 1)) != 0 ||
+        table_bytes > (static_cast<int64_t>(1) << 34)) {
+        return bad("probe_random_reads: the table size must be a power of two between 1 KiB and 16 GiB, reads > 0");
+    }
+    return launch_random_read_probe(table, table_bytes, reads, sink, as_stream(stream));
 }
 
 // ------------------------------------------------------------------ flash attention
@@ -535,29 +603,28 @@ int pto_b200_flash_attn_fwd_f16_host(const uint16_t *q, const uint16_t *k, const
     const size_t q_bytes = static_cast<size_t>(batch_heads) * sq * d * 2;
     const size_t kv_bytes = static_cast<size_t>(batch_heads) * sk * d * 2;
     const size_t o_bytes = static_cast<size_t>(batch_heads) * sq * d * (out_f16 ? 2 : 4);
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    HostArena *ar = arena_of_current_device();
+    if (ar == nullptr) {
+        return kErrCuda;
+    }
     void *dq, *dk, *dv, *dout;
     cudaStream_t s;
     int rc;
-    if ((rc = arena_stream(&s)) != kOk || (rc = arena_get(0, q_bytes, &dq)) != kOk ||
-        (rc = arena_get(1, kv_bytes, &dk)) != kOk || (rc = arena_get(2, kv_bytes, &dv)) != kOk ||
-        (rc = arena_get(3, o_bytes, &dout)) != kOk) {
+    if ((rc = arena_stream(*ar, &s)) != kOk || (rc = arena_get(*ar, 0, q_bytes, &dq)) != kOk ||
+        (rc = arena_get(*ar, 1, kv_bytes, &dk)) != kOk || (rc = arena_get(*ar, 2, kv_bytes, &dv)) != kOk ||
+        (rc = arena_get(*ar, 3, o_bytes, &dout)) != kOk) {
         return rc;
     }
-    if ((rc = check_cuda(cudaMemcpyAsync(dq, q, q_bytes, cudaMemcpyHostToDevice, s), "H2D Q")) != kOk ||
-        (rc = check_cuda(cudaMemcpyAsync(dk, k, kv_bytes, cudaMemcpyHostToDevice, s), "H2D K")) != kOk ||
-        (rc = check_cuda(cudaMemcpyAsync(dv, v, kv_bytes, cudaMemcpyHostToDevice, s), "H2D V")) != kOk) {
-        return rc;
+    if ((rc = check_cuda(cudaMemcpyAsync(dq, q, q_bytes, cudaMemcpyHostToDevice, s), "H2D Q")) == kOk &&
+        (rc = check_cuda(cudaMemcpyAsync(dk, k, kv_bytes, cudaMemcpyHostToDevice, s), "H2D K")) == kOk &&
+        (rc = check_cuda(cudaMemcpyAsync(dv, v, kv_bytes, cudaMemcpyHostToDevice, s), "H2D V")) == kOk &&
+        (rc = launch_flash_attn_fwd(static_cast<const uint16_t *>(dq), static_cast<const uint16_t *>(dk),
+                                    static_cast<const uint16_t *>(dv), dout, batch_heads, sq, sk, d, causal, scale,
+                                    out_f16, s)) == kOk) {
+        rc = check_cuda(cudaMemcpyAsync(o, dout, o_bytes, cudaMemcpyDeviceToHost, s), "D2H O");
     }
-    rc = launch_flash_attn_fwd(static_cast<const uint16_t *>(dq), static_cast<const uint16_t *>(dk),
-                               static_cast<const uint16_t *>(dv), dout, batch_heads, sq, sk, d, causal, scale,
-                               out_f16, s);
-    if (rc != kOk) {
-        return rc;
-    }
-    if ((rc = check_cuda(cudaMemcpyAsync(o, dout, o_bytes, cudaMemcpyDeviceToHost, s), "D2H O")) != kOk) {
-        return rc;
-    }
-    return check_cuda(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    return finish_host_call(rc, s);
 }
 
 // ------------------------------------------------------------------ reference-shaped shims

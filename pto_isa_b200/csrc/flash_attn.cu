@@ -148,6 +148,9 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                       const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o, int sq, int sk,
                       float scale_log2, DeviceStatus *status)
 {
+    if (threadIdx.x == kThreads - 1) {
+        profile_stamp(status, 0);
+    }
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *smem_q = smem;                                // 2 tiles
@@ -554,6 +557,9 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     // ---------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == kThreads - 1) {
+        profile_stamp(status, 1);
+    }
     if (ctl->abort_flag) {
         for (int i = 0; i < 1024; ++i) {
             __nanosleep(1000);
@@ -574,15 +580,10 @@ template <bool kCausal, bool kOutF16, int kPolyOf8>
 int launch_variant(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const CUtensorMap &to, int bh, int sq, int sk,
                    float scale_log2, DeviceStatus *status, cudaStream_t stream)
 {
-    static bool attr_set = false;
-    if (!attr_set) {
-        const int rc = check_cuda(cudaFuncSetAttribute(flash_attn_fwd_kernel<kCausal, kOutF16, kPolyOf8>,
-                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
-                                  "cudaFuncSetAttribute(flash_attn)");
-        if (rc != kOk) {
-            return rc;
-        }
-        attr_set = true;
+    const int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(&flash_attn_fwd_kernel<kCausal, kOutF16, kPolyOf8>),
+                                       kSmemBytes);
+    if (rc != kOk) {
+        return rc;
     }
     const int q_blocks = (sq + 2 * kTileQ - 1) / (2 * kTileQ);
     flash_attn_fwd_kernel<kCausal, kOutF16, kPolyOf8>

@@ -20,6 +20,8 @@
 #include "ptx.cuh"
 #include "internal.h"
 
+#include <mutex>
+
 #include <cstdlib>
 #include <cstring>
 
@@ -289,27 +291,14 @@ int launch_gemm_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, in
     if (status == nullptr) {
         return kErrCuda;
     }
-    static bool attr_set[2] = {false, false};
     if (b_layout == 1) {
-        if (!attr_set[1]) {
-            rc = check_cuda(cudaFuncSetAttribute(gemm_f16f32_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 kSmemBytes),
-                            "cudaFuncSetAttribute(gemm)");
-            if (rc != kOk) {
-                return rc;
-            }
-            attr_set[1] = true;
+        if ((rc = ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm_f16f32_kernel<1>), kSmemBytes)) != kOk) {
+            return rc;
         }
         gemm_f16f32_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c, m, n, k, status);
     } else {
-        if (!attr_set[0]) {
-            rc = check_cuda(cudaFuncSetAttribute(gemm_f16f32_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 kSmemBytes),
-                            "cudaFuncSetAttribute(gemm)");
-            if (rc != kOk) {
-                return rc;
-            }
-            attr_set[0] = true;
+        if ((rc = ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm_f16f32_kernel<0>), kSmemBytes)) != kOk) {
+            return rc;
         }
         gemm_f16f32_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, c, m, n, k, status);
     }
@@ -344,6 +333,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 // looked up once per device (with that device current) and cached here.
 constexpr int kMaxDevicesStatic = 64;
 unsigned char *g_static_scratch_addr[kMaxDevicesStatic] = {nullptr};
+std::mutex g_static_mutex; // guards the table above
 
 size_t round256(size_t x)
 {
@@ -367,9 +357,12 @@ int gemm_f16f32_host_static(const uint16_t *a, const uint16_t *b, float *c, int 
         set_error_text("gemm_host_static: k (and n for a k x n B) must be multiples of 8");
         return kErrUnsupportedShape;
     }
+    // extents far beyond the scratch are turned away before any byte count is formed (no product can wrap)
+    const bool huge = m > (1 << 20) || n > (1 << 20) || k > (1 << 20);
     const size_t a_bytes = static_cast<size_t>(m) * k * 2, b_bytes = static_cast<size_t>(n) * k * 2,
                  c_bytes = static_cast<size_t>(m) * n * 4;
-    const size_t need = kStaticHeaderBytes + round256(a_bytes) + round256(b_bytes) + round256(c_bytes);
+    const size_t need = huge ? ~static_cast<size_t>(0)
+                             : kStaticHeaderBytes + round256(a_bytes) + round256(b_bytes) + round256(c_bytes);
     if (need > kStaticScratchBytes) {
         set_error_text("gemm_host_static: A, B and C need %zu bytes of device staging but the built-in scratch holds "
                        "%zu (about m = n = k = 2048); use pto_b200_gemm_f16f32_host for larger problems",
@@ -385,41 +378,36 @@ int gemm_f16f32_host_static(const uint16_t *a, const uint16_t *b, float *c, int 
         set_error_text("gemm_host_static: device ordinal %d out of range", dev);
         return kErrBadArgument;
     }
-    if (g_static_scratch_addr[dev] == nullptr) {
-        // one-time set-up for this device: resolve the array's device address and raise the kernels'
-        // dynamic shared-memory limit (neither allocates)
-        unsigned char *p = nullptr;
-        rc = check_cuda(cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_static_scratch),
-                        "cudaGetSymbolAddress(static scratch)");
-        if (rc != kOk) {
-            return rc;
+    unsigned char *base = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (g_static_scratch_addr[dev] == nullptr) {
+            // one-time set-up for this device: resolve the array's device address and raise the kernels' dynamic
+            // shared-memory limit.  Neither allocates, but CUDA loads a module's code and data when it is first
+            // touched: this is the moment the array's 36 MiB are taken from the device, which is why the first call
+            // belongs to start-up, before another allocator is handed the rest of the memory.
+            unsigned char *p = nullptr;
+            rc = check_cuda(cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_static_scratch),
+                            "cudaGetSymbolAddress(static scratch; the first call on a device must run while the "
+                            "device still has 36 MiB free)");
+            if (rc != kOk) {
+                return rc;
+            }
+            if ((rc = ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm_f16f32_kernel<0>), kSmemBytes)) != kOk ||
+                (rc = ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm_f16f32_kernel<1>), kSmemBytes)) != kOk) {
+                return rc;
+            }
+            g_static_scratch_addr[dev] = p;
         }
-        rc = check_cuda(cudaFuncSetAttribute(gemm_f16f32_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kSmemBytes),
-                        "cudaFuncSetAttribute(gemm)");
-        if (rc == kOk) {
-            rc = check_cuda(cudaFuncSetAttribute(gemm_f16f32_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 kSmemBytes),
-                            "cudaFuncSetAttribute(gemm)");
-        }
-        if (rc != kOk) {
-            return rc;
-        }
-        g_static_scratch_addr[dev] = p;
+        base = g_static_scratch_addr[dev];
     }
-    unsigned char *base = g_static_scratch_addr[dev];
     DeviceStatus *status = reinterpret_cast<DeviceStatus *>(base);
     uint16_t *da = reinterpret_cast<uint16_t *>(base + kStaticHeaderBytes);
     uint16_t *db = reinterpret_cast<uint16_t *>(base + kStaticHeaderBytes + round256(a_bytes));
     float *dc = reinterpret_cast<float *>(base + kStaticHeaderBytes + round256(a_bytes) + round256(b_bytes));
     cudaStream_t s = nullptr; // legacy default stream: serialises the calls that share the array
 
-    // the status record must start at zero; everything else is overwritten before it is read
-    if ((rc = check_cuda(cudaMemsetAsync(status, 0, sizeof(DeviceStatus), s), "cudaMemsetAsync(status)")) != kOk ||
-        (rc = check_cuda(cudaMemcpyAsync(da, a, a_bytes, cudaMemcpyHostToDevice, s), "H2D A")) != kOk ||
-        (rc = check_cuda(cudaMemcpyAsync(db, b, b_bytes, cudaMemcpyHostToDevice, s), "H2D B")) != kOk) {
-        return rc;
-    }
+    // the tensor maps first: a failure here leaves nothing in flight
     CUtensorMap tmap_a, tmap_b;
     rc = make_tmap_2d(&tmap_a, da, 2, m, k, k, BM, BK, true);
     if (rc == kOk) {
@@ -429,6 +417,17 @@ int gemm_f16f32_host_static(const uint16_t *a, const uint16_t *b, float *c, int 
     if (rc != kOk) {
         return rc;
     }
+    // from the first enqueue on, every error path waits for the stream: no copy may stay in flight on the caller's buffers
+    auto fail = [&](int code) {
+        cudaStreamSynchronize(s);
+        return code;
+    };
+    // the status record must start at zero; everything else is overwritten before it is read
+    if ((rc = check_cuda(cudaMemsetAsync(status, 0, sizeof(DeviceStatus), s), "cudaMemsetAsync(status)")) != kOk ||
+        (rc = check_cuda(cudaMemcpyAsync(da, a, a_bytes, cudaMemcpyHostToDevice, s), "H2D A")) != kOk ||
+        (rc = check_cuda(cudaMemcpyAsync(db, b, b_bytes, cudaMemcpyHostToDevice, s), "H2D B")) != kOk) {
+        return fail(rc);
+    }
     const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
     if (b_layout == 1) {
@@ -437,13 +436,15 @@ int gemm_f16f32_host_static(const uint16_t *a, const uint16_t *b, float *c, int 
         gemm_f16f32_kernel<0><<<grid, kThreads, kSmemBytes, s>>>(tmap_a, tmap_b, dc, m, n, k, status);
     }
     if ((rc = check_launch()) != kOk) {
-        return rc;
+        return fail(rc);
     }
     DeviceStatus host_status;
     if ((rc = check_cuda(cudaMemcpyAsync(c, dc, c_bytes, cudaMemcpyDeviceToHost, s), "D2H C")) != kOk ||
         (rc = check_cuda(cudaMemcpyAsync(&host_status, status, sizeof(DeviceStatus), cudaMemcpyDeviceToHost, s),
-                         "D2H status")) != kOk ||
-        (rc = check_cuda(cudaStreamSynchronize(s), "cudaStreamSynchronize")) != kOk) {
+                         "D2H status")) != kOk) {
+        return fail(rc);
+    }
+    if ((rc = check_cuda(cudaStreamSynchronize(s), "cudaStreamSynchronize")) != kOk) {
         return rc;
     }
     if (host_status.code != 0) {

@@ -164,6 +164,9 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     constexpr int kOut16 = (kMode >> 3) & 3; // 0: fp32 C; 1: C rounded to fp16 on the way out; 2: to bf16 (TSTORE's conversion)
     static_assert(kOut16 == 0 || (!kInt8 && !kBias), "16-bit output: plain fp16 product");
     static_assert(!kInt8 || (kBLayout == 1 && !kBias), "int8: B is n x k, no bias");
+    if (threadIdx.x == kThreads - 1) {
+        profile_stamp(status, 0);
+    }
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *staging = smem + kStages * kStageBytes;
@@ -458,6 +461,9 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // ---------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == kThreads - 1) {
+        profile_stamp(status, 1);
+    }
     if (ctl->abort_flag) {
         for (int i = 0; i < 1024; ++i) {
             __nanosleep(1000);
@@ -478,29 +484,30 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
 } // namespace
 
-int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
-                        cudaStream_t stream, const float *bias)
+namespace {
+
+// One launcher for every instance of the kernel.  kMode: bit 0 B stored n x k, bit 1 bias, bit 2 int8 operands (k
+// counts 16-bit pairs), bits 3-4 output type (0 fp32 / int32, 1 fp16, 2 bf16), bit 5 bfloat16 operands.
+template <int kMode>
+int launch_pair(const void *a, const void *b, void *c, const float *bias, int m, int n, int k, cudaStream_t stream)
 {
+    constexpr bool kBnk = (kMode & 1) != 0;
+    constexpr int kOutBytes = ((kMode >> 3) & 3) == 0 ? 4 : 2;
     CUtensorMap tmap_a, tmap_b, tmap_c;
     int rc = make_tmap_2d(&tmap_a, a, 2, m, k, k, BM, kBoxK, true);
     if (rc != kOk) {
         return rc;
     }
     // C leaves through TMA stores when its rows are 16-byte aligned; otherwise the epilogue stores directly
-    const int c_by_tma = ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0) ? 1 : 0;
+    const int c_by_tma = ((n & (16 / kOutBytes - 1)) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0) ? 1 : 0;
     if (c_by_tma) {
-        rc = make_tmap_2d(&tmap_c, c, 4, m, n, n, 32, 32, true);
-        if (rc != kOk) {
+        if ((rc = make_tmap_2d(&tmap_c, c, kOutBytes, m, n, n, 32, kOutBytes == 4 ? 32 : 64, true)) != kOk) {
             return rc;
         }
     } else {
         tmap_c = tmap_a; // never dereferenced
     }
-    if (b_layout == 1) {
-        rc = make_tmap_2d(&tmap_b, b, 2, n, k, k, BNH, kBoxK, true);
-    } else {
-        rc = make_tmap_2d(&tmap_b, b, 2, k, n, n, BK, 64, true);
-    }
+    rc = kBnk ? make_tmap_2d(&tmap_b, b, 2, n, k, k, BNH, kBoxK, true) : make_tmap_2d(&tmap_b, b, 2, k, n, n, BK, 64, true);
     if (rc != kOk) {
         return rc;
     }
@@ -513,135 +520,48 @@ int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, i
     if (status == nullptr) {
         return kErrCuda;
     }
-    static bool attr_set = false;
-    if (!attr_set) {
-        if ((rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm, 2 blocks per tile)")) != kOk ||
-            (rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm, 2 blocks per tile)")) != kOk ||
-            (rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm, 2 blocks per tile)")) != kOk ||
-            (rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm, 2 blocks per tile)")) != kOk) {
-            return rc;
-        }
-        attr_set = true;
+    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm2_f16f32_kernel<kMode>), kSmemBytes)) != kOk) {
+        return rc;
     }
-    const dim3 grid(2 * pairs);
-    if (bias == nullptr) {
-        if (b_layout == 1) {
-            gemm2_f16f32_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, bias, m, n, k, status);
-        } else {
-            gemm2_f16f32_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, bias, m, n, k, status);
-        }
-    } else if (b_layout == 1) {
-        gemm2_f16f32_kernel<3><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, bias, m, n, k, status);
-    } else {
-        gemm2_f16f32_kernel<2><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, bias, m, n, k, status);
-    }
+    gemm2_f16f32_kernel<kMode><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma,
+                                                                             static_cast<float *>(c), bias, m, n, k, status);
     return check_launch();
 }
 
-// bfloat16 operands, fp32 accumulate and output: the plain kernel with the other operand format in its instruction
-// descriptor (kMode bit 5); arguments validated by the caller
+} // namespace
+
+int launch_gemm2_f16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
+                        cudaStream_t stream, const float *bias)
+{
+    if (bias == nullptr) {
+        return b_layout == 1 ? launch_pair<1>(a, b, c, nullptr, m, n, k, stream)
+                             : launch_pair<0>(a, b, c, nullptr, m, n, k, stream);
+    }
+    return b_layout == 1 ? launch_pair<3>(a, b, c, bias, m, n, k, stream) : launch_pair<2>(a, b, c, bias, m, n, k, stream);
+}
+
+// bfloat16 operands, fp32 accumulate and output: the other operand format in the instruction descriptor (kMode bit 5);
+// arguments validated by the caller
 int launch_gemm2_bf16f32(const uint16_t *a, const uint16_t *b, float *c, int m, int n, int k, int b_layout,
                          cudaStream_t stream)
 {
-    CUtensorMap tmap_a, tmap_b, tmap_c;
-    int rc = make_tmap_2d(&tmap_a, a, 2, m, k, k, BM, kBoxK, true);
-    if (rc != kOk) {
-        return rc;
-    }
-    const int c_by_tma = ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0) ? 1 : 0;
-    if (c_by_tma) {
-        if ((rc = make_tmap_2d(&tmap_c, c, 4, m, n, n, 32, 32, true)) != kOk) {
-            return rc;
-        }
-    } else {
-        tmap_c = tmap_a; // never dereferenced
-    }
-    rc = (b_layout == 1) ? make_tmap_2d(&tmap_b, b, 2, n, k, k, BNH, kBoxK, true) : make_tmap_2d(&tmap_b, b, 2, k, n, n, BK, 64, true);
-    if (rc != kOk) {
-        return rc;
-    }
-    const int tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
-    int pairs = sm_count() / 2;
-    if (tiles < pairs) {
-        pairs = tiles;
-    }
-    DeviceStatus *status = device_status_ptr();
-    if (status == nullptr) {
-        return kErrCuda;
-    }
-    static bool attr_set = false;
-    if (!attr_set) {
-        if ((rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm bf16)")) != kOk ||
-            (rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<33>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm bf16)")) != kOk) {
-            return rc;
-        }
-        attr_set = true;
-    }
-    if (b_layout == 1) {
-        gemm2_f16f32_kernel<33><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, nullptr, m, n, k, status);
-    } else {
-        gemm2_f16f32_kernel<32><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, c, nullptr, m, n, k, status);
-    }
-    return check_launch();
+    return b_layout == 1 ? launch_pair<33>(a, b, c, nullptr, m, n, k, stream)
+                         : launch_pair<32>(a, b, c, nullptr, m, n, k, stream);
 }
 
-// C rounded to fp16 (out16 == 1) or bf16 (2): the same kernel with the converting epilogue (kMode bits 3-4)
+// C rounded to fp16 (out16 == 1) or bf16 (2): the converting epilogue (kMode bits 3-4)
 int launch_gemm2_f16_out16(const uint16_t *a, const uint16_t *b, uint16_t *c, int m, int n, int k, int b_layout, int out16,
                            cudaStream_t stream)
 {
-    CUtensorMap tmap_a, tmap_b, tmap_c;
-    int rc = make_tmap_2d(&tmap_a, a, 2, m, k, k, BM, kBoxK, true);
-    if (rc != kOk) {
-        return rc;
-    }
-    const int c_by_tma = ((n & 7) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0) ? 1 : 0;
-    if (c_by_tma) {
-        if ((rc = make_tmap_2d(&tmap_c, c, 2, m, n, n, 32, 64, true)) != kOk) {
-            return rc;
-        }
-    } else {
-        tmap_c = tmap_a; // never dereferenced
-    }
-    rc = (b_layout == 1) ? make_tmap_2d(&tmap_b, b, 2, n, k, k, BNH, kBoxK, true) : make_tmap_2d(&tmap_b, b, 2, k, n, n, BK, 64, true);
-    if (rc != kOk) {
-        return rc;
-    }
-    const int tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
-    int pairs = sm_count() / 2;
-    if (tiles < pairs) {
-        pairs = tiles;
-    }
-    DeviceStatus *status = device_status_ptr();
-    if (status == nullptr) {
-        return kErrCuda;
-    }
-    static bool attr_set = false;
-    if (!attr_set) {
-        if ((rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm out16)")) != kOk ||
-            (rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<9>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm out16)")) != kOk ||
-            (rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm out16)")) != kOk ||
-            (rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<17>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes), "cudaFuncSetAttribute(gemm out16)")) != kOk) {
-            return rc;
-        }
-        attr_set = true;
-    }
-    const dim3 grid(2 * pairs);
-    float *cf = reinterpret_cast<float *>(c);
     if (out16 == 1) {
-        if (b_layout == 1) {
-            gemm2_f16f32_kernel<9><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, cf, nullptr, m, n, k, status);
-        } else {
-            gemm2_f16f32_kernel<8><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, cf, nullptr, m, n, k, status);
-        }
-    } else if (b_layout == 1) {
-        gemm2_f16f32_kernel<17><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, cf, nullptr, m, n, k, status);
-    } else {
-        gemm2_f16f32_kernel<16><<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma, cf, nullptr, m, n, k, status);
+        return b_layout == 1 ? launch_pair<9>(a, b, c, nullptr, m, n, k, stream)
+                             : launch_pair<8>(a, b, c, nullptr, m, n, k, stream);
     }
-    return check_launch();
+    return b_layout == 1 ? launch_pair<17>(a, b, c, nullptr, m, n, k, stream)
+                         : launch_pair<16>(a, b, c, nullptr, m, n, k, stream);
 }
 
-// C[m x n] int32 = A[m x k] int8 * B[n x k]^T int8 on the same kernel (see kMode bit 2)
+// C[m x n] int32 = A[m x k] int8 * B[n x k]^T int8 (kMode bit 2): rows are handed to TMA as 16-bit pairs
 int launch_gemm2_i8i32(const int8_t *a, const int8_t *b, int32_t *c, int m, int n, int k, cudaStream_t stream)
 {
     if (a == nullptr || b == nullptr || c == nullptr || m <= 0 || n <= 0 || k <= 0) {
@@ -652,43 +572,7 @@ int launch_gemm2_i8i32(const int8_t *a, const int8_t *b, int32_t *c, int m, int 
         set_error_text("gemm_i8: k must be a multiple of 16 and the operands 16-byte aligned");
         return kErrUnsupportedShape;
     }
-    const int k2 = k / 2; // rows as 16-bit elements
-    CUtensorMap tmap_a, tmap_b, tmap_c;
-    int rc;
-    if ((rc = make_tmap_2d(&tmap_a, a, 2, m, k2, k2, BM, kBoxK, true)) != kOk ||
-        (rc = make_tmap_2d(&tmap_b, b, 2, n, k2, k2, BNH, kBoxK, true)) != kOk) {
-        return rc;
-    }
-    const int c_by_tma = ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0) ? 1 : 0;
-    if (c_by_tma) {
-        if ((rc = make_tmap_2d(&tmap_c, c, 4, m, n, n, 32, 32, true)) != kOk) {
-            return rc;
-        }
-    } else {
-        tmap_c = tmap_a; // never dereferenced
-    }
-    const int tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
-    int pairs = sm_count() / 2;
-    if (tiles < pairs) {
-        pairs = tiles;
-    }
-    DeviceStatus *status = device_status_ptr();
-    if (status == nullptr) {
-        return kErrCuda;
-    }
-    static bool attr_set = false;
-    if (!attr_set) {
-        if ((rc = check_cuda(cudaFuncSetAttribute(gemm2_f16f32_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                  kSmemBytes),
-                             "cudaFuncSetAttribute(gemm int8)")) != kOk) {
-            return rc;
-        }
-        attr_set = true;
-    }
-    gemm2_f16f32_kernel<5><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma,
-                                                                        reinterpret_cast<float *>(c), nullptr, m, n, k2,
-                                                                        status);
-    return check_launch();
+    return launch_pair<5>(a, b, c, nullptr, m, n, k / 2, stream);
 }
 
 } // namespace pto_b200

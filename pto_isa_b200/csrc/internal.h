@@ -11,6 +11,11 @@ struct DeviceStatus;
 
 // number of SMs of the current device (cached per device)
 int sm_count();
+// raises the dynamic shared-memory limit of a kernel on the current device, once per (kernel, device): the attribute is
+// kept per device, so a process that drives several GPUs needs it set on each of them
+int ensure_dynamic_smem(const void *kernel, int bytes);
+// ordinal of the current device, -1 when there is none (or more than the library's tables hold)
+int current_device_ordinal();
 // cudaGetLastError() mapped to a status code; records the CUDA error text for pto_b200_last_error()
 int check_launch();
 int check_cuda(cudaError_t e, const char *what);
@@ -22,7 +27,10 @@ int last_status();
 // allocated on first use for the current device
 DeviceStatus *device_status_ptr();
 // reads the status record back (synchronises `stream`) and clears it; returns its code
-int fetch_device_status(cudaStream_t stream);
+int fetch_device_status(cudaStream_t stream, int *record = nullptr); // record: {code, block, where, detail}
+
+// per-block profile stamps of the current device's kernels: on with a buffer of 4 * capacity_blocks words, off with null
+int set_profile_buffer(unsigned long long *stamps, long long capacity_blocks, cudaStream_t stream);
 
 // cuTensorMapEncodeTiled resolved through the runtime (no link-time dependency on libcuda)
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -43,6 +51,8 @@ int launch_tcvt_f32_16(const float *src, uint16_t *dst, int64_t n, bool bf16, cu
 int launch_tcvt_f32_i32(const float *src, int32_t *dst, int64_t n, int mode, cudaStream_t stream);
 int launch_tgather(const void *src0, int64_t numel, const int32_t *idx, void *dst, int64_t n, int elem_bytes,
                    cudaStream_t stream);
+int launch_random_read_probe(const uint32_t *table, int64_t table_bytes, int64_t reads, uint32_t *sink,
+                             cudaStream_t stream);
 int launch_tgather_mask(const void *src, void *dst, int rows, int cols, int pattern, int elem_bytes,
                         cudaStream_t stream);
 int launch_trow_reduce(const float *src, float *dst, int rows, int cols, int64_t row_stride, bool is_max,

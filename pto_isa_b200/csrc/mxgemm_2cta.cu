@@ -564,15 +564,9 @@ static int launch_mx_kernel(int pairs, cudaStream_t stream, const CUtensorMap &t
                             const CUtensorMap &tmap_sfa, const CUtensorMap &tmap_sfb, const CUtensorMap &tmap_c,
                             int c_by_tma, void *c, int m, int n, int k_bytes, int a_fmt, int b_fmt, DeviceStatus *status)
 {
-    static bool attr_set = false;
-    if (!attr_set) {
-        const int rc = check_cuda(cudaFuncSetAttribute(mxgemm2_kernel<kOutF32, kAtoms>,
-                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(kAtoms)),
-                                  "cudaFuncSetAttribute(mxgemm)");
-        if (rc != kOk) {
-            return rc;
-        }
-        attr_set = true;
+    const int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(&mxgemm2_kernel<kOutF32, kAtoms>), smem_bytes(kAtoms));
+    if (rc != kOk) {
+        return rc;
     }
     mxgemm2_kernel<kOutF32, kAtoms><<<2 * pairs, kThreads, smem_bytes(kAtoms), stream>>>(
         tmap_a, tmap_b, tmap_sfa, tmap_sfb, tmap_c, c_by_tma, c, m, n, k_bytes, a_fmt, b_fmt, status);

@@ -17,7 +17,24 @@ struct DeviceStatus {
     int block;     // blockIdx.x that reported
     int where;     // which wait gave up
     int detail;    // stage / phase
+    // optional per-block profile stamps (pto_b200_set_profile_buffer): four words per block,
+    // {%globaltimer at block start, at block end, clock64 at block start, at block end}; null = off
+    unsigned long long *stamps;
+    long long stamps_capacity; // blocks the buffer holds
 };
+
+// first / last thing a block does when stamps are on (one thread; the pointer is re-read at the end so that no
+// register is held across the kernel)
+__device__ __forceinline__ void profile_stamp(const DeviceStatus *status, int which)
+{
+    unsigned long long *st = status->stamps;
+    if (st != nullptr && static_cast<long long>(blockIdx.x) < status->stamps_capacity) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        st[4ull * blockIdx.x + which] = t;
+        st[4ull * blockIdx.x + 2 + which] = static_cast<unsigned long long>(clock64());
+    }
+}
 
 enum StatusCode : int {
     kOk = 0,

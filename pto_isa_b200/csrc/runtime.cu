@@ -5,9 +5,12 @@
 #include "internal.h"
 
 #include <cstdarg>
+#include <cstddef>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <utility>
+#include <vector>
 
 namespace pto_b200 {
 
@@ -68,6 +71,34 @@ int check_launch()
     return check_cuda(cudaGetLastError(), "kernel launch");
 }
 
+int current_device_ordinal()
+{
+    return current_device();
+}
+
+int ensure_dynamic_smem(const void *kernel, int bytes)
+{
+    // (kernel, device) pairs already raised; a handful of kernels times a handful of devices
+    static std::vector<std::pair<const void *, int>> done;
+    const int dev = current_device();
+    if (dev < 0) {
+        set_error_text("no current CUDA device");
+        return kErrCuda;
+    }
+    std::lock_guard<std::mutex> lock(g_mutex);
+    for (const auto &e : done) {
+        if (e.first == kernel && e.second == dev) {
+            return kOk;
+        }
+    }
+    const int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes),
+                              "cudaFuncSetAttribute(max dynamic shared memory)");
+    if (rc == kOk) {
+        done.emplace_back(kernel, dev);
+    }
+    return rc;
+}
+
 int sm_count()
 {
     const int dev = current_device();
@@ -106,7 +137,7 @@ DeviceStatus *device_status_ptr()
     return g_status[dev];
 }
 
-int fetch_device_status(cudaStream_t stream)
+int fetch_device_status(cudaStream_t stream, int *record)
 {
     DeviceStatus *p = device_status_ptr();
     if (p == nullptr) {
@@ -121,12 +152,37 @@ int fetch_device_status(cudaStream_t stream)
     if (rc != kOk) {
         return rc;
     }
+    if (record != nullptr) {
+        record[0] = h.code;
+        record[1] = h.block;
+        record[2] = h.where;
+        record[3] = h.detail;
+    }
     if (h.code != 0) {
         set_error_text("device-side wait gave up: code %d, block %d, where %d, detail %d", h.code, h.block, h.where,
                        h.detail);
-        cudaMemsetAsync(p, 0, sizeof(DeviceStatus), stream);
+        cudaMemsetAsync(p, 0, 4 * sizeof(int), stream); // the four status words; the profile settings stay
     }
     return h.code;
+}
+
+int set_profile_buffer(unsigned long long *stamps, long long capacity_blocks, cudaStream_t stream)
+{
+    DeviceStatus *p = device_status_ptr();
+    if (p == nullptr) {
+        return kErrCuda;
+    }
+    struct {
+        unsigned long long *stamps;
+        long long cap;
+    } v = {stamps, stamps == nullptr ? 0 : capacity_blocks};
+    int rc = check_cuda(cudaMemcpyAsync(reinterpret_cast<char *>(p) + offsetof(DeviceStatus, stamps), &v, sizeof(v),
+                                        cudaMemcpyHostToDevice, stream),
+                        "cudaMemcpyAsync(profile settings)");
+    if (rc == kOk) {
+        rc = check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+    }
+    return rc;
 }
 
 EncodeTiledFn encode_tiled_fn()

@@ -162,6 +162,33 @@ __global__ void __launch_bounds__(kThreads) tgather_b32_kernel(const uint32_t *_
     }
 }
 
+// Random 4-byte reads of a table and nothing else (indices from a hash of the thread's counter, results folded into one
+// word): the measured ceiling for the gather part of TGATHER.
+__global__ void __launch_bounds__(kThreads) random_read_probe_kernel(const uint32_t *__restrict__ table, uint32_t mask,
+                                                                     int64_t per_thread, uint32_t *__restrict__ sink)
+{
+    uint32_t s = (blockIdx.x * blockDim.x + threadIdx.x) * 2654435761u + 12345u;
+    uint32_t acc = 0;
+    for (int64_t it = 0; it < per_thread; it += 4) {
+        uint32_t a[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            s = s * 1664525u + 1013904223u;
+            uint32_t h = s ^ (s >> 15);
+            h *= 2246822519u;
+            h ^= h >> 13;
+            a[v] = h & mask;
+        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            acc ^= __ldg(table + a[v]);
+        }
+    }
+    if (acc == 0x12345678u) {
+        sink[0] = acc; // keeps the loads alive
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads) tgather_scalar_kernel(const T *__restrict__ src0, int64_t numel,
                                                                   const int32_t *__restrict__ idx,
@@ -360,6 +387,17 @@ int launch_tgather(const void *src0, int64_t numel, const int32_t *idx, void *ds
         tgather_scalar_kernel<uint16_t><<<grid_for(n, kThreads), kThreads, 0, stream>>>(
             static_cast<const uint16_t *>(src0), numel, idx, static_cast<uint16_t *>(dst), n);
     }
+    return check_launch();
+}
+
+int launch_random_read_probe(const uint32_t *table, int64_t table_bytes, int64_t reads, uint32_t *sink,
+                             cudaStream_t stream)
+{
+    const int grid = sm_count() * 8;
+    const int64_t threads = static_cast<int64_t>(grid) * kThreads;
+    int64_t per = (reads + threads - 1) / threads;
+    per = (per + 3) / 4 * 4;
+    random_read_probe_kernel<<<grid, kThreads, 0, stream>>>(table, static_cast<uint32_t>(table_bytes / 4 - 1), per, sink);
     return check_launch();
 }
 

@@ -39,12 +39,36 @@ def _need_cuda(*ts):
             raise PtoB200Error("operands must be contiguous")
 
 
+def _out(out, shape, dtype, device, what):
+    """A fresh result tensor, or the caller's `out=` once it is known to be exactly what the kernel will write:
+    the C ABI takes raw pointers, so a wrong shape, type or device here would be an out-of-bounds device write."""
+    shape = tuple(int(x) for x in (shape if isinstance(shape, (tuple, list, torch.Size)) else (shape,)))
+    if out is None:
+        return torch.empty(shape, dtype=dtype, device=device)
+    if not isinstance(out, torch.Tensor):
+        raise PtoB200Error(f"{what}: out= must be a tensor")
+    if tuple(out.shape) != shape or out.dtype != dtype:
+        raise PtoB200Error(f"{what}: out= must have shape {shape} and dtype {dtype}, got {tuple(out.shape)} {out.dtype}")
+    want = torch.device(device)
+    if not out.is_cuda or (want.index is not None and out.device != want):
+        raise PtoB200Error(f"{what}: out= must be a CUDA tensor on {want}")
+    if not out.is_contiguous():
+        raise PtoB200Error(f"{what}: out= must be contiguous")
+    return out
+
+
+def _same_device(what, *ts):
+    for t in ts[1:]:
+        if t.device != ts[0].device:
+            raise PtoB200Error(f"{what}: operands must be on the same device")
+
+
 def TCVT(src, dtype, round_mode=CAST_RINT, out=None):
     """Elementwise cast of an fp32 tensor to torch.float16, torch.bfloat16 or torch.int32."""
     _need_cuda(src)
     if src.dtype != torch.float32:
         raise PtoB200Error("TCVT: source must be float32")
-    out = torch.empty(src.shape, dtype=dtype, device=src.device) if out is None else out
+    out = _out(out, src.shape, dtype, src.device, "TCVT")
     _need_cuda(out)
     with torch.cuda.device(src.device):
         if dtype == torch.float16:
@@ -62,11 +86,12 @@ def TCVT(src, dtype, round_mode=CAST_RINT, out=None):
 def TGATHER(src0, idx, out=None):
     """out[i] = src0.flatten()[idx[i]]; an index outside [0, src0.numel()) gives 0.  4- or 2-byte elements."""
     _need_cuda(src0, idx)
+    _same_device("TGATHER", src0, idx)
     if idx.dtype != torch.int32:
         raise PtoB200Error("TGATHER: indices must be int32")
     if src0.element_size() not in (2, 4):
         raise PtoB200Error("TGATHER: 16- or 32-bit elements only")
-    out = torch.empty(idx.shape, dtype=src0.dtype, device=src0.device) if out is None else out
+    out = _out(out, idx.shape, src0.dtype, src0.device, "TGATHER")
     with torch.cuda.device(src0.device):
         rc = lib().pto_b200_tgather(_ptr(src0), src0.numel(), _ptr(idx), _ptr(out), idx.numel(), src0.element_size(),
                                     _stream(src0))
@@ -82,7 +107,7 @@ def TGATHER_MASK(src, pattern, out=None):
     rows, cols = src.shape
     div, off = {1: (2, 0), 2: (2, 1), 3: (4, 0), 4: (4, 1), 5: (4, 2), 6: (4, 3), 7: (1, 0)}[int(pattern)]
     out_cols = (cols - off + div - 1) // div
-    out = torch.empty(rows * out_cols, dtype=src.dtype, device=src.device) if out is None else out
+    out = _out(out, rows * out_cols, src.dtype, src.device, "TGATHER_MASK")
     with torch.cuda.device(src.device):
         rc = lib().pto_b200_tgather_mask(_ptr(src), _ptr(out), rows, cols, int(pattern), src.element_size(),
                                          _stream(src))
@@ -95,7 +120,7 @@ def _row_reduce(fn_name, src, out):
     if src.dim() != 2 or src.dtype != torch.float32:
         raise PtoB200Error(f"{fn_name}: expects a 2-D float32 tensor")
     rows, cols = src.shape
-    out = torch.empty(rows, dtype=torch.float32, device=src.device) if out is None else out
+    out = _out(out, rows, torch.float32, src.device, "_row_reduce")
     with torch.cuda.device(src.device):
         rc = getattr(lib(), fn_name)(_ptr(src), _ptr(out), rows, cols, cols, _stream(src))
     check(rc, fn_name)
@@ -112,7 +137,9 @@ def TROWSUM(src, out=None):
 
 def TEXP(src, out=None):
     _need_cuda(src)
-    out = torch.empty_like(src) if out is None else out
+    if src.dtype != torch.float32:
+        raise PtoB200Error("TEXP: source must be float32")
+    out = _out(out, src.shape, src.dtype, src.device, "TEXP")
     with torch.cuda.device(src.device):
         rc = lib().pto_b200_texp_f32(_ptr(src), _ptr(out), src.numel(), _stream(src))
     check(rc, "TEXP")
@@ -123,7 +150,7 @@ def _binary(a, b, op, out):
     _need_cuda(a, b)
     if a.shape != b.shape or a.dtype != torch.float32 or b.dtype != torch.float32:
         raise PtoB200Error("binary tile op: operands must be float32 of the same shape")
-    out = torch.empty_like(a) if out is None else out
+    out = _out(out, a.shape, a.dtype, a.device, "_binary")
     with torch.cuda.device(a.device):
         rc = lib().pto_b200_tbinary_f32(_ptr(a), _ptr(b), _ptr(out), a.numel(), op, _stream(a))
     check(rc, "binary tile op")
@@ -156,7 +183,7 @@ def TMIN(a, b, out=None):
 
 def _scalar(a, s, op, out):
     _need_cuda(a)
-    out = torch.empty_like(a) if out is None else out
+    out = _out(out, a.shape, a.dtype, a.device, "_scalar")
     with torch.cuda.device(a.device):
         rc = lib().pto_b200_tscalar_f32(_ptr(a), float(s), _ptr(out), a.numel(), op, _stream(a))
     check(rc, "scalar tile op")
@@ -175,7 +202,7 @@ def _rowexpand(a, row_scalar, op, out):
     _need_cuda(a, row_scalar)
     if a.dim() != 2 or row_scalar.numel() != a.shape[0]:
         raise PtoB200Error("row-expand tile op: expects a 2-D tile and one scalar per row")
-    out = torch.empty_like(a) if out is None else out
+    out = _out(out, a.shape, a.dtype, a.device, "_rowexpand")
     with torch.cuda.device(a.device):
         rc = lib().pto_b200_trowexpand_f32(_ptr(a), _ptr(row_scalar), _ptr(out), a.shape[0], a.shape[1], op,
                                            _stream(a))
@@ -217,7 +244,7 @@ def TROWEXPAND(row_scalar, cols, out=None):
     if row_scalar.dtype != torch.float32:
         raise PtoB200Error("TROWEXPAND: expects float32")
     rows = row_scalar.numel()
-    out = torch.empty(rows, cols, dtype=torch.float32, device=row_scalar.device) if out is None else out
+    out = _out(out, (rows, cols), torch.float32, row_scalar.device, "TROWEXPAND")
     with torch.cuda.device(row_scalar.device):
         rc = lib().pto_b200_trowexpand_f32(None, _ptr(row_scalar), _ptr(out), rows, cols, OP_EXPAND, _stream(row_scalar))
     check(rc, "TROWEXPAND")
@@ -233,7 +260,7 @@ def _col_reduce(src, op, out, what, workspace=None):
     if src.dim() != 2 or src.dtype != torch.float32:
         raise PtoB200Error(f"{what}: expects a 2-D float32 tensor")
     rows, cols = src.shape
-    out = torch.empty(cols, dtype=torch.float32, device=src.device) if out is None else out
+    out = _out(out, cols, torch.float32, src.device, "_col_reduce")
     ws_bytes = lib().pto_b200_tcolreduce_workspace_bytes(rows, cols) if workspace is None else workspace.numel() * workspace.element_size()
     if workspace is None and ws_bytes > 0:
         workspace = torch.empty(ws_bytes // 4, dtype=torch.float32, device=src.device)  # torch's caching allocator
@@ -273,7 +300,7 @@ def TFILLPAD(src, valid_rows, valid_cols, pad=PAD_ZERO, out=None):
     _need_cuda(src)
     if src.dim() != 2 or src.dtype.itemsize not in (2, 4):
         raise PtoB200Error("TFILLPAD: expects a 2-D tensor of 2- or 4-byte elements")
-    out = torch.empty_like(src) if out is None else out
+    out = _out(out, src.shape, src.dtype, src.device, "TFILLPAD")
     with torch.cuda.device(src.device):
         rc = lib().pto_b200_tfillpad(_ptr(src), _ptr(out), src.shape[0], src.shape[1], int(valid_rows), int(valid_cols),
                                      _pad_bits(src.dtype, pad), src.dtype.itemsize, _stream(src))
@@ -285,7 +312,7 @@ def TTRANS(src, out=None):
     _need_cuda(src)
     if src.dim() != 2 or src.dtype.itemsize not in (2, 4):
         raise PtoB200Error("TTRANS: expects a 2-D tensor of 2- or 4-byte elements")
-    out = torch.empty(src.shape[1], src.shape[0], dtype=src.dtype, device=src.device) if out is None else out
+    out = _out(out, (src.shape[1], src.shape[0]), src.dtype, src.device, "TTRANS")
     with torch.cuda.device(src.device):
         rc = lib().pto_b200_ttrans(_ptr(src), _ptr(out), src.shape[0], src.shape[1], src.dtype.itemsize, _stream(src))
     check(rc, "TTRANS")
@@ -299,7 +326,7 @@ def TSEL(mask, src0, src1, out=None):
         raise PtoB200Error("TSEL: operands must have the same shape and a 2- or 4-byte element type")
     if mask.dtype != torch.uint8 or mask.numel() * 8 < src0.numel():
         raise PtoB200Error("TSEL: the mask must be uint8 with one bit per element")
-    out = torch.empty_like(src0) if out is None else out
+    out = _out(out, src0.shape, src0.dtype, src0.device, "TSEL")
     with torch.cuda.device(src0.device):
         rc = lib().pto_b200_tsel(_ptr(mask), _ptr(src0), _ptr(src1), _ptr(out), src0.numel(), src0.dtype.itemsize,
                                  _stream(src0))
@@ -312,7 +339,7 @@ def TCMPS(src, scalar, mode, out=None):
     _need_cuda(src)
     if src.dtype != torch.float32 or src.numel() % 8 != 0:
         raise PtoB200Error("TCMPS: expects float32 with a multiple of 8 elements")
-    out = torch.empty(src.numel() // 8, dtype=torch.uint8, device=src.device) if out is None else out
+    out = _out(out, src.numel() // 8, torch.uint8, src.device, "TCMPS")
     with torch.cuda.device(src.device):
         rc = lib().pto_b200_tcmps_f32(_ptr(src), float(scalar), _ptr(out), src.numel(), int(mode), _stream(src))
     check(rc, "TCMPS")
@@ -324,7 +351,7 @@ def TCMP(a, b, mode, out=None):
     _need_cuda(a, b)
     if a.shape != b.shape or a.dtype != torch.float32 or b.dtype != torch.float32:
         raise PtoB200Error("TCMP: operands must be float32 of the same shape")
-    out = torch.empty_like(a) if out is None else out
+    out = _out(out, a.shape, a.dtype, a.device, "TCMP")
     with torch.cuda.device(a.device):
         rc = lib().pto_b200_tcmp_f32(_ptr(a), _ptr(b), _ptr(out), a.numel(), int(mode), _stream(a))
     check(rc, "TCMP")
@@ -338,7 +365,7 @@ def TTRI(rows, cols, diagonal=0, upper=False, dtype=torch.float32, device="cuda"
     """rows x cols tile of ones inside the lower (c <= r + diagonal) or upper (c >= r + diagonal) triangle, zeros outside."""
     if dtype not in _TRI_DTYPES:
         raise PtoB200Error("TTRI: float32, int32, float16 or int16")
-    out = torch.empty(rows, cols, dtype=dtype, device=device) if out is None else out
+    out = _out(out, (rows, cols), dtype, device, "TTRI")
     _need_cuda(out)
     with torch.cuda.device(out.device):
         rc = lib().pto_b200_ttri(_ptr(out), int(rows), int(cols), int(diagonal), 1 if upper else 0, _TRI_DTYPES[dtype],
@@ -384,7 +411,7 @@ def mx_gemm(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, out=None, fmt=FP8_
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise PtoB200Error("mx_gemm: the output is bfloat16 or float32")
     fa, fb = _fp8_format(a, fmt), _fp8_format(b, fmt)
-    out = torch.empty(m, n, dtype=out_dtype, device=a.device) if out is None else out
+    out = _out(out, (m, n), out_dtype, a.device, "mx_gemm")
     _need_cuda(out)
     need = lib().pto_b200_mxgemm_workspace_bytes(m, n, k)
     if workspace is None:
@@ -413,7 +440,7 @@ def mx_gemm_fp4(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, out=None, work
         raise PtoB200Error("mx_gemm_fp4: k must be a multiple of 32 and the scales (m, k/32) and (n, k/32)")
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise PtoB200Error("mx_gemm_fp4: the output is bfloat16 or float32")
-    out = torch.empty(m, n, dtype=out_dtype, device=a.device) if out is None else out
+    out = _out(out, (m, n), out_dtype, a.device, "mx_gemm_fp4")
     _need_cuda(out)
     need = lib().pto_b200_mxgemm_workspace_bytes(m, n, k)
     if workspace is None:
@@ -437,13 +464,21 @@ def gemm(a, b, b_layout=1, out=None, bias=None):
     _need_cuda(a, b)
     if a.dtype != torch.float16 or b.dtype != torch.float16:
         raise PtoB200Error("gemm: operands must be float16")
+    _same_device("gemm", a, b)
     batched = a.dim() == 3
+    if a.dim() not in (2, 3) or b.dim() != a.dim() or (batched and a.shape[0] != b.shape[0]):
+        raise PtoB200Error("gemm: a and b are both 2-D, or both 3-D with the same batch")
+    if b_layout not in (0, 1):
+        raise PtoB200Error("gemm: b_layout is 0 (b is k x n) or 1 (b is n x k)")
+    if a.shape[-1] != (b.shape[-2] if b_layout == 0 else b.shape[-1]):
+        raise PtoB200Error(f"gemm: the k extents of a {tuple(a.shape)} and b {tuple(b.shape)} differ (b_layout {b_layout})")
     if bias is not None:
         _need_cuda(bias)
+        _same_device("gemm", a, bias)
         n_ = b.shape[-1] if b_layout == 0 else b.shape[-2]
         if batched or bias.dtype != torch.float32 or bias.numel() != n_:
             raise PtoB200Error("gemm: bias is n float32 values, for a single problem")
-        out = torch.empty(a.shape[0], n_, dtype=torch.float32, device=a.device) if out is None else out
+        out = _out(out, (a.shape[0], n_), torch.float32, a.device, "gemm")
         with torch.cuda.device(a.device):
             rc = lib().pto_b200_gemm_f16f32_bias(_ptr(a), _ptr(b), _ptr(bias), _ptr(out), a.shape[0], n_, a.shape[1],
                                                  int(b_layout), _stream(a))
@@ -452,7 +487,7 @@ def gemm(a, b, b_layout=1, out=None, bias=None):
     m, k = a.shape[-2:]
     n = b.shape[-1] if b_layout == 0 else b.shape[-2]
     shape = (a.shape[0], m, n) if batched else (m, n)
-    out = torch.empty(shape, dtype=torch.float32, device=a.device) if out is None else out
+    out = _out(out, shape, torch.float32, a.device, "gemm")
     with torch.cuda.device(a.device):
         if batched:
             rc = lib().pto_b200_gemm_f16f32_batched(_ptr(a), _ptr(b), _ptr(out), m, n, k, int(b_layout), a.shape[0],
@@ -468,9 +503,12 @@ def gemm_bf16(a, b, b_layout=1, out=None):
     _need_cuda(a, b)
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or a.dim() != 2 or b.dim() != 2:
         raise PtoB200Error("gemm_bf16: operands are 2-D bfloat16")
+    _same_device("gemm_bf16", a, b)
+    if b_layout not in (0, 1) or a.shape[1] != (b.shape[0] if b_layout == 0 else b.shape[1]):
+        raise PtoB200Error(f"gemm_bf16: the k extents of a {tuple(a.shape)} and b {tuple(b.shape)} differ (b_layout {b_layout})")
     m, k = a.shape
     n = b.shape[1] if b_layout == 0 else b.shape[0]
-    out = torch.empty(m, n, dtype=torch.float32, device=a.device) if out is None else out
+    out = _out(out, (m, n), torch.float32, a.device, "gemm_bf16")
     with torch.cuda.device(a.device):
         rc = lib().pto_b200_gemm_bf16f32(_ptr(a), _ptr(b), _ptr(out), m, n, k, int(b_layout), _stream(a))
     check(rc, "gemm_bf16")
@@ -482,11 +520,14 @@ def gemm_out16(a, b, b_layout=1, out_dtype=torch.float16, out=None):
     _need_cuda(a, b)
     if a.dtype != torch.float16 or b.dtype != torch.float16 or a.dim() != 2 or b.dim() != 2:
         raise PtoB200Error("gemm_out16: operands are 2-D float16")
+    _same_device("gemm_out16", a, b)
+    if b_layout not in (0, 1) or a.shape[1] != (b.shape[0] if b_layout == 0 else b.shape[1]):
+        raise PtoB200Error(f"gemm_out16: the k extents of a {tuple(a.shape)} and b {tuple(b.shape)} differ (b_layout {b_layout})")
     if out_dtype not in (torch.float16, torch.bfloat16):
         raise PtoB200Error("gemm_out16: the output is float16 or bfloat16")
     m, k = a.shape
     n = b.shape[1] if b_layout == 0 else b.shape[0]
-    out = torch.empty(m, n, dtype=out_dtype, device=a.device) if out is None else out
+    out = _out(out, (m, n), out_dtype, a.device, "gemm_out16")
     with torch.cuda.device(a.device):
         rc = lib().pto_b200_gemm_f16_out16(_ptr(a), _ptr(b), _ptr(out), m, n, k, int(b_layout),
                                            2 if out_dtype == torch.float16 else 4, _stream(a))
@@ -499,9 +540,10 @@ def gemm_i8(a, b, out=None):
     _need_cuda(a, b)
     if a.dtype != torch.int8 or b.dtype != torch.int8 or a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
         raise PtoB200Error("gemm_i8: a is (m, k) and b is (n, k), both int8")
+    _same_device("gemm_i8", a, b)
     m, k = a.shape
     n = b.shape[0]
-    out = torch.empty(m, n, dtype=torch.int32, device=a.device) if out is None else out
+    out = _out(out, (m, n), torch.int32, a.device, "gemm_i8")
     with torch.cuda.device(a.device):
         rc = lib().pto_b200_gemm_i8i32(_ptr(a), _ptr(b), _ptr(out), m, n, k, _stream(a))
     check(rc, "gemm_i8")
@@ -510,6 +552,14 @@ def gemm_i8(a, b, out=None):
 
 def gemm_host(a, b, c, b_layout=1):
     """Same product over HOST tensors (pinned or pageable): copies in, computes, copies out, synchronises."""
+    if any(t.is_cuda or not t.is_contiguous() for t in (a, b, c)) or a.dim() != 2 or b.dim() != 2:
+        raise PtoB200Error("gemm_host: expects contiguous 2-D host tensors")
+    if a.dtype != torch.float16 or b.dtype != torch.float16 or c.dtype != torch.float32 or b_layout not in (0, 1):
+        raise PtoB200Error("gemm_host: a and b are float16, c is float32, b_layout is 0 or 1")
+    if a.shape[1] != (b.shape[0] if b_layout == 0 else b.shape[1]):
+        raise PtoB200Error("gemm_host: the k extents of a and b differ")
+    if tuple(c.shape) != (a.shape[0], b.shape[1] if b_layout == 0 else b.shape[0]):
+        raise PtoB200Error("gemm_host: c must be (m, n)")
     m, k = a.shape
     n = b.shape[1] if b_layout == 0 else b.shape[0]
     rc = lib().pto_b200_gemm_f16f32_host(_ptr(a), _ptr(b), _ptr(c), m, n, k, int(b_layout))
@@ -524,8 +574,12 @@ def gemm_host_batched(a, b, c, b_layout=1):
         raise PtoB200Error("gemm_host_batched: expects 3-D host tensors")
     if not (a.is_contiguous() and b.is_contiguous() and c.is_contiguous()):
         raise PtoB200Error("gemm_host_batched: operands must be contiguous")
+    if a.dtype != torch.float16 or b.dtype != torch.float16 or c.dtype != torch.float32 or b_layout not in (0, 1):
+        raise PtoB200Error("gemm_host_batched: a and b are float16, c is float32, b_layout is 0 or 1")
     batch, m, k = a.shape
     n = b.shape[2] if b_layout == 0 else b.shape[1]
+    if b.shape[0] != batch or k != (b.shape[1] if b_layout == 0 else b.shape[2]) or tuple(c.shape) != (batch, m, n):
+        raise PtoB200Error("gemm_host_batched: a (batch, m, k), b (batch, n, k) or (batch, k, n) and c (batch, m, n) disagree")
     rc = lib().pto_b200_gemm_f16f32_host_batched(_ptr(a), _ptr(b), _ptr(c), m, n, k, int(b_layout), batch, m * k, n * k, m * n)
     check(rc, "gemm_host_batched")
     return c
@@ -536,11 +590,17 @@ def flash_attn_fwd(q, k, v, causal=False, scale=None, out_dtype=torch.float16, o
     _need_cuda(q, k, v)
     if q.dtype != torch.float16 or k.dtype != torch.float16 or v.dtype != torch.float16:
         raise PtoB200Error("flash_attn_fwd: operands must be float16")
+    _same_device("flash_attn_fwd", q, k, v)
+    if out_dtype not in (torch.float16, torch.float32):
+        raise PtoB200Error("flash_attn_fwd: the output is float16 or float32")
+    if q.dim() < 2 or k.shape != v.shape or k.dim() != q.dim() or k.shape[:-2] != q.shape[:-2] or k.shape[-1] != q.shape[-1]:
+        raise PtoB200Error(f"flash_attn_fwd: q {tuple(q.shape)}, k {tuple(k.shape)} and v {tuple(v.shape)} must share "
+                           "their leading (batch, heads) extents and the head size, and k and v their shape")
     sq, d = q.shape[-2:]
     sk = k.shape[-2]
     bh = q.numel() // (sq * d)
     scale = (1.0 / d ** 0.5) if scale is None else float(scale)
-    out = torch.empty(q.shape, dtype=out_dtype, device=q.device) if out is None else out
+    out = _out(out, q.shape, out_dtype, q.device, "flash_attn_fwd")
     with torch.cuda.device(q.device):
         rc = lib().pto_b200_flash_attn_fwd_f16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), bh, sq, sk, d, int(bool(causal)),
                                                scale, 1 if out_dtype == torch.float16 else 0, _stream(q))
@@ -549,6 +609,14 @@ def flash_attn_fwd(q, k, v, causal=False, scale=None, out_dtype=torch.float16, o
 
 
 def flash_attn_fwd_host(q, k, v, o, causal=False, scale=None):
+    """The same over HOST tensors: copies in, computes, copies out, synchronises.  o is float16 or float32, shaped like q."""
+    if any(t.is_cuda or not t.is_contiguous() for t in (q, k, v, o)):
+        raise PtoB200Error("flash_attn_fwd_host: expects contiguous host tensors")
+    if q.dtype != torch.float16 or k.dtype != torch.float16 or v.dtype != torch.float16 or \
+            o.dtype not in (torch.float16, torch.float32):
+        raise PtoB200Error("flash_attn_fwd_host: q, k, v are float16, o is float16 or float32")
+    if k.shape != v.shape or k.shape[:-2] != q.shape[:-2] or k.shape[-1] != q.shape[-1] or o.shape != q.shape:
+        raise PtoB200Error("flash_attn_fwd_host: shapes of q, k, v and o disagree")
     sq, d = q.shape[-2:]
     sk = k.shape[-2]
     bh = q.numel() // (sq * d)
@@ -564,3 +632,39 @@ def device_status(device=None):
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     with torch.cuda.device(dev):
         return lib().pto_b200_device_status(ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+
+
+def device_status_record(device=None):
+    """Reads and clears the status record; returns (code, block, where, detail)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    rec = (ctypes.c_int * 4)()
+    with torch.cuda.device(dev):
+        lib().pto_b200_device_status_ex(ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream), rec)
+    return tuple(rec)
+
+
+def set_profile_buffer(stamps):
+    """Per-block profile stamps: `stamps` is a CUDA int64 tensor of shape (blocks, 4) that the GEMM and attention
+    kernels fill with {timer ns at block start, at block end, SM cycle counter at start, at end}; None switches them off."""
+    if stamps is None:
+        check(lib().pto_b200_set_profile_buffer(None, 0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)),
+              "set_profile_buffer")
+        return
+    _need_cuda(stamps)
+    if stamps.dtype != torch.int64 or stamps.dim() != 2 or stamps.shape[1] != 4:
+        raise PtoB200Error("set_profile_buffer: expects an int64 tensor of shape (blocks, 4)")
+    with torch.cuda.device(stamps.device):
+        check(lib().pto_b200_set_profile_buffer(_ptr(stamps), stamps.shape[0], _stream(stamps)), "set_profile_buffer")
+
+
+def probe_random_reads(table, reads, table_bytes=None):
+    """Launches `reads` random 4-byte reads over the first `table_bytes` of `table` (measurement helper for TGATHER)."""
+    _need_cuda(table)
+    table_bytes = table.numel() * table.element_size() if table_bytes is None else int(table_bytes)
+    if table_bytes > table.numel() * table.element_size():
+        raise PtoB200Error("probe_random_reads: table_bytes exceeds the tensor")
+    sink = torch.zeros(1, dtype=torch.int32, device=table.device)
+    with torch.cuda.device(table.device):
+        check(lib().pto_b200_probe_random_reads(_ptr(table), table_bytes, int(reads), _ptr(sink), _stream(table)),
+              "probe_random_reads")
+    return sink

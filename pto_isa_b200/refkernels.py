@@ -1,10 +1,13 @@
 """Builds the reference's own tile programs against this repository's PTO headers (include/pto/) with nvcc.
 
-The device code of the reference kernels is compiled unchanged.  One thing is not C++ that nvcc accepts:
-Ascend's launch statement `kernel<<<blocks, l2ctrl, stream>>>(args)` (the second launch argument is an L2
-control pointer there, a block shape in CUDA).  `rewrite_launches` turns exactly those statements into
-`PTO_B200_LAUNCH((kernel), blocks, stream, args)`; nothing else in the file is touched.  The rewritten
-text only ever exists in the build directory.
+The device code of the reference kernels is compiled unchanged, with two exceptions that CUDA cannot express as
+written.  (1) Ascend's launch statement `kernel<<<blocks, l2ctrl, stream>>>(args)` (the second launch argument is
+an L2 control pointer there, a block shape in CUDA): `rewrite_launches` turns exactly those statements into
+`PTO_B200_LAUNCH((kernel), blocks, stream, args)`.  (2) A function-local `static T name = init;` in device code:
+in CUDA that is one variable for the whole grid, where the reference means one per core; `rewrite_core_statics`
+turns the declaration into `PTO_B200_CORE_STATIC(T, name, init, slot)` (a per-block value, include/pto/b200/
+runtime.hpp).  Nothing else in the files is touched, and the rewritten text only ever exists in the build directory.
+Unit-test kernels and headers that contain neither construct are included straight from the reference tree.
 
 The result, pto_isa_b200/libpto_b200_refkernels.so, is built where the reference tree is available and
 travels with the package; tests that need it skip when it is absent.
@@ -48,8 +51,31 @@ def rewrite_launches(text):
     return "".join(out)
 
 
-def build(reference="/root/reference", force=False, verbose=False):
+_STATIC = re.compile(r"^(\s*)static\s+([A-Za-z_][\w:]*)\s+([A-Za-z_]\w*)\s*=\s*([^;]+);", re.M)
+
+
+def rewrite_core_statics(text):
+    """`static T name = init;` (indented, i.e. inside a function) -> `PTO_B200_CORE_STATIC(T, name, init, slot);`"""
+    slot = [0]
+
+    def rep(m):
+        if not m.group(1):  # file scope: not a function-local static
+            return m.group(0)
+        out = f"{m.group(1)}PTO_B200_CORE_STATIC({m.group(2)}, {m.group(3)}, {m.group(4).strip()}, {slot[0]});"
+        slot[0] += 1
+        return out
+
+    return _STATIC.sub(rep, text)
+
+
+def default_reference():
+    """The reference tree: $PTO_REFERENCE_ROOT, else a `reference` directory beside the repository."""
+    return os.environ.get("PTO_REFERENCE_ROOT") or os.path.join(os.path.dirname(ROOT), "reference")
+
+
+def build(reference=None, force=False, verbose=False):
     """Returns the path of the built library, or None when the reference tree is not present."""
+    reference = reference or default_reference()
     if not os.path.isdir(os.path.join(reference, "kernels")):
         return OUT if os.path.exists(OUT) else None
     if not force and os.path.exists(OUT) and os.path.getmtime(OUT) >= max(
@@ -60,10 +86,11 @@ def build(reference="/root/reference", force=False, verbose=False):
     os.makedirs(build_dir, exist_ok=True)
     sources = {
         "gemm_performance_kernel.inc": "kernels/manual/a2a3/gemm_performance/gemm_performance_kernel.cpp",
+        "pto_macro_matmul.inc": "kernels/manual/common/flash_atten/pto_macro_matmul.hpp",
     }
     for name, rel in sources.items():
         with open(os.path.join(reference, rel)) as f:
-            text = rewrite_launches(f.read())
+            text = rewrite_core_statics(rewrite_launches(f.read()))
         with open(os.path.join(build_dir, name), "w") as f:
             f.write(text)
     tu = os.path.join(build_dir, "wrappers.cu")
@@ -72,7 +99,7 @@ def build(reference="/root/reference", force=False, verbose=False):
     with open(tu, "w") as f:
         f.write(body)
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--extended-lambda",
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++20", "--extended-lambda", "--expt-relaxed-constexpr",
            "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", build_dir, "-shared", "-o", OUT, tu]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]

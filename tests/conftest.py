@@ -15,3 +15,16 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def golden_dir():
     return os.path.join(ROOT, "tests", "golden")
+
+
+def pytest_terminal_summary(terminalreporter):
+    """Worst measured error of every labelled parity check, against its bar (tests/util.py: PARITY_LOG)."""
+    try:
+        import util
+    except ImportError:
+        return
+    if not util.PARITY_LOG:
+        return
+    terminalreporter.write_line("parity margins (worst relative error / bar):")
+    for label, worst, tol in util.PARITY_LOG:
+        terminalreporter.write_line(f"  {label}: {worst:.2e} / {tol:.0e}")

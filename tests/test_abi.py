@@ -49,7 +49,7 @@ def test_python_signature_table_matches_header(built_lib):
     assert sorted(_lib.SIGNATURES) == header_symbols()
     import re
     header = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "pto_b200.h")).read()
-    assert _lib.lib().pto_b200_version() == int(re.search(r"#define PTO_B200_ABI_VERSION (\d+)", header).group(1)) == 3
+    assert _lib.lib().pto_b200_version() == int(re.search(r"#define PTO_B200_ABI_VERSION (\d+)", header).group(1)) == 4
 
 
 def test_call_kernel_shims_export_the_reference_symbol(built_lib):

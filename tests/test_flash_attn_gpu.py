@@ -1,10 +1,10 @@
 """GPU parity of flash-attention forward against the CPU oracle (the reference's instruction sequence with
 fp16 operands, fp32 softmax, fp16 P) and the golden output of the reference's NumPy model of its kernel.
 
-Tolerance (util.attn_err_ok): relative error |got - want| / max(|want|, rms(want)) <= 2e-3 for at least
-99.99 % of the elements and <= 5e-3 for every element; the few elements between the two bounds come from
-fp16 rounding flips of P in rows that see only a handful of keys.  A half-precision output is compared
-with fp16(oracle O)."""
+Tolerance (util.attn_err_ok): relative error |got - want| / max(|want|, rms(want)) <= 2e-3 for EVERY element.
+A half-precision output must be the round-to-nearest-even of the fp32 output bit for bit; where only the
+half-precision output exists it is compared with the oracle's fp32 output with half an fp16 ulp added for
+that rounding.  Every test prints its worst error (pytest -s, or the captured output of a failure)."""
 import os
 
 import numpy as np
@@ -39,7 +39,7 @@ def test_attention_matches_oracle(shape, causal):
     assert pto.device_status() == 0
     for h in range(bh):
         want = port.attn_head_f16(q[h], k[h], v[h], int(causal), scale)
-        ok, worst, _ = attn_err_ok(o[h], want)
+        ok, worst, _ = attn_err_ok(o[h], want, label=f"{shape} causal={causal} head {h}")
         assert ok, f"head {h}: max relative error {worst:.3e}"
 
 
@@ -56,9 +56,9 @@ def test_attention_internal_scale_and_fp16_output(causal):
     assert np.array_equal(o16, o32.astype(np.float16))  # same kernel, output rounded to nearest even on store
     for h in range(bh):
         want = port.attn_head_f16(q[h], k[h], v[h], int(causal), scale)
-        ok, worst, _ = attn_err_ok(o32[h], want)
+        ok, worst, _ = attn_err_ok(o32[h], want, label=f"internal scale causal={causal} head {h}")
         assert ok, f"head {h}: max relative error {worst:.3e}"
-        ok, worst, _ = attn_err_ok(o16[h].astype(np.float32), want.astype(np.float16).astype(np.float32), tol=3e-3)
+        ok, worst, _ = attn_err_ok(o16[h].astype(np.float32), want, half_output=True)
         assert ok, f"head {h} (fp16 out): max relative error {worst:.3e}"
 
 
@@ -70,7 +70,7 @@ def test_attention_golden(golden_dir):
         o = host(pto.flash_attn_fwd(dev(q[None]), dev(k[None]), dev(v[None]), causal=causal,
                                     out_dtype=torch.float32))[0]
         assert result_cmp(g, o, 1e-3), name
-        ok, worst, _ = attn_err_ok(o, g)
+        ok, worst, _ = attn_err_ok(o, g, label=name)
         assert ok, f"{name}: max relative error {worst:.3e}"
 
 
@@ -87,7 +87,7 @@ def test_attention_large_logits_rescale_path():
     for causal in (False, True):
         o = host(pto.flash_attn_fwd(dev(q), dev(k), dev(v), causal=causal, out_dtype=torch.float32))
         want = port.attn_head_f16(q[0], k[0], v[0], int(causal), scale)
-        ok, worst, _ = attn_err_ok(o[0], want)
+        ok, worst, _ = attn_err_ok(o[0], want, label=f"growing maxima causal={causal}")
         assert ok, f"causal={causal}: max relative error {worst:.3e}"
 
 
@@ -114,7 +114,8 @@ def test_attention_full_size_sampled_heads(causal):
     assert pto.device_status() == 0
     for h in (0, 77, 127):
         want = port.attn_head_f16(host(q[h]), host(k[h]), host(v[h]), int(causal), 1.0)
-        ok, worst, _ = attn_err_ok(host(o[h]).astype(np.float32), want.astype(np.float16).astype(np.float32), tol=3e-3)
+        ok, worst, _ = attn_err_ok(host(o[h]).astype(np.float32), want, half_output=True,
+                                   label=f"B4 H32 S4096 causal={causal} head {h}")
         assert ok, f"head {h}: max relative error {worst:.3e}"
     if causal:
         vmax = torch.cummax(v.float(), dim=1).values
@@ -141,7 +142,7 @@ def test_attention_long_sequence_causal_sampled_rows():
     for h in (0, 5):
         # first 256 queries: a square causal problem of its own
         want = port.attn_head_f16(host(q[h, :256]), host(k[h, :256]), host(v[h, :256]), 1, 1.0)
-        ok, worst, _ = attn_err_ok(host(o[h, :256]), want)
+        ok, worst, _ = attn_err_ok(host(o[h, :256]), want, label=f"S8192 head {h} first 256 rows")
         assert ok, f"head {h} first rows: max relative error {worst:.3e}"
         # last 128 queries against all keys: row i of the block may see keys 0 .. s - 128 + i; the oracle's causal mask
         # works on square problems, so every row is checked as the last row of the problem made of keys 0 .. its own
@@ -149,5 +150,6 @@ def test_attention_long_sequence_causal_sampled_rows():
             qi = host(q[h, row:row + 1]).repeat(128, axis=0)  # 128 copies: the oracle's tile height
             want_row = port.attn_head_f16(qi, host(k[h, :row + 1]), host(v[h, :row + 1]), 0, 1.0)[0]
             got_row = host(o[h, row])
-            assert np.abs(got_row - want_row).max() <= 3e-3 * max(np.abs(want_row).max(), 1e-3), (h, row)
+            ok, worst, _ = attn_err_ok(got_row, want_row, label=f"S8192 head {h} row {row}")
+            assert ok, f"head {h} row {row}: max relative error {worst:.3e}"
     assert bool(torch.isfinite(o).all())

@@ -33,7 +33,7 @@ def test_gemm_matches_oracle(mnk, b_layout):
     a, b = make(m, n, k, b_layout, seed=0)
     want = port.gemm_f16f32(a, b, b_layout)
     got = host(pto.gemm(dev(a), dev(b), b_layout))
-    ok, worst = rel_err_ok(got, want, 2e-3)
+    ok, worst = rel_err_ok(got, want, 2e-3, label=f"gemm {m}x{n}x{k} b_layout={b_layout}")
     assert ok, f"max relative error {worst:.3e}"
     assert result_cmp(want, got, 1e-3)
     assert pto.device_status() == 0

@@ -44,7 +44,7 @@ def test_reference_gemm_tile_program(refk, name, m, k, n):
     b = r.uniform(-1, 1, (n, k)).astype(np.float16)
     da, db = dev(a), dev(b)
     c = torch.full((m, n), float("nan"), device="cuda")
-    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
     assert getattr(refk, name)(_ptr(c), _ptr(da), _ptr(db), _stream(), _ptr(status)) == 0
     assert refk.pto_refk_status(_stream(), _ptr(status)) == 0
     want = port.gemm_f16f32(a, b, 1)
@@ -59,7 +59,7 @@ def test_reference_gemm_tile_program_6144(refk):
     a = (torch.rand(m, k, device="cuda", generator=g) * 2 - 1).half()
     b = (torch.rand(n, k, device="cuda", generator=g) * 2 - 1).half()
     c = torch.full((m, n), float("nan"), device="cuda")
-    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
     assert refk.pto_refk_gemm_6144(_ptr(c), _ptr(a), _ptr(b), _stream(), _ptr(status)) == 0
     assert refk.pto_refk_status(_stream(), _ptr(status)) == 0
     # against the hand-written kernel (itself checked against the oracle): same tensor-core arithmetic

@@ -3,6 +3,11 @@ import numpy as np
 import torch
 
 
+# (label, worst relative error, bar) of every labelled parity check of this run; tests/conftest.py prints the list in
+# pytest's terminal summary, so that the margins are in the log of a passing run too
+PARITY_LOG = []
+
+
 def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
@@ -11,7 +16,7 @@ def host(t):
     return t.detach().cpu().numpy()
 
 
-def rel_err_ok(actual, expected, tol=2e-3):
+def rel_err_ok(actual, expected, tol=2e-3, label=None):
     """Max relative error with a denominator floor: |a - e| <= tol * max(|e|, rms(e)) everywhere.
     The floor keeps outputs that cancel to ~0 from dominating; it is stated with every use."""
     a = np.asarray(actual, np.float64)
@@ -20,6 +25,8 @@ def rel_err_ok(actual, expected, tol=2e-3):
     bound = tol * np.maximum(np.abs(e), floor)
     diff = np.abs(a - e)
     worst = float((diff / np.maximum(np.abs(e), floor)).max())
+    if label is not None:
+        PARITY_LOG.append((label, worst, tol))
     return bool((diff <= bound).all()), worst
 
 
@@ -34,19 +41,31 @@ def result_cmp(golden, actual, eps):
     return int(bad.sum()) <= g.size * eps
 
 
-def attn_err_ok(actual, expected, tol=2e-3, hard=5e-3, quantile_ok=0.9999):
-    """Attention tolerance.  The relative error of an element is |a - e| / max(|e|, rms(e)).
+def attn_err_ok(actual, expected, tol=2e-3, half_output=False, label=None):
+    """Attention tolerance: every element within `tol` (2e-3, the bar this backend is held to) of the oracle, the
+    relative error of an element being |a - e| / max(|e|, rms(e)).
 
-    P is rounded to fp16 before the second product, by the oracle as well as by the kernel.  The kernel's
-    logits come from a tensor-core sum in a different order and its exponentials from ex2.approx, so about
-    0.2 % of the P values fall on the other side of an fp16 rounding boundary (one fp16 ulp, 2^-10 relative).
-    In rows that see only a few keys a single such flip moves an output by more than 2e-3 of its own size.
-    The bar is therefore: at least 99.99 % of the elements within `tol`, every element within `hard`.
-    The reference's own streaming formulation differs from its plain one by the same mechanism."""
+    What the measured error consists of: the oracle and the kernel both round P to fp16 before the second product,
+    but relative to different row maxima (the kernel's running maximum at that key tile, the oracle's maximum of the
+    whole row), so the two roundings are independent: each output carries the difference of two sums of fp16
+    rounding errors, about 4e-4 of its size (rms), 1.3e-3 to 1.5e-3 at the worst element of a head.
+    The reference's own streaming formulation differs from its plain one by the same mechanism.
+
+    `half_output`: `actual` is the kernel's output after its own rounding to fp16 (tested separately to be the
+    round-to-nearest-even of its fp32 output) and `expected` the oracle's unrounded fp32 output; half an fp16 ulp of
+    the value (2^-11 of it, 2^-25 absolute below the normal range) is allowed on top for that rounding.
+    Returns (ok, worst relative error, fraction of elements within tol); prints the worst error when given a label."""
     a = np.asarray(actual, np.float64)
     e = np.asarray(expected, np.float64)
     floor = np.sqrt(np.mean(e * e))
-    rel = np.abs(a - e) / np.maximum(np.abs(e), floor)
-    frac_ok = float((rel <= tol).mean())
+    den = np.maximum(np.abs(e), floor)
+    diff = np.abs(a - e)
+    if half_output:
+        diff = np.maximum(diff - np.maximum(np.abs(a) * 2.0 ** -11, 2.0 ** -25), 0.0)
+    rel = diff / den
     worst = float(rel.max())
-    return bool(frac_ok >= quantile_ok and worst <= hard), worst, frac_ok
+    frac_ok = float((rel <= tol).mean())
+    if label is not None:
+        PARITY_LOG.append((label, worst, tol))
+        print(f"attention parity {label}: worst relative error {worst:.3e} (bar {tol:.0e}), rms of the oracle {floor:.3f}")
+    return bool(worst <= tol), worst, frac_ok
