@@ -4,12 +4,13 @@ flash-attention forward and the vector tile ops measured in the same run as extr
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-A step is one pass over one batch of independent problems: PROBLEMS_PER_RANK (8) GEMMs of 6144^3 per
-GPU, each with its own A, B and C (the batch's inputs, 1.2 GB, exceed the 126 MB L2, so operands come
-from HBM every time).  At 8 GPUs that is the 64-problem configuration; work per GPU is fixed (weak
-scaling) and no collective is on the data path; the all-gather of the outputs is timed separately and
-reported as `with_allgather`.  Under torchrun every rank runs its own problems; the time of the timed
-region is the maximum over ranks.
+A step is REPEATS (20) passes over one batch of independent problems: PROBLEMS_PER_RANK (8) GEMMs of
+6144^3 per GPU, each with its own A, B and C (the batch's inputs, 1.2 GB, exceed the 126 MB L2, so operands
+come from HBM every time): 160 launches, about 56 ms, so that 20 steps fill more than a second, the
+regime of the measured sustained peak, with hundreds of clock samples.  At 8 GPUs the batch is the
+64-problem configuration; work per GPU is fixed (weak scaling) and no collective is on the data path; the
+all-gather of the outputs is measured both after the step and overlapped with it (`with_allgather`).
+Under torchrun every rank runs its own problems; the time of the timed region is the maximum over ranks.
 
 One JSON line is printed by rank 0.  `value` is whole-job TFLOP/s with operands resident in HBM;
 `e2e` is the same metric through the C ABI's host-buffer entry point (pinned host operands, copies in
@@ -34,6 +35,7 @@ if ROOT not in sys.path:
 
 M = N = K = 6144
 PROBLEMS_PER_RANK = 8
+REPEATS = 20  # passes over the batch per step
 FLOPS_PER_PROBLEM = 2.0 * M * N * K
 TILE_M, TILE_N = 128, 256
 TILE_FLOPS = 2.0 * TILE_M * TILE_N * K
@@ -232,28 +234,91 @@ def run_reference_arm(args):
 
 # ------------------------------------------------------------------ GPU arm
 
-def timed_events(torch, fn, iters):
-    """Per-launch durations (ms) with CUDA events on the current (launching) stream."""
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
-    for s, e in evs:
-        s.record()
+def bench_loop(torch, fn, warm, iters):
+    """Average duration (ms) of `fn` over `iters` calls, CUDA events on the launching stream, after `warm` calls."""
+    for _ in range(warm):
         fn()
-        e.record()
     torch.cuda.synchronize()
-    return [s.elapsed_time(e) for s, e in evs]
+    s = torch.cuda.Event(enable_timing=True)
+    e = torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters
 
 
-def sharded_attention(torch, pto, dist, world, rank, barrier, iters=3):
+def stamps_summary(torch, stamps, blocks):
+    """Per-block profile stamps (pto_b200_set_profile_buffer) of the last launch reduced as the reference's host does
+    (kernels/manual/common/flash_atten/main.cpp:616-660): earliest start, latest end, and the clock the blocks ran at."""
+    st = stamps[:blocks].cpu()
+    t0, t1, c0, c1 = st[:, 0], st[:, 1], st[:, 2], st[:, 3]
+    ok = (t1 > t0) & (c1 > c0)
+    if not bool(ok.any()):
+        return None
+    dur_ns = (t1 - t0)[ok].double()
+    mhz = ((c1 - c0)[ok].double() / dur_ns * 1e3)
+    return {"blocks": int(ok.sum()), "kernel_us": float((t1[ok].max() - t0[ok].min()).item()) / 1e3,
+            "block_us_median": float(dur_ns.median().item()) / 1e3,
+            "sm_mhz_median": float(mhz.median().item()), "sm_mhz_min": float(mhz.min().item()),
+            "source": "clock64 / %globaltimer per block (pto_b200_set_profile_buffer)"}
+
+
+def cpu_vector_and_attention_baselines():
+    """The reference's CPU simulation (its own build when present, else the port) on the vector configs and on one
+    attention head, timed on this box's host cores; bounded (a few seconds each)."""
+    import numpy as np
+
+    import oracle
+    lib = oracle.ref if oracle.ref is not None else oracle.port
+    kind = "reference" if oracle.ref is not None else "port"
+    r = np.random.default_rng(1)
+    n = 1 << 24
+    x = r.standard_normal(n).astype(np.float32)
+    out = {}
+    t0 = time.perf_counter()
+    lib.tcvt_f32_f16(x)
+    dt = time.perf_counter() - t0
+    out["tcvt_f16"] = {"value": 6.0 * n / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": kind,
+                       "sample": f"TCVT f32->f16, 16M elements, {dt:.2f} s (the simulation's TCVT loop is single-threaded)"}
+    idx = r.integers(0, n, n).astype(np.int32)
+    src = x.reshape(4096, 4096)
+    t0 = time.perf_counter()
+    lib.tgather(src, idx)
+    dt = time.perf_counter() - t0
+    out["tgather"] = {"value": 12.0 * n / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": kind,
+                      "sample": f"TGATHER f32 by int32 index, 16M of 16M, {dt:.2f} s (single-threaded loop)"}
+    S, D = 2048, 128
+    q = (r.standard_normal((S, D)) / np.sqrt(D)).astype(np.float16)
+    k = r.standard_normal((S, D)).astype(np.float16)
+    v = r.standard_normal((S, D)).astype(np.float16)
+    t0 = time.perf_counter()
+    lib.attn_head_f16(q, k, v, 0, 1.0)
+    dt = time.perf_counter() - t0
+    try:
+        cores = int(lib.lib.pto_ref_hardware_threads() if kind == "reference" else lib.lib.pto_oracle_threads())
+    except Exception:
+        cores = os.cpu_count() or 1
+    out["attention"] = {"value": 4.0 * S * S * D / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": kind,
+                        "sample": f"one head, S=2048, D=128, non-causal, the simulation's instruction sequence, {dt:.2f} s"}
+    return out
+
+
+def sharded_attention(torch, pto, dist, world, rank, barrier, iters=20):
     from pto_isa_b200 import shard
     heads, S, D = 32 * 32, 8192, 128
     b, e = shard.unit_range(heads, world, rank)
     mine = e - b
+    # at one GPU the whole configuration (12.9 GB of Q, K, V, O) is run in four passes over a quarter of the heads
+    passes = 4 if world == 1 else 1
+    chunk = mine // passes
     g = torch.Generator(device="cuda").manual_seed(900 + rank)
-    q = (torch.randn(mine, S, D, device="cuda", generator=g) / D ** 0.5).half()
-    k = torch.randn(mine, S, D, device="cuda", generator=g).half()
-    v = torch.randn(mine, S, D, device="cuda", generator=g).half()
+    q = (torch.randn(chunk, S, D, device="cuda", generator=g) / D ** 0.5).half()
+    k = torch.randn(chunk, S, D, device="cuda", generator=g).half()
+    v = torch.randn(chunk, S, D, device="cuda", generator=g).half()
     o = torch.empty_like(q)
-    for _ in range(2):
+    for _ in range(3):
         pto.flash_attn_fwd(q, k, v, causal=True, scale=1.0, out=o)
     barrier()
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -262,50 +327,71 @@ def sharded_attention(torch, pto, dist, world, rank, barrier, iters=3):
         pto.flash_attn_fwd(q, k, v, causal=True, scale=1.0, out=o)
     s1.record()
     barrier()
-    t = torch.tensor([s0.elapsed_time(s1) / iters], device="cuda", dtype=torch.float64)
+    t = torch.tensor([s0.elapsed_time(s1) / iters * passes], device="cuda", dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     flops = 4.0 * heads * D * S * (S + 1) / 2
     res = {"workload": "flash_attn_fwd f16 batch 32 x 32 heads, S=8192, D=128, causal, fp16 O; heads sharded",
            "value": flops / ms / 1e9, "unit": "TFLOP/s", "ms": ms, "scaling": "strong", "heads_per_gpu": mine,
-           "n_gpus": world, "gpu_launches": iters}
+           "n_gpus": world, "gpu_launches": iters, "timed_launches": iters,
+           "note": "one GPU: the time of four passes over 256 heads each" if passes > 1 else None}
     if dist is not None:
-        full = shard.all_gather_units(o, heads)  # warm-up
-        barrier()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
-        full = shard.all_gather_units(o, heads)
-        g1.record()
-        barrier()
-        tg = torch.tensor([g0.elapsed_time(g1)], device="cuda", dtype=torch.float64)
-        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
-        ag = float(tg.item())
+        gathers = []
+        for i in range(6):  # the first one is the warm-up
+            barrier()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record()
+            full = shard.all_gather_units(o, heads)
+            g1.record()
+            barrier()
+            tg = torch.tensor([g0.elapsed_time(g1)], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+            if i > 0:
+                gathers.append(float(tg.item()))
+            nbytes = int(full.numel() * 2)
+            del full
+        ag = statistics.median(gathers)
         res["allgather_ms"] = ag
-        res["bytes_gathered_per_gpu"] = int(full.numel() * 2)
+        res["allgather_ms_all"] = gathers
+        res["bytes_gathered_per_gpu"] = nbytes
+        res["allgather_recv_gbs_per_gpu"] = nbytes * (world - 1) / world / ag / 1e6
         res["value_with_allgather"] = flops / (ms + ag) / 1e9
-        del full
     del q, k, v, o
     torch.cuda.empty_cache()
     return res
 
 
+def gemm_size_sweep(torch, pto, peaks):
+    """Throughput of the other square sizes of the configurations (1536, 3072, 7680), operand sets rotated so that
+    they come from HBM; 20 launches each after 5 warm-up launches."""
+    out = []
+    g = torch.Generator(device="cuda").manual_seed(7)
+    for size, sets in ((1536, 10), (3072, 4), (7680, 2)):
+        a = [(torch.rand(size, size, device="cuda", generator=g) * 2 - 1).half() for _ in range(sets)]
+        b = [(torch.rand(size, size, device="cuda", generator=g) * 2 - 1).half() for _ in range(sets)]
+        c = [torch.empty(size, size, device="cuda") for _ in range(sets)]
+        i = [0]
+
+        def fn():
+            j = i[0] % sets
+            i[0] += 1
+            pto.gemm(a[j], b[j], 1, out=c[j])
+
+        ms = bench_loop(torch, fn, 5, 20)
+        tf = 2.0 * size ** 3 / ms / 1e9
+        out.append({"workload": f"gemm_f16f32 m=n=k={size}, B stored n x k", "value": tf, "unit": "TFLOP/s", "ms": ms,
+                    "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                 "frac": tf / peaks["bf16_tflops"], "frac_of_nominal_2250": tf / 2250.0,
+                                 "note": f"{sets} rotating operand sets, 20 launches"}})
+        del a, b, c
+    return out
+
+
 def extras(torch, pto, peaks, peak_kind):
     """Attention and vector tile ops, rank 0 only, short.  Buffers are rotated so inputs come from HBM."""
     out = []
-
-    def bench(fn, warm, iters):
-        for _ in range(warm):
-            fn()
-        torch.cuda.synchronize()
-        s = torch.cuda.Event(enable_timing=True)
-        e = torch.cuda.Event(enable_timing=True)
-        s.record()
-        for _ in range(iters):
-            fn()
-        e.record()
-        torch.cuda.synchronize()
-        return s.elapsed_time(e) / iters
+    bench = lambda fn, warm, iters: bench_loop(torch, fn, warm, iters)
 
     g = torch.Generator(device="cuda").manual_seed(5)
     B, H, S, D = 4, 32, 4096, 128
@@ -313,16 +399,38 @@ def extras(torch, pto, peaks, peak_kind):
     k = torch.randn(B * H, S, D, device="cuda", generator=g).half()
     v = torch.randn(B * H, S, D, device="cuda", generator=g).half()
     o = torch.empty_like(q)
+    q4, k4, v4 = (t.view(B, H, S, D) for t in (q, k, v))
+    stamps = torch.zeros(4096, 4, dtype=torch.int64, device="cuda")
     for causal in (False, True):
         ms = bench(lambda: pto.flash_attn_fwd(q, k, v, causal=causal, scale=1.0, out=o), 3, 10)
         flops = 4.0 * B * H * S * S * D if not causal else 4.0 * B * H * D * S * (S + 1) / 2
         tf = flops / ms / 1e9
-        out.append({"workload": f"flash_attn_fwd f16 B=4 H=32 S=4096 D=128 causal={causal}", "value": tf,
-                    "unit": "TFLOP/s", "ms": ms,
-                    "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                                 "frac": tf / peaks["bf16_tflops"], "peak_kind": peak_kind + " burst",
-                                 "frac_of_nominal_2250": tf / 2250.0}})
-    del q, k, v, o
+        # sustained: launches back to back for about a second
+        n_long = max(20, int(1000.0 / ms))
+        ms_long = bench(lambda: pto.flash_attn_fwd(q, k, v, causal=causal, scale=1.0, out=o), 0, n_long)
+        pto.set_profile_buffer(stamps)
+        pto.flash_attn_fwd(q, k, v, causal=causal, scale=1.0, out=o)
+        torch.cuda.synchronize()
+        pto.set_profile_buffer(None)
+        prof = stamps_summary(torch, stamps, B * H * (S // 256))
+        row = {"workload": f"flash_attn_fwd f16 B=4 H=32 S=4096 D=128 causal={causal}", "value": tf,
+               "unit": "TFLOP/s", "ms": ms, "sustained_tflops": flops / ms_long / 1e9, "sustained_launches": n_long,
+               "block_stamps": prof,
+               "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                            "frac": tf / peaks["bf16_tflops"], "peak_kind": peak_kind + " burst",
+                            "frac_of_nominal_2250": tf / 2250.0}}
+        # the vendor library's attention on the same box and inputs (torch SDPA): a denominator measured live
+        try:
+            import torch.nn.functional as F
+            lib_ms = bench(lambda: F.scaled_dot_product_attention(q4, k4, v4, is_causal=causal, scale=1.0), 3, 10)
+            row["roofline"]["library_sdpa_tflops"] = flops / lib_ms / 1e9
+            row["roofline"]["frac_of_library"] = tf / row["roofline"]["library_sdpa_tflops"]
+        except Exception as exc:
+            row["roofline"]["library_sdpa_tflops"] = None
+            row["roofline"]["library_note"] = str(exc)[:120]
+        out.append(row)
+    del q, k, v, o, q4, k4, v4
+    out.extend(gemm_size_sweep(torch, pto, peaks))
     # MX block-scaled fp8 GEMM at the reference's MxMatmul configuration (6144^3, float8_e5m2 operands, e8m0 scales per
     # 32 k, bfloat16 output); four operand sets in rotation (4 x 75 MB of fp8 > L2); scale packing is inside the timing
     mm = 6144
@@ -344,10 +452,10 @@ def extras(torch, pto, peaks, peak_kind):
     out.append({"workload": "MX fp8 GEMM (e5m2 x e5m2, e8m0 scales per 32 k, bf16 out) 6144^3", "value": tf,
                 "unit": "TFLOP/s", "ms": ms,
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": 4500.0, "unit": "TFLOP/s", "frac": tf / 4500.0,
-                             "peak_kind": "nominal dense fp8 (no fp8 peak was measured on this pool)",
+                             "peak_kind": "nominal dense fp8 (no fp8 peak was measured for this GPU)",
                              "vs_measured_bf16_burst": tf / peaks["bf16_tflops"]}})
-    # the vendor library's MXFP8 GEMM on the same box and operand bits (cuBLASLt through torch._scaled_mm, e4m3, unit scales):
-    # a denominator measured live, in the role MEASURED_PEAKS.json's cuBLAS figure plays for the fp16 GEMM
+    # the vendor library's MXFP8 GEMM on the same box and operand bits (cuBLASLt through torch._scaled_mm, e4m3, unit
+    # scales): a denominator measured live, in the role the measured cuBLAS figure plays for the fp16 GEMM
     try:
         ones = torch.full((mm, mm // 32), 127, device="cuda", dtype=torch.uint8).view(torch.float8_e8m0fnu)
         la = [x.view(torch.float8_e4m3fn) for x in mxa]
@@ -379,7 +487,7 @@ def extras(torch, pto, peaks, peak_kind):
     out.append({"workload": "MX fp4 GEMM (packed e2m1, e8m0 scales per 32 k, bf16 out) 6144^3", "value": tf,
                 "unit": "TFLOP/s", "ms": ms,
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": 9000.0, "unit": "TFLOP/s", "frac": tf / 9000.0,
-                             "peak_kind": "nominal dense fp4 (no fp4 peak was measured on this pool)",
+                             "peak_kind": "nominal dense fp4 (no fp4 peak was measured for this GPU)",
                              "vs_measured_bf16_burst": tf / peaks["bf16_tflops"]}})
     # TMATMUL's (int8, int8 -> int32) form at the same size: kind::i8 on the CTA-pair GEMM kernel
     ia = [x.view(torch.int8) for x in mxa]
@@ -395,7 +503,7 @@ def extras(torch, pto, peaks, peak_kind):
     tf = 2.0 * mm ** 3 / ms / 1e9
     out.append({"workload": "int8 GEMM (int32 accumulate and output) 6144^3", "value": tf, "unit": "TOP/s", "ms": ms,
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": 4500.0, "unit": "TOP/s", "frac": tf / 4500.0,
-                             "peak_kind": "nominal dense int8 (no int8 peak was measured on this pool)",
+                             "peak_kind": "nominal dense int8 (no int8 peak was measured for this GPU)",
                              "vs_measured_bf16_burst": tf / peaks["bf16_tflops"]}})
     del mxa, mxb, mxsa, mxsb, mxc, fa, fb, ia, ib, ic
     n = 1 << 24
@@ -439,6 +547,7 @@ def extras(torch, pto, peaks, peak_kind):
         ("TFILLPAD f32 4096x4096, valid 3000x3000", 4.0 * (3000 * 3000 / n) + 4.0,
          rot(lambda j: pto.TFILLPAD(x2[j], 3000, 3000, 3, out=o2[j]))),
     ]
+
     def bench_graph(fn, warm, iters):
         """The same loop captured once in a CUDA graph: these kernels run 13-30 us, less than the host needs for one
         call through the Python layer, so an eager loop would time the host."""
@@ -466,7 +575,58 @@ def extras(torch, pto, peaks, peak_kind):
                     "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                  "frac": gbs / peaks["hbm_gbs"], "peak_kind": peak_kind,
                                  "note": f"{sets} rotating buffer sets (> L2), {5 * sets} launches replayed from one CUDA graph"}})
+    # what bounds TGATHER beside its two streams: this GPU's rate of random 32-byte sectors out of a table of the same
+    # size, measured with no index and no output stream (pto_b200_probe_random_reads)
+    try:
+        probe_ms = bench_graph(lambda: pto.probe_random_reads(xs[0], n), 2, 10)
+        gather = next(r for r in out if r["workload"].startswith("TGATHER"))
+        gather["roofline"]["random_read_ceiling"] = {
+            "reads": n, "table_mib": 64, "us": probe_ms * 1e3, "greads_per_s": n / probe_ms / 1e6,
+            "sector_gbs": n * 32 / probe_ms / 1e6,
+            "note": "16M random 4-byte reads of the 64 MiB table alone; TGATHER does these plus 128 MB of index and output"}
+        gather["roofline"]["frac_of_random_read_ceiling"] = probe_ms / gather["ms"]
+    except Exception as exc:
+        out[-1]["roofline"]["probe_note"] = str(exc)[:120]
     return out
+
+
+def compact_summary(line):
+    """The headline figures of all three parts of the metric in a few hundred characters, placed last in the line."""
+    r3 = lambda x: None if x is None else round(float(x), 3)
+    r0 = lambda x: None if x is None else round(float(x), 1)
+    sm = {"gemm6144_tflops": r0(line["roofline"]["achieved"]), "gemm_frac_sustained": r3(line["roofline"]["frac"]),
+          "gemm_frac_burst_isolated": r3(line["roofline"].get("isolated_frac_of_burst")),
+          "e2e_tflops": r0(line["e2e"]["value"])}
+    sa = line.get("sharded_attention") or {}
+    sm["attn_sharded_tflops"] = r0(sa.get("value"))
+    if sa.get("value_with_allgather") is not None:
+        sm["attn_sharded_with_allgather"] = r0(sa["value_with_allgather"])
+    wa = line.get("with_allgather")
+    if wa:
+        sm["gemm_with_allgather_tflops"] = r0(wa["value"])
+        sm["gemm_overlapped_allgather_tflops"] = r0(wa.get("value_overlapped"))
+        sm["allgather_ms"] = r3(wa["allgather_ms_per_step"])
+    for row in line.get("extras") or []:
+        w = row["workload"]
+        key = None
+        if w.startswith("flash_attn_fwd"):
+            key = "fa_causal" if "causal=True" in w else "fa_nc"
+        elif w.startswith("TCVT f32->f16"):
+            key = "tcvt_f16"
+        elif w.startswith("TCVT f32->bf16"):
+            key = "tcvt_bf16"
+        elif w.startswith("TGATHER"):
+            key = "tgather"
+        elif w.startswith("gemm_f16f32 m=n=k="):
+            key = "gemm" + w.split("=")[3].split(",")[0]
+        if key:
+            sm[key] = [r0(row["value"]), r3(row["roofline"]["frac"])]
+            if key.startswith("fa_") and row["roofline"].get("frac_of_library") is not None:
+                sm[key].append(r3(row["roofline"]["frac_of_library"]))
+            if key == "tgather" and row["roofline"].get("frac_of_random_read_ceiling") is not None:
+                sm[key].append(r3(row["roofline"]["frac_of_random_read_ceiling"]))
+    sm["legend"] = "[value, frac of measured peak(, frac of vendor library | of random-read ceiling)]"
+    return sm
 
 
 def run_gpu_arm(args):
@@ -501,12 +661,12 @@ def run_gpu_arm(args):
     peaks, peak_kind = load_peaks()
 
     g = torch.Generator(device="cuda").manual_seed(100 + rank)
-    P = PROBLEMS_PER_RANK
+    P, R = PROBLEMS_PER_RANK, REPEATS
     a = [(torch.rand(M, K, device="cuda", generator=g) * 2 - 1).half() for _ in range(P)]
     b = [(torch.rand(N, K, device="cuda", generator=g) * 2 - 1).half() for _ in range(P)]  # n x k (Layout::DN)
     c = torch.empty(P, M, N, device="cuda")
 
-    def step():
+    def one_pass():
         for i in range(P):
             pto.gemm(a[i], b[i], 1, out=c[i])
 
@@ -515,8 +675,15 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # ---- 10 launches timed alone after a pause: the burst regime (against the measured burst peak)
+    one_pass()
+    barrier()
+    time.sleep(1.0)
+    iso_ms = bench_loop(torch, lambda: pto.gemm(a[0], b[0], 1, out=c[0]), 0, 10)
+
     for _ in range(max(args.warmup, 3)):
-        step()
+        for _ in range(R):
+            one_pass()
     barrier()
     gpu_uuid = None
     try:
@@ -526,23 +693,24 @@ def run_gpu_arm(args):
     sampler = ClockSampler(local_rank, gpu_uuid) if rank == 0 else None
     if sampler:
         sampler.start()
-    launch_ms = []
+    stamps = torch.zeros(256, 4, dtype=torch.int64, device="cuda")
+    pto.set_profile_buffer(stamps)  # the last launch of the timed region leaves its per-block stamps here
+    pass_events = []
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     ev0.record()
     for _ in range(args.steps):
-        # per-launch events on the launching stream: the roofline's kernel duration comes from these
-        evs = []
-        for i in range(P):
+        for _ in range(R):
+            # events around every pass of P launches on the launching stream: the roofline's kernel duration
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
-            pto.gemm(a[i], b[i], 1, out=c[i])
+            one_pass()
             e.record()
-            evs.append((s, e))
-        launch_ms.append(evs)
+            pass_events.append((s, e))
     ev1.record()
     barrier()
     clocks = sampler.stop() if sampler else None
+    pto.set_profile_buffer(None)
     elapsed_ms = ev0.elapsed_time(ev1)
     if pto.device_status() != 0:
         raise SystemExit("a kernel reported a device-side wait timeout")
@@ -550,37 +718,80 @@ def run_gpu_arm(args):
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     elapsed_ms = float(t.item())
-    total_flops = world * args.steps * P * FLOPS_PER_PROBLEM
+    launches = args.steps * R * P
+    total_flops = world * launches * FLOPS_PER_PROBLEM
     value = total_flops / elapsed_ms / 1e9
-    per_launch = [s.elapsed_time(e) for evs in launch_ms for s, e in evs]
-    avg_launch_ms = sum(per_launch) / len(per_launch)
+    per_pass = [s.elapsed_time(e) for s, e in pass_events]
+    avg_launch_ms = sum(per_pass) / len(per_pass) / P
+    block_stamps = stamps_summary(torch, stamps, 2 * (torch.cuda.get_device_properties(local_rank).multi_processor_count // 2))
 
-    # all-gather of the outputs (every GPU ends up with every C), timed separately
+    # all-gather of the outputs (every GPU ends up with every C): after the pass, and overlapped with it
     with_allgather = None
     if dist is not None:
         full = torch.empty(world * P, M, N, device="cuda")
-        dist.all_gather_into_tensor(full, c)  # warm-up (communicator set-up)
-        barrier()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
-        dist.all_gather_into_tensor(full, c)
-        g1.record()
-        barrier()
-        tg = torch.tensor([g0.elapsed_time(g1)], device="cuda", dtype=torch.float64)
-        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
-        ag_ms = float(tg.item())
-        step_ms = elapsed_ms / args.steps
-        with_allgather = {"allgather_ms_per_step": ag_ms, "bytes_gathered_per_gpu": int(world * P * M * N * 4),
-                          "value": world * P * FLOPS_PER_PROBLEM / (step_ms + ag_ms) / 1e9, "unit": "TFLOP/s"}
-        del full
+        pass_ms = elapsed_ms / (args.steps * R)
+        gathers = []
+        for i in range(6):  # the first one is the warm-up (communicator set-up)
+            barrier()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record()
+            dist.all_gather_into_tensor(full, c)
+            g1.record()
+            barrier()
+            tg = torch.tensor([g0.elapsed_time(g1)], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+            if i > 0:
+                gathers.append(float(tg.item()))
+        ag_ms = statistics.median(gathers)
+        # overlapped: problem i's output is gathered on a second stream as soon as its kernel is done, while the
+        # kernels of problems i + 1 .. run; every rank's slice of problem i lands at full_v[:, i]
+        full_v = full.view(world, P, M, N)
+        comm = torch.cuda.Stream()
+        overl = []
+        for it in range(4):
+            barrier()
+            o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            o0.record()
+            works = []
+            for i in range(P):
+                pto.gemm(a[i], b[i], 1, out=c[i])
+                done = torch.cuda.Event()
+                done.record()
+                comm.wait_event(done)
+                with torch.cuda.stream(comm):
+                    parts = [full_v[r, i] for r in range(world)]
+                    works.append(dist.all_gather(parts, c[i], async_op=True))
+            for w in works:
+                w.wait()
+            torch.cuda.current_stream().wait_stream(comm)
+            o1.record()
+            barrier()
+            to = torch.tensor([o0.elapsed_time(o1)], device="cuda", dtype=torch.float64)
+            dist.all_reduce(to, op=dist.ReduceOp.MAX)
+            if it > 0:
+                overl.append(float(to.item()))
+        ov_ms = statistics.median(overl)
+        nbytes = int(world * P * M * N * 4)
+        with_allgather = {"allgather_ms_per_step": ag_ms, "allgather_ms_all": gathers, "bytes_gathered_per_gpu": nbytes,
+                          "allgather_recv_gbs_per_gpu": nbytes * (world - 1) / world / ag_ms / 1e6,
+                          "nvlink_per_direction_gbs": {"measured_peer_copy": 770.0, "nominal": 900.0},
+                          "compute_ms_per_pass": pass_ms,
+                          "value": world * P * FLOPS_PER_PROBLEM / (pass_ms + ag_ms) / 1e9,
+                          "overlapped_ms_per_pass": ov_ms, "overlapped_ms_all": overl,
+                          "value_overlapped": world * P * FLOPS_PER_PROBLEM / ov_ms / 1e9, "unit": "TFLOP/s",
+                          "limiter": "the gather moves 4 bytes of C per 12288 FLOP; at N GPUs every GPU receives "
+                                     "(N-1)/N of N x 1.2 GB over its NVLink receive direction",
+                          "note": "a pass = the 8 problems of one GPU once; overlapped = each problem's gather issued "
+                                  "on a second stream as soon as its kernel finishes"}
+        del full, full_v
 
     # multi-head attention of the sharding config (batch 32 x 32 heads, S 8192, D 128, causal, fp16 O): the 1024
     # heads are split over the ranks (fixed total work: strong scaling), then every rank gathers all outputs
     sharded_attn = sharded_attention(torch, pto, dist, world, rank, barrier)
 
-    # end to end through the C ABI's host-buffer entry point: a step's P problems in pinned host memory go through
+    # end to end through the C ABI's host-buffer entry point: a pass's P problems in pinned host memory go through
     # pto_b200_gemm_f16f32_host_batched (copy in, kernel and copy out of consecutive problems overlap)
-    e2e_steps = max(1, min(args.steps, 2))
+    e2e_steps = 5
     ha = torch.empty(P, M, K, dtype=torch.float16).pin_memory()
     hb = torch.empty(P, N, K, dtype=torch.float16).pin_memory()
     hc = torch.empty(P, M, N, dtype=torch.float32).pin_memory()
@@ -599,6 +810,8 @@ def run_gpu_arm(args):
     e2e_s = float(te.item())
     e2e_value = world * e2e_steps * P * FLOPS_PER_PROBLEM / e2e_s / 1e12
     e2e_check = bool(torch.equal(hc[P - 1].cuda(), c[P - 1]))  # host path of the last problem equals its device path
+    h2d_bytes, d2h_bytes = int(P * (M * K + N * K) * 2), int(P * M * N * 4)
+    e2e_host_gbs = world * e2e_steps * (h2d_bytes + d2h_bytes) / e2e_s / 1e9
     del ha, hb, hc
 
     if rank != 0:
@@ -607,35 +820,54 @@ def run_gpu_arm(args):
         return 0
 
     achieved = FLOPS_PER_PROBLEM / avg_launch_ms / 1e9
-    peak = peaks["bf16_tflops_sustained"]
+    timed_s = elapsed_ms / 1e3
+    # the sustained figure is the denominator of a region that lasts about a second or more; a shorter one is burst
+    peak = peaks["bf16_tflops_sustained"] if timed_s >= 0.8 else peaks["bf16_tflops"]
+    iso_tf = FLOPS_PER_PROBLEM / iso_ms / 1e9
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": GEMM_DRAM_TRAFFIC_BYTES, "peak_kind": f"{peak_kind} cuBLAS bf16 8192^3, sustained loop "
-                "(launches timed inside a long step)", "frac_of_burst": achieved / peaks["bf16_tflops"],
+                "traffic": GEMM_DRAM_TRAFFIC_BYTES,
+                "peak_kind": f"{peak_kind} cuBLAS bf16 8192^3, " + ("sustained loop" if timed_s >= 0.8 else "burst") +
+                             f" (the timed region lasts {timed_s:.2f} s)",
+                "frac_of_burst": achieved / peaks["bf16_tflops"],
                 "frac_of_nominal_2250": achieved / 2250.0, "kernel": "gemm2_f16f32_kernel<1>",
-                "avg_launch_ms": avg_launch_ms, "algorithmic_flops_per_launch": FLOPS_PER_PROBLEM}
+                "avg_launch_ms": avg_launch_ms, "algorithmic_flops_per_launch": FLOPS_PER_PROBLEM,
+                "isolated_10_launches_tflops": iso_tf, "isolated_frac_of_burst": iso_tf / peaks["bf16_tflops"],
+                "block_stamps_last_launch": block_stamps,
+                "tflops_per_ghz": (achieved / (block_stamps["sm_mhz_median"] / 1e3)) if block_stamps else None}
     cpu = None
     extra = None
     if world == 1:
         cpu_tf, info = cpu_gemm_sample(12.0)
         cpu = {"value": cpu_tf, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"],
                "sample": info["sample"]}
+        try:
+            cpu["others"] = cpu_vector_and_attention_baselines()
+        except Exception as exc:
+            cpu["others_note"] = str(exc)[:160]
         extra = extras(torch, pto, peaks, peak_kind)
     line = {
         "metric": "fp16 GEMM TFLOPS (m=n=k=6144, fp32 accumulate and output)", "value": value, "unit": "TFLOP/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate",
         "data": "synthetic",
-        "config": {"workload": f"gemm_f16f32 m=n=k=6144, {P} independent problems per GPU per step "
-                               f"({world * P} in total), B stored n x k (Layout::DN), uniform[-1,1) seeded",
-                   "l2": "each step reads 1.2 GB of distinct operands per GPU (> 126 MB L2)",
+        "config": {"workload": f"gemm_f16f32 m=n=k=6144, {P} independent problems per GPU ({world * P} in total), "
+                               f"a step = {R} passes over them ({R * P} launches per GPU), B stored n x k "
+                               "(Layout::DN), uniform[-1,1) seeded",
+                   "repeats_per_step": R, "timed_region_s": timed_s,
+                   "l2": "each pass reads 1.2 GB of distinct operands per GPU (> 126 MB L2)",
                    "parallelism": f"{world} GPU(s), problems sharded, no data-path collective"},
         "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
-        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": int(P * (M * K + N * K) * 2),
-                "d2h_bytes_per_step": int(P * M * N * 4), "steps": e2e_steps, "matches_device_path": e2e_check,
-                "api": "pto_b200_gemm_f16f32_host_batched (C ABI, pinned host buffers, copies overlapped with kernels)"},
-        "gpu_launches": args.steps * P, "with_allgather": with_allgather, "sharded_attention": sharded_attn,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_bytes,
+                "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps, "matches_device_path": e2e_check,
+                "host_gbs_both_directions": e2e_host_gbs,
+                "limiter": "host <-> device copies: 12 bytes cross PCIe per 12288 FLOP; all ranks share the host's "
+                           "memory and PCIe root ports",
+                "api": "pto_b200_gemm_f16f32_host_batched (C ABI, pinned host buffers, copies overlapped with kernels); "
+                       "an e2e step = one pass over the 8 problems"},
+        "gpu_launches": launches, "with_allgather": with_allgather, "sharded_attention": sharded_attn,
         "extras": extra,
     }
+    line["summary"] = compact_summary(line)
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -645,7 +877,7 @@ def run_gpu_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     args = ap.parse_args()

@@ -273,6 +273,7 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
         }
         dst.pitch_ = pitch;
         dst.major_ = cols_contig ? b200::kColsContiguous : b200::kRowsContiguous;
+        b200::complete_copies_if_in_order();
     } else if constexpr (TileData::Loc == TileType::Mat) {
         // matrix tiles of 8- and 32-bit elements are kept plain (row-major Rows x Cols, zero outside the valid region);
         // TMATMUL on them runs on the CUDA cores with the simulation's arithmetic
@@ -417,6 +418,12 @@ PTO_INTERNAL void matmul_issue(TileAccT &c, TileLeftT &a, TileRightT &b, bool ac
     using AT = typename TileLeftT::DType;
     static_assert(TileLeftT::Cols % 16 == 0, "TMATMUL: k a multiple of 16");
 #if PTO_B200_DEVICE_CODE
+    if (control()->in_order) {
+        // no flags order the operands' staging before the product: every thread's writes are made visible to the
+        // tensor core here (in a program with flags, set_flag(PIPE_MTE1, PIPE_M, ...) does this)
+        fence_async_proxy();
+        __syncthreads();
+    }
     if (threadIdx.x == 0) {
         constexpr uint32_t kBf16 = std::is_same_v<AT, __nv_bfloat16> ? 1u : 0u;
         const uint32_t idesc = (1u << 4) | (kBf16 << 7) | (kBf16 << 10) | (static_cast<uint32_t>(a.major_) << 15) |
@@ -440,6 +447,7 @@ PTO_INTERNAL void matmul_issue(TileAccT &c, TileLeftT &a, TileRightT &b, bool ac
             mma_f16(d_tmem, a_desc, b_desc, idesc, (accumulate || kk != 0) ? 1u : 0u);
         }
     }
+    complete_matmul_if_in_order();
 #endif
 }
 

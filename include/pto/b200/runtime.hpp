@@ -56,7 +56,7 @@ struct StatusRecord {
 struct Control {
     uint32_t tmem_base;
     int abort_flag;
-    int error_code;
+    int in_order;                   // 1: every instruction completes before the next one starts (LaunchOptions::in_order)
     int fail_where;                 // flag index of the first wait that gave up
     unsigned long long wait_limit_ns;
     uint64_t flags[kNumFlags];
@@ -200,7 +200,8 @@ __device__ __forceinline__ void tc_commit(uint64_t *bar)
 }
 
 // Block prologue / epilogue (called by the launch trampoline, not by tile programs).
-__device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, uint32_t l0a_offset, uint32_t l0b_offset)
+__device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, uint32_t l0a_offset, uint32_t l0b_offset,
+                                            int in_order)
 {
     Control *ctl = control();
     const int nthreads = blockDim.x;
@@ -226,7 +227,7 @@ __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, ui
     }
     if (threadIdx.x == 0) {
         ctl->abort_flag = 0;
-        ctl->error_code = 0;
+        ctl->in_order = in_order;
         ctl->fail_where = -1;
         ctl->wait_limit_ns = wait_limit_ns == 0 ? kWaitLimitNs : wait_limit_ns;
         ctl->l0a_offset = l0a_offset;
@@ -278,15 +279,20 @@ struct LaunchOptions {
     unsigned long long wait_limit_ns = 0;
     uint32_t l0a_offset = PTO_B200_L0A_OFFSET;
     uint32_t l0b_offset = PTO_B200_L0B_OFFSET;
+    // Every instruction completes before the next one starts, as in the reference's CPU simulation.  For tile programs
+    // written for the simulation alone, which carry no set_flag / wait_flag between dependent instructions of
+    // different pipes (e.g. RunTMATMUL_SPLIT_K of tests/cpu/st/testcase/tmatmul/tmatmul_kernel.cpp:104-155 in the
+    // reference); programs that carry their flags do not need it and lose their overlap with it.
+    bool in_order = false;
 };
 
 template <typename Program>
 __global__ void __launch_bounds__(kBlockThreads, 1)
     block_kernel(Program program, StatusRecord *status, unsigned long long wait_limit_ns, uint32_t l0a_offset,
-                 uint32_t l0b_offset)
+                 uint32_t l0b_offset, int in_order)
 {
 #if PTO_B200_DEVICE_CODE
-    block_begin(wait_limit_ns, l0a_offset, l0b_offset);
+    block_begin(wait_limit_ns, l0a_offset, l0b_offset, in_order);
     program();
     block_end(status);
 #endif
@@ -302,7 +308,8 @@ inline cudaError_t launch(uint32_t blocks, void *stream, Program program, const 
         return e;
     }
     block_kernel<Program><<<blocks, kBlockThreads, opt.smem_bytes, static_cast<cudaStream_t>(stream)>>>(
-        program, static_cast<StatusRecord *>(opt.status), opt.wait_limit_ns, opt.l0a_offset, opt.l0b_offset);
+        program, static_cast<StatusRecord *>(opt.status), opt.wait_limit_ns, opt.l0a_offset, opt.l0b_offset,
+        opt.in_order ? 1 : 0);
     return cudaGetLastError();
 }
 template <typename Program>
@@ -403,6 +410,32 @@ PTO_INTERNAL void wait_flag(pipe_t src, pipe_t dst, int id)
     (void)id;
 #endif
 }
+
+namespace pto {
+namespace b200 {
+// in-order launches: what an asynchronous instruction does before it returns
+PTO_INTERNAL void complete_copies_if_in_order()
+{
+#if PTO_B200_DEVICE_CODE
+    if (control()->in_order) {
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();
+    }
+#endif
+}
+PTO_INTERNAL void complete_matmul_if_in_order()
+{
+#if PTO_B200_DEVICE_CODE
+    if (control()->in_order) {
+        // the flag (PIPE_M -> PIPE_ALL, 7) is kept for this; tile programs have no reason to name it
+        set_flag(PIPE_M, PIPE_ALL, 7);
+        wait_flag(PIPE_M, PIPE_ALL, 7);
+        __syncthreads();
+    }
+#endif
+}
+} // namespace b200
+} // namespace pto
 
 PTO_INTERNAL void pipe_barrier(pipe_t pipe)
 {

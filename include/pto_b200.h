@@ -266,6 +266,15 @@ int pto_b200_probe_random_reads(const uint32_t *table, int64_t table_bytes, int6
  * one launch per head there; d must be 128 (the reference's only head size), sq and sk multiples of 128. */
 int pto_b200_flash_attn_fwd_f16(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o, int batch_heads,
                                 int sq, int sk, int d, int causal, float scale, int out_f16, void *stream);
+/* The same with the handling of the running row maximum stated explicitly.  defer_rescale = 0: the maximum that P is
+ * taken relative to follows the running maximum at every key tile (of 128 keys) where it grows, and O is rescaled each
+ * time - the reference's recurrence (kernels/manual/common/flash_atten/pto_macro_fa_softmax.hpp:100-184,
+ * pto_macro_fa_gu.hpp:33-49).  defer_rescale = 1: it follows only once the running maximum has grown 256-fold, which
+ * saves almost every rescale of O; the result is the same up to which fp16 roundings of P occur.
+ * pto_b200_flash_attn_fwd_f16 uses 0 for fp32 output (the reference's output type) and 1 for fp16 output. */
+int pto_b200_flash_attn_fwd_f16_ex(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o, int batch_heads,
+                                   int sq, int sk, int d, int causal, float scale, int out_f16, int defer_rescale,
+                                   void *stream);
 /* HOST-buffer variant (copies in, runs, copies out, synchronises). */
 int pto_b200_flash_attn_fwd_f16_host(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o,
                                      int batch_heads, int sq, int sk, int d, int causal, float scale, int out_f16);

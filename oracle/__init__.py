@@ -19,6 +19,11 @@ def _p(a):
     return a.ctypes.data_as(ctypes.c_void_p)
 
 
+def reference_root():
+    """The reference tree: $PTO_REFERENCE_ROOT, else a directory named `reference` beside the repository."""
+    return os.environ.get("PTO_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
 def build(force=False):
     """Compile liboracle.so (and _ref/libpto_ref.so when the reference tree is present)."""
     so = os.path.join(_HERE, "liboracle.so")
@@ -27,8 +32,9 @@ def build(force=False):
     ref_so = os.path.join(_HERE, "_ref", "libpto_ref.so")
     ref_srcs = [os.path.join(_HERE, f) for f in os.listdir(_HERE) if f.startswith("ref_") and f.endswith(".cpp")]
     stale = os.path.exists(ref_so) and any(os.path.getmtime(f) > os.path.getmtime(ref_so) for f in ref_srcs)
-    if os.path.isdir("/root/reference/include/pto") and (force or stale or not os.path.exists(ref_so)):
-        subprocess.check_call(["make", "-C", _HERE, "ref"], stdout=subprocess.DEVNULL)
+    reference = reference_root()
+    if os.path.isdir(os.path.join(reference, "include", "pto")) and (force or stale or not os.path.exists(ref_so)):
+        subprocess.check_call(["make", "-C", _HERE, "ref", "REFERENCE=" + reference], stdout=subprocess.DEVNULL)
 
 
 class _Lib:

@@ -59,6 +59,7 @@ SIGNATURES = {
     "pto_b200_gemm_f16f32_host_batched": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i64, _i64, _i64]),
     "pto_b200_gemm_f16f32_host_static": (_i, [_vp, _vp, _vp, _i, _i, _i, _i]),
     "pto_b200_flash_attn_fwd_f16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp]),
+    "pto_b200_flash_attn_fwd_f16_ex": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp]),
     "pto_b200_flash_attn_fwd_f16_host": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i]),
     "pto_b200_gemm_call_kernel": (None, [_u32, _vp, _vp, _vp, _vp]),
     "pto_b200_fa_call_kernel": (None, [_vp, _i, _i, _i, ctypes.c_bool] + [_vp] * 11),

@@ -593,6 +593,18 @@ int pto_b200_flash_attn_fwd_f16(const uint16_t *q, const uint16_t *k, const uint
     return launch_flash_attn_fwd(q, k, v, o, batch_heads, sq, sk, d, causal, scale, out_f16, as_stream(stream));
 }
 
+int pto_b200_flash_attn_fwd_f16_ex(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o, int batch_heads,
+                                   int sq, int sk, int d, int causal, float scale, int out_f16, int defer_rescale,
+                                   void *stream)
+{
+    if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || batch_heads <= 0 || sq <= 0 || sk <= 0 ||
+        (defer_rescale != 0 && defer_rescale != 1)) {
+        return bad("flash_attn_fwd_ex: bad argument");
+    }
+    return launch_flash_attn_fwd(q, k, v, o, batch_heads, sq, sk, d, causal, scale, out_f16, as_stream(stream),
+                                 defer_rescale);
+}
+
 int pto_b200_flash_attn_fwd_f16_host(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o,
                                      int batch_heads, int sq, int sk, int d, int causal, float scale, int out_f16)
 {

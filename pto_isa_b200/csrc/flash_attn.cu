@@ -146,9 +146,9 @@ template <bool kCausal, bool kOutF16, int kPolyOf8>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o, int sq, int sk,
-                      float scale_log2, DeviceStatus *status)
+                      float scale_log2, float defer_log2, DeviceStatus *status)
 {
-    if (threadIdx.x == kThreads - 1) {
+    if (threadIdx.x == 0) { // a softmax thread: it has nothing to do until the first logits arrive
         profile_stamp(status, 0);
     }
     extern __shared__ uint8_t smem_raw[];
@@ -418,9 +418,11 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 }
             }
             const float mx = fmaxf(max3(mx8[0], mx8[1], mx8[2]), max3(max3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
-            // move the reference max only when some row of this warp grew by more than 2^8
+            // The reference maximum follows the running maximum as soon as it grows by more than 2^defer_log2:
+            // 0 = at every key tile where it grows at all, the reference's recurrence (pto_macro_fa_softmax.hpp:
+            // 141-165 in the reference); 8 = only after it has grown 256-fold, which saves almost every rescale of O.
             const float m_new = fmaxf(m_run, mx);
-            const bool grow = (m_new - m_run) * scale_log2 > 8.0f; // also true on the first tile (m_run = -inf)
+            const bool grow = (m_new - m_run) * scale_log2 > defer_log2; // also true on the first tile (m_run = -inf)
             const bool rescale = __any_sync(0xffffffffu, grow);
             // The previous PV product must be complete before O is rescaled or P's buffer is rewritten.  The
             // rescale is rare, so normally this wait sits after the exponentials: they overlap that product.
@@ -557,7 +559,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     // ---------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == kThreads - 1) {
+    if (threadIdx.x == 0) {
         profile_stamp(status, 1);
     }
     if (ctl->abort_flag) {
@@ -578,7 +580,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 
 template <bool kCausal, bool kOutF16, int kPolyOf8>
 int launch_variant(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const CUtensorMap &to, int bh, int sq, int sk,
-                   float scale_log2, DeviceStatus *status, cudaStream_t stream)
+                   float scale_log2, float defer_log2, DeviceStatus *status, cudaStream_t stream)
 {
     const int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(&flash_attn_fwd_kernel<kCausal, kOutF16, kPolyOf8>),
                                        kSmemBytes);
@@ -587,27 +589,31 @@ int launch_variant(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorM
     }
     const int q_blocks = (sq + 2 * kTileQ - 1) / (2 * kTileQ);
     flash_attn_fwd_kernel<kCausal, kOutF16, kPolyOf8>
-        <<<bh * q_blocks, kThreads, kSmemBytes, stream>>>(tq, tk, tv, to, sq, sk, scale_log2, status);
+        <<<bh * q_blocks, kThreads, kSmemBytes, stream>>>(tq, tk, tv, to, sq, sk, scale_log2, defer_log2, status);
     return check_launch();
 }
 
 template <int kPolyOf8>
 int launch_mode(bool causal, bool out_f16, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const CUtensorMap &to,
-                int bh, int sq, int sk, float scale_log2, DeviceStatus *status, cudaStream_t stream)
+                int bh, int sq, int sk, float scale_log2, float defer_log2, DeviceStatus *status, cudaStream_t stream)
 {
     if (causal) {
-        return out_f16 ? launch_variant<true, true, kPolyOf8>(tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream)
-                       : launch_variant<true, false, kPolyOf8>(tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream);
+        return out_f16 ? launch_variant<true, true, kPolyOf8>(tq, tk, tv, to, bh, sq, sk, scale_log2, defer_log2, status, stream)
+                       : launch_variant<true, false, kPolyOf8>(tq, tk, tv, to, bh, sq, sk, scale_log2, defer_log2, status, stream);
     }
-    return out_f16 ? launch_variant<false, true, kPolyOf8>(tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream)
-                   : launch_variant<false, false, kPolyOf8>(tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream);
+    return out_f16 ? launch_variant<false, true, kPolyOf8>(tq, tk, tv, to, bh, sq, sk, scale_log2, defer_log2, status, stream)
+                   : launch_variant<false, false, kPolyOf8>(tq, tk, tv, to, bh, sq, sk, scale_log2, defer_log2, status, stream);
 }
 
 } // namespace
 
 int launch_flash_attn_fwd(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o, int bh, int sq, int sk,
-                          int d, int causal, float scale, int out_f16, cudaStream_t stream)
+                          int d, int causal, float scale, int out_f16, cudaStream_t stream, int defer_rescale)
 {
+    if (defer_rescale < 0) {
+        defer_rescale = out_f16; // fp32 O: the reference's recurrence; fp16 O (the benchmark's configuration): deferred
+    }
+    const float defer_log2 = defer_rescale ? 8.0f : 0.0f;
     if (d != kD) {
         set_error_text("flash attention: head size must be 128");
         return kErrUnsupportedShape;
@@ -648,11 +654,11 @@ int launch_flash_attn_fwd(const uint16_t *q, const uint16_t *k, const uint16_t *
         return e != nullptr ? atoi(e) : 1;
     }();
     switch (poly) {
-        case 0: return launch_mode<0>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream);
-        case 2: return launch_mode<2>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream);
-        case 3: return launch_mode<3>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream);
-        case 4: return launch_mode<4>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream);
-        default: return launch_mode<1>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, status, stream);
+        case 0: return launch_mode<0>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, defer_log2, status, stream);
+        case 2: return launch_mode<2>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, defer_log2, status, stream);
+        case 3: return launch_mode<3>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, defer_log2, status, stream);
+        case 4: return launch_mode<4>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, defer_log2, status, stream);
+        default: return launch_mode<1>(causal != 0, out_f16 != 0, tq, tk, tv, to, bh, sq, sk, scale_log2, defer_log2, status, stream);
     }
 }
 

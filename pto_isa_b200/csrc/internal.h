@@ -111,6 +111,6 @@ size_t gemm_static_scratch_bytes();
 
 // flash attention forward; q/k/v/o are [batch*heads, seq, d] contiguous; out_f16 selects the output type
 int launch_flash_attn_fwd(const uint16_t *q, const uint16_t *k, const uint16_t *v, void *o, int bh, int sq, int sk,
-                          int d, int causal, float scale, int out_f16, cudaStream_t stream);
+                          int d, int causal, float scale, int out_f16, cudaStream_t stream, int defer_rescale = -1);
 
 } // namespace pto_b200

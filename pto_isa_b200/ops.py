@@ -585,8 +585,10 @@ def gemm_host_batched(a, b, c, b_layout=1):
     return c
 
 
-def flash_attn_fwd(q, k, v, causal=False, scale=None, out_dtype=torch.float16, out=None):
-    """q: (..., sq, d), k / v: (..., sk, d) fp16 with the same leading (batch, heads) dims.  Returns O like q."""
+def flash_attn_fwd(q, k, v, causal=False, scale=None, out_dtype=torch.float16, out=None, defer_rescale=None):
+    """q: (..., sq, d), k / v: (..., sk, d) fp16 with the same leading (batch, heads) dims.  Returns O like q.
+    defer_rescale: False = the reference's recurrence (the row maximum moves at every key tile where it grows), True =
+    it moves only after growing 256-fold (fewer rescales of O); None = False for float32 output, True for float16."""
     _need_cuda(q, k, v)
     if q.dtype != torch.float16 or k.dtype != torch.float16 or v.dtype != torch.float16:
         raise PtoB200Error("flash_attn_fwd: operands must be float16")
@@ -602,8 +604,13 @@ def flash_attn_fwd(q, k, v, causal=False, scale=None, out_dtype=torch.float16, o
     scale = (1.0 / d ** 0.5) if scale is None else float(scale)
     out = _out(out, q.shape, out_dtype, q.device, "flash_attn_fwd")
     with torch.cuda.device(q.device):
-        rc = lib().pto_b200_flash_attn_fwd_f16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), bh, sq, sk, d, int(bool(causal)),
-                                               scale, 1 if out_dtype == torch.float16 else 0, _stream(q))
+        if defer_rescale is None:
+            rc = lib().pto_b200_flash_attn_fwd_f16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), bh, sq, sk, d, int(bool(causal)),
+                                                   scale, 1 if out_dtype == torch.float16 else 0, _stream(q))
+        else:
+            rc = lib().pto_b200_flash_attn_fwd_f16_ex(_ptr(q), _ptr(k), _ptr(v), _ptr(out), bh, sq, sk, d,
+                                                      int(bool(causal)), scale, 1 if out_dtype == torch.float16 else 0,
+                                                      int(bool(defer_rescale)), _stream(q))
     check(rc, "flash_attn_fwd")
     return out
 

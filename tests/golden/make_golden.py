@@ -421,7 +421,9 @@ def gen_mxgemm_fp4(ref, tmp, out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("PTO_REFERENCE_ROOT") or
+                    os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference"),
+                    help="root of the reference tree (default: $PTO_REFERENCE_ROOT, else `reference` beside the repository)")
     args = ap.parse_args()
     cwd = os.getcwd()
     with tempfile.TemporaryDirectory() as tmp:

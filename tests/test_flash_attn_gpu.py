@@ -53,7 +53,11 @@ def test_attention_internal_scale_and_fp16_output(causal):
     scale = 1.0 / np.sqrt(d)
     o32 = host(pto.flash_attn_fwd(dev(q), dev(k), dev(v), causal=causal, out_dtype=torch.float32))
     o16 = host(pto.flash_attn_fwd(dev(q), dev(k), dev(v), causal=causal, out_dtype=torch.float16))
-    assert np.array_equal(o16, o32.astype(np.float16))  # same kernel, output rounded to nearest even on store
+    # the same computation (here: both with the deferred rescale) differs only by the rounding on store
+    o32d = host(pto.flash_attn_fwd(dev(q), dev(k), dev(v), causal=causal, out_dtype=torch.float32, defer_rescale=True))
+    assert np.array_equal(o16, o32d.astype(np.float16))
+    o16e = host(pto.flash_attn_fwd(dev(q), dev(k), dev(v), causal=causal, out_dtype=torch.float16, defer_rescale=False))
+    assert np.array_equal(o16e, o32.astype(np.float16))
     for h in range(bh):
         want = port.attn_head_f16(q[h], k[h], v[h], int(causal), scale)
         ok, worst, _ = attn_err_ok(o32[h], want, label=f"internal scale causal={causal} head {h}")

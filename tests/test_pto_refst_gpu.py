@@ -157,9 +157,8 @@ def test_reference_tmatmul_cases(refk, golden_dir):
         assert refk.pto_refk_tmatmul(key, _ptr(out), _ptr(dev(a)), _ptr(dev(b)), _stream()) == 0
         torch.cuda.synchronize()
         assert result_cmp(g, host(out), 1e-3), name
-        ok, worst = rel_err_ok(host(out), g, 2e-3)
+        ok, worst = rel_err_ok(host(out), g, 2e-3, label=f"reference tmatmul {name}")
         assert ok, f"{name}: max relative error {worst:.3e}"
-        print(f"tmatmul {name}: max relative error {worst:.3e}")
     # key 4: fp32 120 x 110 x 50 on the CUDA cores, bit-exact against the simulation's sum order
     a, b, g = z["case4_a"][0], z["case4_b"][0], z["case4_golden"]
     out = torch.full(g.shape, float("nan"), device="cuda")
@@ -225,11 +224,12 @@ def test_reference_row_and_exp_programs(refk):
     assert refk.pto_refk_trowmax(2, _ptr(out2), _ptr(dev(x2)), _stream()) == 0
     torch.cuda.synchronize()
     assert np.array_equal(host(out2), x2.max(axis=1))
-    outs = torch.zeros(64, device="cuda")
+    outs = torch.full((64, 64), 9.0, device="cuda")  # the program stores its whole destination tile; sums in column 0
     assert refk.pto_refk_trowsum_f32_64x64(_ptr(outs), _ptr(dev(x)), _stream()) == 0
     torch.cuda.synchronize()
     want = port.trowsum_f32(x)
-    assert np.abs(host(outs) - want).max() <= 2e-6 * np.abs(x).sum(axis=1).max()  # tree sum against a sequential one
+    assert np.abs(host(outs)[:, 0] - want).max() <= 2e-6 * np.abs(x).sum(axis=1).max()  # tree sum / sequential sum
+    assert not host(outs)[:, 1:].any()  # the rest of the tile is what the program's std::fill left there
     oute = torch.zeros(64, 64, device="cuda")
     assert refk.pto_refk_texp(0, _ptr(oute), _ptr(dev(x)), _stream()) == 0
     torch.cuda.synchronize()
@@ -310,9 +310,10 @@ def test_reference_fa_macros_one_head(refk, s0, s1, causal, fifo):
                                  _ptr(p_ws), _ptr(pv_ws), _stream(), _ptr(status)) == 0
     assert refk.pto_refk_status(_stream(), _ptr(status)) == 0, host(status)
     scale = float(_newton_inv_sqrt(d))
-    want = port.fa_tiled_f16(q, k, v, causal, scale, tile_s1=64)
-    ok, worst = rel_err_ok(host(o), want, 2e-3)
-    print(f"fa macros s0={s0} s1={s1} causal={causal} fifo={fifo}: max relative error {worst:.3e}")
+    # non-causal: the oracle's streaming formulation with the program's key tile; causal: its plain formulation (the
+    # streaming one models the reference kernel's 128-row query blocks, which this program's 32-row blocks are not)
+    want = port.attn_head_f16(q, k, v, 1, scale) if causal else port.fa_tiled_f16(q, k, v, 0, scale, tile_s1=64)
+    ok, worst = rel_err_ok(host(o), want, 2e-3, label=f"fa macros + pipes s0={s0} s1={s1} causal={causal} fifo={fifo}")
     assert ok, f"max relative error {worst:.3e}"
 
 
