@@ -240,33 +240,36 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
     using T = typename TileData::DType;
     const T *g = reinterpret_cast<const T *>(src.data());
     const int64_t s3 = src.GetStride(3), s4 = src.GetStride(4);
-    if constexpr (TileData::Loc == TileType::Mat && sizeof(T) == 2) {
-        // 16-bit matrix tiles feed the tensor core: the global tensor's unit-stride dimension decides the staged layout
+    if constexpr (TileData::Loc == TileType::Mat && b200::is_tc_elem<T>::value) {
+        // tiles the tensor core reads: the global tensor's unit-stride dimension decides the staged layout; a line is
+        // 128 bytes of the contiguous dimension (64 16-bit or 128 8-bit elements), 16-byte chunks swizzled by the line
+        constexpr int kCE = 16 / static_cast<int>(sizeof(T)); // elements per 16-byte chunk
         const bool cols_contig = (s4 == 1);
         const int vr = dst.GetValidRow(), vc = dst.GetValidCol();
         const int lines = cols_contig ? TileData::Rows : TileData::Cols;  // index of the strided dimension
         const int span = cols_contig ? TileData::Cols : TileData::Rows;   // extent of the contiguous dimension
         const int v_lines = cols_contig ? vr : vc, v_span = cols_contig ? vc : vr;
         const int64_t line_stride = cols_contig ? s3 : s4;
-        const int chunks_per_line = span / 8;
+        const int chunks_per_line = span / kCE;
         const uint32_t base = b200::smem_u32(b200::arena() + dst.addr_);
         const uint32_t pitch = static_cast<uint32_t>(lines) * 128u;
         // 16-byte asynchronous copies need 16-byte aligned sources; ragged rows are fetched element by element
-        const bool aligned = ((reinterpret_cast<uintptr_t>(g) | static_cast<uintptr_t>(line_stride * 2)) & 15u) == 0 &&
+        const bool aligned = ((reinterpret_cast<uintptr_t>(g) | static_cast<uintptr_t>(line_stride * sizeof(T))) & 15u) == 0 &&
                              !__isShared(g); // (a FIFO entry may lie in the block's own shared memory)
         for (int q = threadIdx.x; q < lines * chunks_per_line; q += blockDim.x) {
             const int l = q / chunks_per_line, ch = q - l * chunks_per_line;
-            const int e0 = ch * 8; // first element of this 16-byte chunk along the contiguous dimension
-            int valid = (l < v_lines) ? (v_span - e0) * 2 : 0;
+            const int e0 = ch * kCE; // first element of this 16-byte chunk along the contiguous dimension
+            int valid = (l < v_lines) ? (v_span - e0) * static_cast<int>(sizeof(T)) : 0;
             valid = valid < 0 ? 0 : (valid > 16 ? 16 : valid);
             const uint32_t off = (ch >> 3) * pitch + l * 128u + (((ch & 7) ^ (l & 7)) << 4);
             if (aligned) {
                 b200::cp_async16(base + off, valid > 0 ? g + l * line_stride + e0 : g, valid);
             } else {
                 uint4 v = make_uint4(0, 0, 0, 0);
-                unsigned short *h = reinterpret_cast<unsigned short *>(&v);
-                for (int e = 0; e < valid / 2; ++e) {
-                    h[e] = reinterpret_cast<const unsigned short *>(g)[l * line_stride + e0 + e];
+                unsigned char *h = reinterpret_cast<unsigned char *>(&v);
+                const unsigned char *gb = reinterpret_cast<const unsigned char *>(g + l * line_stride + e0);
+                for (int e = 0; e < valid; ++e) {
+                    h[e] = gb[e];
                 }
                 *reinterpret_cast<uint4 *>(b200::arena() + dst.addr_ + off) = v;
             }
@@ -275,8 +278,8 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
         dst.major_ = cols_contig ? b200::kColsContiguous : b200::kRowsContiguous;
         b200::complete_copies_if_in_order();
     } else if constexpr (TileData::Loc == TileType::Mat) {
-        // matrix tiles of 8- and 32-bit elements are kept plain (row-major Rows x Cols, zero outside the valid region);
-        // TMATMUL on them runs on the CUDA cores with the simulation's arithmetic
+        // matrix tiles of integers, fp32 and scale bytes are kept plain (row-major Rows x Cols, zero outside the valid
+        // region); TMATMUL on int8 / fp32 runs on the CUDA cores with the simulation's arithmetic
         T *t = reinterpret_cast<T *>(b200::arena() + dst.addr_);
         const int vr = dst.GetValidRow(), vc = dst.GetValidCol();
         for (int i = threadIdx.x; i < TileData::Numel; i += blockDim.x) {
@@ -334,14 +337,42 @@ PTO_INST RecordEvent TEXTRACT(DstTileData &dst, SrcTileData &src, uint16_t index
 {
     TSYNC(events...);
     static_assert(SrcTileData::Loc == TileType::Mat, "TEXTRACT: source must be a Mat tile");
-    static_assert(DstTileData::Loc == TileType::Left || DstTileData::Loc == TileType::Right,
-                  "TEXTRACT: destination must be a Left or Right tile");
+    static_assert(DstTileData::Loc == TileType::Left || DstTileData::Loc == TileType::Right ||
+                      DstTileData::Loc == TileType::ScaleLeft || DstTileData::Loc == TileType::ScaleRight,
+                  "TEXTRACT: destination must be a Left, Right, ScaleLeft or ScaleRight tile");
     static_assert(sizeof(typename DstTileData::DType) == sizeof(typename SrcTileData::DType),
                   "TEXTRACT: element sizes differ");
 #if PTO_B200_DEVICE_CODE
-    if constexpr (sizeof(typename SrcTileData::DType) != 2) {
-        // plain tiles (8- and 32-bit elements): the window, row by row; outside the source tile the operand is zero
-        using T = typename DstTileData::DType;
+    using T = typename DstTileData::DType;
+    if constexpr (DstTileData::Loc == TileType::ScaleLeft || DstTileData::Loc == TileType::ScaleRight) {
+        // e8m0 scales of an MX product, one per 32 k: the window of the plain scale tile is written as the atoms the
+        // tensor core reads - for 128 rows (ScaleLeft) or 128 columns (ScaleRight) and four consecutive scales,
+        // 512 bytes with byte (i % 32) * 16 + (i / 32) * 4 + j for row / column i and scale j.  Atoms are ordered
+        // [group of 128][group of 4 scales]; positions outside the destination's valid region hold 2^0.
+        static_assert(sizeof(T) == 1, "scale tiles hold one byte per scale");
+        constexpr bool kLeftSide = DstTileData::Loc == TileType::ScaleLeft;
+        constexpr int kLines = kLeftSide ? DstTileData::Rows : DstTileData::Cols;   // rows of A / columns of B
+        constexpr int kScales = kLeftSide ? DstTileData::Cols : DstTileData::Rows;  // scales per line
+        constexpr int kGroups = (kLines + 127) / 128, kAtoms = (kScales + 3) / 4;
+        const unsigned char *sp = reinterpret_cast<const unsigned char *>(b200::arena_of<TileType::Mat>() + src.addr_);
+        unsigned char *dp = reinterpret_cast<unsigned char *>(b200::arena_of<DstTileData::Loc>() + dst.addr_);
+        for (int i = threadIdx.x; i < kGroups * kAtoms * 512; i += blockDim.x) {
+            const int atom = i >> 9, b = i & 511;
+            const int grp = atom / kAtoms, a = atom - grp * kAtoms;
+            const int line = grp * 128 + ((b >> 2) & 3) * 32 + (b >> 4), sc = a * 4 + (b & 3);
+            unsigned char v = 127;
+            if (line < kLines && sc < kScales) {
+                const int r = kLeftSide ? line + indexRow : sc + indexRow, c = kLeftSide ? sc + indexCol : line + indexCol;
+                if (r < SrcTileData::Rows && c < SrcTileData::Cols) {
+                    v = sp[r * SrcTileData::Cols + c];
+                }
+            }
+            dp[i] = v;
+        }
+        dst.pitch_ = 0;
+        dst.major_ = b200::kPlain;
+    } else if constexpr (!b200::is_tc_elem<T>::value) {
+        // plain tiles (integers, fp32): the window, row by row; outside the source tile the operand is zero
         const T *s = reinterpret_cast<const T *>(b200::arena_of<TileType::Mat>() + src.addr_);
         T *d = reinterpret_cast<T *>(b200::arena_of<DstTileData::Loc>() + dst.addr_);
         for (int i = threadIdx.x; i < DstTileData::Numel; i += blockDim.x) {
@@ -352,14 +383,15 @@ PTO_INST RecordEvent TEXTRACT(DstTileData &dst, SrcTileData &src, uint16_t index
         dst.pitch_ = 0;
         dst.major_ = b200::kPlain;
     } else {
+        constexpr int kCE = 16 / static_cast<int>(sizeof(T));
         const bool cols_contig = (src.major_ == b200::kColsContiguous);
         const int line0 = cols_contig ? indexRow : indexCol;
-        const int chunk0 = (cols_contig ? indexCol : indexRow) >> 3;
+        const int chunk0 = (cols_contig ? indexCol : indexRow) / kCE;
         const int lines = cols_contig ? DstTileData::Rows : DstTileData::Cols;
-        const int chunks_per_line = (cols_contig ? DstTileData::Cols : DstTileData::Rows) / 8;
+        const int chunks_per_line = (cols_contig ? DstTileData::Cols : DstTileData::Rows) / kCE;
         // lines and chunks of the source tile's own storage; a window that reaches past them reads zeros
         const int src_lines = cols_contig ? SrcTileData::Rows : SrcTileData::Cols;
-        const int src_chunks = (cols_contig ? SrcTileData::Cols : SrcTileData::Rows) / 8;
+        const int src_chunks = (cols_contig ? SrcTileData::Cols : SrcTileData::Rows) / kCE;
         const uint32_t dst_pitch = static_cast<uint32_t>(lines) * 128u;
         const uint8_t *s = b200::arena_of<TileType::Mat>() + src.addr_;
         uint8_t *d = b200::arena_of<DstTileData::Loc>() + dst.addr_;
@@ -516,7 +548,7 @@ template <typename TileAccT, typename TileLeftT, typename TileRightT>
 PTO_INTERNAL void matmul_dispatch(TileAccT &c, TileLeftT &a, TileRightT &b, bool accumulate)
 {
     matmul_check<TileAccT, TileLeftT, TileRightT>();
-    if constexpr (sizeof(typename TileLeftT::DType) == 2) {
+    if constexpr (is_tc_elem<typename TileLeftT::DType>::value) {
         matmul_issue(c, a, b, accumulate);
     } else {
         matmul_plain(c, a, b, accumulate ? 1 : 0, nullptr);
@@ -611,7 +643,7 @@ PTO_INST RecordEvent TMATMUL_BIAS(TileAccT &cMatrix, TileLeftT &aMatrix, TileRig
                   "TMATMUL_BIAS: the bias has the accumulator's type");
     static_assert(TileAccT::Cols % 16 == 0, "TMATMUL_BIAS: accumulator width must be a multiple of 16");
     b200::matmul_check<TileAccT, TileLeftT, TileRightT>();
-    if constexpr (sizeof(typename TileLeftT::DType) != 2) {
+    if constexpr (!b200::is_tc_elem<typename TileLeftT::DType>::value) {
 #if PTO_B200_DEVICE_CODE
         b200::matmul_plain(cMatrix, aMatrix, bMatrix, 2, biasData.data());
 #endif
@@ -644,6 +676,154 @@ PTO_INST RecordEvent TMATMUL_BIAS(TileAccT &cMatrix, TileLeftT &aMatrix, TileRig
                                   WaitEvents &... events)
 {
     return TMATMUL_BIAS(cMatrix, aMatrix, bMatrix, biasData, events...);
+}
+
+// ---------------------------------------------------------------- TMATMUL_MX
+// MX block-scaled product (include/pto/common/pto_instr.hpp:403-460 in the reference; its backends are the A5 / Kirin
+// NPUs, there is no CPU simulation of it): C = (scaleA (x) A) * (scaleB (x) B), A [M x K] and B [K x N] in fp8 (e4m3 or
+// e5m2), one e8m0 scale per 32 consecutive k of a row of A / a column of B, fp32 accumulation.  On B200 this is
+// tcgen05.mma kind::mxf8f6f4 with block scaling: per 128 k the scale atoms (TEXTRACT writes ScaleLeft / ScaleRight
+// tiles as atoms) are copied from shared memory into tensor-memory columns kept for them (tcgen05.cp), then four
+// products of k = 32 each name their scale byte.  Both operands must be K-major (A loaded from an ND tensor, B from a
+// DN one, as the reference's MX kernels do); K a multiple of 32, N at most 256.
+namespace b200 {
+#if PTO_B200_DEVICE_CODE
+// shared-memory descriptor of a scale atom: 32 rows of 16 bytes, no swizzle; 8-row groups are 128 bytes apart
+__device__ __forceinline__ uint64_t scale_atom_desc(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu);
+    d |= static_cast<uint64_t>(128 >> 4) << 32;
+    d |= 1ull << 46;
+    return d;
+}
+// 32 rows x 16 bytes of shared memory -> tensor-memory columns [taddr, taddr + 4), repeated in the four lane quarters
+__device__ __forceinline__ void copy_scale_atom(uint32_t taddr, uint64_t desc)
+{
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void mma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa,
+                                         uint32_t sfb, uint32_t acc)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+#endif
+
+template <typename TileRes, typename TileLeftT, typename TileLeftScaleT, typename TileRightT, typename TileRightScaleT>
+PTO_INTERNAL void matmul_mx_issue(TileRes &c, TileLeftT &a, TileLeftScaleT &sa, TileRightT &b, TileRightScaleT &sb,
+                                  bool accumulate)
+{
+    using AT = typename TileLeftT::DType;
+    using BT = typename TileRightT::DType;
+    static_assert((std::is_same_v<AT, __nv_fp8_e4m3> || std::is_same_v<AT, __nv_fp8_e5m2>)&&(
+                      std::is_same_v<BT, __nv_fp8_e4m3> || std::is_same_v<BT, __nv_fp8_e5m2>),
+                  "TMATMUL_MX: fp8 (e4m3 or e5m2) operands");
+    static_assert(std::is_same_v<typename TileRes::DType, float>, "TMATMUL_MX: fp32 accumulator");
+    static_assert(TileLeftT::Loc == TileType::Left && TileRightT::Loc == TileType::Right && TileRes::Loc == TileType::Acc &&
+                      TileLeftScaleT::Loc == TileType::ScaleLeft && TileRightScaleT::Loc == TileType::ScaleRight,
+                  "TMATMUL_MX: expects (Acc, Left, ScaleLeft, Right, ScaleRight)");
+    static_assert(TileLeftT::Rows <= 128 && TileLeftT::Cols == TileRightT::Rows && TileLeftT::Cols % 32 == 0,
+                  "TMATMUL_MX: m <= 128, k a multiple of 32");
+    static_assert(TileRightT::Cols % 16 == 0 && TileRightT::Cols <= 256 && TileRes::Cols == TileRightT::Cols,
+                  "TMATMUL_MX: n a multiple of 16, at most 256");
+    static_assert(TileLeftScaleT::Cols * 32 == TileLeftT::Cols && TileRightScaleT::Rows * 32 == TileRightT::Rows,
+                  "TMATMUL_MX: one scale per 32 k");
+#if PTO_B200_DEVICE_CODE
+    constexpr int K = TileLeftT::Cols, N = TileRightT::Cols;
+    constexpr int kSpans = (K + 127) / 128, kAtomsK = (K / 32 + 3) / 4, kGroupsN = (N + 127) / 128;
+    if (control()->in_order) {
+        fence_async_proxy();
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        if (a.major_ != 0 || b.major_ != 0 || c.addr_ + N > kMxScaleTmemCol) {
+            give_up(-2); // operand not K-major, or the accumulator reaches into the scale columns: reported, not run
+        } else {
+            constexpr uint32_t a_fmt = std::is_same_v<AT, __nv_fp8_e5m2> ? 1u : 0u;
+            constexpr uint32_t b_fmt = std::is_same_v<BT, __nv_fp8_e5m2> ? 1u : 0u;
+            const uint32_t idesc = (a_fmt << 7) | (b_fmt << 10) | (static_cast<uint32_t>(N >> 3) << 17) | (1u << 23) | (8u << 24);
+            const uint32_t d_tmem = control()->tmem_base + c.addr_;
+            const uint32_t a_addr = smem_u32(arena_of<TileType::Left>() + a.addr_);
+            const uint32_t b_addr = smem_u32(arena_of<TileType::Right>() + b.addr_);
+            const uint32_t sa_addr = smem_u32(arena_of<TileType::ScaleLeft>() + sa.addr_);
+            const uint32_t sb_addr = smem_u32(arena_of<TileType::ScaleRight>() + sb.addr_);
+            tc_fence_after();
+#pragma unroll
+            for (int sp = 0; sp < kSpans; ++sp) {
+                // two slots of 4 (A) + 8 (B) columns in turn: a slot is rewritten two spans later, after the products
+                // that read it, by the same thread (the tensor pipe keeps issue order)
+                const uint32_t sfa_tmem = control()->tmem_base + kMxScaleTmemCol + (sp & 1) * 16;
+                const uint32_t sfb_tmem = sfa_tmem + 4;
+                copy_scale_atom(sfa_tmem, scale_atom_desc(sa_addr + sp * 512));
+#pragma unroll
+                for (int gn = 0; gn < kGroupsN; ++gn) {
+                    copy_scale_atom(sfb_tmem + gn * 4, scale_atom_desc(sb_addr + (gn * kAtomsK + sp) * 512));
+                }
+                const int kk_end = (K - sp * 128) >= 128 ? 4 : (K - sp * 128) / 32;
+                for (int kk = 0; kk < kk_end; ++kk) {
+                    const uint32_t kb = sp * 128 + kk * 32; // first k of this product, in bytes of a line
+                    const uint64_t a_desc = sw128_desc(a_addr + (kb >> 7) * a.pitch_ + (kb & 127u), 16, 1024);
+                    const uint64_t b_desc = sw128_desc(b_addr + (kb >> 7) * b.pitch_ + (kb & 127u), 16, 1024);
+                    const uint32_t sf_id = static_cast<uint32_t>(kk);
+                    mma_mxf8(d_tmem, a_desc, b_desc, idesc | (sf_id << 29) | (sf_id << 4), sfa_tmem, sfb_tmem,
+                             (accumulate || sp != 0 || kk != 0) ? 1u : 0u);
+                }
+            }
+        }
+    }
+    complete_matmul_if_in_order();
+#endif
+}
+} // namespace b200
+
+template <typename TileRes, typename TileLeftT, typename TileLeftScaleT, typename TileRightT, typename TileRightScaleT,
+          typename... WaitEvents,
+          std::enable_if_t<TileLeftScaleT::Loc == TileType::ScaleLeft && TileRightScaleT::Loc == TileType::ScaleRight, int> = 0>
+PTO_INST RecordEvent TMATMUL_MX(TileRes &cMatrix, TileLeftT &aMatrix, TileLeftScaleT &aScaleMatrix, TileRightT &bMatrix,
+                                TileRightScaleT &bScaleMatrix, WaitEvents &... events)
+{
+    TSYNC(events...);
+    b200::matmul_mx_issue(cMatrix, aMatrix, aScaleMatrix, bMatrix, bScaleMatrix, false);
+    return {};
+}
+template <AccPhase Phase, typename TileRes, typename TileLeftT, typename TileLeftScaleT, typename TileRightT,
+          typename TileRightScaleT, typename... WaitEvents,
+          std::enable_if_t<TileLeftScaleT::Loc == TileType::ScaleLeft && TileRightScaleT::Loc == TileType::ScaleRight, int> = 0>
+PTO_INST RecordEvent TMATMUL_MX(TileRes &cMatrix, TileLeftT &aMatrix, TileLeftScaleT &aScaleMatrix, TileRightT &bMatrix,
+                                TileRightScaleT &bScaleMatrix, WaitEvents &... events)
+{
+    TSYNC(events...);
+    b200::matmul_mx_issue(cMatrix, aMatrix, aScaleMatrix, bMatrix, bScaleMatrix, false);
+    return {};
+}
+// accumulating form: cOut = cIn + product (the accumulator is updated in place)
+template <typename TileRes, typename TileLeftT, typename TileLeftScaleT, typename TileRightT, typename TileRightScaleT,
+          typename... WaitEvents,
+          std::enable_if_t<TileLeftT::Loc == TileType::Left && TileLeftScaleT::Loc == TileType::ScaleLeft, int> = 0>
+PTO_INST RecordEvent TMATMUL_MX(TileRes &cOutMatrix, TileRes &cInMatrix, TileLeftT &aMatrix, TileLeftScaleT &aScaleMatrix,
+                                TileRightT &bMatrix, TileRightScaleT &bScaleMatrix, WaitEvents &... events)
+{
+    TSYNC(events...);
+    b200::acc_copy(cOutMatrix, cInMatrix);
+    b200::matmul_mx_issue(cOutMatrix, aMatrix, aScaleMatrix, bMatrix, bScaleMatrix, true);
+    return {};
+}
+template <AccPhase Phase, typename TileRes, typename TileLeftT, typename TileLeftScaleT, typename TileRightT,
+          typename TileRightScaleT, typename... WaitEvents,
+          std::enable_if_t<TileLeftT::Loc == TileType::Left && TileLeftScaleT::Loc == TileType::ScaleLeft, int> = 0>
+PTO_INST RecordEvent TMATMUL_MX(TileRes &cOutMatrix, TileRes &cInMatrix, TileLeftT &aMatrix, TileLeftScaleT &aScaleMatrix,
+                                TileRightT &bMatrix, TileRightScaleT &bScaleMatrix, WaitEvents &... events)
+{
+    TSYNC(events...);
+    b200::acc_copy(cOutMatrix, cInMatrix);
+    b200::matmul_mx_issue(cOutMatrix, aMatrix, aScaleMatrix, bMatrix, bScaleMatrix, true);
+    return {};
 }
 
 // ---------------------------------------------------------------- TSTORE
@@ -847,14 +1027,15 @@ PTO_INST RecordEvent TMOV(DstTileData &dst, SrcTileData &src, WaitEvents &... ev
         } else if constexpr (DstTileData::Loc == TileType::Left || DstTileData::Loc == TileType::Right) {
             static_assert(SrcTileData::Loc == TileType::Vec && SrcTileData::SFractal == SLayout::NoneBox,
                           "TMOV into a matrix operand: from a Mat tile or a plain Vec tile");
-            static_assert(sizeof(typename SrcTileData::DType) == 2, "matrix operands are 16-bit");
+            static_assert(b200::is_tc_elem<typename SrcTileData::DType>::value, "TMOV: half, bfloat16 or fp8 operands");
             static_assert(SrcTileData::Rows == DstTileData::Rows && SrcTileData::Cols == DstTileData::Cols,
                           "TMOV: shapes differ");
             constexpr bool cols_contig = SrcTileData::isRowMajor;
             constexpr int lines = cols_contig ? DstTileData::Rows : DstTileData::Cols;
             constexpr int span = cols_contig ? DstTileData::Cols : DstTileData::Rows;
-            static_assert(span % 8 == 0, "TMOV: the contiguous extent must be a multiple of 8 elements");
-            constexpr int chunks_per_line = span / 8;
+            constexpr int kCE = 16 / static_cast<int>(sizeof(typename SrcTileData::DType));
+            static_assert(span % kCE == 0, "TMOV: the contiguous extent must be a multiple of 16 bytes");
+            constexpr int chunks_per_line = span / kCE;
             constexpr uint32_t dst_pitch = static_cast<uint32_t>(lines) * 128u;
             const uint8_t *s = reinterpret_cast<const uint8_t *>(src.data());
             uint8_t *d = b200::arena_of<DstTileData::Loc>() + dst.addr_;
@@ -862,7 +1043,7 @@ PTO_INST RecordEvent TMOV(DstTileData &dst, SrcTileData &src, WaitEvents &... ev
                 const int l = q / chunks_per_line, ch = q - l * chunks_per_line;
                 const uint32_t d_off = (ch >> 3) * dst_pitch + l * 128u + (((ch & 7) ^ (l & 7)) << 4);
                 *reinterpret_cast<uint4 *>(d + d_off) =
-                    *reinterpret_cast<const uint4 *>(s + (static_cast<uint32_t>(l) * span + ch * 8) * 2u);
+                    *reinterpret_cast<const uint4 *>(s + (static_cast<uint32_t>(l) * span + ch * kCE) * sizeof(typename SrcTileData::DType));
             }
             dst.pitch_ = dst_pitch;
             const bool k_major = (DstTileData::Loc == TileType::Left) ? cols_contig : !cols_contig;

@@ -12,6 +12,7 @@
 //   Left     : [PTO_B200_L0A_OFFSET, PTO_B200_L0B_OFFSET)   48 KiB  (ping at 0, pong at 32 KiB, 16 KiB each)
 //   Right    : [PTO_B200_L0B_OFFSET, end of arena)          64 KiB+ (ping at 0, pong at 32 KiB, 32 KiB each)
 //   Bias     : a 1 KiB table in the control block (one row of up to 256 floats for TMATMUL_BIAS)
+//   ScaleLeft / ScaleRight : the last two 4 KiB of the arena (scale atoms of TMATMUL_MX)
 // Define the two macros before including the PTO headers to move the windows for a whole translation unit, or give
 // the offsets per launch (LaunchOptions).
 // 512 tensor-memory columns are allocated per block for Acc tiles.
@@ -72,6 +73,12 @@ struct Control {
 constexpr int kControlBytes = ((int)sizeof(Control) + 1023) / 1024 * 1024;
 static_assert(kControlBytes == 6 * 1024, "the control block is 6 KiB: the arena is the other 220 KiB");
 constexpr int kDefaultSmemBytes = 227 * 1024; // 1 KiB alignment slack + control (6 KiB) + 220 KiB arena
+// scale tiles of the MX product (TileType::ScaleLeft / ScaleRight) have windows of their own at the end of the arena:
+// 4 KiB each (a program that uses them keeps its Right window below 212 KiB)
+constexpr uint32_t kScaleRightOffset = 212 * 1024;
+constexpr uint32_t kScaleLeftOffset = 216 * 1024;
+// tensor-memory columns kept for the scales of TMATMUL_MX (accumulators of such a program stay below them)
+constexpr uint32_t kMxScaleTmemCol = 480;
 
 #if PTO_B200_DEVICE_CODE
 __device__ __forceinline__ uint8_t *smem_base()
@@ -98,6 +105,10 @@ __device__ __forceinline__ uint8_t *arena_of()
             return arena() + control()->l0a_offset;
         } else if constexpr (Loc == TileType::Right) {
             return arena() + control()->l0b_offset;
+        } else if constexpr (Loc == TileType::ScaleLeft) {
+            return arena() + kScaleLeftOffset;
+        } else if constexpr (Loc == TileType::ScaleRight) {
+            return arena() + kScaleRightOffset;
         } else {
             return arena();
         }

@@ -269,6 +269,21 @@ template <typename Element_, const int Rows_, const int Cols_, const int RowVali
 using TileAcc = Tile<TileType::Acc, Element_, Rows_, Cols_, BLayout::ColMajor, RowValid_, ColValid_, SLayout::RowMajor,
                      TileConfig::fractalCSize>;
 
+template <typename Element_, const int Rows_, const int Cols_, const int RowValid_ = Rows_, const int ColValid_ = Cols_>
+using TileLeftScale = Tile<TileType::ScaleLeft, Element_, Rows_, Cols_, BLayout::RowMajor, RowValid_, ColValid_,
+                           SLayout::RowMajor, TileConfig::fractalMxSize>;
+template <typename Element_, const int Rows_, const int Cols_, const int RowValid_ = Rows_, const int ColValid_ = Cols_>
+using TileRightScale = Tile<TileType::ScaleRight, Element_, Rows_, Cols_, BLayout::ColMajor, RowValid_, ColValid_,
+                            SLayout::ColMajor, TileConfig::fractalMxSize>;
+
+namespace b200 {
+// element types the tensor core reads from shared memory: their matrix tiles are kept in the 128-byte swizzle
+// (8- and 32-bit integers and fp32 are kept plain and multiplied on the CUDA cores)
+template <typename T>
+struct is_tc_elem : std::integral_constant<bool, std::is_same_v<T, __half> || std::is_same_v<T, __nv_bfloat16> ||
+                                                     std::is_same_v<T, __nv_fp8_e4m3> || std::is_same_v<T, __nv_fp8_e5m2>> {};
+} // namespace b200
+
 template <typename T>
 struct is_tile : std::false_type {};
 template <TileType L, typename E, int R, int C, BLayout B, int RV, int CV, SLayout S, int SS, PadValue P, CompactMode CM>

@@ -7,6 +7,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -41,6 +42,10 @@
 using half = __half;
 using aclFloat16 = __half;
 using bfloat16_t = __nv_bfloat16;
+// operand and scale types of the MX block-scaled product (include/pto/common/type.hpp in the reference)
+using float8_e4m3_t = __nv_fp8_e4m3;
+using float8_e5m2_t = __nv_fp8_e5m2;
+using float8_e8m0_t = __nv_fp8_e8m0;
 typedef void *aclrtStream;
 
 // ---------------------------------------------------------------- pipes and events

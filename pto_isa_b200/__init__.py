@@ -12,4 +12,5 @@ from .ops import (  # noqa: F401
     TCVT, TGATHER, TGATHER_MASK, TROWMAX, TROWSUM, TEXP, TROWEXPANDSUB, TROWEXPANDMUL, TROWEXPANDDIV,
     TROWEXPAND, TROWEXPANDADD, TROWEXPANDMAX, TROWEXPANDMIN, TROWEXPANDEXPDIF, TROWMIN, TCOLSUM, TCOLMAX, TCOLMIN,
     TFILLPAD, TTRANS, TTRI, TRESHAPE, TSEL, TCMPS, TCMP, TADD, TSUB, TMUL, TDIV, TMAX, TMIN, TMULS, TADDS, gemm, gemm_i8, gemm_out16, gemm_bf16, gemm_host, gemm_host_batched, mx_gemm, mx_gemm_fp4, flash_attn_fwd, flash_attn_fwd_host, device_status,
+    device_status_record, set_profile_buffer, probe_random_reads,
 )

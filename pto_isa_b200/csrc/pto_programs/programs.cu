@@ -618,6 +618,78 @@ AICORE inline void ProgMlaHead(__gm__ float *out, __gm__ half *q, __gm__ half *k
     TSTORE(go, acc_sd);
 }
 
+// ---------------------------------------------------------------- MX block-scaled product, two k blocks
+// The instruction sequence of the reference's MX kernels (kernels/manual/a5/matmul_mxfp8_performance/
+// mxmatmul_performance_kernel.cpp:24-36,120-150: TLOAD of the data and scale tiles, TEXTRACT of the current k block of
+// each, TMATMUL_MX for the first block and its accumulating form for the others, TSTORE with conversion to bfloat16).
+// A [M x K] fp8, B stored [N x K] fp8 (the DN view), scale A [M x K/32], scale B stored [N x K/32], e8m0.
+template <typename U, int M, int K, int N, int kBaseK>
+AICORE inline void ProgMxMatmul(__gm__ bfloat16_t *out, __gm__ U *a, __gm__ U *b, __gm__ float8_e8m0_t *sa,
+                                __gm__ float8_e8m0_t *sb)
+{
+    constexpr int S = K / 32, kBaseS = kBaseK / 32;
+    using GA = GlobalTensor<U, Shape<1, 1, 1, M, K>, Stride<1, 1, 1, K, 1>>;
+    using GB = GlobalTensor<U, Shape<1, 1, 1, K, N>, Stride<1, 1, 1, 1, K>, Layout::DN>;
+    using GSA = GlobalTensor<float8_e8m0_t, Shape<1, 1, 1, M, S>, Stride<1, 1, 1, S, 1>>;
+    using GSB = GlobalTensor<float8_e8m0_t, Shape<1, 1, 1, S, N>, Stride<1, 1, 1, 1, S>, Layout::DN>;
+    using GC = GlobalTensor<bfloat16_t, Shape<1, 1, 1, M, N>, Stride<1, 1, 1, N, 1>>;
+    using MatA = Tile<TileType::Mat, U, M, K, BLayout::ColMajor, M, K, SLayout::RowMajor>;
+    using MatB = Tile<TileType::Mat, U, K, N, BLayout::RowMajor, K, N, SLayout::ColMajor>;
+    using MatSA = Tile<TileType::Mat, float8_e8m0_t, M, S, BLayout::RowMajor, M, S, SLayout::RowMajor, 32>;
+    using MatSB = Tile<TileType::Mat, float8_e8m0_t, S, N, BLayout::ColMajor, S, N, SLayout::ColMajor, 32>;
+    MatA am;
+    MatB bm;
+    MatSA sam;
+    MatSB sbm;
+    TileLeft<U, M, kBaseK> al;
+    TileRight<U, kBaseK, N> br;
+    TileLeftScale<float8_e8m0_t, M, kBaseS> sal;
+    TileRightScale<float8_e8m0_t, kBaseS, N> sbr;
+    TileAcc<float, M, N> acc;
+    TASSIGN(am, 0x0);
+    TASSIGN(bm, M * K);
+    TASSIGN(sam, M * K + K * N);
+    TASSIGN(sbm, M * K + K * N + ((M * S + 1023) & ~1023));
+    TASSIGN(al, 0x0);
+    TASSIGN(br, 0x0);
+    TASSIGN(sal, 0x0);
+    TASSIGN(sbr, 0x0);
+    TASSIGN(acc, 0x0);
+    GA ga(a);
+    GB gb(b);
+    GSA gsa(sa);
+    GSB gsb(sb);
+    TLOAD(am, ga);
+    TLOAD(bm, gb);
+    TLOAD(sam, gsa);
+    TLOAD(sbm, gsb);
+    set_flag(PIPE_MTE2, PIPE_MTE1, EVENT_ID0);
+    wait_flag(PIPE_MTE2, PIPE_MTE1, EVENT_ID0);
+    for (int kb = 0; kb < K / kBaseK; ++kb) {
+        if (kb > 0) {
+            wait_flag(PIPE_M, PIPE_MTE1, EVENT_ID0); // the previous product has read the operand tiles
+        }
+        TEXTRACT(al, am, 0, kb * kBaseK);
+        TEXTRACT(br, bm, kb * kBaseK, 0);
+        TEXTRACT(sal, sam, 0, kb * kBaseS);
+        TEXTRACT(sbr, sbm, kb * kBaseS, 0);
+        set_flag(PIPE_MTE1, PIPE_M, EVENT_ID0);
+        wait_flag(PIPE_MTE1, PIPE_M, EVENT_ID0);
+        if (kb == 0) {
+            TMATMUL_MX(acc, al, sal, br, sbr);
+        } else {
+            TMATMUL_MX(acc, acc, al, sal, br, sbr);
+        }
+        if (kb + 1 < K / kBaseK) {
+            set_flag(PIPE_M, PIPE_MTE1, EVENT_ID0);
+        }
+    }
+    set_flag(PIPE_M, PIPE_FIX, EVENT_ID0);
+    wait_flag(PIPE_M, PIPE_FIX, EVENT_ID0);
+    GC gc(out);
+    TSTORE(gc, acc);
+}
+
 // ---------------------------------------------------------------- host entry points
 #pragma GCC visibility push(default)
 extern "C" {
@@ -743,6 +815,31 @@ int pto_prog_mla_head_128x64x64(float *out, const __half *q, const __half *k, co
            }) == cudaSuccess
                ? 0
                : 3;
+}
+
+// TMATMUL_MX: C[128 x 256] bf16 = (sa (x) A[128 x 256]) (sb (x) B[256 x 256])^T; fmt 0 = e4m3, 1 = e5m2; two k blocks of 128
+int pto_prog_mx_matmul_128x256x256(void *out, const void *a, const void *b, const void *sa, const void *sb, int fmt,
+                                   void *stream, int *status_dev)
+{
+    pto::b200::LaunchOptions opt;
+    opt.status = status_dev;
+    // matrix and scale tiles: 32 + 64 + 1 + 2 KiB; Left 16 KiB, Right 32 KiB
+    opt.l0a_offset = 116 * 1024;
+    opt.l0b_offset = 148 * 1024;
+    bfloat16_t *o = static_cast<bfloat16_t *>(out);
+    float8_e8m0_t *sa_ = static_cast<float8_e8m0_t *>(const_cast<void *>(sa));
+    float8_e8m0_t *sb_ = static_cast<float8_e8m0_t *>(const_cast<void *>(sb));
+    cudaError_t e;
+    if (fmt == 1) {
+        float8_e5m2_t *a_ = static_cast<float8_e5m2_t *>(const_cast<void *>(a));
+        float8_e5m2_t *b_ = static_cast<float8_e5m2_t *>(const_cast<void *>(b));
+        e = pto::b200::launch(1, stream, [=] __device__() { ProgMxMatmul<float8_e5m2_t, 128, 256, 256, 128>(o, a_, b_, sa_, sb_); }, opt);
+    } else {
+        float8_e4m3_t *a_ = static_cast<float8_e4m3_t *>(const_cast<void *>(a));
+        float8_e4m3_t *b_ = static_cast<float8_e4m3_t *>(const_cast<void *>(b));
+        e = pto::b200::launch(1, stream, [=] __device__() { ProgMxMatmul<float8_e4m3_t, 128, 256, 256, 128>(o, a_, b_, sa_, sb_); }, opt);
+    }
+    return e == cudaSuccess ? 0 : 3;
 }
 
 } // extern "C"

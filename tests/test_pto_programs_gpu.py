@@ -218,3 +218,22 @@ def test_mla_head_program(prog, golden_dir):
         arrs = [np.ascontiguousarray(z[n]) for n in ("q", "k", "v", "wq", "wk", "wv", "wo")]
         assert oracle.ref.lib.pto_ref_mla_head_f16_128x64x64(*[P(a) for a in arrs], P(o2), ctypes.c_float(float(z["scale"]))) == 0
         assert np.array_equal(o2, z["o"])
+
+
+@pytest.mark.parametrize("fmt", [1, 0], ids=["e5m2", "e4m3"])
+def test_tmatmul_mx_tile_program(prog, fmt):
+    """TMATMUL_MX as a tile instruction (include/pto/common/pto_instr.hpp:403-460 in the reference): TLOAD of fp8 data and
+    e8m0 scale tiles, TEXTRACT of the k block of each (the scale tiles become the tensor core's atoms), the product
+    with block scaling and its accumulating form, TSTORE with conversion to bfloat16.  Checked like the C-ABI MX GEMM:
+    against the oracle's exact sums, within one bfloat16 ulp."""
+    from test_mxgemm_gpu import check_bf16, make
+    m, n, k = 128, 256, 256
+    a, b, sa, sb = make(m, n, k, fmt, seed=31 + fmt)
+    want = port.mxgemm_fp8(a, b, sa, sb, fmt, fmt)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    assert prog.pto_prog_mx_matmul_128x256x256(_ptr(out), _ptr(dev(a)), _ptr(dev(b)), _ptr(dev(sa)), _ptr(dev(sb)), fmt,
+                                               _stream(), _ptr(status)) == 0
+    torch.cuda.synchronize()
+    assert host(status).tolist() == [0, 0, 0, 0]
+    check_bf16(host(out.view(torch.int16)).view(np.uint16), want)
