@@ -1,7 +1,9 @@
 """GPU parity of flash-attention forward against the CPU oracle (the reference's instruction sequence with
 fp16 operands, fp32 softmax, fp16 P) and the golden output of the reference's NumPy model of its kernel.
 
-Tolerance (util.attn_err_ok): relative error |got - want| / max(|want|, rms(want)) <= 2e-3 for EVERY element.
+Tolerance (util.attn_err_ok): relative error |got - want| / max(|want|, rms(want)) <= 2e-3 for EVERY element; only the
+causal rows that see fewer than 128 keys get, on top, one flipped fp16 ulp of their largest weight
+(util.few_key_allowance, derived there).
 A half-precision output must be the round-to-nearest-even of the fp32 output bit for bit; where only the
 half-precision output exists it is compared with the oracle's fp32 output with half an fp16 ulp added for
 that rounding.  Every test prints its worst error (pytest -s, or the captured output of a failure)."""
@@ -13,7 +15,7 @@ import torch
 
 import oracle
 import pto_isa_b200 as pto
-from util import attn_err_ok, dev, host, result_cmp
+from util import attn_err_ok, dev, few_key_allowance, host, result_cmp
 
 pytestmark = pytest.mark.gpu
 port = oracle.port
@@ -39,7 +41,8 @@ def test_attention_matches_oracle(shape, causal):
     assert pto.device_status() == 0
     for h in range(bh):
         want = port.attn_head_f16(q[h], k[h], v[h], int(causal), scale)
-        ok, worst, _ = attn_err_ok(o[h], want, label=f"{shape} causal={causal} head {h}")
+        ok, worst, _ = attn_err_ok(o[h], want, label=f"{shape} causal={causal} head {h}",
+                                   allowance=few_key_allowance(q[h], k[h], v[h], scale, causal))
         assert ok, f"head {h}: max relative error {worst:.3e}"
 
 
@@ -60,9 +63,11 @@ def test_attention_internal_scale_and_fp16_output(causal):
     assert np.array_equal(o16e, o32.astype(np.float16))
     for h in range(bh):
         want = port.attn_head_f16(q[h], k[h], v[h], int(causal), scale)
-        ok, worst, _ = attn_err_ok(o32[h], want, label=f"internal scale causal={causal} head {h}")
+        ok, worst, _ = attn_err_ok(o32[h], want, label=f"internal scale causal={causal} head {h}",
+                                   allowance=few_key_allowance(q[h], k[h], v[h], scale, causal))
         assert ok, f"head {h}: max relative error {worst:.3e}"
-        ok, worst, _ = attn_err_ok(o16[h].astype(np.float32), want, half_output=True)
+        ok, worst, _ = attn_err_ok(o16[h].astype(np.float32), want, half_output=True,
+                                   allowance=few_key_allowance(q[h], k[h], v[h], scale, causal))
         assert ok, f"head {h} (fp16 out): max relative error {worst:.3e}"
 
 
@@ -91,7 +96,8 @@ def test_attention_large_logits_rescale_path():
     for causal in (False, True):
         o = host(pto.flash_attn_fwd(dev(q), dev(k), dev(v), causal=causal, out_dtype=torch.float32))
         want = port.attn_head_f16(q[0], k[0], v[0], int(causal), scale)
-        ok, worst, _ = attn_err_ok(o[0], want, label=f"growing maxima causal={causal}")
+        ok, worst, _ = attn_err_ok(o[0], want, label=f"growing maxima causal={causal}",
+                                   allowance=few_key_allowance(q[0], k[0], v[0], scale, causal))
         assert ok, f"causal={causal}: max relative error {worst:.3e}"
 
 
@@ -119,7 +125,8 @@ def test_attention_full_size_sampled_heads(causal):
     for h in (0, 77, 127):
         want = port.attn_head_f16(host(q[h]), host(k[h]), host(v[h]), int(causal), 1.0)
         ok, worst, _ = attn_err_ok(host(o[h]).astype(np.float32), want, half_output=True,
-                                   label=f"B4 H32 S4096 causal={causal} head {h}")
+                                   label=f"B4 H32 S4096 causal={causal} head {h}",
+                                   allowance=few_key_allowance(host(q[h]), host(k[h]), host(v[h]), 1.0, causal))
         assert ok, f"head {h}: max relative error {worst:.3e}"
     if causal:
         vmax = torch.cummax(v.float(), dim=1).values
@@ -146,7 +153,8 @@ def test_attention_long_sequence_causal_sampled_rows():
     for h in (0, 5):
         # first 256 queries: a square causal problem of its own
         want = port.attn_head_f16(host(q[h, :256]), host(k[h, :256]), host(v[h, :256]), 1, 1.0)
-        ok, worst, _ = attn_err_ok(host(o[h, :256]), want, label=f"S8192 head {h} first 256 rows")
+        ok, worst, _ = attn_err_ok(host(o[h, :256]), want, label=f"S8192 head {h} first 256 rows",
+                                   allowance=few_key_allowance(host(q[h, :256]), host(k[h, :256]), host(v[h, :256]), 1.0, True))
         assert ok, f"head {h} first rows: max relative error {worst:.3e}"
         # last 128 queries against all keys: row i of the block may see keys 0 .. s - 128 + i; the oracle's causal mask
         # works on square problems, so every row is checked as the last row of the problem made of keys 0 .. its own
