@@ -2,8 +2,8 @@
 // GEMM tile program as gemm.cu (TLOAD -> TMA, TEXTRACT -> descriptor window, TMATMUL -> tcgen05.mma, TSTORE ->
 // tcgen05.ld + stores, flags -> mbarrier rings), with two thread blocks of a cluster working on one
 // 256 x 256 C tile.  Each block stages its own 128 rows of A and only *half* of the B tile per k step
-// (32 KiB instead of 48 KiB), the MMA of the pair reads both halves, so the shared-memory ring is 6 stages
-// deep and the L2 -> SM traffic per FLOP drops by a third.  Each block ends up with 128 rows x 256 columns
+// (for a 128-deep k step 64 KiB instead of 96 KiB: a ring of three stages), the MMA of the pair reads both
+// halves, so the L2 -> SM traffic per FLOP drops by a third.  Each block ends up with 128 rows x 256 columns
 // of the accumulator in its own tensor memory and stores them itself.
 //
 // Cross-block signalling (no multicast anywhere):
@@ -52,8 +52,9 @@ constexpr int kSlabBytes = 32 * 32 * 4;
 constexpr int kStagingBytes = 4 * 2 * kSlabBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + sizeof(Control) + 1024;
 
-// C tiles are walked in bands of kGroupN tile columns, tile rows fastest inside a band, so that the tiles in
-// flight at any time (one per block pair) form a roughly square patch: their A and B panels stay in L2.
+// C tiles are walked in bands of kGroupN tile columns; inside a band the tile column moves fastest, then the
+// tile row, so that the tiles in flight at any time (one per block pair: 74 tiles = about nine tile rows of a
+// band) form a roughly square patch whose A and B panels stay in L2.
 constexpr int kGroupN = 8;
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &tm, int &tn)
 {
@@ -211,6 +212,7 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
     volatile int *abort_flag = &ctl->abort_flag;
+    const uint32_t peer_abort = map_to_rank(&ctl->abort_flag, rank ^ 1u);
 
     if (warp == 0) {
         // ------------------------------------------------------------ TLOAD: TMA producer (both blocks)
@@ -223,7 +225,7 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 const int row0 = tm * 2 * BM + static_cast<int>(rank) * BM; // this block's rows of A and C
                 const int col0 = tn * BN + static_cast<int>(rank) * BNH;    // this block's half of the B tile
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) {
+                    if (!mbar_wait_pair(&ctl->empty[stage], phase ^ 1u, abort_flag, peer_abort)) {
                         ok = false;
                         break;
                     }
@@ -271,13 +273,13 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const uint32_t empty_mine = map_to_rank(&ctl->empty[0], 0);
             const uint32_t empty_peer = map_to_rank(&ctl->empty[0], 1);
             for (int t = pair; t < num_tiles && ok; t += pairs) {
-                if (!mbar_wait(&ctl->acc_empty[acc], acc_phase ^ 1u, abort_flag)) {
+                if (!mbar_wait_pair(&ctl->acc_empty[acc], acc_phase ^ 1u, abort_flag, peer_abort)) {
                     break;
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(&ctl->full[stage], phase, abort_flag)) {
+                    if (!mbar_wait_pair(&ctl->full[stage], phase, abort_flag, peer_abort)) {
                         ok = false;
                         break;
                     }
@@ -327,7 +329,7 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int t = pair; t < num_tiles; t += pairs) {
             int tm, tn;
             tile_coords(t, tiles_m, tiles_n, tm, tn);
-            if (!mbar_wait(&ctl->acc_full[acc], acc_phase, abort_flag)) {
+            if (!mbar_wait_pair(&ctl->acc_full[acc], acc_phase, abort_flag, peer_abort)) {
                 break;
             }
             tc_fence_after();

@@ -66,8 +66,10 @@ constexpr int kSlabsPerWarp = 1;
 constexpr int kStagingBytes = 4 * kSlabsPerWarp * kSlabBytes;
 __host__ __device__ constexpr int smem_bytes(int atoms)
 {
-    // the fp4 layout fills the 227 KB to the last kilobyte: its buffer is declared 1024-byte aligned instead of being
-    // aligned by hand inside a larger allocation
+    // the fp4 layout (3 x 70 KiB of stages + 16 KiB of store staging + the barriers) ends 944 bytes under the 227 KiB
+    // a block may have, so there is no room for the 1 KiB of slack that aligning by hand inside a larger allocation
+    // takes: its buffer is declared 1024-byte aligned, and the kernel checks the address and reports instead of running
+    // if the declaration was not honoured
     return kStages * stage_bytes(atoms) + kStagingBytes + static_cast<int>(sizeof(Control)) + (atoms == 1 ? 1024 : 0);
 }
 
@@ -300,6 +302,7 @@ mxgemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
     volatile int *abort_flag = &ctl->abort_flag;
+    const uint32_t peer_abort = map_to_rank(&ctl->abort_flag, rank ^ 1u);
 
     if (warp == 0) {
         // ------------------------------------------------------------ TLOAD: TMA producer (both blocks)
@@ -314,7 +317,7 @@ mxgemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 const int sfa_row0 = (tm * 2 + static_cast<int>(rank)) * katoms;
                 const int sfb_row0 = tn * katoms;
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) {
+                    if (!mbar_wait_pair(&ctl->empty[stage], phase ^ 1u, abort_flag, peer_abort)) {
                         ok = false;
                         break;
                     }
@@ -359,7 +362,7 @@ mxgemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 // (and all of the tile before that, which used this accumulator)
                 int ok = 1;
                 if (lane == 0) {
-                    ok = mbar_wait(&ctl->acc_empty, acc_phase ^ 1u, abort_flag) ? 1 : 0;
+                    ok = mbar_wait_pair(&ctl->acc_empty, acc_phase ^ 1u, abort_flag, peer_abort) ? 1 : 0;
                 }
                 if (__shfl_sync(0xffffffffu, ok, 0) == 0) {
                     break;
@@ -369,7 +372,7 @@ mxgemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 ++local_tile;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (lane == 0) {
-                        ok = mbar_wait(&ctl->full[stage], phase, abort_flag) ? 1 : 0;
+                        ok = mbar_wait_pair(&ctl->full[stage], phase, abort_flag, peer_abort) ? 1 : 0;
                     }
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if (ok == 0) {
@@ -436,7 +439,7 @@ mxgemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int t = pair; t < num_tiles; t += pairs) {
             int tm, tn;
             tile_coords(t, tiles_m, tiles_n, tm, tn);
-            if (!mbar_wait(&ctl->acc_full, acc_phase, abort_flag)) {
+            if (!mbar_wait_pair(&ctl->acc_full, acc_phase, abort_flag, peer_abort)) {
                 break;
             }
             tc_fence_after();

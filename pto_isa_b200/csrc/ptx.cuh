@@ -153,6 +153,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     return false;
 }
 
+// The same wait inside a cluster of two blocks: a block that gives up also raises the abort flag of its peer
+// (`peer_abort` = the flag's shared::cluster address in the other block), so that the peer's roles stop at
+// their next poll instead of each running out its own limit.  Both blocks meet at a cluster barrier before
+// either leaves, so the peer's shared memory is alive when the store lands.
+__device__ __forceinline__ bool mbar_wait_pair(uint64_t *bar, uint32_t parity, volatile int *abort_flag, uint32_t peer_abort)
+{
+    if (mbar_wait(bar, parity, abort_flag)) {
+        return true;
+    }
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer_abort), "r"(1u) : "memory");
+    return false;
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map)
 {
