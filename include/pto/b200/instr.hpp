@@ -1027,9 +1027,22 @@ PTO_INST RecordEvent TMOV(DstTileData &dst, SrcTileData &src, WaitEvents &... ev
         } else if constexpr (DstTileData::Loc == TileType::Left || DstTileData::Loc == TileType::Right) {
             static_assert(SrcTileData::Loc == TileType::Vec && SrcTileData::SFractal == SLayout::NoneBox,
                           "TMOV into a matrix operand: from a Mat tile or a plain Vec tile");
-            static_assert(b200::is_tc_elem<typename SrcTileData::DType>::value, "TMOV: half, bfloat16 or fp8 operands");
             static_assert(SrcTileData::Rows == DstTileData::Rows && SrcTileData::Cols == DstTileData::Cols,
                           "TMOV: shapes differ");
+            if constexpr (!b200::is_tc_elem<typename SrcTileData::DType>::value) {
+                // 8- and 32-bit operands are multiplied on the CUDA cores from plain row-major tiles
+                static_assert(sizeof(typename SrcTileData::DType) == sizeof(typename DstTileData::DType), "TMOV: element sizes differ");
+                const typename SrcTileData::DType *s = src.data();
+                auto *d = reinterpret_cast<typename SrcTileData::DType *>(b200::arena_of<DstTileData::Loc>() + dst.addr_);
+                for (int i = threadIdx.x; i < DstTileData::Rows * DstTileData::Cols; i += blockDim.x) {
+                    const int r = i / DstTileData::Cols, c = i - r * DstTileData::Cols;
+                    d[i] = s[b200::vec_offset<SrcTileData>(r, c)];
+                }
+                dst.pitch_ = 0;
+                dst.major_ = b200::kPlain;
+                __syncthreads();
+                return {};
+            }
             constexpr bool cols_contig = SrcTileData::isRowMajor;
             constexpr int lines = cols_contig ? DstTileData::Rows : DstTileData::Cols;
             constexpr int span = cols_contig ? DstTileData::Cols : DstTileData::Rows;

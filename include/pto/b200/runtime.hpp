@@ -123,6 +123,44 @@ __device__ __forceinline__ int flag_index(int src, int dst, int id)
     return ((src & 7) * kNumPipes + (dst & 7)) * EVENT_ID_MAX + (id & 7);
 }
 
+// The bump allocator behind freshly constructed tiles (tile.hpp).  A pipe has no flags with itself (pipe_barrier
+// orders a pipe with itself), so the eight flag words of PIPE_S -> PIPE_S are never barriers: they hold the
+// allocator's counters, four 16-bit counters per warp (every lane of a warp constructs the same tiles in the same
+// order, and so does every warp of a block, so all threads arrive at the same addresses without exchanging any).
+// Counters are in units of 1 KiB for the shared-memory windows (the swizzled layouts want that alignment) and of
+// 32 columns for tensor memory.
+static_assert(PIPE_S == 0 && kWarps * 4 * sizeof(uint16_t) == EVENT_ID_MAX * sizeof(uint64_t),
+              "the tile allocator's counters occupy the flag words of PIPE_S -> PIPE_S");
+__device__ __forceinline__ uint32_t tile_auto_place(int space, uint32_t amount)
+{
+    Control *c = control();
+    volatile uint16_t *ctr = reinterpret_cast<volatile uint16_t *>(&c->flags[0]) + (threadIdx.x >> 5) * 4 + space;
+    const bool tmem = space == kSpaceAcc;
+    const uint32_t unit = tmem ? 32u : 1024u;
+    const uint32_t want = (amount + unit - 1) / unit;
+    uint32_t limit;
+    if (tmem) {
+        limit = kTmemCols / 32;
+    } else if (space == kSpaceVec) {
+        limit = (c->l0a_offset < c->l0b_offset ? c->l0a_offset : c->l0b_offset) / 1024u;
+    } else if (space == kSpaceLeft) {
+        limit = ((c->l0b_offset > c->l0a_offset ? c->l0b_offset : kScaleRightOffset) - c->l0a_offset) / 1024u;
+    } else {
+        limit = ((c->l0a_offset > c->l0b_offset ? c->l0a_offset : kScaleRightOffset) - c->l0b_offset) / 1024u;
+    }
+    __syncwarp();
+    const uint32_t at = *ctr;
+    __syncwarp();
+    if (at + want > limit) {
+        return 0; // the window is used up: the tile has to be assigned an address before it is used
+    }
+    if ((threadIdx.x & 31) == 0) {
+        *ctr = static_cast<uint16_t>(at + want);
+    }
+    __syncwarp();
+    return at * unit;
+}
+
 // ---- mbarrier primitives (bounded waits: a wait that runs out raises the block's abort flag)
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
 {
@@ -220,7 +258,11 @@ __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, ui
         // a flag raised by the matrix pipe is signalled by one tcgen05.commit; every other pipe's work is
         // done by all threads, so all of them arrive
         const int src = f / (kNumPipes * EVENT_ID_MAX);
-        mbar_init(&ctl->flags[f], src == PIPE_M ? 1u : static_cast<uint32_t>(nthreads));
+        if (f < EVENT_ID_MAX) {
+            ctl->flags[f] = 0; // PIPE_S -> PIPE_S: the tile allocator's counters (tile_auto_place)
+        } else {
+            mbar_init(&ctl->flags[f], src == PIPE_M ? 1u : static_cast<uint32_t>(nthreads));
+        }
     }
     if ((threadIdx.x & 31) == 0) {
         for (int w = 0; w < kNumFlags / 32; ++w) {
@@ -377,6 +419,10 @@ PTO_INTERNAL uint32_t get_block_num()
 PTO_INTERNAL void set_flag(pipe_t src, pipe_t dst, int id)
 {
 #if PTO_B200_DEVICE_CODE
+    if (src == dst) {
+        __syncthreads(); // a pipe is ordered with itself by a barrier, not a flag
+        return;
+    }
     uint64_t *bar = &pto::b200::control()->flags[pto::b200::flag_index(src, dst, id)];
     if (src == PIPE_M) {
         if (threadIdx.x == 0) {
@@ -401,6 +447,9 @@ PTO_INTERNAL void set_flag(pipe_t src, pipe_t dst, int id)
 PTO_INTERNAL void wait_flag(pipe_t src, pipe_t dst, int id)
 {
 #if PTO_B200_DEVICE_CODE
+    if (src == dst) {
+        return; // see set_flag
+    }
     pto::b200::Control *ctl = pto::b200::control();
     const int f = pto::b200::flag_index(src, dst, id);
     // all lanes of a warp run the same instruction stream, so the phase is kept once per warp

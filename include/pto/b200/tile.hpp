@@ -175,6 +175,24 @@ namespace b200 {
 // how a staged Mat tile lies in shared memory (decided by TLOAD from the global tensor's contiguous dimension)
 // kPlain: 8- and 32-bit matrix tiles, stored row-major Rows x Cols without swizzle (not read by the tensor core)
 enum : uint8_t { kColsContiguous = 0, kRowsContiguous = 1, kPlain = 2 };
+
+// A tile is constructed with storage of its own, as in the reference's CPU simulation where every tile object owns an
+// array (include/pto/common/pto_tile.hpp, the `data_` member under __CPU_SIM): the constructor takes the next free
+// stretch of its location's window (Vec and Mat tiles share one, Left, Right and Acc have their own) from a bump
+// allocator of the block, and TASSIGN replaces that address as on the NPU.  Programs that assign every tile never
+// see the difference; programs written for the simulation alone, which assign none, get distinct tiles.  Storage is
+// not handed back: once a window is used up, further tiles are placed at its start (and must be assigned before use).
+enum : int { kSpaceVec = 0, kSpaceLeft = 1, kSpaceRight = 2, kSpaceAcc = 3, kSpaceNone = 4 };
+#if PTO_B200_DEVICE_CODE
+__device__ __forceinline__ uint32_t tile_auto_place(int space, uint32_t amount);
+#endif
+constexpr int tile_space(TileType loc)
+{
+    return (loc == TileType::Vec || loc == TileType::Mat)
+               ? kSpaceVec
+               : (loc == TileType::Left ? kSpaceLeft
+                                        : (loc == TileType::Right ? kSpaceRight : (loc == TileType::Acc ? kSpaceAcc : kSpaceNone)));
+}
 } // namespace b200
 
 template <TileType Loc_, typename Element_, const int Rows_, const int Cols_,
@@ -214,24 +232,29 @@ struct Tile {
 
     static_assert(Rows > 0 && Cols > 0 && ValidRow <= Rows && ValidCol <= Cols, "invalid tile shape");
 
-    PTO_INTERNAL Tile() {}
+    PTO_INTERNAL Tile() { place(); }
     template <int RM = ValidRow, int CM = ValidCol>
     PTO_INTERNAL Tile(std::enable_if_t<RM == DYNAMIC && CM == DYNAMIC, size_t> vr,
                       std::enable_if_t<RM == DYNAMIC && CM == DYNAMIC, size_t> vc)
     {
         RowMaskInternal = static_cast<int>(vr);
         ColMaskInternal = static_cast<int>(vc);
+        place();
     }
     template <int RM = ValidRow, int CM = ValidCol>
     PTO_INTERNAL Tile(std::enable_if_t<(RM == DYNAMIC) && (CM > 0), size_t> vr)
     {
         RowMaskInternal = static_cast<int>(vr);
+        place();
     }
     template <int RM = ValidRow, int CM = ValidCol>
     PTO_INTERNAL Tile(std::enable_if_t<(RM > 0) && (CM == DYNAMIC), size_t> vc)
     {
         ColMaskInternal = static_cast<int>(vc);
+        place();
     }
+    Tile(const Tile &) = default;
+    Tile &operator=(const Tile &) = default;
 
     PTO_INTERNAL int GetValidRow() const { return ValidRow == DYNAMIC ? RowMaskInternal : ValidRow; }
     PTO_INTERNAL int GetValidCol() const { return ValidCol == DYNAMIC ? ColMaskInternal : ValidCol; }
@@ -251,6 +274,19 @@ struct Tile {
 
     int RowMaskInternal = ValidRow == DYNAMIC ? 0 : ValidRow;
     int ColMaskInternal = ValidCol == DYNAMIC ? 0 : ValidCol;
+
+    // storage of its own for a freshly constructed tile (see b200::tile_auto_place)
+    PTO_INTERNAL void place()
+    {
+#if PTO_B200_DEVICE_CODE
+        constexpr int space = b200::tile_space(Loc);
+        if constexpr (space == b200::kSpaceAcc) {
+            addr_ = b200::tile_auto_place(space, static_cast<uint32_t>(Cols)); // tensor-memory columns
+        } else if constexpr (space != b200::kSpaceNone) {
+            addr_ = b200::tile_auto_place(space, static_cast<uint32_t>(Numel * sizeof(DType)));
+        }
+#endif
+    }
 
     // ---- backend handle
     uint32_t addr_ = 0;   // Vec / Mat / Left / Right: byte offset in the tile location's window of the arena;

@@ -55,6 +55,9 @@ template <typename T, int kGRows_, int kGCols_, int kTRows_, int kTCols_>
 void LaunchTROWSUM(T *out, T *src, void *stream);
 template <typename T, int kGRows_, int kGCols_, int kTRows_, int kTCols_>
 void LaunchTExp(T *out, T *src, void *stream);
+// the flash-attention unit-test program, one 64 x 32 fp32 head (tests/cpu/st/testcase/tflashattn/tflashattn_kernel.cpp:
+// 110-114), the reference's own tile program compiled for B200
+void LaunchTFLASHATTN(float *out, float *q, float *k, float *v, void *stream);
 // keys as in the reference: 1 half 40 x 50 x 60, 2 int8 6 x 7 x 8, 3 five accumulated half 128 x 128 x 64 products,
 // 4 float 120 x 110 x 50; bias keys 1 int8 8 x 7 x 6, 2 half 16 x 15 x 16, 5 float 127 x 128 x 63.  These run the
 // reference's own tile programs compiled for B200 (libpto_b200_refkernels.so).

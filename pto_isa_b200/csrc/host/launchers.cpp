@@ -12,6 +12,7 @@ extern "C" {
 int pto_refk_tmatmul(int key, uint8_t *out, uint8_t *src0, uint8_t *src1, void *stream) __attribute__((weak));
 int pto_refk_tmatmul_bias(int key, uint8_t *out, uint8_t *src0, uint8_t *src1, uint8_t *src2, void *stream)
     __attribute__((weak));
+int pto_refk_tflashattn_64x32(float *out, float *q, float *k, float *v, void *stream, int *status_dev) __attribute__((weak));
 }
 
 namespace {
@@ -152,6 +153,13 @@ template void LaunchTMATMUL<1>(uint8_t *, uint8_t *, uint8_t *, void *);
 template void LaunchTMATMUL<2>(uint8_t *, uint8_t *, uint8_t *, void *);
 template void LaunchTMATMUL<3>(uint8_t *, uint8_t *, uint8_t *, void *);
 template void LaunchTMATMUL<4>(uint8_t *, uint8_t *, uint8_t *, void *);
+
+void LaunchTFLASHATTN(float *out, float *q, float *k, float *v, void *stream)
+{
+    g_status = pto_refk_tflashattn_64x32 != nullptr
+                   ? pto_refk_tflashattn_64x32(out, q, k, v, stream, static_cast<int *>(pto_b200_status_record()))
+                   : PTO_B200_ERR_UNSUPPORTED_SHAPE;
+}
 
 template <int32_t tilingKey>
 void LaunchTMATMULBIAS(uint8_t *out, uint8_t *src0, uint8_t *src1, uint8_t *src2, void *stream)

@@ -238,6 +238,28 @@ def test_reference_row_and_exp_programs(refk):
     assert ok, f"TEXP max relative error {worst:.3e}"
 
 
+# ---------------------------------------------------------------- the flash-attention unit-test program
+def test_reference_tflashattn_program(refk, golden_dir):
+    """tests/cpu/st/testcase/tflashattn/tflashattn_kernel.cpp unchanged: a 64 x 32 fp32 head in fifteen instructions
+    with no TASSIGN (every tile keeps the storage it was constructed with) and no flags.  Checked against the golden of
+    the reference's generator at the unit test's eps (tflashattn/main.cpp:42-44, 2e-4) and against the oracle's
+    restatement of the same instruction sequence, from which it may differ only by the exponential's last bits and
+    the row sum's order."""
+    z = np.load(os.path.join(golden_dir, "attention.npz"))
+    q, k, v, g = (np.ascontiguousarray(z[f"tflashattn_{n}"]) for n in ("q", "k", "v", "golden"))
+    out = torch.full((64, 32), 7.0, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    assert refk.pto_refk_tflashattn_64x32(_ptr(out), _ptr(dev(q)), _ptr(dev(k)), _ptr(dev(v)), _stream(), _ptr(status)) == 0
+    torch.cuda.synchronize()
+    assert host(status).tolist() == [0, 0, 0, 0]
+    assert result_cmp(g, host(out), 2e-4)
+    want = np.empty_like(g)
+    P = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    port.lib.pto_oracle_attn_head_f32_plain(P(q), P(k), P(v), P(want), 64, 32)
+    ok, worst = rel_err_ok(host(out), want, 1e-5, label="tflashattn unit-test program 64x32 f32")
+    assert ok, f"max relative error {worst:.3e}"
+
+
 # ---------------------------------------------------------------- TEXTRACT, bit for bit
 @pytest.mark.parametrize("which,kstep", [(0, 0), (1, 0), (2, 0), (3, 0), (3, 3), (4, 0), (4, 2), (5, 0), (6, 0)])
 def test_textract_windows_bit_exact(refk, which, kstep):
