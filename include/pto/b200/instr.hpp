@@ -39,7 +39,7 @@ PTO_INTERNAL int vec_offset(int r, int c)
 #if PTO_B200_DEVICE_CODE
 __device__ __forceinline__ void block_sync()
 {
-    __syncthreads();
+    b200::sync();
 }
 
 __device__ __forceinline__ uint64_t sw128_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
@@ -240,6 +240,9 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
     using T = typename TileData::DType;
     const T *g = reinterpret_cast<const T *>(src.data());
     const int64_t s3 = src.GetStride(3), s4 = src.GetStride(4);
+    if (b200::runs(PIPE_MTE2)) {
+        b200::stamp(0x4000);
+    }
     if constexpr (TileData::Loc == TileType::Mat && b200::is_tc_elem<T>::value) {
         // tiles the tensor core reads: the global tensor's unit-stride dimension decides the staged layout; a line is
         // 128 bytes of the contiguous dimension (64 16-bit or 128 8-bit elements), 16-byte chunks swizzled by the line
@@ -256,7 +259,36 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
         // 16-byte asynchronous copies need 16-byte aligned sources; ragged rows are fetched element by element
         const bool aligned = ((reinterpret_cast<uintptr_t>(g) | static_cast<uintptr_t>(line_stride * sizeof(T))) & 15u) == 0 &&
                              !__isShared(g); // (a FIFO entry may lie in the block's own shared memory)
-        for (int q = threadIdx.x; q < lines * chunks_per_line; q += blockDim.x) {
+        const int team = b200::nthreads_l(), me = b200::tid_l();
+        const int lines_per_step = team / chunks_per_line;
+        if (aligned && v_lines == lines && v_span == span && lines_per_step * chunks_per_line == team &&
+            (lines_per_step & 3) == 0) {
+            // whole tile from aligned rows, the team a whole number of lines: a thread keeps its chunk column and walks
+            // the lines, so source and destination advance by constants (the swizzle term depends on the line number's
+            // low three bits only: constant for a step of eight lines, one flipped bit for a step of four)
+            if (me < team) {
+                const int ch = me % chunks_per_line, l0 = me / chunks_per_line;
+                uint32_t off = base + (ch >> 3) * pitch + l0 * 128u + (((ch & 7) ^ (l0 & 7)) << 4);
+                const uint32_t flip = (lines_per_step & 4) ? 64u : 0u;
+                const uint32_t step = static_cast<uint32_t>(lines_per_step) * 128u;
+                const T *gp = g + l0 * line_stride + ch * kCE;
+                const int64_t gstep = lines_per_step * line_stride;
+#pragma unroll 4
+                for (int l = l0; l < lines; l += lines_per_step) {
+                    b200::cp_async16(off, gp, 16);
+                    gp += gstep;
+                    off = (off + step) ^ flip;
+                }
+            }
+            dst.pitch_ = pitch;
+            dst.major_ = cols_contig ? b200::kColsContiguous : b200::kRowsContiguous;
+            b200::complete_copies_if_in_order();
+            if (b200::runs(PIPE_MTE2)) {
+                b200::stamp(0x4001);
+            }
+            return {};
+        }
+        for (int q = b200::tid_l(), q_step = b200::nthreads_l(); q < lines * chunks_per_line; q += q_step) {
             const int l = q / chunks_per_line, ch = q - l * chunks_per_line;
             const int e0 = ch * kCE; // first element of this 16-byte chunk along the contiguous dimension
             int valid = (l < v_lines) ? (v_span - e0) * static_cast<int>(sizeof(T)) : 0;
@@ -282,13 +314,13 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
         // region); TMATMUL on int8 / fp32 runs on the CUDA cores with the simulation's arithmetic
         T *t = reinterpret_cast<T *>(b200::arena() + dst.addr_);
         const int vr = dst.GetValidRow(), vc = dst.GetValidCol();
-        for (int i = threadIdx.x; i < TileData::Numel; i += blockDim.x) {
+        for (int i = b200::tid_l(), i_step = b200::nthreads_l(); i < TileData::Numel; i += i_step) {
             const int r = i / TileData::Cols, c = i - r * TileData::Cols;
             t[i] = (r < vr && c < vc) ? g[r * s3 + c * s4] : T(0);
         }
         dst.pitch_ = 0;
         dst.major_ = b200::kPlain;
-        __syncthreads();
+        b200::sync_l();
     } else {
         static_assert(TileData::Loc == TileType::Vec || TileData::Loc == TileType::Bias,
                       "TLOAD: destination must be a Vec, Bias or Mat tile");
@@ -302,7 +334,7 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
         const int64_t cov_c = TileData::isRowMajor ? n4 : outer * n4;
         if (cov_r < TileData::Rows || cov_c < TileData::Cols) {
             const T pad = b200::pad_value<T, TileData::PadVal>();
-            for (int i = threadIdx.x; i < TileData::Numel; i += blockDim.x) {
+            for (int i = b200::tid_l(), i_step = b200::nthreads_l(); i < TileData::Numel; i += i_step) {
                 const int r = TileData::isRowMajor ? i / TileData::Cols : i % TileData::Rows;
                 const int c = TileData::isRowMajor ? i % TileData::Cols : i / TileData::Rows;
                 if (r >= cov_r || c >= cov_c) {
@@ -311,7 +343,7 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
             }
         }
         const int64_t per = n3 * n4;
-        for (int64_t i = threadIdx.x; i < outer * per; i += blockDim.x) {
+        for (int64_t i = b200::tid_l(), i_step = b200::nthreads_l(); i < outer * per; i += i_step) {
             const int64_t o = i / per, rc = i - o * per;
             // consecutive threads walk the global tensor's unit-stride dimension
             const int64_t r = (s4 == 1) ? rc / n4 : rc % n3, c = (s4 == 1) ? rc % n4 : rc / n3;
@@ -319,7 +351,7 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
             t[b200::folded_offset<TileData>(o, r, c, n3, n4)] =
                 g[i0 * src.GetStride(0) + i1 * src.GetStride(1) + i2 * src.GetStride(2) + r * s3 + c * s4];
         }
-        __syncthreads();
+        b200::sync_l();
     }
 #endif
     return {};
@@ -356,7 +388,7 @@ PTO_INST RecordEvent TEXTRACT(DstTileData &dst, SrcTileData &src, uint16_t index
         constexpr int kGroups = (kLines + 127) / 128, kAtoms = (kScales + 3) / 4;
         const unsigned char *sp = reinterpret_cast<const unsigned char *>(b200::arena_of<TileType::Mat>() + src.addr_);
         unsigned char *dp = reinterpret_cast<unsigned char *>(b200::arena_of<DstTileData::Loc>() + dst.addr_);
-        for (int i = threadIdx.x; i < kGroups * kAtoms * 512; i += blockDim.x) {
+        for (int i = b200::tid_b(), i_step = b200::nthreads_b(); i < kGroups * kAtoms * 512; i += i_step) {
             const int atom = i >> 9, b = i & 511;
             const int grp = atom / kAtoms, a = atom - grp * kAtoms;
             const int line = grp * 128 + ((b >> 2) & 3) * 32 + (b >> 4), sc = a * 4 + (b & 3);
@@ -375,7 +407,7 @@ PTO_INST RecordEvent TEXTRACT(DstTileData &dst, SrcTileData &src, uint16_t index
         // plain tiles (integers, fp32): the window, row by row; outside the source tile the operand is zero
         const T *s = reinterpret_cast<const T *>(b200::arena_of<TileType::Mat>() + src.addr_);
         T *d = reinterpret_cast<T *>(b200::arena_of<DstTileData::Loc>() + dst.addr_);
-        for (int i = threadIdx.x; i < DstTileData::Numel; i += blockDim.x) {
+        for (int i = b200::tid_b(), i_step = b200::nthreads_b(); i < DstTileData::Numel; i += i_step) {
             const int r = i / DstTileData::Cols, c = i - r * DstTileData::Cols;
             const int sr = r + indexRow, sc = c + indexCol;
             d[i] = (sr < SrcTileData::Rows && sc < SrcTileData::Cols) ? s[sr * SrcTileData::Cols + sc] : T(0);
@@ -393,9 +425,23 @@ PTO_INST RecordEvent TEXTRACT(DstTileData &dst, SrcTileData &src, uint16_t index
         const int src_lines = cols_contig ? SrcTileData::Rows : SrcTileData::Cols;
         const int src_chunks = (cols_contig ? SrcTileData::Cols : SrcTileData::Rows) / kCE;
         const uint32_t dst_pitch = static_cast<uint32_t>(lines) * 128u;
+        // Left [M x K] is a K-major operand when its columns are contiguous; Right [K x N] when its rows are
+        const bool k_major = (DstTileData::Loc == TileType::Left) ? cols_contig : !cols_contig;
+        constexpr int kChunksPerBlock = 8; // 128 bytes of the contiguous dimension
+        if ((b200::control()->mode & b200::kModeViews) && (line0 & 7) == 0 && (chunk0 % kChunksPerBlock) == 0 &&
+            line0 + lines <= src_lines && chunk0 + chunks_per_line <= src_chunks) {
+            // the window is a whole number of swizzle atoms inside the staged tile: the tensor core reads it in place
+            dst.addr_ = src.addr_ + static_cast<uint32_t>(chunk0 / kChunksPerBlock) * src.pitch_ + static_cast<uint32_t>(line0) * 128u;
+            dst.pitch_ = src.pitch_;
+            dst.major_ = static_cast<uint8_t>((k_major ? 0 : 1) | b200::kView);
+            if (b200::tid_b() == 0) {
+                b200::held_back()[15] = 1; // flags that free the staged tile wait for the products (runtime.hpp)
+            }
+            return {};
+        }
         const uint8_t *s = b200::arena_of<TileType::Mat>() + src.addr_;
         uint8_t *d = b200::arena_of<DstTileData::Loc>() + dst.addr_;
-        for (int q = threadIdx.x; q < lines * chunks_per_line; q += blockDim.x) {
+        for (int q = b200::tid_b(), q_step = b200::nthreads_b(); q < lines * chunks_per_line; q += q_step) {
             const int l = q / chunks_per_line, ch = q - l * chunks_per_line;
             const int sl = line0 + l, sch = chunk0 + ch;
             const uint32_t s_off = (sch >> 3) * src.pitch_ + sl * 128u + (((sch & 7) ^ (sl & 7)) << 4);
@@ -405,8 +451,6 @@ PTO_INST RecordEvent TEXTRACT(DstTileData &dst, SrcTileData &src, uint16_t index
                                                         : make_uint4(0, 0, 0, 0);
         }
         dst.pitch_ = dst_pitch;
-        // Left [M x K] is a K-major operand when its columns are contiguous; Right [K x N] when its rows are
-        const bool k_major = (DstTileData::Loc == TileType::Left) ? cols_contig : !cols_contig;
         dst.major_ = k_major ? 0 : 1;
     }
     if (DstTileData::ValidRow == DYNAMIC) {
@@ -450,34 +494,37 @@ PTO_INTERNAL void matmul_issue(TileAccT &c, TileLeftT &a, TileRightT &b, bool ac
     using AT = typename TileLeftT::DType;
     static_assert(TileLeftT::Cols % 16 == 0, "TMATMUL: k a multiple of 16");
 #if PTO_B200_DEVICE_CODE
-    if (control()->in_order) {
+    if (control()->mode & kModeInOrder) {
         // no flags order the operands' staging before the product: every thread's writes are made visible to the
         // tensor core here (in a program with flags, set_flag(PIPE_MTE1, PIPE_M, ...) does this)
         fence_async_proxy();
-        __syncthreads();
+        b200::sync();
     }
-    if (threadIdx.x == 0) {
+    if (b200::tid_b() == 0) {
+        stamp(0x6000);
         constexpr uint32_t kBf16 = std::is_same_v<AT, __nv_bfloat16> ? 1u : 0u;
-        const uint32_t idesc = (1u << 4) | (kBf16 << 7) | (kBf16 << 10) | (static_cast<uint32_t>(a.major_) << 15) |
-                               (static_cast<uint32_t>(b.major_) << 16) |
+        const uint32_t a_major = a.major_ & 1u, b_major = b.major_ & 1u;
+        const uint32_t idesc = (1u << 4) | (kBf16 << 7) | (kBf16 << 10) | (a_major << 15) | (b_major << 16) |
                                (static_cast<uint32_t>(TileRightT::Cols >> 3) << 17) | (8u << 24); // M = 128
         const uint32_t d_tmem = control()->tmem_base + c.addr_;
-        const uint32_t a_addr = smem_u32(arena_of<TileType::Left>() + a.addr_);
-        const uint32_t b_addr = smem_u32(arena_of<TileType::Right>() + b.addr_);
+        // a view (TEXTRACT with extract_views) is addressed from the start of the arena
+        const uint32_t a_addr = smem_u32(((a.major_ & kView) ? arena() : arena_of<TileType::Left>()) + a.addr_);
+        const uint32_t b_addr = smem_u32(((b.major_ & kView) ? arena() : arena_of<TileType::Right>()) + b.addr_);
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < TileLeftT::Cols / 16; ++kk) {
             const uint32_t k0 = kk * 16;
             // K-major view: 16 k-values are 32 bytes inside a 128-byte line, blocks of 64 k are `pitch` apart;
             // MN-major view: 16 k-values are 16 lines of 128 bytes, 64-element blocks of M/N are `pitch` apart
-            const uint64_t a_desc = (a.major_ == 0)
+            const uint64_t a_desc = (a_major == 0)
                                         ? sw128_desc(a_addr + (k0 >> 6) * a.pitch_ + (k0 & 63u) * 2u, 16, 1024)
                                         : sw128_desc(a_addr + k0 * 128u, a.pitch_, 1024);
-            const uint64_t b_desc = (b.major_ == 0)
+            const uint64_t b_desc = (b_major == 0)
                                         ? sw128_desc(b_addr + (k0 >> 6) * b.pitch_ + (k0 & 63u) * 2u, 16, 1024)
                                         : sw128_desc(b_addr + k0 * 128u, b.pitch_, 1024);
             mma_f16(d_tmem, a_desc, b_desc, idesc, (accumulate || kk != 0) ? 1u : 0u);
         }
+        stamp(0x6001);
     }
     complete_matmul_if_in_order();
 #endif
@@ -492,14 +539,17 @@ PTO_INTERNAL void matmul_plain(TileAccT &c, TileLeftT &a, TileRightT &b, int mod
     using AT = typename TileLeftT::DType;
     using CT = typename TileAccT::DType;
     constexpr int K = TileLeftT::Cols, N = TileRightT::Cols;
+    if (not_with_pipe_warps(1)) {
+        return; // a product on the CUDA cores needs four warps on the matrix pipe
+    }
     const AT *pa = reinterpret_cast<const AT *>(arena_of<TileType::Left>() + a.addr_);
     const AT *pb = reinterpret_cast<const AT *>(arena_of<TileType::Right>() + b.addr_);
     const int m = a.GetValidRow(), kv = a.GetValidCol(), n = b.GetValidCol();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int quarter = warp & 3, group = warp >> 2, groups = blockDim.x >> 7;
+    const int warp = b200::tid() >> 5, lane = b200::tid() & 31;
+    const int quarter = warp & 3, group = warp >> 2, groups = b200::nthreads() >> 7;
     const int row = quarter * 32 + lane;
     const uint32_t taddr = control()->tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c.addr_;
-    __syncthreads();
+    b200::sync();
     tc_fence_after();
     for (int c0 = group * 16; c0 < N; c0 += groups * 16) {
         uint32_t r[16];
@@ -539,7 +589,7 @@ PTO_INTERNAL void matmul_plain(TileAccT &c, TileLeftT &a, TileRightT &b, int mod
         tmem_st16(taddr + c0, r);
     }
     tc_fence_before();
-    __syncthreads();
+    b200::sync();
     tc_fence_after();
 #endif
 }
@@ -582,9 +632,12 @@ PTO_INTERNAL void acc_copy(TileAccT &dst, TileAccT &src)
 {
 #if PTO_B200_DEVICE_CODE
     if (dst.addr_ != src.addr_) {
-        const int warp = threadIdx.x >> 5, quarter = warp & 3, group = warp >> 2, groups = blockDim.x >> 7;
+        if (not_with_pipe_warps(2)) {
+            return;
+        }
+        const int warp = b200::tid() >> 5, quarter = warp & 3, group = warp >> 2, groups = b200::nthreads() >> 7;
         const uint32_t lane_base = control()->tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-        __syncthreads();
+        b200::sync();
         tc_fence_after();
         for (int c0 = group * 16; c0 < TileAccT::Cols; c0 += groups * 16) {
             uint32_t r[16];
@@ -592,7 +645,7 @@ PTO_INTERNAL void acc_copy(TileAccT &dst, TileAccT &src)
             tmem_st16(lane_base + dst.addr_ + c0, r);
         }
         tc_fence_before();
-        __syncthreads();
+        b200::sync();
         tc_fence_after();
     }
 #endif
@@ -649,9 +702,12 @@ PTO_INST RecordEvent TMATMUL_BIAS(TileAccT &cMatrix, TileLeftT &aMatrix, TileRig
 #endif
     } else {
 #if PTO_B200_DEVICE_CODE
-        const int warp = threadIdx.x >> 5;
+        if (b200::not_with_pipe_warps(3)) {
+            return {};
+        }
+        const int warp = b200::tid() >> 5;
         const int quarter = warp & 3; // tensor-memory lanes [32 * quarter, +32) are writable by this warp
-        const int group = warp >> 2, groups = blockDim.x >> 7;
+        const int group = warp >> 2, groups = b200::nthreads() >> 7;
         const uint32_t taddr = b200::control()->tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + cMatrix.addr_;
         const float *bias = biasData.data();
         const int vc = biasData.GetValidCol();
@@ -664,7 +720,7 @@ PTO_INST RecordEvent TMATMUL_BIAS(TileAccT &cMatrix, TileLeftT &aMatrix, TileRig
             b200::tmem_st16(taddr + c0, r);
         }
         b200::tc_fence_before();
-        __syncthreads();
+        b200::sync();
 #endif
         b200::matmul_issue(cMatrix, aMatrix, bMatrix, true);
     }
@@ -737,20 +793,20 @@ PTO_INTERNAL void matmul_mx_issue(TileRes &c, TileLeftT &a, TileLeftScaleT &sa, 
 #if PTO_B200_DEVICE_CODE
     constexpr int K = TileLeftT::Cols, N = TileRightT::Cols;
     constexpr int kSpans = (K + 127) / 128, kAtomsK = (K / 32 + 3) / 4, kGroupsN = (N + 127) / 128;
-    if (control()->in_order) {
+    if (control()->mode & kModeInOrder) {
         fence_async_proxy();
-        __syncthreads();
+        b200::sync();
     }
-    if (threadIdx.x == 0) {
-        if (a.major_ != 0 || b.major_ != 0 || c.addr_ + N > kMxScaleTmemCol) {
+    if (b200::tid_b() == 0) {
+        if ((a.major_ & 3u) != 0 || (b.major_ & 3u) != 0 || c.addr_ + N > kMxScaleTmemCol) {
             give_up(-2); // operand not K-major, or the accumulator reaches into the scale columns: reported, not run
         } else {
             constexpr uint32_t a_fmt = std::is_same_v<AT, __nv_fp8_e5m2> ? 1u : 0u;
             constexpr uint32_t b_fmt = std::is_same_v<BT, __nv_fp8_e5m2> ? 1u : 0u;
             const uint32_t idesc = (a_fmt << 7) | (b_fmt << 10) | (static_cast<uint32_t>(N >> 3) << 17) | (1u << 23) | (8u << 24);
             const uint32_t d_tmem = control()->tmem_base + c.addr_;
-            const uint32_t a_addr = smem_u32(arena_of<TileType::Left>() + a.addr_);
-            const uint32_t b_addr = smem_u32(arena_of<TileType::Right>() + b.addr_);
+            const uint32_t a_addr = smem_u32(((a.major_ & kView) ? arena() : arena_of<TileType::Left>()) + a.addr_);
+            const uint32_t b_addr = smem_u32(((b.major_ & kView) ? arena() : arena_of<TileType::Right>()) + b.addr_);
             const uint32_t sa_addr = smem_u32(arena_of<TileType::ScaleLeft>() + sa.addr_);
             const uint32_t sb_addr = smem_u32(arena_of<TileType::ScaleRight>() + sb.addr_);
             tc_fence_after();
@@ -860,12 +916,54 @@ PTO_INTERNAL void tstore(GlobalData &dst, TileData &src)
         using CT = typename TileData::DType;
         static_assert(sizeof(CT) == 4, "TSTORE: 32-bit accumulator tiles");
         static_assert(TileData::Cols % 16 == 0, "TSTORE: accumulator width must be a multiple of 16");
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int warp = b200::tid() >> 5, lane = b200::tid() & 31;
         const int quarter = warp & 3;   // tensor-memory lanes [32 * quarter, +32) are readable by this warp
-        const int group = warp >> 2, groups = blockDim.x >> 7;
+        const int group = warp >> 2, groups = b200::nthreads() >> 7;
         const int row = quarter * 32 + lane;
         const uint32_t taddr = control()->tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + src.addr_;
         tc_fence_after();
+        if (runs(PIPE_FIX)) {
+            stamp(0x7000);
+        }
+        if constexpr (std::is_same_v<GT, CT> && kAtomic == AtomicType::AtomicNone && kRelu == ReluPreMode::NoRelu &&
+                      TileData::Cols % 32 == 0) {
+            const uint32_t staging = held_back()[13];
+            if (staging != 0 && s4 == 1 && groups == 1 && vr == TileData::Rows && vc == TileData::Cols &&
+                ((reinterpret_cast<uintptr_t>(g) | static_cast<uintptr_t>(s3 * 4)) & 15u) == 0) {
+                // whole tile to aligned rows: 32 columns at a time, a thread stages the 128 bytes of its row (rows
+                // 144 bytes apart, so that a warp's 16-byte stores spread over all banks) and hands them to a bulk
+                // copy of its own; the staging row is rewritten once that copy has read it
+                if (b200::tid() < TileData::Rows) {
+                    uint8_t *mine = arena() + (staging - 1u) + static_cast<uint32_t>(b200::tid()) * kStoreStagingRowBytes;
+                    const uint32_t mine_s = smem_u32(mine);
+                    GT *grow = g + row * s3;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < TileData::Cols; c0 += 32) {
+                        uint32_t r0[16], r1[16];
+                        tmem_ld16(taddr + c0, r0);
+                        tmem_ld16(taddr + c0 + 16, r1);
+                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            *reinterpret_cast<uint4 *>(mine + j * 16) = make_uint4(r0[4 * j], r0[4 * j + 1], r0[4 * j + 2], r0[4 * j + 3]);
+                            *reinterpret_cast<uint4 *>(mine + 64 + j * 16) = make_uint4(r1[4 * j], r1[4 * j + 1], r1[4 * j + 2], r1[4 * j + 3]);
+                        }
+                        fence_async_proxy();
+                        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 128;" ::"l"(grow + c0), "r"(mine_s)
+                                     : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                    if (control()->mode & kModeInOrder) {
+                        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                    }
+                }
+                tc_fence_before();
+                if (runs(PIPE_FIX)) {
+                    stamp(0x7001);
+                }
+                return;
+            }
+        }
         for (int c0 = group * 16; c0 < TileData::Cols; c0 += groups * 16) {
             uint32_t r[16];
             tmem_ld16(taddr + c0, r);
@@ -900,7 +998,7 @@ PTO_INTERNAL void tstore(GlobalData &dst, TileData &src)
         const int64_t n0 = dst.GetShape(0), n1 = dst.GetShape(1), n2 = dst.GetShape(2), n3 = dst.GetShape(3),
                       n4 = dst.GetShape(4);
         const int64_t outer = n0 * n1 * n2, per = n3 * n4;
-        for (int64_t i = threadIdx.x; i < outer * per; i += blockDim.x) {
+        for (int64_t i = b200::tid(), i_step = b200::nthreads(); i < outer * per; i += i_step) {
             const int64_t o = i / per, rc = i - o * per;
             const int64_t r = (s4 == 1) ? rc / n4 : rc % n3, c = (s4 == 1) ? rc % n4 : rc / n3;
             const int64_t i2 = o % n2, i1 = (o / n2) % n1, i0 = o / (n2 * n1);
@@ -999,8 +1097,8 @@ PTO_INST RecordEvent TMOV(DstTileData &dst, SrcTileData &src, WaitEvents &... ev
 #if PTO_B200_DEVICE_CODE
         if constexpr (SrcTileData::Loc == TileType::Acc) {
             static_assert(DstTileData::Loc == TileType::Vec, "TMOV from an Acc tile goes to a Vec tile");
-            const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quarter = warp & 3;
-            const int group = warp >> 2, groups = blockDim.x >> 7;
+            const int warp = b200::tid() >> 5, lane = b200::tid() & 31, quarter = warp & 3;
+            const int group = warp >> 2, groups = b200::nthreads() >> 7;
             const int row = quarter * 32 + lane;
             const uint32_t taddr = b200::control()->tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + src.addr_;
             typename DstTileData::DType *t = dst.data();
@@ -1034,13 +1132,13 @@ PTO_INST RecordEvent TMOV(DstTileData &dst, SrcTileData &src, WaitEvents &... ev
                 static_assert(sizeof(typename SrcTileData::DType) == sizeof(typename DstTileData::DType), "TMOV: element sizes differ");
                 const typename SrcTileData::DType *s = src.data();
                 auto *d = reinterpret_cast<typename SrcTileData::DType *>(b200::arena_of<DstTileData::Loc>() + dst.addr_);
-                for (int i = threadIdx.x; i < DstTileData::Rows * DstTileData::Cols; i += blockDim.x) {
+                for (int i = b200::tid_b(), i_step = b200::nthreads_b(); i < DstTileData::Rows * DstTileData::Cols; i += i_step) {
                     const int r = i / DstTileData::Cols, c = i - r * DstTileData::Cols;
                     d[i] = s[b200::vec_offset<SrcTileData>(r, c)];
                 }
                 dst.pitch_ = 0;
                 dst.major_ = b200::kPlain;
-                __syncthreads();
+                b200::sync_b();
                 return {};
             }
             constexpr bool cols_contig = SrcTileData::isRowMajor;
@@ -1052,7 +1150,7 @@ PTO_INST RecordEvent TMOV(DstTileData &dst, SrcTileData &src, WaitEvents &... ev
             constexpr uint32_t dst_pitch = static_cast<uint32_t>(lines) * 128u;
             const uint8_t *s = reinterpret_cast<const uint8_t *>(src.data());
             uint8_t *d = b200::arena_of<DstTileData::Loc>() + dst.addr_;
-            for (int q = threadIdx.x; q < lines * chunks_per_line; q += blockDim.x) {
+            for (int q = b200::tid_b(), q_step = b200::nthreads_b(); q < lines * chunks_per_line; q += q_step) {
                 const int l = q / chunks_per_line, ch = q - l * chunks_per_line;
                 const uint32_t d_off = (ch >> 3) * dst_pitch + l * 128u + (((ch & 7) ^ (l & 7)) << 4);
                 *reinterpret_cast<uint4 *>(d + d_off) =
@@ -1061,14 +1159,16 @@ PTO_INST RecordEvent TMOV(DstTileData &dst, SrcTileData &src, WaitEvents &... ev
             dst.pitch_ = dst_pitch;
             const bool k_major = (DstTileData::Loc == TileType::Left) ? cols_contig : !cols_contig;
             dst.major_ = k_major ? 0 : 1;
+            b200::sync_b();
+            return {};
         } else {
             const int vr = src.GetValidRow(), vc = src.GetValidCol();
-            for (int i = threadIdx.x; i < vr * vc; i += blockDim.x) {
+            for (int i = b200::tid(), i_step = b200::nthreads(); i < vr * vc; i += i_step) {
                 const int r = i / vc, c = i - r * vc;
                 dst.data()[b200::vec_offset<DstTileData>(r, c)] = src.data()[b200::vec_offset<SrcTileData>(r, c)];
             }
         }
-        __syncthreads();
+        b200::sync();
 #endif
         return {};
     }
@@ -1081,11 +1181,11 @@ PTO_INTERNAL void for_each_valid(DstT &dst, SrcT &src, F f)
 {
 #if PTO_B200_DEVICE_CODE
     const int vr = src.GetValidRow(), vc = src.GetValidCol();
-    for (int i = threadIdx.x; i < vr * vc; i += blockDim.x) {
+    for (int i = b200::tid(), i_step = b200::nthreads(); i < vr * vc; i += i_step) {
         const int r = i / vc, c = i - r * vc;
         f(dst.data()[vec_offset<DstT>(r, c)], r, c);
     }
-    __syncthreads();
+    b200::sync();
 #endif
 }
 } // namespace b200
@@ -1216,7 +1316,7 @@ PTO_INTERNAL void row_reduce(TileOut &dst, TileIn &src)
 #if PTO_B200_DEVICE_CODE
     using AccT = float;
     const int vr = src.GetValidRow(), vc = src.GetValidCol();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int warp = b200::tid() >> 5, lane = b200::tid() & 31, warps = b200::nthreads() >> 5;
     for (int r = warp; r < vr; r += warps) {
         AccT acc = kMode == 1 ? -INFINITY : (kMode == 2 ? INFINITY : 0.0f);
         for (int c = lane; c < vc; c += 32) {
@@ -1233,7 +1333,7 @@ PTO_INTERNAL void row_reduce(TileOut &dst, TileIn &src)
             dst.data()[vec_offset<TileOut>(r, 0)] = convert<typename TileOut::DType, float>(acc, RoundMode::CAST_RINT);
         }
     }
-    __syncthreads();
+    b200::sync();
 #endif
 }
 } // namespace b200
@@ -1272,7 +1372,7 @@ PTO_INTERNAL void col_reduce(TileOut &dst, TileIn &src)
 #if PTO_B200_DEVICE_CODE
     using T = typename TileOut::DType;
     const int vr = src.GetValidRow(), vc = src.GetValidCol();
-    for (int c = threadIdx.x; c < vc; c += blockDim.x) {
+    for (int c = b200::tid(), c_step = b200::nthreads(); c < vc; c += c_step) {
         T acc = kMode == 0 ? T(0) : static_cast<T>(src.data()[vec_offset<TileIn>(0, c)]);
         for (int r = (kMode == 0 ? 0 : 1); r < vr; ++r) {
             const T v = static_cast<T>(src.data()[vec_offset<TileIn>(r, c)]);
@@ -1286,7 +1386,7 @@ PTO_INTERNAL void col_reduce(TileOut &dst, TileIn &src)
         }
         dst.data()[vec_offset<TileOut>(0, c)] = acc;
     }
-    __syncthreads();
+    b200::sync();
 #endif
 }
 } // namespace b200
@@ -1353,13 +1453,13 @@ PTO_INTERNAL void fill_pad(TileDataDst &dst, TileDataSrc &src)
     const int vr = src.GetValidRow(), vc = src.GetValidCol();
     const auto pad = pad_value<typename TileDataDst::DType, TileDataDst::PadVal>();
     if (dst.GetValidRow() != 0 && dst.GetValidCol() != 0) {
-        for (int i = threadIdx.x; i < TileDataDst::Rows * TileDataDst::Cols; i += blockDim.x) {
+        for (int i = b200::tid(), i_step = b200::nthreads(); i < TileDataDst::Rows * TileDataDst::Cols; i += i_step) {
             const int r = i / TileDataDst::Cols, c = i - r * TileDataDst::Cols;
             dst.data()[vec_offset<TileDataDst>(r, c)] =
                 (r < vr && c < vc) ? static_cast<typename TileDataDst::DType>(src.data()[vec_offset<TileDataSrc>(r, c)]) : pad;
         }
     }
-    __syncthreads();
+    b200::sync();
 #endif
 }
 } // namespace b200
@@ -1401,11 +1501,11 @@ PTO_INST RecordEvent TTRANS(TileDataDst &dst, TileDataSrc &src, TileDataTmp &tmp
                   "TTRANS: the valid extents of dst are those of src exchanged");
 #if PTO_B200_DEVICE_CODE
     const int vr = src.GetValidRow(), vc = src.GetValidCol();
-    for (int i = threadIdx.x; i < vr * vc; i += blockDim.x) {
+    for (int i = b200::tid(), i_step = b200::nthreads(); i < vr * vc; i += i_step) {
         const int c = i / vr, r = i - c * vr; // consecutive threads write consecutive elements of a dst row
         dst.data()[b200::vec_offset<TileDataDst>(c, r)] = src.data()[b200::vec_offset<TileDataSrc>(r, c)];
     }
-    __syncthreads();
+    b200::sync();
 #endif
     return {};
 }
@@ -1421,13 +1521,13 @@ PTO_INST RecordEvent TTRI(TileData &dst, int diagonal, WaitEvents &... events)
 #if PTO_B200_DEVICE_CODE
     using T = typename TileData::DType;
     const int vr = dst.GetValidRow(), vc = dst.GetValidCol();
-    for (int i = threadIdx.x; i < vr * vc; i += blockDim.x) {
+    for (int i = b200::tid(), i_step = b200::nthreads(); i < vr * vc; i += i_step) {
         const int r = i / vc, c = i - r * vc;
         const bool in = isUpperOrLower ? (c >= r + diagonal) : (c <= r + diagonal);
         dst.data()[b200::vec_offset<TileData>(r, c)] = in ? b200::convert<T, float>(1.0f, RoundMode::CAST_RINT)
                                                           : b200::convert<T, float>(0.0f, RoundMode::CAST_RINT);
     }
-    __syncthreads();
+    b200::sync();
 #endif
     return {};
 }
@@ -1507,7 +1607,7 @@ PTO_INST RecordEvent TCMPS(TileDataDst &dst, TileDataSrc &src0, T src1, CmpMode 
     const int svr = src0.GetValidRow(), svc = src0.GetValidCol();
     const int dvr = dst.GetValidRow(), dvc = dst.GetValidCol();
     const auto scalar = static_cast<typename TileDataSrc::DType>(src1);
-    for (int n = threadIdx.x; n < dvr * dvc; n += blockDim.x) {
+    for (int n = b200::tid(), n_step = b200::nthreads(); n < dvr * dvc; n += n_step) {
         if (n >= H * bytes_per_row) {
             break;
         }
@@ -1523,7 +1623,7 @@ PTO_INST RecordEvent TCMPS(TileDataDst &dst, TileDataSrc &src0, T src1, CmpMode 
         const int i = n / dvc, j = n - i * dvc;
         dst.data()[i * W + j] = static_cast<typename TileDataDst::DType>(byte);
     }
-    __syncthreads();
+    b200::sync();
 #endif
     return {};
 }
@@ -1585,11 +1685,11 @@ PTO_INST RecordEvent TGATHER(DstTileData &dst, SrcTileData &src, WaitEvents &...
                                                                                                    : 0;
     const int vr = src.GetValidRow(), vc = src.GetValidCol();
     const int per_row = (vc - off + div - 1) / div;
-    for (int i = threadIdx.x; i < vr * per_row; i += blockDim.x) {
+    for (int i = b200::tid(), i_step = b200::nthreads(); i < vr * per_row; i += i_step) {
         const int r = i / per_row, k = i - r * per_row;
         dst.data()[i] = src.data()[b200::vec_offset<SrcTileData>(r, k * div + off)];
     }
-    __syncthreads();
+    b200::sync();
 #endif
     return {};
 }

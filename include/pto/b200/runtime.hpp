@@ -45,6 +45,21 @@ constexpr unsigned long long kWaitLimitNs = 2000000000ull; // default limit of a
 constexpr int kNumDevFlags = 16;   // cross-core flag ids (wait_flag_dev / ffts_cross_core_sync)
 constexpr int kNumCoreStatics = 2; // function-local statics of tile programs (see PTO_B200_CORE_STATIC)
 constexpr int kWarps = kBlockThreads / 32;
+// How a launch runs its program (LaunchOptions):
+//   kModeInOrder   every instruction completes before the next one starts
+//   kModePipeWarps the pipes of the core run on warps of their own (teams, below); every warp walks the whole
+//                  instruction stream and skips what is not its own, and flags are raised and awaited by the warps of
+//                  the pipes they name
+//   kModeViews     TEXTRACT / TMOV of an aligned window hands the operand tile a view of the staged tile (no copy)
+constexpr int kModeInOrder = 1, kModePipeWarps = 2, kModeViews = 4;
+constexpr int kTeamLThreads = 64;   // warps 0..1
+constexpr int kTeamBWarp = 3;
+constexpr int kTeamCFirstWarp = 4, kTeamCThreads = 128; // warps 4..7
+// TSTORE's staging area (LaunchOptions::store_staging_offset)
+constexpr uint32_t kStoreStagingRowBytes = 128 + 16; // a 128-byte row piece per thread, padded against bank conflicts
+constexpr uint32_t kStoreStagingBytes = 128 * kStoreStagingRowBytes;
+constexpr uint32_t kNoStoreStaging = 0xffffffffu;
+constexpr int kNotAMember = 1 << 20; // thread index handed to threads outside the executing team: their loops are empty
 
 // What a block reports when one of its waits ran out (same layout as the status record of libpto_b200.so).
 struct StatusRecord {
@@ -57,7 +72,7 @@ struct StatusRecord {
 struct Control {
     uint32_t tmem_base;
     int abort_flag;
-    int in_order;                   // 1: every instruction completes before the next one starts (LaunchOptions::in_order)
+    int mode;                       // kModeInOrder | kModePipeWarps | kModeViews (LaunchOptions)
     int fail_where;                 // flag index of the first wait that gave up
     unsigned long long wait_limit_ns;
     uint64_t flags[kNumFlags];
@@ -69,10 +84,15 @@ struct Control {
     uint32_t core_static_init[kWarps];                   // bit s set: slot s of this warp holds a value
     uint32_t l0a_offset;                                 // start of the Left window of the arena (bytes)
     uint32_t l0b_offset;                                 // start of the Right window of the arena (bytes)
+    // pipe_warps: how often each flag was raised and how many of its waits are complete (modulo 256).  A flag is an
+    // mbarrier, which tells "this phase" from "the one before" and no further; a team that runs ahead of the flag's
+    // waiters raises it again only once the previous raise has been consumed (see set_flag).
+    uint8_t raised[kNumFlags];
+    uint8_t consumed[kNumFlags];
 };
 constexpr int kControlBytes = ((int)sizeof(Control) + 1023) / 1024 * 1024;
-static_assert(kControlBytes == 6 * 1024, "the control block is 6 KiB: the arena is the other 220 KiB");
-constexpr int kDefaultSmemBytes = 227 * 1024; // 1 KiB alignment slack + control (6 KiB) + 220 KiB arena
+static_assert(kControlBytes == 7 * 1024, "the control block is 7 KiB: the arena is the other 220 KiB");
+constexpr int kDefaultSmemBytes = 227 * 1024; // control (7 KiB) + 220 KiB arena; the buffer is declared 1 KiB aligned
 // scale tiles of the MX product (TileType::ScaleLeft / ScaleRight) have windows of their own at the end of the arena:
 // 4 KiB each (a program that uses them keeps its Right window below 212 KiB)
 constexpr uint32_t kScaleRightOffset = 212 * 1024;
@@ -80,11 +100,22 @@ constexpr uint32_t kScaleLeftOffset = 216 * 1024;
 // tensor-memory columns kept for the scales of TMATMUL_MX (accumulators of such a program stay below them)
 constexpr uint32_t kMxScaleTmemCol = 480;
 
+#ifdef PTO_B200_TIMELINE
+// Profiling aid, compiled in with -DPTO_B200_TIMELINE: the first thread of each team of block 0 (of the whole block
+// without pipe_warps: thread 0) stamps (code, clock64) at the entry and exit of flags and instructions.
+// Codes: 0x1000 + flag / 0x2000 + flag: wait_flag entered / passed; 0x3000 + flag / 0x3800 + flag: set_flag entered /
+// done; 0x4000 / 0x4001 TLOAD; 0x5000 / 0x5001 TEXTRACT; 0x6000 / 0x6001 TMATMUL; 0x7000 / 0x7001 TSTORE.
+constexpr int kTimelineEntries = 4096;
+static __device__ unsigned long long g_timeline[3][kTimelineEntries];
+static __device__ unsigned int g_timeline_n[3];
+#endif
 #if PTO_B200_DEVICE_CODE
+// The block's dynamic shared memory, declared 1 KiB aligned (the swizzled operand layouts want that).  The launch
+// trampoline checks the address and reports instead of running the program if the declaration was not honoured.
 __device__ __forceinline__ uint8_t *smem_base()
 {
-    extern __shared__ uint8_t pto_b200_dynamic_smem[];
-    return reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(pto_b200_dynamic_smem) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t pto_b200_dynamic_smem[];
+    return pto_b200_dynamic_smem;
 }
 __device__ __forceinline__ Control *control()
 {
@@ -161,6 +192,134 @@ __device__ __forceinline__ uint32_t tile_auto_place(int space, uint32_t amount)
     return at * unit;
 }
 
+// ---- teams: who executes an instruction.  Without kModePipeWarps the whole block does.  With it:
+//   team L  warps 0..1  MTE2 (loads from global memory)
+//   team B  warp  3     MTE1 and M (operand staging and the products, issued by its first lane)
+//   team C  warps 4..7  V, MTE3, FIX, S (vector work and stores; four warps, so that together they reach every
+//                       tensor-memory lane)
+// Warp 2 has no pipe.  Every warp walks the whole instruction stream; an instruction does its work on the threads of
+// its pipe's team and nothing on the others (their thread index is kNotAMember, which empties every loop).
+__device__ __forceinline__ bool pipe_warps()
+{
+    return (control()->mode & kModePipeWarps) != 0;
+}
+enum : int { kTeamL = 0, kTeamB = 1, kTeamC = 2 };
+__device__ __forceinline__ int team_of_pipe(int pipe)
+{
+    return pipe == PIPE_MTE2 ? kTeamL : ((pipe == PIPE_MTE1 || pipe == PIPE_M) ? kTeamB : kTeamC);
+}
+__device__ __forceinline__ int team_threads(int team)
+{
+    return team == kTeamL ? kTeamLThreads : (team == kTeamB ? 32 : kTeamCThreads);
+}
+__device__ __forceinline__ int team_first_thread(int team)
+{
+    return team == kTeamL ? 0 : (team == kTeamB ? kTeamBWarp * 32 : kTeamCFirstWarp * 32);
+}
+template <int kTeam>
+__device__ __forceinline__ int team_tid()
+{
+    if (!pipe_warps()) {
+        return threadIdx.x;
+    }
+    const int t = static_cast<int>(threadIdx.x) - team_first_thread(kTeam);
+    return (t >= 0 && t < team_threads(kTeam)) ? t : kNotAMember;
+}
+template <int kTeam>
+__device__ __forceinline__ int team_size()
+{
+    return pipe_warps() ? team_threads(kTeam) : static_cast<int>(blockDim.x);
+}
+template <int kTeam>
+__device__ __forceinline__ void team_sync()
+{
+    if (!pipe_warps()) {
+        __syncthreads();
+    } else if (team_tid<kTeam>() != kNotAMember) {
+        if (kTeam == kTeamB) {
+            __syncwarp();
+        } else {
+            asm volatile("bar.sync %0, %1;" ::"n"(1 + kTeam), "n"(kTeam == kTeamL ? kTeamLThreads : kTeamCThreads) : "memory");
+        }
+    }
+}
+// does this thread execute instructions of `pipe`?
+__device__ __forceinline__ bool runs(int pipe)
+{
+    if (!pipe_warps()) {
+        return true;
+    }
+    const int team = team_of_pipe(pipe);
+    const int t = static_cast<int>(threadIdx.x) - team_first_thread(team);
+    return t >= 0 && t < team_threads(team);
+}
+// vector, store and scalar instructions (team C) are the default
+__device__ __forceinline__ int tid() { return team_tid<kTeamC>(); }
+__device__ __forceinline__ int nthreads() { return team_size<kTeamC>(); }
+__device__ __forceinline__ void sync() { team_sync<kTeamC>(); }
+__device__ __forceinline__ int tid_l() { return team_tid<kTeamL>(); }
+__device__ __forceinline__ int nthreads_l() { return team_size<kTeamL>(); }
+__device__ __forceinline__ void sync_l() { team_sync<kTeamL>(); }
+__device__ __forceinline__ int tid_b() { return team_tid<kTeamB>(); }
+__device__ __forceinline__ int nthreads_b() { return team_size<kTeamB>(); }
+__device__ __forceinline__ void sync_b() { team_sync<kTeamB>(); }
+// An instruction that pipe_warps does not cover (its work needs threads of two teams): reported through the status
+// record (where = 600 + what) and skipped; the program's waits return at once from then on.
+__device__ __forceinline__ bool not_with_pipe_warps(int what)
+{
+    if (!pipe_warps()) {
+        return false;
+    }
+    Control *c = control();
+    if ((threadIdx.x & 31) == 0 && c->abort_flag == 0) {
+        c->fail_where = 600 + what;
+        c->abort_flag = 1;
+    }
+    return true;
+}
+__device__ __forceinline__ void stamp(int code)
+{
+#ifdef PTO_B200_TIMELINE
+    if (blockIdx.x != 0) {
+        return;
+    }
+    int team = -1;
+    if (!pipe_warps()) {
+        team = threadIdx.x == 0 ? 0 : -1;
+    } else if (threadIdx.x == 0) {
+        team = kTeamL;
+    } else if (threadIdx.x == kTeamBWarp * 32) {
+        team = kTeamB;
+    } else if (threadIdx.x == kTeamCFirstWarp * 32) {
+        team = kTeamC;
+    }
+    if (team >= 0) {
+        // the running count lives in shared memory (the unused flag words of PIPE_MTE1 -> PIPE_MTE1): a stamp costs one
+        // shared-memory round trip and two stores
+        volatile uint32_t *count = reinterpret_cast<volatile uint32_t *>(&control()->flags[flag_index(PIPE_MTE1, PIPE_MTE1, 0)]) + team;
+        const unsigned int i = *count;
+        if (i < kTimelineEntries) {
+            g_timeline[team][i] = (static_cast<unsigned long long>(code) << 48) | (clock64() & 0xffffffffffffull);
+            *count = i + 1;
+            g_timeline_n[team] = i + 1;
+        }
+    }
+#else
+    (void)code;
+#endif
+}
+// Views handed out by TEXTRACT (kModeViews) keep the staged tile in use until the products that read them are
+// complete.  A set_flag(PIPE_MTE1, PIPE_MTE2, id) that follows such a TEXTRACT ("the staged tile may be loaded
+// again") is therefore held back and raised by the tensor core itself (tcgen05.commit) at the next flag that the
+// matrix pipe raises, which in program order comes after the products that read the views.  The list of flags held
+// back lives in the flag words of PIPE_V -> PIPE_V (a pipe has no flags with itself); only the thread that issues the
+// products touches it.
+__device__ __forceinline__ uint32_t *held_back()
+{
+    return reinterpret_cast<uint32_t *>(&control()->flags[flag_index(PIPE_V, PIPE_V, 0)]);
+}
+constexpr int kMaxHeldBack = 12; // held_back()[13]: 1 + arena offset of TSTORE's staging area, 0 = none
+
 // ---- mbarrier primitives (bounded waits: a wait that runs out raises the block's abort flag)
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
 {
@@ -212,6 +371,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int wh
         }
         if ((i & 0x3f) == 0x3f) {
             if (*abort_flag) {
+#ifdef PTO_B200_TRACE_WAITS
+                // debugging aid: which wait each warp of block 0 was held in when the block gave up
+                if (t0 != 0 && blockIdx.x == 0 && (threadIdx.x & 31) == 0) {
+                    printf("pto wait trace: warp %d held in flag %d (src %d dst %d id %d) parity %u\n", threadIdx.x >> 5, where,
+                           (where >> 6) & 7, (where >> 3) & 7, where & 7, parity);
+                }
+#endif
                 return false;
             }
             const unsigned long long now = global_timer_ns();
@@ -225,7 +391,46 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int wh
             }
         }
     }
+#ifdef PTO_B200_TRACE_WAITS
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {
+        printf("pto wait trace: warp %d gave up on flag %d (src %d dst %d id %d) parity %u\n", threadIdx.x >> 5, where,
+               (where >> 6) & 7, (where >> 3) & 7, where & 7, parity);
+    }
+#endif
     give_up(where);
+    return false;
+}
+
+// pipe_warps: before flag `f` is raised for the n-th time, its first n - 1 raises must have been consumed (bounded
+// like every wait; see Control::raised)
+__device__ __forceinline__ bool wait_until_consumed(int f, uint8_t n)
+{
+    Control *ctl = control();
+    volatile uint8_t *consumed = &ctl->consumed[f];
+    volatile int *abort_flag = &ctl->abort_flag;
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
+        if (*consumed == n) {
+            return true;
+        }
+        if ((i & 0x3f) == 0x3f) {
+            if (*abort_flag) {
+                return false;
+            }
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > ctl->wait_limit_ns) {
+                break;
+            }
+        }
+    }
+#ifdef PTO_B200_TRACE_WAITS
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {
+        printf("pto wait trace: warp %d gave up raising flag %d for the %u-th time (consumed %u)\n", threadIdx.x >> 5, f, n, *consumed);
+    }
+#endif
+    give_up(1024 + f);
     return false;
 }
 
@@ -250,16 +455,21 @@ __device__ __forceinline__ void tc_commit(uint64_t *bar)
 
 // Block prologue / epilogue (called by the launch trampoline, not by tile programs).
 __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, uint32_t l0a_offset, uint32_t l0b_offset,
-                                            int in_order)
+                                            int mode, uint32_t store_staging)
 {
     Control *ctl = control();
     const int nthreads = blockDim.x;
     for (int f = threadIdx.x; f < kNumFlags; f += nthreads) {
         // a flag raised by the matrix pipe is signalled by one tcgen05.commit; every other pipe's work is
         // done by all threads, so all of them arrive
-        const int src = f / (kNumPipes * EVENT_ID_MAX);
-        if (f < EVENT_ID_MAX) {
-            ctl->flags[f] = 0; // PIPE_S -> PIPE_S: the tile allocator's counters (tile_auto_place)
+        const int src = f / (kNumPipes * EVENT_ID_MAX), dst = (f / EVENT_ID_MAX) % kNumPipes;
+        if (src == dst) {
+            // no flags of a pipe with itself: PIPE_S -> PIPE_S holds the tile allocator's counters (tile_auto_place),
+            // PIPE_V -> PIPE_V the flags held back for views (held_back)
+            ctl->flags[f] = 0;
+        } else if (mode & kModePipeWarps) {
+            // the threads of the source pipe's team arrive; team B signals through one thread or the tensor core
+            mbar_init(&ctl->flags[f], team_of_pipe(src) == kTeamB ? 1u : static_cast<uint32_t>(team_threads(team_of_pipe(src))));
         } else {
             mbar_init(&ctl->flags[f], src == PIPE_M ? 1u : static_cast<uint32_t>(nthreads));
         }
@@ -275,17 +485,25 @@ __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, ui
     if (threadIdx.x < kNumDevFlags) {
         ctl->dev_flags[threadIdx.x] = 0;
     }
+    for (int f = threadIdx.x; f < kNumFlags; f += nthreads) {
+        ctl->raised[f] = 0;
+        ctl->consumed[f] = 0;
+    }
     if (threadIdx.x < kWarps) {
         ctl->core_static_init[threadIdx.x] = 0;
     }
     if (threadIdx.x == 0) {
         ctl->abort_flag = 0;
-        ctl->in_order = in_order;
+        ctl->mode = mode;
         ctl->fail_where = -1;
         ctl->wait_limit_ns = wait_limit_ns == 0 ? kWaitLimitNs : wait_limit_ns;
         ctl->l0a_offset = l0a_offset;
         ctl->l0b_offset = l0b_offset;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads(); // (the flag words of a pipe with itself were zeroed above)
+    if (threadIdx.x == 0) {
+        held_back()[13] = store_staging == kNoStoreStaging ? 0u : store_staging + 1u;
     }
     if (threadIdx.x < 32) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
@@ -301,6 +519,7 @@ __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, ui
 __device__ __forceinline__ void block_end(StatusRecord *status)
 {
     asm volatile("cp.async.wait_all;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); // bulk stores of TSTORE have read their staging and landed
     tc_fence_before();
     __syncthreads();
     Control *ctl = control();
@@ -337,15 +556,37 @@ struct LaunchOptions {
     // different pipes (e.g. RunTMATMUL_SPLIT_K of tests/cpu/st/testcase/tmatmul/tmatmul_kernel.cpp:104-155 in the
     // reference); programs that carry their flags do not need it and lose their overlap with it.
     bool in_order = false;
+    // The core's pipes on warps of their own (kModePipeWarps above): loads, products and stores of a program that
+    // orders its pipes with set_flag / wait_flag overlap as they do on the NPU.  For programs of one core's pipes
+    // (no cross-core flags or TPipe rings); not together with in_order.
+    bool pipe_warps = false;
+    // TEXTRACT / TMOV (Mat -> Left / Right) of a window that starts on a 128-byte block of the contiguous dimension and
+    // on a multiple of eight lines, and lies inside the staged tile, hands out a view instead of copying (the tensor
+    // core reads any such window through its descriptor).  The flag that frees the staged tile for the next load is
+    // then raised when the products that read the view are complete (see held_back).  Needs pipe_warps, and a
+    // program that does not extract from a reloaded staged tile before the products of the previous one are issued.
+    bool extract_views = false;
+    // Arena offset (bytes, a multiple of 16) of kStoreStagingBytes (18 KiB) that the program's tiles leave free: TSTORE of
+    // a whole fp32 accumulator tile to 16-byte aligned rows then goes through it, each thread staging 128 bytes of
+    // its row and handing them to an asynchronous bulk copy, instead of storing 16 bytes per instruction.
+    uint32_t store_staging_offset = kNoStoreStaging;
 };
 
 template <typename Program>
 __global__ void __launch_bounds__(kBlockThreads, 1)
     block_kernel(Program program, StatusRecord *status, unsigned long long wait_limit_ns, uint32_t l0a_offset,
-                 uint32_t l0b_offset, int in_order)
+                 uint32_t l0b_offset, int mode, uint32_t store_staging)
 {
 #if PTO_B200_DEVICE_CODE
-    block_begin(wait_limit_ns, l0a_offset, l0b_offset, in_order);
+    if ((smem_u32(smem_base()) & 1023u) != 0) {
+        if (threadIdx.x == 0 && status != nullptr && atomicCAS(&status->code, 0, 3) == 0) {
+            status->block = static_cast<int>(blockIdx.x);
+            status->where = -3; // the shared-memory buffer is not 1 KiB aligned
+            status->detail = static_cast<int>(smem_u32(smem_base()) & 1023u);
+        }
+        return;
+    }
+    block_begin(wait_limit_ns, l0a_offset, l0b_offset, mode, store_staging);
     program();
     block_end(status);
 #endif
@@ -362,7 +603,9 @@ inline cudaError_t launch(uint32_t blocks, void *stream, Program program, const 
     }
     block_kernel<Program><<<blocks, kBlockThreads, opt.smem_bytes, static_cast<cudaStream_t>(stream)>>>(
         program, static_cast<StatusRecord *>(opt.status), opt.wait_limit_ns, opt.l0a_offset, opt.l0b_offset,
-        opt.in_order ? 1 : 0);
+        (opt.in_order ? kModeInOrder : 0) | (opt.pipe_warps ? kModePipeWarps : 0) |
+            (opt.pipe_warps && opt.extract_views ? kModeViews : 0),
+        opt.store_staging_offset);
     return cudaGetLastError();
 }
 template <typename Program>
@@ -412,6 +655,8 @@ PTO_INTERNAL uint32_t get_block_num()
 #endif
 }
 
+PTO_INTERNAL void pipe_barrier(pipe_t pipe);
+
 // set_flag(src, dst, id): the flag is raised once everything issued so far on pipe `src` is complete.
 //   PIPE_M    : tcgen05.commit by the issuing thread (covers all earlier tcgen05.mma)
 //   PIPE_MTE2 : every thread arrives when its own asynchronous copies have landed
@@ -420,10 +665,92 @@ PTO_INTERNAL void set_flag(pipe_t src, pipe_t dst, int id)
 {
 #if PTO_B200_DEVICE_CODE
     if (src == dst) {
-        __syncthreads(); // a pipe is ordered with itself by a barrier, not a flag
+        pipe_barrier(src); // a pipe is ordered with itself by a barrier, not a flag
         return;
     }
-    uint64_t *bar = &pto::b200::control()->flags[pto::b200::flag_index(src, dst, id)];
+    pto::b200::Control *ctl = pto::b200::control();
+    const int f = pto::b200::flag_index(src, dst, id);
+    uint64_t *bar = &ctl->flags[f];
+    if (pto::b200::runs(src)) {
+        pto::b200::stamp(0x3000 + f);
+    }
+    if (ctl->mode & pto::b200::kModePipeWarps) {
+        if (!pto::b200::runs(src)) {
+            return;
+        }
+        const int team = pto::b200::team_of_pipe(src);
+        // a flag between two teams is raised again only when its previous raise has been consumed (Control::raised)
+        const bool between_teams = team != pto::b200::team_of_pipe(dst);
+        if (team == pto::b200::kTeamB) {
+            const bool leader = (threadIdx.x & 31) == 0;
+            if (src == PIPE_M) {
+                if (leader) {
+                    if (between_teams) {
+                        const uint8_t n = ctl->raised[f];
+                        pto::b200::wait_until_consumed(f, n);
+                        ctl->raised[f] = static_cast<uint8_t>(n + 1);
+                    }
+                    pto::b200::tc_commit(bar);
+                    // flags held back for views: the products that read them are all issued by now
+                    volatile uint32_t *held = pto::b200::held_back();
+                    const uint32_t count = held[0];
+                    for (uint32_t i = 0; i < count; ++i) {
+                        const int hf = static_cast<int>(held[1 + i]);
+                        const uint8_t n = ctl->raised[hf];
+                        pto::b200::wait_until_consumed(hf, n);
+                        ctl->raised[hf] = static_cast<uint8_t>(n + 1);
+                        pto::b200::tc_commit(&ctl->flags[hf]);
+                    }
+                    held[0] = 0;
+                    held[15] = 0;
+                }
+            } else {
+                volatile uint32_t *held = pto::b200::held_back();
+                // held[15]: a view was handed out since the matrix pipe last raised a flag
+                __syncwarp();
+                const bool hold = dst == PIPE_MTE2 && held[15] != 0 && held[0] < pto::b200::kMaxHeldBack;
+                __syncwarp();
+                if (hold) {
+                    if (leader) {
+                        held[1 + held[0]] = static_cast<uint32_t>(f);
+                        held[0] = held[0] + 1;
+                    }
+                } else {
+                    pto::b200::fence_async_proxy(); // copies of TEXTRACT, visible to the tensor core
+                    __syncwarp();
+                    if (leader) {
+                        if (between_teams) {
+                            const uint8_t n = ctl->raised[f];
+                            pto::b200::wait_until_consumed(f, n);
+                            ctl->raised[f] = static_cast<uint8_t>(n + 1);
+                        }
+                        pto::b200::mbar_arrive(bar);
+                    }
+                }
+            }
+            __syncwarp();
+            pto::b200::stamp(0x3800 + f);
+            return;
+        }
+        if (between_teams) {
+            // every thread of the team reads the count, the first one advances it, all wait for the consumer
+            if (team == pto::b200::kTeamL) {
+                pto::b200::sync_l();
+            } else {
+                pto::b200::sync();
+            }
+            const uint8_t n = *reinterpret_cast<volatile uint8_t *>(&ctl->raised[f]);
+            if (team == pto::b200::kTeamL) {
+                pto::b200::sync_l();
+            } else {
+                pto::b200::sync();
+            }
+            if (static_cast<int>(threadIdx.x) == pto::b200::team_first_thread(team)) {
+                ctl->raised[f] = static_cast<uint8_t>(n + 1);
+            }
+            pto::b200::wait_until_consumed(f, n);
+        }
+    }
     if (src == PIPE_M) {
         if (threadIdx.x == 0) {
             pto::b200::tc_commit(bar);
@@ -436,6 +763,7 @@ PTO_INTERNAL void set_flag(pipe_t src, pipe_t dst, int id)
         pto::b200::tc_fence_before();
         pto::b200::mbar_arrive(bar);
     }
+    pto::b200::stamp(0x3800 + f);
 #else
     (void)src;
     (void)dst;
@@ -451,19 +779,36 @@ PTO_INTERNAL void wait_flag(pipe_t src, pipe_t dst, int id)
         return; // see set_flag
     }
     pto::b200::Control *ctl = pto::b200::control();
+    if ((ctl->mode & pto::b200::kModePipeWarps) && !pto::b200::runs(dst)) {
+        return; // the warps of the waiting pipe wait
+    }
     const int f = pto::b200::flag_index(src, dst, id);
+    pto::b200::stamp(0x1000 + f);
     // all lanes of a warp run the same instruction stream, so the phase is kept once per warp
     volatile uint32_t *word = &ctl->phase[f >> 5][threadIdx.x >> 5];
     const uint32_t bit = 1u << (f & 31);
     const uint32_t parity = (*word & bit) ? 1u : 0u;
-    pto::b200::mbar_wait(&ctl->flags[f], parity, f);
+    const bool ok = pto::b200::mbar_wait(&ctl->flags[f], parity, f);
     __syncwarp();
     if ((threadIdx.x & 31) == 0) {
-        *word ^= bit;
+        *word = *word ^ bit;
     }
     __syncwarp();
+    if ((ctl->mode & pto::b200::kModePipeWarps) && pto::b200::team_of_pipe(src) != pto::b200::team_of_pipe(dst)) {
+        // every warp of the waiting team is past the wait: the flag may be raised again (Control::consumed)
+        const int team = pto::b200::team_of_pipe(dst);
+        if (team == pto::b200::kTeamL) {
+            pto::b200::sync_l();
+        } else if (team == pto::b200::kTeamC) {
+            pto::b200::sync();
+        }
+        if (ok && static_cast<int>(threadIdx.x) == pto::b200::team_first_thread(team)) {
+            ctl->consumed[f] = static_cast<uint8_t>(ctl->consumed[f] + 1);
+        }
+    }
     pto::b200::tc_fence_after();
     pto::b200::fence_async_proxy();
+    pto::b200::stamp(0x2000 + f);
 #else
     (void)src;
     (void)dst;
@@ -477,7 +822,7 @@ namespace b200 {
 PTO_INTERNAL void complete_copies_if_in_order()
 {
 #if PTO_B200_DEVICE_CODE
-    if (control()->in_order) {
+    if ((control()->mode & kModeInOrder)) {
         asm volatile("cp.async.wait_all;" ::: "memory");
         __syncthreads();
     }
@@ -486,7 +831,7 @@ PTO_INTERNAL void complete_copies_if_in_order()
 PTO_INTERNAL void complete_matmul_if_in_order()
 {
 #if PTO_B200_DEVICE_CODE
-    if (control()->in_order) {
+    if ((control()->mode & kModeInOrder)) {
         // the flag (PIPE_M -> PIPE_ALL, 7) is kept for this; tile programs have no reason to name it
         set_flag(PIPE_M, PIPE_ALL, 7);
         wait_flag(PIPE_M, PIPE_ALL, 7);
@@ -499,9 +844,33 @@ PTO_INTERNAL void complete_matmul_if_in_order()
 
 PTO_INTERNAL void pipe_barrier(pipe_t pipe)
 {
-    (void)pipe;
 #if PTO_B200_DEVICE_CODE
-    __syncthreads();
+    if (!pto::b200::pipe_warps()) {
+        __syncthreads();
+        return;
+    }
+    if (pipe == PIPE_ALL) {
+        // every pipe drains: each team completes what it has in flight, then all meet
+        if (pto::b200::runs(PIPE_MTE2)) {
+            asm volatile("cp.async.wait_all;" ::: "memory");
+        }
+        set_flag(PIPE_M, PIPE_ALL, 7);
+        wait_flag(PIPE_M, PIPE_ALL, 7); // (PIPE_ALL is a pipe of team C)
+        if (pto::b200::runs(PIPE_MTE2) || pto::b200::runs(PIPE_M) || pto::b200::runs(PIPE_V)) {
+            asm volatile("bar.sync 4, %0;" ::"n"(pto::b200::kTeamLThreads + 32 + pto::b200::kTeamCThreads) : "memory");
+        }
+    } else {
+        const int team = pto::b200::team_of_pipe(pipe);
+        if (team == pto::b200::kTeamL) {
+            pto::b200::sync_l();
+        } else if (team == pto::b200::kTeamB) {
+            pto::b200::sync_b();
+        } else {
+            pto::b200::sync();
+        }
+    }
+#else
+    (void)pipe;
 #endif
 }
 

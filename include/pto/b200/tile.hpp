@@ -175,6 +175,9 @@ namespace b200 {
 // how a staged Mat tile lies in shared memory (decided by TLOAD from the global tensor's contiguous dimension)
 // kPlain: 8- and 32-bit matrix tiles, stored row-major Rows x Cols without swizzle (not read by the tensor core)
 enum : uint8_t { kColsContiguous = 0, kRowsContiguous = 1, kPlain = 2 };
+// bit of major_ on a Left / Right tile that is a view of a staged Mat tile: its address counts from the start of the
+// arena, not from the operand window (TEXTRACT with LaunchOptions::extract_views)
+enum : uint8_t { kView = 0x80 };
 
 // A tile is constructed with storage of its own, as in the reference's CPU simulation where every tile object owns an
 // array (include/pto/common/pto_tile.hpp, the `data_` member under __CPU_SIM): the constructor takes the next free

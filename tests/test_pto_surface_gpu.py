@@ -35,10 +35,13 @@ def _ptr(t):
 
 
 @pytest.mark.parametrize("name,m,k,n", [("pto_refk_gemm_256x128x512", 256, 128, 512),
-                                        ("pto_refk_gemm_1536", 1536, 1536, 1536)])
+                                        ("pto_refk_gemm_1536", 1536, 1536, 1536),
+                                        ("pto_refk_gemm_pw_256x128x512", 256, 128, 512),
+                                        ("pto_refk_gemm_pw_1536", 1536, 1536, 1536)])
 def test_reference_gemm_tile_program(refk, name, m, k, n):
     """RunGemmE2E (TLOAD / TEXTRACT / TMATMUL / TMATMUL_ACC / TSTORE with its set_flag / wait_flag ping-pong),
-    base tile 128 x 256, k step 64, B stored n x k."""
+    base tile 128 x 256, k step 64, B stored n x k.  The `pw` instances run the core's pipes on warps of their own
+    (loads, products and stores overlap as the program's flags allow; TEXTRACT hands out views)."""
     r = np.random.default_rng(m + n)
     a = r.uniform(-1, 1, (m, k)).astype(np.float16)
     b = r.uniform(-1, 1, (n, k)).astype(np.float16)
@@ -52,7 +55,8 @@ def test_reference_gemm_tile_program(refk, name, m, k, n):
     assert ok, f"max relative error {worst:.3e}"
 
 
-def test_reference_gemm_tile_program_6144(refk):
+@pytest.mark.parametrize("name", ["pto_refk_gemm_6144", "pto_refk_gemm_pw_6144", "pto_refk_gemm_pw_6144_k128"])
+def test_reference_gemm_tile_program_6144(refk, name):
     import pto_isa_b200 as pto
     m = n = k = 6144
     g = torch.Generator(device="cuda").manual_seed(3)
@@ -60,7 +64,7 @@ def test_reference_gemm_tile_program_6144(refk):
     b = (torch.rand(n, k, device="cuda", generator=g) * 2 - 1).half()
     c = torch.full((m, n), float("nan"), device="cuda")
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
-    assert refk.pto_refk_gemm_6144(_ptr(c), _ptr(a), _ptr(b), _stream(), _ptr(status)) == 0
+    assert getattr(refk, name)(_ptr(c), _ptr(a), _ptr(b), _stream(), _ptr(status)) == 0
     assert refk.pto_refk_status(_stream(), _ptr(status)) == 0
     # against the hand-written kernel (itself checked against the oracle): same tensor-core arithmetic
     want = pto.gemm(a, b, 1)
