@@ -228,15 +228,51 @@ PTO_INTERNAL int folded_offset(int64_t outer, int64_t r, int64_t c, int64_t n3, 
 }
 } // namespace b200
 
-template <typename TileData, typename GlobalData, typename... WaitEvents>
-PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... events)
-{
-    TSYNC(events...);
-    static_assert(sizeof(typename TileData::DType) == sizeof(typename GlobalData::DType),
-                  "TLOAD: source and destination element sizes differ");
-    static_assert(GlobalData::layout == Layout::ND || GlobalData::layout == Layout::DN,
-                  "TLOAD: ND and DN global tensors are supported");
 #if PTO_B200_DEVICE_CODE
+namespace b200 {
+// pipe_warps: a whole tile of a registered matrix is fetched by the copy engine.  The first thread of the loading team
+// finds the matrix, turns the tile's address into coordinates and records the copy, which the set_flag that follows
+// issues (runtime.hpp, PendingLoad).  Returns 0 when the tile has to go the cp.async way.  Plain arguments and out of
+// line: the instruction stream of a tile program stays small and nothing of the caller's is forced into memory.
+__device__ __noinline__ uint32_t tload_prepare_engine(unsigned long long addr, uint32_t es, unsigned long long line_stride_bytes,
+                                                      uint32_t lines, uint32_t span_bytes, uint32_t dst_smem, uint32_t pitch)
+{
+    volatile uint32_t *pend = pending_count();
+    const TmaTable *table = tma_table();
+    if ((span_bytes & 127u) != 0 || pend[0] >= static_cast<uint32_t>(kMaxPendingLoads)) {
+        return 0;
+    }
+    for (int r = 0; r < table->count; ++r) {
+        const unsigned long long off = addr - table->base[r];
+        const unsigned long long pitch_bytes = table->pitch_bytes[r];
+        if (addr >= table->base[r] && table->elem_bytes[r] == es && pitch_bytes == line_stride_bytes &&
+            lines % table->box_rows[r] == 0 && (off & 15u) == 0) {
+            const unsigned long long y = off / pitch_bytes, xb = off - y * pitch_bytes;
+            if (xb + span_bytes <= table->row_bytes[r] &&
+                off + static_cast<unsigned long long>(lines - 1) * pitch_bytes + span_bytes <= table->bytes[r]) {
+                PendingLoad *p = pending_loads() + pend[0];
+                p->dst = dst_smem;
+                p->region = static_cast<uint32_t>(r);
+                p->x = static_cast<uint32_t>(xb / es);
+                p->y = static_cast<uint32_t>(y);
+                p->blocks = static_cast<uint16_t>(span_bytes >> 7);
+                p->lines = static_cast<uint16_t>(lines);
+                p->pitch = pitch;
+                pend[0] = pend[0] + 1;
+                return 1;
+            }
+        }
+    }
+    return 0;
+}
+} // namespace b200
+#endif
+
+#if PTO_B200_DEVICE_CODE
+namespace b200 {
+template <typename TileData, typename GlobalData>
+__device__ __forceinline__ void tload_impl(TileData &dst, GlobalData &src)
+{
     using T = typename TileData::DType;
     const T *g = reinterpret_cast<const T *>(src.data());
     const int64_t s3 = src.GetStride(3), s4 = src.GetStride(4);
@@ -286,7 +322,7 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
             if (b200::runs(PIPE_MTE2)) {
                 b200::stamp(0x4001);
             }
-            return {};
+            return;
         }
         for (int q = b200::tid_l(), q_step = b200::nthreads_l(); q < lines * chunks_per_line; q += q_step) {
             const int l = q / chunks_per_line, ch = q - l * chunks_per_line;
@@ -353,6 +389,71 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
         }
         b200::sync_l();
     }
+}
+} // namespace b200
+#endif
+
+template <typename TileData, typename GlobalData, typename... WaitEvents>
+PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... events)
+{
+    TSYNC(events...);
+    static_assert(sizeof(typename TileData::DType) == sizeof(typename GlobalData::DType),
+                  "TLOAD: source and destination element sizes differ");
+    static_assert(GlobalData::layout == Layout::ND || GlobalData::layout == Layout::DN,
+                  "TLOAD: ND and DN global tensors are supported");
+#if PTO_B200_DEVICE_CODE
+    if constexpr (b200::kPipeWarps) {
+        const bool loader = b200::runs(PIPE_MTE2);
+        if (!loader && !b200::runs(PIPE_MTE1)) {
+            return {}; // staged tiles are touched by the loading team and by the thread of MTE1 / M only
+        }
+        if constexpr (TileData::Loc == TileType::Mat && b200::is_tc_elem<typename TileData::DType>::value) {
+            using T = typename TileData::DType;
+            const bool cols_contig = (src.GetStride(4) == 1);
+            const int lines = cols_contig ? TileData::Rows : TileData::Cols;
+            const int span = cols_contig ? TileData::Cols : TileData::Rows;
+            const uint32_t pitch = static_cast<uint32_t>(lines) * 128u;
+            dst.pitch_ = pitch;
+            dst.major_ = cols_contig ? b200::kColsContiguous : b200::kRowsContiguous;
+            if (!loader) {
+                return {};
+            }
+            b200::stamp(0x4000);
+            const int v_lines = cols_contig ? dst.GetValidRow() : dst.GetValidCol();
+            const int v_span = cols_contig ? dst.GetValidCol() : dst.GetValidRow();
+            volatile uint32_t *pend = b200::pending_count();
+            if (threadIdx.x == 0) {
+                uint32_t take = 0;
+                if (v_lines == lines && v_span == span) {
+                    take = b200::tload_prepare_engine(
+                        reinterpret_cast<unsigned long long>(src.data()), static_cast<uint32_t>(sizeof(T)),
+                        static_cast<unsigned long long>(cols_contig ? src.GetStride(3) : src.GetStride(4)) * sizeof(T),
+                        static_cast<uint32_t>(lines), static_cast<uint32_t>(span * sizeof(T)),
+                        b200::smem_u32(b200::arena() + dst.addr_), pitch);
+                }
+                pend[1] = take;
+                if (take == 0) {
+                    b200::held_back()[14] = 1; // tiles written through the generic proxy from here on
+                }
+            }
+            b200::sync_l();
+            const uint32_t take = pend[1];
+            b200::sync_l();
+            if (take != 0) {
+                b200::stamp(0x4001);
+                return {};
+            }
+        } else {
+            if constexpr (TileData::Loc == TileType::Mat) {
+                dst.pitch_ = 0;
+                dst.major_ = b200::kPlain;
+            }
+            if (!loader) {
+                return {};
+            }
+        }
+    }
+    b200::tload_impl(dst, src);
 #endif
     return {};
 }
@@ -363,18 +464,44 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
 // strided dimension, 128 bytes (64 elements) of the contiguous dimension per line and block, 16-byte chunks
 // XOR-swizzled with the line number inside each group of 8 lines.  The offset along the contiguous dimension
 // must be a multiple of 8 elements.
-template <typename DstTileData, typename SrcTileData, typename... WaitEvents>
-PTO_INST RecordEvent TEXTRACT(DstTileData &dst, SrcTileData &src, uint16_t indexRow = 0, uint16_t indexCol = 0,
-                              WaitEvents &... events)
-{
-    TSYNC(events...);
-    static_assert(SrcTileData::Loc == TileType::Mat, "TEXTRACT: source must be a Mat tile");
-    static_assert(DstTileData::Loc == TileType::Left || DstTileData::Loc == TileType::Right ||
-                      DstTileData::Loc == TileType::ScaleLeft || DstTileData::Loc == TileType::ScaleRight,
-                  "TEXTRACT: destination must be a Left, Right, ScaleLeft or ScaleRight tile");
-    static_assert(sizeof(typename DstTileData::DType) == sizeof(typename SrcTileData::DType),
-                  "TEXTRACT: element sizes differ");
 #if PTO_B200_DEVICE_CODE
+namespace b200 {
+// LaunchOptions::extract_views: a window that is a whole number of swizzle atoms inside the staged tile is read by the
+// tensor core in place: the operand tile becomes a view of it (address from the start of the arena, the staged tile's
+// block pitch).  Returns false when the window has to be copied.
+template <typename DstTileData, typename SrcTileData>
+PTO_INTERNAL bool textract_view(DstTileData &dst, SrcTileData &src, int indexRow, int indexCol)
+{
+    using T = typename DstTileData::DType;
+    constexpr int kCE = 16 / static_cast<int>(sizeof(T));
+    constexpr int kChunksPerBlock = 8; // 128 bytes of the contiguous dimension
+    if ((control()->mode & kModeViews) == 0) {
+        return false;
+    }
+    const bool cols_contig = (src.major_ == kColsContiguous);
+    const int line0 = cols_contig ? indexRow : indexCol;
+    const int chunk0 = (cols_contig ? indexCol : indexRow) / kCE;
+    const int lines = cols_contig ? DstTileData::Rows : DstTileData::Cols;
+    const int chunks_per_line = (cols_contig ? DstTileData::Cols : DstTileData::Rows) / kCE;
+    const int src_lines = cols_contig ? SrcTileData::Rows : SrcTileData::Cols;
+    const int src_chunks = (cols_contig ? SrcTileData::Cols : SrcTileData::Rows) / kCE;
+    if ((line0 & 7) != 0 || (chunk0 % kChunksPerBlock) != 0 || line0 + lines > src_lines ||
+        chunk0 + chunks_per_line > src_chunks) {
+        return false;
+    }
+    const bool k_major = (DstTileData::Loc == TileType::Left) ? cols_contig : !cols_contig;
+    dst.addr_ = src.addr_ + static_cast<uint32_t>(chunk0 / kChunksPerBlock) * src.pitch_ + static_cast<uint32_t>(line0) * 128u;
+    dst.pitch_ = src.pitch_;
+    dst.major_ = static_cast<uint8_t>((k_major ? 0 : 1) | kView);
+    if (tid_b() == 0) {
+        held_back()[15] = 1; // flags that free the staged tile wait for the products (runtime.hpp)
+    }
+    return true;
+}
+
+template <typename DstTileData, typename SrcTileData>
+__device__ __forceinline__ void textract_impl(DstTileData &dst, SrcTileData &src, uint16_t indexRow, uint16_t indexCol)
+{
     using T = typename DstTileData::DType;
     if constexpr (DstTileData::Loc == TileType::ScaleLeft || DstTileData::Loc == TileType::ScaleRight) {
         // e8m0 scales of an MX product, one per 32 k: the window of the plain scale tile is written as the atoms the
@@ -427,17 +554,8 @@ PTO_INST RecordEvent TEXTRACT(DstTileData &dst, SrcTileData &src, uint16_t index
         const uint32_t dst_pitch = static_cast<uint32_t>(lines) * 128u;
         // Left [M x K] is a K-major operand when its columns are contiguous; Right [K x N] when its rows are
         const bool k_major = (DstTileData::Loc == TileType::Left) ? cols_contig : !cols_contig;
-        constexpr int kChunksPerBlock = 8; // 128 bytes of the contiguous dimension
-        if ((b200::control()->mode & b200::kModeViews) && (line0 & 7) == 0 && (chunk0 % kChunksPerBlock) == 0 &&
-            line0 + lines <= src_lines && chunk0 + chunks_per_line <= src_chunks) {
-            // the window is a whole number of swizzle atoms inside the staged tile: the tensor core reads it in place
-            dst.addr_ = src.addr_ + static_cast<uint32_t>(chunk0 / kChunksPerBlock) * src.pitch_ + static_cast<uint32_t>(line0) * 128u;
-            dst.pitch_ = src.pitch_;
-            dst.major_ = static_cast<uint8_t>((k_major ? 0 : 1) | b200::kView);
-            if (b200::tid_b() == 0) {
-                b200::held_back()[15] = 1; // flags that free the staged tile wait for the products (runtime.hpp)
-            }
-            return {};
+        if (b200::kPipeWarps && b200::tid_b() == 0) {
+            b200::held_back()[14] = 1; // an operand tile written through the generic proxy
         }
         const uint8_t *s = b200::arena_of<TileType::Mat>() + src.addr_;
         uint8_t *d = b200::arena_of<DstTileData::Loc>() + dst.addr_;
@@ -453,12 +571,46 @@ PTO_INST RecordEvent TEXTRACT(DstTileData &dst, SrcTileData &src, uint16_t index
         dst.pitch_ = dst_pitch;
         dst.major_ = k_major ? 0 : 1;
     }
-    if (DstTileData::ValidRow == DYNAMIC) {
+    if constexpr (DstTileData::ValidRow == DYNAMIC) {
         dst.RowMaskInternal = src.GetValidRow() - indexRow;
     }
-    if (DstTileData::ValidCol == DYNAMIC) {
+    if constexpr (DstTileData::ValidCol == DYNAMIC) {
         dst.ColMaskInternal = src.GetValidCol() - indexCol;
     }
+}
+} // namespace b200
+#endif
+
+template <typename DstTileData, typename SrcTileData, typename... WaitEvents>
+PTO_INST RecordEvent TEXTRACT(DstTileData &dst, SrcTileData &src, uint16_t indexRow = 0, uint16_t indexCol = 0,
+                              WaitEvents &... events)
+{
+    TSYNC(events...);
+    static_assert(SrcTileData::Loc == TileType::Mat, "TEXTRACT: source must be a Mat tile");
+    static_assert(DstTileData::Loc == TileType::Left || DstTileData::Loc == TileType::Right ||
+                      DstTileData::Loc == TileType::ScaleLeft || DstTileData::Loc == TileType::ScaleRight,
+                  "TEXTRACT: destination must be a Left, Right, ScaleLeft or ScaleRight tile");
+    static_assert(sizeof(typename DstTileData::DType) == sizeof(typename SrcTileData::DType),
+                  "TEXTRACT: element sizes differ");
+#if PTO_B200_DEVICE_CODE
+    if constexpr (b200::kPipeWarps) {
+        if (!b200::runs(PIPE_MTE1)) {
+            return {}; // operand tiles are only ever used by the thread of MTE1 and M
+        }
+        if constexpr ((DstTileData::Loc == TileType::Left || DstTileData::Loc == TileType::Right) &&
+                      b200::is_tc_elem<typename DstTileData::DType>::value) {
+            if (b200::textract_view(dst, src, indexRow, indexCol)) {
+                if constexpr (DstTileData::ValidRow == DYNAMIC) {
+                    dst.RowMaskInternal = src.GetValidRow() - indexRow;
+                }
+                if constexpr (DstTileData::ValidCol == DYNAMIC) {
+                    dst.ColMaskInternal = src.GetValidCol() - indexCol;
+                }
+                return {};
+            }
+        }
+    }
+    b200::textract_impl(dst, src, indexRow, indexCol);
 #endif
     return {};
 }
@@ -904,10 +1056,10 @@ PTO_INTERNAL void store_elem(GT *p, GT v)
 #endif
 }
 
-template <AtomicType kAtomic, ReluPreMode kRelu, typename GlobalData, typename TileData>
-PTO_INTERNAL void tstore(GlobalData &dst, TileData &src)
-{
 #if PTO_B200_DEVICE_CODE
+template <AtomicType kAtomic, ReluPreMode kRelu, typename GlobalData, typename TileData>
+__device__ __forceinline__ void tstore_impl(GlobalData &dst, TileData &src)
+{
     using GT = typename GlobalData::DType;
     GT *g = dst.data();
     const int64_t s3 = dst.GetStride(3), s4 = dst.GetStride(4);
@@ -1012,6 +1164,17 @@ PTO_INTERNAL void tstore(GlobalData &dst, TileData &src)
             }
         }
     }
+}
+#endif
+
+template <AtomicType kAtomic, ReluPreMode kRelu, typename GlobalData, typename TileData>
+PTO_INTERNAL void tstore(GlobalData &dst, TileData &src)
+{
+#if PTO_B200_DEVICE_CODE
+    if (kPipeWarps && !runs(TileData::Loc == TileType::Acc ? PIPE_FIX : PIPE_MTE3)) {
+        return;
+    }
+    tstore_impl<kAtomic, kRelu>(dst, src);
 #endif
 }
 } // namespace b200
@@ -1150,6 +1313,9 @@ PTO_INST RecordEvent TMOV(DstTileData &dst, SrcTileData &src, WaitEvents &... ev
             constexpr uint32_t dst_pitch = static_cast<uint32_t>(lines) * 128u;
             const uint8_t *s = reinterpret_cast<const uint8_t *>(src.data());
             uint8_t *d = b200::arena_of<DstTileData::Loc>() + dst.addr_;
+            if (b200::kPipeWarps && b200::tid_b() == 0) {
+                b200::held_back()[14] = 1; // an operand tile written through the generic proxy
+            }
             for (int q = b200::tid_b(), q_step = b200::nthreads_b(); q < lines * chunks_per_line; q += q_step) {
                 const int l = q / chunks_per_line, ch = q - l * chunks_per_line;
                 const uint32_t d_off = (ch >> 3) * dst_pitch + l * 128u + (((ch & 7) ^ (l & 7)) << 4);

@@ -52,6 +52,14 @@ constexpr int kWarps = kBlockThreads / 32;
 //                  the pipes they name
 //   kModeViews     TEXTRACT / TMOV of an aligned window hands the operand tile a view of the staged tile (no copy)
 constexpr int kModeInOrder = 1, kModePipeWarps = 2, kModeViews = 4;
+// kModePipeWarps is a property of the translation unit: define PTO_B200_PIPE_WARPS before including the PTO header and
+// every tile program of the unit runs with its pipes on warps of their own (LaunchOptions::pipe_warps must say the
+// same).  The instructions then know at compile time which threads execute them.
+#ifdef PTO_B200_PIPE_WARPS
+constexpr bool kPipeWarps = true;
+#else
+constexpr bool kPipeWarps = false;
+#endif
 constexpr int kTeamLThreads = 64;   // warps 0..1
 constexpr int kTeamBWarp = 3;
 constexpr int kTeamCFirstWarp = 4, kTeamCThreads = 128; // warps 4..7
@@ -109,6 +117,30 @@ constexpr int kTimelineEntries = 4096;
 static __device__ unsigned long long g_timeline[3][kTimelineEntries];
 static __device__ unsigned int g_timeline_n[3];
 #endif
+// Matrices in global memory that a launch registers so that TLOAD can fetch tiles of them with the copy engine (TMA):
+// a tile program builds its GlobalTensors from raw pointers on the device, where a tensor map cannot be encoded, so the
+// launch encodes one map per registered matrix (rows of `pitch` elements, a box of 128 bytes x `box_rows` rows, 128-byte
+// swizzle) and TLOAD turns a tile's address into coordinates of the matrix it lies in.  Tiles of unregistered memory are
+// fetched with cp.async.  Used with pipe_warps.
+constexpr int kMaxTmaRegions = 4;
+struct TmaRegion {
+    const void *base = nullptr; // element (0, 0) of a row-major matrix, 16-byte aligned
+    uint64_t rows = 0, cols = 0; // extent in elements
+    uint64_t pitch = 0;          // elements between rows (pitch * elem_bytes a multiple of 16)
+    int elem_bytes = 2;
+    uint32_t box_rows = 128;     // rows one copy moves (at most 256); a tile's lines are a multiple of it
+};
+struct TmaTable {
+    CUtensorMap map[kMaxTmaRegions];
+    unsigned long long base[kMaxTmaRegions];
+    unsigned long long bytes[kMaxTmaRegions];       // base .. base + bytes holds the matrix
+    unsigned long long pitch_bytes[kMaxTmaRegions];
+    unsigned long long row_bytes[kMaxTmaRegions];   // cols * elem_bytes
+    uint32_t box_rows[kMaxTmaRegions];
+    uint32_t elem_bytes[kMaxTmaRegions];
+    int count;
+};
+
 #if PTO_B200_DEVICE_CODE
 // The block's dynamic shared memory, declared 1 KiB aligned (the swizzled operand layouts want that).  The launch
 // trampoline checks the address and reports instead of running the program if the declaration was not honoured.
@@ -194,14 +226,14 @@ __device__ __forceinline__ uint32_t tile_auto_place(int space, uint32_t amount)
 
 // ---- teams: who executes an instruction.  Without kModePipeWarps the whole block does.  With it:
 //   team L  warps 0..1  MTE2 (loads from global memory)
-//   team B  warp  3     MTE1 and M (operand staging and the products, issued by its first lane)
+//   team B  the first thread of warp 3: MTE1 and M (operand windows and the products: one thread issues them)
 //   team C  warps 4..7  V, MTE3, FIX, S (vector work and stores; four warps, so that together they reach every
 //                       tensor-memory lane)
 // Warp 2 has no pipe.  Every warp walks the whole instruction stream; an instruction does its work on the threads of
 // its pipe's team and nothing on the others (their thread index is kNotAMember, which empties every loop).
-__device__ __forceinline__ bool pipe_warps()
+__device__ __forceinline__ constexpr bool pipe_warps()
 {
-    return (control()->mode & kModePipeWarps) != 0;
+    return kPipeWarps;
 }
 enum : int { kTeamL = 0, kTeamB = 1, kTeamC = 2 };
 __device__ __forceinline__ int team_of_pipe(int pipe)
@@ -210,7 +242,7 @@ __device__ __forceinline__ int team_of_pipe(int pipe)
 }
 __device__ __forceinline__ int team_threads(int team)
 {
-    return team == kTeamL ? kTeamLThreads : (team == kTeamB ? 32 : kTeamCThreads);
+    return team == kTeamL ? kTeamLThreads : (team == kTeamB ? 1 : kTeamCThreads);
 }
 __device__ __forceinline__ int team_first_thread(int team)
 {
@@ -237,7 +269,7 @@ __device__ __forceinline__ void team_sync()
         __syncthreads();
     } else if (team_tid<kTeam>() != kNotAMember) {
         if (kTeam == kTeamB) {
-            __syncwarp();
+            // one thread
         } else {
             asm volatile("bar.sync %0, %1;" ::"n"(1 + kTeam), "n"(kTeam == kTeamL ? kTeamLThreads : kTeamCThreads) : "memory");
         }
@@ -318,7 +350,38 @@ __device__ __forceinline__ uint32_t *held_back()
 {
     return reinterpret_cast<uint32_t *>(&control()->flags[flag_index(PIPE_V, PIPE_V, 0)]);
 }
-constexpr int kMaxHeldBack = 12; // held_back()[13]: 1 + arena offset of TSTORE's staging area, 0 = none
+constexpr int kMaxHeldBack = 12;
+// held_back()[14]: tiles were written through the generic proxy (cp.async loads, copying TEXTRACT / TMOV) since the
+// block began: waits then order those writes before the tensor core's reads with a proxy fence
+
+// The launch's table of registered matrices (a kernel parameter; its address is kept in the flag words of
+// PIPE_MTE2 -> PIPE_MTE2) and the loads that TLOAD has prepared but not yet issued (flag words of PIPE_MTE3 -> PIPE_MTE3):
+// a copy by the copy engine completes on an mbarrier named when it is issued, and the flag that a load raises is only
+// known at the set_flag that follows it, so TLOAD records the copy and set_flag(PIPE_MTE2, ...) issues it.
+struct PendingLoad {
+    uint32_t dst;       // shared-memory address of the tile
+    uint32_t region;    // index into the table
+    uint32_t x, y;      // element coordinates of the tile's first element
+    uint16_t blocks;    // 128-byte blocks along the contiguous dimension
+    uint16_t lines;     // lines of the tile
+    uint32_t pitch;     // bytes between blocks in shared memory
+};
+constexpr int kMaxPendingLoads = 2;
+__device__ __forceinline__ const TmaTable *&tma_table()
+{
+    return *reinterpret_cast<const TmaTable **>(&control()->flags[flag_index(PIPE_MTE2, PIPE_MTE2, 0)]);
+}
+__device__ __forceinline__ volatile uint32_t *pending_count()
+{
+    return reinterpret_cast<volatile uint32_t *>(&control()->flags[flag_index(PIPE_MTE3, PIPE_MTE3, 0)]);
+}
+__device__ __forceinline__ PendingLoad *pending_loads()
+{
+    return reinterpret_cast<PendingLoad *>(reinterpret_cast<uint8_t *>(&control()->flags[flag_index(PIPE_MTE3, PIPE_MTE3, 0)]) + 16);
+}
+static_assert(16 + kMaxPendingLoads * sizeof(PendingLoad) <= 64, "pending loads fit the eight flag words");
+// [1] of the pending block: TLOAD's decision for the team (1: the copy engine fetches the tile, 0: cp.async)
+ // held_back()[13]: 1 + arena offset of TSTORE's staging area, 0 = none
 
 // ---- mbarrier primitives (bounded waits: a wait that runs out raises the block's abort flag)
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
@@ -360,7 +423,7 @@ __device__ __forceinline__ void give_up(int where)
         ctl->fail_where = where;
     }
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int where = -1)
+__device__ __noinline__ bool mbar_wait_slow(uint64_t *bar, uint32_t parity, int where)
 {
     Control *ctl = control();
     volatile int *abort_flag = &ctl->abort_flag;
@@ -401,9 +464,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int wh
     return false;
 }
 
+// the first poll inline, the bounded polling loop out of line (a tile program has dozens of waits)
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int where = -1)
+{
+    if (mbar_try_wait(bar, parity)) {
+        return true;
+    }
+    return mbar_wait_slow(bar, parity, where);
+}
+
 // pipe_warps: before flag `f` is raised for the n-th time, its first n - 1 raises must have been consumed (bounded
 // like every wait; see Control::raised)
-__device__ __forceinline__ bool wait_until_consumed(int f, uint8_t n)
+__device__ __noinline__ bool wait_until_consumed_slow(int f, uint8_t n)
 {
     Control *ctl = control();
     volatile uint8_t *consumed = &ctl->consumed[f];
@@ -434,6 +506,55 @@ __device__ __forceinline__ bool wait_until_consumed(int f, uint8_t n)
     return false;
 }
 
+__device__ __forceinline__ bool wait_until_consumed(int f, uint8_t n)
+{
+    if (*reinterpret_cast<volatile uint8_t *>(&control()->consumed[f]) == n) {
+        return true;
+    }
+    return wait_until_consumed_slow(f, n);
+}
+
+// ---- loads by the copy engine
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint64_t *bar, int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+// issues the loads that TLOAD prepared, completing on `bar` (called by the first thread of team L before it arrives)
+__device__ __noinline__ void issue_pending_loads(uint64_t *bar)
+{
+    volatile uint32_t *count = pending_count();
+    const uint32_t n = *count;
+    if (n == 0) {
+        return;
+    }
+    const TmaTable *table = tma_table();
+    const PendingLoad *p = pending_loads();
+    uint32_t bytes = 0;
+    for (uint32_t i = 0; i < n; ++i) {
+        bytes += static_cast<uint32_t>(p[i].blocks) * p[i].lines * 128u;
+    }
+    mbar_expect_tx(bar, bytes);
+    for (uint32_t i = 0; i < n; ++i) {
+        const uint32_t r = p[i].region;
+        const uint32_t box_rows = table->box_rows[r];
+        const int block_elems = static_cast<int>(128u / table->elem_bytes[r]);
+        for (uint32_t b = 0; b < p[i].blocks; ++b) {
+            for (uint32_t l = 0; l < p[i].lines; l += box_rows) {
+                tma_load_2d(p[i].dst + b * p[i].pitch + l * 128u, &table->map[r], bar,
+                            static_cast<int>(p[i].x) + static_cast<int>(b) * block_elems, static_cast<int>(p[i].y + l));
+            }
+        }
+    }
+    *count = 0;
+}
+
 // ---- tcgen05 helpers
 __device__ __forceinline__ void tc_fence_before()
 {
@@ -455,7 +576,7 @@ __device__ __forceinline__ void tc_commit(uint64_t *bar)
 
 // Block prologue / epilogue (called by the launch trampoline, not by tile programs).
 __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, uint32_t l0a_offset, uint32_t l0b_offset,
-                                            int mode, uint32_t store_staging)
+                                            int mode, uint32_t store_staging, const TmaTable *table)
 {
     Control *ctl = control();
     const int nthreads = blockDim.x;
@@ -467,7 +588,7 @@ __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, ui
             // no flags of a pipe with itself: PIPE_S -> PIPE_S holds the tile allocator's counters (tile_auto_place),
             // PIPE_V -> PIPE_V the flags held back for views (held_back)
             ctl->flags[f] = 0;
-        } else if (mode & kModePipeWarps) {
+        } else if (kPipeWarps) {
             // the threads of the source pipe's team arrive; team B signals through one thread or the tensor core
             mbar_init(&ctl->flags[f], team_of_pipe(src) == kTeamB ? 1u : static_cast<uint32_t>(team_threads(team_of_pipe(src))));
         } else {
@@ -504,6 +625,7 @@ __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, ui
     __syncthreads(); // (the flag words of a pipe with itself were zeroed above)
     if (threadIdx.x == 0) {
         held_back()[13] = store_staging == kNoStoreStaging ? 0u : store_staging + 1u;
+        tma_table() = table;
     }
     if (threadIdx.x < 32) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
@@ -516,8 +638,38 @@ __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, ui
     tc_fence_after();
 }
 
+// pipe_warps: team L brings its loads to completion (those prepared for the copy engine and not yet issued, and its
+// cp.async copies); the flag PIPE_MTE2 -> PIPE_ALL, 7 is kept for this
+__device__ __noinline__ void complete_loads()
+{
+    if (!kPipeWarps || threadIdx.x >= kTeamLThreads) {
+        return;
+    }
+    Control *ctl = control();
+    const int f = flag_index(PIPE_MTE2, PIPE_ALL, 7);
+    sync_l();
+    const bool pending = *pending_count() != 0;
+    sync_l();
+    if (pending) {
+        if (threadIdx.x == 0) {
+            issue_pending_loads(&ctl->flags[f]);
+        }
+        mbar_arrive_after_copies(&ctl->flags[f]);
+        volatile uint32_t *word = &ctl->phase[f >> 5][threadIdx.x >> 5];
+        const uint32_t bit = 1u << (f & 31);
+        mbar_wait(&ctl->flags[f], (*word & bit) ? 1u : 0u, f);
+        __syncwarp();
+        if ((threadIdx.x & 31) == 0) {
+            *word = *word ^ bit;
+        }
+        __syncwarp();
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+}
+
 __device__ __forceinline__ void block_end(StatusRecord *status)
 {
+    complete_loads();
     asm volatile("cp.async.wait_all;" ::: "memory");
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); // bulk stores of TSTORE have read their staging and landed
     tc_fence_before();
@@ -570,12 +722,62 @@ struct LaunchOptions {
     // a whole fp32 accumulator tile to 16-byte aligned rows then goes through it, each thread staging 128 bytes of
     // its row and handing them to an asynchronous bulk copy, instead of storing 16 bytes per instruction.
     uint32_t store_staging_offset = kNoStoreStaging;
+    // matrices whose tiles TLOAD may fetch with the copy engine (see TmaRegion)
+    TmaRegion tma[kMaxTmaRegions];
+    int tma_count = 0;
 };
+
+// encodes the launch's registered matrices (host)
+inline cudaError_t make_tma_table(const LaunchOptions &opt, TmaTable &table)
+{
+    memset(&table, 0, sizeof(table));
+    if (opt.tma_count == 0) {
+        return cudaSuccess;
+    }
+    if (opt.tma_count < 0 || opt.tma_count > kMaxTmaRegions) {
+        return cudaErrorInvalidValue;
+    }
+    using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || fn == nullptr) {
+        return cudaErrorNotSupported;
+    }
+    for (int i = 0; i < opt.tma_count; ++i) {
+        const TmaRegion &r = opt.tma[i];
+        const uint64_t es = static_cast<uint64_t>(r.elem_bytes);
+        if (r.base == nullptr || (es != 1 && es != 2) || r.box_rows == 0 || r.box_rows > 256 || r.rows == 0 || r.cols == 0 ||
+            (reinterpret_cast<uintptr_t>(r.base) & 15u) != 0 || ((r.pitch * es) & 15u) != 0 || r.pitch < r.cols) {
+            return cudaErrorInvalidValue;
+        }
+        const cuuint64_t dims[2] = {r.cols, r.rows};
+        const cuuint64_t strides[1] = {r.pitch * es};
+        const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / es), r.box_rows};
+        const cuuint32_t elem_strides[2] = {1, 1};
+        if (reinterpret_cast<EncodeFn>(fn)(&table.map[i], es == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2,
+                                           const_cast<void *>(r.base), dims, strides, box, elem_strides,
+                                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            return cudaErrorInvalidValue;
+        }
+        table.base[i] = reinterpret_cast<unsigned long long>(r.base);
+        table.bytes[i] = ((r.rows - 1) * r.pitch + r.cols) * es;
+        table.pitch_bytes[i] = r.pitch * es;
+        table.row_bytes[i] = r.cols * es;
+        table.box_rows[i] = r.box_rows;
+        table.elem_bytes[i] = static_cast<uint32_t>(es);
+    }
+    table.count = opt.tma_count;
+    return cudaSuccess;
+}
 
 template <typename Program>
 __global__ void __launch_bounds__(kBlockThreads, 1)
     block_kernel(Program program, StatusRecord *status, unsigned long long wait_limit_ns, uint32_t l0a_offset,
-                 uint32_t l0b_offset, int mode, uint32_t store_staging)
+                 uint32_t l0b_offset, int mode, uint32_t store_staging, const __grid_constant__ TmaTable tma)
 {
 #if PTO_B200_DEVICE_CODE
     if ((smem_u32(smem_base()) & 1023u) != 0) {
@@ -586,7 +788,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1)
         }
         return;
     }
-    block_begin(wait_limit_ns, l0a_offset, l0b_offset, mode, store_staging);
+    block_begin(wait_limit_ns, l0a_offset, l0b_offset, mode, store_staging, &tma);
     program();
     block_end(status);
 #endif
@@ -596,16 +798,23 @@ __global__ void __launch_bounds__(kBlockThreads, 1)
 template <typename Program>
 inline cudaError_t launch(uint32_t blocks, void *stream, Program program, const LaunchOptions &opt)
 {
-    cudaError_t e =
-        cudaFuncSetAttribute(block_kernel<Program>, cudaFuncAttributeMaxDynamicSharedMemorySize, opt.smem_bytes);
+    if (opt.pipe_warps != kPipeWarps || (opt.pipe_warps && opt.in_order)) {
+        return cudaErrorInvalidValue; // pipe_warps is compiled in (PTO_B200_PIPE_WARPS) and excludes in_order
+    }
+    TmaTable table;
+    cudaError_t e = make_tma_table(opt, table);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    e = cudaFuncSetAttribute(block_kernel<Program>, cudaFuncAttributeMaxDynamicSharedMemorySize, opt.smem_bytes);
     if (e != cudaSuccess) {
         return e;
     }
     block_kernel<Program><<<blocks, kBlockThreads, opt.smem_bytes, static_cast<cudaStream_t>(stream)>>>(
         program, static_cast<StatusRecord *>(opt.status), opt.wait_limit_ns, opt.l0a_offset, opt.l0b_offset,
-        (opt.in_order ? kModeInOrder : 0) | (opt.pipe_warps ? kModePipeWarps : 0) |
+        (opt.in_order ? kModeInOrder : 0) | (kPipeWarps ? kModePipeWarps : 0) |
             (opt.pipe_warps && opt.extract_views ? kModeViews : 0),
-        opt.store_staging_offset);
+        opt.store_staging_offset, table);
     return cudaGetLastError();
 }
 template <typename Program>
@@ -655,7 +864,28 @@ PTO_INTERNAL uint32_t get_block_num()
 #endif
 }
 
-PTO_INTERNAL void pipe_barrier(pipe_t pipe);
+namespace pto {
+namespace b200 {
+// a pipe ordered with itself: the threads that run it meet
+PTO_INTERNAL void pipe_self_barrier(pipe_t pipe)
+{
+#if PTO_B200_DEVICE_CODE
+    if (!kPipeWarps) {
+        __syncthreads();
+        return;
+    }
+    const int team = team_of_pipe(pipe);
+    if (team == kTeamL) {
+        sync_l();
+    } else if (team == kTeamC) {
+        sync();
+    }
+#else
+    (void)pipe;
+#endif
+}
+} // namespace b200
+} // namespace pto
 
 // set_flag(src, dst, id): the flag is raised once everything issued so far on pipe `src` is complete.
 //   PIPE_M    : tcgen05.commit by the issuing thread (covers all earlier tcgen05.mma)
@@ -665,7 +895,7 @@ PTO_INTERNAL void set_flag(pipe_t src, pipe_t dst, int id)
 {
 #if PTO_B200_DEVICE_CODE
     if (src == dst) {
-        pipe_barrier(src); // a pipe is ordered with itself by a barrier, not a flag
+        pto::b200::pipe_self_barrier(src); // a pipe is ordered with itself by a barrier, not a flag
         return;
     }
     pto::b200::Control *ctl = pto::b200::control();
@@ -674,7 +904,7 @@ PTO_INTERNAL void set_flag(pipe_t src, pipe_t dst, int id)
     if (pto::b200::runs(src)) {
         pto::b200::stamp(0x3000 + f);
     }
-    if (ctl->mode & pto::b200::kModePipeWarps) {
+    if (pto::b200::kPipeWarps) {
         if (!pto::b200::runs(src)) {
             return;
         }
@@ -682,53 +912,47 @@ PTO_INTERNAL void set_flag(pipe_t src, pipe_t dst, int id)
         // a flag between two teams is raised again only when its previous raise has been consumed (Control::raised)
         const bool between_teams = team != pto::b200::team_of_pipe(dst);
         if (team == pto::b200::kTeamB) {
-            const bool leader = (threadIdx.x & 31) == 0;
+            // one thread runs MTE1 and M: it raises flags alone
+            volatile uint32_t *held = pto::b200::held_back();
             if (src == PIPE_M) {
-                if (leader) {
-                    if (between_teams) {
-                        const uint8_t n = ctl->raised[f];
-                        pto::b200::wait_until_consumed(f, n);
-                        ctl->raised[f] = static_cast<uint8_t>(n + 1);
-                    }
-                    pto::b200::tc_commit(bar);
-                    // flags held back for views: the products that read them are all issued by now
-                    volatile uint32_t *held = pto::b200::held_back();
-                    const uint32_t count = held[0];
-                    for (uint32_t i = 0; i < count; ++i) {
-                        const int hf = static_cast<int>(held[1 + i]);
-                        const uint8_t n = ctl->raised[hf];
-                        pto::b200::wait_until_consumed(hf, n);
-                        ctl->raised[hf] = static_cast<uint8_t>(n + 1);
-                        pto::b200::tc_commit(&ctl->flags[hf]);
-                    }
+                if (between_teams) {
+                    const uint8_t n = ctl->raised[f];
+                    pto::b200::wait_until_consumed(f, n);
+                    ctl->raised[f] = static_cast<uint8_t>(n + 1);
+                }
+                pto::b200::tc_commit(bar);
+                // flags held back for views: the products that read them are all issued by now
+                const uint32_t count = held[0];
+                for (uint32_t i = 0; i < count; ++i) {
+                    const int hf = static_cast<int>(held[1 + i]);
+                    const uint8_t n = ctl->raised[hf];
+                    pto::b200::wait_until_consumed(hf, n);
+                    ctl->raised[hf] = static_cast<uint8_t>(n + 1);
+                    pto::b200::tc_commit(&ctl->flags[hf]);
+                }
+                if (count != 0) {
                     held[0] = 0;
-                    held[15] = 0;
                 }
+                held[15] = 0;
+            } else if (!between_teams) {
+                // MTE1 -> M: the same thread stages operands and issues products, program order is the order; copies
+                // made through the generic proxy are made visible to the tensor core
+                if (held[14] != 0) {
+                    pto::b200::fence_async_proxy();
+                }
+            } else if (dst == PIPE_MTE2 && held[15] != 0 && held[0] < pto::b200::kMaxHeldBack) {
+                // a view was handed out since the matrix pipe last raised a flag: held back (see held_back)
+                held[1 + held[0]] = static_cast<uint32_t>(f);
+                held[0] = held[0] + 1;
             } else {
-                volatile uint32_t *held = pto::b200::held_back();
-                // held[15]: a view was handed out since the matrix pipe last raised a flag
-                __syncwarp();
-                const bool hold = dst == PIPE_MTE2 && held[15] != 0 && held[0] < pto::b200::kMaxHeldBack;
-                __syncwarp();
-                if (hold) {
-                    if (leader) {
-                        held[1 + held[0]] = static_cast<uint32_t>(f);
-                        held[0] = held[0] + 1;
-                    }
-                } else {
-                    pto::b200::fence_async_proxy(); // copies of TEXTRACT, visible to the tensor core
-                    __syncwarp();
-                    if (leader) {
-                        if (between_teams) {
-                            const uint8_t n = ctl->raised[f];
-                            pto::b200::wait_until_consumed(f, n);
-                            ctl->raised[f] = static_cast<uint8_t>(n + 1);
-                        }
-                        pto::b200::mbar_arrive(bar);
-                    }
+                if (held[14] != 0) {
+                    pto::b200::fence_async_proxy();
                 }
+                const uint8_t n = ctl->raised[f];
+                pto::b200::wait_until_consumed(f, n);
+                ctl->raised[f] = static_cast<uint8_t>(n + 1);
+                pto::b200::mbar_arrive(bar);
             }
-            __syncwarp();
             pto::b200::stamp(0x3800 + f);
             return;
         }
@@ -749,6 +973,9 @@ PTO_INTERNAL void set_flag(pipe_t src, pipe_t dst, int id)
                 ctl->raised[f] = static_cast<uint8_t>(n + 1);
             }
             pto::b200::wait_until_consumed(f, n);
+        }
+        if (src == PIPE_MTE2 && threadIdx.x == 0) {
+            pto::b200::issue_pending_loads(bar); // the copy engine's loads of the TLOADs before this flag complete on it
         }
     }
     if (src == PIPE_M) {
@@ -779,33 +1006,63 @@ PTO_INTERNAL void wait_flag(pipe_t src, pipe_t dst, int id)
         return; // see set_flag
     }
     pto::b200::Control *ctl = pto::b200::control();
-    if ((ctl->mode & pto::b200::kModePipeWarps) && !pto::b200::runs(dst)) {
-        return; // the warps of the waiting pipe wait
-    }
     const int f = pto::b200::flag_index(src, dst, id);
+    if (pto::b200::kPipeWarps) {
+        if (!pto::b200::runs(dst)) {
+            return; // the threads of the waiting pipe wait
+        }
+        const int team = pto::b200::team_of_pipe(dst);
+        const bool between_teams = pto::b200::team_of_pipe(src) != team;
+        if (team == pto::b200::kTeamB && !between_teams && src == PIPE_MTE1) {
+            return; // MTE1 -> M on one thread: see set_flag
+        }
+        pto::b200::stamp(0x1000 + f);
+        volatile uint32_t *word = &ctl->phase[f >> 5][threadIdx.x >> 5];
+        const uint32_t bit = 1u << (f & 31);
+        const uint32_t parity = (*word & bit) ? 1u : 0u;
+        const bool ok = pto::b200::mbar_wait(&ctl->flags[f], parity, f);
+        if (team == pto::b200::kTeamB) {
+            *word = *word ^ bit;
+            if (between_teams && ok) {
+                ctl->consumed[f] = static_cast<uint8_t>(ctl->consumed[f] + 1);
+            }
+            if (pto::b200::held_back()[14] != 0) {
+                pto::b200::fence_async_proxy(); // tiles written through the generic proxy, read by the tensor core
+            }
+        } else {
+            __syncwarp();
+            if ((threadIdx.x & 31) == 0) {
+                *word = *word ^ bit;
+            }
+            __syncwarp();
+            if (between_teams) {
+                // every warp of the waiting team is past the wait: the flag may be raised again (Control::consumed)
+                if (team == pto::b200::kTeamL) {
+                    pto::b200::sync_l();
+                } else {
+                    pto::b200::sync();
+                }
+                if (ok && static_cast<int>(threadIdx.x) == pto::b200::team_first_thread(team)) {
+                    ctl->consumed[f] = static_cast<uint8_t>(ctl->consumed[f] + 1);
+                }
+            }
+            pto::b200::fence_async_proxy();
+        }
+        pto::b200::tc_fence_after();
+        pto::b200::stamp(0x2000 + f);
+        return;
+    }
     pto::b200::stamp(0x1000 + f);
     // all lanes of a warp run the same instruction stream, so the phase is kept once per warp
     volatile uint32_t *word = &ctl->phase[f >> 5][threadIdx.x >> 5];
     const uint32_t bit = 1u << (f & 31);
     const uint32_t parity = (*word & bit) ? 1u : 0u;
-    const bool ok = pto::b200::mbar_wait(&ctl->flags[f], parity, f);
+    pto::b200::mbar_wait(&ctl->flags[f], parity, f);
     __syncwarp();
     if ((threadIdx.x & 31) == 0) {
         *word = *word ^ bit;
     }
     __syncwarp();
-    if ((ctl->mode & pto::b200::kModePipeWarps) && pto::b200::team_of_pipe(src) != pto::b200::team_of_pipe(dst)) {
-        // every warp of the waiting team is past the wait: the flag may be raised again (Control::consumed)
-        const int team = pto::b200::team_of_pipe(dst);
-        if (team == pto::b200::kTeamL) {
-            pto::b200::sync_l();
-        } else if (team == pto::b200::kTeamC) {
-            pto::b200::sync();
-        }
-        if (ok && static_cast<int>(threadIdx.x) == pto::b200::team_first_thread(team)) {
-            ctl->consumed[f] = static_cast<uint8_t>(ctl->consumed[f] + 1);
-        }
-    }
     pto::b200::tc_fence_after();
     pto::b200::fence_async_proxy();
     pto::b200::stamp(0x2000 + f);
@@ -851,9 +1108,7 @@ PTO_INTERNAL void pipe_barrier(pipe_t pipe)
     }
     if (pipe == PIPE_ALL) {
         // every pipe drains: each team completes what it has in flight, then all meet
-        if (pto::b200::runs(PIPE_MTE2)) {
-            asm volatile("cp.async.wait_all;" ::: "memory");
-        }
+        pto::b200::complete_loads();
         set_flag(PIPE_M, PIPE_ALL, 7);
         wait_flag(PIPE_M, PIPE_ALL, 7); // (PIPE_ALL is a pipe of team C)
         if (pto::b200::runs(PIPE_MTE2) || pto::b200::runs(PIPE_M) || pto::b200::runs(PIPE_V)) {
@@ -862,6 +1117,7 @@ PTO_INTERNAL void pipe_barrier(pipe_t pipe)
     } else {
         const int team = pto::b200::team_of_pipe(pipe);
         if (team == pto::b200::kTeamL) {
+            pto::b200::complete_loads();
             pto::b200::sync_l();
         } else if (team == pto::b200::kTeamB) {
             pto::b200::sync_b();

@@ -198,11 +198,32 @@ constexpr int tile_space(TileType loc)
 }
 } // namespace b200
 
+namespace b200 {
+// the valid extents of a tile are members only where they are dynamic: a tile handle stays three words otherwise
+// (arrays of handles indexed at run time live in local memory)
+template <bool kDynamic, int kStatic>
+struct RowMaskMember {
+    static constexpr int RowMaskInternal = kStatic;
+};
+template <int kStatic>
+struct RowMaskMember<true, kStatic> {
+    int RowMaskInternal = 0;
+};
+template <bool kDynamic, int kStatic>
+struct ColMaskMember {
+    static constexpr int ColMaskInternal = kStatic;
+};
+template <int kStatic>
+struct ColMaskMember<true, kStatic> {
+    int ColMaskInternal = 0;
+};
+} // namespace b200
+
 template <TileType Loc_, typename Element_, const int Rows_, const int Cols_,
           const BLayout BFractal_ = BLayout::RowMajor, const int RowValid_ = Rows_, const int ColValid_ = Cols_,
           const SLayout SFractal_ = SLayout::NoneBox, const int SFractalSize_ = TileConfig::fractalABSize,
           const PadValue PadVal_ = PadValue::Null, const CompactMode Compact_ = CompactMode::Null>
-struct Tile {
+struct Tile : public b200::RowMaskMember<RowValid_ == DYNAMIC, RowValid_>, public b200::ColMaskMember<ColValid_ == DYNAMIC, ColValid_> {
     using DType = Element_;
     using TileDType = DType *;
 
@@ -240,27 +261,27 @@ struct Tile {
     PTO_INTERNAL Tile(std::enable_if_t<RM == DYNAMIC && CM == DYNAMIC, size_t> vr,
                       std::enable_if_t<RM == DYNAMIC && CM == DYNAMIC, size_t> vc)
     {
-        RowMaskInternal = static_cast<int>(vr);
-        ColMaskInternal = static_cast<int>(vc);
+        this->RowMaskInternal = static_cast<int>(vr);
+        this->ColMaskInternal = static_cast<int>(vc);
         place();
     }
     template <int RM = ValidRow, int CM = ValidCol>
     PTO_INTERNAL Tile(std::enable_if_t<(RM == DYNAMIC) && (CM > 0), size_t> vr)
     {
-        RowMaskInternal = static_cast<int>(vr);
+        this->RowMaskInternal = static_cast<int>(vr);
         place();
     }
     template <int RM = ValidRow, int CM = ValidCol>
     PTO_INTERNAL Tile(std::enable_if_t<(RM > 0) && (CM == DYNAMIC), size_t> vc)
     {
-        ColMaskInternal = static_cast<int>(vc);
+        this->ColMaskInternal = static_cast<int>(vc);
         place();
     }
     Tile(const Tile &) = default;
     Tile &operator=(const Tile &) = default;
 
-    PTO_INTERNAL int GetValidRow() const { return ValidRow == DYNAMIC ? RowMaskInternal : ValidRow; }
-    PTO_INTERNAL int GetValidCol() const { return ValidCol == DYNAMIC ? ColMaskInternal : ValidCol; }
+    PTO_INTERNAL int GetValidRow() const { return this->RowMaskInternal; }
+    PTO_INTERNAL int GetValidCol() const { return this->ColMaskInternal; }
 
     // pointer to the tile's storage in the block's shared-memory arena (Vec and Mat tiles)
     PTO_INTERNAL TileDType data() const;
@@ -275,8 +296,6 @@ struct Tile {
         return data()[offset];
     }
 
-    int RowMaskInternal = ValidRow == DYNAMIC ? 0 : ValidRow;
-    int ColMaskInternal = ValidCol == DYNAMIC ? 0 : ValidCol;
 
     // storage of its own for a freshly constructed tile (see b200::tile_auto_place)
     PTO_INTERNAL void place()

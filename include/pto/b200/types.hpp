@@ -21,6 +21,8 @@
 #define PTO_INLINE __forceinline__
 #define PTO_INST __host__ __device__ __forceinline__
 #define PTO_INTERNAL __host__ __device__ __forceinline__
+// bodies that are kept out of line so that a tile program's instruction stream stays small (one copy per instance)
+#define PTO_B200_OUTLINE __device__ __noinline__
 #define __aicore__
 #define __gm__
 #define __ubuf__

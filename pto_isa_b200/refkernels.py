@@ -21,6 +21,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 OUT = os.path.join(HERE, "libpto_b200_refkernels.so")
 WRAPPER = os.path.join(HERE, "csrc", "refkernels", "wrappers.cu.in")
+# the same reference sources compiled with the core's pipes on warps of their own (PTO_B200_PIPE_WARPS is a property of a
+# translation unit, and of its library: the two must not be linked into one)
+OUT_PW = os.path.join(HERE, "libpto_b200_refkernels_pw.so")
+WRAPPER_PW = os.path.join(HERE, "csrc", "refkernels", "wrappers_pw.cu.in")
 
 _LAUNCH = re.compile(r"<<<\s*([^,<>]+?)\s*,\s*nullptr\s*,\s*([^,<>]+?)\s*>>>\s*\(")
 
@@ -78,9 +82,9 @@ def build(reference=None, force=False, verbose=False):
     reference = reference or default_reference()
     if not os.path.isdir(os.path.join(reference, "kernels")):
         return OUT if os.path.exists(OUT) else None
-    if not force and os.path.exists(OUT) and os.path.getmtime(OUT) >= max(
-            os.path.getmtime(os.path.join(dp, f)) for dp, _, fs in os.walk(os.path.join(ROOT, "include", "pto"))
-            for f in fs) and os.path.getmtime(OUT) >= os.path.getmtime(WRAPPER):
+    newest = max(max(os.path.getmtime(os.path.join(dp, f)) for dp, _, fs in os.walk(os.path.join(ROOT, "include", "pto"))
+                     for f in fs), os.path.getmtime(WRAPPER), os.path.getmtime(WRAPPER_PW))
+    if not force and all(os.path.exists(o) and os.path.getmtime(o) >= newest for o in (OUT, OUT_PW)):
         return OUT
     build_dir = os.path.join(HERE, "build", "refkernels")
     os.makedirs(build_dir, exist_ok=True)
@@ -93,18 +97,21 @@ def build(reference=None, force=False, verbose=False):
             text = rewrite_core_statics(rewrite_launches(f.read()))
         with open(os.path.join(build_dir, name), "w") as f:
             f.write(text)
-    tu = os.path.join(build_dir, "wrappers.cu")
-    with open(WRAPPER) as f:
-        body = f.read().replace("@REFERENCE@", reference)
-    with open(tu, "w") as f:
-        f.write(body)
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++20", "--extended-lambda", "--expt-relaxed-constexpr",
-           "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", build_dir, "-shared", "-o", OUT, tu]
-    if verbose:
-        cmd[1:1] = ["-Xptxas", "-v"]
-        print(" ".join(cmd))
-    subprocess.check_call(cmd)
+    extra = os.environ.get("PTO_B200_REFK_NVCC_FLAGS", "").split()  # e.g. -DPTO_B200_TIMELINE, -DPTO_B200_TRACE_WAITS
+    for wrapper, out in ((WRAPPER, OUT), (WRAPPER_PW, OUT_PW)):
+        tu = os.path.join(build_dir, os.path.basename(wrapper)[:-3])
+        with open(wrapper) as f:
+            body = f.read().replace("@REFERENCE@", reference)
+        with open(tu, "w") as f:
+            f.write(body)
+        cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++20", "--extended-lambda",
+               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", build_dir,
+               *extra, "-shared", "-o", out, tu]
+        if verbose:
+            cmd[1:1] = ["-Xptxas", "-v"]
+            print(" ".join(cmd))
+        subprocess.check_call(cmd)
     return OUT
 
 

@@ -19,11 +19,23 @@ _SO = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 
                    "libpto_b200_refkernels.so")
 
 
+class _Libs:
+    """Entry points of the two libraries built from the reference's sources: `..._pw_...` names live in the one compiled
+    with the core's pipes on warps of their own (PTO_B200_PIPE_WARPS is a property of a translation unit)."""
+
+    def __init__(self):
+        self.plain = ctypes.CDLL(_SO)
+        self.pw = ctypes.CDLL(_SO.replace("refkernels.so", "refkernels_pw.so"))
+
+    def __getattr__(self, name):
+        return getattr(self.pw if "_pw_" in name else self.plain, name)
+
+
 @pytest.fixture(scope="module")
 def refk():
-    if not os.path.exists(_SO):
-        pytest.skip("libpto_b200_refkernels.so has not been built (needs the reference tree at build time)")
-    return ctypes.CDLL(_SO)
+    if not os.path.exists(_SO) or not os.path.exists(_SO.replace("refkernels.so", "refkernels_pw.so")):
+        pytest.skip("libpto_b200_refkernels*.so have not been built (they need the reference tree at build time)")
+    return _Libs()
 
 
 def _stream():
