@@ -238,22 +238,35 @@ __device__ __noinline__ uint32_t tload_prepare_engine(unsigned long long addr, u
                                                       uint32_t lines, uint32_t span_bytes, uint32_t dst_smem, uint32_t pitch)
 {
     volatile uint32_t *pend = pending_count();
-    const TmaTable *table = tma_table();
+    const RegionBounds *rb = region_bounds();
+    const RegionShapes *rs = region_shapes();
     if ((span_bytes & 127u) != 0 || pend[0] >= static_cast<uint32_t>(kMaxPendingLoads)) {
         return 0;
     }
-    for (int r = 0; r < table->count; ++r) {
-        const unsigned long long off = addr - table->base[r];
-        const unsigned long long pitch_bytes = table->pitch_bytes[r];
-        if (addr >= table->base[r] && table->elem_bytes[r] == es && pitch_bytes == line_stride_bytes &&
-            lines % table->box_rows[r] == 0 && (off & 15u) == 0) {
-            const unsigned long long y = off / pitch_bytes, xb = off - y * pitch_bytes;
-            if (xb + span_bytes <= table->row_bytes[r] &&
-                off + static_cast<unsigned long long>(lines - 1) * pitch_bytes + span_bytes <= table->bytes[r]) {
+    const uint32_t count = rs->count;
+    for (uint32_t r = 0; r < count; ++r) {
+        const unsigned long long base = rb->base[r];
+        const unsigned long long off = addr - base;
+        const uint32_t pitch_bytes = rs->pitch_bytes[r];
+        if (addr >= base && rs->elem_bytes[r] == es && pitch_bytes == line_stride_bytes && lines % rs->box_rows[r] == 0 &&
+            (off & 15u) == 0) {
+            // row and byte offset inside the row: 32-bit arithmetic when the offset allows
+            unsigned long long y;
+            uint32_t xb;
+            if (off < (1ull << 32)) {
+                const uint32_t o = static_cast<uint32_t>(off);
+                y = o / pitch_bytes;
+                xb = o - static_cast<uint32_t>(y) * pitch_bytes;
+            } else {
+                y = off / pitch_bytes;
+                xb = static_cast<uint32_t>(off - y * pitch_bytes);
+            }
+            if (xb + span_bytes <= rs->row_bytes[r] &&
+                addr + static_cast<unsigned long long>(lines - 1) * pitch_bytes + span_bytes <= rb->end[r] && y < (1ull << 31)) {
                 PendingLoad *p = pending_loads() + pend[0];
                 p->dst = dst_smem;
-                p->region = static_cast<uint32_t>(r);
-                p->x = static_cast<uint32_t>(xb / es);
+                p->region = r;
+                p->x = xb / es;
                 p->y = static_cast<uint32_t>(y);
                 p->blocks = static_cast<uint16_t>(span_bytes >> 7);
                 p->lines = static_cast<uint16_t>(lines);
@@ -403,10 +416,11 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
                   "TLOAD: ND and DN global tensors are supported");
 #if PTO_B200_DEVICE_CODE
     if constexpr (b200::kPipeWarps) {
-        const bool loader = b200::runs(PIPE_MTE2);
-        if (!loader && !b200::runs(PIPE_MTE1)) {
-            return {}; // staged tiles are touched by the loading team and by the thread of MTE1 / M only
+        const bool helper = b200::helps_mte2();
+        if (!helper && !b200::runs(PIPE_MTE1)) {
+            return {}; // staged tiles are touched by the loading warps and by the thread of MTE1 / M only
         }
+        volatile uint32_t *pend = b200::pending_count(); // [1]: the copy engine takes the tile
         if constexpr (TileData::Loc == TileType::Mat && b200::is_tc_elem<typename TileData::DType>::value) {
             using T = typename TileData::DType;
             const bool cols_contig = (src.GetStride(4) == 1);
@@ -415,14 +429,13 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
             const uint32_t pitch = static_cast<uint32_t>(lines) * 128u;
             dst.pitch_ = pitch;
             dst.major_ = cols_contig ? b200::kColsContiguous : b200::kRowsContiguous;
-            if (!loader) {
+            if (!helper) {
                 return {};
             }
-            b200::stamp(0x4000);
-            const int v_lines = cols_contig ? dst.GetValidRow() : dst.GetValidCol();
-            const int v_span = cols_contig ? dst.GetValidCol() : dst.GetValidRow();
-            volatile uint32_t *pend = b200::pending_count();
             if (threadIdx.x == 0) {
+                b200::stamp(0x4000);
+                const int v_lines = cols_contig ? dst.GetValidRow() : dst.GetValidCol();
+                const int v_span = cols_contig ? dst.GetValidCol() : dst.GetValidRow();
                 uint32_t take = 0;
                 if (v_lines == lines && v_span == span) {
                     take = b200::tload_prepare_engine(
@@ -432,26 +445,36 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
                         b200::smem_u32(b200::arena() + dst.addr_), pitch);
                 }
                 pend[1] = take;
-                if (take == 0) {
-                    b200::held_back()[14] = 1; // tiles written through the generic proxy from here on
-                }
-            }
-            b200::sync_l();
-            const uint32_t take = pend[1];
-            b200::sync_l();
-            if (take != 0) {
-                b200::stamp(0x4001);
-                return {};
             }
         } else {
             if constexpr (TileData::Loc == TileType::Mat) {
                 dst.pitch_ = 0;
                 dst.major_ = b200::kPlain;
             }
-            if (!loader) {
+            if (!helper) {
                 return {};
             }
+            if (threadIdx.x == 0) {
+                pend[1] = 0;
+            }
         }
+        // the helping threads learn here whether they copy (and, if so, that the loading thread is past its waits)
+        b200::sync_l();
+        const uint32_t take = pend[1];
+        b200::sync_l();
+        if (take != 0) {
+            b200::stamp(0x4001);
+            return {};
+        }
+        // copied by threads: complete when TLOAD returns, so that the loading thread alone can raise the flag
+        b200::complete_loads();
+        b200::tload_impl(dst, src);
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        if (threadIdx.x == 0) {
+            b200::held_back()[14] = 1; // tiles written through the generic proxy from here on
+        }
+        b200::sync_l();
+        return {};
     }
     b200::tload_impl(dst, src);
 #endif
@@ -663,18 +686,20 @@ PTO_INTERNAL void matmul_issue(TileAccT &c, TileLeftT &a, TileRightT &b, bool ac
         const uint32_t a_addr = smem_u32(((a.major_ & kView) ? arena() : arena_of<TileType::Left>()) + a.addr_);
         const uint32_t b_addr = smem_u32(((b.major_ & kView) ? arena() : arena_of<TileType::Right>()) + b.addr_);
         tc_fence_after();
+        // (the tiles' fields are read once: the products' "memory" clobbers would have them read again from the
+        // handles, which live in local memory when a program indexes arrays of tiles at run time)
+        const uint32_t a_pitch = a.pitch_, b_pitch = b.pitch_;
+        // K-major view: 16 k-values are 32 bytes inside a 128-byte line, blocks of 64 k are `pitch` apart;
+        // MN-major view: 16 k-values are 16 lines of 128 bytes, 64-element blocks of M/N are `pitch` apart.
+        // The descriptor of step kk is the first one plus the step's byte offset (a multiple of 16) in its low field.
+        const uint64_t a_desc0 = (a_major == 0) ? sw128_desc(a_addr, 16, 1024) : sw128_desc(a_addr, a_pitch, 1024);
+        const uint64_t b_desc0 = (b_major == 0) ? sw128_desc(b_addr, 16, 1024) : sw128_desc(b_addr, b_pitch, 1024);
 #pragma unroll
         for (int kk = 0; kk < TileLeftT::Cols / 16; ++kk) {
             const uint32_t k0 = kk * 16;
-            // K-major view: 16 k-values are 32 bytes inside a 128-byte line, blocks of 64 k are `pitch` apart;
-            // MN-major view: 16 k-values are 16 lines of 128 bytes, 64-element blocks of M/N are `pitch` apart
-            const uint64_t a_desc = (a_major == 0)
-                                        ? sw128_desc(a_addr + (k0 >> 6) * a.pitch_ + (k0 & 63u) * 2u, 16, 1024)
-                                        : sw128_desc(a_addr + k0 * 128u, a.pitch_, 1024);
-            const uint64_t b_desc = (b_major == 0)
-                                        ? sw128_desc(b_addr + (k0 >> 6) * b.pitch_ + (k0 & 63u) * 2u, 16, 1024)
-                                        : sw128_desc(b_addr + k0 * 128u, b.pitch_, 1024);
-            mma_f16(d_tmem, a_desc, b_desc, idesc, (accumulate || kk != 0) ? 1u : 0u);
+            const uint32_t a_off = (a_major == 0) ? (k0 >> 6) * a_pitch + (k0 & 63u) * 2u : k0 * 128u;
+            const uint32_t b_off = (b_major == 0) ? (k0 >> 6) * b_pitch + (k0 & 63u) * 2u : k0 * 128u;
+            mma_f16(d_tmem, a_desc0 + (a_off >> 4), b_desc0 + (b_off >> 4), idesc, (accumulate || kk != 0) ? 1u : 0u);
         }
         stamp(0x6001);
     }

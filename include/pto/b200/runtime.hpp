@@ -60,7 +60,8 @@ constexpr bool kPipeWarps = true;
 #else
 constexpr bool kPipeWarps = false;
 #endif
-constexpr int kTeamLThreads = 64;   // warps 0..1
+constexpr int kTeamLThreads = 32;   // warp 1: the threads that copy tiles for MTE2 where the copy engine does not
+constexpr int kTmemWarp = 2;        // the warp without a pipe allocates and frees the block's tensor memory
 constexpr int kTeamBWarp = 3;
 constexpr int kTeamCFirstWarp = 4, kTeamCThreads = 128; // warps 4..7
 // TSTORE's staging area (LaunchOptions::store_staging_offset)
@@ -224,13 +225,15 @@ __device__ __forceinline__ uint32_t tile_auto_place(int space, uint32_t amount)
     return at * unit;
 }
 
-// ---- teams: who executes an instruction.  Without kModePipeWarps the whole block does.  With it:
-//   team L  warps 0..1  MTE2 (loads from global memory)
-//   team B  the first thread of warp 3: MTE1 and M (operand windows and the products: one thread issues them)
-//   team C  warps 4..7  V, MTE3, FIX, S (vector work and stores; four warps, so that together they reach every
-//                       tensor-memory lane)
-// Warp 2 has no pipe.  Every warp walks the whole instruction stream; an instruction does its work on the threads of
-// its pipe's team and nothing on the others (their thread index is kNotAMember, which empties every loop).
+// ---- teams: who executes an instruction.  Without PTO_B200_PIPE_WARPS the whole block does.  With it:
+//   MTE2          thread 0 raises and awaits the pipe's flags and hands tiles of registered matrices to the copy
+//                 engine; warp 1 (team L) copies where a tile is copied by threads (cp.async, vector tiles)
+//   MTE1 and M    the first thread of warp 3 (team B): operand windows and the products, issued by one thread
+//   V, MTE3, FIX, S   warps 4..7 (team C): vector work and stores; four warps, so that together they reach every
+//                 tensor-memory lane
+// Warp 2 has no pipe; the other lanes of warps 0 and 3 leave when the block begins (a thread that works alone is not
+// held up by lanes of its warp that wait at barriers).  Every warp walks the whole instruction stream; an instruction does its work on the threads of
+// its pipe and nothing on the others (their thread index is kNotAMember, which empties every loop).
 __device__ __forceinline__ constexpr bool pipe_warps()
 {
     return kPipeWarps;
@@ -246,7 +249,7 @@ __device__ __forceinline__ int team_threads(int team)
 }
 __device__ __forceinline__ int team_first_thread(int team)
 {
-    return team == kTeamL ? 0 : (team == kTeamB ? kTeamBWarp * 32 : kTeamCFirstWarp * 32);
+    return team == kTeamL ? 32 : (team == kTeamB ? kTeamBWarp * 32 : kTeamCFirstWarp * 32);
 }
 template <int kTeam>
 __device__ __forceinline__ int team_tid()
@@ -267,23 +270,32 @@ __device__ __forceinline__ void team_sync()
 {
     if (!pipe_warps()) {
         __syncthreads();
-    } else if (team_tid<kTeam>() != kNotAMember) {
-        if (kTeam == kTeamB) {
-            // one thread
-        } else {
-            asm volatile("bar.sync %0, %1;" ::"n"(1 + kTeam), "n"(kTeam == kTeamL ? kTeamLThreads : kTeamCThreads) : "memory");
+    } else if (kTeam == kTeamL) {
+        // the loading thread (alone in warp 0) and the copying warp
+        if (threadIdx.x == 0 || (threadIdx.x >> 5) == 1) {
+            asm volatile("bar.sync 1, 64;" ::: "memory");
         }
+    } else if (kTeam == kTeamC && team_tid<kTeam>() != kNotAMember) {
+        asm volatile("bar.sync 3, %0;" ::"n"(kTeamCThreads) : "memory");
     }
 }
-// does this thread execute instructions of `pipe`?
+// does this thread raise and await the flags of `pipe` (and execute its instructions)?
 __device__ __forceinline__ bool runs(int pipe)
 {
     if (!pipe_warps()) {
         return true;
     }
     const int team = team_of_pipe(pipe);
+    if (team == kTeamL) {
+        return threadIdx.x == 0;
+    }
     const int t = static_cast<int>(threadIdx.x) - team_first_thread(team);
     return t >= 0 && t < team_threads(team);
+}
+// the threads that copy tiles for MTE2 where the copy engine does not
+__device__ __forceinline__ bool helps_mte2()
+{
+    return !pipe_warps() || threadIdx.x == 0 || (threadIdx.x >> 5) == 1;
 }
 // vector, store and scalar instructions (team C) are the default
 __device__ __forceinline__ int tid() { return team_tid<kTeamC>(); }
@@ -380,6 +392,28 @@ __device__ __forceinline__ PendingLoad *pending_loads()
     return reinterpret_cast<PendingLoad *>(reinterpret_cast<uint8_t *>(&control()->flags[flag_index(PIPE_MTE3, PIPE_MTE3, 0)]) + 16);
 }
 static_assert(16 + kMaxPendingLoads * sizeof(PendingLoad) <= 64, "pending loads fit the eight flag words");
+// what TLOAD needs of the registered matrices, copied from the kernel parameter into shared memory when the block
+// begins (flag words of PIPE_M -> PIPE_M and PIPE_ALL -> PIPE_ALL)
+struct RegionBounds { // 64 bytes
+    unsigned long long base[kMaxTmaRegions];
+    unsigned long long end[kMaxTmaRegions];
+};
+struct RegionShapes { // 52 bytes
+    uint32_t pitch_bytes[kMaxTmaRegions];
+    uint32_t row_bytes[kMaxTmaRegions];
+    uint16_t box_rows[kMaxTmaRegions];
+    uint8_t elem_bytes[kMaxTmaRegions];
+    uint32_t count;
+};
+static_assert(sizeof(RegionBounds) <= 64 && sizeof(RegionShapes) <= 64, "region caches fit eight flag words each");
+__device__ __forceinline__ RegionBounds *region_bounds()
+{
+    return reinterpret_cast<RegionBounds *>(&control()->flags[flag_index(PIPE_M, PIPE_M, 0)]);
+}
+__device__ __forceinline__ RegionShapes *region_shapes()
+{
+    return reinterpret_cast<RegionShapes *>(&control()->flags[flag_index(PIPE_ALL, PIPE_ALL, 0)]);
+}
 // [1] of the pending block: TLOAD's decision for the team (1: the copy engine fetches the tile, 0: cp.async)
  // held_back()[13]: 1 + arena offset of TSTORE's staging area, 0 = none
 
@@ -535,6 +569,7 @@ __device__ __noinline__ void issue_pending_loads(uint64_t *bar)
         return;
     }
     const TmaTable *table = tma_table();
+    const RegionShapes *rs = region_shapes();
     const PendingLoad *p = pending_loads();
     uint32_t bytes = 0;
     for (uint32_t i = 0; i < n; ++i) {
@@ -543,8 +578,8 @@ __device__ __noinline__ void issue_pending_loads(uint64_t *bar)
     mbar_expect_tx(bar, bytes);
     for (uint32_t i = 0; i < n; ++i) {
         const uint32_t r = p[i].region;
-        const uint32_t box_rows = table->box_rows[r];
-        const int block_elems = static_cast<int>(128u / table->elem_bytes[r]);
+        const uint32_t box_rows = rs->box_rows[r];
+        const int block_elems = static_cast<int>(128u / rs->elem_bytes[r]);
         for (uint32_t b = 0; b < p[i].blocks; ++b) {
             for (uint32_t l = 0; l < p[i].lines; l += box_rows) {
                 tma_load_2d(p[i].dst + b * p[i].pitch + l * 128u, &table->map[r], bar,
@@ -590,7 +625,7 @@ __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, ui
             ctl->flags[f] = 0;
         } else if (kPipeWarps) {
             // the threads of the source pipe's team arrive; team B signals through one thread or the tensor core
-            mbar_init(&ctl->flags[f], team_of_pipe(src) == kTeamB ? 1u : static_cast<uint32_t>(team_threads(team_of_pipe(src))));
+            mbar_init(&ctl->flags[f], team_of_pipe(src) == kTeamC ? static_cast<uint32_t>(kTeamCThreads) : 1u);
         } else {
             mbar_init(&ctl->flags[f], src == PIPE_M ? 1u : static_cast<uint32_t>(nthreads));
         }
@@ -626,8 +661,26 @@ __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, ui
     if (threadIdx.x == 0) {
         held_back()[13] = store_staging == kNoStoreStaging ? 0u : store_staging + 1u;
         tma_table() = table;
+        RegionBounds *rb = region_bounds();
+        RegionShapes *rs = region_shapes();
+        rs->count = 0;
+        for (int r = 0; r < table->count && r < kMaxTmaRegions; ++r) {
+            // (pitches of 4 GiB and more are left to the cp.async path)
+            if (table->pitch_bytes[r] < (1ull << 32)) {
+                const uint32_t i = rs->count;
+                rb->base[i] = table->base[r];
+                rb->end[i] = table->base[r] + table->bytes[r];
+                rs->pitch_bytes[i] = static_cast<uint32_t>(table->pitch_bytes[r]);
+                rs->row_bytes[i] = static_cast<uint32_t>(table->row_bytes[r]);
+                rs->box_rows[i] = static_cast<uint16_t>(table->box_rows[r]);
+                rs->elem_bytes[i] = static_cast<uint8_t>(table->elem_bytes[r]);
+                rs->count = i + 1;
+            } else {
+                break; // keeps cache index == table index
+            }
+        }
     }
-    if (threadIdx.x < 32) {
+    if ((threadIdx.x >> 5) == (kPipeWarps ? kTmemWarp : 0)) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
                      "r"(kTmemCols)
                      : "memory");
@@ -638,33 +691,22 @@ __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, ui
     tc_fence_after();
 }
 
-// pipe_warps: team L brings its loads to completion (those prepared for the copy engine and not yet issued, and its
-// cp.async copies); the flag PIPE_MTE2 -> PIPE_ALL, 7 is kept for this
+// pipe_warps: the loading thread brings its loads to completion (those prepared for the copy engine and not yet
+// issued); the flag PIPE_MTE2 -> PIPE_ALL, 7 is kept for this
 __device__ __noinline__ void complete_loads()
 {
-    if (!kPipeWarps || threadIdx.x >= kTeamLThreads) {
+    if (!kPipeWarps || threadIdx.x != 0 || *pending_count() == 0) {
         return;
     }
     Control *ctl = control();
     const int f = flag_index(PIPE_MTE2, PIPE_ALL, 7);
-    sync_l();
-    const bool pending = *pending_count() != 0;
-    sync_l();
-    if (pending) {
-        if (threadIdx.x == 0) {
-            issue_pending_loads(&ctl->flags[f]);
-        }
-        mbar_arrive_after_copies(&ctl->flags[f]);
-        volatile uint32_t *word = &ctl->phase[f >> 5][threadIdx.x >> 5];
-        const uint32_t bit = 1u << (f & 31);
-        mbar_wait(&ctl->flags[f], (*word & bit) ? 1u : 0u, f);
-        __syncwarp();
-        if ((threadIdx.x & 31) == 0) {
-            *word = *word ^ bit;
-        }
-        __syncwarp();
-    }
-    asm volatile("cp.async.wait_all;" ::: "memory");
+    issue_pending_loads(&ctl->flags[f]);
+    mbar_arrive(&ctl->flags[f]);
+    volatile uint32_t *word = &ctl->phase[f >> 5][0];
+    const uint32_t bit = 1u << (f & 31);
+    const uint32_t w = *word;
+    mbar_wait(&ctl->flags[f], (w & bit) ? 1u : 0u, f);
+    *word = w ^ bit;
 }
 
 __device__ __forceinline__ void block_end(StatusRecord *status)
@@ -684,7 +726,7 @@ __device__ __forceinline__ void block_end(StatusRecord *status)
             __threadfence();
         }
     }
-    if (threadIdx.x < 32) {
+    if ((threadIdx.x >> 5) == (kPipeWarps ? kTmemWarp : 0)) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(ctl->tmem_base), "r"(kTmemCols)
                      : "memory");
@@ -789,6 +831,9 @@ __global__ void __launch_bounds__(kBlockThreads, 1)
         return;
     }
     block_begin(wait_limit_ns, l0a_offset, l0b_offset, mode, store_staging, &tma);
+    if (kPipeWarps && (threadIdx.x & 31) != 0 && ((threadIdx.x >> 5) == 0 || (threadIdx.x >> 5) == kTeamBWarp)) {
+        return; // the loading thread and the thread of MTE1 / M work alone in their warps
+    }
     program();
     block_end(status);
 #endif
@@ -891,6 +936,105 @@ PTO_INTERNAL void pipe_self_barrier(pipe_t pipe)
 //   PIPE_M    : tcgen05.commit by the issuing thread (covers all earlier tcgen05.mma)
 //   PIPE_MTE2 : every thread arrives when its own asynchronous copies have landed
 //   others    : their work is synchronous per thread, every thread arrives
+// With PTO_B200_PIPE_WARPS the threads of `src` raise the flag (one thread for MTE2, MTE1 and M, the four warps of
+// team C for the rest), and a flag between two teams is raised again only when its previous raise has been consumed
+// (Control::raised).
+namespace pto {
+namespace b200 {
+#if PTO_B200_DEVICE_CODE
+// the count of raises of a flag between teams, advanced by the one thread that raises it
+__device__ __forceinline__ void next_raise(Control *ctl, int f)
+{
+    const uint8_t n = *reinterpret_cast<volatile uint8_t *>(&ctl->raised[f]);
+    wait_until_consumed(f, n);
+    ctl->raised[f] = static_cast<uint8_t>(n + 1);
+}
+__device__ __forceinline__ void set_flag_pipe_warps(pipe_t src, pipe_t dst, int id)
+{
+    if (!runs(src)) {
+        return;
+    }
+    Control *ctl = control();
+    const int f = flag_index(src, dst, id);
+    uint64_t *bar = &ctl->flags[f];
+    stamp(0x3000 + f);
+    const int team = team_of_pipe(src);
+    const bool between_teams = team != team_of_pipe(dst);
+    volatile uint32_t *held = held_back();
+    if (src == PIPE_M) {
+        if (between_teams) {
+            next_raise(ctl, f);
+        }
+        tc_commit(bar);
+        // flags held back for views: the products that read them are all issued by now
+        const uint32_t count = held[0];
+        for (uint32_t i = 0; i < count; ++i) {
+            const int hf = static_cast<int>(held[1 + i]);
+            next_raise(ctl, hf);
+            tc_commit(&ctl->flags[hf]);
+        }
+        if (count != 0) {
+            held[0] = 0;
+        }
+        held[15] = 0;
+    } else if (src == PIPE_MTE1) {
+        if (!between_teams) {
+            // MTE1 -> M: the same thread stages operands and issues products, program order is the order; copies
+            // made through the generic proxy are made visible to the tensor core
+            if (held[14] != 0) {
+                fence_async_proxy();
+            }
+        } else if (dst == PIPE_MTE2 && held[15] != 0 && held[0] < kMaxHeldBack) {
+            // a view was handed out since the matrix pipe last raised a flag: held back (see held_back)
+            held[1 + held[0]] = static_cast<uint32_t>(f);
+            held[0] = held[0] + 1;
+        } else {
+            if (held[14] != 0) {
+                fence_async_proxy();
+            }
+            next_raise(ctl, f);
+            mbar_arrive(bar);
+        }
+    } else if (src == PIPE_MTE2) {
+        // thread 0: the copy engine's loads of the TLOADs before this flag complete on it; tiles copied by the
+        // helping threads were complete when their TLOAD returned
+        // The copies are issued as soon as the flag's previous phase is complete (their bytes then count for this
+        // one), which is well before the previous raise has been consumed: the data is on its way while the loading
+        // thread waits for the consumer; the arrival that completes the phase comes after that wait.
+        const uint8_t n = *reinterpret_cast<volatile uint8_t *>(&ctl->raised[f]);
+        if (*pending_count() != 0) {
+            mbar_wait(bar, (static_cast<uint32_t>(n) + 1u) & 1u, f); // phase n - 1 (a fresh barrier passes)
+            issue_pending_loads(bar);
+        }
+        if (between_teams) {
+            wait_until_consumed(f, n);
+            ctl->raised[f] = static_cast<uint8_t>(n + 1);
+        }
+        if (held[14] != 0) {
+            fence_async_proxy();
+        }
+        mbar_arrive(bar);
+    } else {
+        // team C: every thread of the four warps arrives; the first one keeps the count
+        if (between_teams) {
+            sync();
+            const uint8_t n = *reinterpret_cast<volatile uint8_t *>(&ctl->raised[f]);
+            sync();
+            if (static_cast<int>(threadIdx.x) == team_first_thread(kTeamC)) {
+                ctl->raised[f] = static_cast<uint8_t>(n + 1);
+            }
+            wait_until_consumed(f, n);
+        }
+        fence_async_proxy();
+        tc_fence_before();
+        mbar_arrive(bar);
+    }
+    stamp(0x3800 + f);
+}
+#endif
+} // namespace b200
+} // namespace pto
+
 PTO_INTERNAL void set_flag(pipe_t src, pipe_t dst, int id)
 {
 #if PTO_B200_DEVICE_CODE
@@ -898,86 +1042,14 @@ PTO_INTERNAL void set_flag(pipe_t src, pipe_t dst, int id)
         pto::b200::pipe_self_barrier(src); // a pipe is ordered with itself by a barrier, not a flag
         return;
     }
+    if constexpr (pto::b200::kPipeWarps) {
+        pto::b200::set_flag_pipe_warps(src, dst, id);
+        return;
+    }
     pto::b200::Control *ctl = pto::b200::control();
     const int f = pto::b200::flag_index(src, dst, id);
     uint64_t *bar = &ctl->flags[f];
-    if (pto::b200::runs(src)) {
-        pto::b200::stamp(0x3000 + f);
-    }
-    if (pto::b200::kPipeWarps) {
-        if (!pto::b200::runs(src)) {
-            return;
-        }
-        const int team = pto::b200::team_of_pipe(src);
-        // a flag between two teams is raised again only when its previous raise has been consumed (Control::raised)
-        const bool between_teams = team != pto::b200::team_of_pipe(dst);
-        if (team == pto::b200::kTeamB) {
-            // one thread runs MTE1 and M: it raises flags alone
-            volatile uint32_t *held = pto::b200::held_back();
-            if (src == PIPE_M) {
-                if (between_teams) {
-                    const uint8_t n = ctl->raised[f];
-                    pto::b200::wait_until_consumed(f, n);
-                    ctl->raised[f] = static_cast<uint8_t>(n + 1);
-                }
-                pto::b200::tc_commit(bar);
-                // flags held back for views: the products that read them are all issued by now
-                const uint32_t count = held[0];
-                for (uint32_t i = 0; i < count; ++i) {
-                    const int hf = static_cast<int>(held[1 + i]);
-                    const uint8_t n = ctl->raised[hf];
-                    pto::b200::wait_until_consumed(hf, n);
-                    ctl->raised[hf] = static_cast<uint8_t>(n + 1);
-                    pto::b200::tc_commit(&ctl->flags[hf]);
-                }
-                if (count != 0) {
-                    held[0] = 0;
-                }
-                held[15] = 0;
-            } else if (!between_teams) {
-                // MTE1 -> M: the same thread stages operands and issues products, program order is the order; copies
-                // made through the generic proxy are made visible to the tensor core
-                if (held[14] != 0) {
-                    pto::b200::fence_async_proxy();
-                }
-            } else if (dst == PIPE_MTE2 && held[15] != 0 && held[0] < pto::b200::kMaxHeldBack) {
-                // a view was handed out since the matrix pipe last raised a flag: held back (see held_back)
-                held[1 + held[0]] = static_cast<uint32_t>(f);
-                held[0] = held[0] + 1;
-            } else {
-                if (held[14] != 0) {
-                    pto::b200::fence_async_proxy();
-                }
-                const uint8_t n = ctl->raised[f];
-                pto::b200::wait_until_consumed(f, n);
-                ctl->raised[f] = static_cast<uint8_t>(n + 1);
-                pto::b200::mbar_arrive(bar);
-            }
-            pto::b200::stamp(0x3800 + f);
-            return;
-        }
-        if (between_teams) {
-            // every thread of the team reads the count, the first one advances it, all wait for the consumer
-            if (team == pto::b200::kTeamL) {
-                pto::b200::sync_l();
-            } else {
-                pto::b200::sync();
-            }
-            const uint8_t n = *reinterpret_cast<volatile uint8_t *>(&ctl->raised[f]);
-            if (team == pto::b200::kTeamL) {
-                pto::b200::sync_l();
-            } else {
-                pto::b200::sync();
-            }
-            if (static_cast<int>(threadIdx.x) == pto::b200::team_first_thread(team)) {
-                ctl->raised[f] = static_cast<uint8_t>(n + 1);
-            }
-            pto::b200::wait_until_consumed(f, n);
-        }
-        if (src == PIPE_MTE2 && threadIdx.x == 0) {
-            pto::b200::issue_pending_loads(bar); // the copy engine's loads of the TLOADs before this flag complete on it
-        }
-    }
+    pto::b200::stamp(0x3000 + f);
     if (src == PIPE_M) {
         if (threadIdx.x == 0) {
             pto::b200::tc_commit(bar);
@@ -999,59 +1071,77 @@ PTO_INTERNAL void set_flag(pipe_t src, pipe_t dst, int id)
 }
 
 // wait_flag(src, dst, id): every thread waits for the matching set_flag (the n-th wait pairs with the n-th set).
+namespace pto {
+namespace b200 {
+#if PTO_B200_DEVICE_CODE
+__device__ __forceinline__ void wait_flag_pipe_warps(pipe_t src, pipe_t dst, int id)
+{
+    if (!runs(dst)) {
+        return; // the threads of the waiting pipe wait
+    }
+    const int team = team_of_pipe(dst);
+    const bool between_teams = team_of_pipe(src) != team;
+    if (team == kTeamB && !between_teams && src == PIPE_MTE1) {
+        return; // MTE1 -> M on one thread: see set_flag
+    }
+    Control *ctl = control();
+    const int f = flag_index(src, dst, id);
+    stamp(0x1000 + f);
+    if (team != kTeamC) {
+        // one thread waits.  Between teams the count of completed waits is also the phase
+        if (between_teams) {
+            const uint8_t done = *reinterpret_cast<volatile uint8_t *>(&ctl->consumed[f]);
+            if (mbar_wait(&ctl->flags[f], done & 1u, f)) {
+                ctl->consumed[f] = static_cast<uint8_t>(done + 1);
+            }
+        } else {
+            volatile uint32_t *word = &ctl->phase[f >> 5][threadIdx.x >> 5];
+            const uint32_t bit = 1u << (f & 31);
+            const uint32_t w = *word;
+            mbar_wait(&ctl->flags[f], (w & bit) ? 1u : 0u, f);
+            *word = w ^ bit;
+        }
+        if (held_back()[14] != 0) {
+            fence_async_proxy(); // tiles written through the generic proxy, read by the tensor core
+        }
+    } else {
+        volatile uint32_t *word = &ctl->phase[f >> 5][threadIdx.x >> 5];
+        const uint32_t bit = 1u << (f & 31);
+        const uint32_t parity = (*word & bit) ? 1u : 0u;
+        const bool ok = mbar_wait(&ctl->flags[f], parity, f);
+        __syncwarp();
+        if ((threadIdx.x & 31) == 0) {
+            *word = *word ^ bit;
+        }
+        __syncwarp();
+        if (between_teams) {
+            // every warp of the team is past the wait: the flag may be raised again (Control::consumed)
+            sync();
+            if (ok && static_cast<int>(threadIdx.x) == team_first_thread(kTeamC)) {
+                ctl->consumed[f] = static_cast<uint8_t>(ctl->consumed[f] + 1);
+            }
+        }
+        fence_async_proxy();
+    }
+    tc_fence_after();
+    stamp(0x2000 + f);
+}
+#endif
+} // namespace b200
+} // namespace pto
+
 PTO_INTERNAL void wait_flag(pipe_t src, pipe_t dst, int id)
 {
 #if PTO_B200_DEVICE_CODE
     if (src == dst) {
         return; // see set_flag
     }
-    pto::b200::Control *ctl = pto::b200::control();
-    const int f = pto::b200::flag_index(src, dst, id);
-    if (pto::b200::kPipeWarps) {
-        if (!pto::b200::runs(dst)) {
-            return; // the threads of the waiting pipe wait
-        }
-        const int team = pto::b200::team_of_pipe(dst);
-        const bool between_teams = pto::b200::team_of_pipe(src) != team;
-        if (team == pto::b200::kTeamB && !between_teams && src == PIPE_MTE1) {
-            return; // MTE1 -> M on one thread: see set_flag
-        }
-        pto::b200::stamp(0x1000 + f);
-        volatile uint32_t *word = &ctl->phase[f >> 5][threadIdx.x >> 5];
-        const uint32_t bit = 1u << (f & 31);
-        const uint32_t parity = (*word & bit) ? 1u : 0u;
-        const bool ok = pto::b200::mbar_wait(&ctl->flags[f], parity, f);
-        if (team == pto::b200::kTeamB) {
-            *word = *word ^ bit;
-            if (between_teams && ok) {
-                ctl->consumed[f] = static_cast<uint8_t>(ctl->consumed[f] + 1);
-            }
-            if (pto::b200::held_back()[14] != 0) {
-                pto::b200::fence_async_proxy(); // tiles written through the generic proxy, read by the tensor core
-            }
-        } else {
-            __syncwarp();
-            if ((threadIdx.x & 31) == 0) {
-                *word = *word ^ bit;
-            }
-            __syncwarp();
-            if (between_teams) {
-                // every warp of the waiting team is past the wait: the flag may be raised again (Control::consumed)
-                if (team == pto::b200::kTeamL) {
-                    pto::b200::sync_l();
-                } else {
-                    pto::b200::sync();
-                }
-                if (ok && static_cast<int>(threadIdx.x) == pto::b200::team_first_thread(team)) {
-                    ctl->consumed[f] = static_cast<uint8_t>(ctl->consumed[f] + 1);
-                }
-            }
-            pto::b200::fence_async_proxy();
-        }
-        pto::b200::tc_fence_after();
-        pto::b200::stamp(0x2000 + f);
+    if constexpr (pto::b200::kPipeWarps) {
+        pto::b200::wait_flag_pipe_warps(src, dst, id);
         return;
     }
+    pto::b200::Control *ctl = pto::b200::control();
+    const int f = pto::b200::flag_index(src, dst, id);
     pto::b200::stamp(0x1000 + f);
     // all lanes of a warp run the same instruction stream, so the phase is kept once per warp
     volatile uint32_t *word = &ctl->phase[f >> 5][threadIdx.x >> 5];
@@ -1107,23 +1197,16 @@ PTO_INTERNAL void pipe_barrier(pipe_t pipe)
         return;
     }
     if (pipe == PIPE_ALL) {
-        // every pipe drains: each team completes what it has in flight, then all meet
+        // every pipe drains what it has in flight: the loads of MTE2, the products of M (awaited by the warps of the
+        // vector and store pipes, which then meet)
         pto::b200::complete_loads();
         set_flag(PIPE_M, PIPE_ALL, 7);
-        wait_flag(PIPE_M, PIPE_ALL, 7); // (PIPE_ALL is a pipe of team C)
-        if (pto::b200::runs(PIPE_MTE2) || pto::b200::runs(PIPE_M) || pto::b200::runs(PIPE_V)) {
-            asm volatile("bar.sync 4, %0;" ::"n"(pto::b200::kTeamLThreads + 32 + pto::b200::kTeamCThreads) : "memory");
-        }
+        wait_flag(PIPE_M, PIPE_ALL, 7);
+        pto::b200::sync();
+    } else if (pipe == PIPE_MTE2) {
+        pto::b200::complete_loads();
     } else {
-        const int team = pto::b200::team_of_pipe(pipe);
-        if (team == pto::b200::kTeamL) {
-            pto::b200::complete_loads();
-            pto::b200::sync_l();
-        } else if (team == pto::b200::kTeamB) {
-            pto::b200::sync_b();
-        } else {
-            pto::b200::sync();
-        }
+        pto::b200::pipe_self_barrier(pipe);
     }
 #else
     (void)pipe;
