@@ -589,7 +589,44 @@ def extras(torch, pto, peaks, peak_kind):
         gather["roofline"]["frac_of_random_read_ceiling"] = probe_ms / gather["ms"]
     except Exception as exc:
         out[-1]["roofline"]["probe_note"] = str(exc)[:120]
+    out.extend(tile_program_gemm(torch, peaks, peak_kind))
     return out
+
+
+def tile_program_gemm(torch, peaks, peak_kind):
+    """The reference's own GEMM tile program (RunGemmE2E) compiled against this repository's PTO headers, 6144^3: every
+    thread executing every instruction, and with the core's pipes on warps of their own (TLOAD by the copy engine,
+    TEXTRACT as views).  The libraries are built where the reference tree is available; absent, no rows."""
+    import ctypes
+    rows = []
+    here = os.path.dirname(os.path.abspath(__file__))
+    cases = (("libpto_b200_refkernels.so", "pto_refk_gemm_6144", "every thread runs every instruction"),
+             ("libpto_b200_refkernels_pw.so", "pto_refk_gemm_pw_6144_k128", "pipes on warps of their own, k step 128"))
+    m = n = k = 6144
+    g = torch.Generator(device="cuda").manual_seed(11)
+    a = (torch.rand(m, k, device="cuda", generator=g) * 2 - 1).half()
+    b = (torch.rand(n, k, device="cuda", generator=g) * 2 - 1).half()
+    c = torch.empty(m, n, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    for so, name, how in cases:
+        path = os.path.join(here, "pto_isa_b200", so)
+        if not os.path.exists(path):
+            continue
+        try:
+            fn = getattr(ctypes.CDLL(path), name)
+            stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            ms = bench_loop(torch, lambda: fn(ptr(c), ptr(a), ptr(b), stream, ptr(status)), 3, 10)
+            if status.tolist() != [0, 0, 0, 0]:
+                raise RuntimeError(f"status record {status.tolist()}")
+            tf = 2.0 * m * n * k / ms / 1e9
+            rows.append({"workload": f"reference GEMM tile program 6144^3 ({how})", "value": tf, "unit": "TFLOP/s", "ms": ms,
+                         "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                      "frac": tf / peaks["bf16_tflops"], "peak_kind": peak_kind + " burst"}})
+        except Exception as exc:  # the rows are extras: a missing or failing library must not cost the bench line
+            rows.append({"workload": f"reference GEMM tile program 6144^3 ({how})", "value": None, "unit": "TFLOP/s",
+                         "note": str(exc)[:160], "roofline": {"frac": None}})
+    return rows
 
 
 def compact_summary(line):
@@ -621,6 +658,10 @@ def compact_summary(line):
             key = "tgather"
         elif w.startswith("gemm_f16f32 m=n=k="):
             key = "gemm" + w.split("=")[3].split(",")[0]
+        elif w.startswith("reference GEMM tile program"):
+            key = "tile_program_pw" if "pipes on warps" in w else "tile_program"
+            if row["value"] is None:
+                continue
         if key:
             sm[key] = [r0(row["value"]), r3(row["roofline"]["frac"])]
             if key.startswith("fa_") and row["roofline"].get("frac_of_library") is not None:

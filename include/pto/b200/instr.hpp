@@ -243,34 +243,48 @@ __device__ __noinline__ uint32_t tload_prepare_engine(unsigned long long addr, u
     if ((span_bytes & 127u) != 0 || pend[0] >= static_cast<uint32_t>(kMaxPendingLoads)) {
         return 0;
     }
+    // which registered matrix holds the address (all bounds are read at once: one round trip to shared memory)
     const uint32_t count = rs->count;
-    for (uint32_t r = 0; r < count; ++r) {
-        const unsigned long long base = rb->base[r];
+    // (independent loads, eight bytes each: the flag words that hold them are eight-byte aligned)
+    const ulonglong2 b01 = make_ulonglong2(rb->base[0], rb->base[1]), b23 = make_ulonglong2(rb->base[2], rb->base[3]);
+    const ulonglong2 e01 = make_ulonglong2(rb->end[0], rb->end[1]), e23 = make_ulonglong2(rb->end[2], rb->end[3]);
+    uint32_t r = kMaxTmaRegions;
+    unsigned long long base = 0, end = 0;
+    if (count > 0 && addr >= b01.x && addr < e01.x) {
+        r = 0, base = b01.x, end = e01.x;
+    } else if (count > 1 && addr >= b01.y && addr < e01.y) {
+        r = 1, base = b01.y, end = e01.y;
+    } else if (count > 2 && addr >= b23.x && addr < e23.x) {
+        r = 2, base = b23.x, end = e23.x;
+    } else if (count > 3 && addr >= b23.y && addr < e23.y) {
+        r = 3, base = b23.y, end = e23.y;
+    }
+    if (r < kMaxTmaRegions) {
         const unsigned long long off = addr - base;
-        const uint32_t pitch_bytes = rs->pitch_bytes[r];
-        if (addr >= base && rs->elem_bytes[r] == es && pitch_bytes == line_stride_bytes && lines % rs->box_rows[r] == 0 &&
-            (off & 15u) == 0) {
+        const uint32_t pitch_bytes = rs->pitch_bytes[r], row_bytes = rs->row_bytes[r], box_rows = rs->box_rows[r];
+        if (rs->elem_bytes[r] == es && pitch_bytes == line_stride_bytes && lines % box_rows == 0 && (off & 15u) == 0) {
             // row and byte offset inside the row: 32-bit arithmetic when the offset allows
             unsigned long long y;
             uint32_t xb;
             if (off < (1ull << 32)) {
                 const uint32_t o = static_cast<uint32_t>(off);
-                y = o / pitch_bytes;
-                xb = o - static_cast<uint32_t>(y) * pitch_bytes;
+                const uint32_t y32 = o / pitch_bytes;
+                y = y32;
+                xb = o - y32 * pitch_bytes;
             } else {
                 y = off / pitch_bytes;
                 xb = static_cast<uint32_t>(off - y * pitch_bytes);
             }
-            if (xb + span_bytes <= rs->row_bytes[r] &&
-                addr + static_cast<unsigned long long>(lines - 1) * pitch_bytes + span_bytes <= rb->end[r] && y < (1ull << 31)) {
-                PendingLoad *p = pending_loads() + pend[0];
-                p->dst = dst_smem;
-                p->region = r;
-                p->x = xb / es;
-                p->y = static_cast<uint32_t>(y);
-                p->blocks = static_cast<uint16_t>(span_bytes >> 7);
-                p->lines = static_cast<uint16_t>(lines);
-                p->pitch = pitch;
+            if (xb + span_bytes <= row_bytes &&
+                addr + static_cast<unsigned long long>(lines - 1) * pitch_bytes + span_bytes <= end && y < (1ull << 31)) {
+                PendingLoad *e = pending_loads() + pend[0];
+                e->dst = dst_smem;
+                e->region = r;
+                e->x = xb / es;
+                e->y = static_cast<uint32_t>(y);
+                e->blocks = static_cast<uint16_t>(span_bytes >> 7);
+                e->lines = static_cast<uint16_t>(lines);
+                e->pitch = pitch;
                 pend[0] = pend[0] + 1;
                 return 1;
             }

@@ -577,13 +577,21 @@ __device__ __noinline__ void issue_pending_loads(uint64_t *bar)
     }
     mbar_expect_tx(bar, bytes);
     for (uint32_t i = 0; i < n; ++i) {
-        const uint32_t r = p[i].region;
-        const uint32_t box_rows = rs->box_rows[r];
-        const int block_elems = static_cast<int>(128u / rs->elem_bytes[r]);
-        for (uint32_t b = 0; b < p[i].blocks; ++b) {
-            for (uint32_t l = 0; l < p[i].lines; l += box_rows) {
-                tma_load_2d(p[i].dst + b * p[i].pitch + l * 128u, &table->map[r], bar,
-                            static_cast<int>(p[i].x) + static_cast<int>(b) * block_elems, static_cast<int>(p[i].y + l));
+        // (the entry is read once: every copy instruction is a compiler barrier for memory)
+        PendingLoad e; // (word by word: the flag words that hold the entries are eight-byte aligned)
+        e.dst = p[i].dst, e.region = p[i].region, e.x = p[i].x, e.y = p[i].y, e.blocks = p[i].blocks, e.lines = p[i].lines,
+        e.pitch = p[i].pitch;
+        const uint32_t box_rows = rs->box_rows[e.region];
+        const int block_elems = static_cast<int>(128u / rs->elem_bytes[e.region]);
+        const CUtensorMap *map = &table->map[e.region];
+        const uint32_t bar_s = smem_u32(bar);
+        for (uint32_t b = 0; b < e.blocks; ++b) {
+            for (uint32_t l = 0; l < e.lines; l += box_rows) {
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                        e.dst + b * e.pitch + l * 128u),
+                    "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_s), "r"(static_cast<int>(e.x) + static_cast<int>(b) * block_elems),
+                    "r"(static_cast<int>(e.y + l)));
             }
         }
     }

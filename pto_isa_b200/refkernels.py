@@ -115,6 +115,55 @@ def build(reference=None, force=False, verbose=False):
     return OUT
 
 
+_CODES = {0x1: "wait_flag entered", 0x2: "wait_flag passed", 0x3: "set_flag", 0x4: "TLOAD", 0x5: "TEXTRACT", 0x6: "TMATMUL",
+          0x7: "TSTORE"}
+
+
+def timeline(name="pto_refk_gemm_pw_6144_k128", first=400, count=48):
+    """Prints the stamps of block 0 of one 6144^3 launch of a GEMM entry point (`name`), from libraries built with
+    PTO_B200_REFK_NVCC_FLAGS=-DPTO_B200_TIMELINE (include/pto/b200/runtime.hpp explains the codes): per stamping thread
+    the cycles between consecutive stamps, `count` of them from entry `first`, and the mean cycles per k iteration."""
+    import ctypes
+
+    import numpy as np
+    import torch
+    lib = ctypes.CDLL(OUT_PW if "_pw_" in name else OUT)
+    m = n = k = 6144
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = (torch.rand(m, k, device="cuda", generator=g) * 2 - 1).half()
+    b = (torch.rand(n, k, device="cuda", generator=g) * 2 - 1).half()
+    c = torch.zeros(m, n, device="cuda")
+    st = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    fn = getattr(lib, name)
+    fn(ptr(c), ptr(a), ptr(b), stream(), ptr(st))
+    torch.cuda.synchronize()
+    lib.pto_refk_timeline(None, None, 1)
+    fn(ptr(c), ptr(a), ptr(b), stream(), ptr(st))
+    torch.cuda.synchronize()
+    out = np.zeros((3, 4096), np.uint64)
+    counts = np.zeros(3, np.uint32)
+    cap = lib.pto_refk_timeline(out.ctypes.data_as(ctypes.c_void_p), counts.ctypes.data_as(ctypes.c_void_p), 0)
+    print("status", st.tolist(), "stamps per thread", counts.tolist())
+    for row, who in enumerate(("thread 0 (MTE2, or the whole block)", "thread of MTE1 / M", "first thread of the vector / store warps")):
+        used = min(int(counts[row]), cap)
+        if used < 2:
+            continue
+        codes = (out[row, :used] >> np.uint64(48)).astype(np.int64)
+        clk = (out[row, :used] & np.uint64((1 << 48) - 1)).astype(np.int64)
+        issues = np.flatnonzero(codes == 0x6000)
+        per_iter = f", {(clk[issues[-1]] - clk[issues[0]]) / max(1, len(issues) - 1):.0f} cycles per TMATMUL" if len(issues) > 1 else ""
+        print(f"--- {who}: {used} stamps{per_iter}")
+        for i in range(min(first, used - 1), min(used, first + count)):
+            kind = _CODES.get(int(codes[i]) >> 12, "?")
+            print(f"  {i:5d} {int(codes[i]):#06x} {kind:18s} +{int(clk[i] - clk[i - 1]) if i else 0:6d}")
+
+
 if __name__ == "__main__":
     import sys
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--timeline" in sys.argv:
+        i = sys.argv.index("--timeline")
+        timeline(*(sys.argv[i + 1:i + 2]))
+    else:
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
