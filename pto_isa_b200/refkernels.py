@@ -160,9 +160,42 @@ def timeline(name="pto_refk_gemm_pw_6144_k128", first=400, count=48):
             print(f"  {i:5d} {int(codes[i]):#06x} {kind:18s} +{int(clk[i] - clk[i - 1]) if i else 0:6d}")
 
 
+def run(name="pto_refk_gemm_pw_6144_k128", launches=12):
+    """Launches a 6144^3 GEMM entry point `launches` times and prints the CUDA-event time of the last ten."""
+    import ctypes
+
+    import torch
+    lib = ctypes.CDLL(OUT_PW if "_pw_" in name else OUT)
+    m = n = k = 6144
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = (torch.rand(m, k, device="cuda", generator=g) * 2 - 1).half()
+    b = (torch.rand(n, k, device="cuda", generator=g) * 2 - 1).half()
+    c = torch.zeros(m, n, device="cuda")
+    st = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    fn = getattr(lib, name)
+    timed = min(10, launches)
+    for _ in range(launches - timed):
+        fn(ptr(c), ptr(a), ptr(b), stream, ptr(st))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(timed):
+        fn(ptr(c), ptr(a), ptr(b), stream, ptr(st))
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / timed
+    print(f"{name}: {ms:.3f} ms per launch, {2.0 * m * n * k / ms / 1e9:.1f} TFLOP/s, status record {st.tolist()}")
+    if st.tolist() != [0, 0, 0, 0]:
+        raise SystemExit(1)
+
+
 if __name__ == "__main__":
     import sys
-    if "--timeline" in sys.argv:
+    if "--run" in sys.argv:
+        i = sys.argv.index("--run")
+        run(sys.argv[i + 1], int(sys.argv[i + 2]) if len(sys.argv) > i + 2 else 12)
+    elif "--timeline" in sys.argv:
         i = sys.argv.index("--timeline")
         timeline(*(sys.argv[i + 1:i + 2]))
     else:
