@@ -262,7 +262,8 @@ __device__ __noinline__ uint32_t tload_prepare_engine(unsigned long long addr, u
     if (r < kMaxTmaRegions) {
         const unsigned long long off = addr - base;
         const uint32_t pitch_bytes = rs->pitch_bytes[r], row_bytes = rs->row_bytes[r], box_rows = rs->box_rows[r];
-        if (rs->elem_bytes[r] == es && pitch_bytes == line_stride_bytes && lines % box_rows == 0 && (off & 15u) == 0) {
+        // (box_rows is a power of two and elements are one or two bytes: make_tma_table checks both)
+        if (rs->elem_bytes[r] == es && pitch_bytes == line_stride_bytes && (lines & (box_rows - 1u)) == 0 && (off & 15u) == 0) {
             // row and byte offset inside the row: 32-bit arithmetic when the offset allows
             unsigned long long y;
             uint32_t xb;
@@ -280,7 +281,7 @@ __device__ __noinline__ uint32_t tload_prepare_engine(unsigned long long addr, u
                 PendingLoad *e = pending_loads() + pend[0];
                 e->dst = dst_smem;
                 e->region = r;
-                e->x = xb / es;
+                e->x = xb >> (es - 1u);
                 e->y = static_cast<uint32_t>(y);
                 e->blocks = static_cast<uint16_t>(span_bytes >> 7);
                 e->lines = static_cast<uint16_t>(lines);

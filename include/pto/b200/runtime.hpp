@@ -129,7 +129,7 @@ struct TmaRegion {
     uint64_t rows = 0, cols = 0; // extent in elements
     uint64_t pitch = 0;          // elements between rows (pitch * elem_bytes a multiple of 16)
     int elem_bytes = 2;
-    uint32_t box_rows = 128;     // rows one copy moves (at most 256); a tile's lines are a multiple of it
+    uint32_t box_rows = 128;     // rows one copy moves (a power of two, at most 256); a tile's lines are a multiple of it
 };
 struct TmaTable {
     CUtensorMap map[kMaxTmaRegions];
@@ -582,7 +582,7 @@ __device__ __noinline__ void issue_pending_loads(uint64_t *bar)
         e.dst = p[i].dst, e.region = p[i].region, e.x = p[i].x, e.y = p[i].y, e.blocks = p[i].blocks, e.lines = p[i].lines,
         e.pitch = p[i].pitch;
         const uint32_t box_rows = rs->box_rows[e.region];
-        const int block_elems = static_cast<int>(128u / rs->elem_bytes[e.region]);
+        const int block_elems = static_cast<int>(128u >> (rs->elem_bytes[e.region] - 1u)); // one- or two-byte elements
         const CUtensorMap *map = &table->map[e.region];
         const uint32_t bar_s = smem_u32(bar);
         for (uint32_t b = 0; b < e.blocks; ++b) {
@@ -799,7 +799,8 @@ inline cudaError_t make_tma_table(const LaunchOptions &opt, TmaTable &table)
     for (int i = 0; i < opt.tma_count; ++i) {
         const TmaRegion &r = opt.tma[i];
         const uint64_t es = static_cast<uint64_t>(r.elem_bytes);
-        if (r.base == nullptr || (es != 1 && es != 2) || r.box_rows == 0 || r.box_rows > 256 || r.rows == 0 || r.cols == 0 ||
+        if (r.base == nullptr || (es != 1 && es != 2) || r.box_rows == 0 || r.box_rows > 256 ||
+            (r.box_rows & (r.box_rows - 1)) != 0 || r.rows == 0 || r.cols == 0 ||
             (reinterpret_cast<uintptr_t>(r.base) & 15u) != 0 || ((r.pitch * es) & 15u) != 0 || r.pitch < r.cols) {
             return cudaErrorInvalidValue;
         }
