@@ -1278,6 +1278,15 @@ PTO_INTERNAL void wait_flag_dev(int id)
 #endif
 }
 PTO_INTERNAL void set_ffts_base_addr(uint64_t) {}
+// the NPU's system counter (the reference's kernels stamp their start and end with it): nanoseconds of the global timer
+PTO_INTERNAL uint64_t get_sys_cnt()
+{
+#if PTO_B200_DEVICE_CODE
+    return pto::b200::global_timer_ns();
+#else
+    return 0;
+#endif
+}
 // one block hosts the cube role and a single vector role
 PTO_INTERNAL uint32_t get_subblockid() { return 0; }
 PTO_INTERNAL uint32_t get_subblockdim() { return 1; }

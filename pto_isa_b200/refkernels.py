@@ -16,6 +16,7 @@ import os
 import re
 import shutil
 import subprocess
+import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
@@ -41,6 +42,14 @@ def rewrite_launches(text):
         # the callee expression runs back to the previous statement / block boundary
         start = max(text.rfind(";", pos, m.start()), text.rfind("{", pos, m.start()), text.rfind("}", pos, m.start())) + 1
         callee = text[start:m.start()]
+        # preprocessor and comment lines between the previous statement and the callee stay where they are
+        while True:
+            stripped = callee.lstrip()
+            if not (stripped.startswith("#") or stripped.startswith("//")):
+                break
+            cut = len(callee) - len(stripped) + (stripped.index("\n") + 1 if "\n" in stripped else len(stripped))
+            start += cut
+            callee = callee[cut:]
         lead = callee[: len(callee) - len(callee.lstrip())]
         # the argument list runs to the matching parenthesis
         depth, i = 1, m.end()
@@ -72,6 +81,41 @@ def rewrite_core_statics(text):
     return _STATIC.sub(rep, text)
 
 
+def fa_kernel_check(reference, build_dir, nvcc, verbose=False):
+    """Compiles the reference's flash-attention kernel file for sm_100a in both of its flavours (cube core / vector
+    cores) against include/pto/: objects only, see csrc/refkernels/fa_kernel_check.cu.in.  The case list header is
+    produced by the reference's own generator with its default cases."""
+    fa = os.path.join(reference, "kernels", "manual", "common", "flash_atten")
+    with open(os.path.join(fa, "fa_performance_kernel.cpp")) as f:
+        text = rewrite_core_statics(rewrite_launches(f.read()))
+    with open(os.path.join(build_dir, "fa_performance_kernel.inc"), "w") as f:
+        f.write(text)
+    # the kernel file includes its matmul macro header by name: the rewritten copy beside it is found first
+    with open(os.path.join(fa, "pto_macro_matmul.hpp")) as f:
+        macro = rewrite_core_statics(rewrite_launches(f.read()))
+    with open(os.path.join(build_dir, "pto_macro_matmul.hpp"), "w") as f:
+        f.write(macro)
+    subprocess.check_call([sys.executable, os.path.join(fa, "scripts", "generate_cases.py"), "--output-header",
+                           os.path.join(build_dir, "generated_cases.h"), "--output-json",
+                           os.path.join(build_dir, "generated_cases.json")], stdout=subprocess.DEVNULL)
+    with open(os.path.join(HERE, "csrc", "refkernels", "fa_kernel_check.cu.in")) as f:
+        template = f.read()
+    objects = []
+    for flavour in ("CUBE", "VEC"):
+        tu = os.path.join(build_dir, f"fa_kernel_check_{flavour.lower()}.cu")
+        with open(tu, "w") as f:
+            f.write(template.replace("@FLAVOUR@", flavour))
+        obj = tu[:-3] + ".o"
+        cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O1", "-std=c++20", "--extended-lambda",
+               "--expt-relaxed-constexpr", "-I", os.path.join(ROOT, "include"), "-I", os.path.join(ROOT, "include", "pto", "b200", "compat"),
+               "-I", build_dir, "-I", fa, "-c", "-o", obj, tu]
+        if verbose:
+            print(" ".join(cmd))
+        subprocess.check_call(cmd)
+        objects.append(obj)
+    return objects
+
+
 def default_reference():
     """The reference tree: $PTO_REFERENCE_ROOT, else a `reference` directory beside the repository."""
     return os.environ.get("PTO_REFERENCE_ROOT") or os.path.join(os.path.dirname(ROOT), "reference")
@@ -98,6 +142,7 @@ def build(reference=None, force=False, verbose=False):
         with open(os.path.join(build_dir, name), "w") as f:
             f.write(text)
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    fa_kernel_check(reference, build_dir, nvcc, verbose)
     extra = os.environ.get("PTO_B200_REFK_NVCC_FLAGS", "").split()  # e.g. -DPTO_B200_TIMELINE, -DPTO_B200_TRACE_WAITS
     for wrapper, out in ((WRAPPER, OUT), (WRAPPER_PW, OUT_PW)):
         tu = os.path.join(build_dir, os.path.basename(wrapper)[:-3])
