@@ -262,30 +262,21 @@ __device__ __noinline__ uint32_t tload_prepare_engine(unsigned long long addr, u
     if (r < kMaxTmaRegions) {
         const unsigned long long off = addr - base;
         const uint32_t pitch_bytes = rs->pitch_bytes[r], row_bytes = rs->row_bytes[r], box_rows = rs->box_rows[r];
-        // (box_rows is a power of two and elements are one or two bytes: make_tma_table checks both)
-        if (rs->elem_bytes[r] == es && pitch_bytes == line_stride_bytes && (lines & (box_rows - 1u)) == 0 && (off & 15u) == 0) {
-            // row and byte offset inside the row: 32-bit arithmetic when the offset allows
-            unsigned long long y;
-            uint32_t xb;
-            if (off < (1ull << 32)) {
-                const uint32_t o = static_cast<uint32_t>(off);
-                const uint32_t y32 = o / pitch_bytes;
-                y = y32;
-                xb = o - y32 * pitch_bytes;
-            } else {
-                y = off / pitch_bytes;
-                xb = static_cast<uint32_t>(off - y * pitch_bytes);
-            }
-            if (xb + span_bytes <= row_bytes &&
-                addr + static_cast<unsigned long long>(lines - 1) * pitch_bytes + span_bytes <= end && y < (1ull << 31)) {
+        // (box_rows is a power of two and elements are one or two bytes: make_tma_table checks both; matrices of 4 GiB
+        // and more go the cp.async way, so that everything below is 32-bit arithmetic)
+        if (rs->elem_bytes[r] == es && pitch_bytes == line_stride_bytes && (lines & (box_rows - 1u)) == 0 && (off & 15u) == 0 &&
+            end - base < (1ull << 32)) {
+            const uint32_t o = static_cast<uint32_t>(off);
+            const uint32_t y = o / pitch_bytes;
+            const uint32_t xb = o - y * pitch_bytes;
+            if (xb + span_bytes <= row_bytes && o + (lines - 1u) * pitch_bytes + span_bytes <= static_cast<uint32_t>(end - base)) {
+                const uint32_t log2_rows = log2_pow2(box_rows);
                 PendingLoad *e = pending_loads() + pend[0];
+                e->map = reinterpret_cast<unsigned long long>(&tma_table()->map[r]);
                 e->dst = dst_smem;
-                e->region = r;
                 e->x = xb >> (es - 1u);
-                e->y = static_cast<uint32_t>(y);
-                e->blocks = static_cast<uint16_t>(span_bytes >> 7);
-                e->lines = static_cast<uint16_t>(lines);
-                e->pitch = pitch;
+                e->y = y;
+                e->shape = (span_bytes >> 7) | ((lines >> log2_rows) << 8) | (log2_rows << 16) | ((128u >> (es - 1u)) << 24);
                 pend[0] = pend[0] + 1;
                 return 1;
             }

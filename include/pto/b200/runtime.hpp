@@ -370,13 +370,12 @@ constexpr int kMaxHeldBack = 12;
 // PIPE_MTE2 -> PIPE_MTE2) and the loads that TLOAD has prepared but not yet issued (flag words of PIPE_MTE3 -> PIPE_MTE3):
 // a copy by the copy engine completes on an mbarrier named when it is issued, and the flag that a load raises is only
 // known at the set_flag that follows it, so TLOAD records the copy and set_flag(PIPE_MTE2, ...) issues it.
-struct PendingLoad {
-    uint32_t dst;       // shared-memory address of the tile
-    uint32_t region;    // index into the table
-    uint32_t x, y;      // element coordinates of the tile's first element
-    uint16_t blocks;    // 128-byte blocks along the contiguous dimension
-    uint16_t lines;     // lines of the tile
-    uint32_t pitch;     // bytes between blocks in shared memory
+struct PendingLoad {   // everything the copy instructions need, ready to use
+    unsigned long long map; // address of the matrix's tensor map
+    uint32_t dst;           // shared-memory address of the tile
+    uint32_t x, y;          // element coordinates of the tile's first element
+    uint32_t shape;         // bits 0..7 128-byte blocks along the contiguous dimension, 8..15 boxes along the lines,
+                            // 16..23 log2 of the box's rows, 24..31 elements per 128-byte block
 };
 constexpr int kMaxPendingLoads = 2;
 __device__ __forceinline__ const TmaTable *&tma_table()
@@ -405,6 +404,10 @@ struct RegionShapes { // 52 bytes
     uint8_t elem_bytes[kMaxTmaRegions];
     uint32_t count;
 };
+__device__ __forceinline__ uint32_t log2_pow2(uint32_t v)
+{
+    return 31u - static_cast<uint32_t>(__clz(static_cast<int>(v)));
+}
 static_assert(sizeof(RegionBounds) <= 64 && sizeof(RegionShapes) <= 64, "region caches fit eight flag words each");
 __device__ __forceinline__ RegionBounds *region_bounds()
 {
@@ -568,30 +571,33 @@ __device__ __noinline__ void issue_pending_loads(uint64_t *bar)
     if (n == 0) {
         return;
     }
-    const TmaTable *table = tma_table();
-    const RegionShapes *rs = region_shapes();
     const PendingLoad *p = pending_loads();
+    // (the entries are read once, before the first copy instruction: each of those is a compiler barrier for memory)
+    PendingLoad e[kMaxPendingLoads];
     uint32_t bytes = 0;
-    for (uint32_t i = 0; i < n; ++i) {
-        bytes += static_cast<uint32_t>(p[i].blocks) * p[i].lines * 128u;
+#pragma unroll
+    for (int i = 0; i < kMaxPendingLoads; ++i) {
+        if (static_cast<uint32_t>(i) < n) {
+            e[i].map = p[i].map, e[i].dst = p[i].dst, e[i].x = p[i].x, e[i].y = p[i].y, e[i].shape = p[i].shape;
+            bytes += ((e[i].shape & 0xffu) * ((e[i].shape >> 8) & 0xffu)) << (((e[i].shape >> 16) & 0xffu) + 7u);
+        }
     }
     mbar_expect_tx(bar, bytes);
-    for (uint32_t i = 0; i < n; ++i) {
-        // (the entry is read once: every copy instruction is a compiler barrier for memory)
-        PendingLoad e; // (word by word: the flag words that hold the entries are eight-byte aligned)
-        e.dst = p[i].dst, e.region = p[i].region, e.x = p[i].x, e.y = p[i].y, e.blocks = p[i].blocks, e.lines = p[i].lines,
-        e.pitch = p[i].pitch;
-        const uint32_t box_rows = rs->box_rows[e.region];
-        const int block_elems = static_cast<int>(128u >> (rs->elem_bytes[e.region] - 1u)); // one- or two-byte elements
-        const CUtensorMap *map = &table->map[e.region];
-        const uint32_t bar_s = smem_u32(bar);
-        for (uint32_t b = 0; b < e.blocks; ++b) {
-            for (uint32_t l = 0; l < e.lines; l += box_rows) {
-                asm volatile(
-                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
-                        e.dst + b * e.pitch + l * 128u),
-                    "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_s), "r"(static_cast<int>(e.x) + static_cast<int>(b) * block_elems),
-                    "r"(static_cast<int>(e.y + l)));
+    const uint32_t bar_s = smem_u32(bar);
+#pragma unroll
+    for (int i = 0; i < kMaxPendingLoads; ++i) {
+        if (static_cast<uint32_t>(i) < n) {
+            const uint32_t blocks = e[i].shape & 0xffu, boxes = (e[i].shape >> 8) & 0xffu, log2_rows = (e[i].shape >> 16) & 0xffu;
+            const int block_elems = static_cast<int>(e[i].shape >> 24);
+            const uint32_t box_bytes = 128u << log2_rows, pitch = boxes * box_bytes;
+            for (uint32_t b = 0; b < blocks; ++b) {
+                for (uint32_t l = 0; l < boxes; ++l) {
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                            e[i].dst + b * pitch + l * box_bytes),
+                        "l"(e[i].map), "r"(bar_s), "r"(static_cast<int>(e[i].x) + static_cast<int>(b) * block_elems),
+                        "r"(static_cast<int>(e[i].y + (l << log2_rows))));
+                }
             }
         }
     }
