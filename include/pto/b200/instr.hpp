@@ -235,12 +235,11 @@ namespace b200 {
 // issues (runtime.hpp, PendingLoad).  Returns 0 when the tile has to go the cp.async way.  Plain arguments and out of
 // line: the instruction stream of a tile program stays small and nothing of the caller's is forced into memory.
 __device__ __noinline__ uint32_t tload_prepare_engine(unsigned long long addr, uint32_t es, unsigned long long line_stride_bytes,
-                                                      uint32_t lines, uint32_t span_bytes, uint32_t dst_smem, uint32_t pitch)
+                                                      uint32_t lines, uint32_t span_bytes, uint32_t dst_smem, PendingLoad *e)
 {
-    volatile uint32_t *pend = pending_count();
     const RegionBounds *rb = region_bounds();
     const RegionShapes *rs = region_shapes();
-    if ((span_bytes & 127u) != 0 || pend[0] >= static_cast<uint32_t>(kMaxPendingLoads)) {
+    if ((span_bytes & 127u) != 0) {
         return 0;
     }
     // which registered matrix holds the address (all bounds are read at once: one round trip to shared memory)
@@ -267,17 +266,15 @@ __device__ __noinline__ uint32_t tload_prepare_engine(unsigned long long addr, u
         if (rs->elem_bytes[r] == es && pitch_bytes == line_stride_bytes && (lines & (box_rows - 1u)) == 0 && (off & 15u) == 0 &&
             end - base < (1ull << 32)) {
             const uint32_t o = static_cast<uint32_t>(off);
-            const uint32_t y = o / pitch_bytes;
-            const uint32_t xb = o - y * pitch_bytes;
+            uint32_t xb;
+            const uint32_t y = divide_by_pitch(o, pitch_bytes, region_reciprocals()[r], xb);
             if (xb + span_bytes <= row_bytes && o + (lines - 1u) * pitch_bytes + span_bytes <= static_cast<uint32_t>(end - base)) {
                 const uint32_t log2_rows = log2_pow2(box_rows);
-                PendingLoad *e = pending_loads() + pend[0];
                 e->map = reinterpret_cast<unsigned long long>(&tma_table()->map[r]);
                 e->dst = dst_smem;
                 e->x = xb >> (es - 1u);
                 e->y = y;
                 e->shape = (span_bytes >> 7) | ((lines >> log2_rows) << 8) | (log2_rows << 16) | ((128u >> (es - 1u)) << 24);
-                pend[0] = pend[0] + 1;
                 return 1;
             }
         }
@@ -438,17 +435,48 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
             if (!helper) {
                 return {};
             }
+            const int v_lines = cols_contig ? dst.GetValidRow() : dst.GetValidCol();
+            const int v_span = cols_contig ? dst.GetValidCol() : dst.GetValidRow();
+            if (b200::control()->mode & b200::kModeEngineLoads) {
+                // the copy is prepared by the thread that runs ahead; the loading thread counts the TLOAD
+                volatile uint32_t *c = b200::load_ring_counters();
+                if (threadIdx.x == b200::kPrepareThread) {
+                    const uint32_t head = c[0];
+                    if (b200::wait_for_count(&c[2], head + 1u - b200::kLoadRing, 1537)) {
+                        b200::PendingLoad *e = b200::load_ring() + (head & (b200::kLoadRing - 1));
+                        uint32_t take = 0;
+                        if (v_lines == lines && v_span == span) {
+                            take = b200::tload_prepare_engine(
+                                reinterpret_cast<unsigned long long>(src.data()), static_cast<uint32_t>(sizeof(T)),
+                                static_cast<unsigned long long>(cols_contig ? src.GetStride(3) : src.GetStride(4)) * sizeof(T),
+                                static_cast<uint32_t>(lines), static_cast<uint32_t>(span * sizeof(T)),
+                                b200::smem_u32(b200::arena() + dst.addr_), e);
+                        }
+                        if (take == 0) {
+                            e->shape = 0;
+                        }
+                        __threadfence_block();
+                        c[0] = head + 1u;
+                    }
+                } else if (threadIdx.x == 0) {
+                    b200::stamp(0x4000);
+                    c[1] = c[1] + 1u;
+                    b200::stamp(0x4001);
+                }
+                return {};
+            }
             if (threadIdx.x == 0) {
                 b200::stamp(0x4000);
-                const int v_lines = cols_contig ? dst.GetValidRow() : dst.GetValidCol();
-                const int v_span = cols_contig ? dst.GetValidCol() : dst.GetValidRow();
                 uint32_t take = 0;
-                if (v_lines == lines && v_span == span) {
+                if (v_lines == lines && v_span == span && pend[0] < static_cast<uint32_t>(b200::kMaxPendingLoads)) {
                     take = b200::tload_prepare_engine(
                         reinterpret_cast<unsigned long long>(src.data()), static_cast<uint32_t>(sizeof(T)),
                         static_cast<unsigned long long>(cols_contig ? src.GetStride(3) : src.GetStride(4)) * sizeof(T),
                         static_cast<uint32_t>(lines), static_cast<uint32_t>(span * sizeof(T)),
-                        b200::smem_u32(b200::arena() + dst.addr_), pitch);
+                        b200::smem_u32(b200::arena() + dst.addr_), b200::pending_loads() + pend[0]);
+                    if (take != 0) {
+                        pend[0] = pend[0] + 1;
+                    }
                 }
                 pend[1] = take;
             }
@@ -458,6 +486,12 @@ PTO_INST RecordEvent TLOAD(TileData &dst, GlobalData &src, WaitEvents &... event
                 dst.major_ = b200::kPlain;
             }
             if (!helper) {
+                return {};
+            }
+            if (b200::control()->mode & b200::kModeEngineLoads) {
+                if (threadIdx.x == 0) {
+                    b200::give_up(601); // a TLOAD that the copy engine cannot do, in a launch that promised there are none
+                }
                 return {};
             }
             if (threadIdx.x == 0) {

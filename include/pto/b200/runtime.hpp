@@ -51,7 +51,8 @@ constexpr int kWarps = kBlockThreads / 32;
 //                  instruction stream and skips what is not its own, and flags are raised and awaited by the warps of
 //                  the pipes they name
 //   kModeViews     TEXTRACT / TMOV of an aligned window hands the operand tile a view of the staged tile (no copy)
-constexpr int kModeInOrder = 1, kModePipeWarps = 2, kModeViews = 4;
+//   kModeEngineLoads every TLOAD is a copy by the copy engine, prepared ahead of time by a thread of its own
+constexpr int kModeInOrder = 1, kModePipeWarps = 2, kModeViews = 4, kModeEngineLoads = 8;
 // kModePipeWarps is a property of the translation unit: define PTO_B200_PIPE_WARPS before including the PTO header and
 // every tile program of the unit runs with its pipes on warps of their own (LaunchOptions::pipe_warps must say the
 // same).  The instructions then know at compile time which threads execute them.
@@ -417,6 +418,40 @@ __device__ __forceinline__ RegionShapes *region_shapes()
 {
     return reinterpret_cast<RegionShapes *>(&control()->flags[flag_index(PIPE_ALL, PIPE_ALL, 0)]);
 }
+// floor(2^32 / pitch) per registered matrix (flag words of PIPE_FIX -> PIPE_FIX): a row number is then a multiply-high
+// and at most two corrections instead of an integer division
+__device__ __forceinline__ uint32_t *region_reciprocals()
+{
+    return reinterpret_cast<uint32_t *>(&control()->flags[flag_index(PIPE_FIX, PIPE_FIX, 0)]);
+}
+// LaunchOptions::engine_loads: the copies that TLOADs become are prepared (matrix found, coordinates computed) by the
+// first thread of warp 1, which walks the instruction stream ahead of the loading thread: no flag holds it, only this
+// ring of two prepared copies (flag words of PIPE_FIX -> PIPE_FIX, behind the reciprocals).  The loading thread counts
+// the TLOADs it passes (`taken`) and issues the prepared copies at the set_flag that follows (`issued`); the preparing
+// thread fills entry `head` when head - issued < 2.  Counters live beside the table's address (PIPE_MTE2 -> PIPE_MTE2).
+constexpr uint32_t kLoadRing = 2;
+constexpr int kPrepareThread = 32;
+__device__ __forceinline__ PendingLoad *load_ring()
+{
+    return reinterpret_cast<PendingLoad *>(reinterpret_cast<uint8_t *>(&control()->flags[flag_index(PIPE_FIX, PIPE_FIX, 0)]) + 16);
+}
+__device__ __forceinline__ volatile uint32_t *load_ring_counters() // [0] head, [1] taken, [2] issued
+{
+    return reinterpret_cast<volatile uint32_t *>(reinterpret_cast<uint8_t *>(&control()->flags[flag_index(PIPE_MTE2, PIPE_MTE2, 0)]) + 8);
+}
+__device__ __forceinline__ uint32_t divide_by_pitch(uint32_t o, uint32_t pitch, uint32_t reciprocal, uint32_t &remainder)
+{
+    uint32_t q = __umulhi(o, reciprocal); // never above the quotient, below it by at most two
+    uint32_t r = o - q * pitch;
+    if (r >= pitch) {
+        q += 1, r -= pitch;
+    }
+    if (r >= pitch) {
+        q += 1, r -= pitch;
+    }
+    remainder = r;
+    return q;
+}
 // [1] of the pending block: TLOAD's decision for the team (1: the copy engine fetches the tile, 0: cp.async)
  // held_back()[13]: 1 + arena offset of TSTORE's staging area, 0 = none
 
@@ -460,6 +495,32 @@ __device__ __forceinline__ void give_up(int where)
         ctl->fail_where = where;
     }
 }
+// waits (bounded like every wait) until *word - base >= least, counters taken modulo 2^32
+__device__ __noinline__ bool wait_for_count(volatile uint32_t *word, uint32_t least, int where)
+{
+    Control *ctl = control();
+    volatile int *abort_flag = &ctl->abort_flag;
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
+        if (static_cast<int32_t>(*word - least) >= 0) {
+            return true;
+        }
+        if ((i & 0x3f) == 0x3f) {
+            if (*abort_flag) {
+                return false;
+            }
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > ctl->wait_limit_ns) {
+                break;
+            }
+        }
+    }
+    give_up(where);
+    return false;
+}
+
 __device__ __noinline__ bool mbar_wait_slow(uint64_t *bar, uint32_t parity, int where)
 {
     Control *ctl = control();
@@ -564,28 +625,21 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         : "memory");
 }
 // issues the loads that TLOAD prepared, completing on `bar` (called by the first thread of team L before it arrives)
-__device__ __noinline__ void issue_pending_loads(uint64_t *bar)
+// the copy instructions of up to two prepared copies, completing on `bar` (entries already in registers: each copy
+// instruction is a compiler barrier for memory)
+__device__ __forceinline__ void issue_copies(uint64_t *bar, const PendingLoad (&e)[2], uint32_t n)
 {
-    volatile uint32_t *count = pending_count();
-    const uint32_t n = *count;
-    if (n == 0) {
-        return;
-    }
-    const PendingLoad *p = pending_loads();
-    // (the entries are read once, before the first copy instruction: each of those is a compiler barrier for memory)
-    PendingLoad e[kMaxPendingLoads];
     uint32_t bytes = 0;
 #pragma unroll
-    for (int i = 0; i < kMaxPendingLoads; ++i) {
+    for (int i = 0; i < 2; ++i) {
         if (static_cast<uint32_t>(i) < n) {
-            e[i].map = p[i].map, e[i].dst = p[i].dst, e[i].x = p[i].x, e[i].y = p[i].y, e[i].shape = p[i].shape;
             bytes += ((e[i].shape & 0xffu) * ((e[i].shape >> 8) & 0xffu)) << (((e[i].shape >> 16) & 0xffu) + 7u);
         }
     }
     mbar_expect_tx(bar, bytes);
     const uint32_t bar_s = smem_u32(bar);
 #pragma unroll
-    for (int i = 0; i < kMaxPendingLoads; ++i) {
+    for (int i = 0; i < 2; ++i) {
         if (static_cast<uint32_t>(i) < n) {
             const uint32_t blocks = e[i].shape & 0xffu, boxes = (e[i].shape >> 8) & 0xffu, log2_rows = (e[i].shape >> 16) & 0xffu;
             const int block_elems = static_cast<int>(e[i].shape >> 24);
@@ -601,7 +655,65 @@ __device__ __noinline__ void issue_pending_loads(uint64_t *bar)
             }
         }
     }
+}
+static_assert(kMaxPendingLoads == 2 && kLoadRing == 2, "issue_copies takes two entries");
+
+// issues the loads that TLOAD prepared, completing on `bar` (called by the loading thread before it arrives)
+__device__ __noinline__ void issue_pending_loads(uint64_t *bar)
+{
+    PendingLoad e[2];
+    if (control()->mode & kModeEngineLoads) {
+        volatile uint32_t *c = load_ring_counters();
+        const uint32_t taken = c[1], issued = c[2];
+        const uint32_t n = taken - issued;
+        if (n == 0) {
+            return;
+        }
+        if (!wait_for_count(&c[0], taken, 1536)) { // the preparing thread has filled the entries
+            return;
+        }
+        const PendingLoad *ring = load_ring();
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if (static_cast<uint32_t>(i) < n) {
+                const PendingLoad *p = ring + ((issued + i) & (kLoadRing - 1));
+                e[i].map = p->map, e[i].dst = p->dst, e[i].x = p->x, e[i].y = p->y, e[i].shape = p->shape;
+                ok = ok && e[i].shape != 0;
+            }
+        }
+        if (!ok) {
+            give_up(601); // a TLOAD that the copy engine cannot do, in a launch that promised there are none
+            c[2] = taken;
+            return;
+        }
+        issue_copies(bar, e, n);
+        c[2] = taken; // the entries may be filled again
+        return;
+    }
+    volatile uint32_t *count = pending_count();
+    const uint32_t n = *count;
+    if (n == 0) {
+        return;
+    }
+    const PendingLoad *p = pending_loads();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (static_cast<uint32_t>(i) < n) {
+            e[i].map = p[i].map, e[i].dst = p[i].dst, e[i].x = p[i].x, e[i].y = p[i].y, e[i].shape = p[i].shape;
+        }
+    }
+    issue_copies(bar, e, n);
     *count = 0;
+}
+// is there a TLOAD whose copy has not been issued yet?
+__device__ __forceinline__ bool loads_pending()
+{
+    if (control()->mode & kModeEngineLoads) {
+        volatile uint32_t *c = load_ring_counters();
+        return c[1] != c[2];
+    }
+    return *pending_count() != 0;
 }
 
 // ---- tcgen05 helpers
@@ -675,6 +787,9 @@ __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, ui
     if (threadIdx.x == 0) {
         held_back()[13] = store_staging == kNoStoreStaging ? 0u : store_staging + 1u;
         tma_table() = table;
+        load_ring_counters()[0] = 0;
+        load_ring_counters()[1] = 0;
+        load_ring_counters()[2] = 0;
         RegionBounds *rb = region_bounds();
         RegionShapes *rs = region_shapes();
         rs->count = 0;
@@ -688,6 +803,7 @@ __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, ui
                 rs->row_bytes[i] = static_cast<uint32_t>(table->row_bytes[r]);
                 rs->box_rows[i] = static_cast<uint16_t>(table->box_rows[r]);
                 rs->elem_bytes[i] = static_cast<uint8_t>(table->elem_bytes[r]);
+                region_reciprocals()[i] = static_cast<uint32_t>((1ull << 32) / table->pitch_bytes[r]);
                 rs->count = i + 1;
             } else {
                 break; // keeps cache index == table index
@@ -709,7 +825,7 @@ __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, ui
 // issued); the flag PIPE_MTE2 -> PIPE_ALL, 7 is kept for this
 __device__ __noinline__ void complete_loads()
 {
-    if (!kPipeWarps || threadIdx.x != 0 || *pending_count() == 0) {
+    if (!kPipeWarps || threadIdx.x != 0 || !loads_pending()) {
         return;
     }
     Control *ctl = control();
@@ -781,6 +897,10 @@ struct LaunchOptions {
     // matrices whose tiles TLOAD may fetch with the copy engine (see TmaRegion)
     TmaRegion tma[kMaxTmaRegions];
     int tma_count = 0;
+    // Every TLOAD of the program is a whole tile of a registered matrix (the launch gives up with {4, block, 601} if one
+    // is not): the copies are then prepared ahead of time by a thread of their own (see load_ring), and the loading
+    // thread only counts TLOADs and issues the prepared copies.  Needs pipe_warps and a registered matrix.
+    bool engine_loads = false;
 };
 
 // encodes the launch's registered matrices (host)
@@ -846,8 +966,9 @@ __global__ void __launch_bounds__(kBlockThreads, 1)
         return;
     }
     block_begin(wait_limit_ns, l0a_offset, l0b_offset, mode, store_staging, &tma);
-    if (kPipeWarps && (threadIdx.x & 31) != 0 && ((threadIdx.x >> 5) == 0 || (threadIdx.x >> 5) == kTeamBWarp)) {
-        return; // the loading thread and the thread of MTE1 / M work alone in their warps
+    if (kPipeWarps && (threadIdx.x & 31) != 0 &&
+        ((threadIdx.x >> 5) == 0 || (threadIdx.x >> 5) == kTeamBWarp || ((mode & kModeEngineLoads) && (threadIdx.x >> 5) == 1))) {
+        return; // the loading thread, the thread of MTE1 / M (and the preparing thread) work alone in their warps
     }
     program();
     block_end(status);
@@ -873,7 +994,8 @@ inline cudaError_t launch(uint32_t blocks, void *stream, Program program, const 
     block_kernel<Program><<<blocks, kBlockThreads, opt.smem_bytes, static_cast<cudaStream_t>(stream)>>>(
         program, static_cast<StatusRecord *>(opt.status), opt.wait_limit_ns, opt.l0a_offset, opt.l0b_offset,
         (opt.in_order ? kModeInOrder : 0) | (kPipeWarps ? kModePipeWarps : 0) |
-            (opt.pipe_warps && opt.extract_views ? kModeViews : 0),
+            (opt.pipe_warps && opt.extract_views ? kModeViews : 0) |
+            (opt.pipe_warps && opt.engine_loads && opt.tma_count > 0 ? kModeEngineLoads : 0),
         opt.store_staging_offset, table);
     return cudaGetLastError();
 }
@@ -1017,12 +1139,17 @@ __device__ __forceinline__ void set_flag_pipe_warps(pipe_t src, pipe_t dst, int 
         // one), which is well before the previous raise has been consumed: the data is on its way while the loading
         // thread waits for the consumer; the arrival that completes the phase comes after that wait.
         const uint8_t n = *reinterpret_cast<volatile uint8_t *>(&ctl->raised[f]);
-        if (*pending_count() != 0) {
-            mbar_wait(bar, (static_cast<uint32_t>(n) + 1u) & 1u, f); // phase n - 1 (a fresh barrier passes)
+        const bool consumed = *reinterpret_cast<volatile uint8_t *>(&ctl->consumed[f]) == n;
+        if (loads_pending()) {
+            if (!consumed) {
+                mbar_wait(bar, (static_cast<uint32_t>(n) + 1u) & 1u, f); // phase n - 1 (a fresh barrier passes)
+            }
             issue_pending_loads(bar);
         }
         if (between_teams) {
-            wait_until_consumed(f, n);
+            if (!consumed) {
+                wait_until_consumed(f, n);
+            }
             ctl->raised[f] = static_cast<uint8_t>(n + 1);
         }
         if (held[14] != 0) {
