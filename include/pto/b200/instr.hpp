@@ -536,25 +536,29 @@ template <typename DstTileData, typename SrcTileData>
 PTO_INTERNAL bool textract_view(DstTileData &dst, SrcTileData &src, int indexRow, int indexCol)
 {
     using T = typename DstTileData::DType;
-    constexpr int kCE = 16 / static_cast<int>(sizeof(T));
-    constexpr int kChunksPerBlock = 8; // 128 bytes of the contiguous dimension
+    constexpr uint32_t kCE = 16 / static_cast<uint32_t>(sizeof(T));
+    constexpr uint32_t kChunksPerBlock = 8; // 128 bytes of the contiguous dimension
     if ((control()->mode & kModeViews) == 0) {
         return false;
     }
-    const bool cols_contig = (src.major_ == kColsContiguous);
-    const int line0 = cols_contig ? indexRow : indexCol;
-    const int chunk0 = (cols_contig ? indexCol : indexRow) / kCE;
-    const int lines = cols_contig ? DstTileData::Rows : DstTileData::Cols;
-    const int chunks_per_line = (cols_contig ? DstTileData::Cols : DstTileData::Rows) / kCE;
-    const int src_lines = cols_contig ? SrcTileData::Rows : SrcTileData::Cols;
-    const int src_chunks = (cols_contig ? SrcTileData::Cols : SrcTileData::Rows) / kCE;
-    if ((line0 & 7) != 0 || (chunk0 % kChunksPerBlock) != 0 || line0 + lines > src_lines ||
-        chunk0 + chunks_per_line > src_chunks) {
+    // (one branch per staged layout, so that each works with the tiles' compile-time extents)
+    const uint32_t src_addr = src.addr_, src_pitch = src.pitch_;
+    uint32_t line0, chunk0;
+    bool fits, k_major;
+    if (src.major_ == kColsContiguous) {
+        line0 = static_cast<uint32_t>(indexRow), chunk0 = static_cast<uint32_t>(indexCol) / kCE;
+        fits = line0 + DstTileData::Rows <= SrcTileData::Rows && chunk0 + DstTileData::Cols / kCE <= SrcTileData::Cols / kCE;
+        k_major = DstTileData::Loc == TileType::Left;
+    } else {
+        line0 = static_cast<uint32_t>(indexCol), chunk0 = static_cast<uint32_t>(indexRow) / kCE;
+        fits = line0 + DstTileData::Cols <= SrcTileData::Cols && chunk0 + DstTileData::Rows / kCE <= SrcTileData::Rows / kCE;
+        k_major = DstTileData::Loc != TileType::Left;
+    }
+    if (((line0 & 7u) | (chunk0 & (kChunksPerBlock - 1u))) != 0 || !fits) {
         return false;
     }
-    const bool k_major = (DstTileData::Loc == TileType::Left) ? cols_contig : !cols_contig;
-    dst.addr_ = src.addr_ + static_cast<uint32_t>(chunk0 / kChunksPerBlock) * src.pitch_ + static_cast<uint32_t>(line0) * 128u;
-    dst.pitch_ = src.pitch_;
+    dst.addr_ = src_addr + (chunk0 / kChunksPerBlock) * src_pitch + line0 * 128u;
+    dst.pitch_ = src_pitch;
     dst.major_ = static_cast<uint8_t>((k_major ? 0 : 1) | kView);
     if (tid_b() == 0) {
         held_back()[15] = 1; // flags that free the staged tile wait for the products (runtime.hpp)
@@ -734,12 +738,23 @@ PTO_INTERNAL void matmul_issue(TileAccT &c, TileLeftT &a, TileRightT &b, bool ac
         // The descriptor of step kk is the first one plus the step's byte offset (a multiple of 16) in its low field.
         const uint64_t a_desc0 = (a_major == 0) ? sw128_desc(a_addr, 16, 1024) : sw128_desc(a_addr, a_pitch, 1024);
         const uint64_t b_desc0 = (b_major == 0) ? sw128_desc(b_addr, 16, 1024) : sw128_desc(b_addr, b_pitch, 1024);
+        if (a_major == 0 && b_major == 0) {
+            // both operands K-major (the common case): the steps inside a 64-k block are constants apart
+            const uint64_t a_block = a_pitch >> 4, b_block = b_pitch >> 4;
 #pragma unroll
-        for (int kk = 0; kk < TileLeftT::Cols / 16; ++kk) {
-            const uint32_t k0 = kk * 16;
-            const uint32_t a_off = (a_major == 0) ? (k0 >> 6) * a_pitch + (k0 & 63u) * 2u : k0 * 128u;
-            const uint32_t b_off = (b_major == 0) ? (k0 >> 6) * b_pitch + (k0 & 63u) * 2u : k0 * 128u;
-            mma_f16(d_tmem, a_desc0 + (a_off >> 4), b_desc0 + (b_off >> 4), idesc, (accumulate || kk != 0) ? 1u : 0u);
+            for (int kk = 0; kk < TileLeftT::Cols / 16; ++kk) {
+                const uint64_t in_block = static_cast<uint64_t>((kk & 3) * 2);
+                mma_f16(d_tmem, a_desc0 + (kk >> 2) * a_block + in_block, b_desc0 + (kk >> 2) * b_block + in_block, idesc,
+                        (accumulate || kk != 0) ? 1u : 0u);
+            }
+        } else {
+#pragma unroll
+            for (int kk = 0; kk < TileLeftT::Cols / 16; ++kk) {
+                const uint32_t k0 = kk * 16;
+                const uint32_t a_off = (a_major == 0) ? (k0 >> 6) * a_pitch + (k0 & 63u) * 2u : k0 * 128u;
+                const uint32_t b_off = (b_major == 0) ? (k0 >> 6) * b_pitch + (k0 & 63u) * 2u : k0 * 128u;
+                mma_f16(d_tmem, a_desc0 + (a_off >> 4), b_desc0 + (b_off >> 4), idesc, (accumulate || kk != 0) ? 1u : 0u);
+            }
         }
         stamp(0x6001);
     }
