@@ -242,6 +242,15 @@ __device__ __noinline__ uint32_t tload_prepare_engine(unsigned long long addr, u
     if ((span_bytes & 127u) != 0) {
         return 0;
     }
+    {
+        // the tile must lie inside the arena (a copy by the engine past the block's shared memory would fault)
+        const uint32_t start = dst_smem - smem_u32(arena());
+        const uint32_t bytes = lines * span_bytes;
+        if (start > kArenaBytes || bytes > kArenaBytes - start) {
+            give_up(602);
+            return 0;
+        }
+    }
     // which registered matrix holds the address (all bounds are read at once: one round trip to shared memory)
     const uint32_t count = rs->count;
     // (independent loads, eight bytes each: the flag words that hold them are eight-byte aligned)
@@ -308,6 +317,10 @@ __device__ __forceinline__ void tload_impl(TileData &dst, GlobalData &src)
         const int chunks_per_line = span / kCE;
         const uint32_t base = b200::smem_u32(b200::arena() + dst.addr_);
         const uint32_t pitch = static_cast<uint32_t>(lines) * 128u;
+        if (!b200::tile_in_arena<TileType::Mat>(dst.addr_, pitch * static_cast<uint32_t>((span * sizeof(T) + 127) / 128))) {
+            b200::give_up(602); // the tile does not fit where it was assigned
+            return;
+        }
         // 16-byte asynchronous copies need 16-byte aligned sources; ragged rows are fetched element by element
         const bool aligned = ((reinterpret_cast<uintptr_t>(g) | static_cast<uintptr_t>(line_stride * sizeof(T))) & 15u) == 0 &&
                              !__isShared(g); // (a FIFO entry may lie in the block's own shared memory)
@@ -623,6 +636,10 @@ __device__ __forceinline__ void textract_impl(DstTileData &dst, SrcTileData &src
         const bool k_major = (DstTileData::Loc == TileType::Left) ? cols_contig : !cols_contig;
         if (b200::kPipeWarps && b200::tid_b() == 0) {
             b200::held_back()[14] = 1; // an operand tile written through the generic proxy
+        }
+        if (!b200::tile_in_arena<DstTileData::Loc>(dst.addr_, dst_pitch * static_cast<uint32_t>((chunks_per_line + 7) / 8))) {
+            b200::give_up(602); // the operand tile does not fit where it was assigned
+            return;
         }
         const uint8_t *s = b200::arena_of<TileType::Mat>() + src.addr_;
         uint8_t *d = b200::arena_of<DstTileData::Loc>() + dst.addr_;

@@ -75,7 +75,10 @@ constexpr int kNotAMember = 1 << 20; // thread index handed to threads outside t
 struct StatusRecord {
     int code;   // 0 ok, 4 = a wait gave up
     int block;  // block index that reported
-    int where;  // index of the flag waited for: ((src pipe * 8 + dst pipe) * 8 + event id); 512 + id for a cross-core flag
+    int where;  // index of the flag waited for: ((src pipe * 8 + dst pipe) * 8 + event id); 512 + id for a cross-core flag;
+                // 600 + n: an instruction that pipe_warps does not cover; 601: a TLOAD that the copy engine cannot do in
+                // a launch with engine_loads; 602: a tile assigned beyond the arena; 1024 + flag: a raise that waited for
+                // the previous one to be consumed; 1536 / 1537: the loading / preparing thread waiting for the other
     int detail; // src pipe * 16 + dst pipe
 };
 
@@ -103,6 +106,7 @@ struct Control {
 constexpr int kControlBytes = ((int)sizeof(Control) + 1023) / 1024 * 1024;
 static_assert(kControlBytes == 7 * 1024, "the control block is 7 KiB: the arena is the other 220 KiB");
 constexpr int kDefaultSmemBytes = 227 * 1024; // control (7 KiB) + 220 KiB arena; the buffer is declared 1 KiB aligned
+constexpr uint32_t kArenaBytes = kDefaultSmemBytes - kControlBytes;
 // scale tiles of the MX product (TileType::ScaleLeft / ScaleRight) have windows of their own at the end of the arena:
 // 4 KiB each (a program that uses them keeps its Right window below 212 KiB)
 constexpr uint32_t kScaleRightOffset = 212 * 1024;
@@ -178,6 +182,15 @@ __device__ __forceinline__ uint8_t *arena_of()
             return arena();
         }
     }
+}
+// Does a tile of `bytes` at offset `addr` of the window of `Loc` lie inside the arena?  Instructions that write whole
+// matrix tiles check this and report {4, block, 602} instead of writing past the block's shared memory (a tile
+// assigned beyond its window's room is a program error that would otherwise fault the GPU).
+template <TileType Loc>
+__device__ __forceinline__ bool tile_in_arena(uint32_t addr, uint32_t bytes)
+{
+    const uint32_t start = static_cast<uint32_t>(arena_of<Loc>() - arena()) + addr;
+    return start <= kArenaBytes && bytes <= kArenaBytes - start;
 }
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {

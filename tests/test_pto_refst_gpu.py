@@ -373,6 +373,30 @@ def test_wait_that_runs_out_reports_and_returns(refk):
     assert np.array_equal(host(y), host(x) + np.float32(3.0))
 
 
+def test_tile_assigned_beyond_the_arena_is_reported_not_written(refk):
+    """A staged tile whose storage would end past the block's shared memory: TLOAD checks before it copies, the block
+    reports {4, block, 602} and runs on; the next launch on the same context works."""
+    import pto_isa_b200 as pto
+    lib = pto.lib()
+    record = lib.pto_b200_status_record()
+    out = torch.zeros(4, dtype=torch.int32, device="cuda")
+    src = torch.ones(128, 128, dtype=torch.float16, device="cuda")
+    refk.pto_refk_tile_beyond_arena.argtypes = [ctypes.c_void_p] * 4
+    assert refk.pto_refk_tile_beyond_arena(_ptr(out), _ptr(src), _stream(), ctypes.c_void_p(record)) == 0
+    rec = (ctypes.c_int * 4)()
+    assert lib.pto_b200_device_status_ex(_stream(), rec) == 4
+    assert rec[0] == 4 and rec[1] == 0 and rec[2] == 602, list(rec)
+    torch.cuda.synchronize()
+    assert int(out[0]) == 4321  # the program ran to its end
+    assert pto.device_status() == 0
+    x = torch.randn(64, 64, device="cuda")
+    y = torch.zeros(64, 64, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    assert refk.pto_refk_typed_events(_ptr(y), _ptr(x), _stream(), _ptr(status)) == 0
+    assert refk.pto_refk_status(_stream(), _ptr(status)) == 0
+    assert np.array_equal(host(y), host(x) + np.float32(3.0))
+
+
 def test_typed_events_program(refk):
     """Event<SrcOp, DstOp>: `event = TXXX(...)` records, TXXX(..., event) waits (include/pto/common/event.hpp:110-152)."""
     x = torch.randn(64, 64, device="cuda")

@@ -49,11 +49,14 @@ def _ptr(t):
 @pytest.mark.parametrize("name,m,k,n", [("pto_refk_gemm_256x128x512", 256, 128, 512),
                                         ("pto_refk_gemm_1536", 1536, 1536, 1536),
                                         ("pto_refk_gemm_pw_256x128x512", 256, 128, 512),
+                                        ("pto_refk_gemm_pw_256x128x512_copies", 256, 128, 512),
                                         ("pto_refk_gemm_pw_1536", 1536, 1536, 1536)])
 def test_reference_gemm_tile_program(refk, name, m, k, n):
     """RunGemmE2E (TLOAD / TEXTRACT / TMATMUL / TMATMUL_ACC / TSTORE with its set_flag / wait_flag ping-pong),
     base tile 128 x 256, k step 64, B stored n x k.  The `pw` instances run the core's pipes on warps of their own
-    (loads, products and stores overlap as the program's flags allow; TEXTRACT hands out views)."""
+    (loads, products and stores overlap as the program's flags allow; TEXTRACT hands out views); `_copies` is that mode's
+    fallback through every instruction: nothing registered (cp.async loads by the copying warp), copying TEXTRACT, TSTORE
+    from registers."""
     r = np.random.default_rng(m + n)
     a = r.uniform(-1, 1, (m, k)).astype(np.float16)
     b = r.uniform(-1, 1, (n, k)).astype(np.float16)
