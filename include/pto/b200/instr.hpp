@@ -246,7 +246,8 @@ __device__ __noinline__ uint32_t tload_prepare_engine(unsigned long long addr, u
         // the tile must lie inside the arena (a copy by the engine past the block's shared memory would fault)
         const uint32_t start = dst_smem - smem_u32(arena());
         const uint32_t bytes = lines * span_bytes;
-        if (start > kArenaBytes || bytes > kArenaBytes - start) {
+        const uint32_t room = arena_bytes();
+        if (start > room || bytes > room - start) {
             give_up(602);
             return 0;
         }

@@ -53,6 +53,7 @@ constexpr int kWarps = kBlockThreads / 32;
 //   kModeViews     TEXTRACT / TMOV of an aligned window hands the operand tile a view of the staged tile (no copy)
 //   kModeEngineLoads every TLOAD is a copy by the copy engine, prepared ahead of time by a thread of its own
 constexpr int kModeInOrder = 1, kModePipeWarps = 2, kModeViews = 4, kModeEngineLoads = 8;
+constexpr int kModeTmemColsShift = 8; // bits 8..17: the tensor-memory columns the block allocates (LaunchOptions::tmem_cols)
 // kModePipeWarps is a property of the translation unit: define PTO_B200_PIPE_WARPS before including the PTO header and
 // every tile program of the unit runs with its pipes on warps of their own (LaunchOptions::pipe_warps must say the
 // same).  The instructions then know at compile time which threads execute them.
@@ -186,11 +187,19 @@ __device__ __forceinline__ uint8_t *arena_of()
 // Does a tile of `bytes` at offset `addr` of the window of `Loc` lie inside the arena?  Instructions that write whole
 // matrix tiles check this and report {4, block, 602} instead of writing past the block's shared memory (a tile
 // assigned beyond its window's room is a program error that would otherwise fault the GPU).
+// the arena of this launch: its dynamic shared memory less the control block (LaunchOptions::smem_bytes)
+__device__ __forceinline__ uint32_t arena_bytes()
+{
+    uint32_t total;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(total));
+    return total - static_cast<uint32_t>(kControlBytes);
+}
 template <TileType Loc>
 __device__ __forceinline__ bool tile_in_arena(uint32_t addr, uint32_t bytes)
 {
     const uint32_t start = static_cast<uint32_t>(arena_of<Loc>() - arena()) + addr;
-    return start <= kArenaBytes && bytes <= kArenaBytes - start;
+    const uint32_t room = arena_bytes();
+    return start <= room && bytes <= room - start;
 }
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -825,7 +834,7 @@ __device__ __forceinline__ void block_begin(unsigned long long wait_limit_ns, ui
     }
     if ((threadIdx.x >> 5) == (kPipeWarps ? kTmemWarp : 0)) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
-                     "r"(kTmemCols)
+                     "r"((mode >> kModeTmemColsShift) & 0x3ff)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -871,7 +880,8 @@ __device__ __forceinline__ void block_end(StatusRecord *status)
     }
     if ((threadIdx.x >> 5) == (kPipeWarps ? kTmemWarp : 0)) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(ctl->tmem_base), "r"(kTmemCols)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(ctl->tmem_base),
+                     "r"((ctl->mode >> kModeTmemColsShift) & 0x3ff)
                      : "memory");
     }
 }
@@ -914,6 +924,10 @@ struct LaunchOptions {
     // is not): the copies are then prepared ahead of time by a thread of their own (see load_ring), and the loading
     // thread only counts TLOADs and issues the prepared copies.  Needs pipe_warps and a registered matrix.
     bool engine_loads = false;
+    // Tensor-memory columns the block allocates (a power of two from 32 to 512: accumulator tiles live below it).  With
+    // 256 and at most half of the shared memory, two blocks share an SM (launch_two_per_sm): what one block's scalar
+    // threads leave idle, the other block's use.
+    int tmem_cols = kTmemCols;
 };
 
 // encodes the launch's registered matrices (host)
@@ -964,8 +978,8 @@ inline cudaError_t make_tma_table(const LaunchOptions &opt, TmaTable &table)
     return cudaSuccess;
 }
 
-template <typename Program>
-__global__ void __launch_bounds__(kBlockThreads, 1)
+template <typename Program, int kBlocksPerSm = 1>
+__global__ void __launch_bounds__(kBlockThreads, kBlocksPerSm)
     block_kernel(Program program, StatusRecord *status, unsigned long long wait_limit_ns, uint32_t l0a_offset,
                  uint32_t l0b_offset, int mode, uint32_t store_staging, const __grid_constant__ TmaTable tma)
 {
@@ -989,28 +1003,56 @@ __global__ void __launch_bounds__(kBlockThreads, 1)
 }
 
 // Launches `program` (a __device__ callable) on `blocks` thread blocks of the stream.
-template <typename Program>
-inline cudaError_t launch(uint32_t blocks, void *stream, Program program, const LaunchOptions &opt)
+template <int kBlocksPerSm, typename Program>
+inline cudaError_t launch_impl(uint32_t blocks, void *stream, Program program, const LaunchOptions &opt)
 {
     if (opt.pipe_warps != kPipeWarps || (opt.pipe_warps && opt.in_order)) {
         return cudaErrorInvalidValue; // pipe_warps is compiled in (PTO_B200_PIPE_WARPS) and excludes in_order
+    }
+    if (opt.tmem_cols < 32 || opt.tmem_cols > kTmemCols || (opt.tmem_cols & (opt.tmem_cols - 1)) != 0 ||
+        opt.smem_bytes <= kControlBytes || opt.smem_bytes > kDefaultSmemBytes) {
+        return cudaErrorInvalidValue;
     }
     TmaTable table;
     cudaError_t e = make_tma_table(opt, table);
     if (e != cudaSuccess) {
         return e;
     }
-    e = cudaFuncSetAttribute(block_kernel<Program>, cudaFuncAttributeMaxDynamicSharedMemorySize, opt.smem_bytes);
+    auto kernel = block_kernel<Program, kBlocksPerSm>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, opt.smem_bytes);
     if (e != cudaSuccess) {
         return e;
     }
-    block_kernel<Program><<<blocks, kBlockThreads, opt.smem_bytes, static_cast<cudaStream_t>(stream)>>>(
+    if (kBlocksPerSm > 1) {
+        // the whole of the SM's shared memory, so that two blocks fit side by side
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) {
+            return e;
+        }
+    }
+    kernel<<<blocks, kBlockThreads, opt.smem_bytes, static_cast<cudaStream_t>(stream)>>>(
         program, static_cast<StatusRecord *>(opt.status), opt.wait_limit_ns, opt.l0a_offset, opt.l0b_offset,
         (opt.in_order ? kModeInOrder : 0) | (kPipeWarps ? kModePipeWarps : 0) |
             (opt.pipe_warps && opt.extract_views ? kModeViews : 0) |
-            (opt.pipe_warps && opt.engine_loads && opt.tma_count > 0 ? kModeEngineLoads : 0),
+            (opt.pipe_warps && opt.engine_loads && opt.tma_count > 0 ? kModeEngineLoads : 0) |
+            (opt.tmem_cols << kModeTmemColsShift),
         opt.store_staging_offset, table);
     return cudaGetLastError();
+}
+template <typename Program>
+inline cudaError_t launch(uint32_t blocks, void *stream, Program program, const LaunchOptions &opt)
+{
+    return launch_impl<1>(blocks, stream, program, opt);
+}
+// The same with two blocks per SM: `opt.smem_bytes` at most half of an SM's shared memory (113 KiB) and
+// `opt.tmem_cols` at most 256; the kernel is compiled for at most 128 registers per thread.
+template <typename Program>
+inline cudaError_t launch_two_per_sm(uint32_t blocks, void *stream, Program program, const LaunchOptions &opt)
+{
+    if (opt.smem_bytes > 113 * 1024 || opt.tmem_cols > 256) {
+        return cudaErrorInvalidValue;
+    }
+    return launch_impl<2>(blocks, stream, program, opt);
 }
 template <typename Program>
 inline cudaError_t launch(uint32_t blocks, void *stream, Program program, void *status = nullptr,

@@ -70,7 +70,8 @@ def test_reference_gemm_tile_program(refk, name, m, k, n):
     assert ok, f"max relative error {worst:.3e}"
 
 
-@pytest.mark.parametrize("name", ["pto_refk_gemm_6144", "pto_refk_gemm_pw_6144", "pto_refk_gemm_pw_6144_k128"])
+@pytest.mark.parametrize("name", ["pto_refk_gemm_6144", "pto_refk_gemm_pw_6144", "pto_refk_gemm_pw_6144_k128",
+                                  "pto_refk_gemm_pw_6144_x2"])
 def test_reference_gemm_tile_program_6144(refk, name):
     import pto_isa_b200 as pto
     m = n = k = 6144
