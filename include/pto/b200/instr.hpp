@@ -731,7 +731,7 @@ PTO_INTERNAL void matmul_issue(TileAccT &c, TileLeftT &a, TileRightT &b, bool ac
     using AT = typename TileLeftT::DType;
     static_assert(TileLeftT::Cols % 16 == 0, "TMATMUL: k a multiple of 16");
 #if PTO_B200_DEVICE_CODE
-    if (control()->mode & kModeInOrder) {
+    if (!kPipeWarps && (control()->mode & kModeInOrder)) { // (in-order launches are not pipe-warps launches)
         // no flags order the operands' staging before the product: every thread's writes are made visible to the
         // tensor core here (in a program with flags, set_flag(PIPE_MTE1, PIPE_M, ...) does this)
         fence_async_proxy();
@@ -1043,7 +1043,7 @@ PTO_INTERNAL void matmul_mx_issue(TileRes &c, TileLeftT &a, TileLeftScaleT &sa, 
 #if PTO_B200_DEVICE_CODE
     constexpr int K = TileLeftT::Cols, N = TileRightT::Cols;
     constexpr int kSpans = (K + 127) / 128, kAtomsK = (K / 32 + 3) / 4, kGroupsN = (N + 127) / 128;
-    if (control()->mode & kModeInOrder) {
+    if (!kPipeWarps && (control()->mode & kModeInOrder)) { // (in-order launches are not pipe-warps launches)
         fence_async_proxy();
         b200::sync();
     }
@@ -1203,7 +1203,7 @@ __device__ __forceinline__ void tstore_impl(GlobalData &dst, TileData &src)
                                      : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
-                    if (control()->mode & kModeInOrder) {
+                    if (!kPipeWarps && (control()->mode & kModeInOrder)) { // (in-order launches are not pipe-warps launches)
                         asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
                     }
                 }

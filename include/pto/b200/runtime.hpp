@@ -1366,7 +1366,7 @@ namespace b200 {
 PTO_INTERNAL void complete_copies_if_in_order()
 {
 #if PTO_B200_DEVICE_CODE
-    if ((control()->mode & kModeInOrder)) {
+    if (!kPipeWarps && (control()->mode & kModeInOrder)) {
         asm volatile("cp.async.wait_all;" ::: "memory");
         __syncthreads();
     }
@@ -1375,7 +1375,7 @@ PTO_INTERNAL void complete_copies_if_in_order()
 PTO_INTERNAL void complete_matmul_if_in_order()
 {
 #if PTO_B200_DEVICE_CODE
-    if ((control()->mode & kModeInOrder)) {
+    if (!kPipeWarps && (control()->mode & kModeInOrder)) {
         // the flag (PIPE_M -> PIPE_ALL, 7) is kept for this; tile programs have no reason to name it
         set_flag(PIPE_M, PIPE_ALL, 7);
         wait_flag(PIPE_M, PIPE_ALL, 7);
