@@ -51,3 +51,16 @@ def test_both_libraries_export_the_gemm_program():
     assert "pto_refk_gemm_6144" in _symbols(refkernels.OUT)
     pw = _symbols(refkernels.OUT_PW)
     assert "pto_refk_gemm_pw_6144_k128" in pw and "pto_refk_gemm_pw_1536" in pw
+
+
+def test_launcher_library_defines_the_declared_templates():
+    """include/pto_b200_launchers.hpp declares the reference hosts' launcher templates; libpto_b200_launchers.so holds
+    the instances a host links against (checked by name, nothing is launched)."""
+    lib = os.path.join(os.path.dirname(refkernels.OUT), "libpto_b200_launchers.so")
+    if not os.path.exists(lib):
+        pytest.skip("libpto_b200_launchers.so has not been built")
+    syms = subprocess.run(["nm", "-DC", lib], capture_output=True, text=True, check=True).stdout
+    for name in ("void LaunchGEMME2E<unsigned short>(", "void LaunchTFA<", "LaunchTMATMUL<1>(", "LaunchTMATMUL<4>(",
+                 "LaunchTMATMULBIAS<5>(", "LaunchTROWMAX<", "LaunchTROWSUM<", "LaunchTExp<", "launchTCVT<",
+                 "LaunchTFLASHATTN(", "pto_b200_launcher_status"):
+        assert name in syms, name
