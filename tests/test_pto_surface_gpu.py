@@ -102,3 +102,16 @@ def test_reference_tcvt_tile_program(refk):
     assert refk.pto_refk_tcvt_f32_i32_128x128(_ptr(di), _ptr(dev(xi)), _stream()) == 0
     torch.cuda.synchronize()
     assert np.array_equal(host(di), port.tcvt_f32_i32(xi, 1))
+
+
+def test_vector_program_with_typed_events_on_pipe_warps(refk):
+    """TLOAD -> TADDS -> TSTORE ordered by three typed events, with the pipes on warps of their own: the load on the
+    loading thread and the copying warp, the vector instruction and the store on the vector / store warps (three blocks
+    run the same program: they write the same values)."""
+    x = torch.randn(64, 64, device="cuda")
+    y = torch.zeros(64, 64, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    assert refk.pto_refk_pw_typed_events(_ptr(y), _ptr(x), _stream(), _ptr(status)) == 0
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    assert np.array_equal(host(y), host(x) + np.float32(3.0))
