@@ -1416,9 +1416,108 @@ PTO_INTERNAL void pipe_barrier(pipe_t pipe)
 // issued so far on `pipe` is complete, wait_flag_dev(id) consumes one raise).  Here one thread block plays both roles
 // in program order, so a flag is a counter in the control block: the raise happens after the block's outstanding
 // copies and stores are complete, the wait is bounded like every other wait.
+#if PTO_B200_DEVICE_CODE
+namespace pto {
+namespace b200 {
+// pipe_warps: a cross-core flag is a count of raises (Control::dev_flags, never decremented) and, per team, a count of
+// the raises it has seen (flag words of PIPE_MTE1 -> PIPE_MTE1, behind the timeline's counters).  The core's scalar unit
+// stalls at wait_flag_dev on the NPU; here every team walks the instruction stream, so every team waits there, each
+// against its own count.
+__device__ __forceinline__ volatile uint8_t *dev_flags_seen(int team)
+{
+    return reinterpret_cast<volatile uint8_t *>(&control()->flags[flag_index(PIPE_MTE1, PIPE_MTE1, 0)]) + 12 + team * kNumDevFlags;
+}
+static_assert(12 + 3 * kNumDevFlags <= 64, "three teams' counts fit the eight flag words");
+// the team whose flags and cross-core waits this thread executes (-1: none)
+__device__ __forceinline__ int my_team()
+{
+    if (threadIdx.x == 0) {
+        return kTeamL;
+    }
+    if (threadIdx.x == kTeamBWarp * 32) {
+        return kTeamB;
+    }
+    return threadIdx.x >= kTeamCFirstWarp * 32 ? kTeamC : -1;
+}
+__device__ __noinline__ void raise_dev_flag_pipe_warps(pipe_t pipe, int id)
+{
+    if (!runs(pipe)) {
+        return;
+    }
+    Control *ctl = control();
+    const int team = team_of_pipe(pipe);
+    // everything issued so far on the pipe is complete, and visible to the other teams, before the raise
+    if (team == kTeamL) {
+        complete_loads();
+        __threadfence();
+        atomicAdd(&ctl->dev_flags[id], 1);
+    } else if (team == kTeamB) {
+        if (pipe == PIPE_M) {
+            set_flag(PIPE_M, PIPE_MTE1, 7); // (PIPE_M -> PIPE_MTE1, 7 is kept for this: the products are complete)
+            wait_flag(PIPE_M, PIPE_MTE1, 7);
+        }
+        __threadfence();
+        atomicAdd(&ctl->dev_flags[id], 1);
+    } else {
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); // staged stores of TSTORE have landed
+        __threadfence();
+        sync();
+        if (static_cast<int>(threadIdx.x) == team_first_thread(kTeamC)) {
+            atomicAdd(&ctl->dev_flags[id], 1);
+        }
+    }
+}
+__device__ __noinline__ void wait_dev_flag_pipe_warps(int id)
+{
+    const int team = my_team();
+    if (team < 0) {
+        return;
+    }
+    Control *ctl = control();
+    volatile uint8_t *seen = dev_flags_seen(team) + id;
+    const uint8_t have = *seen;
+    volatile int *flag = &ctl->dev_flags[id];
+    volatile int *abort_flag = &ctl->abort_flag;
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0; static_cast<uint8_t>(static_cast<uint8_t>(*flag) - have) == 0; ++i) {
+        if ((i & 0x3f) == 0x3f) {
+            if (*abort_flag) {
+                break;
+            }
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > ctl->wait_limit_ns) {
+                give_up(kNumFlags + id);
+                break;
+            }
+        }
+    }
+    if (team == kTeamC) {
+        sync(); // every thread of the team has read its count
+        if (static_cast<int>(threadIdx.x) == team_first_thread(kTeamC)) {
+            *seen = static_cast<uint8_t>(have + 1);
+        }
+        sync();
+    } else {
+        *seen = static_cast<uint8_t>(have + 1);
+    }
+    __threadfence();
+    if (held_back()[14] != 0) {
+        fence_async_proxy();
+    }
+}
+} // namespace b200
+} // namespace pto
+#endif
+
 PTO_INTERNAL void ffts_cross_core_sync(pipe_t pipe, uint64_t config)
 {
 #if PTO_B200_DEVICE_CODE
+    if constexpr (pto::b200::kPipeWarps) {
+        pto::b200::raise_dev_flag_pipe_warps(pipe, static_cast<int>((config >> 8) & 0xf));
+        return;
+    }
     (void)pipe;
     const int id = static_cast<int>((config >> 8) & 0xf);
     asm volatile("cp.async.wait_all;" ::: "memory");
@@ -1436,6 +1535,10 @@ PTO_INTERNAL void ffts_cross_core_sync(pipe_t pipe, uint64_t config)
 PTO_INTERNAL void wait_flag_dev(int id)
 {
 #if PTO_B200_DEVICE_CODE
+    if constexpr (pto::b200::kPipeWarps) {
+        pto::b200::wait_dev_flag_pipe_warps(id & 0xf);
+        return;
+    }
     pto::b200::Control *ctl = pto::b200::control();
     volatile int *flag = &ctl->dev_flags[id & 0xf];
     volatile int *abort_flag = &ctl->abort_flag;

@@ -127,7 +127,8 @@ def build(reference=None, force=False, verbose=False):
     if not os.path.isdir(os.path.join(reference, "kernels")):
         return OUT if os.path.exists(OUT) else None
     newest = max(max(os.path.getmtime(os.path.join(dp, f)) for dp, _, fs in os.walk(os.path.join(ROOT, "include", "pto"))
-                     for f in fs), os.path.getmtime(WRAPPER), os.path.getmtime(WRAPPER_PW))
+                     for f in fs), os.path.getmtime(WRAPPER), os.path.getmtime(WRAPPER_PW),
+                 os.path.getmtime(os.path.join(HERE, "csrc", "refkernels", "ref_fa_head.inc")))
     if not force and all(os.path.exists(o) and os.path.getmtime(o) >= newest for o in (OUT, OUT_PW)):
         return OUT
     build_dir = os.path.join(HERE, "build", "refkernels")
@@ -141,6 +142,7 @@ def build(reference=None, force=False, verbose=False):
             text = rewrite_core_statics(rewrite_launches(f.read()))
         with open(os.path.join(build_dir, name), "w") as f:
             f.write(text)
+    shutil.copyfile(os.path.join(HERE, "csrc", "refkernels", "ref_fa_head.inc"), os.path.join(build_dir, "ref_fa_head.inc"))
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     fa_kernel_check(reference, build_dir, nvcc, verbose)
     extra = os.environ.get("PTO_B200_REFK_NVCC_FLAGS", "").split()  # e.g. -DPTO_B200_TIMELINE, -DPTO_B200_TRACE_WAITS

@@ -311,12 +311,25 @@ def _newton_inv_sqrt(x):
     return np.float32(1.0) / g
 
 
+@pytest.fixture(scope="module")
+def refk_pw():
+    so = _SO.replace("refkernels.so", "refkernels_pw.so")
+    if not os.path.exists(so):
+        pytest.skip("libpto_b200_refkernels_pw.so has not been built (needs the reference tree at build time)")
+    return ctypes.CDLL(so)
+
+
+@pytest.mark.parametrize("pipe_warps", [0, 1], ids=["one_stream", "pipe_warps"])
 @pytest.mark.parametrize("fifo", [0, 1], ids=["gm_fifo", "smem_fifo"])
 @pytest.mark.parametrize("causal", [0, 1])
 @pytest.mark.parametrize("s0,s1", [(32, 64), (64, 256), (128, 128)])
-def test_reference_fa_macros_one_head(refk, s0, s1, causal, fifo):
+def test_reference_fa_macros_one_head(refk, refk_pw, s0, s1, causal, fifo, pipe_warps):
+    """One attention head built from pto_macro_matmul / pto_macro_fa_softmax / pto_macro_fa_gu and three TPipe rings
+    (TPUSH / TPOP with cross-core flags), once with every thread on one instruction stream and once with the pipes on
+    warps of their own (the cross-core flags are then counts that each team of warps waits on)."""
     if causal and s0 != s1:
         pytest.skip("the causal mask of the macros assumes a square problem")
+    entry = refk_pw.pto_refk_pw_fa_head if pipe_warps else refk.pto_refk_fa_head
     d = 128
     r = np.random.default_rng(s0 + s1 + causal)
     q = r.standard_normal((s0, d)).astype(np.float16)
@@ -328,14 +341,15 @@ def test_reference_fa_macros_one_head(refk, s0, s1, causal, fifo):
     p_ws = torch.zeros(blocks * 2 * 32 * 64, dtype=torch.float16, device="cuda")
     pv_ws = torch.zeros(blocks * 2 * 32 * 128, device="cuda")
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
-    assert refk.pto_refk_fa_head(_ptr(o), _ptr(dev(q)), _ptr(dev(k)), _ptr(dev(v)), s0, s1, causal, fifo, _ptr(qk_ws),
-                                 _ptr(p_ws), _ptr(pv_ws), _stream(), _ptr(status)) == 0
+    assert entry(_ptr(o), _ptr(dev(q)), _ptr(dev(k)), _ptr(dev(v)), s0, s1, causal, fifo, _ptr(qk_ws), _ptr(p_ws),
+                 _ptr(pv_ws), _stream(), _ptr(status)) == 0
     assert refk.pto_refk_status(_stream(), _ptr(status)) == 0, host(status)
     scale = float(_newton_inv_sqrt(d))
     # non-causal: the oracle's streaming formulation with the program's key tile; causal: its plain formulation (the
     # streaming one models the reference kernel's 128-row query blocks, which this program's 32-row blocks are not)
     want = port.attn_head_f16(q, k, v, 1, scale) if causal else port.fa_tiled_f16(q, k, v, 0, scale, tile_s1=64)
-    ok, worst = rel_err_ok(host(o), want, 2e-3, label=f"fa macros + pipes s0={s0} s1={s1} causal={causal} fifo={fifo}")
+    ok, worst = rel_err_ok(host(o), want, 2e-3,
+                           label=f"fa macros + pipes s0={s0} s1={s1} causal={causal} fifo={fifo} pipe_warps={pipe_warps}")
     assert ok, f"max relative error {worst:.3e}"
 
 

@@ -50,7 +50,7 @@ def test_both_libraries_export_the_gemm_program():
         pytest.skip("libpto_b200_refkernels*.so have not been built")
     assert "pto_refk_gemm_6144" in _symbols(refkernels.OUT)
     pw = _symbols(refkernels.OUT_PW)
-    assert "pto_refk_gemm_pw_6144_k128" in pw and "pto_refk_gemm_pw_1536" in pw
+    assert "pto_refk_gemm_pw_6144_k128" in pw and "pto_refk_gemm_pw_1536" in pw and "pto_refk_pw_fa_head" in pw
 
 
 def test_launcher_library_defines_the_declared_templates():
