@@ -381,11 +381,34 @@ def gemm_size_sweep(torch, pto, peaks):
             pto.gemm(a[j], b[j], 1, out=c[j])
 
         ms = bench_loop(torch, fn, 5, 20)
+        note = f"{sets} rotating operand sets, 20 launches"
+        eager_ms = None
+        if ms < 0.04:
+            # the launch is shorter than the host's time for one call through the Python layer (about 17 us): the same
+            # 20 launches replayed from one CUDA graph time the kernel, the eager figure is kept beside it
+            eager_ms = ms
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for _ in range(20):
+                    fn()
+            graph.replay()
+            torch.cuda.synchronize()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            graph.replay()
+            s1.record()
+            torch.cuda.synchronize()
+            ms = s0.elapsed_time(s1) / 20
+            note += " replayed from one CUDA graph"
+            del graph
         tf = 2.0 * size ** 3 / ms / 1e9
         out.append({"workload": f"gemm_f16f32 m=n=k={size}, B stored n x k", "value": tf, "unit": "TFLOP/s", "ms": ms,
                     "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                                  "frac": tf / peaks["bf16_tflops"], "frac_of_nominal_2250": tf / 2250.0,
-                                 "note": f"{sets} rotating operand sets, 20 launches"}})
+                                 "note": note}})
+        if eager_ms is not None:
+            out[-1]["eager_ms_per_call"] = eager_ms
         del a, b, c
     return out
 

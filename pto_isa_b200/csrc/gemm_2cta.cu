@@ -22,23 +22,21 @@ namespace pto_b200 {
 namespace {
 
 constexpr int BM = 128;       // rows of A / C per block (256 per pair)
-constexpr int BN = 256;       // columns of C per pair
-constexpr int BNH = 128;      // columns of B staged per block
+// Columns of C per pair (kBN): 256, or 128 for problems whose 256-wide tiles would leave block pairs idle
+// (launch_pair_auto); a block stages kBN / 2 columns of B.
 #ifndef PTO_B200_GEMM2_BK
 #define PTO_B200_GEMM2_BK 128
 #endif
 constexpr int BK = PTO_B200_GEMM2_BK; // k extent of a stage: BK / 16 MMAs per full/empty barrier round trip
 constexpr int kBoxK = 64;             // k extent of one TMA box (128 bytes, the swizzle span)
-constexpr int kStages = (192 * 1024) / ((BM + BNH) * BK * 2);
-constexpr int kABytes = BM * BK * 2;  // 16 KiB
-constexpr int kBBytes = BNH * BK * 2; // 16 KiB
-constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kABytes = BM * BK * 2;  // 32 KiB for a 128-deep k step
+constexpr int kMaxStages = 4;
 constexpr int kThreads = 192; // warp 0 TMA, warp 1 MMA (leader only), warps 2..5 epilogue
 constexpr int kTmemCols = 512;
 
 struct Control {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint32_t tmem_base;
@@ -50,7 +48,17 @@ struct Control {
 // lines issued by one instruction instead of 32 row-strided stores per register.
 constexpr int kSlabBytes = 32 * 32 * 4;
 constexpr int kStagingBytes = 4 * 2 * kSlabBytes;
-constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + sizeof(Control) + 1024;
+// what follows from the tile width
+template <int kBN>
+struct Shape {
+    static constexpr int BN = kBN;
+    static constexpr int BNH = kBN / 2;                                           // columns of B staged per block
+    static constexpr int kStages = (192 * 1024) / ((BM + BNH) * BK * 2);          // 3 (256 wide) or 4 (128 wide)
+    static constexpr int kBBytes = BNH * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + static_cast<int>(sizeof(Control)) + 1024;
+    static_assert(kStages >= 2 && kStages <= kMaxStages && BNH % 64 == 0, "tile width");
+};
 
 // C tiles are walked in bands of kGroupN tile columns; inside a band the tile column moves fastest, then the
 // tile row, so that the tiles in flight at any time (one per block pair: 74 tiles = about nine tile rows of a
@@ -180,12 +188,14 @@ __host__ __device__ constexpr uint32_t make_idesc_i8(int m, int n)
 // accumulator words go out bit for bit, as in the float form.  Bits 3-4 = 16-bit output: the accumulator is rounded
 // (nearest even) to fp16 (1) or bf16 (2) before it is stored, the conversion TSTORE offers on the way out of the
 // accumulator (docs/isa/TSTORE.md:67-72 in the reference).
-template <int kMode>
+template <int kMode, int kBN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_c, int c_by_tma, float *__restrict__ c,
                     const float *__restrict__ bias, int m, int n, int k, DeviceStatus *status)
 {
+    constexpr int BN = Shape<kBN>::BN, BNH = Shape<kBN>::BNH, kStages = Shape<kBN>::kStages;
+    constexpr int kStageBytes = Shape<kBN>::kStageBytes;
     constexpr int kBLayout = kMode & 1;
     constexpr bool kBias = (kMode & 2) != 0;
     constexpr bool kInt8 = (kMode & 4) != 0;
@@ -518,9 +528,10 @@ namespace {
 
 // One launcher for every instance of the kernel.  kMode: bit 0 B stored n x k, bit 1 bias, bit 2 int8 operands (k
 // counts 16-bit pairs), bits 3-4 output type (0 fp32 / int32, 1 fp16, 2 bf16), bit 5 bfloat16 operands.
-template <int kMode>
-int launch_pair(const void *a, const void *b, void *c, const float *bias, int m, int n, int k, cudaStream_t stream)
+template <int kMode, int kBN>
+int launch_pair_bn(const void *a, const void *b, void *c, const float *bias, int m, int n, int k, cudaStream_t stream)
 {
+    constexpr int BN = Shape<kBN>::BN, BNH = Shape<kBN>::BNH, kSmemBytes = Shape<kBN>::kSmemBytes;
     constexpr bool kBnk = (kMode & 1) != 0;
     constexpr int kOutBytes = ((kMode >> 3) & 3) == 0 ? 4 : 2;
     CUtensorMap tmap_a, tmap_b, tmap_c;
@@ -550,12 +561,33 @@ int launch_pair(const void *a, const void *b, void *c, const float *bias, int m,
     if (status == nullptr) {
         return kErrCuda;
     }
-    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm2_f16f32_kernel<kMode>), kSmemBytes)) != kOk) {
+    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void *>(&gemm2_f16f32_kernel<kMode, kBN>), kSmemBytes)) != kOk) {
         return rc;
     }
-    gemm2_f16f32_kernel<kMode><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma,
-                                                                             static_cast<float *>(c), bias, m, n, k, status);
+    gemm2_f16f32_kernel<kMode, kBN><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, tmap_c, c_by_tma,
+                                                                                  static_cast<float *>(c), bias, m, n, k, status);
     return check_launch();
+}
+
+// The tile width follows the problem: 256 columns per block pair unless 128 finish sooner.  A pass over the tile list
+// costs (tiles / pairs, rounded up) tile times, and a 128-wide tile takes half as long as a 256-wide one but pulls half
+// as much again from L2 per FLOP, so the narrow tile is chosen only where it saves at least a tenth (in practice:
+// problems with fewer 256-wide tiles than block pairs, such as 1536^3 with 36 tiles on 74 pairs).
+// PTO_B200_GEMM2_BN=128 / 256 forces a width.
+template <int kMode>
+int launch_pair(const void *a, const void *b, void *c, const float *bias, int m, int n, int k, cudaStream_t stream)
+{
+    static const int forced = [] {
+        const char *e = getenv("PTO_B200_GEMM2_BN");
+        return e != nullptr ? atoi(e) : 0;
+    }();
+    const long long pairs = sm_count() / 2 > 0 ? sm_count() / 2 : 1;
+    const long long rows = (m + 2 * BM - 1) / (2 * BM);
+    const long long waves_wide = (rows * ((n + 255) / 256) + pairs - 1) / pairs;
+    const long long waves_narrow = (rows * ((n + 127) / 128) + pairs - 1) / pairs;
+    const bool narrow = forced == 128 || (forced != 256 && waves_narrow * 11 < waves_wide * 20);
+    return narrow ? launch_pair_bn<kMode, 128>(a, b, c, bias, m, n, k, stream)
+                  : launch_pair_bn<kMode, 256>(a, b, c, bias, m, n, k, stream);
 }
 
 } // namespace
