@@ -912,7 +912,7 @@ def run_gpu_arm(args):
                 "peak_kind": f"{peak_kind} cuBLAS bf16 8192^3, " + ("sustained loop" if timed_s >= 0.8 else "burst") +
                              f" (the timed region lasts {timed_s:.2f} s)",
                 "frac_of_burst": achieved / peaks["bf16_tflops"],
-                "frac_of_nominal_2250": achieved / 2250.0, "kernel": "gemm2_f16f32_kernel<1>",
+                "frac_of_nominal_2250": achieved / 2250.0, "kernel": "gemm2_f16f32_kernel<1, 256>",
                 "avg_launch_ms": avg_launch_ms, "algorithmic_flops_per_launch": FLOPS_PER_PROBLEM,
                 "isolated_10_launches_tflops": iso_tf, "isolated_frac_of_burst": iso_tf / peaks["bf16_tflops"],
                 "block_stamps_last_launch": block_stamps,
