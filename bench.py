@@ -610,6 +610,9 @@ def extras(torch, pto, peaks, peak_kind):
             "sector_gbs": n * 32 / probe_ms / 1e6,
             "note": "16M random 4-byte reads of the 64 MiB table alone; TGATHER does these plus 128 MB of index and output"}
         gather["roofline"]["frac_of_random_read_ceiling"] = probe_ms / gather["ms"]
+        # the same comparison in sectors through L2: TGATHER moves the probe's sectors plus its index and output streams
+        gather["roofline"]["l2_sector_gbs"] = n * (32 + 8) / gather["ms"] / 1e6
+        gather["roofline"]["frac_of_ceiling_in_l2_sectors"] = (n * (32 + 8) / gather["ms"]) / (n * 32 / probe_ms)
     except Exception as exc:
         out[-1]["roofline"]["probe_note"] = str(exc)[:120]
     out.extend(tile_program_gemm(torch, peaks, peak_kind))
