@@ -27,9 +27,8 @@ constexpr int BM = 128;       // rows of A / C per block (256 per pair)
 #ifndef PTO_B200_GEMM2_BK
 #define PTO_B200_GEMM2_BK 128
 #endif
-constexpr int BK = PTO_B200_GEMM2_BK; // k extent of a stage: BK / 16 MMAs per full/empty barrier round trip
-constexpr int kBoxK = 64;             // k extent of one TMA box (128 bytes, the swizzle span)
-constexpr int kABytes = BM * BK * 2;  // 32 KiB for a 128-deep k step
+constexpr int kBaseBK = PTO_B200_GEMM2_BK; // k extent of a stage of the 256-column instance
+constexpr int kBoxK = 64;                  // k extent of one TMA box (128 bytes, the swizzle span)
 constexpr int kMaxStages = 4;
 constexpr int kThreads = 192; // warp 0 TMA, warp 1 MMA (leader only), warps 2..5 epilogue
 constexpr int kTmemCols = 512;
@@ -53,7 +52,12 @@ template <int kBN>
 struct Shape {
     static constexpr int BN = kBN;
     static constexpr int BNH = kBN / 2;                                           // columns of B staged per block
-    static constexpr int kStages = (192 * 1024) / ((BM + BNH) * BK * 2);          // 3 (256 wide) or 4 (128 wide)
+    // k extent of a stage = BK / 16 products per full / empty barrier round trip.  A stage of the narrow instance is
+    // twice as deep: its products take half as long, and the per-stage costs of the loading and the issuing thread
+    // (about 580 and 320 cycles) hide behind 1024 cycles of products, not behind 512.
+    static constexpr int BK = (kBN == 128) ? 2 * kBaseBK : kBaseBK;
+    static constexpr int kABytes = BM * BK * 2;
+    static constexpr int kStages = (192 * 1024) / ((BM + BNH) * BK * 2);          // 3 (256 wide) or 2 (128 wide)
     static constexpr int kBBytes = BNH * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + static_cast<int>(sizeof(Control)) + 1024;
@@ -195,7 +199,7 @@ gemm2_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const float *__restrict__ bias, int m, int n, int k, DeviceStatus *status)
 {
     constexpr int BN = Shape<kBN>::BN, BNH = Shape<kBN>::BNH, kStages = Shape<kBN>::kStages;
-    constexpr int kStageBytes = Shape<kBN>::kStageBytes;
+    constexpr int BK = Shape<kBN>::BK, kABytes = Shape<kBN>::kABytes, kStageBytes = Shape<kBN>::kStageBytes;
     constexpr int kBLayout = kMode & 1;
     constexpr bool kBias = (kMode & 2) != 0;
     constexpr bool kInt8 = (kMode & 4) != 0;
@@ -531,7 +535,7 @@ namespace {
 template <int kMode, int kBN>
 int launch_pair_bn(const void *a, const void *b, void *c, const float *bias, int m, int n, int k, cudaStream_t stream)
 {
-    constexpr int BN = Shape<kBN>::BN, BNH = Shape<kBN>::BNH, kSmemBytes = Shape<kBN>::kSmemBytes;
+    constexpr int BN = Shape<kBN>::BN, BNH = Shape<kBN>::BNH, BK = Shape<kBN>::BK, kSmemBytes = Shape<kBN>::kSmemBytes;
     constexpr bool kBnk = (kMode & 1) != 0;
     constexpr int kOutBytes = ((kMode >> 3) & 3) == 0 ? 4 : 2;
     CUtensorMap tmap_a, tmap_b, tmap_c;
