@@ -213,3 +213,45 @@ def test_gemm_bf16_operands(mnk, b_layout):
     ok, worst = rel_err_ok(got, want, 2e-3)
     assert ok, f"max relative error {worst:.3e}"
     assert pto.device_status() == 0
+
+
+_WIDTH_SCRIPT = r"""
+import random, sys, torch
+import pto_isa_b200 as pto
+random.seed(11)
+for it in range(36):
+    m = random.choice([1, 7, 64, 100, 128, 129, 200, 256, 257, 384, 500, 777, 1024])
+    n = random.choice([8, 16, 64, 72, 120, 128, 136, 192, 256, 264, 400, 512, 1000])
+    k = random.choice([8, 16, 64, 72, 128, 136, 248, 256, 264, 512, 520, 1032])
+    lay = random.choice([0, 1])
+    a = (torch.rand(m, k, device="cuda") * 2 - 1).half()
+    b = ((torch.rand(k, n, device="cuda") if lay == 0 else torch.rand(n, k, device="cuda")) * 2 - 1).half()
+    c = torch.full((m, n), float("nan"), device="cuda")
+    pto.gemm(a, b, lay, out=c)
+    ref = a.double() @ (b.double() if lay == 0 else b.double().t())
+    err = float(((c.double() - ref).abs().max() / max(float(ref.abs().max()), 1e-6)))
+    assert err < 2e-3 and not bool(torch.isnan(c).any()), (m, n, k, lay, err)
+# 16-bit output, bias and int8 go through the same launcher
+a = (torch.rand(300, 264, device="cuda") * 2 - 1).half(); b = (torch.rand(200, 264, device="cuda") * 2 - 1).half()
+c16 = pto.gemm_out16(a, b, 1)
+assert torch.equal(c16, pto.gemm(a, b, 1).half())
+bias = torch.rand(200, device="cuda")
+assert torch.allclose(pto.gemm(a, b, 1, bias=bias), pto.gemm(a, b, 1) + bias, rtol=0, atol=1e-5)
+ai = torch.randint(-128, 128, (130, 272), device="cuda", dtype=torch.int8); bi = torch.randint(-128, 128, (72, 272), device="cuda", dtype=torch.int8)
+assert torch.equal(pto.gemm_i8(ai, bi).cpu().long(), ai.cpu().long() @ bi.cpu().long().t())
+assert pto.device_status() == 0
+print("ok")
+"""
+
+
+@pytest.mark.parametrize("width", ["128", "256"])
+def test_gemm_both_tile_widths_on_ragged_shapes(width):
+    """The block-pair kernel chooses 256- or 128-column tiles by problem size (launch_pair in csrc/gemm_2cta.cu).
+    PTO_B200_GEMM2_BN, read once per process, forces one: 36 seeded shapes with ragged m, n, k in both layouts of B, plus
+    the 16-bit output, the bias form and int8, run in a child process on each width against a float64 product."""
+    import subprocess
+    import sys
+    env = dict(os.environ, PTO_B200_GEMM2_BN=width)
+    env["PYTHONPATH"] = os.pathsep.join([os.path.dirname(os.path.dirname(os.path.abspath(__file__))), env.get("PYTHONPATH", "")])
+    r = subprocess.run([sys.executable, "-c", _WIDTH_SCRIPT], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stdout[-2000:] + r.stderr[-2000:]
