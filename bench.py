@@ -359,6 +359,42 @@ def sharded_attention(torch, pto, dist, world, rank, barrier, iters=20):
         res["bytes_gathered_per_gpu"] = nbytes
         res["allgather_recv_gbs_per_gpu"] = nbytes * (world - 1) / world / ag / 1e6
         res["value_with_allgather"] = flops / (ms + ag) / 1e9
+        # overlapped: the rank's heads go in four launches and each quarter's output is gathered on a second stream while
+        # the next quarter is computed (quarter-major result: every gather writes one contiguous block)
+        parts = 4
+        if mine % parts == 0 and mine >= parts:
+            qh = mine // parts
+            full_q = torch.empty(parts, world, qh, S, D, dtype=torch.float16, device="cuda")
+            comm = torch.cuda.Stream()
+            times = []
+            for it in range(4):
+                barrier()
+                o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                o0.record()
+                works = []
+                for c in range(parts):
+                    sl = slice(c * qh, (c + 1) * qh)
+                    pto.flash_attn_fwd(q[sl], k[sl], v[sl], causal=True, scale=1.0, out=o[sl])
+                    done = torch.cuda.Event()
+                    done.record()
+                    comm.wait_event(done)
+                    with torch.cuda.stream(comm):
+                        works.append(dist.all_gather_into_tensor(full_q[c], o[sl], async_op=True))
+                for w in works:
+                    w.wait()
+                torch.cuda.current_stream().wait_stream(comm)
+                o1.record()
+                barrier()
+                to = torch.tensor([o0.elapsed_time(o1)], device="cuda", dtype=torch.float64)
+                dist.all_reduce(to, op=dist.ReduceOp.MAX)
+                if it > 0:
+                    times.append(float(to.item()))
+            ov = statistics.median(times)
+            res["overlapped_ms"] = ov
+            res["overlapped_ms_all"] = times
+            res["value_overlapped"] = flops / ov / 1e9
+            res["overlapped_note"] = f"{parts} launches of {qh} heads per GPU, each quarter gathered while the next is computed"
+            del full_q
     del q, k, v, o
     torch.cuda.empty_cache()
     return res
@@ -666,6 +702,8 @@ def compact_summary(line):
     sm["attn_sharded_tflops"] = r0(sa.get("value"))
     if sa.get("value_with_allgather") is not None:
         sm["attn_sharded_with_allgather"] = r0(sa["value_with_allgather"])
+    if sa.get("value_overlapped") is not None:
+        sm["attn_overlapped_allgather_tflops"] = r0(sa["value_overlapped"])
     wa = line.get("with_allgather")
     if wa:
         sm["gemm_with_allgather_tflops"] = r0(wa["value"])
