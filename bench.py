@@ -697,6 +697,9 @@ def compact_summary(line):
     r0 = lambda x: None if x is None else round(float(x), 1)
     sm = {"gemm6144_tflops": r0(line["roofline"]["achieved"]), "gemm_frac_sustained": r3(line["roofline"]["frac"]),
           "gemm_frac_burst_isolated": r3(line["roofline"].get("isolated_frac_of_burst")),
+          "gemm_best_launch": [r0(line["roofline"].get("best_single_launch_of_10_tflops")),
+                               r3(line["roofline"].get("best_single_launch_frac_of_burst")),
+                               r3(line["roofline"].get("best_single_launch_frac_of_library"))],
           "e2e_tflops": r0(line["e2e"]["value"])}
     sa = line.get("sharded_attention") or {}
     sm["attn_sharded_tflops"] = r0(sa.get("value"))
@@ -732,7 +735,8 @@ def compact_summary(line):
                 sm[key].append(r3(row["roofline"]["frac_of_library"]))
             if key == "tgather" and row["roofline"].get("frac_of_random_read_ceiling") is not None:
                 sm[key].append(r3(row["roofline"]["frac_of_random_read_ceiling"]))
-    sm["legend"] = "[value, frac of measured peak(, frac of vendor library | of random-read ceiling)]"
+    sm["legend"] = ("[value, frac of measured peak(, frac of vendor library | of random-read ceiling)]; gemm_best_launch: "
+                    "best of 10 single launches, the method of the measured burst peak, and the same for cuBLAS at 6144^3")
     return sm
 
 
@@ -787,6 +791,34 @@ def run_gpu_arm(args):
     barrier()
     time.sleep(1.0)
     iso_ms = bench_loop(torch, lambda: pto.gemm(a[0], b[0], 1, out=c[0]), 0, 10)
+
+    # ---- the burst peak of MEASURED_PEAKS.json is a best of ten single launches: the same method on this kernel, and
+    # on the vendor library with the same operands (fp16 output: torch offers no fp32 output for fp16 operands)
+    def best_single_launch(fn, n=10):
+        best = float("inf")
+        for _ in range(n):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            best = min(best, s.elapsed_time(e))
+        return best
+
+    barrier()
+    time.sleep(1.0)
+    iso_best_ms = best_single_launch(lambda: pto.gemm(a[0], b[0], 1, out=c[0]))
+    lib_best_ms = None
+    if world == 1:
+        try:
+            bt = b[0].t()
+            for _ in range(3):
+                torch.matmul(a[0], bt)
+            torch.cuda.synchronize()
+            time.sleep(1.0)
+            lib_best_ms = best_single_launch(lambda: torch.matmul(a[0], bt))
+        except Exception:
+            lib_best_ms = None
 
     for _ in range(max(args.warmup, 3)):
         for _ in range(R):
@@ -956,6 +988,11 @@ def run_gpu_arm(args):
                 "frac_of_nominal_2250": achieved / 2250.0, "kernel": "gemm2_f16f32_kernel<1, 256>",
                 "avg_launch_ms": avg_launch_ms, "algorithmic_flops_per_launch": FLOPS_PER_PROBLEM,
                 "isolated_10_launches_tflops": iso_tf, "isolated_frac_of_burst": iso_tf / peaks["bf16_tflops"],
+                "best_single_launch_of_10_tflops": FLOPS_PER_PROBLEM / iso_best_ms / 1e9,
+                "best_single_launch_frac_of_burst": FLOPS_PER_PROBLEM / iso_best_ms / 1e9 / peaks["bf16_tflops"],
+                "library_best_single_launch_of_10_tflops": (FLOPS_PER_PROBLEM / lib_best_ms / 1e9) if lib_best_ms else None,
+                "best_single_launch_frac_of_library": (lib_best_ms / iso_best_ms) if lib_best_ms else None,
+                "library_note": "torch.matmul (cuBLAS) on the same fp16 operands with fp16 output, same method, same process",
                 "block_stamps_last_launch": block_stamps,
                 "tflops_per_ghz": (achieved / (block_stamps["sm_mhz_median"] / 1e3)) if block_stamps else None}
     cpu = None
