@@ -697,6 +697,7 @@ def compact_summary(line):
     r0 = lambda x: None if x is None else round(float(x), 1)
     sm = {"gemm6144_tflops": r0(line["roofline"]["achieved"]), "gemm_frac_sustained": r3(line["roofline"]["frac"]),
           "gemm_frac_burst_isolated": r3(line["roofline"].get("isolated_frac_of_burst")),
+          "gemm_frac_of_cublas_sustained_same_operands": r3(line["roofline"].get("frac_of_library_sustained")),
           "gemm_best_launch": [r0(line["roofline"].get("best_single_launch_of_10_tflops")),
                                r3(line["roofline"].get("best_single_launch_frac_of_burst")),
                                r3(line["roofline"].get("best_single_launch_frac_of_library"))],
@@ -864,6 +865,46 @@ def run_gpu_arm(args):
     avg_launch_ms = sum(per_pass) / len(per_pass) / P
     block_stamps = stamps_summary(torch, stamps, 2 * (torch.cuda.get_device_properties(local_rank).multi_processor_count // 2))
 
+    # the vendor library in the same regime, right after the timed region (the GPU is as warm as it was in it): the same
+    # passes over the same operands through torch.matmul (cuBLAS; fp16 output, torch offers no fp32 one), as many
+    # launches as half a second takes
+    lib_sustained = None
+    if world == 1:
+        try:
+            bts = [b[i].t() for i in range(P)]
+            outs16 = [torch.empty(M, N, dtype=torch.float16, device="cuda") for _ in range(P)]
+            for i in range(P):
+                torch.matmul(a[i], bts[i], out=outs16[i])
+            torch.cuda.synchronize()
+            lib_passes = max(1, int(0.5 / (avg_launch_ms * P / 1e3)))
+            l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            l0.record()
+            for _ in range(lib_passes):
+                for i in range(P):
+                    torch.matmul(a[i], bts[i], out=outs16[i])
+            l1.record()
+            torch.cuda.synchronize()
+            lib_ms = l0.elapsed_time(l1) / (lib_passes * P)
+            # like for like: this repository's kernel with the same fp16 output (pto_b200_gemm_f16_out16), same loop
+            for i in range(P):
+                pto.gemm_out16(a[i], b[i], 1, out=outs16[i])
+            torch.cuda.synchronize()
+            l0.record()
+            for _ in range(lib_passes):
+                for i in range(P):
+                    pto.gemm_out16(a[i], b[i], 1, out=outs16[i])
+            l1.record()
+            torch.cuda.synchronize()
+            own16_ms = l0.elapsed_time(l1) / (lib_passes * P)
+            lib_sustained = {"tflops": FLOPS_PER_PROBLEM / lib_ms / 1e9, "ms_per_launch": lib_ms,
+                             "launches": lib_passes * P,
+                             "note": "torch.matmul (cuBLAS), same operands, fp16 output, run right after the timed region",
+                             "own_fp16_output_tflops": FLOPS_PER_PROBLEM / own16_ms / 1e9,
+                             "own_fp16_output_frac_of_library": lib_ms / own16_ms}
+            del bts, outs16
+        except Exception as exc:
+            lib_sustained = {"note": str(exc)[:160]}
+
     # all-gather of the outputs (every GPU ends up with every C): after the pass, and overlapped with it
     with_allgather = None
     if dist is not None:
@@ -993,6 +1034,8 @@ def run_gpu_arm(args):
                 "library_best_single_launch_of_10_tflops": (FLOPS_PER_PROBLEM / lib_best_ms / 1e9) if lib_best_ms else None,
                 "best_single_launch_frac_of_library": (lib_best_ms / iso_best_ms) if lib_best_ms else None,
                 "library_note": "torch.matmul (cuBLAS) on the same fp16 operands with fp16 output, same method, same process",
+                "library_sustained": lib_sustained,
+                "frac_of_library_sustained": (achieved / lib_sustained["tflops"]) if lib_sustained and lib_sustained.get("tflops") else None,
                 "block_stamps_last_launch": block_stamps,
                 "tflops_per_ghz": (achieved / (block_stamps["sm_mhz_median"] / 1e3)) if block_stamps else None}
     cpu = None
